@@ -1,0 +1,409 @@
+// Skinny (1..8 row) weight-streaming projections for decode.
+//
+// With 1-8 live rows every projection of the decode step is bound by streaming the weight matrix from
+// HBM once, so these kernels are organised around 16-byte streaming loads (L1 no-allocate), one warp per
+// output feature (two when that shares the activation registers), fp32 accumulation and a fused epilogue:
+// fp32/bf16 store, SwiGLU of a gate/up pair, or an in-kernel all-reduce over peer memory for K-split
+// (tensor-parallel) projections.  FP8 weights are decoded with the contract formula
+// bf16(f32(e4m3) * scale_inv[n/128][k/128]) on the fly; the product with the bf16 activation is exact in
+// fp32.
+//
+// Replaces: reference `glm_tpu/layers/linear.py:89-128` (+ psum), `layers/mlp.py:55-68`,
+// `kernels/fp8_grouped_matmul/kernel.py:125-299` (decode routed projection, t=1 and t=2).
+#include "common.cuh"
+#include "peer.cuh"
+
+#define SK_WARPS 8
+#define SK_THREADS (SK_WARPS * 32)
+
+// ---------------------------------------------------------------------------------------------------
+// Per-warp dot products.  acc[j][r] accumulates this lane's share of  sum_k w_j[k] * x_r[k].
+template <int R, int NPW>
+__device__ __forceinline__ void warp_dot_bf16(const bf16* const (&xr)[R], const bf16* const (&wp)[NPW], int K, int lane,
+                                              float (&acc)[NPW][R]) {
+#pragma unroll 2
+    for (int k = lane * 8; k < K; k += 256) {
+        float wf[NPW][8];
+#pragma unroll
+        for (int j = 0; j < NPW; ++j) {
+            const uint4 v = ld_stream16(wp[j] + k);
+            wf[j][0] = bf16_lo(v.x); wf[j][1] = bf16_hi(v.x); wf[j][2] = bf16_lo(v.y); wf[j][3] = bf16_hi(v.y);
+            wf[j][4] = bf16_lo(v.z); wf[j][5] = bf16_hi(v.z); wf[j][6] = bf16_lo(v.w); wf[j][7] = bf16_hi(v.w);
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const uint4 v = ld_hot16(xr[r] + k);
+            const float xf[8] = {bf16_lo(v.x), bf16_hi(v.x), bf16_lo(v.y), bf16_hi(v.y),
+                                 bf16_lo(v.z), bf16_hi(v.z), bf16_lo(v.w), bf16_hi(v.w)};
+#pragma unroll
+            for (int j = 0; j < NPW; ++j)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[j][r] = fmaf(wf[j][i], xf[i], acc[j][r]);
+        }
+    }
+}
+
+// FP8 (e4m3 + 128x128 fp32 block scales).  sp[j] points at the scale row of weight row j (K/128 entries).
+template <int R, int NPW>
+__device__ __forceinline__ void warp_dot_fp8(const bf16* const (&xr)[R], const uint8_t* const (&wp)[NPW],
+                                             const float* const (&sp)[NPW], int K, int lane, float (&acc)[NPW][R]) {
+#pragma unroll 2
+    for (int k = lane * 16; k < K; k += 512) {
+        float wf[NPW][16];
+#pragma unroll
+        for (int j = 0; j < NPW; ++j) {
+            const uint4 v = ld_stream16(wp[j] + k);
+            const float s = __ldg(sp[j] + (k >> 7));
+            const uint32_t words[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float2 a = decode_e4m3x2(words[q], s);
+                const float2 b = decode_e4m3x2(words[q] >> 16, s);
+                wf[j][4 * q + 0] = a.x; wf[j][4 * q + 1] = a.y; wf[j][4 * q + 2] = b.x; wf[j][4 * q + 3] = b.y;
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const uint4 v0 = ld_hot16(xr[r] + k);
+            const uint4 v1 = ld_hot16(xr[r] + k + 8);
+            const float xf[16] = {bf16_lo(v0.x), bf16_hi(v0.x), bf16_lo(v0.y), bf16_hi(v0.y), bf16_lo(v0.z), bf16_hi(v0.z),
+                                  bf16_lo(v0.w), bf16_hi(v0.w), bf16_lo(v1.x), bf16_hi(v1.x), bf16_lo(v1.y), bf16_hi(v1.y),
+                                  bf16_lo(v1.z), bf16_hi(v1.z), bf16_lo(v1.w), bf16_hi(v1.w)};
+#pragma unroll
+            for (int j = 0; j < NPW; ++j)
+#pragma unroll
+                for (int i = 0; i < 16; ++i) acc[j][r] = fmaf(wf[j][i], xf[i], acc[j][r]);
+        }
+    }
+}
+
+template <int R, int NPW>
+__device__ __forceinline__ void warp_reduce_all(float (&acc)[NPW][R]) {
+#pragma unroll
+    for (int j = 0; j < NPW; ++j)
+#pragma unroll
+        for (int r = 0; r < R; ++r) acc[j][r] = warp_sum(acc[j][r]);
+}
+
+// ---------------------------------------------------------------------------------------------------
+// out[r][n] = sum_k x[r][k] * w[n][k]          (bf16 weights)
+enum { SK_OUT_F32 = 0, SK_OUT_BF16 = 1, SK_OUT_ALLREDUCE_BF16 = 2 };
+
+template <int R>
+__global__ void __launch_bounds__(SK_THREADS)
+skinny_bf16_kernel(const bf16* __restrict__ x, int64_t xs, int rows, const bf16* __restrict__ w, int64_t ws, int N, int K,
+                   void* __restrict__ out, int64_t os, int mode, int64_t xb, int64_t wb, int64_t ob, PeerComm comm,
+                   int channel) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = (blockIdx.x * SK_WARPS + warp) * 2;
+    // blockIdx.y selects one problem of a batch (per-head projections): element offsets xb / wb / ob.
+    x += (int64_t)blockIdx.y * xb;
+    w += (int64_t)blockIdx.y * wb;
+    out = mode == SK_OUT_F32 ? (void*)(reinterpret_cast<float*>(out) + (int64_t)blockIdx.y * ob)
+                             : (void*)(reinterpret_cast<bf16*>(out) + (int64_t)blockIdx.y * ob);
+    const bf16* xr[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) xr[r] = x + (int64_t)(r < rows ? r : 0) * xs;
+    float acc[2][R];
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int r = 0; r < R; ++r) acc[j][r] = 0.f;
+    if (n0 < N) {
+        const bf16* wp[2] = {w + (int64_t)n0 * ws, w + (int64_t)min(n0 + 1, N - 1) * ws};
+        warp_dot_bf16<R, 2>(xr, wp, K, lane, acc);
+        warp_reduce_all<R, 2>(acc);
+    }
+    if (mode == SK_OUT_ALLREDUCE_BF16) {
+        __shared__ float sh[SK_WARPS * 2 * R];
+        if (lane == 0) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int r = 0; r < R; ++r) sh[(warp * 2 + j) * R + r] = acc[j][r];
+        }
+        __syncthreads();
+        cta_allreduce_f32(comm, channel, sh, SK_WARPS * 2 * R);
+        if (lane == 0) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int r = 0; r < R; ++r)
+                    if (n0 + j < N && r < rows)
+                        reinterpret_cast<bf16*>(out)[(int64_t)r * os + n0 + j] = __float2bfloat16_rn(sh[(warp * 2 + j) * R + r]);
+        }
+        return;
+    }
+    if (lane == 0 && n0 < N) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int r = 0; r < R; ++r)
+                if (n0 + j < N && r < rows) {
+                    if (mode == SK_OUT_F32) reinterpret_cast<float*>(out)[(int64_t)r * os + n0 + j] = acc[j][r];
+                    else reinterpret_cast<bf16*>(out)[(int64_t)r * os + n0 + j] = __float2bfloat16_rn(acc[j][r]);
+                }
+    }
+}
+
+// act[r][n] = bf16( silu(bf16(x.w_gate[n])) * bf16(x.w_up[n]) )       (bf16 weights; dense MLP / shared expert)
+template <int R>
+__global__ void __launch_bounds__(SK_THREADS)
+skinny_bf16_swiglu_kernel(const bf16* __restrict__ x, int64_t xs, int rows, const bf16* __restrict__ wg,
+                          const bf16* __restrict__ wu, int64_t ws, int N, int K, bf16* __restrict__ act, int64_t as) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n = blockIdx.x * SK_WARPS + warp;
+    if (n >= N) return;
+    const bf16* xr[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) xr[r] = x + (int64_t)(r < rows ? r : 0) * xs;
+    float acc[2][R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) acc[0][r] = acc[1][r] = 0.f;
+    const bf16* wp[2] = {wg + (int64_t)n * ws, wu + (int64_t)n * ws};
+    warp_dot_bf16<R, 2>(xr, wp, K, lane, acc);
+    warp_reduce_all<R, 2>(acc);
+    if (lane == 0) {
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+            if (r < rows) {
+                const float g = bf16_round(acc[0][r]), u = bf16_round(acc[1][r]);
+                act[(int64_t)r * as + n] = __float2bfloat16_rn(g * sigmoidf_precise(g) * u);
+            }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Routed experts (FP8), organised as tiles: tile t = up to RT routes of ONE expert.
+//   tile_expert[t]  global expert id (< 0: empty tile)
+//   tile_routes[t*RT + i]  route index p = token_row * top_k + slot, or -1
+// When tile_routes == nullptr every tile is the single route t and its expert is tile_expert[t] (decode).
+// A tile whose expert is not stored on this rank is skipped: expert-parallel ownership is resolved here.
+template <int RT>
+__global__ void __launch_bounds__(SK_THREADS)
+moe_gateup_fp8_kernel(const bf16* __restrict__ x, int64_t xs, int top_k, const int* __restrict__ tile_expert,
+                      const int* __restrict__ tile_routes, const int* __restrict__ n_tiles, const uint8_t* __restrict__ wg,
+                      const uint8_t* __restrict__ wu, const float* __restrict__ sg, const float* __restrict__ su,
+                      int expert_base, int experts_local, int I, int H, bf16* __restrict__ act) {
+    const int t = blockIdx.y;
+    if (n_tiles && t >= *n_tiles) return;
+    const int e = tile_expert[t] - expert_base;
+    if (e < 0 || e >= experts_local) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n = blockIdx.x * SK_WARPS + warp;
+    if (n >= I) return;
+    int route[RT];
+    const bf16* xr[RT];
+#pragma unroll
+    for (int i = 0; i < RT; ++i) {
+        route[i] = tile_routes ? tile_routes[t * RT + i] : (i == 0 ? t : -1);
+        xr[i] = x + (int64_t)(route[i] >= 0 ? route[i] / top_k : 0) * xs;
+    }
+    const int kb = (H + 127) >> 7;
+    const int64_t wofs = ((int64_t)e * I + n) * H;
+    const int64_t sofs = ((int64_t)e * ((I + 127) >> 7) + (n >> 7)) * kb;
+    const uint8_t* wp[2] = {wg + wofs, wu + wofs};
+    const float* sp[2] = {sg + sofs, su + sofs};
+    float acc[2][RT];
+#pragma unroll
+    for (int i = 0; i < RT; ++i) acc[0][i] = acc[1][i] = 0.f;
+    warp_dot_fp8<RT, 2>(xr, wp, sp, H, lane, acc);
+    warp_reduce_all<RT, 2>(acc);
+    if (lane == 0) {
+#pragma unroll
+        for (int i = 0; i < RT; ++i)
+            if (route[i] >= 0) {
+                const float g = bf16_round(acc[0][i]), u = bf16_round(acc[1][i]);
+                act[(int64_t)route[i] * I + n] = __float2bfloat16_rn(g * sigmoidf_precise(g) * u);
+            }
+    }
+}
+
+// dw[p][n] = bf16( bf16(act[p] . w_down[e][n]) * bf16(route_weight[p]) )
+template <int RT>
+__global__ void __launch_bounds__(SK_THREADS)
+moe_down_fp8_kernel(const bf16* __restrict__ act, const float* __restrict__ route_weight, const int* __restrict__ tile_expert,
+                    const int* __restrict__ tile_routes, const int* __restrict__ n_tiles, const uint8_t* __restrict__ wd,
+                    const float* __restrict__ sd, int expert_base, int experts_local, int I, int H, bf16* __restrict__ dw) {
+    const int t = blockIdx.y;
+    if (n_tiles && t >= *n_tiles) return;
+    const int e = tile_expert[t] - expert_base;
+    if (e < 0 || e >= experts_local) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = (blockIdx.x * SK_WARPS + warp) * 2;
+    if (n0 >= H) return;
+    int route[RT];
+    const bf16* xr[RT];
+#pragma unroll
+    for (int i = 0; i < RT; ++i) {
+        route[i] = tile_routes ? tile_routes[t * RT + i] : (i == 0 ? t : -1);
+        xr[i] = act + (int64_t)(route[i] >= 0 ? route[i] : 0) * I;
+    }
+    const int kb = (I + 127) >> 7;
+    const int n1 = min(n0 + 1, H - 1);
+    const uint8_t* wp[2] = {wd + ((int64_t)e * H + n0) * I, wd + ((int64_t)e * H + n1) * I};
+    const float* sp[2] = {sd + ((int64_t)e * ((H + 127) >> 7) + (n0 >> 7)) * kb, sd + ((int64_t)e * ((H + 127) >> 7) + (n1 >> 7)) * kb};
+    float acc[2][RT];
+#pragma unroll
+    for (int i = 0; i < RT; ++i) acc[0][i] = acc[1][i] = 0.f;
+    warp_dot_fp8<RT, 2>(xr, wp, sp, I, lane, acc);
+    warp_reduce_all<RT, 2>(acc);
+    if (lane == 0) {
+#pragma unroll
+        for (int i = 0; i < RT; ++i)
+            if (route[i] >= 0) {
+                const float wgt = bf16_round(route_weight[route[i]]);
+#pragma unroll
+                for (int j = 0; j < 2; ++j)
+                    if (n0 + j < H) dw[(int64_t)route[i] * H + n0 + j] = __float2bfloat16_rn(bf16_round(acc[j][i]) * wgt);
+            }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// MoE combine: for row r, column n
+//   routed = sum over the row's routes owned by this rank, in slot order, of dw[p][n]      (fp32)
+//   shared = this rank's K-slice of the shared-expert down projection                       (fp32, given)
+//   both are summed over the ranks in-kernel (peer-memory all-reduce), then
+//   out = bf16( bf16( bf16(routed) * scale ) + bf16(shared) )
+// plain != 0: out = bf16(sum over ranks of shared_partial)   -- dense MLP / any K-split partial.
+// routed_partial != nullptr: only write the local fp32 route sums there (the caller reduces them with a
+//   library collective: the NCCL baseline and prefill); no exchange, no output.
+// blockIdx.y selects a chunk of GLMB_MAX_ROWS rows.
+#define CB_COLS 16
+__global__ void __launch_bounds__(128)
+moe_combine_kernel(const bf16* __restrict__ dw, const int* __restrict__ topk_ids, const float* __restrict__ shared_partial,
+                   int rows_total, int top_k, int H, int expert_base, int experts_local, float scale, int plain,
+                   bf16* __restrict__ out, float* __restrict__ routed_partial, PeerComm comm, int channel) {
+    __shared__ float sh[2 * GLMB_MAX_ROWS * CB_COLS];
+    const int n0 = blockIdx.x * CB_COLS;
+    const int r0 = blockIdx.y * GLMB_MAX_ROWS;
+    const int rows = min(GLMB_MAX_ROWS, rows_total - r0);
+    const int per = rows * CB_COLS;
+    for (int i = threadIdx.x; i < per; i += blockDim.x) {
+        const int r = r0 + i / CB_COLS, n = n0 + i % CB_COLS;
+        float routed = 0.f, shared = 0.f;
+        if (n < H) {
+            shared = shared_partial ? shared_partial[(int64_t)r * H + n] : 0.f;
+            if (!plain) {
+                for (int s = 0; s < top_k; ++s) {
+                    const int p = r * top_k + s;
+                    const int e = topk_ids[p] - expert_base;
+                    if (e >= 0 && e < experts_local) routed += __bfloat162float(dw[(int64_t)p * H + n]);
+                }
+            }
+            if (routed_partial) routed_partial[(int64_t)r * H + n] = routed;
+        }
+        sh[i] = shared;
+        sh[per + i] = routed;
+    }
+    if (routed_partial) return;
+    __syncthreads();
+    cta_allreduce_f32(comm, channel, sh, plain ? per : 2 * per);
+    for (int i = threadIdx.x; i < per; i += blockDim.x) {
+        const int r = r0 + i / CB_COLS, n = n0 + i % CB_COLS;
+        if (n >= H) continue;
+        float v;
+        if (plain) v = sh[i];
+        else v = bf16_round(bf16_round(sh[per + i]) * scale) + bf16_round(sh[i]);
+        out[(int64_t)r * H + n] = __float2bfloat16_rn(v);
+    }
+}
+
+// ===================================================================================================
+// Host launchers
+#define DISPATCH_R(rows, CALL)                                \
+    do {                                                      \
+        if ((rows) <= 1) { CALL(1); }                         \
+        else if ((rows) <= 2) { CALL(2); }                    \
+        else if ((rows) <= 4) { CALL(4); }                    \
+        else { CALL(8); }                                     \
+    } while (0)
+
+static PeerComm single_comm() {
+    PeerComm c;
+    memset(&c, 0, sizeof(c));
+    c.world = 1;
+    return c;
+}
+
+// x [rows<=8, K] bf16, w [N, K] bf16 -> out [rows, N] (fp32, bf16, or all-reduced bf16).  K % 8 == 0.
+// batch > 1 runs `batch` independent problems whose x / w / out start xb / wb / ob elements apart.
+GLMB_API int glmb_skinny_bf16(const void* x, int64_t xs, int rows, const void* w, int64_t ws, int N, int K, void* out, int64_t os,
+                              int mode, int batch, int64_t xb, int64_t wb, int64_t ob, const PeerComm* comm, int channel,
+                              void* stream) {
+    if (rows < 1 || rows > GLMB_MAX_ROWS || (K & 7) || (xs & 7) || (ws & 7) || (xb & 7) || (wb & 7) || batch < 1) return 1;
+    const dim3 grid(ceil_div(N, SK_WARPS * 2), batch);
+    PeerComm c = comm ? *comm : single_comm();
+    if (mode == SK_OUT_ALLREDUCE_BF16 && c.world > 1 && (int)(grid.x * grid.y) > GLMB_AR_MAX_CTAS) return 2;
+    if (mode == SK_OUT_ALLREDUCE_BF16 && c.world == 1) mode = SK_OUT_BF16;
+#define CALL(RR)                                                                                                   \
+    skinny_bf16_kernel<RR><<<grid, SK_THREADS, 0, (cudaStream_t)stream>>>((const bf16*)x, xs, rows, (const bf16*)w, ws, N, K, \
+                                                                          out, os, mode, xb, wb, ob, c, channel)
+    DISPATCH_R(rows, CALL);
+#undef CALL
+    return (int)cudaGetLastError();
+}
+
+GLMB_API int glmb_skinny_bf16_swiglu(const void* x, int64_t xs, int rows, const void* wg, const void* wu, int64_t ws, int N, int K,
+                                     void* act, int64_t as, void* stream) {
+    if (rows < 1 || rows > GLMB_MAX_ROWS || (K & 7) || (xs & 7) || (ws & 7)) return 1;
+    const int grid = ceil_div(N, SK_WARPS);
+#define CALL(RR)                                                                                                          \
+    skinny_bf16_swiglu_kernel<RR><<<grid, SK_THREADS, 0, (cudaStream_t)stream>>>((const bf16*)x, xs, rows, (const bf16*)wg, \
+                                                                                 (const bf16*)wu, ws, N, K, (bf16*)act, as)
+    DISPATCH_R(rows, CALL);
+#undef CALL
+    return (int)cudaGetLastError();
+}
+
+// Routed gate/up for `tiles` tiles of `rt` routes (rt in {1, 8}).  H % 16 == 0.
+GLMB_API int glmb_moe_gateup_fp8(const void* x, int64_t xs, int top_k, const int* tile_expert, const int* tile_routes,
+                                 const int* n_tiles, int tiles, int rt, const void* wg, const void* wu, const float* sg,
+                                 const float* su, int expert_base, int experts_local, int I, int H, void* act, void* stream) {
+    if ((H & 15) || tiles < 1) return 1;
+    dim3 grid(ceil_div(I, SK_WARPS), tiles);
+    if (rt == 1)
+        moe_gateup_fp8_kernel<1><<<grid, SK_THREADS, 0, (cudaStream_t)stream>>>(
+            (const bf16*)x, xs, top_k, tile_expert, tile_routes, n_tiles, (const uint8_t*)wg, (const uint8_t*)wu, sg, su,
+            expert_base, experts_local, I, H, (bf16*)act);
+    else if (rt == 8)
+        moe_gateup_fp8_kernel<8><<<grid, SK_THREADS, 0, (cudaStream_t)stream>>>(
+            (const bf16*)x, xs, top_k, tile_expert, tile_routes, n_tiles, (const uint8_t*)wg, (const uint8_t*)wu, sg, su,
+            expert_base, experts_local, I, H, (bf16*)act);
+    else
+        return 1;
+    return (int)cudaGetLastError();
+}
+
+GLMB_API int glmb_moe_down_fp8(const void* act, const float* route_weight, const int* tile_expert, const int* tile_routes,
+                               const int* n_tiles, int tiles, int rt, const void* wd, const float* sd, int expert_base,
+                               int experts_local, int I, int H, void* dw, void* stream) {
+    if ((I & 15) || tiles < 1) return 1;
+    dim3 grid(ceil_div(H, SK_WARPS * 2), tiles);
+    if (rt == 1)
+        moe_down_fp8_kernel<1><<<grid, SK_THREADS, 0, (cudaStream_t)stream>>>((const bf16*)act, route_weight, tile_expert, tile_routes,
+                                                                             n_tiles, (const uint8_t*)wd, sd, expert_base,
+                                                                             experts_local, I, H, (bf16*)dw);
+    else if (rt == 8)
+        moe_down_fp8_kernel<8><<<grid, SK_THREADS, 0, (cudaStream_t)stream>>>((const bf16*)act, route_weight, tile_expert, tile_routes,
+                                                                             n_tiles, (const uint8_t*)wd, sd, expert_base,
+                                                                             experts_local, I, H, (bf16*)dw);
+    else
+        return 1;
+    return (int)cudaGetLastError();
+}
+
+// Any number of rows when the exchange is off (world == 1 or routed_partial given); with the in-kernel
+// all-reduce the grid must fit the per-CTA flag table.
+GLMB_API int glmb_moe_combine(const void* dw, const int* topk_ids, const float* shared_partial, int rows, int top_k, int H,
+                              int expert_base, int experts_local, float scale, int plain, void* out, float* routed_partial,
+                              const PeerComm* comm, int channel, void* stream) {
+    if (rows < 1) return 1;
+    dim3 grid(ceil_div(H, CB_COLS), ceil_div(rows, GLMB_MAX_ROWS));
+    PeerComm c = comm ? *comm : single_comm();
+    if (c.world > 1 && !routed_partial && (int)(grid.x * grid.y) > GLMB_AR_MAX_CTAS) return 2;
+    moe_combine_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>((const bf16*)dw, topk_ids, shared_partial, rows, top_k, H, expert_base,
+                                                               experts_local, scale, plain, (bf16*)out, routed_partial, c, channel);
+    return (int)cudaGetLastError();
+}

@@ -1,0 +1,337 @@
+// Normalisation, RoPE, cache-row write and query preparation kernels.
+//
+//   embed_rows          residual[r] = embedding[token[r]]
+//   add_rmsnorm         s = f32(update) + f32(residual); residual = bf16(s); x = bf16(bf16(s*rsqrt(ms+eps)) * w)
+//   qkv_a_post          q_a/kv_a LoRA RMSNorms, RoPE of the key part, cache-row write into the owner's
+//                       stripe, indexer key LayerNorm + RoPE + index-cache write, indexer head weights
+//   q_post              RoPE of every head's query rope part, bf16 rounding of the nope part, indexer
+//                       query RoPE (fp32)
+//   q_absorb            q_c[h] = bf16(q_nope[h] @ W_k[h]) for <= 8 rows, written (and pushed to the
+//                       peers: fused all-gather) into the all-heads query buffer
+//
+// Rounding rules restate reference `glm_tpu/layers/norm.py:55-122,226-248`, `layers/rope.py:94-99,145-199`,
+// `layers/attention/mla.py:379-403,441-475`, `layers/attention/dsa_indexer.py:808-843`.
+#include "common.cuh"
+#include "peer.cuh"
+
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    // scratch: >= 33 floats of shared memory; every thread of the block must call
+    v = warp_sum(v);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < (int)((blockDim.x + 31) >> 5) ? scratch[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+
+// ---------------------------------------------------------------------------------------------------
+__global__ void embed_rows_kernel(const int* __restrict__ tokens, const bf16* __restrict__ table, int vocab, int H,
+                                  bf16* __restrict__ residual, uint32_t* status) {
+    const int r = blockIdx.x;
+    int t = tokens[r];
+    if (t < 0 || t >= vocab) {
+        if (threadIdx.x == 0) raise_status(status, GLMB_STATUS_BAD_INDEX);
+        t = min(max(t, 0), vocab - 1);
+    }
+    const uint4* src = reinterpret_cast<const uint4*>(table + (int64_t)t * H);
+    uint4* dst = reinterpret_cast<uint4*>(residual + (int64_t)r * H);
+    for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = src[i];
+}
+
+// ---------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+add_rmsnorm_kernel(const bf16* __restrict__ update, bf16* __restrict__ residual, const bf16* __restrict__ weight,
+                   bf16* __restrict__ out, int H, float eps) {
+    extern __shared__ float sm[];  // H + 33
+    float* s = sm;
+    float* scratch = sm + H;
+    const int64_t base = (int64_t)blockIdx.x * H;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = __bfloat162float(residual[base + i]);
+        if (update) v = __fadd_rn(__bfloat162float(update[base + i]), v);
+        s[i] = v;
+        ss = fmaf(v, v, ss);
+    }
+    const float total = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(total / (float)H + eps);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float y = bf16_round(s[i] * inv);
+        out[base + i] = __float2bfloat16_rn(y * __bfloat162float(weight[i]));
+        residual[base + i] = __float2bfloat16_rn(s[i]);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------
+struct QkvPostArgs {
+    const float* proj;      // [rows, proj_stride]: q_a (Q) | kv_a (L + rd) | idx_k (D) | idx_w (IH)
+    int64_t proj_stride;
+    const bf16* q_norm_w;   // [Q]
+    const bf16* kv_norm_w;  // [L]
+    const bf16* rope_table; // [capacity, rd]  cos | sin
+    const float* inv_freq;  // [rd/2] fp32, indexer RoPE
+    const float* k_norm_w;  // [D] fp32 (indexer key LayerNorm)
+    const float* k_norm_b;  // [D]
+    const int* row_pos;     // [rows]
+    const int* row_lane;    // [rows]
+    const int* row_active;  // [rows] or nullptr
+    bf16* q_resid;          // [rows, Q]
+    bf16* kv_new;           // [rows, L + rd] this step's rows (also attended by peers in prefill tests); may be nullptr
+    bf16* kv_cache;         // [lanes, layers, local_cap, L + rd]
+    bf16* index_cache;      // [lanes, full_layers, local_cap, D]
+    float* head_w;          // [rows, IH]
+    bf16* idx_key_new;      // [rows, D] may be nullptr
+    int Q, L, rd, D, IH;
+    int has_indexer;
+    int layer, layers, index_slot, full_layers, local_cap;
+    int stripe, world, rank, capacity;
+    float eps, key_eps, head_scale;  // head_scale = IH**-0.5 rounded to fp32 by the host
+    uint32_t* status;
+};
+
+__global__ void __launch_bounds__(256) qkv_a_post_kernel(QkvPostArgs a) {
+    __shared__ float scratch[40];
+    __shared__ float s_key[256];
+    const int r = blockIdx.x;
+    const float* p = a.proj + (int64_t)r * a.proj_stride;
+    int pos = a.row_pos[r];
+    const int lane_id = a.row_lane[r];
+    const bool active = a.row_active ? a.row_active[r] != 0 : true;
+    if (pos < 0 || pos >= a.capacity) {
+        if (threadIdx.x == 0) raise_status(a.status, GLMB_STATUS_BAD_INDEX);
+        pos = min(max(pos, 0), a.capacity - 1);
+    }
+    const int page = a.stripe * a.world;
+    const bool owner = ((pos / a.stripe) % a.world) == a.rank;
+    const int local_row = (pos / page) * a.stripe + pos % a.stripe;
+    const int W = a.L + a.rd;
+    bf16* cache_row = a.kv_cache + (((int64_t)lane_id * a.layers + a.layer) * a.local_cap + local_row) * W;
+    const bool write_cache = owner && active;
+
+    // q_a RMSNorm
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < a.Q; i += blockDim.x) {
+        const float v = bf16_round(p[i]);
+        ss = fmaf(v, v, ss);
+    }
+    float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)a.Q + a.eps);
+    for (int i = threadIdx.x; i < a.Q; i += blockDim.x) {
+        const float y = bf16_round(bf16_round(p[i]) * inv);
+        a.q_resid[(int64_t)r * a.Q + i] = __float2bfloat16_rn(y * __bfloat162float(a.q_norm_w[i]));
+    }
+    // kv_a latent RMSNorm
+    const float* c = p + a.Q;
+    ss = 0.f;
+    for (int i = threadIdx.x; i < a.L; i += blockDim.x) {
+        const float v = bf16_round(c[i]);
+        ss = fmaf(v, v, ss);
+    }
+    inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)a.L + a.eps);
+    for (int i = threadIdx.x; i < a.L; i += blockDim.x) {
+        const float y = bf16_round(bf16_round(c[i]) * inv);
+        const bf16 o = __float2bfloat16_rn(y * __bfloat162float(a.kv_norm_w[i]));
+        if (write_cache) cache_row[i] = o;
+        if (a.kv_new) a.kv_new[(int64_t)r * W + i] = o;
+    }
+    // RoPE of the key part: interleaved pairs, bf16 table, fp32 products, one rounding
+    const int half = a.rd / 2;
+    for (int j = threadIdx.x; j < half; j += blockDim.x) {
+        const float even = bf16_round(c[a.L + 2 * j]), odd = bf16_round(c[a.L + 2 * j + 1]);
+        const float cs = __bfloat162float(a.rope_table[(int64_t)pos * a.rd + j]);
+        const float sn = __bfloat162float(a.rope_table[(int64_t)pos * a.rd + half + j]);
+        const bf16 oe = __float2bfloat16_rn(__fsub_rn(__fmul_rn(even, cs), __fmul_rn(odd, sn)));
+        const bf16 oo = __float2bfloat16_rn(__fadd_rn(__fmul_rn(odd, cs), __fmul_rn(even, sn)));
+        if (write_cache) { cache_row[a.L + 2 * j] = oe; cache_row[a.L + 2 * j + 1] = oo; }
+        if (a.kv_new) { a.kv_new[(int64_t)r * W + a.L + 2 * j] = oe; a.kv_new[(int64_t)r * W + a.L + 2 * j + 1] = oo; }
+    }
+    if (!a.has_indexer) return;
+    // Indexer key: affine LayerNorm (fp32), RoPE on the first rd features (fp32 cos/sin), bf16 store
+    const float* kx = c + W;
+    float v = threadIdx.x < a.D ? kx[threadIdx.x] : 0.f;
+    const float mean = block_sum(v, scratch) / (float)a.D;
+    const float d = threadIdx.x < a.D ? v - mean : 0.f;
+    const float var = block_sum(d * d, scratch) / (float)a.D;
+    const float rstd = 1.0f / sqrtf(var + a.key_eps);
+    if (threadIdx.x < a.D) s_key[threadIdx.x] = __fadd_rn(__fmul_rn(__fmul_rn(d, rstd), a.k_norm_w[threadIdx.x]), a.k_norm_b[threadIdx.x]);
+    __syncthreads();
+    bf16* idx_row = a.index_cache + (((int64_t)lane_id * a.full_layers + a.index_slot) * a.local_cap + local_row) * a.D;
+    if (threadIdx.x < a.D) {
+        const int i = threadIdx.x;
+        float o = s_key[i];
+        if (i < a.rd) {
+            const int j = i >> 1;
+            const float angle = __fmul_rn((float)pos, a.inv_freq[j]);
+            const float cs = cosf(angle), sn = sinf(angle);
+            const float even = s_key[2 * j], odd = s_key[2 * j + 1];
+            o = (i & 1) ? __fadd_rn(__fmul_rn(odd, cs), __fmul_rn(even, sn)) : __fsub_rn(__fmul_rn(even, cs), __fmul_rn(odd, sn));
+        }
+        const bf16 ob = __float2bfloat16_rn(o);
+        if (write_cache) idx_row[i] = ob;
+        if (a.idx_key_new) a.idx_key_new[(int64_t)r * a.D + i] = ob;
+    }
+    // Indexer head weights
+    const float* hw = kx + a.D;
+    const float hscale = a.head_scale;
+    for (int h = threadIdx.x; h < a.IH; h += blockDim.x) a.head_w[(int64_t)r * a.IH + h] = __fmul_rn(hw[h], hscale);
+}
+
+// ---------------------------------------------------------------------------------------------------
+struct QPostArgs {
+    const float* q;          // [rows, q_stride]: heads_local * (nope + rd)  |  IH * D (indexer, when has_indexer)
+    int64_t q_stride;
+    const bf16* rope_table;  // [capacity, rd]
+    const float* inv_freq;   // [rd/2]
+    const int* row_pos;
+    bf16* q_nope;            // [rows, heads_local, nope] bf16-rounded
+    bf16* q_full;            // [rows, heads_total, L + rd]; the rope part of this rank's heads is written here
+    float* q_idx;            // [rows, IH, D] fp32 with RoPE applied
+    int heads_local, head_base, heads_total, nope, rd, L, IH, D, has_indexer, capacity;
+};
+
+__global__ void __launch_bounds__(256) q_post_kernel(QPostArgs a) {
+    const int r = blockIdx.x;
+    const float* q = a.q + (int64_t)r * a.q_stride;
+    const int pos = min(max(a.row_pos[r], 0), a.capacity - 1);
+    const int qk = a.nope + a.rd, half = a.rd / 2, W = a.L + a.rd;
+    for (int i = threadIdx.x; i < a.heads_local * a.nope; i += blockDim.x) {
+        const int h = i / a.nope, d = i % a.nope;
+        a.q_nope[((int64_t)r * a.heads_local + h) * a.nope + d] = __float2bfloat16_rn(q[h * qk + d]);
+    }
+    for (int i = threadIdx.x; i < a.heads_local * half; i += blockDim.x) {
+        const int h = i / half, j = i % half;
+        const float even = bf16_round(q[h * qk + a.nope + 2 * j]), odd = bf16_round(q[h * qk + a.nope + 2 * j + 1]);
+        const float cs = __bfloat162float(a.rope_table[(int64_t)pos * a.rd + j]);
+        const float sn = __bfloat162float(a.rope_table[(int64_t)pos * a.rd + half + j]);
+        bf16* dst = a.q_full + ((int64_t)r * a.heads_total + a.head_base + h) * W + a.L;
+        dst[2 * j] = __float2bfloat16_rn(__fsub_rn(__fmul_rn(even, cs), __fmul_rn(odd, sn)));
+        dst[2 * j + 1] = __float2bfloat16_rn(__fadd_rn(__fmul_rn(odd, cs), __fmul_rn(even, sn)));
+    }
+    if (!a.has_indexer) return;
+    const float* qi = q + a.heads_local * qk;
+    for (int i = threadIdx.x; i < a.IH * a.D; i += blockDim.x) {
+        const int h = i / a.D, d = i % a.D;
+        float o = qi[i];
+        if (d < a.rd) {
+            const int j = d >> 1;
+            const float angle = __fmul_rn((float)pos, a.inv_freq[j]);
+            const float cs = cosf(angle), sn = sinf(angle);
+            const float even = qi[h * a.D + 2 * j], odd = qi[h * a.D + 2 * j + 1];
+            o = (d & 1) ? __fadd_rn(__fmul_rn(odd, cs), __fmul_rn(even, sn)) : __fsub_rn(__fmul_rn(even, cs), __fmul_rn(odd, sn));
+        }
+        a.q_idx[(int64_t)r * a.IH * a.D + i] = o;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// q_c[r][h][c] = bf16( sum_d q_nope[r][h][d] * W_k[h][d][c] ),  W_k[h] = kv_b rows h*(nope+v) .. +nope, [nope, L].
+// grid (heads_local, ceil(L/128)); 8 warps split d, a lane owns 4 columns.  The result row (and, from the
+// blockIdx.y == 0 CTA, the rope part) is also stored into every peer's query buffer: the all-gather of
+// the queries over heads is fused here, and the last CTA signals GLMB_SIG_Q.
+#define QA_COLS 128
+template <int R>
+__global__ void __launch_bounds__(256)
+q_absorb_kernel(const bf16* __restrict__ q_nope, int rows, const bf16* __restrict__ kv_b, int heads_local, int head_base,
+                int heads_total, int nope, int vdim, int L, int rd, bf16* __restrict__ q_full, int64_t q_full_offset,
+                PeerComm comm, int sig) {
+    __shared__ float red[8][R][QA_COLS];
+    const int h = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int c0 = blockIdx.y * QA_COLS + lane * 4;
+    const int per = (nope + 7) / 8;
+    const int d0 = warp * per, d1 = min(nope, d0 + per);
+    float acc[R][4];
+#pragma unroll
+    for (int r = 0; r < R; ++r) acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.f;
+    const bf16* wk = kv_b + (int64_t)h * (nope + vdim) * L;
+    if (c0 < L) {
+#pragma unroll 4
+        for (int d = d0; d < d1; ++d) {
+            const uint2 wv = *reinterpret_cast<const uint2*>(wk + (int64_t)d * L + c0);
+            const float w0 = bf16_lo(wv.x), w1 = bf16_hi(wv.x), w2 = bf16_lo(wv.y), w3 = bf16_hi(wv.y);
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const float qv = __bfloat162float(q_nope[((int64_t)(r < rows ? r : 0) * heads_local + h) * nope + d]);
+                acc[r][0] = fmaf(qv, w0, acc[r][0]); acc[r][1] = fmaf(qv, w1, acc[r][1]);
+                acc[r][2] = fmaf(qv, w2, acc[r][2]); acc[r][3] = fmaf(qv, w3, acc[r][3]);
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) red[warp][r][lane * 4 + i] = acc[r][i];
+    __syncthreads();
+    const int W = L + rd;
+    for (int i = threadIdx.x; i < R * QA_COLS; i += blockDim.x) {
+        const int r = i / QA_COLS, cc = i % QA_COLS, c = blockIdx.y * QA_COLS + cc;
+        if (r >= rows || c >= L) continue;
+        float s = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) s += red[w][r][cc];
+        const bf16 o = __float2bfloat16_rn(s);
+        const int64_t at = ((int64_t)r * heads_total + head_base + h) * W + c;
+        q_full[at] = o;
+        for (int p = 0; p < comm.world; ++p)
+            if (p != comm.rank) reinterpret_cast<bf16*>(comm.data[p] + q_full_offset)[at] = o;
+    }
+    if (comm.world > 1 && blockIdx.y == 0) {
+        // the rope part was written locally by q_post (an earlier kernel); forward it to the peers
+        for (int i = threadIdx.x; i < rows * rd; i += blockDim.x) {
+            const int r = i / rd, j = i % rd;
+            const int64_t at = ((int64_t)r * heads_total + head_base + h) * W + L + j;
+            const bf16 o = q_full[at];
+            for (int p = 0; p < comm.world; ++p)
+                if (p != comm.rank) reinterpret_cast<bf16*>(comm.data[p] + q_full_offset)[at] = o;
+        }
+    }
+    grid_signal_peers(comm, sig);
+}
+
+// ===================================================================================================
+GLMB_API int glmb_embed_rows(const int* tokens, const void* table, int rows, int vocab, int H, void* residual, uint32_t* status,
+                             void* stream) {
+    if (H & 7) return 1;
+    embed_rows_kernel<<<rows, 256, 0, (cudaStream_t)stream>>>(tokens, (const bf16*)table, vocab, H, (bf16*)residual, status);
+    return (int)cudaGetLastError();
+}
+
+GLMB_API int glmb_add_rmsnorm(const void* update, void* residual, const void* weight, void* out, int rows, int H, float eps,
+                              void* stream) {
+    const size_t smem = (size_t)(H + 40) * sizeof(float);
+    if (smem > 48 * 1024) return 1;
+    add_rmsnorm_kernel<<<rows, 256, smem, (cudaStream_t)stream>>>((const bf16*)update, (bf16*)residual, (const bf16*)weight,
+                                                                  (bf16*)out, H, eps);
+    return (int)cudaGetLastError();
+}
+
+GLMB_API int glmb_qkv_a_post(const QkvPostArgs* args, int rows, void* stream) {
+    if (args->D > 256 || (args->rd & 1)) return 1;
+    qkv_a_post_kernel<<<rows, 256, 0, (cudaStream_t)stream>>>(*args);
+    return (int)cudaGetLastError();
+}
+
+GLMB_API int glmb_q_post(const QPostArgs* args, int rows, void* stream) {
+    q_post_kernel<<<rows, 256, 0, (cudaStream_t)stream>>>(*args);
+    return (int)cudaGetLastError();
+}
+
+// q_full must be the staging-buffer address `comm->data[rank] + q_full_offset` when world > 1.
+GLMB_API int glmb_q_absorb(const void* q_nope, int rows, const void* kv_b, int heads_local, int head_base, int heads_total,
+                           int nope, int vdim, int L, int rd, void* q_full, int64_t q_full_offset, const PeerComm* comm, int sig,
+                           void* stream) {
+    if (rows < 1 || rows > GLMB_MAX_ROWS || (L & 3)) return 1;
+    PeerComm c;
+    if (comm) c = *comm; else { memset(&c, 0, sizeof(c)); c.world = 1; }
+    dim3 grid(heads_local, ceil_div(L, QA_COLS));
+#define CALL(RR)                                                                                                              \
+    q_absorb_kernel<RR><<<grid, 256, 0, (cudaStream_t)stream>>>((const bf16*)q_nope, rows, (const bf16*)kv_b, heads_local, head_base, \
+                                                                heads_total, nope, vdim, L, rd, (bf16*)q_full, q_full_offset, c, sig)
+    if (rows <= 1) { CALL(1); } else if (rows <= 2) { CALL(2); } else if (rows <= 4) { CALL(4); } else { CALL(8); }
+#undef CALL
+    return (int)cudaGetLastError();
+}

@@ -1,0 +1,457 @@
+"""The GLM-MoE-DSA decoder as a sequence of CUDA kernel launches on one GPU of the box.
+
+One ``GlmMoeDsaModel`` lives in each per-GPU process.  ``run_rows`` pushes ``R`` token rows through all layers:
+
+* decode (``R`` = live lanes, 1..8): every projection is a weight-streaming skinny kernel; cross-GPU sums and
+  gathers happen *inside* kernels over peer memory (``comm='fused'``) or through NCCL (``comm='nccl'``, the
+  baseline).  The launch sequence is static, reads positions/tokens from device memory and is captured in a CUDA
+  graph by the runner.
+* prefill (``R`` up to a few thousand rows of one lane): dense projections go through cuBLAS (plain library GEMMs),
+  everything else through the same hand-written kernels; collectives use NCCL.
+
+Per layer (decode): add+RMSNorm -> q_a|kv_a|indexer projections -> LoRA norms, RoPE, cache-row write -> q_b ->
+query RoPE -> q-absorb (+ all-gather of queries) -> [full layers: indexer scores (+ all-gather) -> exact top-k]
+-> owner-local sparse MLA partials -> merge (+ exchange to head owners) -> value projection -> o_proj (+ all-reduce)
+-> add+RMSNorm -> dense MLP, or router -> routed FP8 experts + shared expert -> combine (+ all-reduce).
+
+Parity: reference ``glm_tpu/models/glm_moe_dsa/model.py:46-159`` (decode_step), ``decoder_layer.py:538-740`` (layer
+bodies), ``prefill.py:49-235``; the collectives of ``SURVEY`` call sites are replaced as described above.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from glm_tpu_b200.config.cache import CacheConfig
+from glm_tpu_b200.models.glm_moe_dsa.weights import DeviceWeights, LayerWeights
+from glm_tpu_b200.ops import native
+from glm_tpu_b200.oracle.contract import rope_table
+from glm_tpu_b200.parallel.peer import PeerGroup
+
+RING = 64
+
+
+def _f32(x: float) -> float:
+    return float(np.float32(x))
+
+
+@dataclass
+class DecoderState:
+    """Device-resident caches and lane registers (reference ``models/glm_moe_dsa/state.py:23-69``)."""
+
+    kv_cache: torch.Tensor  # [lanes, layers, local_cap, W] bf16
+    index_cache: torch.Tensor  # [lanes, full_layers, local_cap, D] bf16
+    tokens: torch.Tensor  # [lanes] int32: the token each lane feeds next
+    positions: torch.Tensor  # [lanes] int32: its position (= tokens already cached)
+    active: torch.Tensor  # [lanes] int32
+    lane_ids: torch.Tensor  # [lanes] int32 arange
+    out_tokens: torch.Tensor  # [RING, lanes] int32
+    step_counter: torch.Tensor  # [1] int32
+
+    @classmethod
+    def allocate(cls, cache: CacheConfig, device) -> "DecoderState":
+        dev = torch.device(device)
+        z = lambda *s: torch.zeros(s, dtype=torch.int32, device=dev)  # noqa: E731
+        return cls(
+            kv_cache=torch.zeros(cache.kv_cache_shape, dtype=torch.bfloat16, device=dev),
+            index_cache=torch.zeros(cache.index_cache_shape, dtype=torch.bfloat16, device=dev),
+            tokens=z(cache.lanes),
+            positions=z(cache.lanes),
+            active=z(cache.lanes),
+            lane_ids=torch.arange(cache.lanes, dtype=torch.int32, device=dev),
+            out_tokens=torch.full((RING, cache.lanes), -1, dtype=torch.int32, device=dev),
+            step_counter=z(1),
+        )
+
+    def reset_lane(self, lane: int) -> None:
+        """Fresh cache for a new request on ``lane`` (stale rows are never read: reads are bounded by the position)."""
+        self.positions[lane] = 0
+        self.tokens[lane] = 0
+        self.active[lane] = 0
+
+
+class Workspace:
+    """Scratch tensors for ``rows`` token rows.  Peer-visible ones live in the staging buffer when world > 1."""
+
+    def __init__(self, model: "GlmMoeDsaModel", rows: int, tag: str, attn_rows: int | None = None, score_stride: int | None = None,
+                 peer_visible: bool = True):
+        g, lay, dev = model.g, model.layout, model.device
+        self.peer_visible = peer_visible and model.peer.world > 1 and model.comm_mode == "fused"
+        self.rows = rows
+        self.attn_rows = min(rows, attn_rows or rows)
+        H, Q, L, rd, W = g.hidden_size, g.q_lora_rank, g.kv_lora_rank, g.qk_rope_head_dim, g.kv_row_width
+        IH, D, k = g.index_heads, g.index_head_dim, g.index_top_k
+        hl, ht = lay.heads_local, g.attention_heads
+        bf = lambda *s: torch.empty(s, dtype=torch.bfloat16, device=dev)  # noqa: E731
+        f32 = lambda *s: torch.empty(s, dtype=torch.float32, device=dev)  # noqa: E731
+        i32 = lambda *s: torch.zeros(s, dtype=torch.int32, device=dev)  # noqa: E731
+        self.residual, self.x, self.update = bf(rows, H), bf(rows, H), bf(rows, H)
+        self.proj_a = f32(rows, Q + W + D + IH)
+        self.q_resid = bf(rows, Q)
+        self.head_w = f32(rows, IH)
+        self.q_proj = f32(rows, hl * g.qk_head_dim + IH * D)
+        self.q_nope = bf(rows, hl, g.qk_nope_head_dim)
+        self.q_idx = f32(rows, IH, D)
+        self.score_stride = score_stride or model.cache.context_capacity
+        peer = model.peer
+        if self.peer_visible:
+            self.r_q = peer.region(f"{tag}.q_full", rows * ht * W * 2)
+            self.r_scores = peer.region(f"{tag}.scores", rows * self.score_stride * 4)
+            self.r_xpart = peer.region(f"{tag}.xpart", peer.world * self.attn_rows * hl * (L + 2) * 4)
+            self.r_cand = peer.region(f"{tag}.cand", peer.world * rows * 2 * 4)
+            self.q_full = peer.tensor(self.r_q, (rows, ht, W), torch.bfloat16)
+            self.scores = peer.tensor(self.r_scores, (rows, self.score_stride), torch.float32)
+            self.cand = peer.tensor(self.r_cand, (peer.world, rows, 2), torch.float32)
+        else:
+            self.r_q = self.r_scores = self.r_xpart = self.r_cand = None
+            self.q_full = bf(rows, ht, W)
+            self.scores = f32(rows, self.score_stride)
+            self.cand = f32(max(1, peer.world), rows, 2)
+        self.sel_global, self.sel_local, self.sel_counts = i32(rows, k), i32(rows, k), i32(rows, 2)
+        self.max_chunks = -(-k // native.attn_chunk())
+        self.part_o = f32(self.attn_rows, self.max_chunks, ht, L)
+        self.part_ml = f32(self.attn_rows, self.max_chunks, ht, 2)
+        self.o_lat = bf(rows, hl, L)
+        self.attn_v = bf(rows, hl * g.v_head_dim)
+        self.attn_out = bf(rows, H)
+        self.partial = f32(rows, H)
+        E, tk, I = g.num_routed_experts, g.routed_top_k, g.moe_intermediate_size
+        self.router_logits = f32(rows, E)
+        self.topk_ids, self.topk_w = i32(rows, tk), f32(rows, tk)
+        self.act = bf(rows * tk, I)
+        self.dw = bf(rows * tk, H)
+        self.act_shared = bf(rows, max(lay.shared_cols_local, 8))
+        self.dense_act = bf(rows, max(lay.dense_cols_local, 8))
+        self.routed_partial = f32(rows, H)
+        self.logits = bf(rows, lay.vocab_local)
+        self.kv_new = bf(rows, W)
+        self.idx_key_new = bf(rows, D)
+
+
+class GlmMoeDsaModel:
+    def __init__(self, weights: DeviceWeights, cache: CacheConfig, peer: PeerGroup, *, comm: str = "fused", group=None):
+        self.w, self.cache, self.peer = weights, cache, peer
+        self.g, self.layout = weights.geometry, weights.layout
+        self.device = weights.embed.device
+        self.world, self.rank = self.layout.world, self.layout.rank
+        if cache.world != self.world:
+            raise ValueError("cache striping and parallel layout disagree on the world size")
+        if comm not in ("fused", "nccl"):
+            raise ValueError("comm is 'fused' or 'nccl'")
+        self.comm_mode = comm
+        self.group = group
+        g = self.g
+        self.rope = rope_table(cache.context_capacity, g.qk_rope_head_dim, g.rope_theta).to(self.device)
+        j = torch.arange(0, g.qk_rope_head_dim, 2, dtype=torch.float32)
+        self.inv_freq = torch.pow(torch.tensor(g.rope_theta, dtype=torch.float32), -j / g.qk_rope_head_dim).to(self.device)
+        self.status = None  # kernels that take a status pointer get the registry's word
+        self.softmax_scale = _f32(g.qk_head_dim**-0.5)
+        self.index_scale = _f32(g.index_head_dim**-0.5)
+        self.head_scale = _f32(g.index_heads**-0.5)
+        self.trace = None  # set to a dict to record intermediates (tests)
+
+    # ------------------------------------------------------------------------------ helpers
+    @property
+    def _kc(self):
+        """PeerComm for kernels with fused communication (None: single GPU or NCCL baseline)."""
+        return self.peer.kernel_comm if self.comm_mode == "fused" else None
+
+    def _allreduce_rows(self, partial_f32: torch.Tensor) -> torch.Tensor:
+        import torch.distributed as dist
+
+        if self.world > 1:
+            dist.all_reduce(partial_f32, group=self.group)
+        return partial_f32
+
+    def _linear_f32(self, x, w, out, decode: bool):
+        """``out[:, :N] = x @ w.T`` in fp32."""
+        n = w.shape[0]
+        if decode:
+            native.skinny_bf16(x, w, out, native.SK_OUT_F32, N=n, K=w.shape[1])
+        else:
+            out[: x.shape[0], :n] = torch.mm(x, w.t(), out_dtype=torch.float32)
+
+    # ------------------------------------------------------------------------------ attention
+    def _attention(self, ws: Workspace, lw: LayerWeights, layer: int, rows: int, row_pos, row_lane, row_active, state: DecoderState,
+                   decode: bool, max_ctx: int):
+        g, lay, cache = self.g, self.layout, self.cache
+        full = g.indexer_types[layer] == "full"
+        Q, L, rd, W = g.q_lora_rank, g.kv_lora_rank, g.qk_rope_head_dim, g.kv_row_width
+        IH, D = g.index_heads, g.index_head_dim
+        hl, ht = lay.heads_local, g.attention_heads
+        fused = ws.peer_visible
+        kc = self.peer.comm if fused else None
+        x = ws.x[:rows]
+        self._linear_f32(x, lw.w_qkv_a, ws.proj_a, decode)
+        a = native.QkvPostArgs()
+        a.proj, a.proj_stride = ws.proj_a.data_ptr(), ws.proj_a.stride(0)
+        a.q_norm_w, a.kv_norm_w = lw.q_a_norm.data_ptr(), lw.kv_a_norm.data_ptr()
+        a.rope_table, a.inv_freq = self.rope.data_ptr(), self.inv_freq.data_ptr()
+        a.k_norm_w = lw.k_norm_w.data_ptr() if full else None
+        a.k_norm_b = lw.k_norm_b.data_ptr() if full else None
+        a.row_pos, a.row_lane = row_pos.data_ptr(), row_lane.data_ptr()
+        a.row_active = row_active.data_ptr() if row_active is not None else None
+        a.q_resid, a.kv_new = ws.q_resid.data_ptr(), ws.kv_new.data_ptr()
+        a.kv_cache, a.index_cache = state.kv_cache.data_ptr(), state.index_cache.data_ptr()
+        a.head_w, a.idx_key_new = ws.head_w.data_ptr(), ws.idx_key_new.data_ptr()
+        a.Q, a.L, a.rd, a.D, a.IH = Q, L, rd, D, IH
+        a.has_indexer = int(full)
+        a.layer, a.layers = layer, g.num_layers
+        a.index_slot, a.full_layers = g.index_slot(layer), len(g.full_layers)
+        a.local_cap, a.stripe, a.world, a.rank, a.capacity = cache.local_capacity, cache.stripe, self.world, self.rank, cache.context_capacity
+        a.eps, a.key_eps, a.head_scale = g.rms_norm_eps, cache.dsa.key_norm_eps, self.head_scale
+        a.status = self.peer.status_ptr
+        native.qkv_a_post(a, rows)
+
+        self._linear_f32(ws.q_resid[:rows], lw.w_q_b, ws.q_proj, decode)
+        b = native.QPostArgs()
+        b.q, b.q_stride = ws.q_proj.data_ptr(), ws.q_proj.stride(0)
+        b.rope_table, b.inv_freq, b.row_pos = self.rope.data_ptr(), self.inv_freq.data_ptr(), row_pos.data_ptr()
+        b.q_nope, b.q_full, b.q_idx = ws.q_nope.data_ptr(), ws.q_full.data_ptr(), ws.q_idx.data_ptr()
+        b.heads_local, b.head_base, b.heads_total = hl, self.rank * hl, ht
+        b.nope, b.rd, b.L, b.IH, b.D = g.qk_nope_head_dim, rd, L, IH, D
+        b.has_indexer, b.capacity = int(full), cache.context_capacity
+        native.q_post(b, rows)
+
+        if decode:
+            native.q_absorb(ws.q_nope, rows, lw.kv_b, hl, self.rank * hl, ht, g.qk_nope_head_dim, g.v_head_dim, L, rd, ws.q_full,
+                            ws.r_q.offset if fused else 0, kc, native.SIG_Q)
+            if self.world > 1 and not fused:
+                self._allgather_heads(ws.q_full[:rows])
+        else:
+            w_k = lw.kv_b[:, : g.qk_nope_head_dim, :]  # [hl, nope, L]
+            q_c = torch.einsum("rhd,hdc->rhc", ws.q_nope[:rows], w_k)
+            ws.q_full[:rows, self.rank * hl : (self.rank + 1) * hl, :L] = q_c
+            if self.world > 1:
+                self._allgather_heads(ws.q_full[:rows])
+
+        if full:
+            native.indexer_score(ws.q_idx, ws.head_w, state.index_cache, row_pos, row_lane, rows, IH, D, g.index_slot(layer),
+                                 len(g.full_layers), cache.local_capacity, cache.stripe, self.world, self.rank,
+                                 cache.context_capacity, max_ctx, ws.score_stride, self.index_scale, ws.scores,
+                                 ws.r_scores.offset if fused else 0, kc, native.SIG_SCORES, self.peer.status_ptr)
+            if self.world > 1 and not fused:
+                self._merge_scores(ws.scores[:rows], max_ctx)
+            native.topk_select(ws.scores, row_pos, rows, cache.context_capacity, ws.score_stride, g.index_top_k, cache.stripe,
+                               self.world, self.rank, ws.sel_global, ws.sel_local, ws.sel_counts, kc, native.SIG_SCORES)
+            if self.trace is not None:
+                self.trace.setdefault("sel_global", {})[layer] = ws.sel_global[:rows].clone()
+                self.trace.setdefault("scores", {})[layer] = ws.scores[:rows].clone()
+
+        # owner-local partial attention for ALL heads, in passes of attn_rows query rows
+        for r0 in range(0, rows, ws.attn_rows):
+            n = min(ws.attn_rows, rows - r0)
+            native.sparse_mla_partial(ws.q_full[r0:], state.kv_cache, ws.sel_local[r0:], ws.sel_counts[r0:], row_lane[r0:], n, ht, L, rd,
+                                      layer, g.num_layers, cache.local_capacity, g.index_top_k, ws.max_chunks, self.softmax_scale,
+                                      ws.part_o, ws.part_ml, kc, native.SIG_Q if fused else -1, self.peer.status_ptr)
+            if self.world == 1:
+                native.attn_local_merge(ws.part_o, ws.part_ml, ws.sel_counts[r0:], n, ht, L, g.index_top_k, ws.max_chunks, ws.o_lat[r0:], hl)
+            elif fused:
+                native.attn_local_merge(ws.part_o, ws.part_ml, ws.sel_counts[r0:], n, ht, L, g.index_top_k, ws.max_chunks, None, hl,
+                                        ws.r_xpart.offset, kc, native.SIG_ATTN)
+                native.attn_final_merge(n, L, hl, ws.r_xpart.offset, ws.o_lat[r0:], kc, native.SIG_ATTN)
+            else:
+                self._merge_partials_nccl(ws, r0, n)
+        # value projection per head, then the K-split output projection with its reduction
+        if decode:
+            native.skinny_bf16(ws.o_lat, lw.kv_b[:, g.qk_nope_head_dim :, :], ws.attn_v, native.SK_OUT_BF16, rows=rows, N=g.v_head_dim,
+                               K=L, xs=hl * L, ws=L, os_=hl * g.v_head_dim, batch=hl, xb=L, wb=g.kv_b_rows_per_head * L, ob=g.v_head_dim)
+            if fused or self.world == 1:
+                native.skinny_bf16(ws.attn_v[:rows], lw.w_o, ws.attn_out, native.SK_OUT_ALLREDUCE_BF16, comm=kc, channel=native.CH_ATTN)
+            else:
+                native.skinny_bf16(ws.attn_v[:rows], lw.w_o, ws.partial, native.SK_OUT_F32)
+                ws.attn_out[:rows] = self._allreduce_rows(ws.partial[:rows]).to(torch.bfloat16)
+        else:
+            w_v = lw.kv_b[:, g.qk_nope_head_dim :, :]  # [hl, v, L]
+            v = torch.einsum("rhc,hvc->rhv", ws.o_lat[:rows], w_v).reshape(rows, hl * g.v_head_dim)
+            if self.world == 1:
+                ws.attn_out[:rows] = torch.mm(v, lw.w_o.t())
+            else:
+                part = torch.mm(v, lw.w_o.t(), out_dtype=torch.float32)
+                ws.attn_out[:rows] = self._allreduce_rows(part).to(torch.bfloat16)
+        if self.trace is not None:
+            self.trace.setdefault("attn_out", {})[layer] = ws.attn_out[:rows].clone()
+            self.trace.setdefault("kv_new", {})[layer] = ws.kv_new[:rows].clone()
+
+    # NCCL baseline pieces ---------------------------------------------------------------------
+    def _allgather_heads(self, q_full: torch.Tensor) -> None:
+        import torch.distributed as dist
+
+        hl = self.layout.heads_local
+        mine = q_full[:, self.rank * hl : (self.rank + 1) * hl].contiguous()
+        parts = [torch.empty_like(mine) for _ in range(self.world)]
+        dist.all_gather(parts, mine, group=self.group)
+        for p, part in enumerate(parts):
+            q_full[:, p * hl : (p + 1) * hl] = part
+
+    def _merge_scores(self, scores: torch.Tensor, max_ctx: int) -> None:
+        """Every rank wrote only the positions it owns; combine with a masked sum (other entries zeroed first)."""
+        import torch.distributed as dist
+
+        pos = torch.arange(max_ctx, device=scores.device)
+        mine = ((pos // self.cache.stripe) % self.world) == self.rank
+        view = scores[:, :max_ctx]
+        view.mul_(mine.to(view.dtype)[None, :])
+        view.nan_to_num_(0.0, 0.0, 0.0)
+        dist.all_reduce(view, group=self.group)
+
+    def _merge_partials_nccl(self, ws: Workspace, r0: int, n: int) -> None:
+        import torch.distributed as dist
+
+        g, hl = self.g, self.layout.heads_local
+        L, ht = g.kv_lora_rank, g.attention_heads
+        counts = ws.sel_counts[r0 : r0 + n, 1].clamp(0, g.index_top_k)
+        chunks = (counts + native.attn_chunk() - 1) // native.attn_chunk()
+        valid = torch.arange(ws.max_chunks, device=self.device)[None, :] < chunks[:, None]  # [n, chunks]
+        m = torch.where(valid[:, :, None], ws.part_ml[:n, :, :, 0], torch.tensor(float("-inf"), device=self.device))
+        M = m.max(dim=1).values  # [n, ht]
+        wgt = torch.where(valid[:, :, None], torch.exp(m - M[:, None, :]), torch.zeros((), device=self.device))
+        wgt = torch.nan_to_num(wgt, nan=0.0)
+        o = (ws.part_o[:n] * wgt[..., None]).sum(dim=1)  # [n, ht, L]
+        l = (torch.where(valid[:, :, None], ws.part_ml[:n, :, :, 1], torch.zeros((), device=self.device)) * wgt).sum(dim=1)
+        packed = torch.cat([o, M[..., None], l[..., None]], dim=-1)  # [n, ht, L+2]
+        gathered = [torch.empty_like(packed) for _ in range(self.world)]
+        dist.all_gather(gathered, packed.contiguous(), group=self.group)
+        allp = torch.stack(gathered)[:, :, self.rank * hl : (self.rank + 1) * hl]  # [world, n, hl, L+2]
+        Mg = allp[..., L].max(dim=0).values
+        wg = torch.nan_to_num(torch.exp(allp[..., L] - Mg[None]), nan=0.0)
+        num = (allp[..., :L] * wg[..., None]).sum(dim=0)
+        den = (allp[..., L + 1] * wg).sum(dim=0)
+        out = torch.where(den[..., None] > 0, num / den[..., None], torch.zeros((), device=self.device))
+        ws.o_lat[r0 : r0 + n] = out.to(torch.bfloat16)
+
+    # ------------------------------------------------------------------------------ MLP
+    def _mlp(self, ws: Workspace, lw: LayerWeights, layer: int, rows: int, decode: bool):
+        g, lay = self.g, self.layout
+        H = g.hidden_size
+        fused = ws.peer_visible
+        kc = self.peer.comm if fused else None
+        x = ws.x[:rows]
+        if g.mlp_layer_types[layer] == "dense":
+            if decode:
+                native.skinny_bf16_swiglu(x, lw.dense_gate, lw.dense_up, ws.dense_act)
+                if fused or self.world == 1:
+                    native.skinny_bf16(ws.dense_act[:rows], lw.dense_down, ws.update, native.SK_OUT_ALLREDUCE_BF16, comm=kc,
+                                       channel=native.CH_MLP)
+                else:
+                    native.skinny_bf16(ws.dense_act[:rows], lw.dense_down, ws.partial, native.SK_OUT_F32)
+                    ws.update[:rows] = self._allreduce_rows(ws.partial[:rows]).to(torch.bfloat16)
+            else:
+                gate, up = torch.mm(x, lw.dense_gate.t()).float(), torch.mm(x, lw.dense_up.t()).float()
+                act = (gate * torch.sigmoid(gate) * up).to(torch.bfloat16)
+                if self.world == 1:
+                    ws.update[:rows] = torch.mm(act, lw.dense_down.t())
+                else:
+                    ws.update[:rows] = self._allreduce_rows(torch.mm(act, lw.dense_down.t(), out_dtype=torch.float32)).to(torch.bfloat16)
+            return
+        tk, I, E = g.routed_top_k, g.moe_intermediate_size, g.num_routed_experts
+        el, ebase = lay.experts_local, self.rank * lay.experts_local
+        self._linear_f32(x, lw.router_w, ws.router_logits, decode)
+        native.router_topk(ws.router_logits[:rows], lw.router_bias, tk, ws.topk_ids, ws.topk_w)
+        if self.trace is not None:
+            self.trace.setdefault("topk_ids", {})[layer] = ws.topk_ids[:rows].clone()
+            self.trace.setdefault("topk_w", {})[layer] = ws.topk_w[:rows].clone()
+        if decode:
+            tile_expert, tile_routes, n_tiles, tiles, rt = ws.topk_ids, None, None, rows * tk, 1
+        else:
+            tile_expert, tile_routes, n_tiles, tiles, rt = self._route_tiles(ws.topk_ids[:rows], E)
+        native.moe_gateup_fp8(x, tk, tile_expert, tile_routes, n_tiles, tiles, rt, lw.exp_gate_bits, lw.exp_up_bits, lw.exp_gate_scale,
+                              lw.exp_up_scale, ebase, ws.act)
+        native.moe_down_fp8(ws.act, ws.topk_w, tile_expert, tile_routes, n_tiles, tiles, rt, lw.exp_down_bits, lw.exp_down_scale, ebase,
+                            ws.dw)
+        if decode:
+            native.skinny_bf16_swiglu(x, lw.shared_gate, lw.shared_up, ws.act_shared)
+            native.skinny_bf16(ws.act_shared[:rows], lw.shared_down, ws.partial, native.SK_OUT_F32)
+            shared_partial = ws.partial
+        else:
+            gate, up = torch.mm(x, lw.shared_gate.t()).float(), torch.mm(x, lw.shared_up.t()).float()
+            act = (gate * torch.sigmoid(gate) * up).to(torch.bfloat16)
+            shared_partial = torch.mm(act, lw.shared_down.t(), out_dtype=torch.float32)
+        if fused or self.world == 1:
+            native.moe_combine(ws.dw, ws.topk_ids, shared_partial, rows, tk, H, ebase, el, g.routed_scaling_factor, False, ws.update,
+                               None, kc, native.CH_MLP)
+        else:
+            native.moe_combine(ws.dw, ws.topk_ids, shared_partial, rows, tk, H, ebase, el, g.routed_scaling_factor, False, None,
+                               ws.routed_partial)
+            both = torch.stack([ws.routed_partial[:rows], shared_partial[:rows]])
+            self._allreduce_rows(both)
+            routed = (both[0].to(torch.bfloat16).float() * g.routed_scaling_factor).to(torch.bfloat16).float()
+            ws.update[:rows] = (routed + both[1].to(torch.bfloat16).float()).to(torch.bfloat16)
+
+    def _route_tiles(self, topk_ids: torch.Tensor, E: int):
+        """Group routes by expert into tiles of 8 (device-side, no host sync)."""
+        ids = topk_ids.reshape(-1).long()
+        P = ids.numel()
+        order = torch.argsort(ids, stable=True)
+        counts = torch.bincount(ids, minlength=E)
+        tiles_per = (counts + 7) // 8
+        tile_end = torch.cumsum(tiles_per, 0)
+        route_start = torch.cumsum(counts, 0) - counts
+        max_tiles = P // 8 + E
+        t = torch.arange(max_tiles, device=ids.device)
+        expert = torch.searchsorted(tile_end, t, right=True).clamp(max=E - 1)
+        within = t - (tile_end[expert] - tiles_per[expert])
+        valid_tile = t < tile_end[-1]
+        slot = within[:, None] * 8 + torch.arange(8, device=ids.device)[None, :]
+        ok = valid_tile[:, None] & (slot < counts[expert][:, None])
+        src = (route_start[expert][:, None] + slot).clamp(max=P - 1)
+        routes = torch.where(ok, order[src], torch.full_like(src, -1)).to(torch.int32).contiguous()
+        tile_expert = torch.where(valid_tile, expert, torch.full_like(expert, -1)).to(torch.int32).contiguous()
+        n_tiles = tile_end[-1:].to(torch.int32).contiguous()
+        return tile_expert, routes, n_tiles, max_tiles, 8
+
+    # ------------------------------------------------------------------------------ whole model
+    def run_rows(self, ws: Workspace, state: DecoderState, tokens: torch.Tensor, row_pos: torch.Tensor, row_lane: torch.Tensor,
+                 row_active, rows: int, *, decode: bool, max_ctx: int, head_rows: slice | None = None) -> torch.Tensor:
+        """Push ``rows`` token rows through the decoder; returns the bf16 logits of ``head_rows`` (vocabulary slice)."""
+        g = self.g
+        native.embed_rows(tokens, self.w.embed, ws.residual, self.peer.status_ptr)
+        update = None
+        for i, lw in enumerate(self.w.layers):
+            native.add_rmsnorm(update, ws.residual[:rows], lw.input_norm, ws.x, g.rms_norm_eps)
+            self._attention(ws, lw, i, rows, row_pos, row_lane, row_active, state, decode, max_ctx)
+            native.add_rmsnorm(ws.attn_out, ws.residual[:rows], lw.post_norm, ws.x, g.rms_norm_eps)
+            self._mlp(ws, lw, i, rows, decode)
+            update = ws.update
+            if self.trace is not None:
+                self.trace.setdefault("update", {})[i] = ws.update[:rows].clone()
+        native.add_rmsnorm(update, ws.residual[:rows], self.w.final_norm, ws.x, g.rms_norm_eps)
+        hs = head_rows or slice(0, rows)
+        xh = ws.x[hs]
+        n = xh.shape[0]
+        if n <= native.MAX_ROWS:
+            native.skinny_bf16(xh, self.w.lm_head, ws.logits, native.SK_OUT_BF16)
+        else:
+            ws.logits[:n] = torch.mm(xh, self.w.lm_head.t())
+        return ws.logits[:n]
+
+    def sample(self, ws: Workspace, state: DecoderState, logits: torch.Tensor, rows: int, row_active, *, advance: int,
+               tokens_out=None, positions=None, out=None) -> None:
+        """Greedy sampling with the cross-GPU candidate exchange.
+
+        ``advance`` bit 0 stores the token into ``tokens_out`` (default: the lane registers), bit 1 increments the
+        positions.  The token also goes to ``out`` (``[rows]`` int32) or, by default, to the ``out_tokens`` ring.
+        """
+        lay = self.layout
+        fused = ws.peer_visible
+        kc = self.peer.comm if fused else None
+        native.argmax_rows(logits, rows, lay.vocab_local, self.rank * lay.vocab_local, ws.cand, ws.r_cand.offset if fused else 0, kc,
+                           native.SIG_SAMPLE, self.peer.status_ptr)
+        cand = ws.cand
+        if self.world > 1 and not fused:
+            import torch.distributed as dist
+
+            mine = ws.cand[0, :rows].contiguous()  # without a PeerComm the kernel writes set 0
+            parts = [torch.empty_like(mine) for _ in range(self.world)]
+            dist.all_gather(parts, mine, group=self.group)
+            cand = torch.stack(parts).contiguous()
+        tokens = tokens_out if tokens_out is not None else state.tokens
+        pos = positions if positions is not None else state.positions
+        if out is None:
+            out, counter, ring = state.out_tokens, state.step_counter, RING
+        else:
+            counter, ring = None, 1
+        native.step_finalize(cand, self.world, rows, row_active, tokens, pos, out, counter, ring, advance, kc, native.SIG_SAMPLE)

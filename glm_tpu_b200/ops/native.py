@@ -1,0 +1,291 @@
+"""ctypes binding of ``libglmb200.so`` (the hand-written sm_100a kernels).
+
+The library is built in-tree by ``glm_tpu_b200.csrc.build`` and loaded with ``ctypes`` (it links only the
+CUDA runtime).  Every wrapper takes torch CUDA tensors, passes raw device pointers plus the current torch
+stream, and raises on a non-zero return code.  There is no fallback: if the library is missing or a launch
+fails on a GPU machine the call raises.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+import torch
+
+LIB_PATH = Path(__file__).resolve().parent / "libglmb200.so"
+MAX_WORLD = 8
+MAX_ROWS = 8
+
+SK_OUT_F32, SK_OUT_BF16, SK_OUT_ALLREDUCE_BF16 = 0, 1, 2
+STATUS_WAIT_TIMEOUT, STATUS_BAD_INDEX, STATUS_NONFINITE, STATUS_BAD_SHAPE = 1, 2, 4, 8
+
+# signals (producer -> consumer exchanges) and all-reduce channels used by the model
+SIG_Q, SIG_SCORES, SIG_ATTN, SIG_SAMPLE, SIG_TEST = 0, 1, 2, 3, 15
+CH_ATTN, CH_MLP = 0, 1
+
+
+class PeerComm(C.Structure):
+    _fields_ = [
+        ("world", C.c_int),
+        ("rank", C.c_int),
+        ("wait_limit", C.c_uint32),
+        ("pad_", C.c_uint32),
+        ("status", C.c_void_p),
+        ("seq", C.c_void_p),
+        ("data", C.c_void_p * MAX_WORLD),
+        ("flags", C.c_void_p * MAX_WORLD),
+    ]
+
+
+class QkvPostArgs(C.Structure):
+    _fields_ = [
+        ("proj", C.c_void_p), ("proj_stride", C.c_int64),
+        ("q_norm_w", C.c_void_p), ("kv_norm_w", C.c_void_p), ("rope_table", C.c_void_p), ("inv_freq", C.c_void_p),
+        ("k_norm_w", C.c_void_p), ("k_norm_b", C.c_void_p),
+        ("row_pos", C.c_void_p), ("row_lane", C.c_void_p), ("row_active", C.c_void_p),
+        ("q_resid", C.c_void_p), ("kv_new", C.c_void_p), ("kv_cache", C.c_void_p), ("index_cache", C.c_void_p),
+        ("head_w", C.c_void_p), ("idx_key_new", C.c_void_p),
+        ("Q", C.c_int), ("L", C.c_int), ("rd", C.c_int), ("D", C.c_int), ("IH", C.c_int),
+        ("has_indexer", C.c_int),
+        ("layer", C.c_int), ("layers", C.c_int), ("index_slot", C.c_int), ("full_layers", C.c_int), ("local_cap", C.c_int),
+        ("stripe", C.c_int), ("world", C.c_int), ("rank", C.c_int), ("capacity", C.c_int),
+        ("eps", C.c_float), ("key_eps", C.c_float), ("head_scale", C.c_float),
+        ("status", C.c_void_p),
+    ]
+
+
+class QPostArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("q_stride", C.c_int64),
+        ("rope_table", C.c_void_p), ("inv_freq", C.c_void_p), ("row_pos", C.c_void_p),
+        ("q_nope", C.c_void_p), ("q_full", C.c_void_p), ("q_idx", C.c_void_p),
+        ("heads_local", C.c_int), ("head_base", C.c_int), ("heads_total", C.c_int), ("nope", C.c_int), ("rd", C.c_int),
+        ("L", C.c_int), ("IH", C.c_int), ("D", C.c_int), ("has_indexer", C.c_int), ("capacity", C.c_int),
+    ]
+
+
+_lib = None
+
+
+def available() -> bool:
+    return LIB_PATH.exists()
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise RuntimeError(f"{LIB_PATH} is missing: run `python -m glm_tpu_b200.csrc.build`")
+        _lib = C.CDLL(str(LIB_PATH))
+        _lib.glmb_peer_ar_bytes.restype = C.c_size_t
+        _lib.glmb_peer_comm_sizeof.restype = C.c_size_t
+        _lib.glmb_peer_data.restype = C.c_void_p
+        _lib.glmb_peer_status_ptr.restype = C.c_void_p
+        if _lib.glmb_peer_comm_sizeof() != C.sizeof(PeerComm):
+            raise RuntimeError("PeerComm layout differs between Python and the CUDA library")
+    return _lib
+
+
+def _p(t):
+    if t is None:
+        return None
+    if isinstance(t, int):
+        return C.c_void_p(t)
+    return C.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(code: int, what: str) -> None:
+    if code != 0:
+        raise RuntimeError(f"{what} failed with code {code}")
+
+
+def _comm(comm):
+    return C.byref(comm) if comm is not None else None
+
+
+def f32(x: float) -> C.c_float:
+    return C.c_float(x)
+
+
+# ----------------------------------------------------------------------------- projections
+def skinny_bf16(x, w, out, mode=SK_OUT_F32, *, rows=None, comm=None, channel=0, batch=1, xb=0, wb=0, ob=0, N=None, K=None,
+                xs=None, ws=None, os_=None):
+    """``out[r, n] = sum_k x[r, k] w[n, k]`` for 1..8 rows; see ``glmb_skinny_bf16``."""
+    rows = x.shape[0] if rows is None else rows
+    N = w.shape[-2] if N is None else N
+    K = w.shape[-1] if K is None else K
+    xs = x.stride(0) if xs is None else xs
+    ws = w.stride(-2) if ws is None else ws
+    os_ = out.stride(0) if os_ is None else os_
+    _check(
+        lib().glmb_skinny_bf16(_p(x), C.c_int64(xs), rows, _p(w), C.c_int64(ws), N, K, _p(out), C.c_int64(os_), mode, batch,
+                               C.c_int64(xb), C.c_int64(wb), C.c_int64(ob), _comm(comm), channel, _stream()),
+        "skinny_bf16",
+    )
+
+
+def skinny_bf16_swiglu(x, wg, wu, act):
+    _check(
+        lib().glmb_skinny_bf16_swiglu(_p(x), C.c_int64(x.stride(0)), x.shape[0], _p(wg), _p(wu), C.c_int64(wg.stride(0)),
+                                      wg.shape[0], wg.shape[1], _p(act), C.c_int64(act.stride(0)), _stream()),
+        "skinny_bf16_swiglu",
+    )
+
+
+def moe_gateup_fp8(x, top_k, tile_expert, tile_routes, n_tiles, tiles, rt, wg, wu, sg, su, expert_base, act):
+    experts_local, I, H = wg.shape
+    _check(
+        lib().glmb_moe_gateup_fp8(_p(x), C.c_int64(x.stride(0)), top_k, _p(tile_expert), _p(tile_routes), _p(n_tiles), tiles, rt,
+                                  _p(wg), _p(wu), _p(sg), _p(su), expert_base, experts_local, I, H, _p(act), _stream()),
+        "moe_gateup_fp8",
+    )
+
+
+def moe_down_fp8(act, route_weight, tile_expert, tile_routes, n_tiles, tiles, rt, wd, sd, expert_base, dw):
+    experts_local, H, I = wd.shape
+    _check(
+        lib().glmb_moe_down_fp8(_p(act), _p(route_weight), _p(tile_expert), _p(tile_routes), _p(n_tiles), tiles, rt, _p(wd),
+                                _p(sd), expert_base, experts_local, I, H, _p(dw), _stream()),
+        "moe_down_fp8",
+    )
+
+
+def moe_combine(dw, topk_ids, shared_partial, rows, top_k, H, expert_base, experts_local, scale, plain, out, routed_partial=None,
+                comm=None, channel=CH_MLP):
+    _check(
+        lib().glmb_moe_combine(_p(dw), _p(topk_ids), _p(shared_partial), rows, top_k, H, expert_base, experts_local, f32(scale),
+                               int(plain), _p(out), _p(routed_partial), _comm(comm), channel, _stream()),
+        "moe_combine",
+    )
+
+
+# ----------------------------------------------------------------------------- norms / rope / queries
+def embed_rows(tokens, table, residual, status):
+    _check(lib().glmb_embed_rows(_p(tokens), _p(table), tokens.shape[0], table.shape[0], table.shape[1], _p(residual), _p(status),
+                                 _stream()), "embed_rows")
+
+
+def add_rmsnorm(update, residual, weight, out, eps):
+    rows, H = residual.shape
+    _check(lib().glmb_add_rmsnorm(_p(update), _p(residual), _p(weight), _p(out), rows, H, f32(eps), _stream()), "add_rmsnorm")
+
+
+def qkv_a_post(args: QkvPostArgs, rows: int):
+    _check(lib().glmb_qkv_a_post(C.byref(args), rows, _stream()), "qkv_a_post")
+
+
+def q_post(args: QPostArgs, rows: int):
+    _check(lib().glmb_q_post(C.byref(args), rows, _stream()), "q_post")
+
+
+def q_absorb(q_nope, rows, kv_b, heads_local, head_base, heads_total, nope, vdim, L, rd, q_full, q_full_offset=0, comm=None,
+             sig=SIG_Q):
+    _check(
+        lib().glmb_q_absorb(_p(q_nope), rows, _p(kv_b), heads_local, head_base, heads_total, nope, vdim, L, rd, _p(q_full),
+                            C.c_int64(q_full_offset), _comm(comm), sig, _stream()),
+        "q_absorb",
+    )
+
+
+# ----------------------------------------------------------------------------- indexer
+def indexer_score(q_idx, head_w, index_cache, row_pos, row_lane, rows, IH, D, index_slot, full_layers, local_cap, stripe, world,
+                  rank, capacity, max_ctx, score_stride, scale, scores, scores_offset=0, comm=None, sig=SIG_SCORES, status=None):
+    _check(
+        lib().glmb_indexer_score(_p(q_idx), _p(head_w), _p(index_cache), _p(row_pos), _p(row_lane), rows, IH, D, index_slot,
+                                 full_layers, local_cap, stripe, world, rank, capacity, max_ctx, C.c_int64(score_stride),
+                                 f32(scale), _p(scores), C.c_int64(scores_offset), _comm(comm), sig, _p(status), _stream()),
+        "indexer_score",
+    )
+
+
+def topk_select(scores, row_pos, rows, capacity, score_stride, top_k, stripe, world, rank, sel_global, sel_local, sel_counts,
+                comm=None, sig=SIG_SCORES):
+    _check(
+        lib().glmb_topk_select(_p(scores), _p(row_pos), rows, capacity, C.c_int64(score_stride), top_k, stripe, world, rank,
+                               _p(sel_global), _p(sel_local), _p(sel_counts), _comm(comm), sig, _stream()),
+        "topk_select",
+    )
+
+
+# ----------------------------------------------------------------------------- attention
+def attn_chunk() -> int:
+    return lib().glmb_attn_chunk()
+
+
+def sparse_mla_partial(q_full, kv_cache, sel_local, sel_counts, row_lane, rows, H, L, rd, layer, layers, local_cap, top_k,
+                       max_chunks, scale, part_o, part_ml, comm=None, wait_sig=-1, status=None):
+    _check(
+        lib().glmb_sparse_mla_partial(_p(q_full), _p(kv_cache), _p(sel_local), _p(sel_counts), _p(row_lane), rows, H, L, rd, layer,
+                                      layers, local_cap, top_k, max_chunks, f32(scale), _p(part_o), _p(part_ml), _comm(comm),
+                                      wait_sig, _p(status), _stream()),
+        "sparse_mla_partial",
+    )
+
+
+def attn_local_merge(part_o, part_ml, sel_counts, rows, H, L, top_k, max_chunks, o_lat, heads_local, xpart_offset=0, comm=None,
+                     sig=SIG_ATTN):
+    _check(
+        lib().glmb_attn_local_merge(_p(part_o), _p(part_ml), _p(sel_counts), rows, H, L, top_k, max_chunks, _p(o_lat), heads_local,
+                                    C.c_int64(xpart_offset), _comm(comm), sig, _stream()),
+        "attn_local_merge",
+    )
+
+
+def attn_final_merge(rows, L, heads_local, xpart_offset, o_lat, comm, sig=SIG_ATTN):
+    _check(lib().glmb_attn_final_merge(rows, L, heads_local, C.c_int64(xpart_offset), _p(o_lat), _comm(comm), sig, _stream()),
+           "attn_final_merge")
+
+
+# ----------------------------------------------------------------------------- router / sampler / misc
+def router_topk(logits, bias, top_k, ids, weights):
+    rows, E = logits.shape
+    _check(lib().glmb_router_topk(_p(logits), _p(bias), rows, E, top_k, _p(ids), _p(weights), _stream()), "router_topk")
+
+
+def argmax_rows(logits, rows, V, vocab_base, cand, cand_offset=0, comm=None, sig=SIG_SAMPLE, status=None):
+    _check(
+        lib().glmb_argmax_rows(_p(logits), C.c_int64(logits.stride(0)), rows, V, vocab_base, _p(cand), C.c_int64(cand_offset),
+                               _comm(comm), sig, _p(status), _stream()),
+        "argmax_rows",
+    )
+
+
+def step_finalize(cand, n_sets, rows, row_active, tokens, positions, out_tokens, step_counter, ring, advance, comm=None,
+                  sig=SIG_SAMPLE):
+    """advance: bit 0 writes the sampled token into ``tokens``, bit 1 increments ``positions``."""
+    _check(
+        lib().glmb_step_finalize(_p(cand), n_sets, rows, _p(row_active), _p(tokens), _p(positions), _p(out_tokens), _p(step_counter), ring,
+                                 int(advance), _comm(comm), sig, _stream()),
+        "step_finalize",
+    )
+
+
+def fp8_to_bf16(bits, scale, out, block=(128, 128), status=None):
+    N, K = bits.shape[-2], bits.shape[-1]
+    lead = bits.numel() // (N * K)
+    if lead != 1:
+        for i in range(lead):
+            fp8_to_bf16(bits.reshape(lead, N, K)[i], scale.reshape(lead, *scale.shape[-2:])[i], out.reshape(lead, N, K)[i], block,
+                        status)
+        return
+    _check(lib().glmb_fp8_to_bf16(_p(bits), _p(scale), C.c_int64(N), C.c_int64(K), block[0], block[1], _p(out), _p(status),
+                                  _stream()), "fp8_to_bf16")
+
+
+def fill_random_fp8(out, seed):
+    _check(lib().glmb_fill_random_fp8(_p(out), C.c_int64(out.numel()), C.c_uint64(seed), _stream()), "fill_random_fp8")
+
+
+def fill_random_bf16(out, seed, mean=0.0, std=0.02):
+    _check(lib().glmb_fill_random_bf16(_p(out), C.c_int64(out.numel()), C.c_uint64(seed), f32(mean), f32(std), _stream()),
+           "fill_random_bf16")
+
+
+def fill_uniform_f32(out, seed, lo, hi):
+    _check(lib().glmb_fill_uniform_f32(_p(out), C.c_int64(out.numel()), C.c_uint64(seed), f32(lo), f32(hi), _stream()),
+           "fill_uniform_f32")

@@ -1,0 +1,199 @@
+"""Per-GPU model runner: resident weights, caches, the prefill program and the CUDA-graph decode program.
+
+The runner is what the engine drives.  It owns
+
+* the resident weights (``DeviceWeights``) and the peer-buffer registry,
+* the device state for ``lanes`` concurrent chats (striped KV/index caches, token/position registers),
+* the *decode program*: one token for every lane, captured once in a CUDA graph and replayed per step
+  (positions and tokens live in device memory, so the graph is static),
+* the *prefill program*: chunks of one lane's prompt, launched eagerly.
+
+Parity: reference ``glm_tpu/runner/tpu_runner.py:29-289`` (load phases, program set, batch programs),
+``runner/programs.py:80-118``, ``runner/kv_cache_manager.py:15-57``, ``runner/compilation_manager.py:28-69``
+(here a program is a captured CUDA graph instead of a compiled XLA executable).
+"""
+
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+
+import torch
+
+from glm_tpu_b200.config.cache import CacheConfig
+from glm_tpu_b200.config.parallel import ParallelLayout
+from glm_tpu_b200.models.glm_moe_dsa.model import RING, DecoderState, GlmMoeDsaModel, Workspace
+from glm_tpu_b200.models.glm_moe_dsa.weights import DeviceWeights
+from glm_tpu_b200.parallel.peer import PeerGroup
+from glm_tpu_b200.runner.admission import project_memory
+
+
+@dataclass
+class ProgramRecord:
+    name: str
+    kind: str  # 'cuda_graph' or 'eager'
+    rows: int
+    launches: int
+    capture_seconds: float = 0.0
+
+
+@dataclass
+class RunnerReport:
+    phases: dict = field(default_factory=dict)
+    programs: list = field(default_factory=list)
+    memory: dict = field(default_factory=dict)
+
+
+class _LaunchCounter:
+    """Counts kernel launches issued through the native library while a program is being recorded."""
+
+    def __init__(self):
+        self.count = 0
+
+    def __enter__(self):
+        from glm_tpu_b200.ops import native
+
+        self._native = native
+        self._orig = native._check
+
+        def counting(code, what):
+            self.count += 1
+            self._orig(code, what)
+
+        native._check = counting
+        return self
+
+    def __exit__(self, *exc):
+        self._native._check = self._orig
+
+
+class GpuModelRunner:
+    def __init__(self, weights: DeviceWeights, *, context_capacity: int, lanes: int = 1, stripe: int = 64, comm: str = "fused",
+                 group=None, prefill_chunk: int = 512, use_graphs: bool = True, wait_limit: int = 2_000_000,
+                 staging_bytes: int | None = None):
+        self.weights = weights
+        self.g, self.layout = weights.geometry, weights.layout
+        self.device = weights.embed.device
+        self.world, self.rank = self.layout.world, self.layout.rank
+        self.cache = CacheConfig(self.g, context_capacity, world=self.world, stripe=stripe, lanes=lanes)
+        self.lanes = lanes
+        self.report = RunnerReport()
+        self.use_graphs = use_graphs
+        self.prefill_chunk = prefill_chunk
+        t0 = time.perf_counter()
+        if staging_bytes is None:
+            g = self.g
+            staging_bytes = lanes * (g.attention_heads * g.kv_row_width * 2 + context_capacity * 4
+                                     + self.world * self.layout.heads_local * (g.kv_lora_rank + 2) * 4 + self.world * 8) + (1 << 20)
+        with torch.cuda.device(self.device):
+            self.peer = PeerGroup(self.world, self.rank, staging_bytes=staging_bytes if self.world > 1 else 0,
+                                  wait_limit=wait_limit, group=group, device=self.device)
+            self.model = GlmMoeDsaModel(weights, self.cache, self.peer, comm=comm, group=group)
+            self.state = DecoderState.allocate(self.cache, self.device)
+            self.decode_ws = Workspace(self.model, lanes, "decode")
+            self.prefill_ws = None
+            self._prefill_out = torch.zeros(1, dtype=torch.int32, device=self.device)
+            self._graph = None
+            self._graph_stream = torch.cuda.Stream(device=self.device)
+        self.report.phases["allocate"] = time.perf_counter() - t0
+        self.report.memory = project_memory(self.g, self.layout, self.cache, weights.bytes_resident, staging_bytes)
+        self.decode_launches = 0
+
+    # ------------------------------------------------------------------ decode program
+    def _decode_body(self) -> None:
+        st, ws, m = self.state, self.decode_ws, self.model
+        logits = m.run_rows(ws, st, st.tokens, st.positions, st.lane_ids, st.active, self.lanes, decode=True,
+                            max_ctx=self.cache.context_capacity)
+        m.sample(ws, st, logits, self.lanes, st.active, advance=3)
+
+    def build_decode_program(self) -> ProgramRecord:
+        """Warm up eagerly (lanes inactive: no cache write, no advance), then capture the step in a CUDA graph."""
+        t0 = time.perf_counter()
+        with torch.cuda.device(self.device):
+            saved = self.state.active.clone()
+            self.state.active.zero_()
+            with _LaunchCounter() as counter:
+                self._decode_body()
+            self.decode_launches = counter.count
+            torch.cuda.synchronize(self.device)
+            kind = "eager"
+            if self.use_graphs and self.model.comm_mode == "fused" or (self.use_graphs and self.world == 1):
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=self._graph_stream):
+                    self._decode_body()
+                self._graph = graph
+                kind = "cuda_graph"
+            self.state.active.copy_(saved)
+            self.state.step_counter.zero_()
+            torch.cuda.synchronize(self.device)
+            self.peer.check_status()
+        rec = ProgramRecord("decode", kind, self.lanes, self.decode_launches, time.perf_counter() - t0)
+        self.report.programs.append(rec)
+        return rec
+
+    def decode_step(self) -> None:
+        """Enqueue one decode step for every active lane (asynchronous)."""
+        if self._graph is not None:
+            self._graph.replay()
+        else:
+            self._decode_body()
+
+    def read_step_tokens(self, step_index: int) -> list[int]:
+        """Tokens produced by decode step ``step_index`` (synchronizes; one small D2H copy)."""
+        row = self.state.out_tokens[step_index % RING].cpu()
+        return [int(v) for v in row]
+
+    # ------------------------------------------------------------------ prefill program
+    def _ensure_prefill_ws(self) -> Workspace:
+        if self.prefill_ws is None:
+            with torch.cuda.device(self.device):
+                self.prefill_ws = Workspace(self.model, self.prefill_chunk, "prefill", attn_rows=min(self.prefill_chunk, 64),
+                                            score_stride=self.cache.context_capacity, peer_visible=False)
+        return self.prefill_ws
+
+    def prefill(self, lane: int, token_ids) -> int:
+        """Run a prompt through ``lane`` with a fresh cache; returns the first generated token.
+
+        After the call the lane is active, its position is ``len(token_ids)`` and its next input is that token.
+        """
+        n = len(token_ids)
+        if not 0 < n < self.cache.context_capacity:
+            raise ValueError("prompt does not fit the context capacity")
+        ws = self._ensure_prefill_ws()
+        st, m = self.state, self.model
+        with torch.cuda.device(self.device):
+            ids = torch.as_tensor(list(token_ids), dtype=torch.int32).pin_memory().to(self.device, non_blocking=True)
+            lane_t = torch.full((self.prefill_chunk,), lane, dtype=torch.int32, device=self.device)
+            st.reset_lane(lane)
+            logits = None
+            for start in range(0, n, self.prefill_chunk):
+                rows = min(self.prefill_chunk, n - start)
+                pos = torch.arange(start, start + rows, dtype=torch.int32, device=self.device)
+                last = start + rows == n
+                logits = m.run_rows(ws, st, ids[start : start + rows], pos, lane_t, None, rows, decode=False, max_ctx=start + rows,
+                                    head_rows=slice(rows - 1, rows) if last else slice(0, 1))
+            m.sample(ws, st, logits, 1, None, advance=1, tokens_out=st.tokens[lane : lane + 1], positions=st.positions[lane : lane + 1],
+                     out=self._prefill_out)
+            st.positions[lane] = n
+            st.active[lane] = 1
+            token = int(self._prefill_out.cpu()[0])
+            self.peer.check_status()
+        return token
+
+    def deactivate(self, lane: int) -> None:
+        self.state.active[lane] = 0
+
+    def close(self) -> None:
+        self._graph = None
+        self.peer.close()
+
+
+def build_runner(geometry, *, world: int = 1, rank: int = 0, device=None, checkpoint=None, seed: int = 0, **kwargs) -> GpuModelRunner:
+    """Convenience constructor: shard ``checkpoint`` (a runtime-layout mapping) or random-init on the device."""
+    from glm_tpu_b200.models.glm_moe_dsa.weights import random_device_weights, shard_checkpoint
+
+    device = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
+    layout = ParallelLayout(geometry, world, rank)
+    with torch.cuda.device(device):
+        weights = shard_checkpoint(checkpoint, layout, device) if checkpoint is not None else random_device_weights(layout, device, seed)
+    return GpuModelRunner(weights, **kwargs)

@@ -1,0 +1,285 @@
+"""Numerics of each CUDA kernel against the plain-PyTorch fp32 restatement of the same operation (B200 only)."""
+
+import pytest
+import torch
+
+from glm_tpu_b200.oracle import contract
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def bf(x):
+    return x.to(torch.bfloat16)
+
+
+def close(a, b, rtol=2**-7, atol=1e-5):
+    a, b = a.float().cpu(), b.float().cpu()
+    return torch.allclose(a, b, rtol=rtol, atol=atol), (a - b).abs().max().item()
+
+
+@pytest.mark.parametrize("rows", [1, 3, 8])
+@pytest.mark.parametrize("N,K", [(96, 256), (2784, 6144), (37, 64)])
+def test_skinny_bf16(native_lib, rows, N, K):
+    n = native_lib
+    torch.manual_seed(0)
+    x = bf(torch.randn(rows, K, device=DEV))
+    w = bf(torch.randn(N, K, device=DEV) * 0.05)
+    ref = x.float() @ w.float().T
+    out = torch.zeros(rows, N, device=DEV)
+    n.skinny_bf16(x, w, out, n.SK_OUT_F32)
+    ok, err = close(out, ref, rtol=1e-4, atol=1e-3)
+    assert ok, err
+    out16 = torch.zeros(rows, N, dtype=torch.bfloat16, device=DEV)
+    n.skinny_bf16(x, w, out16, n.SK_OUT_BF16)
+    ok, err = close(out16, bf(ref), rtol=2**-7, atol=1e-3)
+    assert ok, err
+    out_ar = torch.zeros(rows, N, dtype=torch.bfloat16, device=DEV)
+    n.skinny_bf16(x, w, out_ar, n.SK_OUT_ALLREDUCE_BF16)  # single GPU: plain store
+    assert torch.equal(out_ar, out16)
+
+
+def test_skinny_batched_heads(native_lib):
+    n = native_lib
+    torch.manual_seed(1)
+    rows, heads, L, v, nope = 4, 8, 128, 64, 64
+    o_lat = bf(torch.randn(rows, heads, L, device=DEV))
+    kv_b = bf(torch.randn(heads, nope + v, L, device=DEV) * 0.1)
+    out = torch.zeros(rows, heads * v, dtype=torch.bfloat16, device=DEV)
+    n.skinny_bf16(o_lat, kv_b[:, nope:, :], out, n.SK_OUT_BF16, rows=rows, N=v, K=L, xs=heads * L, ws=L, os_=heads * v, batch=heads,
+                  xb=L, wb=(nope + v) * L, ob=v)
+    ref = torch.einsum("rhc,hvc->rhv", o_lat.float(), kv_b[:, nope:, :].float()).reshape(rows, heads * v)
+    ok, err = close(out, bf(ref), atol=1e-2)
+    assert ok, err
+
+
+def test_swiglu(native_lib):
+    n = native_lib
+    torch.manual_seed(2)
+    rows, N, K = 4, 200, 512
+    x = bf(torch.randn(rows, K, device=DEV))
+    wg, wu = bf(torch.randn(N, K, device=DEV) * 0.05), bf(torch.randn(N, K, device=DEV) * 0.05)
+    act = torch.zeros(rows, N, dtype=torch.bfloat16, device=DEV)
+    n.skinny_bf16_swiglu(x, wg, wu, act)
+    ref = contract.swiglu_act(contract.linear(x.cpu(), wg.cpu()), contract.linear(x.cpu(), wu.cpu()))
+    ok, err = close(act, ref, rtol=2**-6, atol=2e-3)
+    assert ok, err
+
+
+def test_fp8_decode_is_bit_exact(native_lib):
+    n = native_lib
+    torch.manual_seed(3)
+    bits = torch.randint(0, 256, (300, 520), dtype=torch.uint8)
+    bits[(bits & 0x7F) == 0x7F] = 0x3C  # no NaN codes
+    scale = torch.rand(3, 5) * 0.01 + 1e-4
+    ref = contract.dequantize_fp8(bits, scale)
+    out = torch.zeros(300, 520, dtype=torch.bfloat16, device=DEV)
+    n.fp8_to_bf16(bits.to(DEV), scale.to(DEV), out)
+    assert torch.equal(out.cpu().view(torch.int16), ref.view(torch.int16))
+
+
+def test_add_rmsnorm(native_lib):
+    n = native_lib
+    torch.manual_seed(4)
+    rows, H = 5, 6144
+    upd, res, w = bf(torch.randn(rows, H)), bf(torch.randn(rows, H)), bf(torch.randn(H) * 0.1 + 1)
+    ref_x, ref_res = contract.add_rms_norm(upd, res, w, 1e-5)
+    d_res, out = res.to(DEV).clone(), torch.zeros(rows, H, dtype=torch.bfloat16, device=DEV)
+    n.add_rmsnorm(upd.to(DEV), d_res, w.to(DEV), out, 1e-5)
+    assert torch.equal(d_res.cpu().float(), ref_res)
+    mism = (out.cpu().float() != ref_x).float().mean().item()
+    ok, err = close(out, ref_x, rtol=2**-7, atol=1e-6)
+    assert ok and mism < 0.01, (err, mism)
+    d_res2 = res.to(DEV).clone()
+    n.add_rmsnorm(None, d_res2, w.to(DEV), out, 1e-5)
+    ref_x2, _ = contract.add_rms_norm(None, res, w, 1e-5)
+    ok, err = close(out, ref_x2, rtol=2**-7, atol=1e-6)
+    assert ok, err
+
+
+def _routed_fixture(E, I, H, seed):
+    from glm_tpu_b200.models.glm_moe_dsa.weights import quantize_fp8
+
+    gen = torch.Generator().manual_seed(seed)
+    out = {}
+    for name, shape in (("gate", (E, I, H)), ("up", (E, I, H)), ("down", (E, H, I))):
+        bits, scale = quantize_fp8(torch.randn(shape, generator=gen) * 0.05, (128, 128), gen)
+        out[name] = (bits, scale)
+    return out
+
+
+@pytest.mark.parametrize("rows,tiled", [(3, False), (40, True)])
+def test_routed_experts(native_lib, rows, tiled):
+    n = native_lib
+    torch.manual_seed(5)
+    E, I, H, tk = 8, 256, 512, 2
+    fx = _routed_fixture(E, I, H, 5)
+    x = bf(torch.randn(rows, H) * 0.5)
+    ids = torch.stack([torch.randperm(E)[:tk] for _ in range(rows)]).to(torch.int32)
+    wts = torch.rand(rows, tk)
+    wts = wts / wts.sum(-1, keepdim=True)
+    deq = {k: contract.dequantize_fp8(*v) for k, v in fx.items()}
+    ref = torch.zeros(rows * tk, H)
+    for r in range(rows):
+        for s in range(tk):
+            e = int(ids[r, s])
+            act = contract.swiglu_act(contract.linear(x[r : r + 1], deq["gate"][e]), contract.linear(x[r : r + 1], deq["up"][e]))
+            ref[r * tk + s] = contract.bf16_round(contract.linear(act, deq["down"][e])[0] * contract.bf16_round(wts[r, s]))
+    d = {k: (v[0].to(DEV), v[1].to(DEV)) for k, v in fx.items()}
+    act = torch.zeros(rows * tk, I, dtype=torch.bfloat16, device=DEV)
+    dw = torch.zeros(rows * tk, H, dtype=torch.bfloat16, device=DEV)
+    ids_d, w_d, x_d = ids.to(DEV), wts.to(DEV), x.to(DEV)
+    if tiled:
+        from glm_tpu_b200.models.glm_moe_dsa.model import GlmMoeDsaModel
+
+        te, tr, nt, tiles, rt = GlmMoeDsaModel._route_tiles(None, ids_d, E)
+    else:
+        te, tr, nt, tiles, rt = ids_d, None, None, rows * tk, 1
+    n.moe_gateup_fp8(x_d, tk, te, tr, nt, tiles, rt, d["gate"][0], d["up"][0], d["gate"][1], d["up"][1], 0, act)
+    n.moe_down_fp8(act, w_d, te, tr, nt, tiles, rt, d["down"][0], d["down"][1], 0, dw)
+    ok, err = close(dw, ref, rtol=2**-5, atol=2e-3)
+    assert ok, err
+    # combine on one GPU: route sum, scale, shared
+    shared = torch.randn(rows, H)
+    out = torch.zeros(rows, H, dtype=torch.bfloat16, device=DEV)
+    n.moe_combine(dw, ids_d, shared.to(DEV), rows, tk, H, 0, E, 2.5, False, out)
+    routed = dw.float().cpu().reshape(rows, tk, H).sum(1)
+    ref_out = contract.bf16_round(contract.bf16_round(contract.bf16_round(routed) * 2.5) + contract.bf16_round(shared))
+    ok, err = close(out, ref_out, rtol=2**-7, atol=1e-3)
+    assert ok, err
+
+
+def test_router_topk(native_lib):
+    n = native_lib
+    torch.manual_seed(6)
+    rows, E, H, tk = 7, 256, 512, 8
+    x, w = bf(torch.randn(rows, H)), bf(torch.randn(E, H) * 0.05)
+    bias = torch.randn(E) * 0.02
+    logits = (x.float() @ w.float().T)
+    ids_ref, w_ref, _ = contract.router(x, w, bias, tk)
+    ids = torch.zeros(rows, tk, dtype=torch.int32, device=DEV)
+    wts = torch.zeros(rows, tk, device=DEV)
+    n.router_topk(logits.to(DEV), bias.to(DEV), tk, ids, wts)
+    assert torch.equal(ids.cpu().long(), ids_ref), (ids.cpu(), ids_ref)
+    ok, err = close(wts, w_ref, rtol=1e-5, atol=1e-6)
+    assert ok, err
+    # exact ties go to the lowest expert id
+    flat = torch.zeros(1, E)
+    n.router_topk(flat.to(DEV), torch.zeros(E, device=DEV), tk, ids, wts)
+    assert ids[0].cpu().tolist() == list(range(tk))
+
+
+@pytest.mark.parametrize("n_ctx,top_k", [(10, 16), (100, 16), (5000, 2048), (32768, 2048)])
+def test_topk_select_exact_with_ties(native_lib, n_ctx, top_k):
+    n = native_lib
+    torch.manual_seed(7)
+    cap = 32768
+    # coarse values force many ties at the boundary; include signed zeros
+    scores = (torch.randn(2, cap) * 3).round() / 4
+    scores[0, :50] = 0.0
+    scores[0, 50:60] = -0.0
+    pos = torch.tensor([n_ctx - 1, max(n_ctx // 2, 1) - 1], dtype=torch.int32)
+    sel_g = torch.zeros(2, top_k, dtype=torch.int32, device=DEV)
+    sel_l = torch.zeros(2, top_k, dtype=torch.int32, device=DEV)
+    cnt = torch.zeros(2, 2, dtype=torch.int32, device=DEV)
+    n.topk_select(scores.to(DEV), pos.to(DEV), 2, cap, cap, top_k, 64, 1, 0, sel_g, sel_l, cnt)
+    for r in range(2):
+        ctx = int(pos[r]) + 1
+        ref = contract.top_k_positions(scores[r], ctx, top_k)
+        k = ref.numel()
+        assert cnt[r].cpu().tolist() == [k, k]
+        assert torch.equal(sel_g[r, :k].cpu().long(), ref)
+        assert (sel_g[r, k:] == -1).all()
+        assert torch.equal(sel_l[r, :k].cpu().long(), ref)  # one GPU: local row == position
+
+
+def test_topk_select_striped_ownership(native_lib):
+    n = native_lib
+    torch.manual_seed(8)
+    cap, top_k, stripe, world = 4096, 256, 64, 4
+    scores = torch.randn(1, cap)
+    pos = torch.tensor([3000], dtype=torch.int32)
+    ref = contract.top_k_positions(scores[0], 3001, top_k)
+    for rank in range(world):
+        sel_g = torch.zeros(1, top_k, dtype=torch.int32, device=DEV)
+        sel_l = torch.zeros(1, top_k, dtype=torch.int32, device=DEV)
+        cnt = torch.zeros(1, 2, dtype=torch.int32, device=DEV)
+        n.topk_select(scores.to(DEV), pos.to(DEV), 1, cap, cap, top_k, stripe, world, rank, sel_g, sel_l, cnt)
+        assert torch.equal(sel_g[0].cpu().long(), ref)
+        mine = ref[(ref // stripe) % world == rank]
+        local = (mine // (stripe * world)) * stripe + mine % stripe
+        assert int(cnt[0, 1]) == mine.numel()
+        assert torch.equal(sel_l[0, : mine.numel()].cpu().long(), local)
+
+
+def test_indexer_score(native_lib):
+    n = native_lib
+    torch.manual_seed(9)
+    rows, IH, D, cap, ctx = 2, 32, 128, 4096, 3000
+    q = torch.randn(rows, IH, D)
+    hw = torch.randn(rows, IH) * 0.2
+    keys = bf(torch.randn(1, 1, cap, D))
+    pos = torch.tensor([ctx - 1, 700], dtype=torch.int32)
+    lane = torch.zeros(rows, dtype=torch.int32)
+    scale = float(torch.tensor(D**-0.5, dtype=torch.float32))
+    scores = torch.full((rows, cap), float("nan"), device=DEV)
+    n.indexer_score(q.to(DEV), hw.to(DEV), keys.to(DEV), pos.to(DEV), lane.to(DEV), rows, IH, D, 0, 1, cap, 64, 1, 0, cap, ctx, cap, scale,
+                    scores)
+    for r in range(rows):
+        c = int(pos[r]) + 1
+        dots = torch.einsum("hd,td->ht", q[r], keys[0, 0, :c].float()) * scale
+        ref = (hw[r][:, None] * torch.relu(dots)).sum(0)
+        ok, err = close(scores[r, :c], ref, rtol=1e-4, atol=1e-4)
+        assert ok, err
+        assert torch.isnan(scores[r, c:]).all()  # positions beyond the context are never written
+
+
+@pytest.mark.parametrize("count", [0, 1, 31, 100, 2048])
+def test_sparse_mla_attention(native_lib, count):
+    n = native_lib
+    torch.manual_seed(10)
+    H, L, rd, cap, top_k = 64, 512, 64, 4096, 2048
+    W = L + rd
+    rows = 2
+    q = bf(torch.randn(rows, H, W) * 0.3)
+    cache = bf(torch.randn(1, 1, cap, W))
+    sel = torch.full((rows, top_k), -1, dtype=torch.int32)
+    counts = torch.zeros(rows, 2, dtype=torch.int32)
+    picks = []
+    for r in range(rows):
+        c = count if r == 0 else min(count, 77)
+        p = torch.sort(torch.randperm(cap)[:c]).values
+        sel[r, :c] = p.to(torch.int32)
+        counts[r] = c
+        picks.append(p)
+    chunks = -(-top_k // n.attn_chunk())
+    part_o = torch.zeros(rows, chunks, H, L, device=DEV)
+    part_ml = torch.zeros(rows, chunks, H, 2, device=DEV)
+    o_lat = torch.zeros(rows, H, L, dtype=torch.bfloat16, device=DEV)
+    lane = torch.zeros(rows, dtype=torch.int32, device=DEV)
+    scale = float(torch.tensor((W - rd + rd) ** -0.5, dtype=torch.float32))
+    n.sparse_mla_partial(q.to(DEV), cache.to(DEV), sel.to(DEV), counts.to(DEV), lane, rows, H, L, rd, 0, 1, cap, top_k, chunks, scale,
+                         part_o, part_ml)
+    n.attn_local_merge(part_o, part_ml, counts.to(DEV), rows, H, L, top_k, chunks, o_lat, H)
+    for r in range(rows):
+        ref = contract.absorbed_attention_row(q[r, :, :L], q[r, :, L:], cache[0, 0], picks[r], scale)
+        ok, err = close(o_lat[r], ref, rtol=2**-6, atol=4e-3)
+        assert ok, (r, err)
+
+
+def test_wait_gives_up_and_reports(native_lib):
+    """A wait on a flag that nothing sets runs out, sets the status word and leaves the context usable."""
+    from glm_tpu_b200.parallel.peer import PeerGroup
+
+    n = native_lib
+    peer = PeerGroup(1, 0, wait_limit=2000)
+    assert peer.read_status() == 0
+    import ctypes as C
+
+    code = n.lib().glmb_peer_wait_probe(C.byref(peer.comm), n.SIG_TEST, C.c_uint32(1), C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert code == 0
+    assert peer.read_status() & n.STATUS_WAIT_TIMEOUT
+    assert peer.read_status() == 0  # cleared by the read
+    x = torch.ones(4, device=DEV) * 2
+    assert float(x.sum()) == 8.0
+    peer.close()
