@@ -3,14 +3,20 @@
 // Each GPU holds 1/world of the cached rows.  For a query row the selection kernel has already listed
 // which of the top-k positions live on this GPU (ascending).  Attention runs owner-locally:
 //
-//   sparse_mla_partial   one CTA per (chunk of AT_CHUNK owned selected rows, query row): gathers the rows
-//                        into shared memory, computes the fp32 scores of ALL heads against them, the
-//                        chunk-local softmax statistics and the unnormalized bf16-P . latent product
+//   sparse_mla_partial   one CTA per (chunk of 64 owned selected rows, query row, block of 64 heads): gathers
+//                        the rows and the absorbed queries into shared memory, computes S = Q K^T on the
+//                        tensor cores (bf16 in, fp32 out), the chunk-local softmax statistics in fp32, rounds
+//                        P to bf16 and computes the unnormalized P . latent product on the tensor cores
 //   attn_local_merge     merges a row's chunks per head (log-sum-exp algebra).  With one GPU it normalizes
 //                        and stores bf16.  With several it pushes (o, m, l) of head h straight into the
 //                        buffer of the GPU that owns head h (tensor-parallel by heads) and signals.
 //   attn_final_merge     the head owner waits for the signal, merges the `world` partials in rank order,
 //                        normalizes and stores bf16.
+//
+// The per-row problem is 64 heads x <=2048 gathered keys x 576: far too small and too irregular (every query
+// row has its own key set) to fill a 128-row tcgen05 tile, and it is bound by the gather latency, so the
+// contraction uses warp-level mma.sync m16n8k16 with ldmatrix-fed fragments; the large dense and grouped
+// GEMMs of the model are the tcgen05 kernels.
 //
 // The 2.6 MB selected-row all-reduce of the reference (`glm_tpu/layers/attention/mla.py:484-485`) becomes an
 // exchange of heads x (latent + 2) fp32 per row.  Numerics restate `kernels/sparse_mla/kernel.py:128-183`
@@ -19,99 +25,176 @@
 #include "common.cuh"
 #include "peer.cuh"
 
-#define AT_CHUNK 32
+#define AT_CHUNK 64
 #define AT_THREADS 256
-#define AT_HEAD_TILE 16
+#define AT_HEADS 64   // heads per CTA
+#define AT_PSTRIDE 72 // bf16 elements per P row (64 + 8 padding)
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem_ptr) {
+    const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem_ptr);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem_ptr) {
+    const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem_ptr);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
 
 // part_o  [rows, max_chunks, H, L] fp32 (unnormalized, relative to the chunk max)
 // part_ml [rows, max_chunks, H, 2] fp32 (max, sum)
-__global__ void __launch_bounds__(AT_THREADS)
+// LT: 8-column tiles of the latent handled by one warp; L == 16 * LT (two warps split the latent).
+template <int LT>
+__global__ void __launch_bounds__(AT_THREADS, 1)
 sparse_mla_partial_kernel(const bf16* __restrict__ q_full, const bf16* __restrict__ kv_cache, const int* __restrict__ sel_local,
-                          const int* __restrict__ sel_counts, const int* __restrict__ row_lane, int H, int L, int rd, int layer,
+                          const int* __restrict__ sel_counts, const int* __restrict__ row_lane, int H, int rd, int layer,
                           int layers, int local_cap, int top_k, int max_chunks, float scale, float* __restrict__ part_o,
                           float* __restrict__ part_ml, PeerComm comm, int wait_sig, uint32_t* status) {
+    constexpr int L = 16 * LT;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int W = L + rd;
-    const int WP = W + 8;  // padded row (bf16 elements): keeps 16-byte alignment, staggers banks
-    bf16* kv_s = reinterpret_cast<bf16*>(smem_raw);                        // [AT_CHUNK][WP]
-    float* p_s = reinterpret_cast<float*>(kv_s + AT_CHUNK * WP);           // [H][AT_CHUNK]
-    float* ml_s = p_s + H * AT_CHUNK;                                      // [H][2]
+    const int WP = W + 8;  // padded row (bf16 elements): 16-byte aligned, staggers the banks for ldmatrix
+    bf16* q_s = reinterpret_cast<bf16*>(smem_raw);               // [AT_HEADS][WP]
+    bf16* kv_s = q_s + AT_HEADS * WP;                            // [AT_CHUNK][WP]
+    bf16* p_s = kv_s + AT_CHUNK * WP;                            // [AT_HEADS][AT_PSTRIDE]
+    float* max_s = reinterpret_cast<float*>(p_s + AT_HEADS * AT_PSTRIDE);  // [2][AT_HEADS]
+    float* sum_s = max_s + 2 * AT_HEADS;                         // [2][AT_HEADS]
     if (wait_sig >= 0) cta_wait_signal(comm, wait_sig);
-    const int r = blockIdx.y, chunk = blockIdx.x;
+    const int r = blockIdx.y, chunk = blockIdx.x, h_base = blockIdx.z * AT_HEADS;
     const int count = min(max(sel_counts[2 * r + 1], 0), top_k);
     const int start = chunk * AT_CHUNK;
     if (start >= count) return;
     const int cnt = min(AT_CHUNK, count - start);
     const bf16* cache = kv_cache + ((int64_t)row_lane[r] * layers + layer) * (int64_t)local_cap * W;
-    // gather
     const int vec_per_row = W / 8;
-    for (int i = threadIdx.x; i < cnt * vec_per_row; i += AT_THREADS) {
+    // gather the selected rows (zero-fill the tail of a short chunk) and this CTA's heads of the query
+    for (int i = threadIdx.x; i < AT_CHUNK * vec_per_row; i += AT_THREADS) {
         const int c = i / vec_per_row, v = i % vec_per_row;
-        int row = sel_local[(int64_t)r * top_k + start + c];
-        if (row < 0 || row >= local_cap) { raise_status(status, GLMB_STATUS_BAD_INDEX); row = min(max(row, 0), local_cap - 1); }
-        *reinterpret_cast<uint4*>(kv_s + c * WP + v * 8) = *reinterpret_cast<const uint4*>(cache + (int64_t)row * W + v * 8);
-    }
-    __syncthreads();
-    // scores
-    const bf16* q = q_full + (int64_t)r * H * W;
-    for (int idx = threadIdx.x; idx < H * AT_CHUNK; idx += AT_THREADS) {
-        const int h = idx / AT_CHUNK, c = idx % AT_CHUNK;
-        float s = -INFINITY;
+        uint4 val = make_uint4(0, 0, 0, 0);
         if (c < cnt) {
-            float dot = 0.f;
-            const bf16* qh = q + (int64_t)h * W;
-            const bf16* kr = kv_s + c * WP;
-            for (int v = 0; v < vec_per_row; ++v) {
-                const uint4 a = ld_hot16(qh + v * 8);
-                const uint4 b = *reinterpret_cast<const uint4*>(kr + v * 8);
-                dot = fmaf(bf16_lo(a.x), bf16_lo(b.x), dot); dot = fmaf(bf16_hi(a.x), bf16_hi(b.x), dot);
-                dot = fmaf(bf16_lo(a.y), bf16_lo(b.y), dot); dot = fmaf(bf16_hi(a.y), bf16_hi(b.y), dot);
-                dot = fmaf(bf16_lo(a.z), bf16_lo(b.z), dot); dot = fmaf(bf16_hi(a.z), bf16_hi(b.z), dot);
-                dot = fmaf(bf16_lo(a.w), bf16_lo(b.w), dot); dot = fmaf(bf16_hi(a.w), bf16_hi(b.w), dot);
-            }
-            s = __fmul_rn(dot, scale);
-            if (!isfinite(s)) raise_status(status, GLMB_STATUS_NONFINITE);
+            int row = sel_local[(int64_t)r * top_k + start + c];
+            if (row < 0 || row >= local_cap) { raise_status(status, GLMB_STATUS_BAD_INDEX); row = min(max(row, 0), local_cap - 1); }
+            val = *reinterpret_cast<const uint4*>(cache + (int64_t)row * W + v * 8);
         }
-        p_s[idx] = s;
+        *reinterpret_cast<uint4*>(kv_s + c * WP + v * 8) = val;
+    }
+    const bf16* q = q_full + (int64_t)r * H * W;
+    for (int i = threadIdx.x; i < AT_HEADS * vec_per_row; i += AT_THREADS) {
+        const int h = i / vec_per_row, v = i % vec_per_row;
+        uint4 val = make_uint4(0, 0, 0, 0);
+        if (h_base + h < H) val = ld_hot16(q + (int64_t)(h_base + h) * W + v * 8);
+        *reinterpret_cast<uint4*>(q_s + h * WP + v * 8) = val;
     }
     __syncthreads();
-    // chunk-local softmax statistics: one warp per head (AT_CHUNK == 32 == warp width)
+
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int h = warp; h < H; h += AT_THREADS / 32) {
-        const float s = p_s[h * AT_CHUNK + lane];
-        const float m = warp_max(s);
-        const float p = lane < cnt ? expf(s - m) : 0.f;
-        const float l = warp_sum(p);
-        p_s[h * AT_CHUNK + lane] = bf16_round(p);
-        if (lane == 0) { ml_s[2 * h] = m; ml_s[2 * h + 1] = l; }
-    }
-    __syncthreads();
-    // P . latent
-    const int64_t obase = ((int64_t)r * max_chunks + chunk) * H;
-    for (int h0 = 0; h0 < H; h0 += AT_HEAD_TILE) {
-        const int hn = min(AT_HEAD_TILE, H - h0);
-        for (int j2 = threadIdx.x; j2 < L / 2; j2 += AT_THREADS) {
-            float acc[AT_HEAD_TILE][2];
+    const int hg = warp & 3, half = warp >> 2;  // 16-head group, key half (scores) / latent half (P.V)
+    const int g = lane >> 2, t = lane & 3, mi = lane >> 3, mr = lane & 7;
+    const bool live = h_base + hg * 16 < H;  // warp-uniform
+
+    // ---- S = Q K^T for 16 heads x 32 keys ---------------------------------------------------------
+    float s_acc[4][4];
 #pragma unroll
-            for (int i = 0; i < AT_HEAD_TILE; ++i) acc[i][0] = acc[i][1] = 0.f;
-            for (int c = 0; c < cnt; ++c) {
-                const uint32_t kvv = *reinterpret_cast<const uint32_t*>(kv_s + c * WP + 2 * j2);
-                const float v0 = bf16_lo(kvv), v1 = bf16_hi(kvv);
+    for (int j = 0; j < 4; ++j) s_acc[j][0] = s_acc[j][1] = s_acc[j][2] = s_acc[j][3] = 0.f;
+    if (live) {
+        const bf16* a_base = q_s + (hg * 16 + mr + 8 * (mi & 1)) * WP + 8 * (mi >> 1);
+        const bf16* b_base = kv_s + (half * 32 + mr + 8 * (mi >> 1)) * WP + 8 * (mi & 1);
+        for (int k0 = 0; k0 < W; k0 += 16) {
+            uint32_t a[4], b[4];
+            ldmatrix_x4(a, a_base + k0);
 #pragma unroll
-                for (int i = 0; i < AT_HEAD_TILE; ++i) {
-                    if (i < hn) {
-                        const float p = p_s[(h0 + i) * AT_CHUNK + c];
-                        acc[i][0] = fmaf(p, v0, acc[i][0]);
-                        acc[i][1] = fmaf(p, v1, acc[i][1]);
-                    }
-                }
+            for (int pair = 0; pair < 2; ++pair) {
+                ldmatrix_x4(b, b_base + pair * 16 * WP + k0);
+                mma_bf16_16816(s_acc[pair * 2], a, b[0], b[1]);
+                mma_bf16_16816(s_acc[pair * 2 + 1], a, b[2], b[3]);
             }
-#pragma unroll
-            for (int i = 0; i < AT_HEAD_TILE; ++i)
-                if (i < hn) *reinterpret_cast<float2*>(part_o + (obase + h0 + i) * L + 2 * j2) = make_float2(acc[i][0], acc[i][1]);
         }
     }
-    for (int i = threadIdx.x; i < 2 * H; i += AT_THREADS) part_ml[obase * 2 + i] = ml_s[i];
+    // s_acc[j][e]: head g (e < 2) or g + 8 (e >= 2), key half*32 + 8j + 2t + (e & 1)
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int c = half * 32 + 8 * j + 2 * t + (e & 1);
+            float s = __fmul_rn(s_acc[j][e], scale);
+            if (c >= cnt) s = -INFINITY;
+            else if (live && !isfinite(s)) raise_status(status, GLMB_STATUS_NONFINITE);
+            s_acc[j][e] = s;
+            mx[e >> 1] = fmaxf(mx[e >> 1], s);
+        }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+        mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+    }
+    if (t == 0) { max_s[half * AT_HEADS + hg * 16 + g] = mx[0]; max_s[half * AT_HEADS + hg * 16 + g + 8] = mx[1]; }
+    __syncthreads();
+    float m[2], ls[2] = {0.f, 0.f};
+    m[0] = fmaxf(max_s[hg * 16 + g], max_s[AT_HEADS + hg * 16 + g]);
+    m[1] = fmaxf(max_s[hg * 16 + g + 8], max_s[AT_HEADS + hg * 16 + g + 8]);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        float p[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            p[e] = s_acc[j][e] == -INFINITY ? 0.f : expf(s_acc[j][e] - m[e >> 1]);
+            ls[e >> 1] += p[e];
+        }
+        const int c = half * 32 + 8 * j + 2 * t;
+        *reinterpret_cast<uint32_t*>(p_s + (hg * 16 + g) * AT_PSTRIDE + c) = pack_bf16(p[0], p[1]);
+        *reinterpret_cast<uint32_t*>(p_s + (hg * 16 + g + 8) * AT_PSTRIDE + c) = pack_bf16(p[2], p[3]);
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        ls[i] += __shfl_xor_sync(0xffffffffu, ls[i], 1);
+        ls[i] += __shfl_xor_sync(0xffffffffu, ls[i], 2);
+    }
+    if (t == 0) { sum_s[half * AT_HEADS + hg * 16 + g] = ls[0]; sum_s[half * AT_HEADS + hg * 16 + g + 8] = ls[1]; }
+    __syncthreads();
+
+    // ---- O = P V for 16 heads x (L/2) latent columns ----------------------------------------------
+    if (!live) return;
+    float o_acc[LT][4];
+#pragma unroll
+    for (int j = 0; j < LT; ++j) o_acc[j][0] = o_acc[j][1] = o_acc[j][2] = o_acc[j][3] = 0.f;
+    const bf16* pa_base = p_s + (hg * 16 + mr + 8 * (mi & 1)) * AT_PSTRIDE + 8 * (mi >> 1);
+    const bf16* vb_base = kv_s + (mr + 8 * (mi & 1)) * WP + half * (L / 2) + 8 * (mi >> 1);
+#pragma unroll
+    for (int kk = 0; kk < AT_CHUNK; kk += 16) {
+        uint32_t a[4];
+        ldmatrix_x4(a, pa_base + kk);
+#pragma unroll
+        for (int jn = 0; jn < LT; jn += 2) {
+            uint32_t b[4];
+            ldmatrix_x4_trans(b, vb_base + kk * WP + jn * 8);
+            mma_bf16_16816(o_acc[jn], a, b[0], b[1]);
+            mma_bf16_16816(o_acc[jn + 1], a, b[2], b[3]);
+        }
+    }
+    const int64_t obase = ((int64_t)r * max_chunks + chunk) * H;
+    const int h0 = h_base + hg * 16 + g, h1 = h0 + 8;
+#pragma unroll
+    for (int jn = 0; jn < LT; ++jn) {
+        const int col = half * (L / 2) + jn * 8 + 2 * t;
+        if (h0 < H) *reinterpret_cast<float2*>(part_o + (obase + h0) * L + col) = make_float2(o_acc[jn][0], o_acc[jn][1]);
+        if (h1 < H) *reinterpret_cast<float2*>(part_o + (obase + h1) * L + col) = make_float2(o_acc[jn][2], o_acc[jn][3]);
+    }
+    if (half == 0 && t == 0) {
+        if (h0 < H) {
+            part_ml[(obase + h0) * 2] = m[0];
+            part_ml[(obase + h0) * 2 + 1] = sum_s[hg * 16 + g] + sum_s[AT_HEADS + hg * 16 + g];
+        }
+        if (h1 < H) {
+            part_ml[(obase + h1) * 2] = m[1];
+            part_ml[(obase + h1) * 2 + 1] = sum_s[hg * 16 + g + 8] + sum_s[AT_HEADS + hg * 16 + g + 8];
+        }
+    }
 }
 
 // grid (H, rows).  world == 1: o_lat[r][h] = bf16(o / l).  world > 1: push (o[L], m, l) to head owner.
@@ -119,6 +202,7 @@ __global__ void __launch_bounds__(128)
 attn_local_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, const int* __restrict__ sel_counts,
                         int H, int L, int top_k, int max_chunks, bf16* __restrict__ o_lat, int heads_local,
                         int64_t xpart_offset, PeerComm comm, int sig) {
+    __shared__ float w_s[64];
     const int h = blockIdx.x, r = blockIdx.y;
     const int count = min(max(sel_counts[2 * r + 1], 0), top_k);
     const int chunks = (count + AT_CHUNK - 1) / AT_CHUNK;
@@ -127,14 +211,17 @@ attn_local_merge_kernel(const float* __restrict__ part_o, const float* __restric
     float l = 0.f;
     for (int c = 0; c < chunks; ++c) {
         const float* ml = part_ml + (((int64_t)r * max_chunks + c) * H + h) * 2;
-        l += ml[1] * expf(ml[0] - M);
+        const float wgt = expf(ml[0] - M);
+        l += ml[1] * wgt;
+        if (threadIdx.x == 0 && c < 64) w_s[c] = wgt;
     }
+    __syncthreads();
     const int rows = gridDim.y;
     for (int j = threadIdx.x; j < L; j += blockDim.x) {
         float o = 0.f;
         for (int c = 0; c < chunks; ++c) {
             const int64_t at = ((int64_t)r * max_chunks + c) * H + h;
-            o = fmaf(part_o[at * L + j], expf(part_ml[at * 2] - M), o);
+            o = fmaf(part_o[at * L + j], c < 64 ? w_s[c] : expf(part_ml[at * 2] - M), o);
         }
         if (comm.world == 1) {
             o_lat[((int64_t)r * H + h) * L + j] = __float2bfloat16_rn(chunks > 0 ? o / l : 0.f);
@@ -176,25 +263,42 @@ attn_final_merge_kernel(int L, int heads_local, int64_t xpart_offset, bf16* __re
 // ===================================================================================================
 GLMB_API int glmb_attn_chunk(void) { return AT_CHUNK; }
 
+template <int LT>
+static int launch_partial(const void* q_full, const void* kv_cache, const int* sel_local, const int* sel_counts, const int* row_lane,
+                          int rows, int H, int rd, int layer, int layers, int local_cap, int top_k, int max_chunks, float scale,
+                          float* part_o, float* part_ml, const PeerComm& c, int wait_sig, uint32_t* status, cudaStream_t stream) {
+    const int W = 16 * LT + rd;
+    const size_t smem = (size_t)(AT_HEADS + AT_CHUNK) * (W + 8) * 2 + (size_t)AT_HEADS * AT_PSTRIDE * 2 + 4 * AT_HEADS * 4;
+    if (smem > 220 * 1024) return 2;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(sparse_mla_partial_kernel<LT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+        if (e != cudaSuccess) return (int)e;
+        attr_set = true;
+    }
+    dim3 grid(max_chunks, rows, (H + AT_HEADS - 1) / AT_HEADS);
+    sparse_mla_partial_kernel<LT><<<grid, AT_THREADS, smem, stream>>>((const bf16*)q_full, (const bf16*)kv_cache, sel_local, sel_counts,
+                                                                     row_lane, H, rd, layer, layers, local_cap, top_k, max_chunks,
+                                                                     scale, part_o, part_ml, c, wait_sig, status);
+    return (int)cudaGetLastError();
+}
+
+// L in {64, 128, 512}; (L + rd) % 16 == 0.
 GLMB_API int glmb_sparse_mla_partial(const void* q_full, const void* kv_cache, const int* sel_local, const int* sel_counts,
                                      const int* row_lane, int rows, int H, int L, int rd, int layer, int layers, int local_cap,
                                      int top_k, int max_chunks, float scale, float* part_o, float* part_ml, const PeerComm* comm,
                                      int wait_sig, uint32_t* status, void* stream) {
-    if (((L + rd) & 7) || (L & 1)) return 1;
+    if ((L + rd) & 15) return 1;
     PeerComm c;
     if (comm) c = *comm; else { memset(&c, 0, sizeof(c)); c.world = 1; }
-    const size_t smem = (size_t)AT_CHUNK * (L + rd + 8) * 2 + (size_t)H * AT_CHUNK * 4 + (size_t)H * 2 * 4;
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaFuncSetAttribute(sparse_mla_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
-        attr_set = true;
-    }
-    if (smem > 100 * 1024) return 2;
-    dim3 grid(max_chunks, rows);
-    sparse_mla_partial_kernel<<<grid, AT_THREADS, smem, (cudaStream_t)stream>>>(
-        (const bf16*)q_full, (const bf16*)kv_cache, sel_local, sel_counts, row_lane, H, L, rd, layer, layers, local_cap, top_k,
-        max_chunks, scale, part_o, part_ml, c, wait_sig, status);
-    return (int)cudaGetLastError();
+    cudaStream_t st = (cudaStream_t)stream;
+#define ARGS q_full, kv_cache, sel_local, sel_counts, row_lane, rows, H, rd, layer, layers, local_cap, top_k, max_chunks, scale, part_o, \
+             part_ml, c, wait_sig, status, st
+    if (L == 512) return launch_partial<32>(ARGS);
+    if (L == 128) return launch_partial<8>(ARGS);
+    if (L == 64) return launch_partial<4>(ARGS);
+#undef ARGS
+    return 1;
 }
 
 GLMB_API int glmb_attn_local_merge(const float* part_o, const float* part_ml, const int* sel_counts, int rows, int H, int L,
