@@ -79,6 +79,13 @@ __device__ __forceinline__ uint32_t orderable_u32(float x) {
     return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
 }
 
+// A sampling candidate packed so that an unsigned 64-bit maximum picks the highest logit and, among equal
+// logits, the lowest token id (-0 is folded into +0 first).
+__device__ __forceinline__ unsigned long long candidate_key(float value, int id) {
+    return ((unsigned long long)orderable_u32(value + 0.0f) << 32) | (unsigned long long)(0xFFFFFFFFu - (uint32_t)id);
+}
+__device__ __forceinline__ int candidate_id(unsigned long long key) { return (int)(0xFFFFFFFFu - (uint32_t)(key & 0xFFFFFFFFull)); }
+
 __device__ __forceinline__ void raise_status(uint32_t* status, uint32_t bits) {
     if (status) atomicOr(status, bits);
 }

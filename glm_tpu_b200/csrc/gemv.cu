@@ -21,7 +21,7 @@
 template <int R, int NPW>
 __device__ __forceinline__ void warp_dot_bf16(const bf16* const (&xr)[R], const bf16* const (&wp)[NPW], int K, int lane,
                                               float (&acc)[NPW][R]) {
-#pragma unroll 2
+#pragma unroll (R * NPW <= 4 ? 4 : 2)
     for (int k = lane * 8; k < K; k += 256) {
         float wf[NPW][8];
 #pragma unroll
@@ -47,7 +47,7 @@ __device__ __forceinline__ void warp_dot_bf16(const bf16* const (&xr)[R], const 
 template <int R, int NPW>
 __device__ __forceinline__ void warp_dot_fp8(const bf16* const (&xr)[R], const uint8_t* const (&wp)[NPW],
                                              const float* const (&sp)[NPW], int K, int lane, float (&acc)[NPW][R]) {
-#pragma unroll 2
+#pragma unroll (R * NPW <= 2 ? 4 : 2)
     for (int k = lane * 16; k < K; k += 512) {
         float wf[NPW][16];
 #pragma unroll
@@ -87,7 +87,7 @@ __device__ __forceinline__ void warp_reduce_all(float (&acc)[NPW][R]) {
 
 // ---------------------------------------------------------------------------------------------------
 // out[r][n] = sum_k x[r][k] * w[n][k]          (bf16 weights)
-enum { SK_OUT_F32 = 0, SK_OUT_BF16 = 1, SK_OUT_ALLREDUCE_BF16 = 2 };
+enum { SK_OUT_F32 = 0, SK_OUT_BF16 = 1, SK_OUT_ALLREDUCE_BF16 = 2, SK_OUT_ARGMAX = 3 };
 
 template <int R>
 __global__ void __launch_bounds__(SK_THREADS)
@@ -131,6 +131,33 @@ skinny_bf16_kernel(const bf16* __restrict__ x, int64_t xs, int rows, const bf16*
                 for (int r = 0; r < R; ++r)
                     if (n0 + j < N && r < rows)
                         reinterpret_cast<bf16*>(out)[(int64_t)r * os + n0 + j] = __float2bfloat16_rn(sh[(warp * 2 + j) * R + r]);
+        }
+        return;
+    }
+    if (mode == SK_OUT_ARGMAX) {
+        // out: unsigned long long best[rows]; `channel` carries the id of output column 0 (vocabulary offset).
+        __shared__ unsigned long long best_s[SK_WARPS][R];
+        if (lane == 0) {
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                unsigned long long key = 0ull;
+#pragma unroll
+                for (int j = 0; j < 2; ++j)
+                    if (n0 + j < N) {
+                        const float v = bf16_round(acc[j][r]);
+                        if (!isfinite(v)) raise_status(comm.status, GLMB_STATUS_NONFINITE);
+                        const unsigned long long k2 = candidate_key(v, channel + n0 + j);
+                        key = k2 > key ? k2 : key;
+                    }
+                best_s[warp][r] = key;
+            }
+        }
+        __syncthreads();
+        if ((int)threadIdx.x < rows && (int)threadIdx.x < R) {
+            unsigned long long key = 0ull;
+#pragma unroll
+            for (int w = 0; w < SK_WARPS; ++w) key = best_s[w][threadIdx.x] > key ? best_s[w][threadIdx.x] : key;
+            if (key) atomicMax(reinterpret_cast<unsigned long long*>(out) + threadIdx.x, key);
         }
         return;
     }

@@ -52,6 +52,56 @@ router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ b
     if (lane < top_k) weights[(int64_t)r * top_k + lane] = my_score / (picked_sum + 1e-20f);
 }
 
+// Same selection for E <= 256: every lane loads its (up to 8) logits once and keeps score and key in registers.
+__global__ void __launch_bounds__(128)
+router_topk256_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int rows, int E, int top_k,
+                      int* __restrict__ ids, float* __restrict__ weights) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (r >= rows) return;
+    const float* lg = logits + (int64_t)r * E;
+    float lv[8], bv[8], sc[8];
+    uint32_t key[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int e = lane + 32 * i;
+        lv[i] = e < E ? lg[e] : 0.f;
+        bv[i] = e < E ? bias[e] : 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        sc[i] = sigmoidf_precise(lv[i]);
+        key[i] = orderable_u32(__fadd_rn(sc[i], bv[i]));
+    }
+    uint32_t taken = 0;
+    float picked_sum = 0.f, my_score = 0.f;
+    for (int s = 0; s < top_k; ++s) {
+        uint32_t best_key = 0;
+        int best_e = 0x7fffffff;
+        float best_score = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int e = lane + 32 * i;
+            if (e < E && !((taken >> i) & 1u) && (best_e == 0x7fffffff || key[i] > best_key)) {
+                best_key = key[i]; best_e = e; best_score = sc[i];
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const uint32_t k2 = __shfl_xor_sync(0xffffffffu, best_key, o);
+            const int e2 = __shfl_xor_sync(0xffffffffu, best_e, o);
+            const float s2 = __shfl_xor_sync(0xffffffffu, best_score, o);
+            const bool theirs = e2 != 0x7fffffff && (best_e == 0x7fffffff || k2 > best_key || (k2 == best_key && e2 < best_e));
+            if (theirs) { best_key = k2; best_e = e2; best_score = s2; }
+        }
+        if (best_e != 0x7fffffff && (best_e & 31) == lane) taken |= 1u << (best_e >> 5);
+        if (lane == s) my_score = best_score;
+        picked_sum += best_score;
+        if (lane == 0) ids[(int64_t)r * top_k + s] = best_e == 0x7fffffff ? 0 : best_e;
+    }
+    if (lane < top_k) weights[(int64_t)r * top_k + lane] = my_score / (picked_sum + 1e-20f);
+}
+
 // ---------------------------------------------------------------------------------------------------
 // cand [world][rows][2] (fp32 value, int32 global id) lives in the staging buffer when world > 1.
 __global__ void __launch_bounds__(1024)
@@ -91,39 +141,52 @@ argmax_rows_kernel(const bf16* __restrict__ logits, int64_t stride, int V, int v
         }
         if (lane == 0) {
             const int gid = best_i == 0x7fffffff ? vocab_base : vocab_base + best_i;
-            const int64_t at = ((int64_t)comm.rank * rows + r) * 2;
-            cand[at] = best;
-            reinterpret_cast<int*>(cand)[at + 1] = gid;
+            const unsigned long long key = candidate_key(best, gid);
+            const int64_t at = (int64_t)comm.rank * rows + r;
+            reinterpret_cast<unsigned long long*>(cand)[at] = key;
             for (int p = 0; p < comm.world; ++p)
-                if (p != comm.rank) {
-                    float* box = reinterpret_cast<float*>(comm.data[p] + cand_offset);
-                    box[at] = best;
-                    reinterpret_cast<int*>(box)[at + 1] = gid;
-                }
+                if (p != comm.rank) reinterpret_cast<unsigned long long*>(comm.data[p] + cand_offset)[at] = key;
         }
     }
     grid_signal_peers(comm, sig);
 }
 
 // One CTA.  tokens / positions are the device-resident lane state that the next step reads.
-// n_sets candidate sets [n_sets][rows][2] are compared (one per rank).  advance bit 0: write the token into
-// tokens[r]; bit 1: increment positions[r].  Inactive rows are left untouched and report -1.
-__global__ void step_finalize_kernel(const float* __restrict__ cand, int n_sets, int rows, const int* __restrict__ row_active,
-                                     int* __restrict__ tokens, int* __restrict__ positions, int* __restrict__ out_tokens,
-                                     int* __restrict__ step_counter, int ring, int advance, PeerComm comm, int sig) {
-    cta_wait_signal(comm, sig);
+// n_sets candidate keys per row, cand[set][row] (one set per rank), are compared.  When `local_best` is given
+// (the lm_head kernel reduced this rank's vocabulary slice into it with atomicMax) this kernel first publishes
+// local_best[r] as this rank's candidate -- locally and into every peer's candidate table -- clears it for the
+// next step, signals and waits for the peers; otherwise the candidates were already exchanged by argmax_rows
+// (or by a library all-gather) and it only waits.  advance bit 0: write the token into tokens[r]; bit 1:
+// increment positions[r].  Inactive rows are left untouched and report -1.
+__global__ void step_finalize_kernel(unsigned long long* __restrict__ cand, int64_t cand_offset,
+                                     unsigned long long* __restrict__ local_best, int n_sets, int rows,
+                                     const int* __restrict__ row_active, int* __restrict__ tokens, int* __restrict__ positions,
+                                     int* __restrict__ out_tokens, int* __restrict__ step_counter, int ring, int advance,
+                                     PeerComm comm, int sig) {
     const int r = threadIdx.x;
+    if (local_best) {
+        if (r < rows) {
+            const unsigned long long key = local_best[r];
+            local_best[r] = 0ull;
+            const int64_t at = (int64_t)comm.rank * rows + r;
+            cand[at] = key;
+            for (int p = 0; p < comm.world; ++p)
+                if (p != comm.rank) reinterpret_cast<unsigned long long*>(comm.data[p] + cand_offset)[at] = key;
+        }
+        grid_signal_peers(comm, sig);
+        __syncthreads();
+    }
+    cta_wait_signal(comm, sig);
     const int step = step_counter ? *step_counter : 0;
     if (r < rows) {
-        float best = -INFINITY;
-        int best_id = 0x7fffffff;
+        unsigned long long best = 0ull;
         for (int p = 0; p < n_sets; ++p) {
-            const int64_t at = ((int64_t)p * rows + r) * 2;
-            const float v = comm.world > 1 ? ld_sys_f32(cand + at) : cand[at];
-            const int id = comm.world > 1 ? __float_as_int(ld_sys_f32(cand + at + 1)) : reinterpret_cast<const int*>(cand)[at + 1];
-            if (v > best || (v == best && id < best_id)) { best = v; best_id = id; }
+            unsigned long long key;
+            if (comm.world > 1) asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(key) : "l"(cand + (int64_t)p * rows + r) : "memory");
+            else key = cand[(int64_t)p * rows + r];
+            best = key > best ? key : best;
         }
-        if (best_id == 0x7fffffff) best_id = 0;
+        int best_id = best ? candidate_id(best) : 0;
         const bool active = row_active ? row_active[r] != 0 : true;
         out_tokens[(int64_t)(step % ring) * rows + r] = active ? best_id : -1;
         if (active && (advance & 1)) tokens[r] = best_id;
@@ -178,7 +241,10 @@ __global__ void fill_uniform_f32_kernel(float* __restrict__ out, int64_t n, uint
 GLMB_API int glmb_router_topk(const float* logits, const float* bias, int rows, int E, int top_k, int* ids, float* weights,
                               void* stream) {
     if (E > 1024 || top_k > 32 || top_k > E) return 1;
-    router_topk_kernel<<<ceil_div(rows, 4), 128, 0, (cudaStream_t)stream>>>(logits, bias, rows, E, top_k, ids, weights);
+    if (E <= 256)
+        router_topk256_kernel<<<ceil_div(rows, 4), 128, 0, (cudaStream_t)stream>>>(logits, bias, rows, E, top_k, ids, weights);
+    else
+        router_topk_kernel<<<ceil_div(rows, 4), 128, 0, (cudaStream_t)stream>>>(logits, bias, rows, E, top_k, ids, weights);
     return (int)cudaGetLastError();
 }
 
@@ -191,14 +257,15 @@ GLMB_API int glmb_argmax_rows(const void* logits, int64_t stride, int rows, int 
     return (int)cudaGetLastError();
 }
 
-GLMB_API int glmb_step_finalize(const float* cand, int n_sets, int rows, const int* row_active, int* tokens, int* positions,
-                                int* out_tokens, int* step_counter, int ring, int advance, const PeerComm* comm, int sig,
-                                void* stream) {
+GLMB_API int glmb_step_finalize(void* cand, int64_t cand_offset, void* local_best, int n_sets, int rows, const int* row_active,
+                                int* tokens, int* positions, int* out_tokens, int* step_counter, int ring, int advance,
+                                const PeerComm* comm, int sig, void* stream) {
     if (rows > 32 || n_sets < 1 || ring < 1) return 1;
     PeerComm c;
     if (comm) c = *comm; else { memset(&c, 0, sizeof(c)); c.world = 1; }
-    step_finalize_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(cand, n_sets, rows, row_active, tokens, positions, out_tokens, step_counter, ring,
-                                                             advance, c, sig);
+    step_finalize_kernel<<<1, 32, 0, (cudaStream_t)stream>>>((unsigned long long*)cand, cand_offset, (unsigned long long*)local_best,
+                                                             n_sets, rows, row_active, tokens, positions, out_tokens, step_counter,
+                                                             ring, advance, c, sig);
     return (int)cudaGetLastError();
 }
 

@@ -45,26 +45,64 @@ __global__ void embed_rows_kernel(const int* __restrict__ tokens, const bf16* __
 }
 
 // ---------------------------------------------------------------------------------------------------
+// One CTA per row; every thread owns up to RN_VECS 8-element vectors, all loaded before any arithmetic so the
+// row costs one memory round trip.  H % 8 == 0 and H <= 256 * 8 * RN_VECS.
+#define RN_VECS 4
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+    f[0] = bf16_lo(v.x); f[1] = bf16_hi(v.x); f[2] = bf16_lo(v.y); f[3] = bf16_hi(v.y);
+    f[4] = bf16_lo(v.z); f[5] = bf16_hi(v.z); f[6] = bf16_lo(v.w); f[7] = bf16_hi(v.w);
+}
 __global__ void __launch_bounds__(256)
 add_rmsnorm_kernel(const bf16* __restrict__ update, bf16* __restrict__ residual, const bf16* __restrict__ weight,
                    bf16* __restrict__ out, int H, float eps) {
-    extern __shared__ float sm[];  // H + 33
-    float* s = sm;
-    float* scratch = sm + H;
+    __shared__ float scratch[40];
     const int64_t base = (int64_t)blockIdx.x * H;
+    const int nvec = H >> 3;
+    uint4 rv[RN_VECS], uv[RN_VECS], wv[RN_VECS];
+#pragma unroll
+    for (int i = 0; i < RN_VECS; ++i) {
+        const int v = threadIdx.x + i * 256;
+        if (v < nvec) {
+            rv[i] = *reinterpret_cast<const uint4*>(residual + base + v * 8);
+            uv[i] = update ? *reinterpret_cast<const uint4*>(update + base + v * 8) : make_uint4(0, 0, 0, 0);
+            wv[i] = *reinterpret_cast<const uint4*>(weight + v * 8);
+        }
+    }
+    float s[RN_VECS][8];
     float ss = 0.f;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        float v = __bfloat162float(residual[base + i]);
-        if (update) v = __fadd_rn(__bfloat162float(update[base + i]), v);
-        s[i] = v;
-        ss = fmaf(v, v, ss);
+#pragma unroll
+    for (int i = 0; i < RN_VECS; ++i) {
+        const int v = threadIdx.x + i * 256;
+        if (v < nvec) {
+            float r8[8], u8[8];
+            unpack8(rv[i], r8);
+            unpack8(uv[i], u8);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                s[i][e] = update ? __fadd_rn(u8[e], r8[e]) : r8[e];
+                ss = fmaf(s[i][e], s[i][e], ss);
+            }
+        }
     }
     const float total = block_sum(ss, scratch);
     const float inv = 1.0f / sqrtf(total / (float)H + eps);
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        const float y = bf16_round(s[i] * inv);
-        out[base + i] = __float2bfloat16_rn(y * __bfloat162float(weight[i]));
-        residual[base + i] = __float2bfloat16_rn(s[i]);
+#pragma unroll
+    for (int i = 0; i < RN_VECS; ++i) {
+        const int v = threadIdx.x + i * 256;
+        if (v < nvec) {
+            float w8[8];
+            unpack8(wv[i], w8);
+            uint4 o, rr;
+            uint32_t* op = reinterpret_cast<uint32_t*>(&o);
+            uint32_t* rp = reinterpret_cast<uint32_t*>(&rr);
+#pragma unroll
+            for (int e = 0; e < 8; e += 2) {
+                op[e >> 1] = pack_bf16(bf16_round(s[i][e] * inv) * w8[e], bf16_round(s[i][e + 1] * inv) * w8[e + 1]);
+                rp[e >> 1] = pack_bf16(s[i][e], s[i][e + 1]);
+            }
+            *reinterpret_cast<uint4*>(out + base + v * 8) = o;
+            *reinterpret_cast<uint4*>(residual + base + v * 8) = rr;
+        }
     }
 }
 
@@ -199,11 +237,15 @@ __global__ void __launch_bounds__(256) q_post_kernel(QPostArgs a) {
     const float* q = a.q + (int64_t)r * a.q_stride;
     const int pos = min(max(a.row_pos[r], 0), a.capacity - 1);
     const int qk = a.nope + a.rd, half = a.rd / 2, W = a.L + a.rd;
-    for (int i = threadIdx.x; i < a.heads_local * a.nope; i += blockDim.x) {
-        const int h = i / a.nope, d = i % a.nope;
-        a.q_nope[((int64_t)r * a.heads_local + h) * a.nope + d] = __float2bfloat16_rn(q[h * qk + d]);
+    // blockIdx.y spreads one row's work over several CTAs: each thread touches a few elements only
+    const int tid = blockIdx.y * blockDim.x + threadIdx.x, nth = gridDim.y * blockDim.x;
+    const int np2 = a.nope >> 1;
+    for (int i = tid; i < a.heads_local * np2; i += nth) {
+        const int h = i / np2, d = (i % np2) * 2;
+        const float2 v = *reinterpret_cast<const float2*>(q + h * qk + d);
+        *reinterpret_cast<uint32_t*>(a.q_nope + ((int64_t)r * a.heads_local + h) * a.nope + d) = pack_bf16(v.x, v.y);
     }
-    for (int i = threadIdx.x; i < a.heads_local * half; i += blockDim.x) {
+    for (int i = tid; i < a.heads_local * half; i += nth) {
         const int h = i / half, j = i % half;
         const float even = bf16_round(q[h * qk + a.nope + 2 * j]), odd = bf16_round(q[h * qk + a.nope + 2 * j + 1]);
         const float cs = __bfloat162float(a.rope_table[(int64_t)pos * a.rd + j]);
@@ -214,7 +256,7 @@ __global__ void __launch_bounds__(256) q_post_kernel(QPostArgs a) {
     }
     if (!a.has_indexer) return;
     const float* qi = q + a.heads_local * qk;
-    for (int i = threadIdx.x; i < a.IH * a.D; i += blockDim.x) {
+    for (int i = tid; i < a.IH * a.D; i += nth) {
         const int h = i / a.D, d = i % a.D;
         float o = qi[i];
         if (d < a.rd) {
@@ -302,9 +344,8 @@ GLMB_API int glmb_embed_rows(const int* tokens, const void* table, int rows, int
 
 GLMB_API int glmb_add_rmsnorm(const void* update, void* residual, const void* weight, void* out, int rows, int H, float eps,
                               void* stream) {
-    const size_t smem = (size_t)(H + 40) * sizeof(float);
-    if (smem > 48 * 1024) return 1;
-    add_rmsnorm_kernel<<<rows, 256, smem, (cudaStream_t)stream>>>((const bf16*)update, (bf16*)residual, (const bf16*)weight,
+    if ((H & 7) || H > 256 * 8 * RN_VECS) return 1;
+    add_rmsnorm_kernel<<<rows, 256, 0, (cudaStream_t)stream>>>((const bf16*)update, (bf16*)residual, (const bf16*)weight,
                                                                   (bf16*)out, H, eps);
     return (int)cudaGetLastError();
 }
@@ -316,7 +357,10 @@ GLMB_API int glmb_qkv_a_post(const QkvPostArgs* args, int rows, void* stream) {
 }
 
 GLMB_API int glmb_q_post(const QPostArgs* args, int rows, void* stream) {
-    q_post_kernel<<<rows, 256, 0, (cudaStream_t)stream>>>(*args);
+    if ((args->nope & 1) || (args->q_stride & 1)) return 1;
+    const int work = args->heads_local * (args->nope / 2 + args->rd / 2) + (args->has_indexer ? args->IH * args->D : 0);
+    dim3 grid(rows, rows <= 16 ? max(1, min(32, ceil_div(work, 512))) : 1);
+    q_post_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(*args);
     return (int)cudaGetLastError();
 }
 

@@ -101,15 +101,16 @@ class Workspace:
             self.r_q = peer.region(f"{tag}.q_full", rows * ht * W * 2)
             self.r_scores = peer.region(f"{tag}.scores", rows * self.score_stride * 4)
             self.r_xpart = peer.region(f"{tag}.xpart", peer.world * self.attn_rows * hl * (L + 2) * 4)
-            self.r_cand = peer.region(f"{tag}.cand", peer.world * rows * 2 * 4)
+            self.r_cand = peer.region(f"{tag}.cand", peer.world * rows * 8)
             self.q_full = peer.tensor(self.r_q, (rows, ht, W), torch.bfloat16)
             self.scores = peer.tensor(self.r_scores, (rows, self.score_stride), torch.float32)
-            self.cand = peer.tensor(self.r_cand, (peer.world, rows, 2), torch.float32)
+            self.cand = peer.tensor(self.r_cand, (peer.world, rows), torch.int64)
         else:
             self.r_q = self.r_scores = self.r_xpart = self.r_cand = None
             self.q_full = bf(rows, ht, W)
             self.scores = f32(rows, self.score_stride)
-            self.cand = f32(max(1, peer.world), rows, 2)
+            self.cand = torch.zeros((max(1, peer.world), rows), dtype=torch.int64, device=dev)
+        self.local_best = torch.zeros(rows, dtype=torch.int64, device=dev)  # packed argmax keys of this rank's vocabulary slice
         self.sel_global, self.sel_local, self.sel_counts = i32(rows, k), i32(rows, k), i32(rows, 2)
         self.max_chunks = -(-k // native.attn_chunk())
         self.part_o = f32(self.attn_rows, self.max_chunks, ht, L)
@@ -405,8 +406,13 @@ class GlmMoeDsaModel:
 
     # ------------------------------------------------------------------------------ whole model
     def run_rows(self, ws: Workspace, state: DecoderState, tokens: torch.Tensor, row_pos: torch.Tensor, row_lane: torch.Tensor,
-                 row_active, rows: int, *, decode: bool, max_ctx: int, head_rows: slice | None = None) -> torch.Tensor:
-        """Push ``rows`` token rows through the decoder; returns the bf16 logits of ``head_rows`` (vocabulary slice)."""
+                 row_active, rows: int, *, decode: bool, max_ctx: int, head_rows: slice | None = None, head: str = "logits"):
+        """Push ``rows`` token rows through the decoder.
+
+        ``head='logits'`` returns the bf16 logits of ``head_rows`` (this rank's vocabulary slice).  ``head='argmax'``
+        (decode) fuses the greedy reduction into the lm_head kernel: the packed best candidate of every row lands in
+        ``ws.local_best`` and ``None`` is returned; ``sample`` then finishes the step.
+        """
         g = self.g
         native.embed_rows(tokens, self.w.embed, ws.residual, self.peer.status_ptr)
         update = None
@@ -422,6 +428,10 @@ class GlmMoeDsaModel:
         hs = head_rows or slice(0, rows)
         xh = ws.x[hs]
         n = xh.shape[0]
+        if head == "argmax":
+            native.skinny_bf16(xh, self.w.lm_head, ws.local_best, native.SK_OUT_ARGMAX, comm=self.peer.comm,
+                               channel=self.rank * self.layout.vocab_local, os_=0)
+            return None
         if n <= native.MAX_ROWS:
             native.skinny_bf16(xh, self.w.lm_head, ws.logits, native.SK_OUT_BF16)
         else:
@@ -438,8 +448,16 @@ class GlmMoeDsaModel:
         lay = self.layout
         fused = ws.peer_visible
         kc = self.peer.comm if fused else None
-        native.argmax_rows(logits, rows, lay.vocab_local, self.rank * lay.vocab_local, ws.cand, ws.r_cand.offset if fused else 0, kc,
-                           native.SIG_SAMPLE, self.peer.status_ptr)
+        local_best = None
+        if logits is None:
+            local_best = ws.local_best  # filled by the lm_head kernel in argmax mode
+            if self.world > 1 and not fused:
+                ws.cand[0, :rows] = ws.local_best[:rows]
+                ws.local_best.zero_()
+                local_best = None
+        else:
+            native.argmax_rows(logits, rows, lay.vocab_local, self.rank * lay.vocab_local, ws.cand, ws.r_cand.offset if fused else 0,
+                               kc, native.SIG_SAMPLE, self.peer.status_ptr)
         cand = ws.cand
         if self.world > 1 and not fused:
             import torch.distributed as dist
@@ -454,4 +472,5 @@ class GlmMoeDsaModel:
             out, counter, ring = state.out_tokens, state.step_counter, RING
         else:
             counter, ring = None, 1
-        native.step_finalize(cand, self.world, rows, row_active, tokens, pos, out, counter, ring, advance, kc, native.SIG_SAMPLE)
+        native.step_finalize(cand, self.world, rows, row_active, tokens, pos, out, counter, ring, advance, kc, native.SIG_SAMPLE,
+                             local_best=local_best, cand_offset=ws.r_cand.offset if fused else 0)

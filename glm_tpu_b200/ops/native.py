@@ -17,7 +17,7 @@ LIB_PATH = Path(__file__).resolve().parent / "libglmb200.so"
 MAX_WORLD = 8
 MAX_ROWS = 8
 
-SK_OUT_F32, SK_OUT_BF16, SK_OUT_ALLREDUCE_BF16 = 0, 1, 2
+SK_OUT_F32, SK_OUT_BF16, SK_OUT_ALLREDUCE_BF16, SK_OUT_ARGMAX = 0, 1, 2, 3
 STATUS_WAIT_TIMEOUT, STATUS_BAD_INDEX, STATUS_NONFINITE, STATUS_BAD_SHAPE = 1, 2, 4, 8
 
 # signals (producer -> consumer exchanges) and all-reduce channels used by the model
@@ -256,11 +256,15 @@ def argmax_rows(logits, rows, V, vocab_base, cand, cand_offset=0, comm=None, sig
 
 
 def step_finalize(cand, n_sets, rows, row_active, tokens, positions, out_tokens, step_counter, ring, advance, comm=None,
-                  sig=SIG_SAMPLE):
-    """advance: bit 0 writes the sampled token into ``tokens``, bit 1 increments ``positions``."""
+                  sig=SIG_SAMPLE, local_best=None, cand_offset=0):
+    """Pick the best of ``n_sets`` packed candidates per row (``cand`` is ``[n_sets, rows]`` 64-bit keys).
+
+    ``local_best`` (``[rows]`` int64 filled by the lm_head kernel in argmax mode) is first published as this rank's
+    candidate.  advance: bit 0 writes the sampled token into ``tokens``, bit 1 increments ``positions``.
+    """
     _check(
-        lib().glmb_step_finalize(_p(cand), n_sets, rows, _p(row_active), _p(tokens), _p(positions), _p(out_tokens), _p(step_counter), ring,
-                                 int(advance), _comm(comm), sig, _stream()),
+        lib().glmb_step_finalize(_p(cand), C.c_int64(cand_offset), _p(local_best), n_sets, rows, _p(row_active), _p(tokens),
+                                 _p(positions), _p(out_tokens), _p(step_counter), ring, int(advance), _comm(comm), sig, _stream()),
         "step_finalize",
     )
 

@@ -103,7 +103,7 @@ class GpuModelRunner:
     def _decode_body(self) -> None:
         st, ws, m = self.state, self.decode_ws, self.model
         logits = m.run_rows(ws, st, st.tokens, st.positions, st.lane_ids, st.active, self.lanes, decode=True,
-                            max_ctx=self.cache.context_capacity)
+                            max_ctx=self.cache.context_capacity, head="argmax")
         m.sample(ws, st, logits, self.lanes, st.active, advance=3)
 
     def build_decode_program(self) -> ProgramRecord:
