@@ -27,13 +27,18 @@
 
 #define AT_CHUNK 64
 #define AT_THREADS 256
-#define AT_HEADS 64   // heads per CTA
+#define AT_WARPS 8
+#define AT_HEADS 16   // heads per CTA (one m16 tile)
 #define AT_PSTRIDE 72 // bf16 elements per P row (64 + 8 padding)
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem_ptr) {
     const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem_ptr);
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x2(uint32_t (&r)[2], const void* smem_ptr) {
+    const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem_ptr);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(addr));
 }
 __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem_ptr) {
     const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem_ptr);
@@ -48,22 +53,23 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a
 
 // part_o  [rows, max_chunks, H, L] fp32 (unnormalized, relative to the chunk max)
 // part_ml [rows, max_chunks, H, 2] fp32 (max, sum)
-// LT: 8-column tiles of the latent handled by one warp; L == 16 * LT (two warps split the latent).
-template <int LT>
-__global__ void __launch_bounds__(AT_THREADS, 1)
+// One CTA: 16 heads x 64 gathered keys.  Scores: warp w owns keys 8w..8w+7.  P.V: PVW warps each own TPW
+// 8-column tiles of the latent (L == 8 * TPW * PVW).
+template <int TPW, int PVW>
+__global__ void __launch_bounds__(AT_THREADS)
 sparse_mla_partial_kernel(const bf16* __restrict__ q_full, const bf16* __restrict__ kv_cache, const int* __restrict__ sel_local,
                           const int* __restrict__ sel_counts, const int* __restrict__ row_lane, int H, int rd, int layer,
                           int layers, int local_cap, int top_k, int max_chunks, float scale, float* __restrict__ part_o,
                           float* __restrict__ part_ml, PeerComm comm, int wait_sig, uint32_t* status) {
-    constexpr int L = 16 * LT;
+    constexpr int L = 8 * TPW * PVW;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int W = L + rd;
     const int WP = W + 8;  // padded row (bf16 elements): 16-byte aligned, staggers the banks for ldmatrix
     bf16* q_s = reinterpret_cast<bf16*>(smem_raw);               // [AT_HEADS][WP]
     bf16* kv_s = q_s + AT_HEADS * WP;                            // [AT_CHUNK][WP]
     bf16* p_s = kv_s + AT_CHUNK * WP;                            // [AT_HEADS][AT_PSTRIDE]
-    float* max_s = reinterpret_cast<float*>(p_s + AT_HEADS * AT_PSTRIDE);  // [2][AT_HEADS]
-    float* sum_s = max_s + 2 * AT_HEADS;                         // [2][AT_HEADS]
+    float* max_s = reinterpret_cast<float*>(p_s + AT_HEADS * AT_PSTRIDE);  // [AT_WARPS][AT_HEADS]
+    float* sum_s = max_s + AT_WARPS * AT_HEADS;                  // [AT_WARPS][AT_HEADS]
     if (wait_sig >= 0) cta_wait_signal(comm, wait_sig);
     const int r = blockIdx.y, chunk = blockIdx.x, h_base = blockIdx.z * AT_HEADS;
     const int count = min(max(sel_counts[2 * r + 1], 0), top_k);
@@ -93,107 +99,97 @@ sparse_mla_partial_kernel(const bf16* __restrict__ q_full, const bf16* __restric
     __syncthreads();
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int hg = warp & 3, half = warp >> 2;  // 16-head group, key half (scores) / latent half (P.V)
     const int g = lane >> 2, t = lane & 3, mi = lane >> 3, mr = lane & 7;
-    const bool live = h_base + hg * 16 < H;  // warp-uniform
 
-    // ---- S = Q K^T for 16 heads x 32 keys ---------------------------------------------------------
-    float s_acc[4][4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) s_acc[j][0] = s_acc[j][1] = s_acc[j][2] = s_acc[j][3] = 0.f;
-    if (live) {
-        const bf16* a_base = q_s + (hg * 16 + mr + 8 * (mi & 1)) * WP + 8 * (mi >> 1);
-        const bf16* b_base = kv_s + (half * 32 + mr + 8 * (mi >> 1)) * WP + 8 * (mi & 1);
+    // ---- S = Q K^T: 16 heads x 8 keys per warp ------------------------------------------------------
+    float s_acc[4] = {0.f, 0.f, 0.f, 0.f};
+    {
+        const bf16* a_base = q_s + (mr + 8 * (mi & 1)) * WP + 8 * (mi >> 1);
+        const bf16* b_base = kv_s + (warp * 8 + mr) * WP + 8 * (mi & 1);
         for (int k0 = 0; k0 < W; k0 += 16) {
-            uint32_t a[4], b[4];
+            uint32_t a[4], b[2];
             ldmatrix_x4(a, a_base + k0);
-#pragma unroll
-            for (int pair = 0; pair < 2; ++pair) {
-                ldmatrix_x4(b, b_base + pair * 16 * WP + k0);
-                mma_bf16_16816(s_acc[pair * 2], a, b[0], b[1]);
-                mma_bf16_16816(s_acc[pair * 2 + 1], a, b[2], b[3]);
-            }
+            ldmatrix_x2(b, b_base + k0);
+            mma_bf16_16816(s_acc, a, b[0], b[1]);
         }
     }
-    // s_acc[j][e]: head g (e < 2) or g + 8 (e >= 2), key half*32 + 8j + 2t + (e & 1)
+    // s_acc[e]: head g (e < 2) or g + 8 (e >= 2), key 8*warp + 2t + (e & 1)
     float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const int c = half * 32 + 8 * j + 2 * t + (e & 1);
-            float s = __fmul_rn(s_acc[j][e], scale);
-            if (c >= cnt) s = -INFINITY;
-            else if (live && !isfinite(s)) raise_status(status, GLMB_STATUS_NONFINITE);
-            s_acc[j][e] = s;
-            mx[e >> 1] = fmaxf(mx[e >> 1], s);
-        }
+    for (int e = 0; e < 4; ++e) {
+        const int c = warp * 8 + 2 * t + (e & 1);
+        float s = __fmul_rn(s_acc[e], scale);
+        if (c >= cnt) s = -INFINITY;
+        else if (!isfinite(s)) raise_status(status, GLMB_STATUS_NONFINITE);
+        s_acc[e] = s;
+        mx[e >> 1] = fmaxf(mx[e >> 1], s);
+    }
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
         mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
     }
-    if (t == 0) { max_s[half * AT_HEADS + hg * 16 + g] = mx[0]; max_s[half * AT_HEADS + hg * 16 + g + 8] = mx[1]; }
+    if (t == 0) { max_s[warp * AT_HEADS + g] = mx[0]; max_s[warp * AT_HEADS + g + 8] = mx[1]; }
     __syncthreads();
-    float m[2], ls[2] = {0.f, 0.f};
-    m[0] = fmaxf(max_s[hg * 16 + g], max_s[AT_HEADS + hg * 16 + g]);
-    m[1] = fmaxf(max_s[hg * 16 + g + 8], max_s[AT_HEADS + hg * 16 + g + 8]);
+    float m[2] = {-INFINITY, -INFINITY}, ls[2] = {0.f, 0.f};
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int w2 = 0; w2 < AT_WARPS; ++w2) {
+        m[0] = fmaxf(m[0], max_s[w2 * AT_HEADS + g]);
+        m[1] = fmaxf(m[1], max_s[w2 * AT_HEADS + g + 8]);
+    }
+    {
         float p[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-            p[e] = s_acc[j][e] == -INFINITY ? 0.f : expf(s_acc[j][e] - m[e >> 1]);
+            p[e] = s_acc[e] == -INFINITY ? 0.f : expf(s_acc[e] - m[e >> 1]);
             ls[e >> 1] += p[e];
         }
-        const int c = half * 32 + 8 * j + 2 * t;
-        *reinterpret_cast<uint32_t*>(p_s + (hg * 16 + g) * AT_PSTRIDE + c) = pack_bf16(p[0], p[1]);
-        *reinterpret_cast<uint32_t*>(p_s + (hg * 16 + g + 8) * AT_PSTRIDE + c) = pack_bf16(p[2], p[3]);
+        const int c = warp * 8 + 2 * t;
+        *reinterpret_cast<uint32_t*>(p_s + g * AT_PSTRIDE + c) = pack_bf16(p[0], p[1]);
+        *reinterpret_cast<uint32_t*>(p_s + (g + 8) * AT_PSTRIDE + c) = pack_bf16(p[2], p[3]);
     }
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         ls[i] += __shfl_xor_sync(0xffffffffu, ls[i], 1);
         ls[i] += __shfl_xor_sync(0xffffffffu, ls[i], 2);
     }
-    if (t == 0) { sum_s[half * AT_HEADS + hg * 16 + g] = ls[0]; sum_s[half * AT_HEADS + hg * 16 + g + 8] = ls[1]; }
+    if (t == 0) { sum_s[warp * AT_HEADS + g] = ls[0]; sum_s[warp * AT_HEADS + g + 8] = ls[1]; }
     __syncthreads();
 
-    // ---- O = P V for 16 heads x (L/2) latent columns ----------------------------------------------
-    if (!live) return;
-    float o_acc[LT][4];
-#pragma unroll
-    for (int j = 0; j < LT; ++j) o_acc[j][0] = o_acc[j][1] = o_acc[j][2] = o_acc[j][3] = 0.f;
-    const bf16* pa_base = p_s + (hg * 16 + mr + 8 * (mi & 1)) * AT_PSTRIDE + 8 * (mi >> 1);
-    const bf16* vb_base = kv_s + (mr + 8 * (mi & 1)) * WP + half * (L / 2) + 8 * (mi >> 1);
-#pragma unroll
-    for (int kk = 0; kk < AT_CHUNK; kk += 16) {
-        uint32_t a[4];
-        ldmatrix_x4(a, pa_base + kk);
-#pragma unroll
-        for (int jn = 0; jn < LT; jn += 2) {
-            uint32_t b[4];
-            ldmatrix_x4_trans(b, vb_base + kk * WP + jn * 8);
-            mma_bf16_16816(o_acc[jn], a, b[0], b[1]);
-            mma_bf16_16816(o_acc[jn + 1], a, b[2], b[3]);
-        }
-    }
+    // ---- O = P V: 16 heads x (8 * TPW) latent columns per warp ---------------------------------------
     const int64_t obase = ((int64_t)r * max_chunks + chunk) * H;
-    const int h0 = h_base + hg * 16 + g, h1 = h0 + 8;
+    const int h0 = h_base + g, h1 = h0 + 8;
+    if (warp < PVW) {
+        float o_acc[TPW][4];
 #pragma unroll
-    for (int jn = 0; jn < LT; ++jn) {
-        const int col = half * (L / 2) + jn * 8 + 2 * t;
-        if (h0 < H) *reinterpret_cast<float2*>(part_o + (obase + h0) * L + col) = make_float2(o_acc[jn][0], o_acc[jn][1]);
-        if (h1 < H) *reinterpret_cast<float2*>(part_o + (obase + h1) * L + col) = make_float2(o_acc[jn][2], o_acc[jn][3]);
+        for (int j = 0; j < TPW; ++j) o_acc[j][0] = o_acc[j][1] = o_acc[j][2] = o_acc[j][3] = 0.f;
+        const bf16* pa_base = p_s + (mr + 8 * (mi & 1)) * AT_PSTRIDE + 8 * (mi >> 1);
+        const bf16* vb_base = kv_s + (mr + 8 * (mi & 1)) * WP + warp * (8 * TPW) + 8 * (mi >> 1);
+#pragma unroll
+        for (int kk = 0; kk < AT_CHUNK; kk += 16) {
+            uint32_t a[4];
+            ldmatrix_x4(a, pa_base + kk);
+#pragma unroll
+            for (int jn = 0; jn < TPW; jn += 2) {
+                uint32_t b[4];
+                ldmatrix_x4_trans(b, vb_base + kk * WP + jn * 8);
+                mma_bf16_16816(o_acc[jn], a, b[0], b[1]);
+                mma_bf16_16816(o_acc[jn + 1], a, b[2], b[3]);
+            }
+        }
+#pragma unroll
+        for (int jn = 0; jn < TPW; ++jn) {
+            const int col = warp * (8 * TPW) + jn * 8 + 2 * t;
+            if (h0 < H) *reinterpret_cast<float2*>(part_o + (obase + h0) * L + col) = make_float2(o_acc[jn][0], o_acc[jn][1]);
+            if (h1 < H) *reinterpret_cast<float2*>(part_o + (obase + h1) * L + col) = make_float2(o_acc[jn][2], o_acc[jn][3]);
+        }
     }
-    if (half == 0 && t == 0) {
-        if (h0 < H) {
-            part_ml[(obase + h0) * 2] = m[0];
-            part_ml[(obase + h0) * 2 + 1] = sum_s[hg * 16 + g] + sum_s[AT_HEADS + hg * 16 + g];
-        }
-        if (h1 < H) {
-            part_ml[(obase + h1) * 2] = m[1];
-            part_ml[(obase + h1) * 2 + 1] = sum_s[hg * 16 + g + 8] + sum_s[AT_HEADS + hg * 16 + g + 8];
-        }
+    if (warp == 0 && t == 0) {
+        float l0 = 0.f, l1 = 0.f;
+#pragma unroll
+        for (int w2 = 0; w2 < AT_WARPS; ++w2) { l0 += sum_s[w2 * AT_HEADS + g]; l1 += sum_s[w2 * AT_HEADS + g + 8]; }
+        if (h0 < H) { part_ml[(obase + h0) * 2] = m[0]; part_ml[(obase + h0) * 2 + 1] = l0; }
+        if (h1 < H) { part_ml[(obase + h1) * 2] = m[1]; part_ml[(obase + h1) * 2 + 1] = l1; }
     }
 }
 
@@ -263,23 +259,24 @@ attn_final_merge_kernel(int L, int heads_local, int64_t xpart_offset, bf16* __re
 // ===================================================================================================
 GLMB_API int glmb_attn_chunk(void) { return AT_CHUNK; }
 
-template <int LT>
+template <int TPW, int PVW>
 static int launch_partial(const void* q_full, const void* kv_cache, const int* sel_local, const int* sel_counts, const int* row_lane,
                           int rows, int H, int rd, int layer, int layers, int local_cap, int top_k, int max_chunks, float scale,
                           float* part_o, float* part_ml, const PeerComm& c, int wait_sig, uint32_t* status, cudaStream_t stream) {
-    const int W = 16 * LT + rd;
-    const size_t smem = (size_t)(AT_HEADS + AT_CHUNK) * (W + 8) * 2 + (size_t)AT_HEADS * AT_PSTRIDE * 2 + 4 * AT_HEADS * 4;
-    if (smem > 220 * 1024) return 2;
+    const int W = 8 * TPW * PVW + rd;
+    const size_t smem = (size_t)(AT_HEADS + AT_CHUNK) * (W + 8) * 2 + (size_t)AT_HEADS * AT_PSTRIDE * 2 + 2 * AT_WARPS * AT_HEADS * 4;
+    if (smem > 200 * 1024) return 2;
     static bool attr_set = false;
     if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(sparse_mla_partial_kernel<LT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(sparse_mla_partial_kernel<TPW, PVW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (e != cudaSuccess) return (int)e;
         attr_set = true;
     }
     dim3 grid(max_chunks, rows, (H + AT_HEADS - 1) / AT_HEADS);
-    sparse_mla_partial_kernel<LT><<<grid, AT_THREADS, smem, stream>>>((const bf16*)q_full, (const bf16*)kv_cache, sel_local, sel_counts,
-                                                                     row_lane, H, rd, layer, layers, local_cap, top_k, max_chunks,
-                                                                     scale, part_o, part_ml, c, wait_sig, status);
+    sparse_mla_partial_kernel<TPW, PVW><<<grid, AT_THREADS, smem, stream>>>((const bf16*)q_full, (const bf16*)kv_cache, sel_local,
+                                                                           sel_counts, row_lane, H, rd, layer, layers, local_cap,
+                                                                           top_k, max_chunks, scale, part_o, part_ml, c, wait_sig,
+                                                                           status);
     return (int)cudaGetLastError();
 }
 
@@ -294,9 +291,9 @@ GLMB_API int glmb_sparse_mla_partial(const void* q_full, const void* kv_cache, c
     cudaStream_t st = (cudaStream_t)stream;
 #define ARGS q_full, kv_cache, sel_local, sel_counts, row_lane, rows, H, rd, layer, layers, local_cap, top_k, max_chunks, scale, part_o, \
              part_ml, c, wait_sig, status, st
-    if (L == 512) return launch_partial<32>(ARGS);
-    if (L == 128) return launch_partial<8>(ARGS);
-    if (L == 64) return launch_partial<4>(ARGS);
+    if (L == 512) return launch_partial<8, 8>(ARGS);
+    if (L == 128) return launch_partial<2, 8>(ARGS);
+    if (L == 64) return launch_partial<2, 4>(ARGS);
 #undef ARGS
     return 1;
 }

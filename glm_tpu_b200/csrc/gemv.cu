@@ -19,10 +19,10 @@
 // ---------------------------------------------------------------------------------------------------
 // Per-warp dot products.  acc[j][r] accumulates this lane's share of  sum_k w_j[k] * x_r[k].
 template <int R, int NPW>
-__device__ __forceinline__ void warp_dot_bf16(const bf16* const (&xr)[R], const bf16* const (&wp)[NPW], int K, int lane,
-                                              float (&acc)[NPW][R]) {
+__device__ __forceinline__ void warp_dot_bf16(const bf16* const (&xr)[R], const bf16* const (&wp)[NPW], int kbeg, int kend,
+                                              int lane, float (&acc)[NPW][R]) {
 #pragma unroll (R * NPW <= 4 ? 4 : 2)
-    for (int k = lane * 8; k < K; k += 256) {
+    for (int k = kbeg + lane * 8; k < kend; k += 256) {
         float wf[NPW][8];
 #pragma unroll
         for (int j = 0; j < NPW; ++j) {
@@ -89,13 +89,17 @@ __device__ __forceinline__ void warp_reduce_all(float (&acc)[NPW][R]) {
 // out[r][n] = sum_k x[r][k] * w[n][k]          (bf16 weights)
 enum { SK_OUT_F32 = 0, SK_OUT_BF16 = 1, SK_OUT_ALLREDUCE_BF16 = 2, SK_OUT_ARGMAX = 3 };
 
+// ks (1, 2, 4 or 8) warps of a CTA split K for the same pair of output rows and add their partial sums through
+// shared memory: small-N projections then still fill the machine.  A CTA produces 16 / ks output rows.
 template <int R>
 __global__ void __launch_bounds__(SK_THREADS)
 skinny_bf16_kernel(const bf16* __restrict__ x, int64_t xs, int rows, const bf16* __restrict__ w, int64_t ws, int N, int K,
-                   void* __restrict__ out, int64_t os, int mode, int64_t xb, int64_t wb, int64_t ob, PeerComm comm,
+                   void* __restrict__ out, int64_t os, int mode, int ks, int64_t xb, int64_t wb, int64_t ob, PeerComm comm,
                    int channel) {
+    __shared__ float red[SK_WARPS][2][R];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = (blockIdx.x * SK_WARPS + warp) * 2;
+    const int group = warp / ks, kpart = warp % ks, groups = SK_WARPS / ks;
+    const int n0 = (blockIdx.x * groups + group) * 2;
     // blockIdx.y selects one problem of a batch (per-head projections): element offsets xb / wb / ob.
     x += (int64_t)blockIdx.y * xb;
     w += (int64_t)blockIdx.y * wb;
@@ -111,26 +115,44 @@ skinny_bf16_kernel(const bf16* __restrict__ x, int64_t xs, int rows, const bf16*
         for (int r = 0; r < R; ++r) acc[j][r] = 0.f;
     if (n0 < N) {
         const bf16* wp[2] = {w + (int64_t)n0 * ws, w + (int64_t)min(n0 + 1, N - 1) * ws};
-        warp_dot_bf16<R, 2>(xr, wp, K, lane, acc);
+        const int kspan = K / ks;
+        warp_dot_bf16<R, 2>(xr, wp, kpart * kspan, (kpart + 1) * kspan, lane, acc);
         warp_reduce_all<R, 2>(acc);
     }
-    if (mode == SK_OUT_ALLREDUCE_BF16) {
-        __shared__ float sh[SK_WARPS * 2 * R];
+    if (ks > 1) {
         if (lane == 0) {
 #pragma unroll
             for (int j = 0; j < 2; ++j)
 #pragma unroll
-                for (int r = 0; r < R; ++r) sh[(warp * 2 + j) * R + r] = acc[j][r];
+                for (int r = 0; r < R; ++r) red[warp][j][r] = acc[j][r];
         }
         __syncthreads();
-        cta_allreduce_f32(comm, channel, sh, SK_WARPS * 2 * R);
-        if (lane == 0) {
+        if (kpart == 0 && lane == 0) {
+            for (int p = 1; p < ks; ++p)
+#pragma unroll
+                for (int j = 0; j < 2; ++j)
+#pragma unroll
+                    for (int r = 0; r < R; ++r) acc[j][r] += red[warp + p][j][r];
+        }
+    }
+    const bool writer = lane == 0 && kpart == 0;
+    if (mode == SK_OUT_ALLREDUCE_BF16) {
+        __shared__ float sh[SK_WARPS * 2 * R];
+        if (writer) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int r = 0; r < R; ++r) sh[(group * 2 + j) * R + r] = acc[j][r];
+        }
+        __syncthreads();
+        cta_allreduce_f32(comm, channel, sh, groups * 2 * R);
+        if (writer) {
 #pragma unroll
             for (int j = 0; j < 2; ++j)
 #pragma unroll
                 for (int r = 0; r < R; ++r)
                     if (n0 + j < N && r < rows)
-                        reinterpret_cast<bf16*>(out)[(int64_t)r * os + n0 + j] = __float2bfloat16_rn(sh[(warp * 2 + j) * R + r]);
+                        reinterpret_cast<bf16*>(out)[(int64_t)r * os + n0 + j] = __float2bfloat16_rn(sh[(group * 2 + j) * R + r]);
         }
         return;
     }
@@ -143,7 +165,7 @@ skinny_bf16_kernel(const bf16* __restrict__ x, int64_t xs, int rows, const bf16*
                 unsigned long long key = 0ull;
 #pragma unroll
                 for (int j = 0; j < 2; ++j)
-                    if (n0 + j < N) {
+                    if (kpart == 0 && n0 + j < N) {
                         const float v = bf16_round(acc[j][r]);
                         if (!isfinite(v)) raise_status(comm.status, GLMB_STATUS_NONFINITE);
                         const unsigned long long k2 = candidate_key(v, channel + n0 + j);
@@ -156,12 +178,12 @@ skinny_bf16_kernel(const bf16* __restrict__ x, int64_t xs, int rows, const bf16*
         if ((int)threadIdx.x < rows && (int)threadIdx.x < R) {
             unsigned long long key = 0ull;
 #pragma unroll
-            for (int w = 0; w < SK_WARPS; ++w) key = best_s[w][threadIdx.x] > key ? best_s[w][threadIdx.x] : key;
+            for (int w2 = 0; w2 < SK_WARPS; ++w2) key = best_s[w2][threadIdx.x] > key ? best_s[w2][threadIdx.x] : key;
             if (key) atomicMax(reinterpret_cast<unsigned long long*>(out) + threadIdx.x, key);
         }
         return;
     }
-    if (lane == 0 && n0 < N) {
+    if (writer && n0 < N) {
 #pragma unroll
         for (int j = 0; j < 2; ++j)
 #pragma unroll
@@ -177,20 +199,36 @@ skinny_bf16_kernel(const bf16* __restrict__ x, int64_t xs, int rows, const bf16*
 template <int R>
 __global__ void __launch_bounds__(SK_THREADS)
 skinny_bf16_swiglu_kernel(const bf16* __restrict__ x, int64_t xs, int rows, const bf16* __restrict__ wg,
-                          const bf16* __restrict__ wu, int64_t ws, int N, int K, bf16* __restrict__ act, int64_t as) {
+                          const bf16* __restrict__ wu, int64_t ws, int N, int K, bf16* __restrict__ act, int64_t as, int ks) {
+    __shared__ float red[SK_WARPS][2][R];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n = blockIdx.x * SK_WARPS + warp;
-    if (n >= N) return;
+    const int group = warp / ks, kpart = warp % ks;
+    const int n = blockIdx.x * (SK_WARPS / ks) + group;
+    const bool valid = n < N;
     const bf16* xr[R];
 #pragma unroll
     for (int r = 0; r < R; ++r) xr[r] = x + (int64_t)(r < rows ? r : 0) * xs;
     float acc[2][R];
 #pragma unroll
     for (int r = 0; r < R; ++r) acc[0][r] = acc[1][r] = 0.f;
-    const bf16* wp[2] = {wg + (int64_t)n * ws, wu + (int64_t)n * ws};
-    warp_dot_bf16<R, 2>(xr, wp, K, lane, acc);
-    warp_reduce_all<R, 2>(acc);
-    if (lane == 0) {
+    if (valid) {
+        const bf16* wp[2] = {wg + (int64_t)n * ws, wu + (int64_t)n * ws};
+        const int kspan = K / ks;
+        warp_dot_bf16<R, 2>(xr, wp, kpart * kspan, (kpart + 1) * kspan, lane, acc);
+        warp_reduce_all<R, 2>(acc);
+    }
+    if (ks > 1) {
+        if (lane == 0) {
+#pragma unroll
+            for (int r = 0; r < R; ++r) { red[warp][0][r] = acc[0][r]; red[warp][1][r] = acc[1][r]; }
+        }
+        __syncthreads();
+        if (kpart == 0 && lane == 0)
+            for (int p = 1; p < ks; ++p)
+#pragma unroll
+                for (int r = 0; r < R; ++r) { acc[0][r] += red[warp + p][0][r]; acc[1][r] += red[warp + p][1][r]; }
+    }
+    if (lane == 0 && kpart == 0 && valid) {
 #pragma unroll
         for (int r = 0; r < R; ++r)
             if (r < rows) {
@@ -347,6 +385,13 @@ moe_combine_kernel(const bf16* __restrict__ dw, const int* __restrict__ topk_ids
         else { CALL(8); }                                     \
     } while (0)
 
+// How many warps share one unit of output (a row pair or a gate/up pair) so that about four CTAs land on every SM.
+static int pick_ksplit(int units, int K) {
+    int ks = 1;
+    while (ks < SK_WARPS && units * ks < 148 * 4 * SK_WARPS && K % (ks * 2 * 256) == 0 && K / (ks * 2) >= 512) ks *= 2;
+    return ks;
+}
+
 static PeerComm single_comm() {
     PeerComm c;
     memset(&c, 0, sizeof(c));
@@ -360,13 +405,14 @@ GLMB_API int glmb_skinny_bf16(const void* x, int64_t xs, int rows, const void* w
                               int mode, int batch, int64_t xb, int64_t wb, int64_t ob, const PeerComm* comm, int channel,
                               void* stream) {
     if (rows < 1 || rows > GLMB_MAX_ROWS || (K & 7) || (xs & 7) || (ws & 7) || (xb & 7) || (wb & 7) || batch < 1) return 1;
-    const dim3 grid(ceil_div(N, SK_WARPS * 2), batch);
+    const int ks = pick_ksplit(ceil_div(N, 2) * batch, K);
+    const dim3 grid(ceil_div(N, (SK_WARPS / ks) * 2), batch);
     PeerComm c = comm ? *comm : single_comm();
     if (mode == SK_OUT_ALLREDUCE_BF16 && c.world > 1 && (int)(grid.x * grid.y) > GLMB_AR_MAX_CTAS) return 2;
     if (mode == SK_OUT_ALLREDUCE_BF16 && c.world == 1) mode = SK_OUT_BF16;
 #define CALL(RR)                                                                                                   \
     skinny_bf16_kernel<RR><<<grid, SK_THREADS, 0, (cudaStream_t)stream>>>((const bf16*)x, xs, rows, (const bf16*)w, ws, N, K, \
-                                                                          out, os, mode, xb, wb, ob, c, channel)
+                                                                          out, os, mode, ks, xb, wb, ob, c, channel)
     DISPATCH_R(rows, CALL);
 #undef CALL
     return (int)cudaGetLastError();
@@ -375,10 +421,11 @@ GLMB_API int glmb_skinny_bf16(const void* x, int64_t xs, int rows, const void* w
 GLMB_API int glmb_skinny_bf16_swiglu(const void* x, int64_t xs, int rows, const void* wg, const void* wu, int64_t ws, int N, int K,
                                      void* act, int64_t as, void* stream) {
     if (rows < 1 || rows > GLMB_MAX_ROWS || (K & 7) || (xs & 7) || (ws & 7)) return 1;
-    const int grid = ceil_div(N, SK_WARPS);
+    const int ks = pick_ksplit(N, K);
+    const int grid = ceil_div(N, SK_WARPS / ks);
 #define CALL(RR)                                                                                                          \
     skinny_bf16_swiglu_kernel<RR><<<grid, SK_THREADS, 0, (cudaStream_t)stream>>>((const bf16*)x, xs, rows, (const bf16*)wg, \
-                                                                                 (const bf16*)wu, ws, N, K, (bf16*)act, as)
+                                                                                 (const bf16*)wu, ws, N, K, (bf16*)act, as, ks)
     DISPATCH_R(rows, CALL);
 #undef CALL
     return (int)cudaGetLastError();

@@ -153,24 +153,31 @@ __global__ void __launch_bounds__(256) qkv_a_post_kernel(QkvPostArgs a) {
     const bool write_cache = owner && active;
 
     // q_a RMSNorm
-    float ss = 0.f;
-    for (int i = threadIdx.x; i < a.Q; i += blockDim.x) {
-        const float v = bf16_round(p[i]);
-        ss = fmaf(v, v, ss);
+    // (both sums of squares are accumulated in one sweep of float4 loads and reduced together)
+    const float* c = p + a.Q;
+    float ss = 0.f, ss_kv = 0.f;
+    for (int i = threadIdx.x * 4; i < a.Q; i += blockDim.x * 4) {
+        const float4 v4 = *reinterpret_cast<const float4*>(p + i);
+        const float v0 = bf16_round(v4.x), v1 = bf16_round(v4.y), v2 = bf16_round(v4.z), v3 = bf16_round(v4.w);
+        ss = fmaf(v0, v0, ss); ss = fmaf(v1, v1, ss); ss = fmaf(v2, v2, ss); ss = fmaf(v3, v3, ss);
+    }
+    for (int i = threadIdx.x * 4; i < a.L; i += blockDim.x * 4) {
+        const float4 v4 = *reinterpret_cast<const float4*>(c + i);
+        const float v0 = bf16_round(v4.x), v1 = bf16_round(v4.y), v2 = bf16_round(v4.z), v3 = bf16_round(v4.w);
+        ss_kv = fmaf(v0, v0, ss_kv); ss_kv = fmaf(v1, v1, ss_kv); ss_kv = fmaf(v2, v2, ss_kv); ss_kv = fmaf(v3, v3, ss_kv);
     }
     float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)a.Q + a.eps);
-    for (int i = threadIdx.x; i < a.Q; i += blockDim.x) {
-        const float y = bf16_round(bf16_round(p[i]) * inv);
-        a.q_resid[(int64_t)r * a.Q + i] = __float2bfloat16_rn(y * __bfloat162float(a.q_norm_w[i]));
+    const float inv_kv = 1.0f / sqrtf(block_sum(ss_kv, scratch) / (float)a.L + a.eps);
+    for (int i = threadIdx.x * 4; i < a.Q; i += blockDim.x * 4) {
+        const float4 v4 = *reinterpret_cast<const float4*>(p + i);
+        const uint2 w2 = *reinterpret_cast<const uint2*>(a.q_norm_w + i);
+        uint2 o;
+        o.x = pack_bf16(bf16_round(bf16_round(v4.x) * inv) * bf16_lo(w2.x), bf16_round(bf16_round(v4.y) * inv) * bf16_hi(w2.x));
+        o.y = pack_bf16(bf16_round(bf16_round(v4.z) * inv) * bf16_lo(w2.y), bf16_round(bf16_round(v4.w) * inv) * bf16_hi(w2.y));
+        *reinterpret_cast<uint2*>(a.q_resid + (int64_t)r * a.Q + i) = o;
     }
     // kv_a latent RMSNorm
-    const float* c = p + a.Q;
-    ss = 0.f;
-    for (int i = threadIdx.x; i < a.L; i += blockDim.x) {
-        const float v = bf16_round(c[i]);
-        ss = fmaf(v, v, ss);
-    }
-    inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)a.L + a.eps);
+    inv = inv_kv;
     for (int i = threadIdx.x; i < a.L; i += blockDim.x) {
         const float y = bf16_round(bf16_round(c[i]) * inv);
         const bf16 o = __float2bfloat16_rn(y * __bfloat162float(a.kv_norm_w[i]));
@@ -291,7 +298,7 @@ q_absorb_kernel(const bf16* __restrict__ q_nope, int rows, const bf16* __restric
     for (int r = 0; r < R; ++r) acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.f;
     const bf16* wk = kv_b + (int64_t)h * (nope + vdim) * L;
     if (c0 < L) {
-#pragma unroll 4
+#pragma unroll 8
         for (int d = d0; d < d1; ++d) {
             const uint2 wv = *reinterpret_cast<const uint2*>(wk + (int64_t)d * L + c0);
             const float w0 = bf16_lo(wv.x), w1 = bf16_hi(wv.x), w2 = bf16_lo(wv.y), w3 = bf16_hi(wv.y);
@@ -351,7 +358,7 @@ GLMB_API int glmb_add_rmsnorm(const void* update, void* residual, const void* we
 }
 
 GLMB_API int glmb_qkv_a_post(const QkvPostArgs* args, int rows, void* stream) {
-    if (args->D > 256 || (args->rd & 1)) return 1;
+    if (args->D > 256 || (args->rd & 1) || (args->Q & 3) || (args->L & 3) || (args->proj_stride & 3)) return 1;
     qkv_a_post_kernel<<<rows, 256, 0, (cudaStream_t)stream>>>(*args);
     return (int)cudaGetLastError();
 }

@@ -89,7 +89,7 @@ class Workspace:
         f32 = lambda *s: torch.empty(s, dtype=torch.float32, device=dev)  # noqa: E731
         i32 = lambda *s: torch.zeros(s, dtype=torch.int32, device=dev)  # noqa: E731
         self.residual, self.x, self.update = bf(rows, H), bf(rows, H), bf(rows, H)
-        self.proj_a = f32(rows, Q + W + D + IH)
+        self.proj_a = f32(rows, (Q + W + D + IH + 3) // 4 * 4)  # rows stay 16-byte aligned for float4 loads
         self.q_resid = bf(rows, Q)
         self.head_w = f32(rows, IH)
         self.q_proj = f32(rows, hl * g.qk_head_dim + IH * D)
