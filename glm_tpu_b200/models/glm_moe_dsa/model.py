@@ -295,9 +295,10 @@ class GlmMoeDsaModel:
         pos = torch.arange(max_ctx, device=scores.device)
         mine = ((pos // self.cache.stripe) % self.world) == self.rank
         view = scores[:, :max_ctx]
-        view.mul_(mine.to(view.dtype)[None, :])
-        view.nan_to_num_(0.0, 0.0, 0.0)
-        dist.all_reduce(view, group=self.group)
+        merged = torch.where(mine[None, :], view, torch.zeros((), device=scores.device)).contiguous()
+        merged.nan_to_num_(0.0, 0.0, 0.0)
+        dist.all_reduce(merged, group=self.group)
+        view.copy_(merged)
 
     def _merge_partials_nccl(self, ws: Workspace, r0: int, n: int) -> None:
         import torch.distributed as dist

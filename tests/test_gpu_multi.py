@@ -1,0 +1,60 @@
+"""Two-GPU model test: in-kernel peer-memory collectives vs the NCCL baseline vs the CPU oracle.
+
+The ranks run as child processes (torch.distributed.run, 127.0.0.1 rendezvous) with NVLS off; every device wait is
+bounded, so a protocol bug shows up as a status word, not as a hang.
+"""
+
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+from glm_tpu_b200.config.model import small_geometry
+from glm_tpu_b200.models.glm_moe_dsa.weights import random_checkpoint
+from glm_tpu_b200.oracle import contract
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def _launch(world, out):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=str(ROOT))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+           "--master-port", "29533", str(ROOT / "tests" / "multi_gpu_worker.py"), "--out", str(out)]
+    done = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert done.returncode == 0, done.stdout[-3000:] + done.stderr[-3000:]
+    return json.loads(Path(out).read_text())
+
+
+def _bad_tokens(g, ckpt, prompt, generated, capacity, decisions):
+    w = contract.OracleWeights.from_checkpoint(g, ckpt)
+    seq = list(prompt) + list(generated[:-1])
+    selected = {int(k): [torch.tensor(r, dtype=torch.int64) for r in v[: len(seq)]] for k, v in decisions["selected"].items()}
+    experts = {int(k): torch.tensor(v[: len(seq)], dtype=torch.int64) for k, v in decisions["experts"].items()}
+    trace = contract.forward(w, seq, capacity=capacity, selected=selected, expert_ids=experts)
+    bad = []
+    for i, tok in enumerate(generated):
+        row = trace.logits[len(prompt) - 1 + i]
+        gap = float(row.max() - row[tok])
+        if gap > 2 * 2**-7 * float(row.abs().max()) + 1e-6:
+            bad.append((i, tok, int(trace.tokens[len(prompt) - 1 + i]), gap))
+    return bad
+
+
+def test_two_gpu_fused_matches_oracle_and_nccl(native_lib, tmp_path):
+    world = 2
+    res = _launch(world, tmp_path / "out.json")
+    g = small_geometry(4)
+    ckpt = random_checkpoint(g, seed=5)
+    assert res["all_ranks_agree"]
+    assert res["fused_graph_kind"] == "cuda_graph"
+    assert res["fused_graph"] == res["fused_eager"]
+    bad = _bad_tokens(g, ckpt, res["prompt"], res["fused_eager"], 128, res["decisions"])
+    assert not bad, bad
+    # the baseline sums partials in another order, so compare it with the oracle under the same decisions
+    assert not _bad_tokens(g, ckpt, res["prompt"], res["nccl"], 128, res["decisions"]) or res["nccl"] == res["fused_eager"]
+    assert len(res["two_lanes"]) == 2 and all(len(t) == 6 for t in res["two_lanes"])
