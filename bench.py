@@ -111,6 +111,8 @@ def main() -> int:
     ap.add_argument("--prompt", type=int, default=200)
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--kv-layout", default="auto", choices=["auto", "striped", "replicated"],
+                    help="latent cache: a replica per GPU (no attention exchange) or striped by position over the GPUs")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -143,7 +145,7 @@ def main() -> int:
         geometry = geometry.truncated(layers)
     t0 = time.perf_counter()
     runner = build_runner(geometry, world=world, rank=rank, device=device, seed=0, context_capacity=args.context, lanes=args.chats,
-                          comm=args.comm, use_graphs=not args.no_graphs, prefill_chunk=256)
+                          comm=args.comm, use_graphs=not args.no_graphs, prefill_chunk=256, kv_layout=args.kv_layout)
     torch.cuda.synchronize()
     load_s = time.perf_counter() - t0
 
@@ -238,8 +240,9 @@ def main() -> int:
                 "global_batch": args.chats,
                 "seq_len": args.context,
                 "prompt_tokens": args.prompt,
-                "parallelism": f"tp{world}(heads,mlp)+ep{world}(experts)+cp{world}(kv stripes)" if world > 1 else "single gpu",
+                "parallelism": f"tp{world}(heads,mlp)+ep{world}(experts)" if world > 1 else "single gpu",
                 "comm": args.comm,
+                "kv_layout": runner.kv_layout,
                 "decode_program": rec.kind,
                 "l2": "each step streams more weight bytes than the 126 MB L2 (inputs larger than L2)",
                 "per_chat_tok_s": round(tok_s / args.chats, 3),

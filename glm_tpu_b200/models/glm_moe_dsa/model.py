@@ -84,7 +84,7 @@ class Workspace:
         self.attn_rows = min(rows, attn_rows or rows)
         H, Q, L, rd, W = g.hidden_size, g.q_lora_rank, g.kv_lora_rank, g.qk_rope_head_dim, g.kv_row_width
         IH, D, k = g.index_heads, g.index_head_dim, g.index_top_k
-        hl, ht = lay.heads_local, g.attention_heads
+        hl, ht = lay.heads_local, model.attn_heads
         bf = lambda *s: torch.empty(s, dtype=torch.bfloat16, device=dev)  # noqa: E731
         f32 = lambda *s: torch.empty(s, dtype=torch.float32, device=dev)  # noqa: E731
         i32 = lambda *s: torch.zeros(s, dtype=torch.int32, device=dev)  # noqa: E731
@@ -97,19 +97,21 @@ class Workspace:
         self.q_idx = f32(rows, IH, D)
         self.score_stride = score_stride or model.cache.context_capacity
         peer = model.peer
+        self.r_q = self.r_scores = self.r_xpart = self.r_cand = None
         if self.peer_visible:
+            self.r_cand = peer.region(f"{tag}.cand", peer.world * rows * 8)
+            self.cand = peer.tensor(self.r_cand, (peer.world, rows), torch.int64)
+        else:
+            self.cand = torch.zeros((max(1, peer.world), rows), dtype=torch.int64, device=dev)
+        if self.peer_visible and model.striped:  # the attention exchanges exist only with position-striped caches
             self.r_q = peer.region(f"{tag}.q_full", rows * ht * W * 2)
             self.r_scores = peer.region(f"{tag}.scores", rows * self.score_stride * 4)
             self.r_xpart = peer.region(f"{tag}.xpart", peer.world * self.attn_rows * hl * (L + 2) * 4)
-            self.r_cand = peer.region(f"{tag}.cand", peer.world * rows * 8)
             self.q_full = peer.tensor(self.r_q, (rows, ht, W), torch.bfloat16)
             self.scores = peer.tensor(self.r_scores, (rows, self.score_stride), torch.float32)
-            self.cand = peer.tensor(self.r_cand, (peer.world, rows), torch.int64)
         else:
-            self.r_q = self.r_scores = self.r_xpart = self.r_cand = None
             self.q_full = bf(rows, ht, W)
             self.scores = f32(rows, self.score_stride)
-            self.cand = torch.zeros((max(1, peer.world), rows), dtype=torch.int64, device=dev)
         self.local_best = torch.zeros(rows, dtype=torch.int64, device=dev)  # packed argmax keys of this rank's vocabulary slice
         self.sel_global, self.sel_local, self.sel_counts = i32(rows, k), i32(rows, k), i32(rows, 2)
         self.max_chunks = -(-k // native.attn_chunk())
@@ -138,8 +140,15 @@ class GlmMoeDsaModel:
         self.g, self.layout = weights.geometry, weights.layout
         self.device = weights.embed.device
         self.world, self.rank = self.layout.world, self.layout.rank
-        if cache.world != self.world:
-            raise ValueError("cache striping and parallel layout disagree on the world size")
+        # cache.world == world: caches striped by position over the GPUs (needed when a replica would not fit);
+        # cache.world == 1 with several GPUs: every GPU keeps the whole latent cache (it is shared by all heads),
+        # attends with its own heads only, and attention needs no cross-GPU exchange at all.
+        if cache.world not in (1, self.world):
+            raise ValueError("the caches are either replicated (cache world 1) or striped over all GPUs")
+        self.striped = cache.world > 1
+        self.cache_rank = self.rank if self.striped else 0
+        self.attn_heads = self.g.attention_heads if (self.striped or self.world == 1) else self.layout.heads_local
+        self.head_base = self.rank * self.layout.heads_local if self.striped else 0
         if comm not in ("fused", "nccl"):
             raise ValueError("comm is 'fused' or 'nccl'")
         self.comm_mode = comm
@@ -182,9 +191,13 @@ class GlmMoeDsaModel:
         full = g.indexer_types[layer] == "full"
         Q, L, rd, W = g.q_lora_rank, g.kv_lora_rank, g.qk_rope_head_dim, g.kv_row_width
         IH, D = g.index_heads, g.index_head_dim
-        hl, ht = lay.heads_local, g.attention_heads
+        hl, ht, hb = lay.heads_local, self.attn_heads, self.head_base
         fused = ws.peer_visible
         kc = self.peer.comm if fused else None
+        cw, cr = cache.world, self.cache_rank
+        gather = self.striped and self.world > 1  # attention spans the GPUs: queries, scores and partials are exchanged
+        xf = fused and gather                      # ... inside the kernels
+        kx = kc if xf else None
         x = ws.x[:rows]
         self._linear_f32(x, lw.w_qkv_a, ws.proj_a, decode)
         a = native.QkvPostArgs()
@@ -202,7 +215,7 @@ class GlmMoeDsaModel:
         a.has_indexer = int(full)
         a.layer, a.layers = layer, g.num_layers
         a.index_slot, a.full_layers = g.index_slot(layer), len(g.full_layers)
-        a.local_cap, a.stripe, a.world, a.rank, a.capacity = cache.local_capacity, cache.stripe, self.world, self.rank, cache.context_capacity
+        a.local_cap, a.stripe, a.world, a.rank, a.capacity = cache.local_capacity, cache.stripe, cw, cr, cache.context_capacity
         a.eps, a.key_eps, a.head_scale = g.rms_norm_eps, cache.dsa.key_norm_eps, self.head_scale
         a.status = self.peer.status_ptr
         native.qkv_a_post(a, rows)
@@ -212,32 +225,32 @@ class GlmMoeDsaModel:
         b.q, b.q_stride = ws.q_proj.data_ptr(), ws.q_proj.stride(0)
         b.rope_table, b.inv_freq, b.row_pos = self.rope.data_ptr(), self.inv_freq.data_ptr(), row_pos.data_ptr()
         b.q_nope, b.q_full, b.q_idx = ws.q_nope.data_ptr(), ws.q_full.data_ptr(), ws.q_idx.data_ptr()
-        b.heads_local, b.head_base, b.heads_total = hl, self.rank * hl, ht
+        b.heads_local, b.head_base, b.heads_total = hl, hb, ht
         b.nope, b.rd, b.L, b.IH, b.D = g.qk_nope_head_dim, rd, L, IH, D
         b.has_indexer, b.capacity = int(full), cache.context_capacity
         native.q_post(b, rows)
 
         if decode:
-            native.q_absorb(ws.q_nope, rows, lw.kv_b, hl, self.rank * hl, ht, g.qk_nope_head_dim, g.v_head_dim, L, rd, ws.q_full,
-                            ws.r_q.offset if fused else 0, kc, native.SIG_Q)
-            if self.world > 1 and not fused:
+            native.q_absorb(ws.q_nope, rows, lw.kv_b, hl, hb, ht, g.qk_nope_head_dim, g.v_head_dim, L, rd, ws.q_full,
+                            ws.r_q.offset if xf else 0, kx, native.SIG_Q)
+            if gather and not xf:
                 self._allgather_heads(ws.q_full[:rows])
         else:
             w_k = lw.kv_b[:, : g.qk_nope_head_dim, :]  # [hl, nope, L]
             q_c = torch.einsum("rhd,hdc->rhc", ws.q_nope[:rows], w_k)
-            ws.q_full[:rows, self.rank * hl : (self.rank + 1) * hl, :L] = q_c
-            if self.world > 1:
+            ws.q_full[:rows, hb : hb + hl, :L] = q_c
+            if gather:
                 self._allgather_heads(ws.q_full[:rows])
 
         if full:
             native.indexer_score(ws.q_idx, ws.head_w, state.index_cache, row_pos, row_lane, rows, IH, D, g.index_slot(layer),
-                                 len(g.full_layers), cache.local_capacity, cache.stripe, self.world, self.rank,
+                                 len(g.full_layers), cache.local_capacity, cache.stripe, cw, cr,
                                  cache.context_capacity, max_ctx, ws.score_stride, self.index_scale, ws.scores,
-                                 ws.r_scores.offset if fused else 0, kc, native.SIG_SCORES, self.peer.status_ptr)
-            if self.world > 1 and not fused:
+                                 ws.r_scores.offset if xf else 0, kx, native.SIG_SCORES, self.peer.status_ptr)
+            if gather and not xf:
                 self._merge_scores(ws.scores[:rows], max_ctx)
             native.topk_select(ws.scores, row_pos, rows, cache.context_capacity, ws.score_stride, g.index_top_k, cache.stripe,
-                               self.world, self.rank, ws.sel_global, ws.sel_local, ws.sel_counts, kc, native.SIG_SCORES)
+                               cw, cr, ws.sel_global, ws.sel_local, ws.sel_counts, kx, native.SIG_SCORES)
             if self.trace is not None:
                 self.trace.setdefault("sel_global", {})[layer] = ws.sel_global[:rows].clone()
                 self.trace.setdefault("scores", {})[layer] = ws.scores[:rows].clone()
@@ -247,13 +260,13 @@ class GlmMoeDsaModel:
             n = min(ws.attn_rows, rows - r0)
             native.sparse_mla_partial(ws.q_full[r0:], state.kv_cache, ws.sel_local[r0:], ws.sel_counts[r0:], row_lane[r0:], n, ht, L, rd,
                                       layer, g.num_layers, cache.local_capacity, g.index_top_k, ws.max_chunks, self.softmax_scale,
-                                      ws.part_o, ws.part_ml, kc, native.SIG_Q if fused else -1, self.peer.status_ptr)
-            if self.world == 1:
+                                      ws.part_o, ws.part_ml, kx, native.SIG_Q if xf else -1, self.peer.status_ptr)
+            if not gather:
                 native.attn_local_merge(ws.part_o, ws.part_ml, ws.sel_counts[r0:], n, ht, L, g.index_top_k, ws.max_chunks, ws.o_lat[r0:], hl)
-            elif fused:
+            elif xf:
                 native.attn_local_merge(ws.part_o, ws.part_ml, ws.sel_counts[r0:], n, ht, L, g.index_top_k, ws.max_chunks, None, hl,
-                                        ws.r_xpart.offset, kc, native.SIG_ATTN)
-                native.attn_final_merge(n, L, hl, ws.r_xpart.offset, ws.o_lat[r0:], kc, native.SIG_ATTN)
+                                        ws.r_xpart.offset, kx, native.SIG_ATTN)
+                native.attn_final_merge(n, L, hl, ws.r_xpart.offset, ws.o_lat[r0:], kx, native.SIG_ATTN)
             else:
                 self._merge_partials_nccl(ws, r0, n)
         # value projection per head, then the K-split output projection with its reduction

@@ -70,12 +70,21 @@ class _LaunchCounter:
 class GpuModelRunner:
     def __init__(self, weights: DeviceWeights, *, context_capacity: int, lanes: int = 1, stripe: int = 64, comm: str = "fused",
                  group=None, prefill_chunk: int = 512, use_graphs: bool = True, wait_limit: int = 2_000_000,
-                 staging_bytes: int | None = None):
+                 staging_bytes: int | None = None, kv_layout: str = "auto", replica_budget_bytes: int = 32 << 30):
         self.weights = weights
         self.g, self.layout = weights.geometry, weights.layout
         self.device = weights.embed.device
         self.world, self.rank = self.layout.world, self.layout.rank
-        self.cache = CacheConfig(self.g, context_capacity, world=self.world, stripe=stripe, lanes=lanes)
+        # KV layout: a full replica of the latent cache on every GPU removes all attention exchanges; stripe the caches
+        # by position over the GPUs once a replica would not fit the budget (long contexts, many lanes).
+        if kv_layout not in ("auto", "striped", "replicated"):
+            raise ValueError("kv_layout is 'auto', 'striped' or 'replicated'")
+        replica = CacheConfig(self.g, context_capacity, world=1, stripe=stripe, lanes=lanes)
+        if kv_layout == "auto":
+            kv_layout = "replicated" if replica.cache_bytes_per_gpu() <= replica_budget_bytes else "striped"
+        self.kv_layout = kv_layout if self.world > 1 else "local"
+        self.cache = replica if kv_layout == "replicated" else CacheConfig(self.g, context_capacity, world=self.world, stripe=stripe,
+                                                                          lanes=lanes)
         self.lanes = lanes
         self.report = RunnerReport()
         self.use_graphs = use_graphs

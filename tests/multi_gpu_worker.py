@@ -16,11 +16,11 @@ import torch  # noqa: E402
 import torch.distributed as dist  # noqa: E402
 
 
-def run(g, ckpt, prompt, new_tokens, capacity, stripe, comm, use_graphs, record, world, rank, device, lanes=1):
+def run(g, ckpt, prompt, new_tokens, capacity, stripe, comm, use_graphs, record, world, rank, device, lanes=1, kv_layout="striped"):
     from glm_tpu_b200.runner.gpu_runner import build_runner
 
     runner = build_runner(g, world=world, rank=rank, device=device, checkpoint=ckpt, context_capacity=capacity, lanes=lanes,
-                          stripe=stripe, use_graphs=use_graphs, prefill_chunk=32, comm=comm, wait_limit=4_000_000)
+                          stripe=stripe, use_graphs=use_graphs, prefill_chunk=32, comm=comm, wait_limit=4_000_000, kv_layout=kv_layout)
     decisions = {"selected": {i: [] for i in g.full_layers}, "experts": {i: [] for i in g.sparse_layers}}
     if record:
         inner = runner.model.run_rows
@@ -86,6 +86,13 @@ def main():
     prompts2 = [prompt[0][:40], prompt[0][20:65]]
     both, _, _ = run(g, ckpt, prompts2, 6, 128, 16, "fused", True, False, world, rank, device, lanes=2)
     result["two_lanes"] = both
+    # the same chat with a full cache replica per GPU (no attention exchange), graph and NCCL-baseline variants
+    rep_eager, rep_dec, _ = run(g, ckpt, prompt, 10, 128, 16, "fused", False, True, world, rank, device, kv_layout="replicated")
+    result["replicated_eager"] = rep_eager[0]
+    result["replicated_decisions"] = {"selected": {str(k): v for k, v in rep_dec["selected"].items()},
+                                      "experts": {str(k): v for k, v in rep_dec["experts"].items()}}
+    rep, _, _ = run(g, ckpt, prompt, 10, 128, 16, "fused", True, False, world, rank, device, kv_layout="replicated")
+    result["replicated_graph"] = rep[0]
     result["prompt"] = prompt[0]
     gathered = [None] * world
     dist.all_gather_object(gathered, result["fused_graph"])
