@@ -61,6 +61,7 @@ sparse_mla_partial_kernel(const bf16* __restrict__ q_full, const bf16* __restric
                           const int* __restrict__ sel_counts, const int* __restrict__ row_lane, int H, int rd, int layer,
                           int layers, int local_cap, int top_k, int max_chunks, float scale, float* __restrict__ part_o,
                           float* __restrict__ part_ml, PeerComm comm, int wait_sig, uint32_t* status) {
+    GLMB_PDL_PROLOGUE();
     constexpr int L = 8 * TPW * PVW;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int W = L + rd;
@@ -198,6 +199,7 @@ __global__ void __launch_bounds__(128)
 attn_local_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, const int* __restrict__ sel_counts,
                         int H, int L, int top_k, int max_chunks, bf16* __restrict__ o_lat, int heads_local,
                         int64_t xpart_offset, PeerComm comm, int sig) {
+    GLMB_PDL_PROLOGUE();
     __shared__ float w_s[64];
     const int h = blockIdx.x, r = blockIdx.y;
     const int count = min(max(sel_counts[2 * r + 1], 0), top_k);
@@ -235,6 +237,7 @@ attn_local_merge_kernel(const float* __restrict__ part_o, const float* __restric
 // grid (heads_local, rows): merge the `world` partials of this rank's heads in rank order.
 __global__ void __launch_bounds__(128)
 attn_final_merge_kernel(int L, int heads_local, int64_t xpart_offset, bf16* __restrict__ o_lat, PeerComm comm, int sig) {
+    GLMB_PDL_PROLOGUE();
     cta_wait_signal(comm, sig);
     const int hl = blockIdx.x, r = blockIdx.y, rows = gridDim.y;
     const float* base = reinterpret_cast<const float*>(comm.data[comm.rank] + xpart_offset);
@@ -273,7 +276,7 @@ static int launch_partial(const void* q_full, const void* kv_cache, const int* s
         attr_set = true;
     }
     dim3 grid(max_chunks, rows, (H + AT_HEADS - 1) / AT_HEADS);
-    sparse_mla_partial_kernel<TPW, PVW><<<grid, AT_THREADS, smem, stream>>>((const bf16*)q_full, (const bf16*)kv_cache, sel_local,
+    GLMB_LAUNCH((sparse_mla_partial_kernel<TPW, PVW>), grid, AT_THREADS, smem, stream, (const bf16*)q_full, (const bf16*)kv_cache, sel_local,
                                                                            sel_counts, row_lane, H, rd, layer, layers, local_cap,
                                                                            top_k, max_chunks, scale, part_o, part_ml, c, wait_sig,
                                                                            status);
@@ -304,7 +307,7 @@ GLMB_API int glmb_attn_local_merge(const float* part_o, const float* part_ml, co
     PeerComm c;
     if (comm) c = *comm; else { memset(&c, 0, sizeof(c)); c.world = 1; }
     dim3 grid(H, rows);
-    attn_local_merge_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(part_o, part_ml, sel_counts, H, L, top_k, max_chunks,
+    GLMB_LAUNCH(attn_local_merge_kernel, grid, 128, 0, (cudaStream_t)stream, part_o, part_ml, sel_counts, H, L, top_k, max_chunks,
                                                                     (bf16*)o_lat, heads_local, xpart_offset, c, sig);
     return (int)cudaGetLastError();
 }
@@ -313,6 +316,6 @@ GLMB_API int glmb_attn_final_merge(int rows, int L, int heads_local, int64_t xpa
                                    int sig, void* stream) {
     if (!comm || comm->world < 2) return 1;
     dim3 grid(heads_local, rows);
-    attn_final_merge_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(L, heads_local, xpart_offset, (bf16*)o_lat, *comm, sig);
+    GLMB_LAUNCH(attn_final_merge_kernel, grid, 128, 0, (cudaStream_t)stream, L, heads_local, xpart_offset, (bf16*)o_lat, *comm, sig);
     return (int)cudaGetLastError();
 }

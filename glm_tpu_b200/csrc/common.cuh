@@ -91,3 +91,34 @@ __device__ __forceinline__ void raise_status(uint32_t* status, uint32_t bits) {
 }
 
 static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+// ---- programmatic dependent launch ----------------------------------------------------------------------
+// Every kernel starts with GLMB_PDL_PROLOGUE: it lets the NEXT kernel of the stream start launching right away
+// (its CTAs become resident as this grid's CTAs retire) and then waits until the PREVIOUS kernel has completed and
+// its memory is visible.  With ~1500 small kernels per decode step this hides most of the launch latency.
+// Nothing may be read or written before the wait.  Without the launch attribute both instructions are no-ops.
+#define GLMB_PDL_PROLOGUE()                                      \
+    do {                                                         \
+        asm volatile("griddepcontrol.launch_dependents;");       \
+        asm volatile("griddepcontrol.wait;" ::: "memory");       \
+    } while (0)
+
+// 1: launch with the programmatic-serialization attribute (default); 0: plain stream order.
+extern int g_glmb_pdl_enabled;
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t glmb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                      Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = g_glmb_pdl_enabled ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#define GLMB_LAUNCH(kernel, grid, block, smem, stream, ...) (void)glmb_launch(kernel, dim3(grid), dim3(block), smem, stream, __VA_ARGS__)

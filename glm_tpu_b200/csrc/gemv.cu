@@ -96,6 +96,7 @@ __global__ void __launch_bounds__(SK_THREADS)
 skinny_bf16_kernel(const bf16* __restrict__ x, int64_t xs, int rows, const bf16* __restrict__ w, int64_t ws, int N, int K,
                    void* __restrict__ out, int64_t os, int mode, int ks, int64_t xb, int64_t wb, int64_t ob, PeerComm comm,
                    int channel) {
+    GLMB_PDL_PROLOGUE();
     __shared__ float red[SK_WARPS][2][R];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int group = warp / ks, kpart = warp % ks, groups = SK_WARPS / ks;
@@ -200,6 +201,7 @@ template <int R>
 __global__ void __launch_bounds__(SK_THREADS)
 skinny_bf16_swiglu_kernel(const bf16* __restrict__ x, int64_t xs, int rows, const bf16* __restrict__ wg,
                           const bf16* __restrict__ wu, int64_t ws, int N, int K, bf16* __restrict__ act, int64_t as, int ks) {
+    GLMB_PDL_PROLOGUE();
     __shared__ float red[SK_WARPS][2][R];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int group = warp / ks, kpart = warp % ks;
@@ -250,6 +252,7 @@ moe_gateup_fp8_kernel(const bf16* __restrict__ x, int64_t xs, int top_k, const i
                       const int* __restrict__ tile_routes, const int* __restrict__ n_tiles, const uint8_t* __restrict__ wg,
                       const uint8_t* __restrict__ wu, const float* __restrict__ sg, const float* __restrict__ su,
                       int expert_base, int experts_local, int I, int H, bf16* __restrict__ act) {
+    GLMB_PDL_PROLOGUE();
     const int t = blockIdx.y;
     if (n_tiles && t >= *n_tiles) return;
     const int e = tile_expert[t] - expert_base;
@@ -290,6 +293,7 @@ __global__ void __launch_bounds__(SK_THREADS)
 moe_down_fp8_kernel(const bf16* __restrict__ act, const float* __restrict__ route_weight, const int* __restrict__ tile_expert,
                     const int* __restrict__ tile_routes, const int* __restrict__ n_tiles, const uint8_t* __restrict__ wd,
                     const float* __restrict__ sd, int expert_base, int experts_local, int I, int H, bf16* __restrict__ dw) {
+    GLMB_PDL_PROLOGUE();
     const int t = blockIdx.y;
     if (n_tiles && t >= *n_tiles) return;
     const int e = tile_expert[t] - expert_base;
@@ -340,6 +344,7 @@ __global__ void __launch_bounds__(128)
 moe_combine_kernel(const bf16* __restrict__ dw, const int* __restrict__ topk_ids, const float* __restrict__ shared_partial,
                    int rows_total, int top_k, int H, int expert_base, int experts_local, float scale, int plain,
                    bf16* __restrict__ out, float* __restrict__ routed_partial, PeerComm comm, int channel) {
+    GLMB_PDL_PROLOGUE();
     __shared__ float sh[2 * GLMB_MAX_ROWS * CB_COLS];
     const int n0 = blockIdx.x * CB_COLS;
     const int r0 = blockIdx.y * GLMB_MAX_ROWS;
@@ -411,7 +416,7 @@ GLMB_API int glmb_skinny_bf16(const void* x, int64_t xs, int rows, const void* w
     if (mode == SK_OUT_ALLREDUCE_BF16 && c.world > 1 && (int)(grid.x * grid.y) > GLMB_AR_MAX_CTAS) return 2;
     if (mode == SK_OUT_ALLREDUCE_BF16 && c.world == 1) mode = SK_OUT_BF16;
 #define CALL(RR)                                                                                                   \
-    skinny_bf16_kernel<RR><<<grid, SK_THREADS, 0, (cudaStream_t)stream>>>((const bf16*)x, xs, rows, (const bf16*)w, ws, N, K, \
+    GLMB_LAUNCH(skinny_bf16_kernel<RR>, grid, SK_THREADS, 0, (cudaStream_t)stream, (const bf16*)x, xs, rows, (const bf16*)w, ws, N, K, \
                                                                           out, os, mode, ks, xb, wb, ob, c, channel)
     DISPATCH_R(rows, CALL);
 #undef CALL
@@ -424,7 +429,7 @@ GLMB_API int glmb_skinny_bf16_swiglu(const void* x, int64_t xs, int rows, const 
     const int ks = pick_ksplit(N, K);
     const int grid = ceil_div(N, SK_WARPS / ks);
 #define CALL(RR)                                                                                                          \
-    skinny_bf16_swiglu_kernel<RR><<<grid, SK_THREADS, 0, (cudaStream_t)stream>>>((const bf16*)x, xs, rows, (const bf16*)wg, \
+    GLMB_LAUNCH(skinny_bf16_swiglu_kernel<RR>, grid, SK_THREADS, 0, (cudaStream_t)stream, (const bf16*)x, xs, rows, (const bf16*)wg, \
                                                                                  (const bf16*)wu, ws, N, K, (bf16*)act, as, ks)
     DISPATCH_R(rows, CALL);
 #undef CALL
@@ -438,11 +443,11 @@ GLMB_API int glmb_moe_gateup_fp8(const void* x, int64_t xs, int top_k, const int
     if ((H & 15) || tiles < 1) return 1;
     dim3 grid(ceil_div(I, SK_WARPS), tiles);
     if (rt == 1)
-        moe_gateup_fp8_kernel<1><<<grid, SK_THREADS, 0, (cudaStream_t)stream>>>(
+        GLMB_LAUNCH(moe_gateup_fp8_kernel<1>, grid, SK_THREADS, 0, (cudaStream_t)stream, 
             (const bf16*)x, xs, top_k, tile_expert, tile_routes, n_tiles, (const uint8_t*)wg, (const uint8_t*)wu, sg, su,
             expert_base, experts_local, I, H, (bf16*)act);
     else if (rt == 8)
-        moe_gateup_fp8_kernel<8><<<grid, SK_THREADS, 0, (cudaStream_t)stream>>>(
+        GLMB_LAUNCH(moe_gateup_fp8_kernel<8>, grid, SK_THREADS, 0, (cudaStream_t)stream, 
             (const bf16*)x, xs, top_k, tile_expert, tile_routes, n_tiles, (const uint8_t*)wg, (const uint8_t*)wu, sg, su,
             expert_base, experts_local, I, H, (bf16*)act);
     else
@@ -456,11 +461,11 @@ GLMB_API int glmb_moe_down_fp8(const void* act, const float* route_weight, const
     if ((I & 15) || tiles < 1) return 1;
     dim3 grid(ceil_div(H, SK_WARPS * 2), tiles);
     if (rt == 1)
-        moe_down_fp8_kernel<1><<<grid, SK_THREADS, 0, (cudaStream_t)stream>>>((const bf16*)act, route_weight, tile_expert, tile_routes,
+        GLMB_LAUNCH(moe_down_fp8_kernel<1>, grid, SK_THREADS, 0, (cudaStream_t)stream, (const bf16*)act, route_weight, tile_expert, tile_routes,
                                                                              n_tiles, (const uint8_t*)wd, sd, expert_base,
                                                                              experts_local, I, H, (bf16*)dw);
     else if (rt == 8)
-        moe_down_fp8_kernel<8><<<grid, SK_THREADS, 0, (cudaStream_t)stream>>>((const bf16*)act, route_weight, tile_expert, tile_routes,
+        GLMB_LAUNCH(moe_down_fp8_kernel<8>, grid, SK_THREADS, 0, (cudaStream_t)stream, (const bf16*)act, route_weight, tile_expert, tile_routes,
                                                                              n_tiles, (const uint8_t*)wd, sd, expert_base,
                                                                              experts_local, I, H, (bf16*)dw);
     else
@@ -477,7 +482,7 @@ GLMB_API int glmb_moe_combine(const void* dw, const int* topk_ids, const float* 
     dim3 grid(ceil_div(H, CB_COLS), ceil_div(rows, GLMB_MAX_ROWS));
     PeerComm c = comm ? *comm : single_comm();
     if (c.world > 1 && !routed_partial && (int)(grid.x * grid.y) > GLMB_AR_MAX_CTAS) return 2;
-    moe_combine_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>((const bf16*)dw, topk_ids, shared_partial, rows, top_k, H, expert_base,
+    GLMB_LAUNCH(moe_combine_kernel, grid, 128, 0, (cudaStream_t)stream, (const bf16*)dw, topk_ids, shared_partial, rows, top_k, H, expert_base,
                                                                experts_local, scale, plain, (bf16*)out, routed_partial, c, channel);
     return (int)cudaGetLastError();
 }

@@ -23,6 +23,7 @@ indexer_score_kernel(const float* __restrict__ q_idx, const float* __restrict__ 
                      const int* __restrict__ row_pos, const int* __restrict__ row_lane, int IH, int index_slot, int full_layers,
                      int local_cap, int stripe, int world, int rank, int capacity, int64_t score_stride, float scale,
                      float* __restrict__ scores, int64_t scores_offset, PeerComm comm, int sig, uint32_t* status) {
+    GLMB_PDL_PROLOGUE();
     extern __shared__ float sq[];  // IH * D query, then IH weights
     float* sw = sq + IH * D;
     const int r = blockIdx.y;
@@ -104,6 +105,7 @@ __global__ void __launch_bounds__(TK_THREADS)
 topk_select_kernel(const float* __restrict__ scores, const int* __restrict__ row_pos, int capacity, int64_t score_stride, int top_k, int stripe,
                    int world, int rank, int* __restrict__ sel_global, int* __restrict__ sel_local, int* __restrict__ sel_counts,
                    PeerComm comm, int sig) {
+    GLMB_PDL_PROLOGUE();
     __shared__ uint32_t hist[256];
     __shared__ uint32_t warp_totals[33];
     __shared__ uint32_t s_bucket, s_need;
@@ -218,7 +220,7 @@ GLMB_API int glmb_indexer_score(const float* q_idx, const float* head_w, const v
     const size_t smem = (size_t)(IH * D + IH) * sizeof(float);
     cudaStream_t st = (cudaStream_t)stream;
 #define CALL(DD)                                                                                                          \
-    indexer_score_kernel<DD><<<grid, 256, smem, st>>>(q_idx, head_w, (const bf16*)index_cache, row_pos, row_lane, IH, index_slot, \
+    GLMB_LAUNCH(indexer_score_kernel<DD>, grid, 256, smem, st, q_idx, head_w, (const bf16*)index_cache, row_pos, row_lane, IH, index_slot, \
                                                       full_layers, local_cap, stripe, world, rank, capacity, score_stride, scale, scores,  \
                                                       scores_offset, c, sig, status)
     if (D == 128) { CALL(128); } else if (D == 64) { CALL(64); } else if (D == 32) { CALL(32); } else return 1;
@@ -233,7 +235,7 @@ GLMB_API int glmb_topk_select(const float* scores, const int* row_pos, int rows,
     if (top_k > 65535) return 1;
     PeerComm c;
     if (comm) c = *comm; else { memset(&c, 0, sizeof(c)); c.world = 1; }
-    topk_select_kernel<<<rows, TK_THREADS, 0, (cudaStream_t)stream>>>(scores, row_pos, capacity, score_stride, top_k, stripe, world, rank,
+    GLMB_LAUNCH(topk_select_kernel, rows, TK_THREADS, 0, (cudaStream_t)stream, scores, row_pos, capacity, score_stride, top_k, stripe, world, rank,
                                                                       sel_global, sel_local, sel_counts, c, sig);
     return (int)cudaGetLastError();
 }

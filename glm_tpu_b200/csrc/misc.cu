@@ -16,6 +16,7 @@
 __global__ void __launch_bounds__(128)
 router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int rows, int E, int top_k,
                    int* __restrict__ ids, float* __restrict__ weights) {
+    GLMB_PDL_PROLOGUE();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = blockIdx.x * (blockDim.x >> 5) + warp;
     if (r >= rows) return;
@@ -56,6 +57,7 @@ router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ b
 __global__ void __launch_bounds__(128)
 router_topk256_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int rows, int E, int top_k,
                       int* __restrict__ ids, float* __restrict__ weights) {
+    GLMB_PDL_PROLOGUE();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = blockIdx.x * (blockDim.x >> 5) + warp;
     if (r >= rows) return;
@@ -107,6 +109,7 @@ router_topk256_kernel(const float* __restrict__ logits, const float* __restrict_
 __global__ void __launch_bounds__(1024)
 argmax_rows_kernel(const bf16* __restrict__ logits, int64_t stride, int V, int vocab_base, float* __restrict__ cand,
                    int64_t cand_offset, PeerComm comm, int sig, uint32_t* status) {
+    GLMB_PDL_PROLOGUE();
     __shared__ float s_val[32];
     __shared__ int s_idx[32];
     const int r = blockIdx.x, rows = gridDim.x;
@@ -163,6 +166,7 @@ __global__ void step_finalize_kernel(unsigned long long* __restrict__ cand, int6
                                      const int* __restrict__ row_active, int* __restrict__ tokens, int* __restrict__ positions,
                                      int* __restrict__ out_tokens, int* __restrict__ step_counter, int ring, int advance,
                                      PeerComm comm, int sig) {
+    GLMB_PDL_PROLOGUE();
     const int r = threadIdx.x;
     if (local_best) {
         if (r < rows) {
@@ -199,6 +203,7 @@ __global__ void step_finalize_kernel(unsigned long long* __restrict__ cand, int6
 // ---------------------------------------------------------------------------------------------------
 __global__ void fp8_to_bf16_kernel(const uint8_t* __restrict__ bits, const float* __restrict__ scale, int64_t N, int64_t K,
                                    int bn, int bk, bf16* __restrict__ out, uint32_t* status) {
+    GLMB_PDL_PROLOGUE();
     const int64_t total = N * K;
     const int64_t kb = (K + bk - 1) / bk;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
@@ -223,16 +228,19 @@ __device__ __forceinline__ float approx_normal(uint32_t h) {
 
 // e4m3 codes whose decoded values are ~N(0, 112^2) clipped to +-448 (4 sigma fills the e4m3 range).
 __global__ void fill_random_fp8_kernel(uint8_t* __restrict__ out, int64_t n, uint64_t seed) {
+    GLMB_PDL_PROLOGUE();
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
         const float z = approx_normal(mix32(seed * 0x9e3779b97f4a7c15ULL + (uint64_t)i));
         out[i] = (uint8_t)__nv_cvt_float_to_fp8(z * 112.0f, __NV_SATFINITE, __NV_E4M3);
     }
 }
 __global__ void fill_random_bf16_kernel(bf16* __restrict__ out, int64_t n, uint64_t seed, float mean, float std) {
+    GLMB_PDL_PROLOGUE();
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
         out[i] = __float2bfloat16_rn(mean + std * approx_normal(mix32(seed * 0x9e3779b97f4a7c15ULL + (uint64_t)i)));
 }
 __global__ void fill_uniform_f32_kernel(float* __restrict__ out, int64_t n, uint64_t seed, float lo, float hi) {
+    GLMB_PDL_PROLOGUE();
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
         out[i] = lo + (hi - lo) * ((float)mix32(seed * 0x9e3779b97f4a7c15ULL + (uint64_t)i) * (1.0f / 4294967296.0f));
 }
@@ -242,9 +250,9 @@ GLMB_API int glmb_router_topk(const float* logits, const float* bias, int rows, 
                               void* stream) {
     if (E > 1024 || top_k > 32 || top_k > E) return 1;
     if (E <= 256)
-        router_topk256_kernel<<<ceil_div(rows, 4), 128, 0, (cudaStream_t)stream>>>(logits, bias, rows, E, top_k, ids, weights);
+        GLMB_LAUNCH(router_topk256_kernel, ceil_div(rows, 4), 128, 0, (cudaStream_t)stream, logits, bias, rows, E, top_k, ids, weights);
     else
-        router_topk_kernel<<<ceil_div(rows, 4), 128, 0, (cudaStream_t)stream>>>(logits, bias, rows, E, top_k, ids, weights);
+        GLMB_LAUNCH(router_topk_kernel, ceil_div(rows, 4), 128, 0, (cudaStream_t)stream, logits, bias, rows, E, top_k, ids, weights);
     return (int)cudaGetLastError();
 }
 
@@ -252,7 +260,7 @@ GLMB_API int glmb_argmax_rows(const void* logits, int64_t stride, int rows, int 
                               const PeerComm* comm, int sig, uint32_t* status, void* stream) {
     PeerComm c;
     if (comm) c = *comm; else { memset(&c, 0, sizeof(c)); c.world = 1; }
-    argmax_rows_kernel<<<rows, 1024, 0, (cudaStream_t)stream>>>((const bf16*)logits, stride, V, vocab_base, cand, cand_offset, c, sig,
+    GLMB_LAUNCH(argmax_rows_kernel, rows, 1024, 0, (cudaStream_t)stream, (const bf16*)logits, stride, V, vocab_base, cand, cand_offset, c, sig,
                                                                 status);
     return (int)cudaGetLastError();
 }
@@ -263,7 +271,7 @@ GLMB_API int glmb_step_finalize(void* cand, int64_t cand_offset, void* local_bes
     if (rows > 32 || n_sets < 1 || ring < 1) return 1;
     PeerComm c;
     if (comm) c = *comm; else { memset(&c, 0, sizeof(c)); c.world = 1; }
-    step_finalize_kernel<<<1, 32, 0, (cudaStream_t)stream>>>((unsigned long long*)cand, cand_offset, (unsigned long long*)local_best,
+    GLMB_LAUNCH(step_finalize_kernel, 1, 32, 0, (cudaStream_t)stream, (unsigned long long*)cand, cand_offset, (unsigned long long*)local_best,
                                                              n_sets, rows, row_active, tokens, positions, out_tokens, step_counter,
                                                              ring, advance, c, sig);
     return (int)cudaGetLastError();
@@ -273,19 +281,19 @@ GLMB_API int glmb_fp8_to_bf16(const void* bits, const float* scale, int64_t N, i
                               uint32_t* status, void* stream) {
     const int64_t total = N * K;
     const int grid = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
-    fp8_to_bf16_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const uint8_t*)bits, scale, N, K, bn, bk, (bf16*)out, status);
+    GLMB_LAUNCH(fp8_to_bf16_kernel, grid, 256, 0, (cudaStream_t)stream, (const uint8_t*)bits, scale, N, K, bn, bk, (bf16*)out, status);
     return (int)cudaGetLastError();
 }
 
 GLMB_API int glmb_fill_random_fp8(void* out, int64_t n, uint64_t seed, void* stream) {
-    fill_random_fp8_kernel<<<148 * 8, 256, 0, (cudaStream_t)stream>>>((uint8_t*)out, n, seed);
+    GLMB_LAUNCH(fill_random_fp8_kernel, 148 * 8, 256, 0, (cudaStream_t)stream, (uint8_t*)out, n, seed);
     return (int)cudaGetLastError();
 }
 GLMB_API int glmb_fill_random_bf16(void* out, int64_t n, uint64_t seed, float mean, float std, void* stream) {
-    fill_random_bf16_kernel<<<148 * 8, 256, 0, (cudaStream_t)stream>>>((bf16*)out, n, seed, mean, std);
+    GLMB_LAUNCH(fill_random_bf16_kernel, 148 * 8, 256, 0, (cudaStream_t)stream, (bf16*)out, n, seed, mean, std);
     return (int)cudaGetLastError();
 }
 GLMB_API int glmb_fill_uniform_f32(float* out, int64_t n, uint64_t seed, float lo, float hi, void* stream) {
-    fill_uniform_f32_kernel<<<148 * 8, 256, 0, (cudaStream_t)stream>>>(out, n, seed, lo, hi);
+    GLMB_LAUNCH(fill_uniform_f32_kernel, 148 * 8, 256, 0, (cudaStream_t)stream, out, n, seed, lo, hi);
     return (int)cudaGetLastError();
 }

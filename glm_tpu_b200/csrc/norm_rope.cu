@@ -33,6 +33,7 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 // ---------------------------------------------------------------------------------------------------
 __global__ void embed_rows_kernel(const int* __restrict__ tokens, const bf16* __restrict__ table, int vocab, int H,
                                   bf16* __restrict__ residual, uint32_t* status) {
+    GLMB_PDL_PROLOGUE();
     const int r = blockIdx.x;
     int t = tokens[r];
     if (t < 0 || t >= vocab) {
@@ -55,6 +56,7 @@ __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
 __global__ void __launch_bounds__(256)
 add_rmsnorm_kernel(const bf16* __restrict__ update, bf16* __restrict__ residual, const bf16* __restrict__ weight,
                    bf16* __restrict__ out, int H, float eps) {
+    GLMB_PDL_PROLOGUE();
     __shared__ float scratch[40];
     const int64_t base = (int64_t)blockIdx.x * H;
     const int nvec = H >> 3;
@@ -134,6 +136,7 @@ struct QkvPostArgs {
 };
 
 __global__ void __launch_bounds__(256) qkv_a_post_kernel(QkvPostArgs a) {
+    GLMB_PDL_PROLOGUE();
     __shared__ float scratch[40];
     __shared__ float s_key[256];
     const int r = blockIdx.x;
@@ -240,6 +243,7 @@ struct QPostArgs {
 };
 
 __global__ void __launch_bounds__(256) q_post_kernel(QPostArgs a) {
+    GLMB_PDL_PROLOGUE();
     const int r = blockIdx.x;
     const float* q = a.q + (int64_t)r * a.q_stride;
     const int pos = min(max(a.row_pos[r], 0), a.capacity - 1);
@@ -288,6 +292,7 @@ __global__ void __launch_bounds__(256)
 q_absorb_kernel(const bf16* __restrict__ q_nope, int rows, const bf16* __restrict__ kv_b, int heads_local, int head_base,
                 int heads_total, int nope, int vdim, int L, int rd, bf16* __restrict__ q_full, int64_t q_full_offset,
                 PeerComm comm, int sig) {
+    GLMB_PDL_PROLOGUE();
     __shared__ float red[8][R][QA_COLS];
     const int h = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int c0 = blockIdx.y * QA_COLS + lane * 4;
@@ -345,21 +350,21 @@ q_absorb_kernel(const bf16* __restrict__ q_nope, int rows, const bf16* __restric
 GLMB_API int glmb_embed_rows(const int* tokens, const void* table, int rows, int vocab, int H, void* residual, uint32_t* status,
                              void* stream) {
     if (H & 7) return 1;
-    embed_rows_kernel<<<rows, 256, 0, (cudaStream_t)stream>>>(tokens, (const bf16*)table, vocab, H, (bf16*)residual, status);
+    GLMB_LAUNCH(embed_rows_kernel, rows, 256, 0, (cudaStream_t)stream, tokens, (const bf16*)table, vocab, H, (bf16*)residual, status);
     return (int)cudaGetLastError();
 }
 
 GLMB_API int glmb_add_rmsnorm(const void* update, void* residual, const void* weight, void* out, int rows, int H, float eps,
                               void* stream) {
     if ((H & 7) || H > 256 * 8 * RN_VECS) return 1;
-    add_rmsnorm_kernel<<<rows, 256, 0, (cudaStream_t)stream>>>((const bf16*)update, (bf16*)residual, (const bf16*)weight,
+    GLMB_LAUNCH(add_rmsnorm_kernel, rows, 256, 0, (cudaStream_t)stream, (const bf16*)update, (bf16*)residual, (const bf16*)weight,
                                                                   (bf16*)out, H, eps);
     return (int)cudaGetLastError();
 }
 
 GLMB_API int glmb_qkv_a_post(const QkvPostArgs* args, int rows, void* stream) {
     if (args->D > 256 || (args->rd & 1) || (args->Q & 3) || (args->L & 3) || (args->proj_stride & 3)) return 1;
-    qkv_a_post_kernel<<<rows, 256, 0, (cudaStream_t)stream>>>(*args);
+    GLMB_LAUNCH(qkv_a_post_kernel, rows, 256, 0, (cudaStream_t)stream, *args);
     return (int)cudaGetLastError();
 }
 
@@ -367,7 +372,7 @@ GLMB_API int glmb_q_post(const QPostArgs* args, int rows, void* stream) {
     if ((args->nope & 1) || (args->q_stride & 1)) return 1;
     const int work = args->heads_local * (args->nope / 2 + args->rd / 2) + (args->has_indexer ? args->IH * args->D : 0);
     dim3 grid(rows, rows <= 16 ? max(1, min(32, ceil_div(work, 512))) : 1);
-    q_post_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(*args);
+    GLMB_LAUNCH(q_post_kernel, grid, 256, 0, (cudaStream_t)stream, *args);
     return (int)cudaGetLastError();
 }
 
@@ -380,7 +385,7 @@ GLMB_API int glmb_q_absorb(const void* q_nope, int rows, const void* kv_b, int h
     if (comm) c = *comm; else { memset(&c, 0, sizeof(c)); c.world = 1; }
     dim3 grid(heads_local, ceil_div(L, QA_COLS));
 #define CALL(RR)                                                                                                              \
-    q_absorb_kernel<RR><<<grid, 256, 0, (cudaStream_t)stream>>>((const bf16*)q_nope, rows, (const bf16*)kv_b, heads_local, head_base, \
+    GLMB_LAUNCH(q_absorb_kernel<RR>, grid, 256, 0, (cudaStream_t)stream, (const bf16*)q_nope, rows, (const bf16*)kv_b, heads_local, head_base, \
                                                                 heads_total, nope, vdim, L, rd, (bf16*)q_full, q_full_offset, c, sig)
     if (rows <= 1) { CALL(1); } else if (rows <= 2) { CALL(2); } else if (rows <= 4) { CALL(4); } else { CALL(8); }
 #undef CALL

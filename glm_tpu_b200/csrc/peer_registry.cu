@@ -123,6 +123,7 @@ GLMB_API int glmb_peer_destroy(PeerRegistry* r) {
 // Self-test kernels for the wait primitive: a wait on a flag that nothing sets must give up after the
 // iteration limit, set the status word and return (the context stays usable).
 __global__ void wait_probe_kernel(PeerComm c, int sig, uint32_t bump) {
+    GLMB_PDL_PROLOGUE();
     if (threadIdx.x == 0 && bump) c.seq[GLMB_SEQ_SIG_BASE + sig] += bump;  // expect a round nobody signalled
     __syncthreads();
     // force the wait path even with one rank
@@ -139,12 +140,13 @@ __global__ void wait_probe_kernel(PeerComm c, int sig, uint32_t bump) {
 }
 
 GLMB_API int glmb_peer_wait_probe(const PeerComm* comm, int sig, uint32_t bump, void* stream) {
-    wait_probe_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(*comm, sig, bump);
+    GLMB_LAUNCH(wait_probe_kernel, 1, 32, 0, (cudaStream_t)stream, *comm, sig, bump);
     return (int)cudaGetLastError();
 }
 
 // All-reduce self-test: every rank contributes `count` floats; result (identical on all ranks) in `out`.
 __global__ void allreduce_probe_kernel(const float* in, float* out, int count, PeerComm c, int channel) {
+    GLMB_PDL_PROLOGUE();
     __shared__ float sh[GLMB_AR_SLICE];
     const int base = blockIdx.x * GLMB_AR_SLICE;
     const int n = min(GLMB_AR_SLICE, count - base);
@@ -157,6 +159,12 @@ __global__ void allreduce_probe_kernel(const float* in, float* out, int count, P
 GLMB_API int glmb_peer_allreduce_probe(const float* in, float* out, int count, const PeerComm* comm, int channel, void* stream) {
     const int grid = ceil_div(count, GLMB_AR_SLICE);
     if (grid > GLMB_AR_MAX_CTAS) return 1;
-    allreduce_probe_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(in, out, count, *comm, channel);
+    GLMB_LAUNCH(allreduce_probe_kernel, grid, 128, 0, (cudaStream_t)stream, in, out, count, *comm, channel);
     return (int)cudaGetLastError();
 }
+
+// ---------------------------------------------------------------------------------------------------
+// Library-wide launch mode (see GLMB_PDL_PROLOGUE in common.cuh).
+int g_glmb_pdl_enabled = 1;
+GLMB_API void glmb_set_pdl(int enabled) { g_glmb_pdl_enabled = enabled ? 1 : 0; }
+GLMB_API int glmb_get_pdl(void) { return g_glmb_pdl_enabled; }

@@ -84,6 +84,10 @@ def lib() -> C.CDLL:
         _lib.glmb_peer_status_ptr.restype = C.c_void_p
         if _lib.glmb_peer_comm_sizeof() != C.sizeof(PeerComm):
             raise RuntimeError("PeerComm layout differs between Python and the CUDA library")
+        import os
+
+        if os.environ.get("GLM_B200_PDL", "1") == "0":  # programmatic dependent launch off: plain stream order
+            _lib.glmb_set_pdl(0)
     return _lib
 
 
