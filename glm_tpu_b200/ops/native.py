@@ -297,3 +297,22 @@ def fill_random_bf16(out, seed, mean=0.0, std=0.02):
 def fill_uniform_f32(out, seed, lo, hi):
     _check(lib().glmb_fill_uniform_f32(_p(out), C.c_int64(out.numel()), C.c_uint64(seed), f32(lo), f32(hi), _stream()),
            "fill_uniform_f32")
+
+
+# ----------------------------------------------------------------------------- tcgen05 GEMM
+def gemm_bf16_tc(a, b, out, *, experts=1, tiles=None, n_tiles=None, status=None):
+    """``out[rows, N] = a[rows, K] @ b[N, K].T`` on the tcgen05 tensor cores (bf16 in, fp32 accumulate).
+
+    ``b`` may be ``[experts, N, K]`` with ``tiles`` (``[max_tiles, 4]`` int32: first row, end row, expert, 0) and
+    ``n_tiles`` (device int32) describing 128-row tiles of the expert-sorted ``a``: grouped mode.
+    ``out`` is bf16 or fp32.
+    """
+    rows, K = a.shape
+    N = b.shape[-2]
+    out_f32 = int(out.dtype == torch.float32)
+    max_tiles = tiles.shape[0] if tiles is not None else 0
+    _check(
+        lib().glmb_gemm_bf16_tcgen05(_p(a), C.c_int64(a.stride(0)), _p(b), C.c_int64(b.stride(-2)), _p(out), C.c_int64(out.stride(0)),
+                                     rows, N, K, experts, _p(tiles), _p(n_tiles), max_tiles, out_f32, _p(status), _stream()),
+        "gemm_bf16_tcgen05",
+    )
