@@ -176,13 +176,26 @@ class GlmMoeDsaModel:
             dist.all_reduce(partial_f32, group=self.group)
         return partial_f32
 
+    def _mm(self, x: torch.Tensor, w: torch.Tensor, f32: bool = False) -> torch.Tensor:
+        """``x @ w.T`` (bf16 operands, fp32 accumulate) for many rows: the tcgen05 GEMM; shapes it does not take
+        (a dimension that is not a multiple of 8) go to the library GEMM."""
+        rows, K = x.shape
+        N = w.shape[0]
+        dtype = torch.float32 if f32 else torch.bfloat16
+        if K % 8 == 0 and N % 8 == 0 and x.stride(1) == 1 and w.stride(1) == 1 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 \
+                and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0:
+            out = torch.empty((rows, N), dtype=dtype, device=x.device)
+            native.gemm_bf16_tc(x, w, out, status=self.peer.status_ptr)
+            return out
+        return torch.mm(x, w.t(), out_dtype=torch.float32) if f32 else torch.mm(x, w.t())
+
     def _linear_f32(self, x, w, out, decode: bool):
         """``out[:, :N] = x @ w.T`` in fp32."""
         n = w.shape[0]
         if decode:
             native.skinny_bf16(x, w, out, native.SK_OUT_F32, N=n, K=w.shape[1])
         else:
-            out[: x.shape[0], :n] = torch.mm(x, w.t(), out_dtype=torch.float32)
+            out[: x.shape[0], :n] = self._mm(x, w, f32=True)
 
     # ------------------------------------------------------------------------------ attention
     def _attention(self, ws: Workspace, lw: LayerWeights, layer: int, rows: int, row_pos, row_lane, row_active, state: DecoderState,
@@ -282,9 +295,9 @@ class GlmMoeDsaModel:
             w_v = lw.kv_b[:, g.qk_nope_head_dim :, :]  # [hl, v, L]
             v = torch.einsum("rhc,hvc->rhv", ws.o_lat[:rows], w_v).reshape(rows, hl * g.v_head_dim)
             if self.world == 1:
-                ws.attn_out[:rows] = torch.mm(v, lw.w_o.t())
+                ws.attn_out[:rows] = self._mm(v, lw.w_o)
             else:
-                part = torch.mm(v, lw.w_o.t(), out_dtype=torch.float32)
+                part = self._mm(v, lw.w_o, f32=True)
                 ws.attn_out[:rows] = self._allreduce_rows(part).to(torch.bfloat16)
         if self.trace is not None:
             self.trace.setdefault("attn_out", {})[layer] = ws.attn_out[:rows].clone()
@@ -355,12 +368,12 @@ class GlmMoeDsaModel:
                     native.skinny_bf16(ws.dense_act[:rows], lw.dense_down, ws.partial, native.SK_OUT_F32)
                     ws.update[:rows] = self._allreduce_rows(ws.partial[:rows]).to(torch.bfloat16)
             else:
-                gate, up = torch.mm(x, lw.dense_gate.t()).float(), torch.mm(x, lw.dense_up.t()).float()
+                gate, up = self._mm(x, lw.dense_gate).float(), self._mm(x, lw.dense_up).float()
                 act = (gate * torch.sigmoid(gate) * up).to(torch.bfloat16)
                 if self.world == 1:
-                    ws.update[:rows] = torch.mm(act, lw.dense_down.t())
+                    ws.update[:rows] = self._mm(act, lw.dense_down)
                 else:
-                    ws.update[:rows] = self._allreduce_rows(torch.mm(act, lw.dense_down.t(), out_dtype=torch.float32)).to(torch.bfloat16)
+                    ws.update[:rows] = self._allreduce_rows(self._mm(act, lw.dense_down, f32=True)).to(torch.bfloat16)
             return
         tk, I, E = g.routed_top_k, g.moe_intermediate_size, g.num_routed_experts
         el, ebase = lay.experts_local, self.rank * lay.experts_local
@@ -382,9 +395,9 @@ class GlmMoeDsaModel:
             native.skinny_bf16(ws.act_shared[:rows], lw.shared_down, ws.partial, native.SK_OUT_F32)
             shared_partial = ws.partial
         else:
-            gate, up = torch.mm(x, lw.shared_gate.t()).float(), torch.mm(x, lw.shared_up.t()).float()
+            gate, up = self._mm(x, lw.shared_gate).float(), self._mm(x, lw.shared_up).float()
             act = (gate * torch.sigmoid(gate) * up).to(torch.bfloat16)
-            shared_partial = torch.mm(act, lw.shared_down.t(), out_dtype=torch.float32)
+            shared_partial = self._mm(act, lw.shared_down, f32=True)
         if fused or self.world == 1:
             native.moe_combine(ws.dw, ws.topk_ids, shared_partial, rows, tk, H, ebase, el, g.routed_scaling_factor, False, ws.update,
                                None, kc, native.CH_MLP)
@@ -449,7 +462,7 @@ class GlmMoeDsaModel:
         if n <= native.MAX_ROWS:
             native.skinny_bf16(xh, self.w.lm_head, ws.logits, native.SK_OUT_BF16)
         else:
-            ws.logits[:n] = torch.mm(xh, self.w.lm_head.t())
+            ws.logits[:n] = self._mm(xh, self.w.lm_head)
         return ws.logits[:n]
 
     def sample(self, ws: Workspace, state: DecoderState, logits: torch.Tensor, rows: int, row_active, *, advance: int,
