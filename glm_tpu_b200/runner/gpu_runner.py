@@ -107,6 +107,7 @@ class GpuModelRunner:
         self.report.phases["allocate"] = time.perf_counter() - t0
         self.report.memory = project_memory(self.g, self.layout, self.cache, weights.bytes_resident, staging_bytes)
         self.decode_launches = 0
+        self.steps_issued = 0
 
     # ------------------------------------------------------------------ decode program
     def _decode_body(self) -> None:
@@ -134,6 +135,7 @@ class GpuModelRunner:
                 kind = "cuda_graph"
             self.state.active.copy_(saved)
             self.state.step_counter.zero_()
+            self.steps_issued = 0
             torch.cuda.synchronize(self.device)
             self.peer.check_status()
         rec = ProgramRecord("decode", kind, self.lanes, self.decode_launches, time.perf_counter() - t0)
@@ -142,10 +144,21 @@ class GpuModelRunner:
 
     def decode_step(self) -> None:
         """Enqueue one decode step for every active lane (asynchronous)."""
+        if self._graph is None and not self.report.programs:
+            self.build_decode_program()
         if self._graph is not None:
             self._graph.replay()
         else:
             self._decode_body()
+        self.steps_issued += 1
+
+    def read_last_tokens(self) -> list[int]:
+        """Tokens of the most recent decode step, one per lane (-1 for a frozen lane).  Synchronizes."""
+        return self.read_step_tokens(self.steps_issued - 1)
+
+    def read_status(self) -> int:
+        """The device status word (0 = clean); reading clears it."""
+        return self.peer.read_status()
 
     def read_step_tokens(self, step_index: int) -> list[int]:
         """Tokens produced by decode step ``step_index`` (synchronizes; one small D2H copy)."""
