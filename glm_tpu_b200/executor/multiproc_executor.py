@@ -1,0 +1,169 @@
+"""The controller: stages a run, starts one worker per GPU, supervises them, serves a resident session and collects.
+
+    python -m glm_tpu_b200.executor.multiproc_executor --request prepared.json --gpus 8 --model random:glm53 \
+        [--keep-loaded] [--wall-seconds N] [--print-answers]
+
+One-shot: stage the request, start the workers, wait for them (exit codes + wall deadline), summarize.  Resident
+(``--keep-loaded``): after the first request the workers stay loaded; the controller polls the run directory --
+``resident-ready.json`` says which sequence is done, ``inbox/NNNN.json`` is the next request (validated, then written
+as one line to every worker's stdin), ``inbox/stop.json`` ends the session.  A run is good only if every rank's record
+agrees on the request, the token digests and the program kinds.
+
+There are no retries: a failed worker ends the run, the remaining workers are terminated (only process groups this
+controller started), and ``controller_terminal.json`` records what happened.
+
+Parity: reference ``glm_tpu/executor/multihost_executor.py:77-504`` (main, resident_controller, supervision, summarize).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+import time
+from pathlib import Path
+
+from glm_tpu_b200.engine import request as request_schema
+from glm_tpu_b200.engine import resident_protocol as proto
+from glm_tpu_b200.executor import fleet as fleet_mod
+from glm_tpu_b200.executor import jobs, staging
+from glm_tpu_b200.utils.io_utils import persist_json, read_bounded
+
+REPO = Path(__file__).resolve().parents[2]
+
+
+def parse_args(argv=None):
+    ap = argparse.ArgumentParser(prog="glm_tpu_b200.executor.multiproc_executor")
+    ap.add_argument("--request", help="prepared request or batch (JSON file)")
+    ap.add_argument("--run-root", default=None)
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--model", default="random:tiny")
+    ap.add_argument("--backend", default="gpu", choices=["gpu", "oracle"])
+    ap.add_argument("--context", type=int, default=0)
+    ap.add_argument("--lanes", type=int, default=1)
+    ap.add_argument("--comm", default="fused")
+    ap.add_argument("--kv-layout", default="auto")
+    ap.add_argument("--keep-loaded", action="store_true")
+    ap.add_argument("--wall-seconds", type=float, default=3600.0)
+    ap.add_argument("--print-answers", action="store_true")
+    ap.add_argument("--policy", default="record", choices=["record", "strict"])
+    ap.add_argument("--master-port", type=int, default=29577)
+    ap.add_argument("--poll-seconds", type=float, default=0.5)
+    return ap.parse_args(argv)
+
+
+def default_run_root() -> Path:
+    from glm_tpu_b200 import envs
+
+    return envs.GLM_B200_RUN_ROOT or Path.home() / ".cache" / "glm-b200" / "runs"
+
+
+def summarize(run_dir: Path, world: int, sequence: int = 0) -> dict:
+    """Do all ranks agree?  Same requests, same token digests, same program kinds."""
+    out_dir = proto.result_dir(run_dir, sequence)
+    records, missing = [], []
+    for rank in range(world):
+        path = out_dir / proto.runner_file(rank)
+        if not path.exists():
+            path = run_dir / proto.runner_file(rank)
+        if path.exists():
+            records.append(json.loads(path.read_text()))
+        else:
+            missing.append(rank)
+    digests = [[(r["request_id"], r["token_sha256"]) for r in rec.get("requests", [])] for rec in records]
+    programs = [[(p["name"], p["kind"]) for p in rec.get("programs", [])] for rec in records]
+    agree = not missing and bool(records) and all(d == digests[0] for d in digests) and all(p == programs[0] for p in programs)
+    failures = [rec.get("failure_type") for rec in records if rec.get("failure_type")]
+    reports = records[0].get("requests", []) if records else []
+    return {
+        "ranks": len(records),
+        "missing_ranks": missing,
+        "agree": bool(agree and not failures),
+        "failures": failures,
+        "requests": [
+            {"request_id": r["request_id"], "emitted": r["emitted"], "finish_reason": r["finish_reason"],
+             "decode_tokens_per_second": min((rec["requests"][i]["decode_tokens_per_second"] or 0.0) for rec in records) or None,
+             "prefill_seconds": max(rec["requests"][i]["prefill_seconds"] for rec in records), "token_sha256": r["token_sha256"]}
+            for i, r in enumerate(reports)
+        ] if agree else [],
+    }
+
+
+def resident_controller(fl: fleet_mod.Fleet, run_dir: Path, world: int, profile_check, deadline: float, poll: float) -> dict:
+    """Feed ``inbox/NNNN.json`` requests to the loaded workers until ``inbox/stop.json`` or a failure."""
+    inbox = run_dir / proto.INBOX_DIR
+    served, sequence = [], 0
+    while time.monotonic() < deadline:
+        codes = fl.poll()
+        if any(c is not None for c in codes):
+            return {"stopped": "worker_exit", "exit_codes": codes, "served": served}
+        ready = run_dir / proto.READY_FILE
+        ready_seq = json.loads(ready.read_text()).get("sequence", -1) if ready.exists() else -1
+        if ready_seq == sequence:
+            if sequence > 0 and sequence not in served:
+                summary = summarize(run_dir, world, sequence)
+                persist_json(proto.result_dir(run_dir, sequence) / proto.MEASUREMENT_FILE, summary)
+                print(proto.STDOUT_RESIDENT_RESULT + json.dumps({"sequence": sequence, **summary}), flush=True)
+                served.append(sequence)
+            if (inbox / proto.STOP_FILE).exists():
+                fl.send_all(proto.STOP_COMMAND)
+                return {"stopped": "stop_file", "served": served}
+            nxt = inbox / proto.inbox_name(sequence + 1)
+            if nxt.exists():
+                payload = json.loads(read_bounded(nxt, request_schema.PAYLOAD_CAP))
+                profile_check(payload)
+                sequence += 1
+                fl.send_all(proto.encode_command(sequence, payload))
+                continue
+        time.sleep(poll)
+    fl.send_all(proto.STOP_COMMAND)
+    return {"stopped": "deadline", "served": served}
+
+
+def main(argv=None) -> int:
+    args = parse_args(argv)
+    run_root = Path(args.run_root) if args.run_root else default_run_root()
+    payload = json.loads(read_bounded(Path(args.request), request_schema.PAYLOAD_CAP)) if args.request else None
+    if payload is None and not args.keep_loaded:
+        raise SystemExit("--request is required unless --keep-loaded starts a resident session")
+    with jobs.fleet_job(run_root, repo=REPO, policy=args.policy, require_idle=args.backend == "gpu") as job:
+        run_dir = staging.new_run_dir(run_root)
+        print(proto.STDOUT_RUN + str(run_dir), flush=True)
+        staged = staging.stage_request(run_dir, payload)
+        jobs.write_identity(run_dir, job, {"args": vars(args)})
+        worker_args = ["--run-dir", str(run_dir), "--model", args.model, "--backend", args.backend, "--lanes", str(args.lanes),
+                       "--comm", args.comm, "--kv-layout", args.kv_layout]
+        if args.context:
+            worker_args += ["--context", str(args.context)]
+        if staged is not None:
+            worker_args += ["--request", str(staged), "--request-sha256", payload["request_sha256"]]
+        if args.keep_loaded:
+            worker_args.append("--keep-loaded")
+        specs = fleet_mod.worker_specs(world=args.gpus, run_dir=run_dir, worker_args=worker_args, master_port=args.master_port)
+        deadline = time.monotonic() + args.wall_seconds
+        fl = job.start(specs, keep_stdin=args.keep_loaded)
+        terminal: dict = {"run_dir": str(run_dir)}
+        if args.keep_loaded:
+            def check(p):
+                pass  # the workers validate against the loaded profile; the controller only bounds and parses
+
+            terminal["resident"] = resident_controller(fl, run_dir, args.gpus, check, deadline, args.poll_seconds)
+            codes = fl.wait(time.monotonic() + 30.0)
+        else:
+            codes = fl.wait(deadline)
+        terminal["exit_codes"] = codes
+        terminal["timed_out"] = any(c is None for c in codes)
+        if any(c is None for c in codes) or any(c not in (None, 0) for c in codes):
+            terminal["cleanup_exit_codes"] = fl.cleanup()
+        summary = summarize(run_dir, args.gpus) if payload is not None else {"agree": all(c == 0 for c in codes), "requests": []}
+        persist_json(run_dir / proto.SUMMARY_FILE, summary)
+        terminal["ok"] = bool(summary["agree"]) and all(c == 0 for c in codes)
+        persist_json(run_dir / proto.CONTROLLER_TERMINAL_FILE, terminal)
+        if args.print_answers and (run_dir / proto.ANSWER_FILE).exists():
+            print((run_dir / proto.ANSWER_FILE).read_text())
+        print(json.dumps({"ok": terminal["ok"], "summary": summary}), flush=True)
+        return 0 if terminal["ok"] else 1
+
+
+if __name__ == "__main__":
+    sys.exit(main())
