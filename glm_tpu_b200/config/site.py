@@ -1,0 +1,168 @@
+"""The site file: where this installation keeps its runs, its checkpoint and its pins.
+
+``site.toml`` is read fail-closed: it must be a regular file owned by the user and closed to group and others
+(0600), every table must have exactly its known keys, paths must be absolute and plain, pins must be 64 lowercase
+hex digits, the box shape must be one the engine supports.  ``resolved_json()`` is the canonical form handed to the
+workers, ``sha256`` its digest (workers refuse a site that differs from the controller's).  Precedence everywhere:
+CLI flag > ``GLM_B200_*`` environment variable > site file > default.
+
+Tables::
+
+    [box]        gpus = 8                       # 1, 2, 4 or 8 GPUs of one NVLink/NVSwitch box
+    [paths]      run_root, model_path, packed_path, state_root
+    [checkpoint] manifest_sha256, source_marker_sha256      # optional pins ("" = unpinned)
+    [topology]   binding_sha256                              # optional pin of the captured GPU topology
+    [launch]     policy = "record" | "strict", master_port, wall_seconds
+    [serve]      port
+
+Parity: reference ``glm_tpu/config/site.py:92-684`` (7 tables, exact key sets, 0600, 64-hex pins, resolved JSON + SHA).
+"""
+
+from __future__ import annotations
+
+import hashlib
+import os
+import re
+import stat
+import tomllib
+from dataclasses import asdict, dataclass, field
+from pathlib import Path
+
+from glm_tpu_b200.exceptions import ConfigValidationError
+from glm_tpu_b200.utils.json_utils import canonical_wire_bytes
+
+_HEX64 = re.compile(r"[0-9a-f]{64}")
+_PLAIN = re.compile(r"[A-Za-z0-9_./+@:-]+")
+SUPPORTED_GPUS = (1, 2, 4, 8)
+TABLE_KEYS = {
+    "box": {"gpus"},
+    "paths": {"run_root", "model_path", "packed_path", "state_root"},
+    "checkpoint": {"manifest_sha256", "source_marker_sha256"},
+    "topology": {"binding_sha256"},
+    "launch": {"policy", "master_port", "wall_seconds"},
+    "serve": {"port"},
+}
+
+
+@dataclass(frozen=True)
+class Paths:
+    run_root: Path
+    model_path: Path | None = None
+    packed_path: Path | None = None
+    state_root: Path | None = None
+
+
+@dataclass(frozen=True)
+class SiteConfig:
+    gpus: int = 8
+    paths: Paths = field(default_factory=lambda: Paths(Path.home() / ".cache" / "glm-b200" / "runs"))
+    manifest_sha256: str = ""
+    source_marker_sha256: str = ""
+    topology_binding_sha256: str = ""
+    policy: str = "record"
+    master_port: int = 29577
+    wall_seconds: int = 86400
+    serve_port: int = 8011
+    source: str = "<defaults>"
+
+    # ------------------------------------------------------------------ loading
+    @classmethod
+    def load(cls, path: Path | None = None, *, required: bool = False) -> "SiteConfig":
+        from glm_tpu_b200 import envs
+
+        path = Path(path) if path is not None else envs.GLM_B200_SITE_CONFIG
+        if not path.exists():
+            if required:
+                raise ConfigValidationError(f"site file {path} does not exist")
+            return cls()._with_env()
+        return cls.parse(path)._with_env()
+
+    @classmethod
+    def parse(cls, path: Path) -> "SiteConfig":
+        path = Path(path)
+        info = os.lstat(path)
+        if not stat.S_ISREG(info.st_mode):
+            raise ConfigValidationError("the site file must be a regular file (not a symlink)")
+        if info.st_uid != os.geteuid() or stat.S_IMODE(info.st_mode) & 0o077:
+            raise ConfigValidationError("the site file must be owned by you with mode 0600")
+        try:
+            doc = tomllib.loads(path.read_text(encoding="utf-8"))
+        except tomllib.TOMLDecodeError as exc:
+            raise ConfigValidationError(f"the site file is not valid TOML: {exc}") from exc
+        unknown = set(doc) - set(TABLE_KEYS)
+        if unknown:
+            raise ConfigValidationError(f"unknown site tables: {sorted(unknown)}")
+        for table, keys in TABLE_KEYS.items():
+            present = doc.get(table, {})
+            if not isinstance(present, dict):
+                raise ConfigValidationError(f"[{table}] must be a table")
+            extra = set(present) - keys
+            if extra:
+                raise ConfigValidationError(f"unknown keys in [{table}]: {sorted(extra)}")
+        if "paths" not in doc or "run_root" not in doc["paths"]:
+            raise ConfigValidationError("[paths] run_root is required")
+
+        def plain(name):
+            value = doc["paths"].get(name)
+            if value in (None, ""):
+                return None
+            if type(value) is not str or not os.path.isabs(value) or not _PLAIN.fullmatch(value) or ".." in Path(value).parts:
+                raise ConfigValidationError(f"[paths] {name} must be an absolute plain path")
+            return Path(value)
+
+        def pin(table, name):
+            value = doc.get(table, {}).get(name, "")
+            if value != "" and (type(value) is not str or not _HEX64.fullmatch(value)):
+                raise ConfigValidationError(f"[{table}] {name} must be 64 lowercase hex digits or empty")
+            return value
+
+        def integer(table, name, default, lo, hi):
+            value = doc.get(table, {}).get(name, default)
+            if type(value) is not int or not lo <= value <= hi:
+                raise ConfigValidationError(f"[{table}] {name} must be an integer in [{lo}, {hi}]")
+            return value
+
+        gpus = integer("box", "gpus", 8, 1, 8)
+        if gpus not in SUPPORTED_GPUS:
+            raise ConfigValidationError(f"[box] gpus must be one of {SUPPORTED_GPUS}")
+        policy = doc.get("launch", {}).get("policy", "record")
+        if policy not in ("record", "strict"):
+            raise ConfigValidationError("[launch] policy must be 'record' or 'strict'")
+        return cls(
+            gpus=gpus,
+            paths=Paths(plain("run_root"), plain("model_path"), plain("packed_path"), plain("state_root")),
+            manifest_sha256=pin("checkpoint", "manifest_sha256"),
+            source_marker_sha256=pin("checkpoint", "source_marker_sha256"),
+            topology_binding_sha256=pin("topology", "binding_sha256"),
+            policy=policy,
+            master_port=integer("launch", "master_port", 29577, 1024, 65535),
+            wall_seconds=integer("launch", "wall_seconds", 86400, 1, 30 * 86400),
+            serve_port=integer("serve", "port", 8011, 1024, 65535),
+            source=str(path),
+        )
+
+    def _with_env(self) -> "SiteConfig":
+        from dataclasses import replace
+
+        from glm_tpu_b200 import envs
+
+        paths = self.paths
+        if envs.GLM_B200_RUN_ROOT is not None:
+            paths = replace(paths, run_root=envs.GLM_B200_RUN_ROOT)
+        if envs.GLM_B200_MODEL_PATH is not None:
+            paths = replace(paths, model_path=envs.GLM_B200_MODEL_PATH)
+        return replace(self, paths=paths)
+
+    # ------------------------------------------------------------------ canonical form
+    def resolved(self) -> dict:
+        out = asdict(self)
+        out["paths"] = {k: (str(v) if v is not None else None) for k, v in out["paths"].items()}
+        del out["source"]
+        return out
+
+    def resolved_json(self) -> bytes:
+        return canonical_wire_bytes(self.resolved())
+
+    @property
+    def sha256(self) -> str:
+        return hashlib.sha256(self.resolved_json()).hexdigest()

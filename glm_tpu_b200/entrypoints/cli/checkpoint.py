@@ -1,0 +1,39 @@
+"""``glm-b200 checkpoint inventory|mark-source|pack|verify``.
+
+Every action prints one JSON report.  ``pack`` holds the workload lease of the site's run root while it writes.
+
+Parity: reference ``glm_tpu/entrypoints/cli/checkpoint.py``.
+"""
+
+from __future__ import annotations
+
+import json
+
+
+def main(args) -> int:
+    from glm_tpu_b200.config.site import SiteConfig
+    from glm_tpu_b200.model_loader import source_inventory, source_marker
+
+    if args.action == "inventory":
+        inv = source_inventory.read_source_inventory(args.source)
+        by_dtype: dict = {}
+        for t in inv.tensors.values():
+            by_dtype[t.dtype] = by_dtype.get(t.dtype, 0) + (t.end - t.begin)
+        report = {"ok": True, "source": str(args.source), "inventory_sha256": inv.sha256, "tensors": len(inv.tensors),
+                  "shards": len(inv.shards), "total_bytes": sum(inv.shards.values()), "bytes_by_dtype": dict(sorted(by_dtype.items()))}
+    elif args.action == "mark-source":
+        marker = source_marker.mark_source(args.source)
+        report = {"ok": True, "source": str(args.source), "inventory_sha256": marker["inventory_sha256"],
+                  "tensor_count": marker["tensor_count"], "total_bytes": marker["total_bytes"]}
+    elif args.action == "pack":
+        from glm_tpu_b200.executor.pack_job import pack_checkpoint
+
+        site = SiteConfig.load(getattr(args, "site", None))
+        report = pack_checkpoint(args.source, args.target, args.gpus, run_root=site.paths.run_root, layers=args.layers)
+    else:
+        from glm_tpu_b200.model_loader.sharded_state.verify import verify_runtime_checkpoint
+
+        site = SiteConfig.load(getattr(args, "site", None))
+        report = verify_runtime_checkpoint(args.target, pins={"manifest_sha256": site.manifest_sha256})
+    print(json.dumps(report, indent=2, sort_keys=True))
+    return 0

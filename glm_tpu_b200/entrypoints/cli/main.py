@@ -1,0 +1,160 @@
+"""``glm-b200``: the command line of the engine (``python -m glm_tpu_b200``).
+
+    info                         supported scope and limits
+    ask [QUESTION | --questions FILE] [--context 8k|32k|128k|256k] [--concurrent] [--keep-loaded] ...
+    prepare-request              messages or token ids -> prepared request (nothing is launched)
+    collect-env | doctor         environment report checked against a profile
+    checkpoint inventory|mark-source|pack|verify
+    topology capture|bind
+    serve                        loopback chat UI + OpenAI-compatible /v1 attached to a resident session
+
+Subcommand modules are imported only when their command runs, so ``info`` and ``--help`` never import torch.
+
+Parity: reference ``glm_tpu/entrypoints/cli/main.py:87-146``.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+from pathlib import Path
+from typing import Sequence
+
+CONTEXTS = ("8k", "32k", "128k", "256k")
+
+
+def _info(args) -> int:
+    print(json.dumps({
+        "engine": "glm_tpu_b200",
+        "model": "GlmMoeDsaForCausalLM (GLM-5.3), FP8 e4m3 routed experts with 128x128 block scales, bf16 elsewhere",
+        "hardware": "one box of 1, 2, 4 or 8 NVIDIA B200 (sm_100a) with NVLink peer access",
+        "modes": ["one-shot answer", "sequential queue (<= 10)", "four concurrent chats (32k)", "resident session",
+                  "loopback chat UI", "OpenAI-compatible /v1 (chat completions, models, tools, SSE)"],
+        "decoding": "greedy only; sampling parameters are accepted and ignored",
+        "contexts": {"8k": 8192, "32k": 32768, "128k": 166912, "256k": 262144},
+        "recovery": "none: a failed step poisons the engine; there are no retries",
+        "not_loaded": "the checkpoint's multi-token-prediction layer",
+    }, indent=2, sort_keys=True))
+    return 0
+
+
+def _ask(args) -> int:
+    from glm_tpu_b200.entrypoints.cli.ask import main
+
+    return main(args)
+
+
+def _prepare(args) -> int:
+    from glm_tpu_b200.entrypoints.cli.prepare import main
+
+    return main(args)
+
+
+def _collect_env(args) -> int:
+    from glm_tpu_b200.entrypoints.cli.collect_env import main
+
+    return main(args)
+
+
+def _checkpoint(args) -> int:
+    from glm_tpu_b200.entrypoints.cli.checkpoint import main
+
+    return main(args)
+
+
+def _topology(args) -> int:
+    from glm_tpu_b200.entrypoints.cli.topology import main
+
+    return main(args)
+
+
+def _serve(args) -> int:
+    from glm_tpu_b200.entrypoints.serve.server import main
+
+    argv = ["--run", str(args.run), "--state", str(args.state), "--port", str(args.port)] + (["--no-api"] if args.no_api else [])
+    return main(argv)
+
+
+def build_parser() -> argparse.ArgumentParser:
+    parser = argparse.ArgumentParser(prog="glm-b200", description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    sub = parser.add_subparsers(dest="command", required=True)
+
+    sub.add_parser("info", help="show supported scope and limits").set_defaults(fn=_info)
+
+    ask = sub.add_parser("ask", help="answer questions; optionally batch up to four concurrent chats")
+    inputs = ask.add_mutually_exclusive_group(required=True)
+    inputs.add_argument("question", nargs="?")
+    inputs.add_argument("--questions", type=Path, help="private JSON array of one to ten question strings")
+    ask.add_argument("--context", choices=CONTEXTS, default="32k")
+    ask.add_argument("--capacity", type=int, help="explicit context slots (fixtures); overrides --context")
+    ask.add_argument("--keep-loaded", action="store_true", help="keep the model loaded as a resident session")
+    ask.add_argument("--concurrent", action="store_true", help="run up to four questions as concurrent chats (32k)")
+    ask.add_argument("--max-new-tokens", type=int)
+    ask.add_argument("--wall-seconds", type=int, default=86400)
+    ask.add_argument("--prepare-only", action="store_true")
+    ask.add_argument("--model", help="random:<tiny|small|glm53>[:layers] or a packed checkpoint (default: the site's)")
+    ask.add_argument("--backend", choices=("gpu", "oracle"), default="gpu")
+    ask.add_argument("--gpus", type=int)
+    ask.add_argument("--site", type=Path)
+    ask.set_defaults(fn=_ask)
+
+    prep = sub.add_parser("prepare-request", help="prepare a request without launching the model")
+    source = prep.add_mutually_exclusive_group(required=True)
+    source.add_argument("--messages", type=Path, help="JSON array of chat messages")
+    source.add_argument("--token-ids", type=Path, help="JSON array of prompt token ids")
+    prep.add_argument("--output", type=Path, required=True)
+    prep.add_argument("--request-id", default="request-01")
+    prep.add_argument("--context", choices=CONTEXTS, default="32k")
+    prep.add_argument("--capacity", type=int)
+    prep.add_argument("--max-new-tokens", type=int)
+    prep.add_argument("--reasoning-effort", choices=("low", "high", "max"), default="max")
+    prep.add_argument("--model", default="random:glm53")
+    prep.add_argument("--site", type=Path)
+    prep.set_defaults(fn=_prepare)
+
+    for name in ("collect-env", "doctor"):
+        env = sub.add_parser(name, help="report the environment and check it against a profile")
+        env.add_argument("--profile", choices=("dev", "serve"), default="dev")
+        env.set_defaults(fn=_collect_env)
+
+    ck = sub.add_parser("checkpoint", help="inventory, mark, pack and verify checkpoints")
+    cks = ck.add_subparsers(dest="action", required=True)
+    inv = cks.add_parser("inventory", help="read the safetensors headers of a source checkpoint")
+    inv.add_argument("source", type=Path)
+    mark = cks.add_parser("mark-source", help="write SOURCE_COMPLETE.json after checking the source against its index")
+    mark.add_argument("source", type=Path)
+    pack = cks.add_parser("pack", help="pack a source checkpoint into per-GPU runtime shards")
+    pack.add_argument("source", type=Path)
+    pack.add_argument("target", type=Path)
+    pack.add_argument("--gpus", type=int, default=8)
+    pack.add_argument("--layers", type=int, default=0)
+    ver = cks.add_parser("verify", help="re-hash a packed checkpoint against its manifest and seal")
+    ver.add_argument("target", type=Path)
+    ck.set_defaults(fn=_checkpoint)
+
+    topo = sub.add_parser("topology", help="capture and bind the GPU topology")
+    tops = topo.add_subparsers(dest="action", required=True)
+    cap = tops.add_parser("capture")
+    cap.add_argument("--output", type=Path, required=True)
+    bind = tops.add_parser("bind")
+    bind.add_argument("capture", type=Path)
+    bind.add_argument("--gpus", type=int, default=8)
+    topo.set_defaults(fn=_topology)
+
+    srv = sub.add_parser("serve", help="chat UI + /v1 API attached to a resident session")
+    srv.add_argument("--run", type=Path, required=True)
+    srv.add_argument("--state", type=Path, required=True)
+    srv.add_argument("--port", type=int, default=8011)
+    srv.add_argument("--no-api", action="store_true")
+    srv.set_defaults(fn=_serve)
+    return parser
+
+
+def main(argv: Sequence[str] | None = None) -> int:
+    args = build_parser().parse_args(argv)
+    return args.fn(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

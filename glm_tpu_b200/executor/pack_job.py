@@ -1,0 +1,78 @@
+"""The pack job: inventory -> marker check -> workers -> receipts -> manifest -> seal -> verify.
+
+The controller holds the workload lease, pins the source inventory digest, distributes the files of the packed
+checkpoint (``shared`` + one expert file per GPU rank) over ``jobs`` worker processes, waits for every receipt, assembles
+the manifest from the receipts only, installs geometry + manifest + ``SUCCESS`` create-once and finally re-verifies the
+sealed directory from disk.  A failing worker fails the job; nothing is sealed and the partial target stays unusable.
+
+Parity: reference ``glm_tpu/executor/pack_job.py:38-145``.
+"""
+
+from __future__ import annotations
+
+import json
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+from glm_tpu_b200.exceptions import CheckpointValidationError
+from glm_tpu_b200.executor.jobs import workload_lease
+from glm_tpu_b200.model_loader import pack_worker, source_inventory, source_marker
+from glm_tpu_b200.model_loader.sharded_state import manifest as manifest_mod
+from glm_tpu_b200.model_loader.sharded_state import seal, verify
+
+
+def pack_checkpoint(source: Path, target: Path, world: int, *, run_root: Path | None = None, layers: int = 0, jobs: int = 0,
+                    require_marker: bool = True, timeout: float = 24 * 3600.0) -> dict:
+    source, target = Path(source), Path(target)
+    if (target / "SUCCESS").exists():
+        raise CheckpointValidationError(f"{target} is already a sealed checkpoint")
+    marker = source_marker.require_marker(source) if require_marker else None
+    inv = source_inventory.read_source_inventory(source)
+    geometry = pack_worker.source_geometry(source, layers)
+    target.mkdir(parents=True, exist_ok=True, mode=0o700)
+    files = ["shared"] + [str(r) for r in range(world)]
+    jobs = max(1, min(jobs or len(files), len(files)))
+    receipts_dir = target / "receipts"
+    receipts_dir.mkdir(exist_ok=True)
+    started = time.time()
+
+    def body() -> dict:
+        if jobs == 1:
+            receipts = [pack_worker.run(source, target, world, files, inv.sha256, layers)]
+        else:
+            procs = []
+            for j in range(jobs):
+                mine = files[j::jobs]
+                receipt = receipts_dir / f"receipt.{j}.json"
+                argv = [sys.executable, "-m", "glm_tpu_b200.model_loader.pack_worker", "--source", str(source), "--target", str(target),
+                        "--world", str(world), "--files", ",".join(mine), "--inventory-sha256", inv.sha256, "--receipt", str(receipt),
+                        "--layers", str(layers)]
+                log = (receipts_dir / f"worker.{j}.log").open("wb")
+                procs.append((subprocess.Popen(argv, stdout=log, stderr=subprocess.STDOUT, stdin=subprocess.DEVNULL), receipt, log))
+            failed = []
+            deadline = time.monotonic() + timeout
+            for proc, receipt, log in procs:
+                try:
+                    code = proc.wait(timeout=max(0.0, deadline - time.monotonic()))
+                except subprocess.TimeoutExpired:
+                    proc.kill()
+                    code = -9
+                log.close()
+                if code != 0 or not receipt.exists():
+                    failed.append((receipt.name, code))
+            if failed:
+                raise CheckpointValidationError(f"pack workers failed: {failed}; see {receipts_dir}")
+            receipts = [json.loads(r.read_text()) for _, r, _ in procs]
+        man = manifest_mod.assemble_manifest(receipts, geometry, world, inv.sha256)
+        sealed = seal.install(target, geometry, man)
+        report = verify.verify_runtime_checkpoint(target)
+        return {"ok": True, "target": str(target), "world": world, "files": report["files"], "total_bytes": man["total_bytes"],
+                "manifest_sha256": sealed["manifest_sha256"], "geometry_sha256": geometry.geometry_hash,
+                "source_inventory_sha256": inv.sha256, "source_marker": bool(marker), "seconds": round(time.time() - started, 3)}
+
+    if run_root is None:
+        return body()
+    with workload_lease(run_root):
+        return body()

@@ -1,0 +1,61 @@
+"""Verification of a packed checkpoint: seal -> manifest -> files (size, digest, header contents vs the placement plan).
+
+``verify_runtime_checkpoint(dir, files=None, pins=None)`` checks the seal and the manifest, re-derives from the geometry
+which tensors every file must hold (names, dtypes, shapes), re-hashes the listed files (default: all; a worker passes
+its own two) and compares optional pins (manifest digest).  Any difference raises ``CheckpointValidationError``.
+
+Parity: reference ``glm_tpu/model_loader/sharded_state/verify.py:156-323``.
+"""
+
+from __future__ import annotations
+
+import json
+from pathlib import Path
+
+from glm_tpu_b200.config.model import ModelGeometry
+from glm_tpu_b200.exceptions import CheckpointValidationError
+from glm_tpu_b200.model_loader import placement
+from glm_tpu_b200.model_loader.sharded_state import format as fmt
+from glm_tpu_b200.model_loader.sharded_state import manifest as manifest_mod
+from glm_tpu_b200.model_loader.sharded_state import seal as seal_mod
+
+
+def read_geometry(target: Path) -> ModelGeometry:
+    raw = json.loads((Path(target) / fmt.GEOMETRY_FILE).read_text())
+    for key in ("indexer_types", "mlp_layer_types", "fp8_block_shape", "eos_ids"):
+        raw[key] = tuple(raw[key])
+    return ModelGeometry(**raw)
+
+
+def verify_runtime_checkpoint(target: Path, files: list | None = None, pins: dict | None = None, rehash: bool = True) -> dict:
+    target = Path(target)
+    seal, manifest = seal_mod.read_seal(target)
+    geometry = read_geometry(target)
+    if geometry.geometry_hash != manifest["geometry_sha256"] or manifest["geometry_sha256"] != seal["geometry_sha256"]:
+        raise CheckpointValidationError("geometry, manifest and seal disagree")
+    if pins and pins.get("manifest_sha256") not in (None, "", seal["manifest_sha256"]):
+        raise CheckpointValidationError("the checkpoint is not the pinned one")
+    world = manifest["world"]
+    if sorted(manifest["files"]) != sorted(manifest_mod.expected_files(world)):
+        raise CheckpointValidationError("the manifest does not list exactly the files of this world size")
+    checked = []
+    for name in files if files is not None else sorted(manifest["files"]):
+        record = manifest["files"].get(name)
+        if record is None:
+            raise CheckpointValidationError(f"{name} is not part of this checkpoint")
+        path = target / name
+        if not path.is_file() or path.stat().st_size != record["size"]:
+            raise CheckpointValidationError(f"{name}: missing or wrong size")
+        header, _ = fmt.read_header(path)
+        meta = header.get("__metadata__", {})
+        if meta.get("format") != fmt.FORMAT_VERSION or meta.get("geometry_sha256") != geometry.geometry_hash or meta.get("world") != str(world):
+            raise CheckpointValidationError(f"{name}: foreign or stale file (metadata differs)")
+        rank = None if name == fmt.SHARED_FILE else int(name.split("rank")[1].split("of")[0])
+        want = placement.packed_tensor_shapes(geometry, world, rank)
+        have = {n: (e["dtype"], tuple(e["shape"])) for n, e in header.items() if n != "__metadata__"}
+        if have != {n: (d, tuple(s)) for n, (d, s) in want.items()}:
+            raise CheckpointValidationError(f"{name}: tensor list differs from the placement plan")
+        if rehash and fmt.file_sha256(path) != record["sha256"]:
+            raise CheckpointValidationError(f"{name}: content digest differs from the manifest")
+        checked.append(name)
+    return {"ok": True, "files": checked, "manifest_sha256": seal["manifest_sha256"], "world": world, "geometry_sha256": geometry.geometry_hash}

@@ -1,0 +1,57 @@
+"""``SOURCE_COMPLETE.json``: the marker that a downloaded source checkpoint is whole.
+
+``mark_source`` re-reads the inventory, checks every shard against the expected sizes / SHA-256 digests when a
+``checksums.json`` (``{file: {"size": n, "sha256": hex}}``, e.g. exported from the hub's LFS pointers) is present, hashes
+the small configuration files, and writes the marker create-once.  Packing refuses a source without a valid marker.
+
+Parity: reference ``glm_tpu/model_loader/source_marker.py:138-243``.
+"""
+
+from __future__ import annotations
+
+import json
+from pathlib import Path
+
+from glm_tpu_b200.exceptions import CheckpointValidationError
+from glm_tpu_b200.model_loader import source_inventory
+from glm_tpu_b200.model_loader.sharded_state.format import file_sha256
+from glm_tpu_b200.utils.io_utils import create_private_exclusive
+from glm_tpu_b200.utils.json_utils import canonical_wire_bytes
+
+MARKER_FILE = "SOURCE_COMPLETE.json"
+CHECKSUMS_FILE = "checksums.json"
+SMALL_FILES = ("config.json", "generation_config.json", "tokenizer.json", "tokenizer_config.json", "chat_template.jinja",
+               source_inventory.INDEX_FILE)
+
+
+def mark_source(root: Path, *, hash_shards: bool = False) -> dict:
+    root = Path(root)
+    inv = source_inventory.read_source_inventory(root)
+    expected = json.loads((root / CHECKSUMS_FILE).read_text()) if (root / CHECKSUMS_FILE).exists() else {}
+    files = {}
+    for shard, size in inv.shards.items():
+        record = {"size": size}
+        want = expected.get(shard)
+        if want is not None and want.get("size") not in (None, size):
+            raise CheckpointValidationError(f"{shard}: size {size} differs from the expected {want['size']}")
+        if hash_shards or (want is not None and want.get("sha256")):
+            record["sha256"] = file_sha256(root / shard)
+            if want is not None and want.get("sha256") not in (None, record["sha256"]):
+                raise CheckpointValidationError(f"{shard}: content differs from the expected digest")
+        files[shard] = record
+    small = {name: file_sha256(root / name) for name in SMALL_FILES if (root / name).exists()}
+    marker = {"schema": "glm_b200_source_marker_v1", "inventory_sha256": inv.sha256, "tensor_count": len(inv.tensors),
+              "total_bytes": sum(inv.shards.values()), "shards": files, "small_files": small}
+    create_private_exclusive(root / MARKER_FILE, canonical_wire_bytes(marker) + b"\n")
+    return marker
+
+
+def require_marker(root: Path) -> dict:
+    path = Path(root) / MARKER_FILE
+    if not path.exists():
+        raise CheckpointValidationError("the source has no SOURCE_COMPLETE.json: run `checkpoint mark-source` first")
+    marker = json.loads(path.read_text())
+    inv = source_inventory.read_source_inventory(root)
+    if marker.get("inventory_sha256") != inv.sha256:
+        raise CheckpointValidationError("the source changed after it was marked complete")
+    return marker

@@ -220,6 +220,10 @@ def shard_checkpoint(arrays: Mapping[str, torch.Tensor], layout: ParallelLayout,
     g = layout.geometry
     r, hl = layout.rank, layout.heads_local
     dev = torch.device(device)
+    # A packed checkpoint hands over the routed experts already cut for (rank, world); it says so with this marker.
+    presliced = "__experts_presliced__" in arrays
+    if presliced and arrays["__experts_presliced__"].tolist() != [layout.rank, layout.world]:
+        raise ValueError("the expert tensors were cut for another rank or world size")
 
     def to_dev(name, dtype=None):
         t = arrays[name].to(dev)
@@ -264,8 +268,12 @@ def shard_checkpoint(arrays: Mapping[str, torch.Tensor], layout: ParallelLayout,
                 prefix = f"{p}.mlp.experts.{proj}"
                 if prefix + ".weight_bits" not in arrays:
                     raise ValueError(f"{prefix} must be stored as FP8 (weight_bits + scale_inv)")
-                setattr(lw, attr + "_bits", arrays[prefix + ".weight_bits"][r * el : (r + 1) * el].to(dev).contiguous())
-                setattr(lw, attr + "_scale", arrays[prefix + ".scale_inv"][r * el : (r + 1) * el].to(dev, torch.float32).contiguous())
+                cut = slice(None) if presliced else slice(r * el, (r + 1) * el)
+                bits, scale = arrays[prefix + ".weight_bits"][cut], arrays[prefix + ".scale_inv"][cut]
+                if bits.shape[0] != el:
+                    raise ValueError(f"{prefix}: {bits.shape[0]} experts where this GPU holds {el}")
+                setattr(lw, attr + "_bits", bits.to(dev).contiguous())
+                setattr(lw, attr + "_scale", scale.to(dev, torch.float32).contiguous())
             lw.shared_gate = _decode(arrays, p + ".mlp.shared_experts.gate_proj", g, dev, use_kernel)[r * c : (r + 1) * c].contiguous()
             lw.shared_up = _decode(arrays, p + ".mlp.shared_experts.up_proj", g, dev, use_kernel)[r * c : (r + 1) * c].contiguous()
             lw.shared_down = _decode(arrays, p + ".mlp.shared_experts.down_proj", g, dev, use_kernel)[:, r * c : (r + 1) * c].contiguous()

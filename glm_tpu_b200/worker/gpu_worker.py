@@ -19,7 +19,6 @@ resident_loop, records).
 from __future__ import annotations
 
 import argparse
-import hashlib
 import json
 import os
 import sys
@@ -32,7 +31,6 @@ from glm_tpu_b200.engine.llm_engine import LLMEngine
 from glm_tpu_b200.engine.outputs import final_channel
 from glm_tpu_b200.engine.request_session import LocalVote, ProcessGroupVote
 from glm_tpu_b200.utils.io_utils import persist_json
-from glm_tpu_b200.utils.json_utils import canonical_wire_bytes
 
 
 def parse_args(argv=None):
