@@ -109,6 +109,8 @@ def main() -> int:
     ap.add_argument("--chats", type=int, default=1, help="concurrent chats (lanes): 1 or 4")
     ap.add_argument("--context", type=int, default=32768)
     ap.add_argument("--prompt", type=int, default=200)
+    ap.add_argument("--depth", type=int, default=0,
+                    help="instead of a real prefill, make every chat this many tokens deep with a synthetic (random) cache: decode cost at depth")
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--kv-layout", default="auto", choices=["auto", "striped", "replicated"],
@@ -153,6 +155,10 @@ def main() -> int:
     t0 = time.perf_counter()
     first = []
     for lane in range(args.chats):
+        if args.depth:
+            runner.synthetic_context(lane, args.depth - 97 * lane, seed=lane)
+            first.append(-1)
+            continue
         n = args.prompt if args.chats == 1 else (150, 200, 250, 300, 200, 200, 200, 200)[lane]
         prompt = torch.randint(0, geometry.vocab_size, (n,), generator=gen).tolist()
         first.append(runner.prefill(lane, prompt))
@@ -239,7 +245,9 @@ def main() -> int:
                 "model": f"GLM-5.3 architecture, {layers} of 78 layers" + ("" if layers == 78 else " (truncation for < 8 GPUs)"),
                 "global_batch": args.chats,
                 "seq_len": args.context,
-                "prompt_tokens": args.prompt,
+                "prompt_tokens": args.prompt if not args.depth else None,
+                "context_depth": args.depth or args.prompt,
+                "context_fill": "synthetic random cache rows (no prefill)" if args.depth else "real prefill of the prompt",
                 "parallelism": f"tp{world}(heads,mlp)+ep{world}(experts)" if world > 1 else "single gpu",
                 "comm": args.comm,
                 "kv_layout": runner.kv_layout,

@@ -3,7 +3,7 @@
 // Each GPU holds 1/world of the cached rows.  For a query row the selection kernel has already listed
 // which of the top-k positions live on this GPU (ascending).  Attention runs owner-locally:
 //
-//   sparse_mla_partial   one CTA per (chunk of 64 owned selected rows, query row, block of 64 heads): gathers
+//   sparse_mla_partial   one CTA per (chunk of 64 owned selected rows, query row, block of 16 heads): gathers
 //                        the rows and the absorbed queries into shared memory, computes S = Q K^T on the
 //                        tensor cores (bf16 in, fp32 out), the chunk-local softmax statistics in fp32, rounds
 //                        P to bf16 and computes the unnormalized P . latent product on the tensor cores
@@ -31,6 +31,9 @@
 #define AT_HEADS 16   // heads per CTA (one m16 tile)
 #define AT_PSTRIDE 72 // bf16 elements per P row (64 + 8 padding)
 
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gmem_src) : "memory");
+}
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem_ptr) {
     const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem_ptr);
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
@@ -79,24 +82,35 @@ sparse_mla_partial_kernel(const bf16* __restrict__ q_full, const bf16* __restric
     const int cnt = min(AT_CHUNK, count - start);
     const bf16* cache = kv_cache + ((int64_t)row_lane[r] * layers + layer) * (int64_t)local_cap * W;
     const int vec_per_row = W / 8;
-    // gather the selected rows (zero-fill the tail of a short chunk) and this CTA's heads of the query
+    // Gather the selected rows (zero-fill the tail of a short chunk) and this CTA's heads of the query.  The row
+    // numbers are fetched first, then every 16-byte piece is an asynchronous copy (L2 -> shared memory, no
+    // registers, all in flight at once): the gather costs about one memory round trip.
+    __shared__ int row_s[AT_CHUNK];
+    if (threadIdx.x < AT_CHUNK) {
+        int row = -1;
+        if ((int)threadIdx.x < cnt) {
+            row = sel_local[(int64_t)r * top_k + start + threadIdx.x];
+            if (row < 0 || row >= local_cap) { raise_status(status, GLMB_STATUS_BAD_INDEX); row = min(max(row, 0), local_cap - 1); }
+        }
+        row_s[threadIdx.x] = row;
+    }
+    __syncthreads();
     for (int i = threadIdx.x; i < AT_CHUNK * vec_per_row; i += AT_THREADS) {
         const int c = i / vec_per_row, v = i % vec_per_row;
-        uint4 val = make_uint4(0, 0, 0, 0);
-        if (c < cnt) {
-            int row = sel_local[(int64_t)r * top_k + start + c];
-            if (row < 0 || row >= local_cap) { raise_status(status, GLMB_STATUS_BAD_INDEX); row = min(max(row, 0), local_cap - 1); }
-            val = *reinterpret_cast<const uint4*>(cache + (int64_t)row * W + v * 8);
-        }
-        *reinterpret_cast<uint4*>(kv_s + c * WP + v * 8) = val;
+        const int row = row_s[c];
+        bf16* dst = kv_s + c * WP + v * 8;
+        if (row >= 0) cp_async16(dst, cache + (int64_t)row * W + v * 8);
+        else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
     }
     const bf16* q = q_full + (int64_t)r * H * W;
     for (int i = threadIdx.x; i < AT_HEADS * vec_per_row; i += AT_THREADS) {
         const int h = i / vec_per_row, v = i % vec_per_row;
-        uint4 val = make_uint4(0, 0, 0, 0);
-        if (h_base + h < H) val = ld_hot16(q + (int64_t)(h_base + h) * W + v * 8);
-        *reinterpret_cast<uint4*>(q_s + h * WP + v * 8) = val;
+        bf16* dst = q_s + h * WP + v * 8;
+        if (h_base + h < H) cp_async16(dst, q + (int64_t)(h_base + h) * W + v * 8);  // .cg: read at L2, where peers' pushes land
+        else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
     }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -195,39 +209,68 @@ sparse_mla_partial_kernel(const bf16* __restrict__ q_full, const bf16* __restric
 }
 
 // grid (H, rows).  world == 1: o_lat[r][h] = bf16(o / l).  world > 1: push (o[L], m, l) to head owner.
+// The chunk statistics are fetched by one thread per chunk and the partial rows by float4 loads issued eight
+// chunks at a time, so the kernel costs a few memory round trips however many chunks a row has.
+#define AM_MAX_CHUNKS 128
 __global__ void __launch_bounds__(128)
 attn_local_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, const int* __restrict__ sel_counts,
                         int H, int L, int top_k, int max_chunks, bf16* __restrict__ o_lat, int heads_local,
                         int64_t xpart_offset, PeerComm comm, int sig) {
     GLMB_PDL_PROLOGUE();
-    __shared__ float w_s[64];
+    __shared__ float w_s[AM_MAX_CHUNKS];
+    __shared__ float red_s[8];
     const int h = blockIdx.x, r = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int count = min(max(sel_counts[2 * r + 1], 0), top_k);
-    const int chunks = (count + AT_CHUNK - 1) / AT_CHUNK;
-    float M = -INFINITY;
-    for (int c = 0; c < chunks; ++c) M = fmaxf(M, part_ml[(((int64_t)r * max_chunks + c) * H + h) * 2]);
-    float l = 0.f;
-    for (int c = 0; c < chunks; ++c) {
-        const float* ml = part_ml + (((int64_t)r * max_chunks + c) * H + h) * 2;
-        const float wgt = expf(ml[0] - M);
-        l += ml[1] * wgt;
-        if (threadIdx.x == 0 && c < 64) w_s[c] = wgt;
+    const int chunks = min((count + AT_CHUNK - 1) / AT_CHUNK, AM_MAX_CHUNKS);
+    const int64_t base = (int64_t)r * max_chunks * H + h;  // chunk c of this (row, head) is at base + c * H
+    // every thread owns at most one chunk's statistics (chunks <= 128 == blockDim.x)
+    float my_m = -INFINITY, my_l = 0.f;
+    if ((int)threadIdx.x < chunks) {
+        const float2 ml = *reinterpret_cast<const float2*>(part_ml + (base + (int64_t)threadIdx.x * H) * 2);
+        my_m = ml.x; my_l = ml.y;
     }
+    float M = my_m;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+    if (lane == 0) red_s[warp] = M;
     __syncthreads();
+    M = fmaxf(fmaxf(red_s[0], red_s[1]), fmaxf(red_s[2], red_s[3]));
+    const float my_w = (int)threadIdx.x < chunks ? expf(my_m - M) : 0.f;
+    w_s[threadIdx.x] = my_w;
+    float l = my_l * my_w;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+    if (lane == 0) red_s[4 + warp] = l;
+    __syncthreads();
+    l = (red_s[4] + red_s[5]) + (red_s[6] + red_s[7]);
     const int rows = gridDim.y;
-    for (int j = threadIdx.x; j < L; j += blockDim.x) {
-        float o = 0.f;
-        for (int c = 0; c < chunks; ++c) {
-            const int64_t at = ((int64_t)r * max_chunks + c) * H + h;
-            o = fmaf(part_o[at * L + j], c < 64 ? w_s[c] : expf(part_ml[at * 2] - M), o);
+    for (int j = threadIdx.x * 4; j < L; j += blockDim.x * 4) {
+        float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int c0 = 0; c0 < chunks; c0 += 8) {
+            float4 v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                v[u] = c0 + u < chunks ? *reinterpret_cast<const float4*>(part_o + (base + (int64_t)(c0 + u) * H) * L + j)
+                                       : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const float wgt = c0 + u < chunks ? w_s[c0 + u] : 0.f;
+                o.x = fmaf(v[u].x, wgt, o.x); o.y = fmaf(v[u].y, wgt, o.y);
+                o.z = fmaf(v[u].z, wgt, o.z); o.w = fmaf(v[u].w, wgt, o.w);
+            }
         }
         if (comm.world == 1) {
-            o_lat[((int64_t)r * H + h) * L + j] = __float2bfloat16_rn(chunks > 0 ? o / l : 0.f);
+            uint2 packed;
+            if (chunks > 0) { o.x /= l; o.y /= l; o.z /= l; o.w /= l; }  // the contract divides (no reciprocal)
+            packed.x = pack_bf16(o.x, o.y);
+            packed.y = pack_bf16(o.z, o.w);
+            *reinterpret_cast<uint2*>(o_lat + ((int64_t)r * H + h) * L + j) = packed;
         } else {
             const int dst = h / heads_local, hl = h % heads_local;
             float* box = reinterpret_cast<float*>(comm.data[dst] + xpart_offset) +
                          (((int64_t)comm.rank * rows + r) * heads_local + hl) * (L + 2);
-            box[j] = o;
+            box[j] = o.x; box[j + 1] = o.y; box[j + 2] = o.z; box[j + 3] = o.w;  // L + 2 floats per box: 8-byte aligned only
             if (j == 0) { box[L] = chunks > 0 ? M : -INFINITY; box[L + 1] = chunks > 0 ? l : 0.f; }
         }
     }
@@ -304,6 +347,7 @@ GLMB_API int glmb_sparse_mla_partial(const void* q_full, const void* kv_cache, c
 GLMB_API int glmb_attn_local_merge(const float* part_o, const float* part_ml, const int* sel_counts, int rows, int H, int L,
                                    int top_k, int max_chunks, void* o_lat, int heads_local, int64_t xpart_offset,
                                    const PeerComm* comm, int sig, void* stream) {
+    if ((L & 3) || max_chunks > AM_MAX_CHUNKS) return 1;
     PeerComm c;
     if (comm) c = *comm; else { memset(&c, 0, sizeof(c)); c.world = 1; }
     dim3 grid(H, rows);

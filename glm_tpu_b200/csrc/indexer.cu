@@ -15,10 +15,15 @@
 #include "common.cuh"
 #include "peer.cuh"
 
-// One thread per cached key.  The key (D bf16) lives in registers as packed words; the query heads are
-// read from shared memory as broadcast float4.
-template <int D>
-__global__ void __launch_bounds__(256)
+// Each thread scores IX_KPT adjacent cached keys.  The keys (D bf16 each) live in registers as packed words; the
+// query heads are read from shared memory as broadcast float4, HG heads at a time.  A broadcast float4 read
+// still returns 512 bytes to the warp, so the shared-memory return path, not the FMA pipe, is the limit: every
+// query value fetched is therefore used for IX_KPT keys, and each key element is unpacked once per group of heads.
+// Per key and head the dot product is four chains combined as (d0+d1)+(d2+d3).
+#define IX_KPT 2
+#define IX_THREADS 128
+template <int D, int HG>
+__global__ void __launch_bounds__(IX_THREADS)
 indexer_score_kernel(const float* __restrict__ q_idx, const float* __restrict__ head_w, const bf16* __restrict__ index_cache,
                      const int* __restrict__ row_pos, const int* __restrict__ row_lane, int IH, int index_slot, int full_layers,
                      int local_cap, int stripe, int world, int rank, int capacity, int64_t score_stride, float scale,
@@ -27,51 +32,106 @@ indexer_score_kernel(const float* __restrict__ q_idx, const float* __restrict__ 
     extern __shared__ float sq[];  // IH * D query, then IH weights
     float* sw = sq + IH * D;
     const int r = blockIdx.y;
-    for (int i = threadIdx.x; i < IH * D; i += blockDim.x) sq[i] = q_idx[(int64_t)r * IH * D + i];
+    {
+        // the query (IH * D fp32, D % 4 == 0) in batches of eight independent 16-byte loads per thread
+        const float4* src = reinterpret_cast<const float4*>(q_idx + (int64_t)r * IH * D);
+        float4* dst = reinterpret_cast<float4*>(sq);
+        const int nvec = IH * D / 4;
+        for (int base = 0; base < nvec; base += IX_THREADS * 8) {
+            float4 v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int i = base + u * IX_THREADS + threadIdx.x;
+                v[u] = i < nvec ? src[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int i = base + u * IX_THREADS + threadIdx.x;
+                if (i < nvec) dst[i] = v[u];
+            }
+        }
+    }
     for (int i = threadIdx.x; i < IH; i += blockDim.x) sw[i] = head_w[(int64_t)r * IH + i];
-    __syncthreads();
     const int pos = min(max(row_pos[r], 0), capacity - 1);
     const int ctx = pos + 1;
     const int page = stripe * world;
     // number of positions < ctx stored on this rank
     const int rest = ctx % page;
     const int owned = (ctx / page) * stripe + min(max(rest - rank * stripe, 0), stripe);
-    const int j = blockIdx.x * blockDim.x + threadIdx.x;
-    if (j < owned) {
-        const bf16* key = index_cache + (((int64_t)row_lane[r] * full_layers + index_slot) * local_cap + j) * D;
-        uint32_t kw[D / 2];
+    const int j0 = (blockIdx.x * blockDim.x + threadIdx.x) * IX_KPT;
+    uint32_t kw[IX_KPT][D / 2];
+    if (j0 < owned) {
+        const bf16* key = index_cache + (((int64_t)row_lane[r] * full_layers + index_slot) * local_cap + j0) * D;
 #pragma unroll
-        for (int i = 0; i < D / 8; ++i) {
-            const uint4 v = *reinterpret_cast<const uint4*>(key + i * 8);
-            kw[4 * i] = v.x; kw[4 * i + 1] = v.y; kw[4 * i + 2] = v.z; kw[4 * i + 3] = v.w;
-        }
-        float score = 0.f;
-        for (int h = 0; h < IH; ++h) {
-            const float4* qh = reinterpret_cast<const float4*>(sq + h * D);
-            float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;  // four chains: the dot is latency-, not throughput-bound
+        for (int k = 0; k < IX_KPT; ++k)
+#pragma unroll
+            for (int i = 0; i < D / 8; ++i) {
+                // a key past the owned range is read as its own neighbour and its score dropped
+                const uint4 v = *reinterpret_cast<const uint4*>(key + (j0 + k < owned ? k : 0) * D + i * 8);
+                kw[k][4 * i] = v.x; kw[k][4 * i + 1] = v.y; kw[k][4 * i + 2] = v.z; kw[k][4 * i + 3] = v.w;
+            }
+    }
+    __syncthreads();
+    if (j0 < owned) {
+        float score[IX_KPT];
+#pragma unroll
+        for (int k = 0; k < IX_KPT; ++k) score[k] = 0.f;
+        for (int h0 = 0; h0 < IH; h0 += HG) {
+            float acc[IX_KPT][HG][4];
+#pragma unroll
+            for (int k = 0; k < IX_KPT; ++k)
+#pragma unroll
+                for (int h = 0; h < HG; ++h) acc[k][h][0] = acc[k][h][1] = acc[k][h][2] = acc[k][h][3] = 0.f;
+            // The unpacking constants come from an opaque move so that the compiler re-unpacks the keys in every
+            // group of heads instead of hoisting 2 * D fp32 values out of the loop (which spills).
+            uint32_t lo_shift, hi_mask;
+            asm volatile("mov.u32 %0, 16; mov.u32 %1, 0xffff0000;" : "=r"(lo_shift), "=r"(hi_mask));
 #pragma unroll
             for (int i = 0; i < D / 4; ++i) {
-                const float4 qv = qh[i];
-                d0 = fmaf(qv.x, bf16_lo(kw[2 * i]), d0);
-                d1 = fmaf(qv.y, bf16_hi(kw[2 * i]), d1);
-                d2 = fmaf(qv.z, bf16_lo(kw[2 * i + 1]), d2);
-                d3 = fmaf(qv.w, bf16_hi(kw[2 * i + 1]), d3);
+                float kv[IX_KPT][4];
+#pragma unroll
+                for (int k = 0; k < IX_KPT; ++k) {
+                    kv[k][0] = __uint_as_float(kw[k][2 * i] << lo_shift); kv[k][1] = __uint_as_float(kw[k][2 * i] & hi_mask);
+                    kv[k][2] = __uint_as_float(kw[k][2 * i + 1] << lo_shift); kv[k][3] = __uint_as_float(kw[k][2 * i + 1] & hi_mask);
+                }
+#pragma unroll
+                for (int h = 0; h < HG; ++h) {
+                    const float4 qv = reinterpret_cast<const float4*>(sq + (h0 + h) * D)[i];
+#pragma unroll
+                    for (int k = 0; k < IX_KPT; ++k) {
+                        acc[k][h][0] = fmaf(qv.x, kv[k][0], acc[k][h][0]);
+                        acc[k][h][1] = fmaf(qv.y, kv[k][1], acc[k][h][1]);
+                        acc[k][h][2] = fmaf(qv.z, kv[k][2], acc[k][h][2]);
+                        acc[k][h][3] = fmaf(qv.w, kv[k][3], acc[k][h][3]);
+                    }
+                }
             }
-            const float dot = (d0 + d1) + (d2 + d3);
-            score = fmaf(sw[h], fmaxf(__fmul_rn(dot, scale), 0.f), score);
+#pragma unroll
+            for (int h = 0; h < HG; ++h)
+#pragma unroll
+                for (int k = 0; k < IX_KPT; ++k) {
+                    const float dot = (acc[k][h][0] + acc[k][h][1]) + (acc[k][h][2] + acc[k][h][3]);
+                    score[k] = fmaf(sw[h0 + h], fmaxf(__fmul_rn(dot, scale), 0.f), score[k]);
+                }
         }
-        if (!isfinite(score)) raise_status(status, GLMB_STATUS_NONFINITE);
-        const int g = (j / stripe) * page + rank * stripe + j % stripe;
-        const int64_t at = (int64_t)r * score_stride + g;
-        scores[at] = score;
-        for (int p = 0; p < comm.world; ++p)
-            if (p != comm.rank) reinterpret_cast<float*>(comm.data[p] + scores_offset)[at] = score;
+#pragma unroll
+        for (int k = 0; k < IX_KPT; ++k) {
+            const int j = j0 + k;
+            if (j >= owned) break;
+            if (!isfinite(score[k])) raise_status(status, GLMB_STATUS_NONFINITE);
+            const int g = (j / stripe) * page + rank * stripe + j % stripe;
+            const int64_t at = (int64_t)r * score_stride + g;
+            scores[at] = score[k];
+            for (int p = 0; p < comm.world; ++p)
+                if (p != comm.rank) reinterpret_cast<float*>(comm.data[p] + scores_offset)[at] = score[k];
+        }
     }
     grid_signal_peers(comm, sig);
 }
 
 // ---------------------------------------------------------------------------------------------------
 #define TK_THREADS 1024
+#define TK_SMEM_LIMIT (200 * 1024)  // score rows up to 51,200 positions are selected out of shared memory
 
 // Exclusive block scan of one uint32 per thread; returns the exclusive prefix, *total receives the sum.
 __device__ __forceinline__ uint32_t block_exclusive_scan(uint32_t v, uint32_t* warp_totals, uint32_t* total) {
@@ -101,11 +161,17 @@ __device__ __forceinline__ uint32_t block_exclusive_scan(uint32_t v, uint32_t* w
     return warp_totals[warp] + inc - v;
 }
 
+// SMEM: the order-preserving keys of the whole score row are staged in shared memory once (capacity * 4 bytes)
+// and every pass runs over shared memory; otherwise every pass re-reads the scores through L2.
+// POW2: stripe and world are powers of two, so the owner / local-row arithmetic is shifts and masks (an integer
+// division by a run-time value costs more than the rest of the per-position work).
+template <bool SMEM, bool POW2>
 __global__ void __launch_bounds__(TK_THREADS)
 topk_select_kernel(const float* __restrict__ scores, const int* __restrict__ row_pos, int capacity, int64_t score_stride, int top_k, int stripe,
                    int world, int rank, int* __restrict__ sel_global, int* __restrict__ sel_local, int* __restrict__ sel_counts,
                    PeerComm comm, int sig) {
     GLMB_PDL_PROLOGUE();
+    extern __shared__ uint32_t keys_s[];
     __shared__ uint32_t hist[256];
     __shared__ uint32_t warp_totals[33];
     __shared__ uint32_t s_bucket, s_need;
@@ -116,26 +182,56 @@ topk_select_kernel(const float* __restrict__ scores, const int* __restrict__ row
     int* out_g = sel_global + (int64_t)r * top_k;
     int* out_l = sel_local + (int64_t)r * top_k;
     const int page = stripe * world;
+    const int stripe_sh = 31 - __clz(stripe), page_sh = 31 - __clz(page);
+    auto owner_is_me = [&](int i) -> bool { return (POW2 ? ((i >> stripe_sh) & (world - 1)) : ((i / stripe) % world)) == rank; };
+    auto local_row = [&](int i) -> int {
+        return POW2 ? (((i >> page_sh) << stripe_sh) | (i & (stripe - 1))) : ((i / page) * stripe + i % stripe);
+    };
     const int ipt = (n + TK_THREADS - 1) / TK_THREADS;
     const int begin = min(n, (int)threadIdx.x * ipt), end = min(n, begin + ipt);
+    const int lane = threadIdx.x & 31;
+    if (SMEM) {
+        for (int base = 0; base < n; base += TK_THREADS * 8) {  // eight independent loads per thread per round trip
+            float v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int i = base + u * TK_THREADS + threadIdx.x;
+                v[u] = i < n ? __ldcg(sc + i) : 0.f;
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int i = base + u * TK_THREADS + threadIdx.x;
+                if (i < n) keys_s[i] = orderable_u32(v[u]);
+            }
+        }
+        __syncthreads();
+    }
+    auto key_at = [&](int i) -> uint32_t { return SMEM ? keys_s[i] : orderable_u32(sc[i]); };
 
     uint32_t thresh = 0, need = 0;
     const bool take_all = n <= top_k;
     if (!take_all) {
         uint32_t prefix = 0, mask = 0;
         need = top_k;
+        const int n_up = ipt * TK_THREADS;  // whole warps walk the row together (the ballots need every lane)
         for (int pass = 0; pass < 4; ++pass) {
             const int shift = 24 - 8 * pass;
             if (threadIdx.x < 256) hist[threadIdx.x] = 0;
             __syncthreads();
-            for (int i = threadIdx.x; i < n; i += TK_THREADS) {
-                const uint32_t key = orderable_u32(sc[i]);
-                if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1u);
+            for (int i = threadIdx.x; i < n_up; i += TK_THREADS) {
+                const uint32_t key = i < n ? key_at(i) : 0u;
+                const bool in = i < n && (key & mask) == prefix;
+                const uint32_t bin = (key >> shift) & 255u;
+                const unsigned active = __ballot_sync(0xffffffffu, in);
+                if (in) {
+                    // scores cluster in a few bins: one atomic per distinct bin per warp instead of one per key
+                    const unsigned same = __match_any_sync(active, bin);
+                    if (lane == __ffs(same) - 1) atomicAdd(&hist[bin], (uint32_t)__popc(same));
+                }
             }
             __syncthreads();
             if (threadIdx.x < 32) {
                 // lane l owns bins 255-8l .. 248-8l (descending); find the bin where the running count reaches `need`
-                const int lane = threadIdx.x;
                 uint32_t local[8], sum = 0;
 #pragma unroll
                 for (int i = 0; i < 8; ++i) { local[i] = hist[255 - (lane * 8 + i)]; sum += local[i]; }
@@ -166,18 +262,18 @@ topk_select_kernel(const float* __restrict__ scores, const int* __restrict__ row
     // ordered compaction: each thread owns a contiguous run of positions
     uint32_t eq_mine = 0;
     if (!take_all)
-        for (int i = begin; i < end; ++i) eq_mine += orderable_u32(sc[i]) == thresh;
+        for (int i = begin; i < end; ++i) eq_mine += key_at(i) == thresh;
     uint32_t eq_total;
     uint32_t eq_before = block_exclusive_scan(eq_mine, warp_totals, &eq_total);
     uint32_t sel_mine = 0, own_mine = 0;
     for (int i = begin; i < end; ++i) {
         bool sel = true;
         if (!take_all) {
-            const uint32_t key = orderable_u32(sc[i]);
+            const uint32_t key = key_at(i);
             sel = key > thresh;
             if (key == thresh) { sel = eq_before < need; ++eq_before; }
         }
-        if (sel) { ++sel_mine; own_mine += ((i / stripe) % world) == rank; }
+        if (sel) { ++sel_mine; own_mine += owner_is_me(i); }
     }
     eq_before -= eq_mine;  // restore for the second sweep
     uint32_t packed_total;
@@ -186,15 +282,15 @@ topk_select_kernel(const float* __restrict__ scores, const int* __restrict__ row
     for (int i = begin; i < end; ++i) {
         bool sel = true;
         if (!take_all) {
-            const uint32_t key = orderable_u32(sc[i]);
+            const uint32_t key = key_at(i);
             sel = key > thresh;
             if (key == thresh) { sel = eq_before < need; ++eq_before; }
         }
         if (sel) {
             if (at_g < (uint32_t)top_k) out_g[at_g] = i;
             ++at_g;
-            if (((i / stripe) % world) == rank) {
-                if (at_l < (uint32_t)top_k) out_l[at_l] = (i / page) * stripe + i % stripe;
+            if (owner_is_me(i)) {
+                if (at_l < (uint32_t)top_k) out_l[at_l] = local_row(i);
                 ++at_l;
             }
         }
@@ -216,14 +312,16 @@ GLMB_API int glmb_indexer_score(const float* q_idx, const float* head_w, const v
     // grid.x covers the largest number of rows any rank can own for a context of max_ctx positions
     const int page = stripe * world;
     const int owned_max = (max_ctx / page) * stripe + min(max_ctx % page, stripe);
-    dim3 grid(ceil_div(owned_max > 0 ? owned_max : 1, 256), rows);
+    dim3 grid(ceil_div(owned_max > 0 ? owned_max : 1, IX_THREADS * IX_KPT), rows);
     const size_t smem = (size_t)(IH * D + IH) * sizeof(float);
     cudaStream_t st = (cudaStream_t)stream;
-#define CALL(DD)                                                                                                          \
-    GLMB_LAUNCH(indexer_score_kernel<DD>, grid, 256, smem, st, q_idx, head_w, (const bf16*)index_cache, row_pos, row_lane, IH, index_slot, \
+#define CALL(DD, HH)                                                                                                      \
+    GLMB_LAUNCH((indexer_score_kernel<DD, HH>), grid, IX_THREADS, smem, st, q_idx, head_w, (const bf16*)index_cache, row_pos, row_lane, IH, index_slot, \
                                                       full_layers, local_cap, stripe, world, rank, capacity, score_stride, scale, scores,  \
                                                       scores_offset, c, sig, status)
-    if (D == 128) { CALL(128); } else if (D == 64) { CALL(64); } else if (D == 32) { CALL(32); } else return 1;
+#define CALL_D(DD) do { if (IH % 8 == 0) { CALL(DD, 8); } else if (IH % 4 == 0) { CALL(DD, 4); } else if (IH % 2 == 0) { CALL(DD, 2); } else { CALL(DD, 1); } } while (0)
+    if (D == 128) CALL_D(128); else if (D == 64) CALL_D(64); else if (D == 32) CALL_D(32); else return 1;
+#undef CALL_D
 #undef CALL
     return (int)cudaGetLastError();
 }
@@ -235,7 +333,24 @@ GLMB_API int glmb_topk_select(const float* scores, const int* row_pos, int rows,
     if (top_k > 65535) return 1;
     PeerComm c;
     if (comm) c = *comm; else { memset(&c, 0, sizeof(c)); c.world = 1; }
-    GLMB_LAUNCH(topk_select_kernel, rows, TK_THREADS, 0, (cudaStream_t)stream, scores, row_pos, capacity, score_stride, top_k, stripe, world, rank,
-                                                                      sel_global, sel_local, sel_counts, c, sig);
+    const size_t smem = (size_t)capacity * sizeof(uint32_t);
+    const bool pow2 = stripe > 0 && world > 0 && !(stripe & (stripe - 1)) && !(world & (world - 1));
+#define TK_LAUNCH(S, P, BYTES)                                                                                              \
+    GLMB_LAUNCH((topk_select_kernel<S, P>), rows, TK_THREADS, BYTES, (cudaStream_t)stream, scores, row_pos, capacity, score_stride, top_k, \
+                stripe, world, rank, sel_global, sel_local, sel_counts, c, sig)
+    if (smem <= TK_SMEM_LIMIT) {
+        static bool attr_set = false;
+        if (!attr_set) {
+            cudaError_t e = cudaFuncSetAttribute(topk_select_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, TK_SMEM_LIMIT);
+            if (e == cudaSuccess)
+                e = cudaFuncSetAttribute(topk_select_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, TK_SMEM_LIMIT);
+            if (e != cudaSuccess) return (int)e;
+            attr_set = true;
+        }
+        if (pow2) { TK_LAUNCH(true, true, smem); } else { TK_LAUNCH(true, false, smem); }
+    } else {
+        if (pow2) { TK_LAUNCH(false, true, 0); } else { TK_LAUNCH(false, false, 0); }
+    }
+#undef TK_LAUNCH
     return (int)cudaGetLastError();
 }

@@ -287,6 +287,8 @@ __global__ void __launch_bounds__(256) q_post_kernel(QPostArgs a) {
 // blockIdx.y == 0 CTA, the rope part) is also stored into every peer's query buffer: the all-gather of
 // the queries over heads is fused here, and the last CTA signals GLMB_SIG_Q.
 #define QA_COLS 128
+#define QA_BATCH 12     // weight rows in flight per thread
+#define QA_MAX_NOPE 256 // widest no-position part of a query head the kernel stages
 template <int R>
 __global__ void __launch_bounds__(256)
 q_absorb_kernel(const bf16* __restrict__ q_nope, int rows, const bf16* __restrict__ kv_b, int heads_local, int head_base,
@@ -294,25 +296,46 @@ q_absorb_kernel(const bf16* __restrict__ q_nope, int rows, const bf16* __restric
                 PeerComm comm, int sig) {
     GLMB_PDL_PROLOGUE();
     __shared__ float red[8][R][QA_COLS];
+    __shared__ float qs[R][QA_MAX_NOPE];
     const int h = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int c0 = blockIdx.y * QA_COLS + lane * 4;
     const int per = (nope + 7) / 8;
     const int d0 = warp * per, d1 = min(nope, d0 + per);
+    for (int i = threadIdx.x; i < R * nope; i += blockDim.x) {
+        const int r = i / nope, d = i % nope;
+        qs[r][d] = __bfloat162float(q_nope[((int64_t)(r < rows ? r : 0) * heads_local + h) * nope + d]);
+    }
     float acc[R][4];
 #pragma unroll
     for (int r = 0; r < R; ++r) acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.f;
     const bf16* wk = kv_b + (int64_t)h * (nope + vdim) * L;
+    // this warp's slice of the weight in two batches of independent loads, issued before the query is needed
+    uint2 wv[QA_BATCH];
     if (c0 < L) {
-#pragma unroll 8
-        for (int d = d0; d < d1; ++d) {
-            const uint2 wv = *reinterpret_cast<const uint2*>(wk + (int64_t)d * L + c0);
-            const float w0 = bf16_lo(wv.x), w1 = bf16_hi(wv.x), w2 = bf16_lo(wv.y), w3 = bf16_hi(wv.y);
 #pragma unroll
-            for (int r = 0; r < R; ++r) {
-                const float qv = __bfloat162float(q_nope[((int64_t)(r < rows ? r : 0) * heads_local + h) * nope + d]);
-                acc[r][0] = fmaf(qv, w0, acc[r][0]); acc[r][1] = fmaf(qv, w1, acc[r][1]);
-                acc[r][2] = fmaf(qv, w2, acc[r][2]); acc[r][3] = fmaf(qv, w3, acc[r][3]);
+        for (int u = 0; u < QA_BATCH; ++u)
+            wv[u] = d0 + u < d1 ? *reinterpret_cast<const uint2*>(wk + (int64_t)(d0 + u) * L + c0) : make_uint2(0, 0);
+    }
+    __syncthreads();
+    if (c0 < L) {
+        for (int db = d0; db < d1; db += QA_BATCH) {
+            uint2 nx[QA_BATCH];
+#pragma unroll
+            for (int u = 0; u < QA_BATCH; ++u)
+                nx[u] = db + QA_BATCH + u < d1 ? *reinterpret_cast<const uint2*>(wk + (int64_t)(db + QA_BATCH + u) * L + c0) : make_uint2(0, 0);
+#pragma unroll
+            for (int u = 0; u < QA_BATCH; ++u) {
+                if (db + u >= d1) break;
+                const float w0 = bf16_lo(wv[u].x), w1 = bf16_hi(wv[u].x), w2 = bf16_lo(wv[u].y), w3 = bf16_hi(wv[u].y);
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    const float qv = qs[r][db + u];
+                    acc[r][0] = fmaf(qv, w0, acc[r][0]); acc[r][1] = fmaf(qv, w1, acc[r][1]);
+                    acc[r][2] = fmaf(qv, w2, acc[r][2]); acc[r][3] = fmaf(qv, w3, acc[r][3]);
+                }
             }
+#pragma unroll
+            for (int u = 0; u < QA_BATCH; ++u) wv[u] = nx[u];
         }
     }
 #pragma unroll
@@ -380,7 +403,7 @@ GLMB_API int glmb_q_post(const QPostArgs* args, int rows, void* stream) {
 GLMB_API int glmb_q_absorb(const void* q_nope, int rows, const void* kv_b, int heads_local, int head_base, int heads_total,
                            int nope, int vdim, int L, int rd, void* q_full, int64_t q_full_offset, const PeerComm* comm, int sig,
                            void* stream) {
-    if (rows < 1 || rows > GLMB_MAX_ROWS || (L & 3)) return 1;
+    if (rows < 1 || rows > GLMB_MAX_ROWS || (L & 3) || nope > QA_MAX_NOPE) return 1;
     PeerComm c;
     if (comm) c = *comm; else { memset(&c, 0, sizeof(c)); c.world = 1; }
     dim3 grid(heads_local, ceil_div(L, QA_COLS));

@@ -88,7 +88,53 @@ def lib() -> C.CDLL:
 
         if os.environ.get("GLM_B200_PDL", "1") == "0":  # programmatic dependent launch off: plain stream order
             _lib.glmb_set_pdl(0)
-    return _lib
+    return _lib if _timeline is None else _TimedLib(_lib)
+
+
+_timeline = None  # when a list: every launch appends (entry point, plain integer arguments, start event, end event)
+
+
+class _TimedLib:
+    """Brackets every entry point that launches on the current stream with a pair of CUDA events."""
+
+    def __init__(self, inner):
+        self._inner = inner
+
+    def __getattr__(self, name):
+        fn = getattr(self._inner, name)
+        if not name.startswith("glmb_") or name.startswith(("glmb_peer_", "glmb_set_", "glmb_attn_chunk")):
+            return fn
+
+        def timed(*args):
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            code = fn(*args)
+            end.record()
+            ints = tuple(a if isinstance(a, int) else a.value for a in args if isinstance(a, (int, C.c_int64, C.c_int)))
+            _timeline.append((name[5:], ints, start, end))
+            return code
+
+        return timed
+
+
+class kernel_timeline:
+    """``with kernel_timeline() as tl:`` collects per-launch device times (eager launches only, not graph replays).
+
+    ``tl.rows()`` synchronizes and returns ``[(entry point, integer arguments, milliseconds), ...]`` in launch order.
+    """
+
+    def __enter__(self):
+        global _timeline
+        self.events = _timeline = []
+        return self
+
+    def __exit__(self, *exc):
+        global _timeline
+        _timeline = None
+
+    def rows(self):
+        torch.cuda.synchronize()
+        return [(name, ints, start.elapsed_time(end)) for name, ints, start, end in self.events]
 
 
 def _p(t):

@@ -24,6 +24,7 @@ from glm_tpu_b200.config.cache import CacheConfig
 from glm_tpu_b200.config.parallel import ParallelLayout
 from glm_tpu_b200.models.glm_moe_dsa.model import RING, DecoderState, GlmMoeDsaModel, Workspace
 from glm_tpu_b200.models.glm_moe_dsa.weights import DeviceWeights
+from glm_tpu_b200.ops import native
 from glm_tpu_b200.parallel.peer import PeerGroup
 from glm_tpu_b200.runner.admission import project_memory
 
@@ -201,6 +202,24 @@ class GpuModelRunner:
             token = int(self._prefill_out.cpu()[0])
             self.peer.check_status()
         return token
+
+    def synthetic_context(self, lane: int, depth: int, seed: int = 0) -> None:
+        """Benchmarks only: make ``lane`` look ``depth`` tokens deep without running a prefill.
+
+        The lane's cache rows are filled with random bf16 values (a normalized latent and a rotated key have this
+        scale), its position is set to ``depth`` and it is activated; decode steps then cost what they cost at that
+        depth (indexer scoring over ``depth`` keys, top-k, 2,048 selected rows), which a short prompt does not show.
+        """
+        if not 0 < depth < self.cache.context_capacity:
+            raise ValueError("depth does not fit the context capacity")
+        st = self.state
+        with torch.cuda.device(self.device):
+            native.fill_random_bf16(st.kv_cache[lane], seed * 2 + 1, 0.0, 0.5)
+            native.fill_random_bf16(st.index_cache[lane], seed * 2 + 2, 0.0, 0.5)
+            st.tokens[lane] = 1 + (seed % 1000)
+            st.positions[lane] = depth
+            st.active[lane] = 1
+            torch.cuda.synchronize(self.device)
 
     def deactivate(self, lane: int) -> None:
         self.state.active[lane] = 0
