@@ -23,6 +23,7 @@ def main(argv=None) -> int:
     ap.add_argument("--shapes", default=DEFAULT_SHAPES)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--no-library", action="store_true", help="skip the library GEMM (profiling runs)")
+    ap.add_argument("--variant", type=int, default=0, help="0 auto, 1 one 128x128 tile per CTA, 2 persistent 128x256 kernel")
     ap.add_argument("--out", type=Path)
     args = ap.parse_args(argv)
 
@@ -32,6 +33,7 @@ def main(argv=None) -> int:
     from glm_tpu_b200.ops import native
 
     build()
+    native.set_gemm_variant(args.variant)
     dev = torch.device("cuda", 0)
     peaks_file = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
     peak = json.loads(peaks_file.read_text())["bf16_tflops"] if peaks_file.exists() else 1590.0
@@ -52,7 +54,7 @@ def main(argv=None) -> int:
             out.append(a.elapsed_time(b))
         return min(out), statistics.median(out)
 
-    lines = [f"bf16 GEMM C[M,N] = A[M,K] . B[N,K]^T, fp32 accumulate; library peak (measured burst) {peak:.0f} TFLOP/s; L2 flushed between runs",
+    lines = [f"bf16 GEMM C[M,N] = A[M,K] . B[N,K]^T, fp32 accumulate; kernel variant {args.variant} (0 = chosen by size); library peak (measured burst) {peak:.0f} TFLOP/s; L2 flushed between runs",
              "", "| M x N x K | tcgen05 best us | median us | TFLOP/s (best) | of measured library peak | library best us | library TFLOP/s | max abs diff |",
              "|---|---|---|---|---|---|---|---|"]
     for shape in args.shapes.split(","):

@@ -19,9 +19,7 @@
 // Replaces reference `glm_tpu/kernels/fp8_grouped_matmul/panel_kernel.py:31-153` (prefill expert panels, after the
 // load-time style decode of the FP8 tables to bf16) and the prefill projections of `layers/linear.py:89-128`.
 #include "common.cuh"
-
-#include <cuda.h>
-#include <mutex>
+#include "tcgen05.cuh"
 
 #define TC_BM 128
 #define TC_BN 128
@@ -32,66 +30,8 @@
 #define TC_TMEM_COLS 128
 #define TC_STAGE_BYTES ((TC_BM + TC_BN) * TC_BK * 2)
 #define TC_SMEM_BYTES (TC_STAGES * TC_STAGE_BYTES + 1024 + 256)
-#define TC_WAIT_LIMIT 4000000u
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-// Bounded parity wait.  Returns false when the limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-    const uint32_t addr = smem_u32(bar);
-    for (uint32_t i = 0; i < TC_WAIT_LIMIT; ++i) {
-        uint32_t done;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.b32 %0, 1, 0, p;\n\t}"
-            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
-        if (done) return true;
-    }
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
-}
-// K-major operand tile, 128-byte swizzle: rows are 128 bytes, 8-row groups are 1024 bytes apart.
-__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
-    return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
-}
-// kind::f16: D fp32, A and B bf16, both K-major, M = 128, N = 128.
-__device__ __forceinline__ constexpr uint32_t umma_idesc_bf16_128x128() {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TC_BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
-}
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
-          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr) : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-struct TcTile { int row0, row_end, expert, pad; };
 
 // tiles == nullptr: dense GEMM, tile t covers rows 128 t .. of `rows` rows.  out_f32: store fp32 instead of bf16.
 __global__ void __launch_bounds__(TC_THREADS, 1)
@@ -146,7 +86,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            const uint32_t idesc = umma_idesc_bf16_128x128();
+            constexpr uint32_t idesc = umma_idesc_bf16(TC_BM, TC_BN);
             bool ok = true;
             for (int kb = 0; kb < kblocks && ok; ++kb) {
                 const int s = kb % TC_STAGES;
@@ -212,35 +152,166 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 }
 
 // ===================================================================================================
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+// Persistent variant for large problems: one CTA per SM walks 128 x 256 output tiles.  The TMEM holds two
+// 256-column accumulators, so the epilogue warps drain tile i while the MMA warp already fills tile i + 1; the
+// operand ring (4 stages of 48 KB) keeps running across tile boundaries.  Tiles are visited in groups of eight
+// row-tiles by all column-tiles so that CTAs running at the same time share operand tiles in L2.
+#define T2_BN 256
+#define T2_STAGES 4
+#define T2_STAGE_BYTES ((TC_BM + T2_BN) * TC_BK * 2)
+#define T2_SMEM_BYTES (T2_STAGES * T2_STAGE_BYTES + 1024 + 256)
+#define T2_TMEM_COLS 512
+#define T2_GROUP_M 8
 
-static EncodeTiledFn encode_tiled() {
-    static EncodeTiledFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(p);
-    });
-    return fn;
+__device__ __forceinline__ void t2_tile(int t, int m_tiles, int n_blocks, int& m, int& n) {
+    const int group = T2_GROUP_M * n_blocks;
+    const int first_m = (t / group) * T2_GROUP_M;
+    const int gm = min(m_tiles - first_m, T2_GROUP_M);
+    m = first_m + (t % group) % gm;
+    n = (t % group) / gm;
 }
 
-// [rows, K] bf16 row-major (leading dimension ld elements), box 128 rows x 64 columns, 128-byte swizzle.
-static int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t K, uint64_t ld) {
-    EncodeTiledFn fn = encode_tiled();
-    if (!fn) return 1;
-    const cuuint64_t dims[2] = {K, rows};
-    const cuuint64_t strides[1] = {ld * 2};
-    const cuuint32_t box[2] = {TC_BK, TC_BM};
-    const cuuint32_t elem[2] = {1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? 0 : 2;
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_bf16_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                                    void* __restrict__ c, int64_t ldc, int rows, int N, int K, const TcTile* __restrict__ tiles,
+                                    const int* __restrict__ n_tiles, int max_tiles, int out_f32, uint32_t* status) {
+    GLMB_PDL_PROLOGUE();
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char* ring = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(ring + T2_STAGES * T2_STAGE_BYTES);
+    uint64_t* empty_bar = full_bar + T2_STAGES;
+    uint64_t* acc_full = empty_bar + T2_STAGES;   // [2] MMA -> epilogue
+    uint64_t* acc_empty = acc_full + 2;           // [2] epilogue (4 warps) -> MMA
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    volatile uint32_t* fail_slot = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m_tiles = tiles ? min(max(*n_tiles, 0), max_tiles) : (rows + TC_BM - 1) / TC_BM;
+    const int n_blocks = (N + T2_BN - 1) / T2_BN;
+    const int total = m_tiles * n_blocks;
+    const int kblocks = (K + TC_BK - 1) / TC_BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < T2_STAGES; ++s) { mbar_init(full_bar + s, 1); mbar_init(empty_bar + s, 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(acc_full + a, 1); mbar_init(acc_empty + a, 4); }
+        *fail_slot = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(T2_TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t g = 0;  // k-blocks issued so far, across tiles
+            for (int t = blockIdx.x; t < total && !*fail_slot; t += gridDim.x) {
+                int m, n;
+                t2_tile(t, m_tiles, n_blocks, m, n);
+                const int row0 = tiles ? tiles[m].row0 : m * TC_BM;
+                const int b_row = (tiles ? tiles[m].expert : 0) * N + n * T2_BN;
+                for (int kb = 0; kb < kblocks; ++kb, ++g) {
+                    const uint32_t s = g % T2_STAGES, lap = g / T2_STAGES;
+                    if (lap > 0 && !mbar_wait(empty_bar + s, (lap - 1) & 1)) { *fail_slot = 1; break; }
+                    unsigned char* a_dst = ring + s * T2_STAGE_BYTES;
+                    unsigned char* b_dst = a_dst + TC_BM * TC_BK * 2;
+                    mbar_expect_tx(full_bar + s, T2_STAGE_BYTES);
+                    tma_load_2d(a_dst, &map_a, full_bar + s, kb * TC_BK, row0);
+                    tma_load_2d(b_dst, &map_b, full_bar + s, kb * TC_BK, b_row);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_bf16(TC_BM, T2_BN);
+            uint32_t g = 0, i = 0;
+            for (int t = blockIdx.x; t < total && !*fail_slot; t += gridDim.x, ++i) {
+                const uint32_t acc = i & 1, use = i >> 1;
+                if (use > 0 && !mbar_wait(acc_empty + acc, (use - 1) & 1)) { *fail_slot = 1; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t tmem_d = tmem_base + acc * T2_BN;
+                bool ok = true;
+                for (int kb = 0; kb < kblocks; ++kb, ++g) {
+                    const uint32_t s = g % T2_STAGES, lap = g / T2_STAGES;
+                    if (!mbar_wait(full_bar + s, lap & 1)) { *fail_slot = 1; ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t a_addr = smem_u32(ring + s * T2_STAGE_BYTES);
+                    const uint32_t b_addr = a_addr + TC_BM * TC_BK * 2;
+#pragma unroll
+                    for (int k = 0; k < TC_BK / TC_UMMA_K; ++k)
+                        umma_bf16(tmem_d, umma_desc_sw128(a_addr + k * TC_UMMA_K * 2), umma_desc_sw128(b_addr + k * TC_UMMA_K * 2), idesc,
+                                  (kb > 0 || k > 0) ? 1u : 0u);
+                    umma_commit(empty_bar + s);
+                }
+                umma_commit(acc_full + acc);  // complete, or abandoned after a timeout: either way release the epilogue
+                if (!ok) break;
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        uint32_t i = 0;
+        for (int t = blockIdx.x; t < total; t += gridDim.x, ++i) {
+            const uint32_t acc = i & 1, use = i >> 1;
+            const bool ok = mbar_wait(acc_full + acc, use & 1);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (!ok || *fail_slot) {
+                if (lane == 0) { *fail_slot = 1; raise_status(status, GLMB_STATUS_WAIT_TIMEOUT); }
+                break;
+            }
+            int m, n;
+            t2_tile(t, m_tiles, n_blocks, m, n);
+            const int row0 = tiles ? tiles[m].row0 : m * TC_BM;
+            const int row_end = tiles ? tiles[m].row_end : rows;
+            const int row = row0 + quarter * 32 + lane;
+            const int n0 = n * T2_BN;
+#pragma unroll 2
+            for (int cb = 0; cb < T2_BN / 32; ++cb) {
+                uint32_t v[32];
+                tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * T2_BN + cb * 32, v);
+                const int col = n0 + cb * 32;
+                if (row < row_end && col < N) {
+                    if (out_f32) {
+                        float* dst = reinterpret_cast<float*>(c) + (int64_t)row * ldc + col;
+#pragma unroll
+                        for (int e = 0; e < 32; e += 4)
+                            if (col + e < N)
+                                *reinterpret_cast<float4*>(dst + e) = make_float4(__uint_as_float(v[e]), __uint_as_float(v[e + 1]),
+                                                                                  __uint_as_float(v[e + 2]), __uint_as_float(v[e + 3]));
+                    } else {
+                        bf16* dst = reinterpret_cast<bf16*>(c) + (int64_t)row * ldc + col;
+#pragma unroll
+                        for (int e = 0; e < 32; e += 8)
+                            if (col + e < N) {
+                                uint4 o;
+                                o.x = pack_bf16(__uint_as_float(v[e]), __uint_as_float(v[e + 1]));
+                                o.y = pack_bf16(__uint_as_float(v[e + 2]), __uint_as_float(v[e + 3]));
+                                o.z = pack_bf16(__uint_as_float(v[e + 4]), __uint_as_float(v[e + 5]));
+                                o.w = pack_bf16(__uint_as_float(v[e + 6]), __uint_as_float(v[e + 7]));
+                                *reinterpret_cast<uint4*>(dst + e) = o;
+                            }
+                    }
+                }
+            }
+            // this warp's quarter of the accumulator has been read: hand it back to the MMA warp
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty + acc);
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(T2_TMEM_COLS) : "memory");
+    }
 }
+
+// ===================================================================================================
+static int g_gemm_variant = 0;
 
 // a [rows, K] bf16 (lda), b [experts * N, K] bf16 (ldb), c [rows, N] bf16 or fp32 (ldc).  K % 8 == 0; a, b 16-byte
 // aligned with lda, ldb multiples of 8.  tiles / n_tiles: device arrays for grouped mode (max_tiles entries) or NULL.
@@ -250,17 +321,37 @@ GLMB_API int glmb_gemm_bf16_tcgen05(const void* a, int64_t lda, const void* b, i
     if (rows < 1 || N < 8 || (N & 7) || K < 8 || (K & 7) || (lda & 7) || (ldb & 7) || (ldc & (out_f32 ? 3 : 7)) || experts < 1) return 1;
     if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15) || (reinterpret_cast<uintptr_t>(c) & 15)) return 1;
     CUtensorMap map_a, map_b;
+    const int m_tiles = tiles ? max_tiles : ceil_div(rows, TC_BM);
+    static int sm_count = 0;
+    if (!sm_count) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count < 1) sm_count = 148;
+    }
+    // Problems of at least 64 tiles of 128 x 256 run the persistent kernel (measured faster from there on); smaller ones keep 128 x 128 tiles,
+    // which give twice as many CTAs to spread over the SMs.
+    const int total2 = m_tiles * ceil_div(N, T2_BN);
+    const bool persistent = g_gemm_variant == 2 || (g_gemm_variant == 0 && total2 >= 64);
     if (make_map(&map_a, a, (uint64_t)rows, (uint64_t)K, (uint64_t)lda)) return 3;
-    if (make_map(&map_b, b, (uint64_t)experts * N, (uint64_t)K, (uint64_t)ldb)) return 3;
+    if (make_map(&map_b, b, (uint64_t)experts * N, (uint64_t)K, (uint64_t)ldb, persistent ? T2_BN : TC_BN)) return 3;
     static bool attr_set = false;
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(gemm_bf16_tcgen05_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T2_SMEM_BYTES);
         if (e != cudaSuccess) return (int)e;
         attr_set = true;
     }
-    const int tile_rows = tiles ? max_tiles : ceil_div(rows, TC_BM);
-    dim3 grid(ceil_div(N, TC_BN), tile_rows);
+    if (persistent) {
+        GLMB_LAUNCH(gemm_bf16_tcgen05_persistent_kernel, dim3(total2 < sm_count ? total2 : sm_count), TC_THREADS, T2_SMEM_BYTES,
+                    (cudaStream_t)stream, map_a, map_b, c, ldc, rows, N, K, (const TcTile*)tiles, n_tiles, max_tiles, out_f32, status);
+        return (int)cudaGetLastError();
+    }
+    dim3 grid(ceil_div(N, TC_BN), m_tiles);
     GLMB_LAUNCH(gemm_bf16_tcgen05_kernel, grid, TC_THREADS, TC_SMEM_BYTES, (cudaStream_t)stream, map_a, map_b, c, ldc, rows, N, K,
                 (const TcTile*)tiles, n_tiles, out_f32, status);
     return (int)cudaGetLastError();
 }
+
+// 0: choose by problem size; 1: always 128 x 128 tiles, one per CTA; 2: always the persistent 128 x 256 kernel.
+GLMB_API void glmb_set_gemm_variant(int variant) { g_gemm_variant = variant; }

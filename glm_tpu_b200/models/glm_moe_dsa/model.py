@@ -132,6 +132,14 @@ class Workspace:
         self.logits = bf(rows, lay.vocab_local)
         self.kv_new = bf(rows, W)
         self.idx_key_new = bf(rows, D)
+        self._sorted = None
+
+    def sorted_buffers(self, routes: int, H: int, I: int):
+        """Expert-sorted activations and SwiGLU outputs of the grouped (prefill) expert GEMM, allocated on first use."""
+        if self._sorted is None or self._sorted[0].shape[0] < routes:
+            dev = self.residual.device
+            self._sorted = (torch.empty((routes, H), dtype=torch.bfloat16, device=dev), torch.empty((routes, I), dtype=torch.bfloat16, device=dev))
+        return self._sorted[0][:routes], self._sorted[1][:routes]
 
 
 class GlmMoeDsaModel:
@@ -382,14 +390,24 @@ class GlmMoeDsaModel:
         if self.trace is not None:
             self.trace.setdefault("topk_ids", {})[layer] = ws.topk_ids[:rows].clone()
             self.trace.setdefault("topk_w", {})[layer] = ws.topk_w[:rows].clone()
-        if decode:
-            tile_expert, tile_routes, n_tiles, tiles, rt = ws.topk_ids, None, None, rows * tk, 1
+        if not decode and rows * tk >= 128 and H % 16 == 0 and I % 16 == 0:
+            # many rows: expert-sorted routes through the tcgen05 grouped GEMM (FP8 decoded inside the kernel)
+            tiles_t, n_tiles, perm = self._route_tiles128(ws.topk_ids[:rows], ebase, el)
+            xs, acts = ws.sorted_buffers(rows * tk, H, I)
+            native.gather_rows(x, perm, tk, xs)
+            native.moe_grouped_fp8w(xs, lw.exp_gate_bits, lw.exp_up_bits, lw.exp_gate_scale, lw.exp_up_scale, tiles_t, n_tiles, 0, acts,
+                                    status=self.peer.status_ptr)
+            native.moe_grouped_fp8w(acts, lw.exp_down_bits, None, lw.exp_down_scale, None, tiles_t, n_tiles, 1, ws.dw, perm=perm,
+                                    route_weight=ws.topk_w, status=self.peer.status_ptr)
         else:
-            tile_expert, tile_routes, n_tiles, tiles, rt = self._route_tiles(ws.topk_ids[:rows], E)
-        native.moe_gateup_fp8(x, tk, tile_expert, tile_routes, n_tiles, tiles, rt, lw.exp_gate_bits, lw.exp_up_bits, lw.exp_gate_scale,
-                              lw.exp_up_scale, ebase, ws.act)
-        native.moe_down_fp8(ws.act, ws.topk_w, tile_expert, tile_routes, n_tiles, tiles, rt, lw.exp_down_bits, lw.exp_down_scale, ebase,
-                            ws.dw)
+            if decode:
+                tile_expert, tile_routes, n_tiles, tiles, rt = ws.topk_ids, None, None, rows * tk, 1
+            else:
+                tile_expert, tile_routes, n_tiles, tiles, rt = self._route_tiles(ws.topk_ids[:rows], E)
+            native.moe_gateup_fp8(x, tk, tile_expert, tile_routes, n_tiles, tiles, rt, lw.exp_gate_bits, lw.exp_up_bits,
+                                  lw.exp_gate_scale, lw.exp_up_scale, ebase, ws.act)
+            native.moe_down_fp8(ws.act, ws.topk_w, tile_expert, tile_routes, n_tiles, tiles, rt, lw.exp_down_bits, lw.exp_down_scale,
+                                ebase, ws.dw)
         if decode:
             native.skinny_bf16_swiglu(x, lw.shared_gate, lw.shared_up, ws.act_shared)
             native.skinny_bf16(ws.act_shared[:rows], lw.shared_down, ws.partial, native.SK_OUT_F32)
@@ -408,6 +426,34 @@ class GlmMoeDsaModel:
             self._allreduce_rows(both)
             routed = (both[0].to(torch.bfloat16).float() * g.routed_scaling_factor).to(torch.bfloat16).float()
             ws.update[:rows] = (routed + both[1].to(torch.bfloat16).float()).to(torch.bfloat16)
+
+    def _route_tiles128(self, topk_ids: torch.Tensor, ebase: int, el: int):
+        """Sort this GPU's routes by expert and cut them into 128-route tiles (device-side, no host sync).
+
+        Returns ``tiles [max_tiles, 4]`` (first sorted row, end row, local expert, 0), ``n_tiles [1]`` and
+        ``perm [routes]`` (sorted position -> route id ``row * top_k + slot``; -1 past this GPU's routes).
+        """
+        dev = topk_ids.device
+        ids = topk_ids.reshape(-1).long() - ebase
+        P = ids.numel()
+        key = torch.where((ids >= 0) & (ids < el), ids, torch.full_like(ids, el))  # other GPUs' routes sort last
+        order = torch.argsort(key, stable=True)
+        counts = torch.bincount(key, minlength=el + 1)[:el]
+        n_local = counts.sum()
+        perm = torch.where(torch.arange(P, device=dev) < n_local, order, torch.full_like(order, -1)).to(torch.int32).contiguous()
+        tiles_per = (counts + 127) // 128
+        tile_end = torch.cumsum(tiles_per, 0)
+        route_start = torch.cumsum(counts, 0) - counts
+        max_tiles = P // 128 + el
+        t = torch.arange(max_tiles, device=dev)
+        expert = torch.searchsorted(tile_end, t, right=True).clamp(max=el - 1)
+        within = t - (tile_end[expert] - tiles_per[expert])
+        valid = t < tile_end[-1]
+        row0 = route_start[expert] + within * 128
+        row_end = route_start[expert] + counts[expert]
+        zero = torch.zeros_like(t)
+        tiles = torch.stack([torch.where(valid, row0, zero), torch.where(valid, row_end, zero), torch.where(valid, expert, zero), zero], dim=1)
+        return tiles.to(torch.int32).contiguous(), tile_end[-1:].to(torch.int32).contiguous(), perm
 
     def _route_tiles(self, topk_ids: torch.Tensor, E: int):
         """Group routes by expert into tiles of 8 (device-side, no host sync)."""

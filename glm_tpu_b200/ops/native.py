@@ -205,6 +205,26 @@ def moe_down_fp8(act, route_weight, tile_expert, tile_routes, n_tiles, tiles, rt
     )
 
 
+def moe_grouped_fp8w(a_sorted, w0, w1, s0, s1, tiles, n_tiles, mode, out, *, perm=None, route_weight=None, status=None):
+    """Grouped expert GEMM over expert-sorted routes with in-kernel FP8 decode (tcgen05); see ``glmb_moe_grouped_fp8w``.
+
+    mode 0: ``out[sorted, I] = bf16(silu(a @ w0[e].T) * (a @ w1[e].T))``; mode 1: ``out[perm[sorted], H] = bf16(bf16(a @ w0[e].T) *
+    bf16(route_weight))``.  ``tiles`` is ``[max_tiles, 4]`` int32 (first sorted row, end row, local expert, 0).
+    """
+    experts, N, K = w0.shape
+    _check(
+        lib().glmb_moe_grouped_fp8w(_p(a_sorted), a_sorted.shape[0], _p(w0), _p(w1), _p(s0), _p(s1), experts, N, K, _p(tiles),
+                                    _p(n_tiles), tiles.shape[0], mode, _p(perm), _p(route_weight), _p(out), _p(status), _stream()),
+        "moe_grouped_fp8w",
+    )
+
+
+def gather_rows(src, idx, divisor, dst):
+    """``dst[i] = src[idx[i] // divisor]`` (a row of zeros where ``idx[i] < 0``); bf16 rows, width a multiple of 8."""
+    _check(lib().glmb_gather_rows(_p(src), C.c_int64(src.stride(0)), _p(idx), divisor, _p(dst), dst.shape[0], dst.shape[1], _stream()),
+           "gather_rows")
+
+
 def moe_combine(dw, topk_ids, shared_partial, rows, top_k, H, expert_base, experts_local, scale, plain, out, routed_partial=None,
                 comm=None, channel=CH_MLP):
     _check(
@@ -346,6 +366,11 @@ def fill_uniform_f32(out, seed, lo, hi):
 
 
 # ----------------------------------------------------------------------------- tcgen05 GEMM
+def set_gemm_variant(variant: int) -> None:
+    """0: pick by problem size (default); 1: one 128x128 tile per CTA; 2: the persistent 128x256 kernel."""
+    lib().glmb_set_gemm_variant(int(variant))
+
+
 def gemm_bf16_tc(a, b, out, *, experts=1, tiles=None, n_tiles=None, status=None):
     """``out[rows, N] = a[rows, K] @ b[N, K].T`` on the tcgen05 tensor cores (bf16 in, fp32 accumulate).
 

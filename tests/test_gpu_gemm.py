@@ -7,9 +7,17 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
-@pytest.mark.parametrize("rows,N,K", [(128, 128, 64), (300, 256, 512), (1000, 384, 6144), (64, 2048, 200)])
+@pytest.fixture(params=[1, 2], ids=["tile128x128", "persistent128x256"])
+def variant(request, native_lib):
+    """Both kernels behind the one entry point: 128x128 tile per CTA, and the persistent 128x256 kernel."""
+    native_lib.set_gemm_variant(request.param)
+    yield request.param
+    native_lib.set_gemm_variant(0)
+
+
+@pytest.mark.parametrize("rows,N,K", [(128, 128, 64), (300, 256, 512), (1000, 384, 6144), (64, 2048, 200), (2500, 1288, 136)])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
-def test_dense_gemm(native_lib, rows, N, K, out_dtype):
+def test_dense_gemm(native_lib, variant, rows, N, K, out_dtype):
     n = native_lib
     torch.manual_seed(rows + N + K)
     a = (torch.randn(rows, K, device=DEV) * 0.5).to(torch.bfloat16)
@@ -24,10 +32,11 @@ def test_dense_gemm(native_lib, rows, N, K, out_dtype):
     assert torch.allclose(out.float(), ref, rtol=tol, atol=tol * float(ref.abs().max())), err
 
 
-def test_grouped_gemm(native_lib):
+@pytest.mark.parametrize("N", [256, 328])
+def test_grouped_gemm(native_lib, variant, N):
     n = native_lib
     torch.manual_seed(5)
-    E, N, K = 4, 256, 512
+    E, K = 4, 512
     counts = [130, 0, 257, 5]
     rows = sum(counts)
     a = (torch.randn(rows, K, device=DEV) * 0.5).to(torch.bfloat16)
@@ -59,6 +68,7 @@ def test_gemm_throughput_is_tensor_core_class(native_lib):
     a = torch.randn(M, K, device=DEV).to(torch.bfloat16)
     b = torch.randn(N, K, device=DEV).to(torch.bfloat16)
     out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    n.set_gemm_variant(0)
     for _ in range(2):
         n.gemm_bf16_tc(a, b, out)
     torch.cuda.synchronize()
@@ -71,3 +81,18 @@ def test_gemm_throughput_is_tensor_core_class(native_lib):
     tflops = 5 * 2 * M * N * K / (s.elapsed_time(e) * 1e-3) / 1e12
     print(f"tcgen05 gemm 8192^3: {tflops:.0f} TFLOP/s")
     assert tflops > 150
+
+
+def test_many_tiles_per_cta(native_lib, variant):
+    """More tiles than SMs: the persistent kernel reuses both accumulators and wraps the operand ring many times."""
+    n = native_lib
+    torch.manual_seed(11)
+    rows, N, K = 4096, 2560, 320
+    a = (torch.randn(rows, K, device=DEV) * 0.5).to(torch.bfloat16)
+    b = (torch.randn(N, K, device=DEV) * 0.5).to(torch.bfloat16)
+    out = torch.full((rows, N), float("nan"), dtype=torch.float32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    n.gemm_bf16_tc(a, b, out, status=status)
+    ref = a.float() @ b.float().T
+    assert int(status.cpu()[0]) == 0
+    assert torch.allclose(out, ref, rtol=1e-4, atol=1e-4 * float(ref.abs().max()))

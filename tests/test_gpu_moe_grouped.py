@@ -1,0 +1,75 @@
+"""The grouped expert GEMM with in-kernel FP8 decode (tcgen05) against a plain fp32 PyTorch restatement (B200 only)."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _tiles(local_ids, el):
+    """Host restatement of the route sort: tiles, n_tiles, perm for routes whose local expert id is in [0, el)."""
+    P = local_ids.numel()
+    key = torch.where((local_ids >= 0) & (local_ids < el), local_ids, torch.full_like(local_ids, el))
+    order = torch.argsort(key, stable=True)
+    counts = torch.bincount(key, minlength=el + 1)[:el]
+    n_local = int(counts.sum())
+    perm = torch.where(torch.arange(P) < n_local, order, torch.full_like(order, -1)).to(torch.int32)
+    tiles, start = [], 0
+    for e in range(el):
+        c = int(counts[e])
+        for r0 in range(start, start + c, 128):
+            tiles.append([r0, start + c, e, 0])
+        start += c
+    n = len(tiles)
+    tiles += [[0, 0, 0, 0]] * 5
+    return torch.tensor(tiles, dtype=torch.int32), torch.tensor([n], dtype=torch.int32), perm
+
+
+@pytest.mark.parametrize("rows,tk,E,el,H,I", [(64, 4, 8, 8, 512, 256), (300, 8, 16, 6, 1024, 384), (96, 8, 8, 4, 6144, 2048)])
+def test_grouped_fp8_experts(native_lib, rows, tk, E, el, H, I):
+    from glm_tpu_b200.models.glm_moe_dsa.weights import quantize_fp8
+    from glm_tpu_b200.oracle.contract import dequantize_fp8
+
+    n = native_lib
+    gen = torch.Generator().manual_seed(rows + H)
+    x = (torch.randn(rows, H, generator=gen) * 0.5).to(torch.bfloat16)
+    ids = torch.stack([torch.randperm(E, generator=gen)[:tk] for _ in range(rows)])  # [rows, tk], distinct per row
+    ids[0] = ids[1]  # a repeated pattern, so one expert gets adjacent routes
+    weight = torch.rand(rows, tk, generator=gen) + 0.1
+    wg, sg = quantize_fp8(torch.randn(el, I, H, generator=gen) * 0.05, (128, 128), gen)
+    wu, su = quantize_fp8(torch.randn(el, I, H, generator=gen) * 0.05, (128, 128), gen)
+    wd, sd = quantize_fp8(torch.randn(el, H, I, generator=gen) * 0.05, (128, 128), gen)
+    tiles, n_tiles, perm = _tiles(ids.reshape(-1).long(), el)
+    P = rows * tk
+    xs = torch.zeros(P, H, dtype=torch.bfloat16, device=DEV)
+    acts = torch.full((P, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    dw = torch.full((P, H), float("nan"), dtype=torch.bfloat16, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    d = lambda t: t.to(DEV).contiguous()  # noqa: E731
+    perm_d, tiles_d, n_d = d(perm), d(tiles), d(n_tiles)
+    n.gather_rows(d(x), perm_d, tk, xs)
+    n.moe_grouped_fp8w(xs, d(wg), d(wu), d(sg), d(su), tiles_d, n_d, 0, acts, status=status)
+    n.moe_grouped_fp8w(acts, d(wd), None, d(sd), None, tiles_d, n_d, 1, dw, perm=perm_d, route_weight=d(weight), status=status)
+    torch.cuda.synchronize()
+    assert int(status.cpu()[0]) == 0
+    bf = lambda t: t.to(torch.bfloat16).float()  # noqa: E731
+    dq = [dequantize_fp8(w, s, (128, 128)).float() for w, s in ((wg, sg), (wu, su), (wd, sd))]
+    got_x, got_act, got_dw = xs.cpu().float(), acts.cpu().float(), dw.cpu().float()
+    checked = 0
+    for pos in range(P):
+        route = int(perm[pos])
+        if route < 0:
+            continue
+        r, e = route // tk, int(ids.reshape(-1)[route])
+        assert torch.equal(got_x[pos], x[r].float())
+        g, u = bf(x[r].float() @ dq[0][e].T), bf(x[r].float() @ dq[1][e].T)
+        act = bf(g * torch.sigmoid(g) * u)
+        assert torch.allclose(got_act[pos], act, rtol=2**-6, atol=2**-8 * float(act.abs().max())), (pos, route)
+        down = bf(bf(got_act[pos] @ dq[2][e].T) * bf(weight.reshape(-1)[route]))
+        assert torch.allclose(got_dw[route], down, rtol=2**-6, atol=2**-8 * float(down.abs().max())), (pos, route)
+        checked += 1
+    assert checked == int((ids < el).sum())
+    # routes of experts this GPU does not hold are never written
+    foreign = (ids.reshape(-1) >= el).nonzero().flatten()
+    assert bool(torch.isnan(got_dw[foreign]).all())
