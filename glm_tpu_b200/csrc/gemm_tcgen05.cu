@@ -19,6 +19,7 @@
 // Replaces reference `glm_tpu/kernels/fp8_grouped_matmul/panel_kernel.py:31-153` (prefill expert panels, after the
 // load-time style decode of the FP8 tables to bf16) and the prefill projections of `layers/linear.py:89-128`.
 #include "common.cuh"
+#include "peer.cuh"
 #include "tcgen05.cuh"
 
 #define TC_BM 128
@@ -163,6 +164,21 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 #define T2_TMEM_COLS 512
 #define T2_GROUP_M 8
 
+// Fused all-reduce of K-split partial products over NVLink peer memory (enabled != 0; dense mode, bf16 output).
+// Every rank runs the same GEMM on its K-slice.  Tile t belongs to rank t % world: the other ranks store their
+// fp32 partial tile into the owner's staging (slot (t / world) * world + source rank) and raise a flag; the owner's
+// CTA waits for the world - 1 flags, adds the partials to its own accumulator in rank order, rounds to bf16 and
+// stores the tile into every rank's output buffer (the same offset in every staging buffer).  The last CTA to
+// finish signals `sig` to all ranks; the consumer waits for that signal from every rank before it reads.
+struct GemmAllReduce {
+    int enabled;
+    int sig;
+    int64_t part_offset;  // byte offset of the partial-tile slots inside every staging buffer
+    int64_t out_offset;   // byte offset of the bf16 output [rows, N] inside every staging buffer
+    PeerComm comm;
+};
+#define T2_TILE_FLOATS (TC_BM * T2_BN)
+
 __device__ __forceinline__ void t2_tile(int t, int m_tiles, int n_blocks, int& m, int& n) {
     const int group = T2_GROUP_M * n_blocks;
     const int first_m = (t / group) * T2_GROUP_M;
@@ -174,7 +190,7 @@ __device__ __forceinline__ void t2_tile(int t, int m_tiles, int n_blocks, int& m
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_bf16_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                                     void* __restrict__ c, int64_t ldc, int rows, int N, int K, const TcTile* __restrict__ tiles,
-                                    const int* __restrict__ n_tiles, int max_tiles, int out_f32, uint32_t* status) {
+                                    const int* __restrict__ n_tiles, int max_tiles, int out_f32, uint32_t* status, GemmAllReduce ar) {
     GLMB_PDL_PROLOGUE();
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* ring = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -186,6 +202,8 @@ gemm_bf16_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, c
     volatile uint32_t* fail_slot = tmem_slot + 1;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // every CTA reads the round number before any CTA can finish, and the last CTA to finish advances it
+    const uint32_t ar_epoch = ar.enabled ? ar.comm.seq[GLMB_SEQ_GEMM] + 1 : 0;
     const int m_tiles = tiles ? min(max(*n_tiles, 0), max_tiles) : (rows + TC_BM - 1) / TC_BM;
     const int n_blocks = (N + T2_BN - 1) / T2_BN;
     const int total = m_tiles * n_blocks;
@@ -268,12 +286,74 @@ gemm_bf16_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, c
             const int row_end = tiles ? tiles[m].row_end : rows;
             const int row = row0 + quarter * 32 + lane;
             const int n0 = n * T2_BN;
+            if (ar.enabled) {
+                const PeerComm& pc = ar.comm;
+                const int owner = t % pc.world;
+                const int64_t slot = (int64_t)(t / pc.world) * pc.world;
+                const int trow = quarter * 32 + lane;  // row inside the tile
+                const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * T2_BN;
+                if (owner != pc.rank) {
+                    float* dst = reinterpret_cast<float*>(pc.data[owner] + ar.part_offset) + (slot + pc.rank) * T2_TILE_FLOATS + trow * T2_BN;
+#pragma unroll 1
+                    for (int cb = 0; cb < T2_BN / 32; ++cb) {
+                        uint32_t v[32];
+                        tmem_ld32(lane_addr + cb * 32, v);
+#pragma unroll
+                        for (int e = 0; e < 32; e += 4)
+                            *reinterpret_cast<uint4*>(dst + cb * 32 + e) = make_uint4(v[e], v[e + 1], v[e + 2], v[e + 3]);
+                    }
+                    __threadfence_system();
+                    asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
+                    if (warp == 2 && lane == 0)
+                        st_release_sys(pc.flags[owner] + GLMB_FLAG_GEMM_BASE + (size_t)t * GLMB_MAX_WORLD + pc.rank, ar_epoch);
+                } else {
+                    if (warp == 2 && lane < pc.world && lane != pc.rank) {
+                        if (!wait_flag_reached(pc.flags[pc.rank] + GLMB_FLAG_GEMM_BASE + (size_t)t * GLMB_MAX_WORLD + lane, ar_epoch, pc.wait_limit))
+                            raise_status(status, GLMB_STATUS_WAIT_TIMEOUT);
+                    }
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    const float* inbox = reinterpret_cast<const float*>(pc.data[pc.rank] + ar.part_offset) + slot * T2_TILE_FLOATS + trow * T2_BN;
+#pragma unroll 1
+                    for (int cb = 0; cb < T2_BN / 32; ++cb) {
+                        uint32_t v[32];
+                        tmem_ld32(lane_addr + cb * 32, v);
+                        const int col = n0 + cb * 32;
+                        if (row >= rows || col >= N) continue;
+#pragma unroll
+                        for (int e = 0; e < 32; e += 8) {
+                            if (col + e >= N) break;
+                            float sum[8];
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) sum[i] = 0.f;
+                            for (int p = 0; p < pc.world; ++p) {  // rank order: the same sum on every run
+                                if (p == pc.rank) {
+#pragma unroll
+                                    for (int i = 0; i < 8; ++i) sum[i] += __uint_as_float(v[e + i]);
+                                } else {
+                                    const float* src = inbox + (int64_t)p * T2_TILE_FLOATS + cb * 32 + e;
+                                    const uint4 lo = ld_sys_u4(src), hi = ld_sys_u4(src + 4);
+                                    sum[0] += __uint_as_float(lo.x); sum[1] += __uint_as_float(lo.y);
+                                    sum[2] += __uint_as_float(lo.z); sum[3] += __uint_as_float(lo.w);
+                                    sum[4] += __uint_as_float(hi.x); sum[5] += __uint_as_float(hi.y);
+                                    sum[6] += __uint_as_float(hi.z); sum[7] += __uint_as_float(hi.w);
+                                }
+                            }
+                            const uint4 o = make_uint4(pack_bf16(sum[0], sum[1]), pack_bf16(sum[2], sum[3]), pack_bf16(sum[4], sum[5]),
+                                                       pack_bf16(sum[6], sum[7]));
+                            const int64_t at = (int64_t)row * N + col + e;
+                            for (int p = 0; p < pc.world; ++p)
+                                *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(pc.data[p] + ar.out_offset) + at) = o;
+                        }
+                    }
+                }
+            } else
 #pragma unroll 2
             for (int cb = 0; cb < T2_BN / 32; ++cb) {
                 uint32_t v[32];
                 tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * T2_BN + cb * 32, v);
                 const int col = n0 + cb * 32;
                 if (row < row_end && col < N) {
+
                     if (out_f32) {
                         float* dst = reinterpret_cast<float*>(c) + (int64_t)row * ldc + col;
 #pragma unroll
@@ -308,10 +388,33 @@ gemm_bf16_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, c
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(T2_TMEM_COLS) : "memory");
     }
+    if (ar.enabled) {
+        __threadfence_system();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const PeerComm& pc = ar.comm;
+            uint32_t* done = pc.seq + GLMB_SEQ_DONE_BASE + ar.sig;
+            if (atomicAdd(done, 1u) == gridDim.x - 1) {
+                __threadfence_system();
+                atomicExch(done, 0u);
+                pc.seq[GLMB_SEQ_GEMM] = ar_epoch;
+                const uint32_t e = pc.seq[GLMB_SEQ_SIG_BASE + ar.sig] + 1;
+                pc.seq[GLMB_SEQ_SIG_BASE + ar.sig] = e;
+                for (int p = 0; p < pc.world; ++p)
+                    st_release_sys(pc.flags[p] + GLMB_FLAG_SIG_BASE + ar.sig * GLMB_MAX_WORLD + pc.rank, e);
+            }
+        }
+    }
 }
 
 // ===================================================================================================
 static int g_gemm_variant = 0;
+
+static GemmAllReduce no_allreduce() {
+    GemmAllReduce ar;
+    memset(&ar, 0, sizeof(ar));
+    return ar;
+}
 
 // a [rows, K] bf16 (lda), b [experts * N, K] bf16 (ldb), c [rows, N] bf16 or fp32 (ldc).  K % 8 == 0; a, b 16-byte
 // aligned with lda, ldb multiples of 8.  tiles / n_tiles: device arrays for grouped mode (max_tiles entries) or NULL.
@@ -344,7 +447,7 @@ GLMB_API int glmb_gemm_bf16_tcgen05(const void* a, int64_t lda, const void* b, i
     }
     if (persistent) {
         GLMB_LAUNCH(gemm_bf16_tcgen05_persistent_kernel, dim3(total2 < sm_count ? total2 : sm_count), TC_THREADS, T2_SMEM_BYTES,
-                    (cudaStream_t)stream, map_a, map_b, c, ldc, rows, N, K, (const TcTile*)tiles, n_tiles, max_tiles, out_f32, status);
+                    (cudaStream_t)stream, map_a, map_b, c, ldc, rows, N, K, (const TcTile*)tiles, n_tiles, max_tiles, out_f32, status, no_allreduce());
         return (int)cudaGetLastError();
     }
     dim3 grid(ceil_div(N, TC_BN), m_tiles);
@@ -355,3 +458,44 @@ GLMB_API int glmb_gemm_bf16_tcgen05(const void* a, int64_t lda, const void* b, i
 
 // 0: choose by problem size; 1: always 128 x 128 tiles, one per CTA; 2: always the persistent 128 x 256 kernel.
 GLMB_API void glmb_set_gemm_variant(int variant) { g_gemm_variant = variant; }
+
+// out[rows, N] (bf16, at comm->data[p] + out_offset on EVERY rank p) = sum over ranks of a_r[rows, K_r] . b_r[N, K_r]^T.
+// One kernel: tcgen05 tiles, partial tiles pushed to the tile owner over NVLink, rank-ordered fp32 sum, bf16 result
+// pushed to all ranks, then signal `sig`.  The caller launches glmb_wait_signal(sig) before reading the output.
+// part_offset must leave room for ceil(tiles / world) * world slots of 128 x 256 fp32 (tiles = ceil(rows/128) * ceil(N/256)).
+GLMB_API int glmb_gemm_bf16_tcgen05_allreduce(const void* a, int64_t lda, const void* b, int64_t ldb, int rows, int N, int K,
+                                              const PeerComm* comm, int64_t part_offset, int64_t out_offset, int sig, uint32_t* status,
+                                              void* stream) {
+    if (!comm || comm->world < 2 || rows < 1 || N < 8 || (N & 7) || K < 8 || (K & 7) || (lda & 7) || (ldb & 7)) return 1;
+    if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15) || (part_offset & 15) || (out_offset & 15)) return 1;
+    const int total = ceil_div(rows, TC_BM) * ceil_div(N, T2_BN);
+    if (total > GLMB_GEMM_MAX_TILES || sig < 0 || sig >= GLMB_SIGNALS) return 2;
+    CUtensorMap map_a, map_b;
+    if (make_map(&map_a, a, (uint64_t)rows, (uint64_t)K, (uint64_t)lda)) return 3;
+    if (make_map(&map_b, b, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, T2_BN)) return 3;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tcgen05_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T2_SMEM_BYTES);
+        if (e != cudaSuccess) return (int)e;
+        attr_set = true;
+    }
+    int dev = 0, sm_count = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count < 1) sm_count = 148;
+    GemmAllReduce ar;
+    ar.enabled = 1;
+    ar.sig = sig;
+    ar.part_offset = part_offset;
+    ar.out_offset = out_offset;
+    ar.comm = *comm;
+    void* c = comm->data[comm->rank] + out_offset;
+    GLMB_LAUNCH(gemm_bf16_tcgen05_persistent_kernel, dim3(total < sm_count ? total : sm_count), TC_THREADS, T2_SMEM_BYTES, (cudaStream_t)stream,
+                map_a, map_b, c, (int64_t)N, rows, N, K, (const TcTile*)nullptr, (const int*)nullptr, 0, 0, status, ar);
+    return (int)cudaGetLastError();
+}
+
+// Bytes of partial-tile slots glmb_gemm_bf16_tcgen05_allreduce needs at part_offset.
+GLMB_API int64_t glmb_gemm_allreduce_part_bytes(int rows, int N, int world) {
+    const int64_t total = (int64_t)ceil_div(rows, TC_BM) * ceil_div(N, T2_BN);
+    return ((total + world - 1) / world) * world * (int64_t)T2_TILE_FLOATS * 4;
+}

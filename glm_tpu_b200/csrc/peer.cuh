@@ -33,11 +33,14 @@
 // Offsets (in uint32 words) inside the flag buffer and the local sequence buffer.
 #define GLMB_FLAG_AR_WORDS (GLMB_AR_CHANNELS * GLMB_AR_MAX_CTAS * GLMB_MAX_WORLD)
 #define GLMB_FLAG_SIG_BASE GLMB_FLAG_AR_WORDS
-#define GLMB_FLAG_WORDS (GLMB_FLAG_AR_WORDS + GLMB_SIGNALS * GLMB_MAX_WORLD)
+#define GLMB_GEMM_MAX_TILES 2048  // output tiles of one GEMM with a fused all-reduce: one flag per (tile, source rank)
+#define GLMB_FLAG_GEMM_BASE (GLMB_FLAG_SIG_BASE + GLMB_SIGNALS * GLMB_MAX_WORLD)
+#define GLMB_FLAG_WORDS (GLMB_FLAG_GEMM_BASE + GLMB_GEMM_MAX_TILES * GLMB_MAX_WORLD)
 #define GLMB_SEQ_AR_WORDS (GLMB_AR_CHANNELS * GLMB_AR_MAX_CTAS)
 #define GLMB_SEQ_SIG_BASE GLMB_SEQ_AR_WORDS
 #define GLMB_SEQ_DONE_BASE (GLMB_SEQ_SIG_BASE + GLMB_SIGNALS)
-#define GLMB_SEQ_WORDS (GLMB_SEQ_DONE_BASE + GLMB_SIGNALS)
+#define GLMB_SEQ_GEMM (GLMB_SEQ_DONE_BASE + GLMB_SIGNALS)  // number of fused GEMM all-reduces completed
+#define GLMB_SEQ_WORDS (GLMB_SEQ_GEMM + 1)
 // Bytes at the start of the staging buffer reserved for the all-reduce channels.
 #define GLMB_AR_BYTES ((size_t)GLMB_AR_CHANNELS * GLMB_AR_MAX_CTAS * GLMB_MAX_WORLD * GLMB_AR_SLICE * 4)
 

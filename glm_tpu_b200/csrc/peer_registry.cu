@@ -144,6 +144,19 @@ GLMB_API int glmb_peer_wait_probe(const PeerComm* comm, int sig, uint32_t bump, 
     return (int)cudaGetLastError();
 }
 
+// Consumer side of a signal as a kernel of its own: later kernels of the stream start after every rank's round of
+// `sig` has arrived (used after a GEMM with a fused all-reduce, whose consumers are ordinary kernels).
+__global__ void wait_signal_kernel(PeerComm c, int sig) {
+    GLMB_PDL_PROLOGUE();
+    cta_wait_signal(c, sig);
+}
+
+GLMB_API int glmb_wait_signal(const PeerComm* comm, int sig, void* stream) {
+    if (!comm || sig < 0 || sig >= GLMB_SIGNALS) return 1;
+    GLMB_LAUNCH(wait_signal_kernel, 1, 32, 0, (cudaStream_t)stream, *comm, sig);
+    return (int)cudaGetLastError();
+}
+
 // All-reduce self-test: every rank contributes `count` floats; result (identical on all ranks) in `out`.
 __global__ void allreduce_probe_kernel(const float* in, float* out, int count, PeerComm c, int channel) {
     GLMB_PDL_PROLOGUE();

@@ -133,6 +133,15 @@ class Workspace:
         self.kv_new = bf(rows, W)
         self.idx_key_new = bf(rows, D)
         self._sorted = None
+        # many-row workspaces on several GPUs: output and partial-tile slots of the GEMM with the fused all-reduce
+        self.r_gemm_out = self.r_gemm_part = None
+        if rows > 8 and peer.world > 1 and model.comm_mode == "fused":
+            try:
+                self.r_gemm_out = peer.region(f"{tag}.gemm_out", rows * H * 2)
+                self.r_gemm_part = peer.region(f"{tag}.gemm_part", native.gemm_allreduce_part_bytes(rows, H, peer.world))
+                self.gemm_out = peer.tensor(self.r_gemm_out, (rows, H), torch.bfloat16)
+            except MemoryError:  # staging sized without it: the caller falls back to the library all-reduce
+                self.r_gemm_out = self.r_gemm_part = None
 
     def sorted_buffers(self, routes: int, H: int, I: int):
         """Expert-sorted activations and SwiGLU outputs of the grouped (prefill) expert GEMM, allocated on first use."""
@@ -196,6 +205,17 @@ class GlmMoeDsaModel:
             native.gemm_bf16_tc(x, w, out, status=self.peer.status_ptr)
             return out
         return torch.mm(x, w.t(), out_dtype=torch.float32) if f32 else torch.mm(x, w.t())
+
+    def _mm_allreduce(self, ws: "Workspace", x: torch.Tensor, w: torch.Tensor) -> torch.Tensor | None:
+        """``bf16(sum over GPUs of x_r @ w_r.T)`` ([rows, hidden]) in one kernel: tcgen05 tiles whose epilogue exchanges the
+        partial tiles over NVLink.  None when this workspace has no staging for it or the shape does not fit."""
+        rows, K = x.shape
+        if ws.r_gemm_out is None or w.shape[0] != self.g.hidden_size or K % 8 or x.stride(1) != 1 or x.stride(0) % 8 \
+                or x.data_ptr() % 16 or w.data_ptr() % 16 or w.stride(0) % 8:
+            return None
+        native.gemm_bf16_tc_allreduce(x, w, self.peer.comm, ws.r_gemm_part.offset, ws.r_gemm_out.offset, status=self.peer.status_ptr)
+        native.wait_signal(self.peer.comm, native.SIG_GEMM)
+        return ws.gemm_out[:rows]
 
     def _linear_f32(self, x, w, out, decode: bool):
         """``out[:, :N] = x @ w.T`` in fp32."""
@@ -305,8 +325,12 @@ class GlmMoeDsaModel:
             if self.world == 1:
                 ws.attn_out[:rows] = self._mm(v, lw.w_o)
             else:
-                part = self._mm(v, lw.w_o, f32=True)
-                ws.attn_out[:rows] = self._allreduce_rows(part).to(torch.bfloat16)
+                fused_out = self._mm_allreduce(ws, v, lw.w_o)
+                if fused_out is not None:
+                    ws.attn_out[:rows] = fused_out
+                else:
+                    part = self._mm(v, lw.w_o, f32=True)
+                    ws.attn_out[:rows] = self._allreduce_rows(part).to(torch.bfloat16)
         if self.trace is not None:
             self.trace.setdefault("attn_out", {})[layer] = ws.attn_out[:rows].clone()
             self.trace.setdefault("kv_new", {})[layer] = ws.kv_new[:rows].clone()
@@ -381,7 +405,11 @@ class GlmMoeDsaModel:
                 if self.world == 1:
                     ws.update[:rows] = self._mm(act, lw.dense_down)
                 else:
-                    ws.update[:rows] = self._allreduce_rows(self._mm(act, lw.dense_down, f32=True)).to(torch.bfloat16)
+                    fused_out = self._mm_allreduce(ws, act, lw.dense_down)
+                    if fused_out is not None:
+                        ws.update[:rows] = fused_out
+                    else:
+                        ws.update[:rows] = self._allreduce_rows(self._mm(act, lw.dense_down, f32=True)).to(torch.bfloat16)
             return
         tk, I, E = g.routed_top_k, g.moe_intermediate_size, g.num_routed_experts
         el, ebase = lay.experts_local, self.rank * lay.experts_local

@@ -21,7 +21,7 @@ SK_OUT_F32, SK_OUT_BF16, SK_OUT_ALLREDUCE_BF16, SK_OUT_ARGMAX = 0, 1, 2, 3
 STATUS_WAIT_TIMEOUT, STATUS_BAD_INDEX, STATUS_NONFINITE, STATUS_BAD_SHAPE = 1, 2, 4, 8
 
 # signals (producer -> consumer exchanges) and all-reduce channels used by the model
-SIG_Q, SIG_SCORES, SIG_ATTN, SIG_SAMPLE, SIG_TEST = 0, 1, 2, 3, 15
+SIG_Q, SIG_SCORES, SIG_ATTN, SIG_SAMPLE, SIG_GEMM, SIG_TEST = 0, 1, 2, 3, 4, 15
 CH_ATTN, CH_MLP = 0, 1
 
 
@@ -366,6 +366,28 @@ def fill_uniform_f32(out, seed, lo, hi):
 
 
 # ----------------------------------------------------------------------------- tcgen05 GEMM
+def gemm_allreduce_part_bytes(rows: int, N: int, world: int) -> int:
+    fn = lib().glmb_gemm_allreduce_part_bytes
+    fn.restype = C.c_int64
+    return int(fn(rows, N, world))
+
+
+def gemm_bf16_tc_allreduce(a, b, comm, part_offset, out_offset, *, sig=SIG_GEMM, status=None):
+    """One kernel: ``sum over ranks of a_r @ b_r.T`` (tcgen05 tiles + NVLink partial exchange), bf16 result ``[rows, N]`` at
+    ``out_offset`` of every rank's staging buffer.  Follow with ``wait_signal(comm, sig)`` before reading it."""
+    rows, K = a.shape
+    N = b.shape[0]
+    _check(
+        lib().glmb_gemm_bf16_tcgen05_allreduce(_p(a), C.c_int64(a.stride(0)), _p(b), C.c_int64(b.stride(0)), rows, N, K, _comm(comm),
+                                               C.c_int64(part_offset), C.c_int64(out_offset), sig, _p(status), _stream()),
+        "gemm_bf16_tcgen05_allreduce",
+    )
+
+
+def wait_signal(comm, sig):
+    _check(lib().glmb_wait_signal(_comm(comm), sig, _stream()), "wait_signal")
+
+
 def set_gemm_variant(variant: int) -> None:
     """0: pick by problem size (default); 1: one 128x128 tile per CTA; 2: the persistent 128x256 kernel."""
     lib().glmb_set_gemm_variant(int(variant))

@@ -95,6 +95,8 @@ class GpuModelRunner:
             g = self.g
             staging_bytes = lanes * (g.attention_heads * g.kv_row_width * 2 + context_capacity * 4
                                      + self.world * self.layout.heads_local * (g.kv_lora_rank + 2) * 4 + self.world * 8) + (1 << 20)
+            if self.world > 1 and prefill_chunk > 8:  # output + partial-tile slots of the prefill GEMM with the fused all-reduce
+                staging_bytes += prefill_chunk * g.hidden_size * 2 + native.gemm_allreduce_part_bytes(prefill_chunk, g.hidden_size, self.world) + 8192
         with torch.cuda.device(self.device):
             self.peer = PeerGroup(self.world, self.rank, staging_bytes=staging_bytes if self.world > 1 else 0,
                                   wait_limit=wait_limit, group=group, device=self.device)

@@ -56,6 +56,40 @@ def run(g, ckpt, prompt, new_tokens, capacity, stripe, comm, use_graphs, record,
     return out, decisions, kind
 
 
+def gemm_allreduce_check(world, rank, device):
+    """The tcgen05 GEMM with the fused NVLink all-reduce against fp32 partial products summed by the library all-reduce."""
+    from glm_tpu_b200.ops import native
+    from glm_tpu_b200.parallel.peer import PeerGroup
+
+    out = {}
+    for rows, N, K in ((300, 1024, 512), (1000, 6144, 256), (128, 520, 2048)):
+        part_bytes = native.gemm_allreduce_part_bytes(rows, N, world)
+        peer = PeerGroup(world, rank, staging_bytes=part_bytes + rows * N * 2 + 8192, device=device)
+        r_out = peer.region("out", rows * N * 2)
+        r_part = peer.region("part", part_bytes)
+        got = peer.tensor(r_out, (rows, N), torch.bfloat16)
+        gen = torch.Generator().manual_seed(100 * rank + rows)
+        a = (torch.randn(rows, K, generator=gen) * 0.5).to(torch.bfloat16).to(device)
+        b = (torch.randn(N, K, generator=gen) * 0.5).to(torch.bfloat16).to(device)
+        worst = 0.0
+        for round_ in range(3):  # several rounds through the same slots and flags
+            got.fill_(float("nan"))
+            torch.cuda.synchronize()
+            dist.barrier()
+            native.gemm_bf16_tc_allreduce(a, b, peer.comm, r_part.offset, r_out.offset, status=peer.status_ptr)
+            native.wait_signal(peer.comm, native.SIG_GEMM)
+            ref = a.float() @ b.float().T
+            dist.all_reduce(ref)
+            torch.cuda.synchronize()
+            err = (got.float() - ref).abs().max().item() / max(ref.abs().max().item(), 1e-6)
+            worst = max(worst, err if err == err else 1e9)
+            a = (a.float() * -0.5 + 0.25).to(torch.bfloat16)
+        out[f"{rows}x{N}x{K}"] = {"rel_err": worst, "status": peer.read_status()}
+        dist.barrier()
+        peer.close()
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--out", required=True)
@@ -94,6 +128,7 @@ def main():
     rep, _, _ = run(g, ckpt, prompt, 10, 128, 16, "fused", True, False, world, rank, device, kv_layout="replicated")
     result["replicated_graph"] = rep[0]
     result["prompt"] = prompt[0]
+    result["gemm_allreduce"] = gemm_allreduce_check(world, rank, device)
     gathered = [None] * world
     dist.all_gather_object(gathered, result["fused_graph"])
     result["all_ranks_agree"] = all(x == gathered[0] for x in gathered)

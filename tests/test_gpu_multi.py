@@ -58,6 +58,9 @@ def test_two_gpu_fused_matches_oracle_and_nccl(native_lib, tmp_path):
     # the baseline sums partials in another order, so compare it with the oracle under the same decisions
     assert not _bad_tokens(g, ckpt, res["prompt"], res["nccl"], 128, res["decisions"]) or res["nccl"] == res["fused_eager"]
     assert len(res["two_lanes"]) == 2 and all(len(t) == 6 for t in res["two_lanes"])
+    # the tcgen05 GEMM whose epilogue all-reduces over NVLink: bf16 rounding of the fp32 sum, clean status, three rounds
+    for shape, record in res["gemm_allreduce"].items():
+        assert record["status"] == 0 and record["rel_err"] < 2**-7, (shape, record)
     # a cache replica per GPU changes where rows are read from, not what is computed
     # (near-tie decisions may differ from the striped run, so it is checked under its own recorded decisions)
     assert not _bad_tokens(g, ckpt, res["prompt"], res["replicated_eager"], 128, res["replicated_decisions"])
