@@ -160,7 +160,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 #define T2_BN 256
 #define T2_STAGES 4
 #define T2_STAGE_BYTES ((TC_BM + T2_BN) * TC_BK * 2)
-#define T2_SMEM_BYTES (T2_STAGES * T2_STAGE_BYTES + 1024 + 256)
+#define T2_EPI_STRIDE 36   // floats per row of a 32 x 32 fp32 epilogue staging tile (16-byte aligned rows)
+#define T2_EPI_HSTRIDE 40  // bf16 per row of the 32 x 32 bf16 result tile behind it
+#define T2_EPI_WARP_BYTES (32 * T2_EPI_STRIDE * 4 + 32 * T2_EPI_HSTRIDE * 2)
+#define T2_SMEM_BYTES (T2_STAGES * T2_STAGE_BYTES + 1024 + 256 + 4 * T2_EPI_WARP_BYTES)
 #define T2_TMEM_COLS 512
 #define T2_GROUP_M 8
 
@@ -200,6 +203,7 @@ gemm_bf16_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, c
     uint64_t* acc_empty = acc_full + 2;           // [2] epilogue (4 warps) -> MMA
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     volatile uint32_t* fail_slot = tmem_slot + 1;
+    unsigned char* epi_stage = ring + T2_STAGES * T2_STAGE_BYTES + 256;  // per epilogue warp: fp32 tile, then bf16 tile
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // every CTA reads the round number before any CTA can finish, and the last CTA to finish advances it
@@ -292,15 +296,29 @@ gemm_bf16_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, c
                 const int64_t slot = (int64_t)(t / pc.world) * pc.world;
                 const int trow = quarter * 32 + lane;  // row inside the tile
                 const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * T2_BN;
+                // Row-per-thread accumulator fragments go through a per-warp shared-memory tile so that every store
+                // instruction writes whole 128-byte lines (8 lanes x 16 bytes per row, 4 rows): NVLink and HBM both
+                // want full lines, and a 16-byte store per lane at a 1 KB stride wastes most of each packet.
+                float* stage = reinterpret_cast<float*>(epi_stage + (warp - 2) * T2_EPI_WARP_BYTES);
+                const int sub_row = lane >> 3, sub_col = (lane & 7) * 4;
                 if (owner != pc.rank) {
-                    float* dst = reinterpret_cast<float*>(pc.data[owner] + ar.part_offset) + (slot + pc.rank) * T2_TILE_FLOATS + trow * T2_BN;
+                    float* dst = reinterpret_cast<float*>(pc.data[owner] + ar.part_offset) + (slot + pc.rank) * T2_TILE_FLOATS +
+                                 (quarter * 32) * T2_BN;
 #pragma unroll 1
                     for (int cb = 0; cb < T2_BN / 32; ++cb) {
                         uint32_t v[32];
                         tmem_ld32(lane_addr + cb * 32, v);
+                        __syncwarp();
 #pragma unroll
                         for (int e = 0; e < 32; e += 4)
-                            *reinterpret_cast<uint4*>(dst + cb * 32 + e) = make_uint4(v[e], v[e + 1], v[e + 2], v[e + 3]);
+                            *reinterpret_cast<uint4*>(stage + lane * T2_EPI_STRIDE + e) = make_uint4(v[e], v[e + 1], v[e + 2], v[e + 3]);
+                        __syncwarp();
+#pragma unroll
+                        for (int r4 = 0; r4 < 32; r4 += 4) {
+                            const int r = r4 + sub_row;
+                            *reinterpret_cast<uint4*>(dst + r * T2_BN + cb * 32 + sub_col) =
+                                *reinterpret_cast<const uint4*>(stage + r * T2_EPI_STRIDE + sub_col);
+                        }
                     }
                     __threadfence_system();
                     asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
@@ -312,37 +330,58 @@ gemm_bf16_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, c
                             raise_status(status, GLMB_STATUS_WAIT_TIMEOUT);
                     }
                     asm volatile("bar.sync 1, 128;" ::: "memory");
-                    const float* inbox = reinterpret_cast<const float*>(pc.data[pc.rank] + ar.part_offset) + slot * T2_TILE_FLOATS + trow * T2_BN;
+                    const float* inbox = reinterpret_cast<const float*>(pc.data[pc.rank] + ar.part_offset) + slot * T2_TILE_FLOATS +
+                                         (quarter * 32) * T2_BN;
+                    bf16* stage_h = reinterpret_cast<bf16*>(stage);
+                    const int out_col = (lane & 3) * 8;              // 8 bf16 = 16 bytes per lane, 4 lanes = the 64 bytes of one row of the block
 #pragma unroll 1
                     for (int cb = 0; cb < T2_BN / 32; ++cb) {
                         uint32_t v[32];
                         tmem_ld32(lane_addr + cb * 32, v);
-                        const int col = n0 + cb * 32;
-                        if (row >= rows || col >= N) continue;
+                        __syncwarp();
+                        // own accumulator -> shared memory, so that the sum below runs in the coalesced (4 rows x 8 lanes) layout
 #pragma unroll
-                        for (int e = 0; e < 32; e += 8) {
-                            if (col + e >= N) break;
-                            float sum[8];
+                        for (int e = 0; e < 32; e += 4)
+                            *reinterpret_cast<uint4*>(stage + lane * T2_EPI_STRIDE + e) = make_uint4(v[e], v[e + 1], v[e + 2], v[e + 3]);
+                        __syncwarp();
+                        float4 sum[8];
 #pragma unroll
-                            for (int i = 0; i < 8; ++i) sum[i] = 0.f;
-                            for (int p = 0; p < pc.world; ++p) {  // rank order: the same sum on every run
+                        for (int i = 0; i < 8; ++i) sum[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        for (int p = 0; p < pc.world; ++p) {  // rank order: the same sum on every run
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                const int r = i * 4 + sub_row;
+                                float4 x;
                                 if (p == pc.rank) {
-#pragma unroll
-                                    for (int i = 0; i < 8; ++i) sum[i] += __uint_as_float(v[e + i]);
+                                    x = *reinterpret_cast<const float4*>(stage + r * T2_EPI_STRIDE + sub_col);
                                 } else {
-                                    const float* src = inbox + (int64_t)p * T2_TILE_FLOATS + cb * 32 + e;
-                                    const uint4 lo = ld_sys_u4(src), hi = ld_sys_u4(src + 4);
-                                    sum[0] += __uint_as_float(lo.x); sum[1] += __uint_as_float(lo.y);
-                                    sum[2] += __uint_as_float(lo.z); sum[3] += __uint_as_float(lo.w);
-                                    sum[4] += __uint_as_float(hi.x); sum[5] += __uint_as_float(hi.y);
-                                    sum[6] += __uint_as_float(hi.z); sum[7] += __uint_as_float(hi.w);
+                                    const uint4 u = ld_sys_u4(inbox + (int64_t)p * T2_TILE_FLOATS + r * T2_BN + cb * 32 + sub_col);
+                                    x = make_float4(__uint_as_float(u.x), __uint_as_float(u.y), __uint_as_float(u.z), __uint_as_float(u.w));
                                 }
+                                sum[i].x += x.x; sum[i].y += x.y; sum[i].z += x.z; sum[i].w += x.w;
                             }
-                            const uint4 o = make_uint4(pack_bf16(sum[0], sum[1]), pack_bf16(sum[2], sum[3]), pack_bf16(sum[4], sum[5]),
-                                                       pack_bf16(sum[6], sum[7]));
-                            const int64_t at = (int64_t)row * N + col + e;
-                            for (int p = 0; p < pc.world; ++p)
-                                *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(pc.data[p] + ar.out_offset) + at) = o;
+                        }
+                        __syncwarp();
+                        // bf16 result of this 32-column block through the small bf16 tile: 4 lanes x 16 bytes per row, 8 rows per store
+                        bf16* tile_h = stage_h + 32 * T2_EPI_STRIDE * 2;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const int r = i * 4 + sub_row;
+                            *reinterpret_cast<uint2*>(tile_h + r * T2_EPI_HSTRIDE + sub_col) =
+                                make_uint2(pack_bf16(sum[i].x, sum[i].y), pack_bf16(sum[i].z, sum[i].w));
+                        }
+                        __syncwarp();
+                        const int col = n0 + cb * 32 + out_col;
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const int r = i * 8 + (lane >> 2);
+                            const int grow = row0 + quarter * 32 + r;
+                            if (grow < rows && col < N) {
+                                const uint4 o = *reinterpret_cast<const uint4*>(tile_h + r * T2_EPI_HSTRIDE + out_col);
+                                const int64_t at = (int64_t)grow * N + col;
+                                for (int p = 0; p < pc.world; ++p)
+                                    *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(pc.data[p] + ar.out_offset) + at) = o;
+                            }
                         }
                     }
                 }
