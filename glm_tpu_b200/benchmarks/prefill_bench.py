@@ -26,6 +26,7 @@ def main(argv=None) -> int:
     ap.add_argument("--context", type=int, default=32768)
     ap.add_argument("--repeat", type=int, default=3)
     ap.add_argument("--kv-layout", default="auto")
+    ap.add_argument("--shard", type=int, default=1, help="emulate one GPU of this many: experts and vocabulary divided (small profiling runs)")
     ap.add_argument("--out", type=Path)
     args = ap.parse_args(argv)
 
@@ -46,6 +47,11 @@ def main(argv=None) -> int:
         dist.init_process_group("nccl", device_id=device)
         dist.barrier()
     g = glm53_geometry().truncated(args.layers)
+    if args.shard > 1:
+        import dataclasses
+
+        g = dataclasses.replace(g, num_routed_experts=g.num_routed_experts // args.shard, vocab_size=g.vocab_size // args.shard,
+                                eos_ids=tuple(e % (g.vocab_size // args.shard) for e in g.eos_ids))
     runner = build_runner(g, world=world, rank=rank, device=device, seed=0, context_capacity=args.context, lanes=1,
                           prefill_chunk=args.chunk, kv_layout=args.kv_layout)
     gen = torch.Generator().manual_seed(7)
@@ -66,7 +72,7 @@ def main(argv=None) -> int:
     runner.peer.check_status()
     if rank == 0:
         best, med = min(times), statistics.median(times)
-        text = (f"prefill: GLM-5.3 architecture, {args.layers} of 78 layers, {world} GPU(s), kv layout {runner.kv_layout}, prompt {args.prompt} tokens in "
+        text = (f"prefill: GLM-5.3 architecture, {args.layers} of 78 layers, {g.num_routed_experts} experts, {world} GPU(s), kv layout {runner.kv_layout}, prompt {args.prompt} tokens in "
                 f"chunks of {args.chunk}, context capacity {args.context}\n"
                 f"time to first token: best {best * 1e3:.1f} ms, median {med * 1e3:.1f} ms ({args.repeat} runs after a warm-up)\n"
                 f"prefill rate: {args.prompt / best:.0f} tokens/s (best), {args.prompt / med:.0f} tokens/s (median); first token {token}\n")
