@@ -75,6 +75,34 @@ class ParallelLayout:
     def expert_owner(self, expert: int) -> int:
         return expert // self.experts_local
 
+    def layout_summary(self) -> dict:
+        """Which tensor is split how, and which exchange follows it (the mesh contract every rank must agree on)."""
+        w = self.world
+        return {
+            "world": w,
+            "hidden_state": "replicated",
+            "embedding": "replicated",
+            "q_a|kv_a|indexer_k|indexer_weights": "replicated (one fused projection)",
+            "q_b,kv_b,o_proj": f"by attention head: {self.heads_local} of {self.geometry.attention_heads} per GPU; o_proj partials all-reduced",
+            "indexer_q": "replicated",
+            "dense_mlp": f"by column: {self.dense_cols_local} per GPU; down partials all-reduced",
+            "shared_expert": f"by column: {self.shared_cols_local} per GPU; summed with the routed partials in one all-reduce",
+            "routed_experts": f"whole experts: {self.experts_local} of {self.geometry.num_routed_experts} per GPU (FP8 resident); route sums all-reduced",
+            "router": "replicated",
+            "lm_head": f"by vocabulary row: {self.vocab_local} per GPU; packed (logit, id) candidates exchanged",
+            "kv_cache,index_cache": "replicated, or striped by position in 64-row stripes (runner choice)",
+            "reductions": "fp32 partial sums in rank order, one bf16 rounding",
+        }
+
+    @property
+    def layout_hash(self) -> str:
+        """SHA-256 of the canonical summary + geometry hash: workers compare it before they exchange anything."""
+        import hashlib
+
+        from glm_tpu_b200.utils.json_utils import canonical_hash_bytes
+
+        return hashlib.sha256(canonical_hash_bytes({"layout": self.layout_summary(), "geometry": self.geometry.geometry_hash})).hexdigest()
+
     def describe(self) -> dict:
         return {
             "world": self.world,

@@ -6,8 +6,10 @@ One ``GlmMoeDsaModel`` lives in each per-GPU process.  ``run_rows`` pushes ``R``
   gathers happen *inside* kernels over peer memory (``comm='fused'``) or through NCCL (``comm='nccl'``, the
   baseline).  The launch sequence is static, reads positions/tokens from device memory and is captured in a CUDA
   graph by the runner.
-* prefill (``R`` up to a few thousand rows of one lane): dense projections go through cuBLAS (plain library GEMMs),
-  everything else through the same hand-written kernels; collectives use NCCL.
+* prefill (``R`` up to a few thousand rows of one lane): projections run on the tcgen05 GEMM (with the all-reduce of
+  K-split partial tiles fused into its epilogue on several GPUs), routed experts on the grouped tcgen05 kernel that decodes
+  FP8 on the way to the tensor core, everything else through the same hand-written kernels as decode; the score and
+  attention-partial merges of prefill use NCCL.
 
 Per layer (decode): add+RMSNorm -> q_a|kv_a|indexer projections -> LoRA norms, RoPE, cache-row write -> q_b ->
 query RoPE -> q-absorb (+ all-gather of queries) -> [full layers: indexer scores (+ all-gather) -> exact top-k]
@@ -15,7 +17,7 @@ query RoPE -> q-absorb (+ all-gather of queries) -> [full layers: indexer scores
 -> add+RMSNorm -> dense MLP, or router -> routed FP8 experts + shared expert -> combine (+ all-reduce).
 
 Parity: reference ``glm_tpu/models/glm_moe_dsa/model.py:46-159`` (decode_step), ``decoder_layer.py:538-740`` (layer
-bodies), ``prefill.py:49-235``; the collectives of ``SURVEY`` call sites are replaced as described above.
+bodies), ``prefill.py:49-235``; the reference's ``lax.psum`` / ``all_gather`` call sites are replaced as described above.
 """
 
 from __future__ import annotations

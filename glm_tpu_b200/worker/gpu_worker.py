@@ -194,6 +194,11 @@ class Worker:
         self.profile = profile_for(geometry, capacity)
         self.engine = LLMEngine(runner, vote=self.vote, profile=self.profile, digest_consensus=self.digest_consensus)
         self.record["geometry_hash"] = geometry.geometry_hash
+        from glm_tpu_b200.config.parallel import ParallelLayout
+
+        layout_hash = ParallelLayout(geometry, self.world, self.rank).layout_hash  # which tensor is split how: must agree on every rank
+        self.record["layout_hash"] = layout_hash
+        self.vote.all(self.digest_consensus(layout_hash), "layout_agreed")
         self.record["context_capacity"] = capacity
         self.record["kv_layout"] = getattr(runner, "kv_layout", None)
         self.record["memory_admission"] = getattr(getattr(runner, "report", None), "memory", None)
