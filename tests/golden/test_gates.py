@@ -1,0 +1,57 @@
+"""Thin wrappers over ``tools/equivalence``: the gates must match their goldens, and the mutation self-test must catch every mutant."""
+
+import json
+import sys
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parents[2]
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+from tools.equivalence import compare_run, driver, imports  # noqa: E402
+
+
+@pytest.mark.parametrize("gate", ["g3_oracle_digests", "g4_checkpoint_identity", "g9_wire_formats"])
+def test_gate_matches_golden(gate):
+    assert driver.check({gate}) == {}
+
+
+@pytest.mark.slow
+def test_import_closures_only_shrink():
+    assert driver.check({"g6_import_closures"}) == {}
+
+
+def test_entry_points_stay_light():
+    golden = driver.load("g6_import_closures")
+    assert golden["glm_tpu_b200.entrypoints.cli.main"]["heavy"] == []  # `info` and `--help` never import torch
+    assert "torch" not in golden["glm_tpu_b200.config.site"]["heavy"]
+    assert not any(m.startswith("glm_tpu_b200.ops") for m in golden["glm_tpu_b200.engine.llm_engine"]["modules"])  # the engine is device-free
+    assert not any(m.startswith("glm_tpu_b200.models") for m in golden["glm_tpu_b200.entrypoints.serve.http_handler"]["modules"])
+    assert imports.grown(golden, golden) == {}
+    assert imports.grown({"x": {"modules": ["a"], "heavy": []}}, {"x": {"modules": ["a", "b"], "heavy": ["torch"]}}) == {"x": {"modules": ["b"], "heavy": ["torch"]}}
+
+
+@pytest.mark.slow
+def test_mutation_selftest_catches_every_mutant():
+    from tools.equivalence import selftest
+
+    results = selftest.run()
+    assert results and all(results.values()), results
+
+
+def test_compare_run(tmp_path):
+    def make(run, tokens):
+        d = tmp_path / run
+        d.mkdir()
+        (d / "runner.rank0.json").write_text(json.dumps({"requests": [{"request_id": "question-01", "request_sha256": "ab" * 32}]}))
+        (d / "tokens.jsonl").write_text("".join(json.dumps({"request_id": "question-01", "index": i, "token_id": t, "finish_reason": None}) + "\n"
+                                                for i, t in enumerate(tokens)))
+        return d
+
+    a, b, c = make("a", [5, 6, 7]), make("b", [5, 6, 7]), make("c", [5, 9, 7])
+    assert compare_run.compare(a, b) == (1, [])
+    matched, diffs = compare_run.compare(a, c)
+    assert matched == 1 and diffs[0]["first_difference"] == 1
+    assert compare_run.main([str(a), str(b)]) == 0 and compare_run.main([str(a), str(c)]) == 1 and compare_run.main([str(a), str(tmp_path)]) in (0, 1, 2)

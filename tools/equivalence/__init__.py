@@ -1,0 +1,12 @@
+"""Equivalence gates: frozen fingerprints of what must not change silently (wire formats, oracle execution digests,
+checkpoint bytes, import closures) plus a mutation self-test of the gates themselves.
+
+    python -m tools.equivalence.driver check            # compare against tests/golden/data/*.json
+    python -m tools.equivalence.driver update           # rewrite the goldens after an intended change
+    python -m tools.equivalence.driver selftest         # every mutant must change at least one digest
+    python -m tools.equivalence.compare_run RUN_A RUN_B # token-stream identity of two real runs
+
+Gate names follow the reference's (``tools/equivalence/README.md:69-132``): G3 execution digests, G4 checkpoint identity,
+G6 import closures (may only shrink), G9 wire formats, G14 mutation self-test.  G1/G2/G7 (StableHLO fingerprints of compiled
+programs, executed-function sets) have no counterpart: there is no compiler, the program is the static launch list.
+"""
