@@ -135,3 +135,58 @@ def test_decode_is_deterministic(native_lib):
     a, _ = _run_engine(g, ckpt, prompt, 10, capacity=64, stripe=8, use_graphs=True)
     b, _ = _run_engine(g, ckpt, prompt, 10, capacity=64, stripe=8, use_graphs=True)
     assert a == b
+
+
+def test_lanes_are_isolated_bitwise(native_lib):
+    """Batched decode: a lane's tokens and cached rows do not change when the OTHER lane's conversation changes
+    (reference ``tests/models/glm_moe_dsa/test_model.py:88-99``: bitwise isolation under perturbation of one lane)."""
+    from glm_tpu_b200.runner.gpu_runner import build_runner
+
+    g = small_geometry(4)
+    ckpt = random_checkpoint(g, seed=11)
+    gen = torch.Generator().manual_seed(11)
+    mine = torch.randint(0, g.vocab_size, (45,), generator=gen).tolist()
+    others = [torch.randint(0, g.vocab_size, (n,), generator=gen).tolist() for n in (30, 61)]
+    results = []
+    for other in others:
+        runner = build_runner(g, checkpoint=ckpt, context_capacity=128, lanes=2, stripe=16, use_graphs=True, prefill_chunk=32)
+        first = runner.prefill(0, mine)
+        runner.prefill(1, other)
+        runner.build_decode_program()
+        toks = [first]
+        for step in range(8):
+            runner.decode_step()
+            toks.append(runner.read_step_tokens(step)[0])
+        torch.cuda.synchronize()
+        rows = len(mine) + 8
+        results.append((toks, runner.state.kv_cache[0, :, :rows].clone().cpu(), runner.state.index_cache[0, :, :rows].clone().cpu()))
+        runner.peer.check_status()
+        runner.close()
+    assert results[0][0] == results[1][0]
+    assert torch.equal(results[0][1].view(torch.int16), results[1][1].view(torch.int16))
+    assert torch.equal(results[0][2].view(torch.int16), results[1][2].view(torch.int16))
+
+
+def test_inactive_lane_is_frozen(native_lib):
+    """A deactivated lane neither advances nor writes its cache while the other lane keeps decoding."""
+    from glm_tpu_b200.runner.gpu_runner import build_runner
+
+    g = tiny_geometry()
+    ckpt = random_checkpoint(g, seed=2)
+    runner = build_runner(g, checkpoint=ckpt, context_capacity=64, lanes=2, stripe=16, use_graphs=True, prefill_chunk=16)
+    runner.prefill(0, list(range(3, 20)))
+    runner.prefill(1, list(range(40, 52)))
+    runner.build_decode_program()
+    runner.decode_step()
+    runner.deactivate(1)
+    torch.cuda.synchronize()
+    before = (runner.state.kv_cache[1].clone(), int(runner.state.positions[1]), int(runner.state.tokens[1]))
+    for step in range(1, 5):
+        runner.decode_step()
+        assert runner.read_step_tokens(step)[1] == -1
+    torch.cuda.synchronize()
+    assert int(runner.state.positions[1]) == before[1] and int(runner.state.tokens[1]) == before[2]
+    assert torch.equal(runner.state.kv_cache[1].view(torch.int16), before[0].view(torch.int16))
+    assert int(runner.state.positions[0]) == 17 + 5
+    runner.peer.check_status()
+    runner.close()

@@ -42,7 +42,7 @@ def test_grouped_fp8_experts(native_lib, rows, tk, E, el, H, I):
     wd, sd = quantize_fp8(torch.randn(el, H, I, generator=gen) * 0.05, (128, 128), gen)
     tiles, n_tiles, perm = _tiles(ids.reshape(-1).long(), el)
     P = rows * tk
-    xs = torch.zeros(P, H, dtype=torch.bfloat16, device=DEV)
+    xs = torch.full((P, H), float("nan"), dtype=torch.bfloat16, device=DEV)  # poison: rows past this GPU's routes become zeros, never leak
     acts = torch.full((P, I), float("nan"), dtype=torch.bfloat16, device=DEV)
     dw = torch.full((P, H), float("nan"), dtype=torch.bfloat16, device=DEV)
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
@@ -73,3 +73,5 @@ def test_grouped_fp8_experts(native_lib, rows, tk, E, el, H, I):
     # routes of experts this GPU does not hold are never written
     foreign = (ids.reshape(-1) >= el).nonzero().flatten()
     assert bool(torch.isnan(got_dw[foreign]).all())
+    # padding rows of the sorted activation buffer were overwritten with zeros, and no NaN reached a real route
+    assert bool((got_x[checked:] == 0).all()) and not bool(torch.isnan(got_dw[(ids.reshape(-1) < el).nonzero().flatten()]).any())
