@@ -207,3 +207,45 @@ def test_checkpoint_cli_round_trip(tmp_path, monkeypatch, capsys):
                  ["checkpoint", "verify", str(tmp_path / "packed")]):
         assert cli.main(argv) == 0
         assert json.loads(capsys.readouterr().out)["ok"]
+
+
+def test_per_rank_topology_capture(tmp_path):
+    """Two threads = two ranks with a rendezvous instead of the process group (no GPU, no torch.distributed)."""
+    import threading
+
+    from glm_tpu_b200.parallel import topology_capture as tc
+
+    found = topo.discover_topology(FakeNvml(n=2))
+    binding = topo.derive_topology_binding(found, 2)
+    uuids = [r["uuid"] for r in binding["ranks"]]
+
+    def run(assignment, bindings=(binding, binding)):
+        box, barrier, errors = [None, None], threading.Barrier(2), [None, None]
+
+        def gather_for(rank):
+            def gather(obj):
+                box[rank] = obj
+                barrier.wait(timeout=10)
+                return list(box)
+            return gather
+
+        def body(rank):
+            try:
+                out = tmp_path / f"case{len(list(tmp_path.iterdir()))}-{rank}"
+                out.mkdir()
+                tc.capture_rank(rank, bindings[rank], assignment[rank], gather_for(rank), out)
+            except Exception as exc:  # noqa: BLE001
+                errors[rank] = exc
+
+        threads = [threading.Thread(target=body, args=(r,)) for r in range(2)]
+        [t.start() for t in threads]
+        [t.join() for t in threads]
+        return errors
+
+    assert run(uuids) == [None, None]
+    swapped = run(uuids[::-1])
+    assert all(isinstance(e, ConfigValidationError) and "binding gives it" in str(e) for e in swapped)
+    doubled = run([uuids[0], uuids[0]])
+    assert all(isinstance(e, ConfigValidationError) for e in doubled)
+    other = dict(binding, binding_sha256="f" * 64)
+    assert all(isinstance(e, ConfigValidationError) and "different topology bindings" in str(e) for e in run(uuids, (binding, other)))
