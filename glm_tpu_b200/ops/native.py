@@ -263,8 +263,24 @@ def q_absorb(q_nope, rows, kv_b, heads_local, head_base, heads_total, nope, vdim
 
 
 # ----------------------------------------------------------------------------- indexer
+def _indexer_tensor_cores() -> bool:
+    import os
+
+    return os.environ.get("GLM_B200_INDEXER", "tcgen05") != "cuda"  # 'cuda': force the CUDA-core kernel (A/B runs)
+
+
 def indexer_score(q_idx, head_w, index_cache, row_pos, row_lane, rows, IH, D, index_slot, full_layers, local_cap, stripe, world,
                   rank, capacity, max_ctx, score_stride, scale, scores, scores_offset=0, comm=None, sig=SIG_SCORES, status=None):
+    if D == 128 and IH == 32 and _indexer_tensor_cores():
+        # the usual head shape: keys x query pieces on tcgen05 (see csrc/indexer_tcgen05.cu)
+        _check(
+            lib().glmb_indexer_score_tc(_p(q_idx), _p(head_w), _p(index_cache), C.c_int64(index_cache.numel() // D), _p(row_pos),
+                                        _p(row_lane), rows, IH, D, index_slot, full_layers, local_cap, stripe, world, rank, capacity,
+                                        max_ctx, C.c_int64(score_stride), f32(scale), _p(scores), C.c_int64(scores_offset),
+                                        _comm(comm), sig, _p(status), _stream()),
+            "indexer_score_tc",
+        )
+        return
     _check(
         lib().glmb_indexer_score(_p(q_idx), _p(head_w), _p(index_cache), _p(row_pos), _p(row_lane), rows, IH, D, index_slot,
                                  full_layers, local_cap, stripe, world, rank, capacity, max_ctx, C.c_int64(score_stride),

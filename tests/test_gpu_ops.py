@@ -234,6 +234,42 @@ def test_indexer_score(native_lib):
         assert torch.isnan(scores[r, c:]).all()  # positions beyond the context are never written
 
 
+@pytest.mark.parametrize("path", ["tcgen05", "cuda"])
+def test_indexer_score_lanes_slots_and_stripes(native_lib, monkeypatch, path):
+    """Both indexer kernels on a cache with several lanes and index slots, a striped layout (this GPU = rank 1 of 2) and ragged contexts."""
+    monkeypatch.setenv("GLM_B200_INDEXER", path)
+    n = native_lib
+    torch.manual_seed(19)
+    rows, IH, D, cap, stripe, world, rank = 3, 32, 128, 2048, 64, 2, 1
+    lanes, slots, slot = 3, 2, 1
+    local_cap = cap // world
+    q = torch.randn(rows, IH, D) * 3.0
+    hw = torch.randn(rows, IH) * 0.2
+    keys = bf(torch.randn(lanes, slots, local_cap, D))
+    pos = torch.tensor([1999, 130, 63], dtype=torch.int32)  # the last row owns nothing on rank 1 (positions 0..63 are rank 0's)
+    lane = torch.tensor([2, 0, 1], dtype=torch.int32)
+    scale = float(torch.tensor(D**-0.5, dtype=torch.float32))
+    scores = torch.full((rows, cap), float("nan"), device=DEV)
+    n.indexer_score(q.to(DEV), hw.to(DEV), keys.to(DEV), pos.to(DEV), lane.to(DEV), rows, IH, D, slot, slots, local_cap, stripe, world, rank, cap,
+                    cap, cap, scale, scores)
+    torch.cuda.synchronize()
+    page = stripe * world
+    for r in range(rows):
+        ctx = int(pos[r]) + 1
+        mine = [g for g in range(ctx) if (g // stripe) % world == rank]
+        local = torch.tensor([(g // page) * stripe + g % stripe for g in mine], dtype=torch.long)
+        got = scores[r].cpu()
+        written = torch.zeros(cap, dtype=torch.bool)
+        written[mine] = True
+        assert torch.isnan(got[~written]).all()  # other ranks' positions and everything past the context stay untouched
+        if mine:
+            k = keys[int(lane[r]), slot, local].float()
+            dots = torch.einsum("hd,td->ht", q[r], k) * scale
+            ref = (hw[r][:, None] * torch.relu(dots)).sum(0)
+            ok, err = close(got[mine], ref, rtol=1e-4, atol=1e-4)
+            assert ok, (path, r, err)
+
+
 @pytest.mark.parametrize("count", [0, 1, 31, 100, 2048])
 def test_sparse_mla_attention(native_lib, count):
     n = native_lib
