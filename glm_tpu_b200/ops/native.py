@@ -289,6 +289,11 @@ def indexer_score(q_idx, head_w, index_cache, row_pos, row_lane, rows, IH, D, in
     )
 
 
+def set_topk_cluster(enabled: int) -> None:
+    """1 (default): exact top-k on an 8-CTA cluster per row; 0: the single-CTA kernel."""
+    lib().glmb_set_topk_cluster(int(enabled))
+
+
 def topk_select(scores, row_pos, rows, capacity, score_stride, top_k, stripe, world, rank, sel_global, sel_local, sel_counts,
                 comm=None, sig=SIG_SCORES):
     _check(

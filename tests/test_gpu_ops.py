@@ -169,8 +169,16 @@ def test_router_topk(native_lib):
     assert ids[0].cpu().tolist() == list(range(tk))
 
 
-@pytest.mark.parametrize("n_ctx,top_k", [(10, 16), (100, 16), (5000, 2048), (32768, 2048)])
-def test_topk_select_exact_with_ties(native_lib, n_ctx, top_k):
+@pytest.fixture(params=[1, 0], ids=["cluster8", "single_cta"])
+def topk_kernel(request, native_lib):
+    """Both selection kernels behind the one entry point: the 8-CTA cluster (distributed shared memory) and the single CTA."""
+    native_lib.set_topk_cluster(request.param)
+    yield request.param
+    native_lib.set_topk_cluster(1)
+
+
+@pytest.mark.parametrize("n_ctx,top_k", [(10, 16), (100, 16), (5000, 2048), (32768, 2048), (2049, 2048), (7, 2048)])
+def test_topk_select_exact_with_ties(native_lib, topk_kernel, n_ctx, top_k):
     n = native_lib
     torch.manual_seed(7)
     cap = 32768
@@ -193,7 +201,7 @@ def test_topk_select_exact_with_ties(native_lib, n_ctx, top_k):
         assert torch.equal(sel_l[r, :k].cpu().long(), ref)  # one GPU: local row == position
 
 
-def test_topk_select_striped_ownership(native_lib):
+def test_topk_select_striped_ownership(native_lib, topk_kernel):
     n = native_lib
     torch.manual_seed(8)
     cap, top_k, stripe, world = 4096, 256, 64, 4
@@ -210,6 +218,21 @@ def test_topk_select_striped_ownership(native_lib):
         local = (mine // (stripe * world)) * stripe + mine % stripe
         assert int(cnt[0, 1]) == mine.numel()
         assert torch.equal(sel_l[0, : mine.numel()].cpu().long(), local)
+
+
+def test_topk_select_long_context_all_equal(native_lib, topk_kernel):
+    """A 166,912-slot row (beyond what one CTA can stage) where every score ties: the lowest positions win, in order."""
+    n = native_lib
+    cap, top_k = 166912, 2048
+    scores = torch.full((1, cap), 0.25)
+    scores[0, 100000:100010] = 0.5
+    pos = torch.tensor([150000], dtype=torch.int32)
+    sel_g = torch.zeros(1, top_k, dtype=torch.int32, device=DEV)
+    sel_l = torch.zeros(1, top_k, dtype=torch.int32, device=DEV)
+    cnt = torch.zeros(1, 2, dtype=torch.int32, device=DEV)
+    n.topk_select(scores.to(DEV), pos.to(DEV), 1, cap, cap, top_k, 64, 1, 0, sel_g, sel_l, cnt)
+    want = list(range(top_k - 10)) + list(range(100000, 100010))
+    assert sel_g[0].cpu().tolist() == want and cnt[0].cpu().tolist() == [top_k, top_k]
 
 
 def test_indexer_score(native_lib):
