@@ -181,6 +181,11 @@ class GlmMoeDsaModel:
         self.index_scale = _f32(g.index_head_dim**-0.5)
         self.head_scale = _f32(g.index_heads**-0.5)
         self.trace = None  # set to a dict to record intermediates (tests)
+        import os
+
+        # independent branches of the decode step (shared expert | routed experts; absorbed query | indexer + top-k) run on two
+        # streams; GLM_B200_OVERLAP=0 keeps everything on one stream
+        self.side = torch.cuda.Stream(device=self.device) if os.environ.get("GLM_B200_OVERLAP", "1") != "0" else None
 
     # ------------------------------------------------------------------------------ helpers
     @property
@@ -207,6 +212,19 @@ class GlmMoeDsaModel:
             native.gemm_bf16_tc(x, w, out, status=self.peer.status_ptr)
             return out
         return torch.mm(x, w.t(), out_dtype=torch.float32) if f32 else torch.mm(x, w.t())
+
+    def _fork(self):
+        """Make the side stream wait for everything issued so far on the current stream; returns the current stream."""
+        main = torch.cuda.current_stream()
+        event = torch.cuda.Event()
+        event.record(main)
+        self.side.wait_event(event)
+        return main
+
+    def _join(self, main) -> None:
+        event = torch.cuda.Event()
+        event.record(self.side)
+        main.wait_event(event)
 
     def _mm_allreduce(self, ws: "Workspace", x: torch.Tensor, w: torch.Tensor) -> torch.Tensor | None:
         """``bf16(sum over GPUs of x_r @ w_r.T)`` ([rows, hidden]) in one kernel: tcgen05 tiles whose epilogue exchanges the
@@ -273,9 +291,18 @@ class GlmMoeDsaModel:
         b.has_indexer, b.capacity = int(full), cache.context_capacity
         native.q_post(b, rows)
 
+        forked = None
         if decode:
-            native.q_absorb(ws.q_nope, rows, lw.kv_b, hl, hb, ht, g.qk_nope_head_dim, g.v_head_dim, L, rd, ws.q_full,
-                            ws.r_q.offset if xf else 0, kx, native.SIG_Q)
+            if full and not gather and self.side is not None:
+                # the absorbed query (needed by the attention) and the indexer scores + top-k (needed by the attention too)
+                # depend on the same inputs and not on each other: run the former on the side stream
+                forked = self._fork()
+                with torch.cuda.stream(self.side):
+                    native.q_absorb(ws.q_nope, rows, lw.kv_b, hl, hb, ht, g.qk_nope_head_dim, g.v_head_dim, L, rd, ws.q_full, 0, None,
+                                    native.SIG_Q)
+            else:
+                native.q_absorb(ws.q_nope, rows, lw.kv_b, hl, hb, ht, g.qk_nope_head_dim, g.v_head_dim, L, rd, ws.q_full,
+                                ws.r_q.offset if xf else 0, kx, native.SIG_Q)
             if gather and not xf:
                 self._allgather_heads(ws.q_full[:rows])
         else:
@@ -298,6 +325,8 @@ class GlmMoeDsaModel:
                 self.trace.setdefault("sel_global", {})[layer] = ws.sel_global[:rows].clone()
                 self.trace.setdefault("scores", {})[layer] = ws.scores[:rows].clone()
 
+        if forked is not None:
+            self._join(forked)
         # owner-local partial attention for ALL heads, in passes of attn_rows query rows
         for r0 in range(0, rows, ws.attn_rows):
             n = min(ws.attn_rows, rows - r0)
@@ -415,6 +444,14 @@ class GlmMoeDsaModel:
             return
         tk, I, E = g.routed_top_k, g.moe_intermediate_size, g.num_routed_experts
         el, ebase = lay.experts_local, self.rank * lay.experts_local
+        forked = None
+        if decode and self.side is not None:
+            # the shared expert needs only the normalized hidden state: it runs on the side stream while the main stream
+            # goes through router -> top-8 -> routed gate/up -> routed down; the combine joins the two
+            forked = self._fork()
+            with torch.cuda.stream(self.side):
+                native.skinny_bf16_swiglu(x, lw.shared_gate, lw.shared_up, ws.act_shared)
+                native.skinny_bf16(ws.act_shared[:rows], lw.shared_down, ws.partial, native.SK_OUT_F32)
         self._linear_f32(x, lw.router_w, ws.router_logits, decode)
         native.router_topk(ws.router_logits[:rows], lw.router_bias, tk, ws.topk_ids, ws.topk_w)
         if self.trace is not None:
@@ -439,8 +476,11 @@ class GlmMoeDsaModel:
             native.moe_down_fp8(ws.act, ws.topk_w, tile_expert, tile_routes, n_tiles, tiles, rt, lw.exp_down_bits, lw.exp_down_scale,
                                 ebase, ws.dw)
         if decode:
-            native.skinny_bf16_swiglu(x, lw.shared_gate, lw.shared_up, ws.act_shared)
-            native.skinny_bf16(ws.act_shared[:rows], lw.shared_down, ws.partial, native.SK_OUT_F32)
+            if forked is not None:
+                self._join(forked)
+            else:
+                native.skinny_bf16_swiglu(x, lw.shared_gate, lw.shared_up, ws.act_shared)
+                native.skinny_bf16(ws.act_shared[:rows], lw.shared_down, ws.partial, native.SK_OUT_F32)
             shared_partial = ws.partial
         else:
             gate, up = self._mm(x, lw.shared_gate).float(), self._mm(x, lw.shared_up).float()
