@@ -436,11 +436,25 @@ GLMB_API int glmb_skinny_bf16_swiglu(const void* x, int64_t xs, int rows, const 
     return (int)cudaGetLastError();
 }
 
+// Tensor-core variants (moe_gemv_mma.cu), used when the shapes are whole 64-wide k chunks and 16-row panels.
+int glmb_launch_moe_gateup_mma(const void* x, int64_t xs, int top_k, const int* tile_expert, const int* tile_routes, const int* n_tiles,
+                               int tiles, int rt, const void* wg, const void* wu, const float* sg, const float* su, int expert_base,
+                               int experts_local, int I, int H, void* act, cudaStream_t stream);
+int glmb_launch_moe_down_mma(const void* act, const float* route_weight, const int* tile_expert, const int* tile_routes, const int* n_tiles,
+                             int tiles, int rt, const void* wd, const float* sd, int expert_base, int experts_local, int I, int H, void* dw,
+                             cudaStream_t stream);
+static int g_moe_mma = 1;
+// 1 (default): decode the FP8 experts into mma.sync fragments; 0: the fp32-FMA kernels.
+GLMB_API void glmb_set_moe_mma(int enabled) { g_moe_mma = enabled ? 1 : 0; }
+
 // Routed gate/up for `tiles` tiles of `rt` routes (rt in {1, 8}).  H % 16 == 0.
 GLMB_API int glmb_moe_gateup_fp8(const void* x, int64_t xs, int top_k, const int* tile_expert, const int* tile_routes,
                                  const int* n_tiles, int tiles, int rt, const void* wg, const void* wu, const float* sg,
                                  const float* su, int expert_base, int experts_local, int I, int H, void* act, void* stream) {
     if ((H & 15) || tiles < 1) return 1;
+    if (g_moe_mma && (rt == 1 || rt == 8) && !(H & 63) && !(I & 15) && !(xs & 7))
+        return glmb_launch_moe_gateup_mma(x, xs, top_k, tile_expert, tile_routes, n_tiles, tiles, rt, wg, wu, sg, su, expert_base,
+                                          experts_local, I, H, act, (cudaStream_t)stream);
     dim3 grid(ceil_div(I, SK_WARPS), tiles);
     if (rt == 1)
         GLMB_LAUNCH(moe_gateup_fp8_kernel<1>, grid, SK_THREADS, 0, (cudaStream_t)stream, 
@@ -459,6 +473,9 @@ GLMB_API int glmb_moe_down_fp8(const void* act, const float* route_weight, const
                                const int* n_tiles, int tiles, int rt, const void* wd, const float* sd, int expert_base,
                                int experts_local, int I, int H, void* dw, void* stream) {
     if ((I & 15) || tiles < 1) return 1;
+    if (g_moe_mma && (rt == 1 || rt == 8) && !(I & 63) && !(H & 15))
+        return glmb_launch_moe_down_mma(act, route_weight, tile_expert, tile_routes, n_tiles, tiles, rt, wd, sd, expert_base, experts_local,
+                                        I, H, dw, (cudaStream_t)stream);
     dim3 grid(ceil_div(H, SK_WARPS * 2), tiles);
     if (rt == 1)
         GLMB_LAUNCH(moe_down_fp8_kernel<1>, grid, SK_THREADS, 0, (cudaStream_t)stream, (const bf16*)act, route_weight, tile_expert, tile_routes,

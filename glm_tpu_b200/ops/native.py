@@ -187,6 +187,11 @@ def skinny_bf16_swiglu(x, wg, wu, act):
     )
 
 
+def set_moe_mma(enabled: int) -> None:
+    """1 (default): FP8 expert GEMVs feed mma.sync; 0: the fp32-FMA kernels."""
+    lib().glmb_set_moe_mma(int(enabled))
+
+
 def moe_gateup_fp8(x, top_k, tile_expert, tile_routes, n_tiles, tiles, rt, wg, wu, sg, su, expert_base, act):
     experts_local, I, H = wg.shape
     _check(

@@ -108,9 +108,11 @@ def _routed_fixture(E, I, H, seed):
     return out
 
 
+@pytest.mark.parametrize("mma", [1, 0], ids=["mma_sync", "fp32_fma"])
 @pytest.mark.parametrize("rows,tiled", [(3, False), (40, True)])
-def test_routed_experts(native_lib, rows, tiled):
+def test_routed_experts(native_lib, rows, tiled, mma):
     n = native_lib
+    n.set_moe_mma(mma)
     torch.manual_seed(5)
     E, I, H, tk = 8, 256, 512, 2
     fx = _routed_fixture(E, I, H, 5)
@@ -137,6 +139,7 @@ def test_routed_experts(native_lib, rows, tiled):
         te, tr, nt, tiles, rt = ids_d, None, None, rows * tk, 1
     n.moe_gateup_fp8(x_d, tk, te, tr, nt, tiles, rt, d["gate"][0], d["up"][0], d["gate"][1], d["up"][1], 0, act)
     n.moe_down_fp8(act, w_d, te, tr, nt, tiles, rt, d["down"][0], d["down"][1], 0, dw)
+    n.set_moe_mma(1)
     ok, err = close(dw, ref, rtol=2**-5, atol=2e-3)
     assert ok, err
     # combine on one GPU: route sum, scale, shared
