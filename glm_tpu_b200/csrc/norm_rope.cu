@@ -135,7 +135,7 @@ struct QkvPostArgs {
     uint32_t* status;
 };
 
-__global__ void __launch_bounds__(256) qkv_a_post_kernel(QkvPostArgs a) {
+__global__ void __launch_bounds__(256) qkv_a_post_generic_kernel(QkvPostArgs a) {
     GLMB_PDL_PROLOGUE();
     __shared__ float scratch[40];
     __shared__ float s_key[256];
@@ -227,6 +227,140 @@ __global__ void __launch_bounds__(256) qkv_a_post_kernel(QkvPostArgs a) {
     const float* hw = kx + a.D;
     const float hscale = a.head_scale;
     for (int h = threadIdx.x; h < a.IH; h += blockDim.x) a.head_w[(int64_t)r * a.IH + h] = __fmul_rn(hw[h], hscale);
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Three block sums with the reduction tree of block_sum (so each is bit-identical to a separate call), one barrier set.
+__device__ __forceinline__ void block_sum3(float& a, float& b, float& c, float (*scratch)[40]) {
+    a = warp_sum(a); b = warp_sum(b); c = warp_sum(c);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __syncthreads();
+    if (lane == 0) { scratch[0][warp] = a; scratch[1][warp] = b; scratch[2][warp] = c; }
+    __syncthreads();
+    if (warp < 3) {
+        float t = lane < (int)((blockDim.x + 31) >> 5) ? scratch[warp][lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) scratch[warp][32] = t;
+    }
+    __syncthreads();
+    a = scratch[0][32]; b = scratch[1][32]; c = scratch[2][32];
+}
+
+// The same computation as qkv_a_post_generic_kernel for Q <= 2048 and L <= 1024 (every supported geometry): all of the
+// row's inputs are fetched before the first reduction, the three independent sums share one reduction, and the latent
+// is stored four values at a time.  One memory round trip and two reductions instead of four and four.
+__global__ void __launch_bounds__(256) qkv_a_post_kernel(QkvPostArgs a) {
+    GLMB_PDL_PROLOGUE();
+    __shared__ float scratch[3][40];
+    __shared__ float s_key[256];
+    const int r = blockIdx.x, tid = threadIdx.x;
+    const float* p = a.proj + (int64_t)r * a.proj_stride;
+    int pos = a.row_pos[r];
+    const int lane_id = a.row_lane[r];
+    const bool active = a.row_active ? a.row_active[r] != 0 : true;
+    if (pos < 0 || pos >= a.capacity) {
+        if (tid == 0) raise_status(a.status, GLMB_STATUS_BAD_INDEX);
+        pos = min(max(pos, 0), a.capacity - 1);
+    }
+    const int page = a.stripe * a.world;
+    const bool owner = ((pos / a.stripe) % a.world) == a.rank;
+    const int local_row = (pos / page) * a.stripe + pos % a.stripe;
+    const int W = a.L + a.rd, half = a.rd / 2;
+    bf16* cache_row = a.kv_cache + (((int64_t)lane_id * a.layers + a.layer) * a.local_cap + local_row) * W;
+    const bool write_cache = owner && active;
+    const float* c = p + a.Q;
+    const float* kx = c + W;
+
+    // ---- every input of the row, before any arithmetic
+    float4 qv[2];
+    uint2 qw[2];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+        const int i = tid * 4 + k * 1024;
+        qv[k] = i < a.Q ? *reinterpret_cast<const float4*>(p + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        qw[k] = i < a.Q ? *reinterpret_cast<const uint2*>(a.q_norm_w + i) : make_uint2(0, 0);
+    }
+    const int li = tid * 4;
+    const float4 cv = li < a.L ? *reinterpret_cast<const float4*>(c + li) : make_float4(0.f, 0.f, 0.f, 0.f);
+    const uint2 cw = li < a.L ? *reinterpret_cast<const uint2*>(a.kv_norm_w + li) : make_uint2(0, 0);
+    float r_even = 0.f, r_odd = 0.f, r_cs = 0.f, r_sn = 0.f;
+    if (tid < half) {
+        r_even = c[a.L + 2 * tid]; r_odd = c[a.L + 2 * tid + 1];
+        r_cs = __bfloat162float(a.rope_table[(int64_t)pos * a.rd + tid]);
+        r_sn = __bfloat162float(a.rope_table[(int64_t)pos * a.rd + half + tid]);
+    }
+    float key_v = 0.f, key_w = 0.f, key_b = 0.f, key_f = 0.f, hw_v = 0.f;
+    if (a.has_indexer) {
+        if (tid < a.D) { key_v = kx[tid]; key_w = a.k_norm_w[tid]; key_b = a.k_norm_b[tid]; }
+        if (tid < a.rd) key_f = a.inv_freq[tid >> 1];
+        if (tid < a.IH) hw_v = kx[a.D + tid];
+    }
+
+    // ---- sums of squares of q_a and of the latent (bf16-rounded inputs), and the indexer key's sum, in one reduction
+    float ss = 0.f, ss_kv = 0.f, ksum = key_v;
+    float qr[2][4];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+        qr[k][0] = bf16_round(qv[k].x); qr[k][1] = bf16_round(qv[k].y); qr[k][2] = bf16_round(qv[k].z); qr[k][3] = bf16_round(qv[k].w);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) ss = fmaf(qr[k][e], qr[k][e], ss);
+    }
+    const float cr[4] = {bf16_round(cv.x), bf16_round(cv.y), bf16_round(cv.z), bf16_round(cv.w)};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) ss_kv = fmaf(cr[e], cr[e], ss_kv);
+    block_sum3(ss, ss_kv, ksum, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)a.Q + a.eps);
+    const float inv_kv = 1.0f / sqrtf(ss_kv / (float)a.L + a.eps);
+
+    // ---- q_a RMSNorm -> q_resid
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+        const int i = tid * 4 + k * 1024;
+        if (i < a.Q) {
+            uint2 o;
+            o.x = pack_bf16(bf16_round(qr[k][0] * inv) * bf16_lo(qw[k].x), bf16_round(qr[k][1] * inv) * bf16_hi(qw[k].x));
+            o.y = pack_bf16(bf16_round(qr[k][2] * inv) * bf16_lo(qw[k].y), bf16_round(qr[k][3] * inv) * bf16_hi(qw[k].y));
+            *reinterpret_cast<uint2*>(a.q_resid + (int64_t)r * a.Q + i) = o;
+        }
+    }
+    // ---- kv_a latent RMSNorm -> cache row (and this step's row)
+    if (li < a.L) {
+        uint2 o;
+        o.x = pack_bf16(bf16_round(cr[0] * inv_kv) * bf16_lo(cw.x), bf16_round(cr[1] * inv_kv) * bf16_hi(cw.x));
+        o.y = pack_bf16(bf16_round(cr[2] * inv_kv) * bf16_lo(cw.y), bf16_round(cr[3] * inv_kv) * bf16_hi(cw.y));
+        if (write_cache) *reinterpret_cast<uint2*>(cache_row + li) = o;
+        if (a.kv_new) *reinterpret_cast<uint2*>(a.kv_new + (int64_t)r * W + li) = o;
+    }
+    // ---- RoPE of the key part: interleaved pairs, bf16 table, fp32 products, one rounding
+    if (tid < half) {
+        const float even = bf16_round(r_even), odd = bf16_round(r_odd);
+        const uint32_t o = pack_bf16(__fsub_rn(__fmul_rn(even, r_cs), __fmul_rn(odd, r_sn)), __fadd_rn(__fmul_rn(odd, r_cs), __fmul_rn(even, r_sn)));
+        if (write_cache) *reinterpret_cast<uint32_t*>(cache_row + a.L + 2 * tid) = o;
+        if (a.kv_new) *reinterpret_cast<uint32_t*>(a.kv_new + (int64_t)r * W + a.L + 2 * tid) = o;
+    }
+    if (!a.has_indexer) return;
+    // ---- indexer key: affine LayerNorm (fp32), RoPE on the first rd features (fp32 cos/sin), bf16 store
+    const float mean = ksum / (float)a.D;
+    const float d = tid < a.D ? key_v - mean : 0.f;
+    const float var = block_sum(d * d, scratch[0]) / (float)a.D;
+    const float rstd = 1.0f / sqrtf(var + a.key_eps);
+    if (tid < a.D) s_key[tid] = __fadd_rn(__fmul_rn(__fmul_rn(d, rstd), key_w), key_b);
+    __syncthreads();
+    bf16* idx_row = a.index_cache + (((int64_t)lane_id * a.full_layers + a.index_slot) * a.local_cap + local_row) * a.D;
+    if (tid < a.D) {
+        float o = s_key[tid];
+        if (tid < a.rd) {
+            const int j = tid >> 1;
+            const float angle = __fmul_rn((float)pos, key_f);
+            const float cs = cosf(angle), sn = sinf(angle);
+            const float even = s_key[2 * j], odd = s_key[2 * j + 1];
+            o = (tid & 1) ? __fadd_rn(__fmul_rn(odd, cs), __fmul_rn(even, sn)) : __fsub_rn(__fmul_rn(even, cs), __fmul_rn(odd, sn));
+        }
+        const bf16 ob = __float2bfloat16_rn(o);
+        if (write_cache) idx_row[tid] = ob;
+        if (a.idx_key_new) a.idx_key_new[(int64_t)r * a.D + tid] = ob;
+    }
+    if (tid < a.IH) a.head_w[(int64_t)r * a.IH + tid] = __fmul_rn(hw_v, a.head_scale);
 }
 
 // ---------------------------------------------------------------------------------------------------
@@ -385,9 +519,17 @@ GLMB_API int glmb_add_rmsnorm(const void* update, void* residual, const void* we
     return (int)cudaGetLastError();
 }
 
+static int g_qkv_fast = 1;
+// 1 (default): the single-round-trip kernel; 0: the generic one (comparison runs).
+GLMB_API void glmb_set_qkv_fast(int enabled) { g_qkv_fast = enabled ? 1 : 0; }
+
 GLMB_API int glmb_qkv_a_post(const QkvPostArgs* args, int rows, void* stream) {
     if (args->D > 256 || (args->rd & 1) || (args->Q & 3) || (args->L & 3) || (args->proj_stride & 3)) return 1;
-    GLMB_LAUNCH(qkv_a_post_kernel, rows, 256, 0, (cudaStream_t)stream, *args);
+    const int W = args->L + args->rd;
+    if (g_qkv_fast && args->Q <= 2048 && args->L <= 1024 && args->rd <= 512 && args->IH <= 256 && !(W & 3))
+        GLMB_LAUNCH(qkv_a_post_kernel, rows, 256, 0, (cudaStream_t)stream, *args);
+    else
+        GLMB_LAUNCH(qkv_a_post_generic_kernel, rows, 256, 0, (cudaStream_t)stream, *args);
     return (int)cudaGetLastError();
 }
 

@@ -250,6 +250,11 @@ def add_rmsnorm(update, residual, weight, out, eps):
     _check(lib().glmb_add_rmsnorm(_p(update), _p(residual), _p(weight), _p(out), rows, H, f32(eps), _stream()), "add_rmsnorm")
 
 
+def set_qkv_fast(enabled: int) -> None:
+    """1 (default): the single-round-trip qkv_a_post kernel; 0: the generic one."""
+    lib().glmb_set_qkv_fast(int(enabled))
+
+
 def qkv_a_post(args: QkvPostArgs, rows: int):
     _check(lib().glmb_qkv_a_post(C.byref(args), rows, _stream()), "qkv_a_post")
 

@@ -345,3 +345,56 @@ def test_wait_gives_up_and_reports(native_lib):
     x = torch.ones(4, device=DEV) * 2
     assert float(x.sum()) == 8.0
     peer.close()
+
+
+@pytest.mark.parametrize("shape", ["glm53", "small"])
+def test_qkv_a_post_fast_equals_generic(native_lib, shape):
+    """The single-round-trip kernel and the generic one must agree bit for bit (same rounding points, same reduction trees)."""
+    n = native_lib
+    Q, L, rd, D, IH = (2048, 512, 64, 128, 32) if shape == "glm53" else (128, 64, 16, 32, 4)
+    rows, cap, lanes, layers, slots = 4, 256, 2, 3, 2
+    W = L + rd
+    torch.manual_seed(31)
+    width = (Q + W + D + IH + 3) // 4 * 4
+    proj = (torch.randn(rows, width) * 1.5).to(DEV)
+    qw, kw = bf(torch.randn(Q) * 0.1 + 1).to(DEV), bf(torch.randn(L) * 0.1 + 1).to(DEV)
+    knw, knb = (torch.randn(D) * 0.1 + 1).to(DEV), (torch.randn(D) * 0.05).to(DEV)
+    table = contract.rope_table(cap, rd, 8e6).to(DEV)
+    inv_freq = torch.pow(torch.tensor(8e6), -torch.arange(0, rd, 2, dtype=torch.float32) / rd).to(DEV)
+    pos = torch.tensor([0, 17, 200, 255], dtype=torch.int32, device=DEV)
+    lane = torch.tensor([0, 1, 1, 0], dtype=torch.int32, device=DEV)
+    active = torch.tensor([1, 1, 0, 1], dtype=torch.int32, device=DEV)
+    results = []
+    for fast in (1, 0):
+        n.set_qkv_fast(fast)
+        out = {"q_resid": torch.zeros(rows, Q, dtype=torch.bfloat16, device=DEV), "kv_new": torch.zeros(rows, W, dtype=torch.bfloat16, device=DEV),
+               "kv_cache": torch.zeros(lanes, layers, cap, W, dtype=torch.bfloat16, device=DEV),
+               "index_cache": torch.zeros(lanes, slots, cap, D, dtype=torch.bfloat16, device=DEV),
+               "head_w": torch.zeros(rows, IH, device=DEV), "idx_key_new": torch.zeros(rows, D, dtype=torch.bfloat16, device=DEV)}
+        status = torch.zeros(1, dtype=torch.int32, device=DEV)
+        a = n.QkvPostArgs()
+        a.proj, a.proj_stride = proj.data_ptr(), proj.stride(0)
+        a.q_norm_w, a.kv_norm_w = qw.data_ptr(), kw.data_ptr()
+        a.rope_table, a.inv_freq = table.data_ptr(), inv_freq.data_ptr()
+        a.k_norm_w, a.k_norm_b = knw.data_ptr(), knb.data_ptr()
+        a.row_pos, a.row_lane, a.row_active = pos.data_ptr(), lane.data_ptr(), active.data_ptr()
+        a.q_resid, a.kv_new = out["q_resid"].data_ptr(), out["kv_new"].data_ptr()
+        a.kv_cache, a.index_cache = out["kv_cache"].data_ptr(), out["index_cache"].data_ptr()
+        a.head_w, a.idx_key_new = out["head_w"].data_ptr(), out["idx_key_new"].data_ptr()
+        a.Q, a.L, a.rd, a.D, a.IH = Q, L, rd, D, IH
+        a.has_indexer = 1
+        a.layer, a.layers, a.index_slot, a.full_layers = 1, layers, 1, slots
+        a.local_cap, a.stripe, a.world, a.rank, a.capacity = cap, 64, 1, 0, cap
+        a.eps, a.key_eps, a.head_scale = 1e-5, 1e-6, float(torch.tensor(IH**-0.5, dtype=torch.float32))
+        a.status = status.data_ptr()
+        n.qkv_a_post(a, rows)
+        torch.cuda.synchronize()
+        assert int(status.cpu()[0]) == 0
+        results.append({k: v.cpu() for k, v in out.items()})
+    n.set_qkv_fast(1)
+    for key in results[0]:
+        x, y = results[0][key], results[1][key]
+        assert torch.equal(x.view(torch.int16) if x.dtype == torch.bfloat16 else x, y.view(torch.int16) if y.dtype == torch.bfloat16 else y), key
+    # the inactive row wrote this step's row but not the cache; active rows wrote their cache rows
+    assert bool((results[0]["kv_cache"][1, 1, 200] == 0).all()) and bool((results[0]["kv_cache"][1, 1, 17] != 0).any())
+    assert bool((results[0]["kv_new"][2] != 0).any())
