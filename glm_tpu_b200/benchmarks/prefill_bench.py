@@ -27,6 +27,7 @@ def main(argv=None) -> int:
     ap.add_argument("--repeat", type=int, default=3)
     ap.add_argument("--kv-layout", default="auto")
     ap.add_argument("--shard", type=int, default=1, help="emulate one GPU of this many: experts and vocabulary divided (small profiling runs)")
+    ap.add_argument("--timeline", action="store_true", help="after the timed runs, one more prefill with every launch of the library bracketed by CUDA events")
     ap.add_argument("--out", type=Path)
     args = ap.parse_args(argv)
 
@@ -70,12 +71,31 @@ def main(argv=None) -> int:
         if i > 0:
             times.append(float(dt[0]))
     runner.peer.check_status()
+    timeline_text = ""
+    if args.timeline:
+        from glm_tpu_b200.ops import native
+
+        with native.kernel_timeline() as tl:
+            t0 = time.perf_counter()
+            runner.prefill(0, prompt)
+            torch.cuda.synchronize()
+            wall = time.perf_counter() - t0
+            rows = tl.rows()
+        agg: dict = {}
+        for name, _, ms in rows:
+            agg.setdefault(name, [0, 0.0])
+            agg[name][0] += 1
+            agg[name][1] += ms
+        total = sum(v[1] for v in agg.values())
+        timeline_text = (f"\nbracketed prefill: wall {wall * 1e3:.1f} ms, library kernels {total:.1f} ms over {len(rows)} launches (the rest is framework glue: "
+                         f"route sorting, copies, casts)\n| kernel | launches | total ms | share of kernel time |\n|---|---|---|---|\n"
+                         + "".join(f"| {k} | {c} | {t:.2f} | {t / total:.1%} |\n" for k, (c, t) in sorted(agg.items(), key=lambda kv: -kv[1][1])))
     if rank == 0:
         best, med = min(times), statistics.median(times)
         text = (f"prefill: GLM-5.3 architecture, {args.layers} of 78 layers, {g.num_routed_experts} experts, {world} GPU(s), kv layout {runner.kv_layout}, prompt {args.prompt} tokens in "
                 f"chunks of {args.chunk}, context capacity {args.context}\n"
                 f"time to first token: best {best * 1e3:.1f} ms, median {med * 1e3:.1f} ms ({args.repeat} runs after a warm-up)\n"
-                f"prefill rate: {args.prompt / best:.0f} tokens/s (best), {args.prompt / med:.0f} tokens/s (median); first token {token}\n")
+                f"prefill rate: {args.prompt / best:.0f} tokens/s (best), {args.prompt / med:.0f} tokens/s (median); first token {token}\n" + timeline_text)
         print(text)
         if args.out:
             args.out.parent.mkdir(parents=True, exist_ok=True)

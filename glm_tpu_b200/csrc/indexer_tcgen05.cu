@@ -8,7 +8,7 @@
 // exact in fp32, so the three partial dots add up to the fp32-accurate q . key.
 //
 //   all threads   split the query row into pieces and write them to shared memory in the 128-byte-swizzled K-major layout
-//   warp 0        TMA: 128 keys x 128 features (two 64-wide boxes) straight from the index cache
+//   thread 0      TMA: 128 keys x 128 features (two 64-wide boxes) straight from the index cache, issued first
 //   warp 1        one lane issues 8 tcgen05.mma (M 128, N 96, K 16) into 96 TMEM columns
 //   warps 2-5     tcgen05.ld (lane = key), per-head relu and weighting, store the score at its global position in this
 //                 rank's score row and in every peer's (fused all-gather), then the last CTA signals
@@ -31,11 +31,20 @@
 #define IT_SMEM_BYTES (IT_A_BYTES + IT_B_BYTES + 1024 + 128 + IT_IH * 4)
 #define IT_TMEM_COLS 128
 
+// When q_raw is set, the query comes straight from the q_b projection (fp32, before RoPE) and the kernel rotates its first
+// rd features itself (fp32 cos/sin of position * inv_freq, interleaved pairs: the arithmetic of q_post).
+struct IndexerRawQuery {
+    const float* q_raw;  // [rows, q_stride], index head h at q_offset + h * 128
+    int64_t q_stride, q_offset;
+    const float* inv_freq;  // [rd / 2]
+    int rd;
+};
+
 __global__ void __launch_bounds__(IT_THREADS)
 indexer_score_tc_kernel(const __grid_constant__ CUtensorMap map_keys, const float* __restrict__ q_idx, const float* __restrict__ head_w,
                         const int* __restrict__ row_pos, const int* __restrict__ row_lane, int index_slot, int full_layers, int local_cap,
                         int stripe, int world, int rank, int capacity, int64_t score_stride, float scale, float* __restrict__ scores,
-                        int64_t scores_offset, PeerComm comm, int sig, uint32_t* status) {
+                        int64_t scores_offset, PeerComm comm, int sig, uint32_t* status, IndexerRawQuery raw) {
     GLMB_PDL_PROLOGUE();
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* a_s = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -60,18 +69,36 @@ indexer_score_tc_kernel(const __grid_constant__ CUtensorMap map_keys, const floa
             mbar_init(full_bar, 1);
             mbar_init(acc_bar, 1);
             asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            // the key tile is requested first, so that it lands while the query pieces are being built
+            const int cache_row = (row_lane[r] * full_layers + index_slot) * local_cap + j0;
+            mbar_expect_tx(full_bar, IT_A_BYTES);
+            tma_load_2d(a_s, &map_keys, full_bar, 0, cache_row);
+            tma_load_2d(a_s + IT_KEYS * 128, &map_keys, full_bar, 64, cache_row);
         }
         if (warp == 1) {
             asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(IT_TMEM_COLS) : "memory");
             asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
         }
         // query row -> three exact bf16 pieces, rows [piece * 32 + head] of the N operand
-        const float* q = q_idx + (int64_t)r * IT_IH * IT_D;
+        const float* q = raw.q_raw ? raw.q_raw + (int64_t)r * raw.q_stride + raw.q_offset : q_idx + (int64_t)r * IT_IH * IT_D;
         for (int i = threadIdx.x; i < IT_IH * IT_D / 8; i += IT_THREADS) {  // one 8-feature chunk of one head per step
             const int h = i / (IT_D / 8), c8 = i % (IT_D / 8);             // c8: 16-byte chunk index along K (0..15)
             const float4 x0 = *reinterpret_cast<const float4*>(q + h * IT_D + c8 * 8);
             const float4 x1 = *reinterpret_cast<const float4*>(q + h * IT_D + c8 * 8 + 4);
-            const float v[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+            float v[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+            if (raw.q_raw && c8 * 8 < raw.rd) {
+#pragma unroll
+                for (int pr = 0; pr < 4; ++pr) {
+                    const int d = c8 * 8 + 2 * pr;
+                    if (d < raw.rd) {
+                        const float angle = __fmul_rn((float)pos, raw.inv_freq[d >> 1]);
+                        const float cs = cosf(angle), sn = sinf(angle);
+                        const float even = v[2 * pr], odd = v[2 * pr + 1];
+                        v[2 * pr] = __fsub_rn(__fmul_rn(even, cs), __fmul_rn(odd, sn));
+                        v[2 * pr + 1] = __fadd_rn(__fmul_rn(odd, cs), __fmul_rn(even, sn));
+                    }
+                }
+            }
             float hi[8], mid[8], lo[8];
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
@@ -97,14 +124,7 @@ indexer_score_tc_kernel(const __grid_constant__ CUtensorMap map_keys, const floa
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t tmem_base = *tmem_slot;
 
-        if (warp == 0) {
-            if (lane == 0) {
-                const int cache_row = (row_lane[r] * full_layers + index_slot) * local_cap + j0;
-                mbar_expect_tx(full_bar, IT_A_BYTES);
-                tma_load_2d(a_s, &map_keys, full_bar, 0, cache_row);
-                tma_load_2d(a_s + IT_KEYS * 128, &map_keys, full_bar, 64, cache_row);
-            }
-        } else if (warp == 1) {
+        if (warp == 1) {
             if (lane == 0) {
                 constexpr uint32_t idesc = umma_idesc_bf16(IT_KEYS, IT_N);
                 if (mbar_wait(full_bar, 0)) {
@@ -161,13 +181,40 @@ indexer_score_tc_kernel(const __grid_constant__ CUtensorMap map_keys, const floa
 
 // Same contract as glmb_indexer_score for D == 128 and IH == 32.  cache_rows: rows of the whole index cache viewed as
 // [lanes * full_layers * local_cap, 128] bf16 (the TMA tensor map covers it; a tile is addressed by its first row).
+static int indexer_tc_launch(const float* q_idx, const IndexerRawQuery& raw, const float* head_w, const void* index_cache, int64_t cache_rows,
+                             const int* row_pos, const int* row_lane, int rows, int IH, int D, int index_slot, int full_layers, int local_cap,
+                             int stripe, int world, int rank, int capacity, int max_ctx, int64_t score_stride, float scale, float* scores,
+                             int64_t scores_offset, const PeerComm* comm, int sig, uint32_t* status, void* stream);
+
 GLMB_API int glmb_indexer_score_tc(const float* q_idx, const float* head_w, const void* index_cache, int64_t cache_rows, const int* row_pos,
                                    const int* row_lane, int rows, int IH, int D, int index_slot, int full_layers, int local_cap, int stripe,
                                    int world, int rank, int capacity, int max_ctx, int64_t score_stride, float scale, float* scores,
                                    int64_t scores_offset, const PeerComm* comm, int sig, uint32_t* status, void* stream) {
-    if (IH != IT_IH || D != IT_D || rows < 1 || cache_rows < 1 || (reinterpret_cast<uintptr_t>(index_cache) & 15) ||
-        (reinterpret_cast<uintptr_t>(q_idx) & 15))
-        return 1;
+    if (!q_idx || (reinterpret_cast<uintptr_t>(q_idx) & 15)) return 1;
+    IndexerRawQuery raw;
+    memset(&raw, 0, sizeof(raw));
+    return indexer_tc_launch(q_idx, raw, head_w, index_cache, cache_rows, row_pos, row_lane, rows, IH, D, index_slot, full_layers, local_cap, stripe,
+                             world, rank, capacity, max_ctx, score_stride, scale, scores, scores_offset, comm, sig, status, stream);
+}
+
+// The same with the query taken from the raw q_b projection (fp32 [rows, q_stride], index heads at q_offset) and rotated in-kernel.
+GLMB_API int glmb_indexer_score_tc_raw(const float* q_raw, int64_t q_stride, int64_t q_offset, const float* inv_freq, int rd, const float* head_w,
+                                       const void* index_cache, int64_t cache_rows, const int* row_pos, const int* row_lane, int rows, int IH,
+                                       int D, int index_slot, int full_layers, int local_cap, int stripe, int world, int rank, int capacity,
+                                       int max_ctx, int64_t score_stride, float scale, float* scores, int64_t scores_offset,
+                                       const PeerComm* comm, int sig, uint32_t* status, void* stream) {
+    if (!q_raw || !inv_freq || (rd & 1) || rd > D || (q_stride & 3) || (q_offset & 3) || (reinterpret_cast<uintptr_t>(q_raw) & 15)) return 1;
+    IndexerRawQuery raw;
+    raw.q_raw = q_raw; raw.q_stride = q_stride; raw.q_offset = q_offset; raw.inv_freq = inv_freq; raw.rd = rd;
+    return indexer_tc_launch(nullptr, raw, head_w, index_cache, cache_rows, row_pos, row_lane, rows, IH, D, index_slot, full_layers, local_cap,
+                             stripe, world, rank, capacity, max_ctx, score_stride, scale, scores, scores_offset, comm, sig, status, stream);
+}
+
+static int indexer_tc_launch(const float* q_idx, const IndexerRawQuery& raw, const float* head_w, const void* index_cache, int64_t cache_rows,
+                             const int* row_pos, const int* row_lane, int rows, int IH, int D, int index_slot, int full_layers, int local_cap,
+                             int stripe, int world, int rank, int capacity, int max_ctx, int64_t score_stride, float scale, float* scores,
+                             int64_t scores_offset, const PeerComm* comm, int sig, uint32_t* status, void* stream) {
+    if (IH != IT_IH || D != IT_D || rows < 1 || cache_rows < 1 || (reinterpret_cast<uintptr_t>(index_cache) & 15)) return 1;
     PeerComm c;
     if (comm) c = *comm; else { memset(&c, 0, sizeof(c)); c.world = 1; }
     CUtensorMap map_keys;
@@ -182,6 +229,6 @@ GLMB_API int glmb_indexer_score_tc(const float* q_idx, const float* head_w, cons
     const int owned_max = (max_ctx / page) * stripe + min(max_ctx % page, stripe);
     dim3 grid(ceil_div(owned_max > 0 ? owned_max : 1, IT_KEYS), rows);
     GLMB_LAUNCH(indexer_score_tc_kernel, grid, IT_THREADS, IT_SMEM_BYTES, (cudaStream_t)stream, map_keys, q_idx, head_w, row_pos, row_lane,
-                index_slot, full_layers, local_cap, stripe, world, rank, capacity, score_stride, scale, scores, scores_offset, c, sig, status);
+                index_slot, full_layers, local_cap, stripe, world, rank, capacity, score_stride, scale, scores, scores_offset, c, sig, status, raw);
     return (int)cudaGetLastError();
 }

@@ -423,11 +423,21 @@ __global__ void __launch_bounds__(256) q_post_kernel(QPostArgs a) {
 #define QA_COLS 128
 #define QA_BATCH 12     // weight rows in flight per thread
 #define QA_MAX_NOPE 256 // widest no-position part of a query head the kernel stages
+// When q_proj is set the kernel takes the raw q_b projection (fp32 [rows, q_stride], head h at h * (nope + rd)) instead of
+// the rounded q_nope, and also rotates the rope part of its head into q_full: the separate q_post launch is not needed.
+struct QAbsorbSource {
+    const float* q_proj;
+    int64_t q_stride;
+    const bf16* rope_table;  // [capacity, rd] cos | sin
+    const int* row_pos;
+    int capacity;
+};
+
 template <int R>
 __global__ void __launch_bounds__(256)
 q_absorb_kernel(const bf16* __restrict__ q_nope, int rows, const bf16* __restrict__ kv_b, int heads_local, int head_base,
                 int heads_total, int nope, int vdim, int L, int rd, bf16* __restrict__ q_full, int64_t q_full_offset,
-                PeerComm comm, int sig) {
+                PeerComm comm, int sig, QAbsorbSource src) {
     GLMB_PDL_PROLOGUE();
     __shared__ float red[8][R][QA_COLS];
     __shared__ float qs[R][QA_MAX_NOPE];
@@ -437,7 +447,8 @@ q_absorb_kernel(const bf16* __restrict__ q_nope, int rows, const bf16* __restric
     const int d0 = warp * per, d1 = min(nope, d0 + per);
     for (int i = threadIdx.x; i < R * nope; i += blockDim.x) {
         const int r = i / nope, d = i % nope;
-        qs[r][d] = __bfloat162float(q_nope[((int64_t)(r < rows ? r : 0) * heads_local + h) * nope + d]);
+        qs[r][d] = src.q_proj ? bf16_round(src.q_proj[(int64_t)(r < rows ? r : 0) * src.q_stride + h * (nope + rd) + d])
+                              : __bfloat162float(q_nope[((int64_t)(r < rows ? r : 0) * heads_local + h) * nope + d]);
     }
     float acc[R][4];
 #pragma unroll
@@ -490,8 +501,24 @@ q_absorb_kernel(const bf16* __restrict__ q_nope, int rows, const bf16* __restric
         for (int p = 0; p < comm.world; ++p)
             if (p != comm.rank) reinterpret_cast<bf16*>(comm.data[p] + q_full_offset)[at] = o;
     }
+    if (src.q_proj && blockIdx.y == 0) {
+        // rope part of this head: interleaved pairs, bf16 table, fp32 products, one rounding (as q_post does)
+        const int half = rd / 2;
+        for (int i = threadIdx.x; i < rows * half; i += blockDim.x) {
+            const int r = i / half, j = i % half;
+            const int pos = min(max(src.row_pos[r], 0), src.capacity - 1);
+            const float* q = src.q_proj + (int64_t)r * src.q_stride + h * (nope + rd) + nope;
+            const float even = bf16_round(q[2 * j]), odd = bf16_round(q[2 * j + 1]);
+            const float cs = __bfloat162float(src.rope_table[(int64_t)pos * rd + j]);
+            const float sn = __bfloat162float(src.rope_table[(int64_t)pos * rd + half + j]);
+            bf16* dst = q_full + ((int64_t)r * heads_total + head_base + h) * W + L;
+            dst[2 * j] = __float2bfloat16_rn(__fsub_rn(__fmul_rn(even, cs), __fmul_rn(odd, sn)));
+            dst[2 * j + 1] = __float2bfloat16_rn(__fadd_rn(__fmul_rn(odd, cs), __fmul_rn(even, sn)));
+        }
+        __syncthreads();
+    }
     if (comm.world > 1 && blockIdx.y == 0) {
-        // the rope part was written locally by q_post (an earlier kernel); forward it to the peers
+        // the rope part was written locally (above, or by q_post in an earlier kernel); forward it to the peers
         for (int i = threadIdx.x; i < rows * rd; i += blockDim.x) {
             const int r = i / rd, j = i % rd;
             const int64_t at = ((int64_t)r * heads_total + head_base + h) * W + L + j;
@@ -541,6 +568,17 @@ GLMB_API int glmb_q_post(const QPostArgs* args, int rows, void* stream) {
     return (int)cudaGetLastError();
 }
 
+static int launch_q_absorb(const void* q_nope, int rows, const void* kv_b, int heads_local, int head_base, int heads_total, int nope, int vdim,
+                           int L, int rd, void* q_full, int64_t q_full_offset, const PeerComm& c, int sig, const QAbsorbSource& src, void* stream) {
+    dim3 grid(heads_local, ceil_div(L, QA_COLS));
+#define CALL(RR)                                                                                                              \
+    GLMB_LAUNCH(q_absorb_kernel<RR>, grid, 256, 0, (cudaStream_t)stream, (const bf16*)q_nope, rows, (const bf16*)kv_b, heads_local, head_base, \
+                                                                heads_total, nope, vdim, L, rd, (bf16*)q_full, q_full_offset, c, sig, src)
+    if (rows <= 1) { CALL(1); } else if (rows <= 2) { CALL(2); } else if (rows <= 4) { CALL(4); } else { CALL(8); }
+#undef CALL
+    return (int)cudaGetLastError();
+}
+
 // q_full must be the staging-buffer address `comm->data[rank] + q_full_offset` when world > 1.
 GLMB_API int glmb_q_absorb(const void* q_nope, int rows, const void* kv_b, int heads_local, int head_base, int heads_total,
                            int nope, int vdim, int L, int rd, void* q_full, int64_t q_full_offset, const PeerComm* comm, int sig,
@@ -548,11 +586,20 @@ GLMB_API int glmb_q_absorb(const void* q_nope, int rows, const void* kv_b, int h
     if (rows < 1 || rows > GLMB_MAX_ROWS || (L & 3) || nope > QA_MAX_NOPE) return 1;
     PeerComm c;
     if (comm) c = *comm; else { memset(&c, 0, sizeof(c)); c.world = 1; }
-    dim3 grid(heads_local, ceil_div(L, QA_COLS));
-#define CALL(RR)                                                                                                              \
-    GLMB_LAUNCH(q_absorb_kernel<RR>, grid, 256, 0, (cudaStream_t)stream, (const bf16*)q_nope, rows, (const bf16*)kv_b, heads_local, head_base, \
-                                                                heads_total, nope, vdim, L, rd, (bf16*)q_full, q_full_offset, c, sig)
-    if (rows <= 1) { CALL(1); } else if (rows <= 2) { CALL(2); } else if (rows <= 4) { CALL(4); } else { CALL(8); }
-#undef CALL
-    return (int)cudaGetLastError();
+    QAbsorbSource src;
+    memset(&src, 0, sizeof(src));
+    return launch_q_absorb(q_nope, rows, kv_b, heads_local, head_base, heads_total, nope, vdim, L, rd, q_full, q_full_offset, c, sig, src, stream);
+}
+
+// The same with the q_post work folded in: q_proj is the fp32 output of the q_b projection ([rows, q_stride]); the kernel
+// rounds the no-position parts itself and writes the rotated rope parts of its heads into q_full.
+GLMB_API int glmb_q_absorb_from_proj(const float* q_proj, int64_t q_stride, const void* rope_table, const int* row_pos, int capacity,
+                                     int rows, const void* kv_b, int heads_local, int head_base, int heads_total, int nope, int vdim,
+                                     int L, int rd, void* q_full, int64_t q_full_offset, const PeerComm* comm, int sig, void* stream) {
+    if (rows < 1 || rows > GLMB_MAX_ROWS || (L & 3) || nope > QA_MAX_NOPE || (rd & 1) || !q_proj || !rope_table || !row_pos) return 1;
+    PeerComm c;
+    if (comm) c = *comm; else { memset(&c, 0, sizeof(c)); c.world = 1; }
+    QAbsorbSource src;
+    src.q_proj = q_proj; src.q_stride = q_stride; src.rope_table = (const bf16*)rope_table; src.row_pos = row_pos; src.capacity = capacity;
+    return launch_q_absorb(nullptr, rows, kv_b, heads_local, head_base, heads_total, nope, vdim, L, rd, q_full, q_full_offset, c, sig, src, stream);
 }

@@ -186,6 +186,7 @@ class GlmMoeDsaModel:
         # independent branches of the decode step (shared expert | routed experts; absorbed query | indexer + top-k) run on two
         # streams; GLM_B200_OVERLAP=0 keeps everything on one stream
         self.side = torch.cuda.Stream(device=self.device) if os.environ.get("GLM_B200_OVERLAP", "1") != "0" else None
+        self.fold_q_post = os.environ.get("GLM_B200_FOLD_Q_POST", "1") != "0"
 
     # ------------------------------------------------------------------------------ helpers
     @property
@@ -289,7 +290,12 @@ class GlmMoeDsaModel:
         b.heads_local, b.head_base, b.heads_total = hl, hb, ht
         b.nope, b.rd, b.L, b.IH, b.D = g.qk_nope_head_dim, rd, L, IH, D
         b.has_indexer, b.capacity = int(full), cache.context_capacity
-        native.q_post(b, rows)
+        # decode: the q_post work is folded into its consumers (q_absorb rounds and rotates its heads, the tcgen05 indexer
+        # rotates the index query), one launch less per layer; prefill and other head shapes keep the separate kernel
+        fold = decode and self.fold_q_post and self.trace is None and (not full or native.indexer_takes_raw_query(IH, D))
+        if not fold:
+            native.q_post(b, rows)
+        fold_args = dict(q_proj=ws.q_proj, rope_table=self.rope, row_pos=row_pos, capacity=cache.context_capacity) if fold else {}
 
         forked = None
         if decode:
@@ -299,10 +305,10 @@ class GlmMoeDsaModel:
                 forked = self._fork()
                 with torch.cuda.stream(self.side):
                     native.q_absorb(ws.q_nope, rows, lw.kv_b, hl, hb, ht, g.qk_nope_head_dim, g.v_head_dim, L, rd, ws.q_full, 0, None,
-                                    native.SIG_Q)
+                                    native.SIG_Q, **fold_args)
             else:
                 native.q_absorb(ws.q_nope, rows, lw.kv_b, hl, hb, ht, g.qk_nope_head_dim, g.v_head_dim, L, rd, ws.q_full,
-                                ws.r_q.offset if xf else 0, kx, native.SIG_Q)
+                                ws.r_q.offset if xf else 0, kx, native.SIG_Q, **fold_args)
             if gather and not xf:
                 self._allgather_heads(ws.q_full[:rows])
         else:
@@ -316,7 +322,8 @@ class GlmMoeDsaModel:
             native.indexer_score(ws.q_idx, ws.head_w, state.index_cache, row_pos, row_lane, rows, IH, D, g.index_slot(layer),
                                  len(g.full_layers), cache.local_capacity, cache.stripe, cw, cr,
                                  cache.context_capacity, max_ctx, ws.score_stride, self.index_scale, ws.scores,
-                                 ws.r_scores.offset if xf else 0, kx, native.SIG_SCORES, self.peer.status_ptr)
+                                 ws.r_scores.offset if xf else 0, kx, native.SIG_SCORES, self.peer.status_ptr,
+                                 **(dict(q_raw=ws.q_proj, q_offset=hl * g.qk_head_dim, inv_freq=self.inv_freq, rd=rd) if fold else {}))
             if gather and not xf:
                 self._merge_scores(ws.scores[:rows], max_ctx)
             native.topk_select(ws.scores, row_pos, rows, cache.context_capacity, ws.score_stride, g.index_top_k, cache.stripe,

@@ -264,7 +264,16 @@ def q_post(args: QPostArgs, rows: int):
 
 
 def q_absorb(q_nope, rows, kv_b, heads_local, head_base, heads_total, nope, vdim, L, rd, q_full, q_full_offset=0, comm=None,
-             sig=SIG_Q):
+             sig=SIG_Q, *, q_proj=None, rope_table=None, row_pos=None, capacity=0):
+    """``q_proj`` (fp32 output of the q_b projection) replaces ``q_nope`` and makes the kernel do the q_post work of its heads too."""
+    if q_proj is not None:
+        _check(
+            lib().glmb_q_absorb_from_proj(_p(q_proj), C.c_int64(q_proj.stride(0)), _p(rope_table), _p(row_pos), capacity, rows, _p(kv_b),
+                                          heads_local, head_base, heads_total, nope, vdim, L, rd, _p(q_full), C.c_int64(q_full_offset),
+                                          _comm(comm), sig, _stream()),
+            "q_absorb_from_proj",
+        )
+        return
     _check(
         lib().glmb_q_absorb(_p(q_nope), rows, _p(kv_b), heads_local, head_base, heads_total, nope, vdim, L, rd, _p(q_full),
                             C.c_int64(q_full_offset), _comm(comm), sig, _stream()),
@@ -273,6 +282,10 @@ def q_absorb(q_nope, rows, kv_b, heads_local, head_base, heads_total, nope, vdim
 
 
 # ----------------------------------------------------------------------------- indexer
+def indexer_takes_raw_query(IH: int, D: int) -> bool:
+    return D == 128 and IH == 32 and _indexer_tensor_cores()
+
+
 def _indexer_tensor_cores() -> bool:
     import os
 
@@ -280,7 +293,21 @@ def _indexer_tensor_cores() -> bool:
 
 
 def indexer_score(q_idx, head_w, index_cache, row_pos, row_lane, rows, IH, D, index_slot, full_layers, local_cap, stripe, world,
-                  rank, capacity, max_ctx, score_stride, scale, scores, scores_offset=0, comm=None, sig=SIG_SCORES, status=None):
+                  rank, capacity, max_ctx, score_stride, scale, scores, scores_offset=0, comm=None, sig=SIG_SCORES, status=None, *,
+                  q_raw=None, q_offset=0, inv_freq=None, rd=0):
+    """``q_raw`` (fp32 q_b projection, index heads at ``q_offset``) replaces ``q_idx``: the tcgen05 kernel applies the RoPE itself."""
+    if q_raw is not None:
+        if not indexer_takes_raw_query(IH, D):
+            raise ValueError("the raw-query path needs the tcgen05 indexer (32 heads of 128)")
+        _check(
+            lib().glmb_indexer_score_tc_raw(_p(q_raw), C.c_int64(q_raw.stride(0)), C.c_int64(q_offset), _p(inv_freq), rd, _p(head_w),
+                                            _p(index_cache), C.c_int64(index_cache.numel() // D), _p(row_pos), _p(row_lane), rows, IH, D,
+                                            index_slot, full_layers, local_cap, stripe, world, rank, capacity, max_ctx,
+                                            C.c_int64(score_stride), f32(scale), _p(scores), C.c_int64(scores_offset), _comm(comm), sig,
+                                            _p(status), _stream()),
+            "indexer_score_tc_raw",
+        )
+        return
     if D == 128 and IH == 32 and _indexer_tensor_cores():
         # the usual head shape: keys x query pieces on tcgen05 (see csrc/indexer_tcgen05.cu)
         _check(

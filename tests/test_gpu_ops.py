@@ -398,3 +398,49 @@ def test_qkv_a_post_fast_equals_generic(native_lib, shape):
     # the inactive row wrote this step's row but not the cache; active rows wrote their cache rows
     assert bool((results[0]["kv_cache"][1, 1, 200] == 0).all()) and bool((results[0]["kv_cache"][1, 1, 17] != 0).any())
     assert bool((results[0]["kv_new"][2] != 0).any())
+
+
+def test_q_post_fold_is_bit_identical(native_lib):
+    """q_absorb fed with the raw q_b projection, and the tcgen05 indexer fed with the raw index query, against the two-kernel
+    path (q_post first): the absorbed queries, their rope parts and the index scores must agree bit for bit."""
+    n = native_lib
+    torch.manual_seed(41)
+    rows, hl, nope, rd, vd, L, IH, D, cap = 3, 8, 192, 64, 256, 512, 32, 128, 2048
+    qk, W = nope + rd, L + rd
+    q_proj = (torch.randn(rows, hl * qk + IH * D) * 0.7).to(DEV)
+    kv_b = bf(torch.randn(hl, nope + vd, L) * 0.05).to(DEV)
+    table = contract.rope_table(cap, rd, 8e6).to(DEV)
+    inv_freq = torch.pow(torch.tensor(8e6), -torch.arange(0, rd, 2, dtype=torch.float32) / rd).to(DEV)
+    pos = torch.tensor([5, 1000, 2047], dtype=torch.int32, device=DEV)
+    lane = torch.zeros(rows, dtype=torch.int32, device=DEV)
+    hw = (torch.randn(rows, IH) * 0.2).to(DEV)
+    keys = bf(torch.randn(1, 1, cap, D)).to(DEV)
+    scale = float(torch.tensor(D**-0.5, dtype=torch.float32))
+    # two-kernel path
+    q_nope = torch.zeros(rows, hl, nope, dtype=torch.bfloat16, device=DEV)
+    q_full_a = torch.zeros(rows, hl, W, dtype=torch.bfloat16, device=DEV)
+    q_idx = torch.zeros(rows, IH, D, device=DEV)
+    b = n.QPostArgs()
+    b.q, b.q_stride = q_proj.data_ptr(), q_proj.stride(0)
+    b.rope_table, b.inv_freq, b.row_pos = table.data_ptr(), inv_freq.data_ptr(), pos.data_ptr()
+    b.q_nope, b.q_full, b.q_idx = q_nope.data_ptr(), q_full_a.data_ptr(), q_idx.data_ptr()
+    b.heads_local, b.head_base, b.heads_total = hl, 0, hl
+    b.nope, b.rd, b.L, b.IH, b.D = nope, rd, L, IH, D
+    b.has_indexer, b.capacity = 1, cap
+    n.q_post(b, rows)
+    n.q_absorb(q_nope, rows, kv_b, hl, 0, hl, nope, vd, L, rd, q_full_a)
+    scores_a = torch.full((rows, cap), float("nan"), device=DEV)
+    n.indexer_score(q_idx, hw, keys, pos, lane, rows, IH, D, 0, 1, cap, 64, 1, 0, cap, cap, cap, scale, scores_a)
+    # folded path
+    q_full_b = torch.zeros(rows, hl, W, dtype=torch.bfloat16, device=DEV)
+    n.q_absorb(None, rows, kv_b, hl, 0, hl, nope, vd, L, rd, q_full_b, q_proj=q_proj, rope_table=table, row_pos=pos, capacity=cap)
+    scores_b = torch.full((rows, cap), float("nan"), device=DEV)
+    n.indexer_score(None, hw, keys, pos, lane, rows, IH, D, 0, 1, cap, 64, 1, 0, cap, cap, cap, scale, scores_b, q_raw=q_proj, q_offset=hl * qk,
+                    inv_freq=inv_freq, rd=rd)
+    torch.cuda.synchronize()
+    assert torch.equal(q_full_a.view(torch.int16), q_full_b.view(torch.int16))
+    assert bool((q_full_a[..., L:] != 0).any())
+    for r in range(rows):
+        c = int(pos[r]) + 1
+        assert torch.equal(scores_a[r, :c], scores_b[r, :c])
+        assert torch.isnan(scores_b[r, c:]).all()
