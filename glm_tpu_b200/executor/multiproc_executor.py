@@ -89,10 +89,15 @@ def summarize(run_dir: Path, world: int, sequence: int = 0) -> dict:
     }
 
 
-def resident_controller(fl: fleet_mod.Fleet, run_dir: Path, world: int, profile_check, deadline: float, poll: float) -> dict:
-    """Feed ``inbox/NNNN.json`` requests to the loaded workers until ``inbox/stop.json`` or a failure."""
+def resident_controller(fl: fleet_mod.Fleet, run_dir: Path, world: int, profile_check, deadline: float, poll: float, *,
+                        initial: bool = False, print_answers: bool = False) -> dict:
+    """Feed ``inbox/NNNN.json`` requests to the loaded workers until ``inbox/stop.json`` or a failure.
+
+    ``initial``: the session was started with a request (sequence 0); its result is reported as soon as the workers are ready
+    for the next one, not only when the session ends."""
     inbox = run_dir / proto.INBOX_DIR
     served, sequence = [], 0
+    reported_initial = not initial
     while time.monotonic() < deadline:
         codes = fl.poll()
         if any(c is not None for c in codes):
@@ -100,6 +105,11 @@ def resident_controller(fl: fleet_mod.Fleet, run_dir: Path, world: int, profile_
         ready = run_dir / proto.READY_FILE
         ready_seq = json.loads(ready.read_text()).get("sequence", -1) if ready.exists() else -1
         if ready_seq == sequence:
+            if not reported_initial:
+                reported_initial = True
+                if print_answers and (run_dir / proto.ANSWER_FILE).exists():
+                    print((run_dir / proto.ANSWER_FILE).read_text(), flush=True)
+                print(proto.STDOUT_RESIDENT_RESULT + json.dumps({"sequence": 0, **summarize(run_dir, world)}), flush=True)
             if sequence > 0 and sequence not in served:
                 summary = summarize(run_dir, world, sequence)
                 persist_json(proto.result_dir(run_dir, sequence) / proto.MEASUREMENT_FILE, summary)
@@ -147,7 +157,8 @@ def main(argv=None) -> int:
             def check(p):
                 pass  # the workers validate against the loaded profile; the controller only bounds and parses
 
-            terminal["resident"] = resident_controller(fl, run_dir, args.gpus, check, deadline, args.poll_seconds)
+            terminal["resident"] = resident_controller(fl, run_dir, args.gpus, check, deadline, args.poll_seconds,
+                                                       initial=payload is not None, print_answers=args.print_answers)
             codes = fl.wait(time.monotonic() + 30.0)
         else:
             codes = fl.wait(deadline)
