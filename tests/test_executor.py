@@ -84,9 +84,13 @@ def test_resident_session_serves_the_inbox(tmp_path):
         assert (run_dir / proto.READY_FILE).exists(), "".join(lines)
         req1, path1 = prepared(tmp_path, name="next.json", rid="q2", ids=(9, 10, 11), n=2)
         os.link(path1, run_dir / proto.INBOX_DIR / proto.inbox_name(1))  # publish: never overwrites
-        while time.time() < deadline and not any(ln.startswith(proto.STDOUT_RESIDENT_RESULT) for ln in lines):
+        def results():
+            return [json.loads(ln[len(proto.STDOUT_RESIDENT_RESULT):]) for ln in lines if ln.startswith(proto.STDOUT_RESIDENT_RESULT)]
+
+        while time.time() < deadline and len(results()) < 2:
             time.sleep(0.1)
-        result = json.loads(next(ln for ln in lines if ln.startswith(proto.STDOUT_RESIDENT_RESULT))[len(proto.STDOUT_RESIDENT_RESULT):])
+        first, result = results()[:2]
+        assert first["sequence"] == 0 and first["agree"]  # the request the session was started with is reported at once
         assert result["sequence"] == 1 and result["agree"] and result["requests"][0]["request_id"] == "q2"
         assert (proto.result_dir(run_dir, 1) / proto.TOKENS_FILE).exists()
         (run_dir / proto.INBOX_DIR / proto.STOP_FILE).write_text('{"stop":true}')
