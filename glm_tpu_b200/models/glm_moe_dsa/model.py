@@ -187,6 +187,11 @@ class GlmMoeDsaModel:
         # streams; GLM_B200_OVERLAP=0 keeps everything on one stream
         self.side = torch.cuda.Stream(device=self.device) if os.environ.get("GLM_B200_OVERLAP", "1") != "0" else None
         self.fold_q_post = os.environ.get("GLM_B200_FOLD_Q_POST", "1") != "0"
+        # Prefill projections whose K is split over the GPUs: the GEMM with the all-reduce in its epilogue is 1.25-1.7x the
+        # GEMM + library all-reduce on 2 GPUs and 0.85-0.9x on 8 (one SM per owned tile reads seven partial tiles), so it is
+        # the default up to 4 GPUs; GLM_B200_PREFILL_GEMM_AR=fused|nccl overrides.
+        choice = os.environ.get("GLM_B200_PREFILL_GEMM_AR", "auto")
+        self.prefill_gemm_allreduce = choice == "fused" or (choice == "auto" and self.world <= 4)
 
     # ------------------------------------------------------------------------------ helpers
     @property
@@ -231,6 +236,8 @@ class GlmMoeDsaModel:
         """``bf16(sum over GPUs of x_r @ w_r.T)`` ([rows, hidden]) in one kernel: tcgen05 tiles whose epilogue exchanges the
         partial tiles over NVLink.  None when this workspace has no staging for it or the shape does not fit."""
         rows, K = x.shape
+        if not self.prefill_gemm_allreduce:
+            return None
         if ws.r_gemm_out is None or w.shape[0] != self.g.hidden_size or K % 8 or x.stride(1) != 1 or x.stride(0) % 8 \
                 or x.data_ptr() % 16 or w.data_ptr() % 16 or w.stride(0) % 8:
             return None
