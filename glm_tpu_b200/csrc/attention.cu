@@ -208,6 +208,169 @@ sparse_mla_partial_kernel(const bf16* __restrict__ q_full, const bf16* __restric
     }
 }
 
+// ---------------------------------------------------------------------------------------------------
+// Many query rows (prefill) on one GPU's cache: one CTA per (query row, block of 16 heads) walks ALL of the row's
+// selected keys in chunks of 64 with a running (max, sum) per head and rescaled accumulators, normalizes at the
+// end and stores bf16 directly.  Nothing is written per chunk, so the [rows, chunks, heads, latent] fp32 partials
+// of the split kernels (the bulk of their memory traffic when there are thousands of rows) and the merge kernel
+// disappear.  Decode keeps the split kernels: with 1-8 rows the chunks are the parallelism.
+template <int TPW, int PVW>
+__global__ void __launch_bounds__(AT_THREADS)
+sparse_mla_rows_kernel(const bf16* __restrict__ q_full, const bf16* __restrict__ kv_cache, const int* __restrict__ sel_local,
+                       const int* __restrict__ sel_counts, const int* __restrict__ row_lane, int H, int rd, int layer, int layers,
+                       int local_cap, int top_k, float scale, bf16* __restrict__ o_lat, uint32_t* status) {
+    GLMB_PDL_PROLOGUE();
+    constexpr int L = 8 * TPW * PVW;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int W = L + rd;
+    const int WP = W + 8;
+    bf16* q_s = reinterpret_cast<bf16*>(smem_raw);
+    bf16* kv_s = q_s + AT_HEADS * WP;
+    bf16* p_s = kv_s + AT_CHUNK * WP;
+    float* max_s = reinterpret_cast<float*>(p_s + AT_HEADS * AT_PSTRIDE);
+    float* sum_s = max_s + AT_WARPS * AT_HEADS;
+    __shared__ int row_s[AT_CHUNK];
+    const int r = blockIdx.x, h_base = blockIdx.y * AT_HEADS;
+    const int count = min(max(sel_counts[2 * r + 1], 0), top_k);
+    const bf16* cache = kv_cache + ((int64_t)row_lane[r] * layers + layer) * (int64_t)local_cap * W;
+    const int vec_per_row = W / 8;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3, mi = lane >> 3, mr = lane & 7;
+    const int h0 = h_base + g, h1 = h0 + 8;
+
+    const bf16* q = q_full + (int64_t)r * H * W;
+    for (int i = threadIdx.x; i < AT_HEADS * vec_per_row; i += AT_THREADS) {
+        const int h = i / vec_per_row, v = i % vec_per_row;
+        bf16* dst = q_s + h * WP + v * 8;
+        if (h_base + h < H) cp_async16(dst, q + (int64_t)(h_base + h) * W + v * 8);
+        else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+    }
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    float o_acc[TPW][4];
+#pragma unroll
+    for (int j = 0; j < TPW; ++j) o_acc[j][0] = o_acc[j][1] = o_acc[j][2] = o_acc[j][3] = 0.f;
+
+    for (int start = 0; start < count; start += AT_CHUNK) {
+        const int cnt = min(AT_CHUNK, count - start);
+        if (threadIdx.x < AT_CHUNK) {
+            int row = -1;
+            if ((int)threadIdx.x < cnt) {
+                row = sel_local[(int64_t)r * top_k + start + threadIdx.x];
+                if (row < 0 || row >= local_cap) { raise_status(status, GLMB_STATUS_BAD_INDEX); row = min(max(row, 0), local_cap - 1); }
+            }
+            row_s[threadIdx.x] = row;
+        }
+        __syncthreads();  // also: every warp has finished reading kv_s / p_s of the previous chunk
+        for (int i = threadIdx.x; i < AT_CHUNK * vec_per_row; i += AT_THREADS) {
+            const int c = i / vec_per_row, v = i % vec_per_row;
+            const int row = row_s[c];
+            bf16* dst = kv_s + c * WP + v * 8;
+            if (row >= 0) cp_async16(dst, cache + (int64_t)row * W + v * 8);
+            else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+
+        float s_acc[4] = {0.f, 0.f, 0.f, 0.f};
+        {
+            const bf16* a_base = q_s + (mr + 8 * (mi & 1)) * WP + 8 * (mi >> 1);
+            const bf16* b_base = kv_s + (warp * 8 + mr) * WP + 8 * (mi & 1);
+            for (int k0 = 0; k0 < W; k0 += 16) {
+                uint32_t a[4], b[2];
+                ldmatrix_x4(a, a_base + k0);
+                ldmatrix_x2(b, b_base + k0);
+                mma_bf16_16816(s_acc, a, b[0], b[1]);
+            }
+        }
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int c = warp * 8 + 2 * t + (e & 1);
+            float s = __fmul_rn(s_acc[e], scale);
+            if (c >= cnt) s = -INFINITY;
+            else if (!isfinite(s)) raise_status(status, GLMB_STATUS_NONFINITE);
+            s_acc[e] = s;
+            mx[e >> 1] = fmaxf(mx[e >> 1], s);
+        }
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+            mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+        }
+        if (t == 0) { max_s[warp * AT_HEADS + g] = mx[0]; max_s[warp * AT_HEADS + g + 8] = mx[1]; }
+        __syncthreads();
+        float m_new[2] = {m_run[0], m_run[1]};
+#pragma unroll
+        for (int w2 = 0; w2 < AT_WARPS; ++w2) {
+            m_new[0] = fmaxf(m_new[0], max_s[w2 * AT_HEADS + g]);
+            m_new[1] = fmaxf(m_new[1], max_s[w2 * AT_HEADS + g + 8]);
+        }
+        float ls[2] = {0.f, 0.f};
+        {
+            float p[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                p[e] = s_acc[e] == -INFINITY ? 0.f : expf(s_acc[e] - m_new[e >> 1]);
+                ls[e >> 1] += p[e];
+            }
+            const int c = warp * 8 + 2 * t;
+            *reinterpret_cast<uint32_t*>(p_s + g * AT_PSTRIDE + c) = pack_bf16(p[0], p[1]);
+            *reinterpret_cast<uint32_t*>(p_s + (g + 8) * AT_PSTRIDE + c) = pack_bf16(p[2], p[3]);
+        }
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            ls[i] += __shfl_xor_sync(0xffffffffu, ls[i], 1);
+            ls[i] += __shfl_xor_sync(0xffffffffu, ls[i], 2);
+        }
+        if (t == 0) { sum_s[warp * AT_HEADS + g] = ls[0]; sum_s[warp * AT_HEADS + g + 8] = ls[1]; }
+        __syncthreads();
+        // running statistics (every thread keeps the pair of its heads g and g + 8) and accumulator rescale
+        float alpha[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            float chunk_sum = 0.f;
+#pragma unroll
+            for (int w2 = 0; w2 < AT_WARPS; ++w2) chunk_sum += sum_s[w2 * AT_HEADS + g + 8 * i];
+            alpha[i] = m_run[i] == -INFINITY ? 0.f : expf(m_run[i] - m_new[i]);
+            l_run[i] = l_run[i] * alpha[i] + chunk_sum;
+            m_run[i] = m_new[i];
+        }
+        if (warp < PVW) {
+#pragma unroll
+            for (int j = 0; j < TPW; ++j) { o_acc[j][0] *= alpha[0]; o_acc[j][1] *= alpha[0]; o_acc[j][2] *= alpha[1]; o_acc[j][3] *= alpha[1]; }
+            const bf16* pa_base = p_s + (mr + 8 * (mi & 1)) * AT_PSTRIDE + 8 * (mi >> 1);
+            const bf16* vb_base = kv_s + (mr + 8 * (mi & 1)) * WP + warp * (8 * TPW) + 8 * (mi >> 1);
+#pragma unroll
+            for (int kk = 0; kk < AT_CHUNK; kk += 16) {
+                uint32_t a[4];
+                ldmatrix_x4(a, pa_base + kk);
+#pragma unroll
+                for (int jn = 0; jn < TPW; jn += 2) {
+                    uint32_t b[4];
+                    ldmatrix_x4_trans(b, vb_base + kk * WP + jn * 8);
+                    mma_bf16_16816(o_acc[jn], a, b[0], b[1]);
+                    mma_bf16_16816(o_acc[jn + 1], a, b[2], b[3]);
+                }
+            }
+        }
+    }
+    asm volatile("cp.async.wait_all;" ::: "memory");  // an empty row never waited for its query copies
+    if (warp < PVW) {
+        // an empty row (no selected key) gives zeros
+#pragma unroll
+        for (int jn = 0; jn < TPW; ++jn) {
+            const int col = warp * (8 * TPW) + jn * 8 + 2 * t;
+            if (h0 < H)
+                *reinterpret_cast<uint32_t*>(o_lat + ((int64_t)r * H + h0) * L + col) =
+                    count > 0 ? pack_bf16(o_acc[jn][0] / l_run[0], o_acc[jn][1] / l_run[0]) : 0u;
+            if (h1 < H)
+                *reinterpret_cast<uint32_t*>(o_lat + ((int64_t)r * H + h1) * L + col) =
+                    count > 0 ? pack_bf16(o_acc[jn][2] / l_run[1], o_acc[jn][3] / l_run[1]) : 0u;
+        }
+    }
+}
+
 // grid (H, rows).  world == 1: o_lat[r][h] = bf16(o / l).  world > 1: push (o[L], m, l) to head owner.
 // The chunk statistics are fetched by one thread per chunk and the partial rows by float4 loads issued eight
 // chunks at a time, so the kernel costs a few memory round trips however many chunks a row has.
@@ -340,6 +503,40 @@ GLMB_API int glmb_sparse_mla_partial(const void* q_full, const void* kv_cache, c
     if (L == 512) return launch_partial<8, 8>(ARGS);
     if (L == 128) return launch_partial<2, 8>(ARGS);
     if (L == 64) return launch_partial<2, 4>(ARGS);
+#undef ARGS
+    return 1;
+}
+
+template <int TPW, int PVW>
+static int launch_rows(const void* q_full, const void* kv_cache, const int* sel_local, const int* sel_counts, const int* row_lane, int rows,
+                       int H, int rd, int layer, int layers, int local_cap, int top_k, float scale, void* o_lat, uint32_t* status,
+                       cudaStream_t stream) {
+    const int W = 8 * TPW * PVW + rd;
+    const size_t smem = (size_t)(AT_HEADS + AT_CHUNK) * (W + 8) * 2 + (size_t)AT_HEADS * AT_PSTRIDE * 2 + 2 * AT_WARPS * AT_HEADS * 4;
+    if (smem > 200 * 1024) return 2;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(sparse_mla_rows_kernel<TPW, PVW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e != cudaSuccess) return (int)e;
+        attr_set = true;
+    }
+    dim3 grid(rows, (H + AT_HEADS - 1) / AT_HEADS);
+    GLMB_LAUNCH((sparse_mla_rows_kernel<TPW, PVW>), grid, AT_THREADS, smem, stream, (const bf16*)q_full, (const bf16*)kv_cache, sel_local, sel_counts,
+                row_lane, H, rd, layer, layers, local_cap, top_k, scale, (bf16*)o_lat, status);
+    return (int)cudaGetLastError();
+}
+
+// o_lat[rows, H, L] (bf16, normalized) for any number of rows: every selected key of a row lives in this GPU's cache
+// (single GPU, or a replicated cache).  L in {64, 128, 512}; (L + rd) % 16 == 0.
+GLMB_API int glmb_sparse_mla_rows(const void* q_full, const void* kv_cache, const int* sel_local, const int* sel_counts, const int* row_lane,
+                                  int rows, int H, int L, int rd, int layer, int layers, int local_cap, int top_k, float scale, void* o_lat,
+                                  uint32_t* status, void* stream) {
+    if (((L + rd) & 15) || rows < 1) return 1;
+    cudaStream_t st = (cudaStream_t)stream;
+#define ARGS q_full, kv_cache, sel_local, sel_counts, row_lane, rows, H, rd, layer, layers, local_cap, top_k, scale, o_lat, status, st
+    if (L == 512) return launch_rows<8, 8>(ARGS);
+    if (L == 128) return launch_rows<2, 8>(ARGS);
+    if (L == 64) return launch_rows<2, 4>(ARGS);
 #undef ARGS
     return 1;
 }

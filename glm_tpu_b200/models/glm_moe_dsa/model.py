@@ -190,6 +190,7 @@ class GlmMoeDsaModel:
         # Prefill projections whose K is split over the GPUs: the GEMM with the all-reduce in its epilogue is 1.25-1.7x the
         # GEMM + library all-reduce on 2 GPUs and 0.85-0.9x on 8 (one SM per owned tile reads seven partial tiles), so it is
         # the default up to 4 GPUs; GLM_B200_PREFILL_GEMM_AR=fused|nccl overrides.
+        self.prefill_rows_attention = os.environ.get("GLM_B200_PREFILL_ATTENTION", "rows") != "split"
         choice = os.environ.get("GLM_B200_PREFILL_GEMM_AR", "auto")
         self.prefill_gemm_allreduce = choice == "fused" or (choice == "auto" and self.world <= 4)
 
@@ -341,8 +342,12 @@ class GlmMoeDsaModel:
 
         if forked is not None:
             self._join(forked)
+        if not decode and not gather and self.prefill_rows_attention:
+            # many rows, every key local: one kernel, running softmax per (row, 16 heads), bf16 output, no partials
+            native.sparse_mla_rows(ws.q_full, state.kv_cache, ws.sel_local, ws.sel_counts, row_lane, rows, ht, L, rd, layer, g.num_layers,
+                                   cache.local_capacity, g.index_top_k, self.softmax_scale, ws.o_lat, self.peer.status_ptr)
         # owner-local partial attention for ALL heads, in passes of attn_rows query rows
-        for r0 in range(0, rows, ws.attn_rows):
+        for r0 in range(0, rows, ws.attn_rows) if (decode or gather or not self.prefill_rows_attention) else ():
             n = min(ws.attn_rows, rows - r0)
             native.sparse_mla_partial(ws.q_full[r0:], state.kv_cache, ws.sel_local[r0:], ws.sel_counts[r0:], row_lane[r0:], n, ht, L, rd,
                                       layer, g.num_layers, cache.local_capacity, g.index_top_k, ws.max_chunks, self.softmax_scale,

@@ -355,6 +355,17 @@ def sparse_mla_partial(q_full, kv_cache, sel_local, sel_counts, row_lane, rows, 
     )
 
 
+def sparse_mla_rows(q_full, kv_cache, sel_local, sel_counts, row_lane, rows, H, L, rd, layer, layers, local_cap, top_k, scale, o_lat,
+                    status=None):
+    """Attention of many query rows whose selected keys all live in this GPU's cache: one CTA per (row, 16 heads) walks every
+    chunk with running softmax statistics and writes normalized bf16 ``o_lat [rows, H, L]`` (no partials, no merge)."""
+    _check(
+        lib().glmb_sparse_mla_rows(_p(q_full), _p(kv_cache), _p(sel_local), _p(sel_counts), _p(row_lane), rows, H, L, rd, layer, layers,
+                                   local_cap, top_k, f32(scale), _p(o_lat), _p(status), _stream()),
+        "sparse_mla_rows",
+    )
+
+
 def attn_local_merge(part_o, part_ml, sel_counts, rows, H, L, top_k, max_chunks, o_lat, heads_local, xpart_offset=0, comm=None,
                      sig=SIG_ATTN):
     _check(

@@ -323,10 +323,17 @@ def test_sparse_mla_attention(native_lib, count):
     n.sparse_mla_partial(q.to(DEV), cache.to(DEV), sel.to(DEV), counts.to(DEV), lane, rows, H, L, rd, 0, 1, cap, top_k, chunks, scale,
                          part_o, part_ml)
     n.attn_local_merge(part_o, part_ml, counts.to(DEV), rows, H, L, top_k, chunks, o_lat, H)
+    # the one-kernel variant for many rows (running softmax statistics, no partials) against the same reference
+    o_rows = torch.full((rows, H, L), float("nan"), dtype=torch.bfloat16, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    n.sparse_mla_rows(q.to(DEV), cache.to(DEV), sel.to(DEV), counts.to(DEV), lane, rows, H, L, rd, 0, 1, cap, top_k, scale, o_rows, status)
+    assert int(status.cpu()[0]) == 0
     for r in range(rows):
         ref = contract.absorbed_attention_row(q[r, :, :L], q[r, :, L:], cache[0, 0], picks[r], scale)
         ok, err = close(o_lat[r], ref, rtol=2**-6, atol=4e-3)
         assert ok, (r, err)
+        ok, err = close(o_rows[r], ref, rtol=2**-6, atol=4e-3)
+        assert ok, ("rows", r, err)
 
 
 def test_wait_gives_up_and_reports(native_lib):
