@@ -168,11 +168,12 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 #define T2_GROUP_M 8
 
 // Fused all-reduce of K-split partial products over NVLink peer memory (enabled != 0; dense mode, bf16 output).
-// Every rank runs the same GEMM on its K-slice.  Tile t belongs to rank t % world: the other ranks store their
-// fp32 partial tile into the owner's staging (slot (t / world) * world + source rank) and raise a flag; the owner's
-// CTA waits for the world - 1 flags, adds the partials to its own accumulator in rank order, rounds to bf16 and
-// stores the tile into every rank's output buffer (the same offset in every staging buffer).  The last CTA to
-// finish signals `sig` to all ranks; the consumer waits for that signal from every rank before it reads.
+// Every rank runs the same GEMM on its K-slice.  The 32-column block cb of tile t belongs to rank (t + cb) % world: the
+// other ranks store their fp32 partial block into the owner's staging (slot (owned-block index, source rank)) and raise
+// a flag per block; the owner waits for the world - 1 flags, adds the partials to its own accumulator in rank order,
+// rounds to bf16 and stores the block into every rank's output buffer (the same offset in every staging buffer).  So
+// every CTA of every rank pushes, reduces and broadcasts the same amount.  The last CTA to finish signals `sig` to all
+// ranks; the consumer waits for that signal from every rank before it reads.  world must divide 8.
 struct GemmAllReduce {
     int enabled;
     int sig;
@@ -181,6 +182,7 @@ struct GemmAllReduce {
     PeerComm comm;
 };
 #define T2_TILE_FLOATS (TC_BM * T2_BN)
+#define T2_BLOCK_FLOATS (TC_BM * 32)  // one 32-column block of a tile
 
 __device__ __forceinline__ void t2_tile(int t, int m_tiles, int n_blocks, int& m, int& n) {
     const int group = T2_GROUP_M * n_blocks;
@@ -291,97 +293,102 @@ gemm_bf16_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, c
             const int row = row0 + quarter * 32 + lane;
             const int n0 = n * T2_BN;
             if (ar.enabled) {
+                // Ownership is per 32-column block of a tile: block cb of tile t belongs to rank (t + cb) % world, so every CTA
+                // of every rank pushes 7/8 of its tile, reduces 1/8 of it and broadcasts that eighth: the reduce work is spread
+                // over all SMs of all GPUs instead of sitting on the one CTA that owned a whole tile.
                 const PeerComm& pc = ar.comm;
-                const int owner = t % pc.world;
-                const int64_t slot = (int64_t)(t / pc.world) * pc.world;
-                const int trow = quarter * 32 + lane;  // row inside the tile
+                const int per_tile = (T2_BN / 32) / pc.world;  // owned blocks per tile (world divides 8)
                 const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * T2_BN;
                 // Row-per-thread accumulator fragments go through a per-warp shared-memory tile so that every store
                 // instruction writes whole 128-byte lines (8 lanes x 16 bytes per row, 4 rows): NVLink and HBM both
                 // want full lines, and a 16-byte store per lane at a 1 KB stride wastes most of each packet.
                 float* stage = reinterpret_cast<float*>(epi_stage + (warp - 2) * T2_EPI_WARP_BYTES);
+                bf16* tile_h = reinterpret_cast<bf16*>(stage) + 32 * T2_EPI_STRIDE * 2;
                 const int sub_row = lane >> 3, sub_col = (lane & 7) * 4;
-                if (owner != pc.rank) {
-                    float* dst = reinterpret_cast<float*>(pc.data[owner] + ar.part_offset) + (slot + pc.rank) * T2_TILE_FLOATS +
-                                 (quarter * 32) * T2_BN;
+                const int out_col = (lane & 3) * 8;
+                // ---- push the blocks other ranks own: slot (owned-block index, source rank), 128 rows x 32 fp32 each
 #pragma unroll 1
-                    for (int cb = 0; cb < T2_BN / 32; ++cb) {
-                        uint32_t v[32];
-                        tmem_ld32(lane_addr + cb * 32, v);
-                        __syncwarp();
+                for (int cb = 0; cb < T2_BN / 32; ++cb) {
+                    const int owner = (t + cb) % pc.world;
+                    if (owner == pc.rank) continue;
+                    uint32_t v[32];
+                    tmem_ld32(lane_addr + cb * 32, v);
+                    __syncwarp();
 #pragma unroll
-                        for (int e = 0; e < 32; e += 4)
-                            *reinterpret_cast<uint4*>(stage + lane * T2_EPI_STRIDE + e) = make_uint4(v[e], v[e + 1], v[e + 2], v[e + 3]);
-                        __syncwarp();
+                    for (int e = 0; e < 32; e += 4)
+                        *reinterpret_cast<uint4*>(stage + lane * T2_EPI_STRIDE + e) = make_uint4(v[e], v[e + 1], v[e + 2], v[e + 3]);
+                    __syncwarp();
+                    const int64_t idx = (int64_t)t * per_tile + cb / pc.world;
+                    float* dst = reinterpret_cast<float*>(pc.data[owner] + ar.part_offset) + (idx * pc.world + pc.rank) * T2_BLOCK_FLOATS +
+                                 (quarter * 32) * 32;
 #pragma unroll
-                        for (int r4 = 0; r4 < 32; r4 += 4) {
-                            const int r = r4 + sub_row;
-                            *reinterpret_cast<uint4*>(dst + r * T2_BN + cb * 32 + sub_col) =
-                                *reinterpret_cast<const uint4*>(stage + r * T2_EPI_STRIDE + sub_col);
-                        }
+                    for (int r4 = 0; r4 < 32; r4 += 4) {
+                        const int r = r4 + sub_row;
+                        *reinterpret_cast<uint4*>(dst + r * 32 + sub_col) = *reinterpret_cast<const uint4*>(stage + r * T2_EPI_STRIDE + sub_col);
                     }
-                    __threadfence_system();
-                    asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
-                    if (warp == 2 && lane == 0)
-                        st_release_sys(pc.flags[owner] + GLMB_FLAG_GEMM_BASE + (size_t)t * GLMB_MAX_WORLD + pc.rank, ar_epoch);
-                } else {
+                }
+                __threadfence_system();
+                asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps: the whole tile's pushes are out
+                if (warp == 2 && lane < T2_BN / 32) {
+                    const int cb = lane, owner = (t + cb) % pc.world;
+                    if (owner != pc.rank)
+                        st_release_sys(pc.flags[owner] + GLMB_FLAG_GEMM_BASE + ((size_t)t * (T2_BN / 32) + cb) * GLMB_MAX_WORLD + pc.rank, ar_epoch);
+                }
+                // ---- reduce and broadcast the blocks this rank owns
+#pragma unroll 1
+                for (int cb = 0; cb < T2_BN / 32; ++cb) {
+                    if ((t + cb) % pc.world != pc.rank) continue;
                     if (warp == 2 && lane < pc.world && lane != pc.rank) {
-                        if (!wait_flag_reached(pc.flags[pc.rank] + GLMB_FLAG_GEMM_BASE + (size_t)t * GLMB_MAX_WORLD + lane, ar_epoch, pc.wait_limit))
+                        if (!wait_flag_reached(pc.flags[pc.rank] + GLMB_FLAG_GEMM_BASE + ((size_t)t * (T2_BN / 32) + cb) * GLMB_MAX_WORLD + lane,
+                                               ar_epoch, pc.wait_limit))
                             raise_status(status, GLMB_STATUS_WAIT_TIMEOUT);
                     }
                     asm volatile("bar.sync 1, 128;" ::: "memory");
-                    const float* inbox = reinterpret_cast<const float*>(pc.data[pc.rank] + ar.part_offset) + slot * T2_TILE_FLOATS +
-                                         (quarter * 32) * T2_BN;
-                    bf16* stage_h = reinterpret_cast<bf16*>(stage);
-                    const int out_col = (lane & 3) * 8;              // 8 bf16 = 16 bytes per lane, 4 lanes = the 64 bytes of one row of the block
-#pragma unroll 1
-                    for (int cb = 0; cb < T2_BN / 32; ++cb) {
-                        uint32_t v[32];
-                        tmem_ld32(lane_addr + cb * 32, v);
-                        __syncwarp();
-                        // own accumulator -> shared memory, so that the sum below runs in the coalesced (4 rows x 8 lanes) layout
+                    uint32_t v[32];
+                    tmem_ld32(lane_addr + cb * 32, v);
+                    __syncwarp();
 #pragma unroll
-                        for (int e = 0; e < 32; e += 4)
-                            *reinterpret_cast<uint4*>(stage + lane * T2_EPI_STRIDE + e) = make_uint4(v[e], v[e + 1], v[e + 2], v[e + 3]);
-                        __syncwarp();
-                        float4 sum[8];
+                    for (int e = 0; e < 32; e += 4)
+                        *reinterpret_cast<uint4*>(stage + lane * T2_EPI_STRIDE + e) = make_uint4(v[e], v[e + 1], v[e + 2], v[e + 3]);
+                    __syncwarp();
+                    const int64_t idx = (int64_t)t * per_tile + cb / pc.world;
+                    const float* inbox = reinterpret_cast<const float*>(pc.data[pc.rank] + ar.part_offset) + idx * pc.world * T2_BLOCK_FLOATS +
+                                         (quarter * 32) * 32;
+                    float4 sum[8];
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) sum[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-                        for (int p = 0; p < pc.world; ++p) {  // rank order: the same sum on every run
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) {
-                                const int r = i * 4 + sub_row;
-                                float4 x;
-                                if (p == pc.rank) {
-                                    x = *reinterpret_cast<const float4*>(stage + r * T2_EPI_STRIDE + sub_col);
-                                } else {
-                                    const uint4 u = ld_sys_u4(inbox + (int64_t)p * T2_TILE_FLOATS + r * T2_BN + cb * 32 + sub_col);
-                                    x = make_float4(__uint_as_float(u.x), __uint_as_float(u.y), __uint_as_float(u.z), __uint_as_float(u.w));
-                                }
-                                sum[i].x += x.x; sum[i].y += x.y; sum[i].z += x.z; sum[i].w += x.w;
-                            }
-                        }
-                        __syncwarp();
-                        // bf16 result of this 32-column block through the small bf16 tile: 4 lanes x 16 bytes per row, 8 rows per store
-                        bf16* tile_h = stage_h + 32 * T2_EPI_STRIDE * 2;
+                    for (int i = 0; i < 8; ++i) sum[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (int p = 0; p < pc.world; ++p) {  // rank order: the same sum on every run
 #pragma unroll
                         for (int i = 0; i < 8; ++i) {
                             const int r = i * 4 + sub_row;
-                            *reinterpret_cast<uint2*>(tile_h + r * T2_EPI_HSTRIDE + sub_col) =
-                                make_uint2(pack_bf16(sum[i].x, sum[i].y), pack_bf16(sum[i].z, sum[i].w));
-                        }
-                        __syncwarp();
-                        const int col = n0 + cb * 32 + out_col;
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const int r = i * 8 + (lane >> 2);
-                            const int grow = row0 + quarter * 32 + r;
-                            if (grow < rows && col < N) {
-                                const uint4 o = *reinterpret_cast<const uint4*>(tile_h + r * T2_EPI_HSTRIDE + out_col);
-                                const int64_t at = (int64_t)grow * N + col;
-                                for (int p = 0; p < pc.world; ++p)
-                                    *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(pc.data[p] + ar.out_offset) + at) = o;
+                            float4 x;
+                            if (p == pc.rank) {
+                                x = *reinterpret_cast<const float4*>(stage + r * T2_EPI_STRIDE + sub_col);
+                            } else {
+                                const uint4 u = ld_sys_u4(inbox + (int64_t)p * T2_BLOCK_FLOATS + r * 32 + sub_col);
+                                x = make_float4(__uint_as_float(u.x), __uint_as_float(u.y), __uint_as_float(u.z), __uint_as_float(u.w));
                             }
+                            sum[i].x += x.x; sum[i].y += x.y; sum[i].z += x.z; sum[i].w += x.w;
+                        }
+                    }
+                    __syncwarp();
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int r = i * 4 + sub_row;
+                        *reinterpret_cast<uint2*>(tile_h + r * T2_EPI_HSTRIDE + sub_col) =
+                            make_uint2(pack_bf16(sum[i].x, sum[i].y), pack_bf16(sum[i].z, sum[i].w));
+                    }
+                    __syncwarp();
+                    const int col = n0 + cb * 32 + out_col;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int r = i * 8 + (lane >> 2);
+                        const int grow = row0 + quarter * 32 + r;
+                        if (grow < rows && col < N) {
+                            const uint4 o = *reinterpret_cast<const uint4*>(tile_h + r * T2_EPI_HSTRIDE + out_col);
+                            const int64_t at = (int64_t)grow * N + col;
+                            for (int p = 0; p < pc.world; ++p)
+                                *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(pc.data[p] + ar.out_offset) + at) = o;
                         }
                     }
                 }
@@ -501,14 +508,14 @@ GLMB_API void glmb_set_gemm_variant(int variant) { g_gemm_variant = variant; }
 // out[rows, N] (bf16, at comm->data[p] + out_offset on EVERY rank p) = sum over ranks of a_r[rows, K_r] . b_r[N, K_r]^T.
 // One kernel: tcgen05 tiles, partial tiles pushed to the tile owner over NVLink, rank-ordered fp32 sum, bf16 result
 // pushed to all ranks, then signal `sig`.  The caller launches glmb_wait_signal(sig) before reading the output.
-// part_offset must leave room for ceil(tiles / world) * world slots of 128 x 256 fp32 (tiles = ceil(rows/128) * ceil(N/256)).
+// part_offset must leave room for tiles * 128 x 256 fp32 (tiles = ceil(rows/128) * ceil(N/256)): see glmb_gemm_allreduce_part_bytes.
 GLMB_API int glmb_gemm_bf16_tcgen05_allreduce(const void* a, int64_t lda, const void* b, int64_t ldb, int rows, int N, int K,
                                               const PeerComm* comm, int64_t part_offset, int64_t out_offset, int sig, uint32_t* status,
                                               void* stream) {
     if (!comm || comm->world < 2 || rows < 1 || N < 8 || (N & 7) || K < 8 || (K & 7) || (lda & 7) || (ldb & 7)) return 1;
     if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15) || (part_offset & 15) || (out_offset & 15)) return 1;
     const int total = ceil_div(rows, TC_BM) * ceil_div(N, T2_BN);
-    if (total > GLMB_GEMM_MAX_TILES || sig < 0 || sig >= GLMB_SIGNALS) return 2;
+    if (total * (T2_BN / 32) > GLMB_GEMM_MAX_TILES || sig < 0 || sig >= GLMB_SIGNALS || (T2_BN / 32) % comm->world) return 2;
     CUtensorMap map_a, map_b;
     if (make_map(&map_a, a, (uint64_t)rows, (uint64_t)K, (uint64_t)lda)) return 3;
     if (make_map(&map_b, b, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, T2_BN)) return 3;
@@ -535,6 +542,7 @@ GLMB_API int glmb_gemm_bf16_tcgen05_allreduce(const void* a, int64_t lda, const 
 
 // Bytes of partial-tile slots glmb_gemm_bf16_tcgen05_allreduce needs at part_offset.
 GLMB_API int64_t glmb_gemm_allreduce_part_bytes(int rows, int N, int world) {
+    (void)world;  // every rank owns 8 / world blocks of every tile and receives world - 1 (+ its own unused) copies of each
     const int64_t total = (int64_t)ceil_div(rows, TC_BM) * ceil_div(N, T2_BN);
-    return ((total + world - 1) / world) * world * (int64_t)T2_TILE_FLOATS * 4;
+    return total * (int64_t)T2_TILE_FLOATS * 4;
 }

@@ -33,7 +33,7 @@
 // Offsets (in uint32 words) inside the flag buffer and the local sequence buffer.
 #define GLMB_FLAG_AR_WORDS (GLMB_AR_CHANNELS * GLMB_AR_MAX_CTAS * GLMB_MAX_WORLD)
 #define GLMB_FLAG_SIG_BASE GLMB_FLAG_AR_WORDS
-#define GLMB_GEMM_MAX_TILES 2048  // output tiles of one GEMM with a fused all-reduce: one flag per (tile, source rank)
+#define GLMB_GEMM_MAX_TILES 16384  // 32-column blocks of the output tiles of one GEMM with a fused all-reduce: one flag per (block, source rank)
 #define GLMB_FLAG_GEMM_BASE (GLMB_FLAG_SIG_BASE + GLMB_SIGNALS * GLMB_MAX_WORLD)
 #define GLMB_FLAG_WORDS (GLMB_FLAG_GEMM_BASE + GLMB_GEMM_MAX_TILES * GLMB_MAX_WORLD)
 #define GLMB_SEQ_AR_WORDS (GLMB_AR_CHANNELS * GLMB_AR_MAX_CTAS)
