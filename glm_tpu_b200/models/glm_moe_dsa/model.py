@@ -187,12 +187,10 @@ class GlmMoeDsaModel:
         # streams; GLM_B200_OVERLAP=0 keeps everything on one stream
         self.side = torch.cuda.Stream(device=self.device) if os.environ.get("GLM_B200_OVERLAP", "1") != "0" else None
         self.fold_q_post = os.environ.get("GLM_B200_FOLD_Q_POST", "1") != "0"
-        # Prefill projections whose K is split over the GPUs: the GEMM with the all-reduce in its epilogue is 1.25-1.7x the
-        # GEMM + library all-reduce on 2 GPUs and 0.85-0.9x on 8 (one SM per owned tile reads seven partial tiles), so it is
-        # the default up to 4 GPUs; GLM_B200_PREFILL_GEMM_AR=fused|nccl overrides.
         self.prefill_rows_attention = os.environ.get("GLM_B200_PREFILL_ATTENTION", "rows") != "split"
-        choice = os.environ.get("GLM_B200_PREFILL_GEMM_AR", "auto")
-        self.prefill_gemm_allreduce = choice == "fused" or (choice == "auto" and self.world <= 4)
+        # Prefill projections whose K is split over the GPUs use the GEMM with the all-reduce in its epilogue (about 1.2x the
+        # GEMM + library all-reduce on 2 and on 8 GPUs); GLM_B200_PREFILL_GEMM_AR=nccl selects the library path.
+        self.prefill_gemm_allreduce = os.environ.get("GLM_B200_PREFILL_GEMM_AR", "fused") != "nccl"
 
     # ------------------------------------------------------------------------------ helpers
     @property
