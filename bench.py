@@ -147,7 +147,7 @@ def main() -> int:
         geometry = geometry.truncated(layers)
     t0 = time.perf_counter()
     runner = build_runner(geometry, world=world, rank=rank, device=device, seed=0, context_capacity=args.context, lanes=args.chats,
-                          comm=args.comm, use_graphs=not args.no_graphs, prefill_chunk=256, kv_layout=args.kv_layout)
+                          comm=args.comm, use_graphs=not args.no_graphs, prefill_chunk=1024, kv_layout=args.kv_layout)
     torch.cuda.synchronize()
     load_s = time.perf_counter() - t0
 

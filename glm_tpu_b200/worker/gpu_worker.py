@@ -187,7 +187,7 @@ class Worker:
             stripe = 64 if capacity % (64 * self.world) == 0 else max(1, capacity // (8 * self.world))
             runner = build_runner(geometry, world=self.world, rank=self.rank, device=device, checkpoint=checkpoint, seed=self.args.seed,
                                   context_capacity=capacity, lanes=lanes, comm=self.args.comm, kv_layout=self.args.kv_layout,
-                                  stripe=stripe, prefill_chunk=min(512, capacity))
+                                  stripe=stripe, prefill_chunk=min(2048 if capacity <= 65536 else 1024, capacity))  # rows per prefill pass: weights are re-streamed per pass
         from glm_tpu_b200.tokenizer import load_tokenizer
 
         self.tokenizer = load_tokenizer(path if kind == "checkpoint" else None, vocab_size=geometry.vocab_size, eos_ids=geometry.eos_ids)
