@@ -187,6 +187,7 @@ class GlmMoeDsaModel:
         # streams; GLM_B200_OVERLAP=0 keeps everything on one stream
         self.side = torch.cuda.Stream(device=self.device) if os.environ.get("GLM_B200_OVERLAP", "1") != "0" else None
         self.fold_q_post = os.environ.get("GLM_B200_FOLD_Q_POST", "1") != "0"
+        self.nvtx = os.environ.get("GLM_B200_NVTX", "0") == "1"
         self.prefill_rows_attention = os.environ.get("GLM_B200_PREFILL_ATTENTION", "rows") != "split"
         # Prefill projections whose K is split over the GPUs use the GEMM with the all-reduce in its epilogue (about 1.2x the
         # GEMM + library all-reduce on 2 and on 8 GPUs); GLM_B200_PREFILL_GEMM_AR=nccl selects the library path.
@@ -576,11 +577,17 @@ class GlmMoeDsaModel:
         g = self.g
         native.embed_rows(tokens, self.w.embed, ws.residual, self.peer.status_ptr)
         update = None
+        mark = torch.cuda.nvtx.range_push if self.nvtx else (lambda name: None)
+        done = torch.cuda.nvtx.range_pop if self.nvtx else (lambda: None)
         for i, lw in enumerate(self.w.layers):
+            mark(f"layer{i}.attention.{g.indexer_types[i]}")  # region names for profilers (GLM_B200_NVTX=1)
             native.add_rmsnorm(update, ws.residual[:rows], lw.input_norm, ws.x, g.rms_norm_eps)
             self._attention(ws, lw, i, rows, row_pos, row_lane, row_active, state, decode, max_ctx)
+            done()
+            mark(f"layer{i}.mlp.{g.mlp_layer_types[i]}")
             native.add_rmsnorm(ws.attn_out, ws.residual[:rows], lw.post_norm, ws.x, g.rms_norm_eps)
             self._mlp(ws, lw, i, rows, decode)
+            done()
             update = ws.update
             if self.trace is not None:
                 self.trace.setdefault("update", {})[i] = ws.update[:rows].clone()

@@ -93,12 +93,24 @@ class PeerGroup:
                 raise ValueError(f"region {name!r} already exists with a smaller size")
             return self.regions[name]
         nbytes = _align(nbytes, 256)
-        if self._cursor + nbytes > self._total:
+        if self._cursor + nbytes + GUARD_BYTES > self._total:
             raise MemoryError(f"staging buffer exhausted while reserving {name!r}")
         reg = Region(name, self._cursor, nbytes)
-        self._cursor += nbytes
+        self._cursor += nbytes + GUARD_BYTES
         self.regions[name] = reg
+        # canary words behind the region: peers push into this memory, so an overrun by a kernel of ANY rank lands here
+        self._bytes[reg.offset + nbytes : reg.offset + nbytes + GUARD_BYTES].fill_(GUARD_PATTERN)
         return reg
+
+    def check_canaries(self) -> None:
+        """Raise if a guard band behind any region was overwritten (synchronizes; call between steps, not per step)."""
+        bad = []
+        for reg in self.regions.values():
+            guard = self._bytes[reg.offset + reg.nbytes : reg.offset + reg.nbytes + GUARD_BYTES]
+            if not bool((guard == GUARD_PATTERN).all()):
+                bad.append(reg.name)
+        if bad:
+            raise DeviceStatusError(f"staging regions overrun: {bad}", 0)
 
     def tensor(self, region: Region, shape, dtype) -> torch.Tensor:
         count = 1
@@ -134,6 +146,10 @@ class PeerGroup:
             self._bytes = None
             self._lib.glmb_peer_destroy(self._handle)
             self._handle = C.c_void_p()
+
+
+GUARD_BYTES = 256
+GUARD_PATTERN = 0xA5
 
 
 def _align(n: int, a: int) -> int:

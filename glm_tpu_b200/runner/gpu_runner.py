@@ -205,6 +205,21 @@ class GpuModelRunner:
             self.peer.check_status()
         return token
 
+    def memory_stats(self) -> dict:
+        """Device memory as the allocator and the driver see it, plus what this runner knows it holds (per-request records)."""
+        free, total = torch.cuda.mem_get_info(self.device)
+        st = self.state
+        return {
+            "device_total_bytes": int(total), "device_free_bytes": int(free),
+            "torch_allocated_bytes": int(torch.cuda.memory_allocated(self.device)),
+            "torch_peak_allocated_bytes": int(torch.cuda.max_memory_allocated(self.device)),
+            "weights_bytes": int(self.model.w.bytes_resident),
+            "kv_cache_bytes": int(st.kv_cache.numel() * st.kv_cache.element_size()),
+            "index_cache_bytes": int(st.index_cache.numel() * st.index_cache.element_size()),
+            "staging_bytes": int(self.peer._total) if self.world > 1 else 0,
+            "kv_layout": self.kv_layout,
+        }
+
     def synthetic_context(self, lane: int, depth: int, seed: int = 0) -> None:
         """Benchmarks only: make ``lane`` look ``depth`` tokens deep without running a prefill.
 
@@ -228,6 +243,9 @@ class GpuModelRunner:
 
     def close(self) -> None:
         self._graph = None
+        if self.world > 1:
+            torch.cuda.synchronize(self.device)
+            self.peer.check_canaries()  # a kernel (of any rank) that overran a staging region wrote into its guard band
         self.peer.close()
 
 

@@ -84,6 +84,7 @@ def gemm_allreduce_check(world, rank, device):
             err = (got.float() - ref).abs().max().item() / max(ref.abs().max().item(), 1e-6)
             worst = max(worst, err if err == err else 1e9)
             a = (a.float() * -0.5 + 0.25).to(torch.bfloat16)
+        peer.check_canaries()  # the pushes of both ranks stayed inside their regions
         out[f"{rows}x{N}x{K}"] = {"rel_err": worst, "status": peer.read_status()}
         dist.barrier()
         peer.close()

@@ -451,3 +451,20 @@ def test_q_post_fold_is_bit_identical(native_lib):
         c = int(pos[r]) + 1
         assert torch.equal(scores_a[r, :c], scores_b[r, :c])
         assert torch.isnan(scores_b[r, c:]).all()
+
+
+def test_staging_canaries_catch_an_overrun(native_lib):
+    """A write past the end of a staging region lands in its guard band and is reported (host-side check, no fault involved)."""
+    from glm_tpu_b200.exceptions import DeviceStatusError
+    from glm_tpu_b200.parallel.peer import PeerGroup
+
+    peer = PeerGroup(1, 0, staging_bytes=8192)
+    a = peer.region("a", 1000)
+    b = peer.region("b", 512)
+    peer.tensor(a, (250,), torch.float32).fill_(1.0)
+    peer.tensor(b, (128,), torch.float32).fill_(2.0)
+    peer.check_canaries()
+    peer._bytes[a.offset + a.nbytes + 3] = 0  # one byte past region a (inside the staging buffer: nothing faults)
+    with pytest.raises(DeviceStatusError, match="overrun"):
+        peer.check_canaries()
+    peer.close()
