@@ -137,11 +137,15 @@ moe_grouped_fp8w_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         // ---- decode: FP8 tile (row-major, 64 bytes per row) -> bf16 tile (K-major, 128-byte swizzle) ----------
         const int ct = threadIdx.x - 64;  // 0 .. 255
         bool ok = true;
+        float next_lo = sc0[0], next_hi = sc1[0];
         for (int kb = 0; kb < kblocks && ok; ++kb) {
             const int s = kb % MG_STAGES, lap = kb / MG_STAGES;
             const int j = kb % MG_BSTAGES, blap = kb / MG_BSTAGES;
-            const int kblk = min((kb * MG_BK) >> 7, n_scale_cols - 1);
-            const float scale_lo = sc0[kblk], scale_hi = sc1[kblk];
+            // the block scales of the NEXT k step are requested now, a whole step before their first use: a load issued
+            // after the waits below would add its L2 latency to every step of the warps that bound this kernel
+            const float scale_lo = next_lo, scale_hi = next_hi;
+            const int kblk = min(((kb + 1) * MG_BK) >> 7, n_scale_cols - 1);
+            next_lo = sc0[kblk]; next_hi = sc1[kblk];
             if (!mbar_wait(full_bar + s, lap & 1) || (blap > 0 && !mbar_wait(b_empty + j, (blap - 1) & 1))) { *fail_slot = 1; ok = false; break; }
             const unsigned char* w8 = ring + s * MG_STAGE_BYTES + MG_A_BYTES;
             unsigned char* bt = bring + j * MG_B_BYTES;

@@ -114,6 +114,9 @@ class Workspace:
         else:
             self.q_full = bf(rows, ht, W)
             self.scores = f32(rows, self.score_stride)
+        # N operand of the many-rows indexer (three bf16 pieces of every fp32 query row): prefill workspaces only
+        self.idx_pieces = (torch.empty(native.indexer_rows_scratch_bytes(rows), dtype=torch.uint8, device=dev)
+                           if rows >= native.INDEXER_ROWS_MIN and native.indexer_takes_raw_query(g.index_heads, g.index_head_dim) else None)
         self.local_best = torch.zeros(rows, dtype=torch.int64, device=dev)  # packed argmax keys of this rank's vocabulary slice
         self.sel_global, self.sel_local, self.sel_counts = i32(rows, k), i32(rows, k), i32(rows, 2)
         self.max_chunks = -(-k // native.attn_chunk())
@@ -255,7 +258,7 @@ class GlmMoeDsaModel:
 
     # ------------------------------------------------------------------------------ attention
     def _attention(self, ws: Workspace, lw: LayerWeights, layer: int, rows: int, row_pos, row_lane, row_active, state: DecoderState,
-                   decode: bool, max_ctx: int):
+                   decode: bool, max_ctx: int, lane_of_rows: int | None = None):
         g, lay, cache = self.g, self.layout, self.cache
         full = g.indexer_types[layer] == "full"
         Q, L, rd, W = g.q_lora_rank, g.kv_lora_rank, g.qk_rope_head_dim, g.kv_row_width
@@ -330,7 +333,8 @@ class GlmMoeDsaModel:
                                  len(g.full_layers), cache.local_capacity, cache.stripe, cw, cr,
                                  cache.context_capacity, max_ctx, ws.score_stride, self.index_scale, ws.scores,
                                  ws.r_scores.offset if xf else 0, kx, native.SIG_SCORES, self.peer.status_ptr,
-                                 **(dict(q_raw=ws.q_proj, q_offset=hl * g.qk_head_dim, inv_freq=self.inv_freq, rd=rd) if fold else {}))
+                                 **(dict(q_raw=ws.q_proj, q_offset=hl * g.qk_head_dim, inv_freq=self.inv_freq, rd=rd) if fold else {}),
+                                 **(dict(pieces=ws.idx_pieces, lane=lane_of_rows) if lane_of_rows is not None and ws.idx_pieces is not None else {}))
             if gather and not xf:
                 self._merge_scores(ws.scores[:rows], max_ctx)
             native.topk_select(ws.scores, row_pos, rows, cache.context_capacity, ws.score_stride, g.index_top_k, cache.stripe,
@@ -567,8 +571,12 @@ class GlmMoeDsaModel:
 
     # ------------------------------------------------------------------------------ whole model
     def run_rows(self, ws: Workspace, state: DecoderState, tokens: torch.Tensor, row_pos: torch.Tensor, row_lane: torch.Tensor,
-                 row_active, rows: int, *, decode: bool, max_ctx: int, head_rows: slice | None = None, head: str = "logits"):
+                 row_active, rows: int, *, decode: bool, max_ctx: int, head_rows: slice | None = None, head: str = "logits",
+                 lane_of_rows: int | None = None):
         """Push ``rows`` token rows through the decoder.
+
+        ``lane_of_rows``: the cache lane that EVERY row belongs to (a prefill chunk of one chat), when the caller knows it; it
+        lets the indexer keep the key tiles resident while the rows stream past them.
 
         ``head='logits'`` returns the bf16 logits of ``head_rows`` (this rank's vocabulary slice).  ``head='argmax'``
         (decode) fuses the greedy reduction into the lm_head kernel: the packed best candidate of every row lands in
@@ -582,7 +590,7 @@ class GlmMoeDsaModel:
         for i, lw in enumerate(self.w.layers):
             mark(f"layer{i}.attention.{g.indexer_types[i]}")  # region names for profilers (GLM_B200_NVTX=1)
             native.add_rmsnorm(update, ws.residual[:rows], lw.input_norm, ws.x, g.rms_norm_eps)
-            self._attention(ws, lw, i, rows, row_pos, row_lane, row_active, state, decode, max_ctx)
+            self._attention(ws, lw, i, rows, row_pos, row_lane, row_active, state, decode, max_ctx, lane_of_rows)
             done()
             mark(f"layer{i}.mlp.{g.mlp_layer_types[i]}")
             native.add_rmsnorm(ws.attn_out, ws.residual[:rows], lw.post_norm, ws.x, g.rms_norm_eps)

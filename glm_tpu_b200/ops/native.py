@@ -82,6 +82,7 @@ def lib() -> C.CDLL:
         _lib.glmb_peer_comm_sizeof.restype = C.c_size_t
         _lib.glmb_peer_data.restype = C.c_void_p
         _lib.glmb_peer_status_ptr.restype = C.c_void_p
+        _lib.glmb_indexer_rows_scratch_bytes.restype = C.c_int64
         if _lib.glmb_peer_comm_sizeof() != C.sizeof(PeerComm):
             raise RuntimeError("PeerComm layout differs between Python and the CUDA library")
         import os
@@ -292,10 +293,37 @@ def _indexer_tensor_cores() -> bool:
     return os.environ.get("GLM_B200_INDEXER", "tcgen05") != "cuda"  # 'cuda': force the CUDA-core kernel (A/B runs)
 
 
+INDEXER_ROWS_MIN = 16  # from this many rows of one chat on, the many-rows indexer kernel is the faster one
+
+
+def indexer_rows_scratch_bytes(rows: int) -> int:
+    lib()
+    return int(_lib.glmb_indexer_rows_scratch_bytes(int(rows)))
+
+
 def indexer_score(q_idx, head_w, index_cache, row_pos, row_lane, rows, IH, D, index_slot, full_layers, local_cap, stripe, world,
                   rank, capacity, max_ctx, score_stride, scale, scores, scores_offset=0, comm=None, sig=SIG_SCORES, status=None, *,
-                  q_raw=None, q_offset=0, inv_freq=None, rd=0):
-    """``q_raw`` (fp32 q_b projection, index heads at ``q_offset``) replaces ``q_idx``: the tcgen05 kernel applies the RoPE itself."""
+                  q_raw=None, q_offset=0, inv_freq=None, rd=0, pieces=None, lane=None):
+    """``q_raw`` (fp32 q_b projection, index heads at ``q_offset``) replaces ``q_idx``: the tcgen05 kernel applies the RoPE itself.
+
+    ``pieces`` (scratch of :func:`indexer_rows_scratch_bytes`) with ``lane`` selects the many-rows kernel: every row belongs to
+    the chat in cache lane ``lane`` (a prefill chunk), the key tiles stay resident while the rows stream past them."""
+    if pieces is not None and rows >= INDEXER_ROWS_MIN and indexer_takes_raw_query(IH, D):
+        if lane is None:
+            raise ValueError("the many-rows indexer needs the cache lane that all rows share")
+        if pieces.numel() * pieces.element_size() < indexer_rows_scratch_bytes(rows):
+            raise ValueError("indexer scratch too small")
+        q = q_raw if q_raw is not None else q_idx
+        _check(
+            lib().glmb_indexer_score_tc_rows(_p(q), C.c_int64(q.stride(0) if q_raw is not None else IH * D), C.c_int64(q_offset if q_raw is not None else 0),
+                                             _p(inv_freq) if q_raw is not None else None, rd if q_raw is not None else 0, _p(head_w),
+                                             _p(index_cache), C.c_int64(index_cache.numel() // D), _p(row_pos), int(lane), rows, IH, D,
+                                             index_slot, full_layers, local_cap, stripe, world, rank, capacity, max_ctx,
+                                             C.c_int64(score_stride), f32(scale), _p(scores), C.c_int64(scores_offset), _p(pieces),
+                                             _comm(comm), sig, _p(status), _stream()),
+            "indexer_score_tc_rows",
+        )
+        return
     if q_raw is not None:
         if not indexer_takes_raw_query(IH, D):
             raise ValueError("the raw-query path needs the tcgen05 indexer (32 heads of 128)")

@@ -196,7 +196,7 @@ class GpuModelRunner:
                 pos = torch.arange(start, start + rows, dtype=torch.int32, device=self.device)
                 last = start + rows == n
                 logits = m.run_rows(ws, st, ids[start : start + rows], pos, lane_t, None, rows, decode=False, max_ctx=start + rows,
-                                    head_rows=slice(rows - 1, rows) if last else slice(0, 1))
+                                    head_rows=slice(rows - 1, rows) if last else slice(0, 1), lane_of_rows=lane)
             m.sample(ws, st, logits, 1, None, advance=1, tokens_out=st.tokens[lane : lane + 1], positions=st.positions[lane : lane + 1],
                      out=self._prefill_out)
             st.positions[lane] = n
