@@ -24,6 +24,7 @@ def main(argv=None) -> int:
     ap.add_argument("--kv-layout", default="striped", choices=["striped", "replicated", "auto"])
     ap.add_argument("--depth", type=int, default=30000)
     ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--topk-cluster", type=int, choices=[0, 1], help="force the 8-CTA-cluster (1) or the single-CTA (0) top-k kernel (A/B runs)")
     ap.add_argument("--out", type=Path)
     args = ap.parse_args(argv)
 
@@ -46,6 +47,10 @@ def main(argv=None) -> int:
     runner = build_runner(g, world=world, rank=rank, device=dev, seed=0, context_capacity=32768, lanes=4, prefill_chunk=4096, use_graphs=False,
                           kv_layout=args.kv_layout)
     model, st, lw = runner.model, runner.state, runner.model.w.layers[0]
+    if args.topk_cluster is not None:
+        from glm_tpu_b200.ops import native as _native
+
+        _native.set_topk_cluster(args.topk_cluster)
     for lane in range(4):
         runner.synthetic_context(lane, args.depth - 97 * lane, seed=lane)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)

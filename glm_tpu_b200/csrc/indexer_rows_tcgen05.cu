@@ -9,8 +9,10 @@
 //      straight from the q_b projection) split exactly into three bf16 pieces, [row][piece * 32 + head][128] in global memory;
 //   2. `indexer_score_rows_kernel`: one CTA keeps 4 key tiles (512 keys x 128 features, 128 KB) resident in shared memory and
 //      walks up to 128 rows: a 3-stage TMA ring streams each row's 24 KB of pieces and its 32 head weights, one lane issues
-//      8 tcgen05.mma (M 128 keys, N 96, K 16) per (row, key tile) into a ring of five 96-column TMEM accumulators, and four
-//      epilogue warps (thread = key) apply relu, the head weights and the sum over heads and store the scores.
+//      8 tcgen05.mma (M 128 keys, N 96, K 16) per (row, key tile) into a ring of five 96-column TMEM accumulators (four
+//      issuing threads take the accumulators in turn: one thread cannot issue as fast as these small MMAs retire), and two
+//      groups of four epilogue warps (thread = key), taking the accumulators alternately, apply relu, the head weights and the
+//      sum over heads and store the scores.
 //
 // Per (row, key tile) the SM reads 6 KB of L2 instead of 56 KB, no CTA is launched per row, and the tensor pipe sees back-to-
 // back MMAs.  Rows above a key tile in the causal triangle (context <= first key) are skipped by every role alike.
@@ -29,7 +31,8 @@
 #define IR_QSTAGES 3
 #define IR_BUFS 5
 #define IR_ROWS 128
-#define IR_THREADS 192
+#define IR_ISSUERS 4                               // one lane of each of four warps issues the MMAs of every fourth accumulator
+#define IR_THREADS 416                             // TMA warp, MMA warp, two epilogue groups of 4 warps, three more MMA warps
 #define IR_A_BYTES (IR_KEYS * IR_D * 2)            // one key tile: two 16 KB boxes
 #define IR_Q_BYTES (IR_N * IR_D * 2)               // one row's pieces: two 12 KB boxes
 #define IR_W_BYTES (IR_IH * 4)
@@ -99,6 +102,18 @@ __device__ __forceinline__ void ir_bulk_load(void* smem_dst, const void* src, ui
                  : "memory");
 }
 
+// tcgen05.ld of 32 columns without the wait: the caller issues several and waits once
+__device__ __forceinline__ void ir_tmem_ld32_issue(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+
 __global__ void __launch_bounds__(IR_THREADS, 1)
 indexer_score_rows_kernel(const __grid_constant__ CUtensorMap map_keys, const __grid_constant__ CUtensorMap map_q, const float* __restrict__ head_w,
                           const int* __restrict__ row_pos, int cache_row_base, int rows, int stripe, int world, int rank, int capacity,
@@ -126,7 +141,7 @@ indexer_score_rows_kernel(const __grid_constant__ CUtensorMap map_keys, const __
 
     if (threadIdx.x == 0) {
         mbar_init(a_bar, 1);
-        for (int s = 0; s < IR_QSTAGES; ++s) { mbar_init(q_full + s, 1); mbar_init(q_empty + s, 5); }  // the MMA commit + 4 epilogue warps
+        for (int s = 0; s < IR_QSTAGES; ++s) { mbar_init(q_full + s, 1); mbar_init(q_empty + s, IR_ISSUERS + 8); }  // the MMA issuers' commits + 8 epilogue warps
         for (int b = 0; b < IR_BUFS; ++b) { mbar_init(t_full + b, 1); mbar_init(t_empty + b, 4); }
         *fail_slot = 0;
         *owned_max_slot = 0;
@@ -174,10 +189,12 @@ indexer_score_rows_kernel(const __grid_constant__ CUtensorMap map_keys, const __
                     ++li;
                 }
             }
-        } else if (warp == 1) {
-            // ---- MMA issuer ------------------------------------------------------------------------------------------
+        } else if (warp == 1 || warp >= 10) {
+            // ---- MMA issuers: an N = 96 instruction keeps the tensor core busy for ~50 cycles, less than one thread needs to wait for
+            //      a free accumulator, build the descriptors and issue; four threads take the accumulators in turn ------------------------------------------------------------------------------------------
             if (lane == 0) {
                 constexpr uint32_t idesc = umma_idesc_bf16(IR_KEYS, IR_N);
+                const int issuer = warp == 1 ? 0 : warp - 9;
                 bool ok = mbar_wait(a_bar, 0);
                 int li = 0, n = 0;
                 for (int i = 0; i < n_rows && ok; ++i) {
@@ -188,6 +205,7 @@ indexer_score_rows_kernel(const __grid_constant__ CUtensorMap map_keys, const __
                     const uint32_t b_addr = smem_u32(q_s + s * IR_STAGE_BYTES);
                     const int tiles = min(IR_TILES, (own - j0 + IR_KEYS - 1) / IR_KEYS);
                     for (int t = 0; t < tiles; ++t, ++n) {
+                        if (n % IR_ISSUERS != issuer) continue;
                         const int b = n % IR_BUFS, blap = n / IR_BUFS;
                         if (blap > 0 && !mbar_wait(t_empty + b, (blap - 1) & 1)) { ok = false; break; }
                         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -201,14 +219,14 @@ indexer_score_rows_kernel(const __grid_constant__ CUtensorMap map_keys, const __
                         umma_commit(t_full + b);
                     }
                     if (!ok) break;
-                    umma_commit(q_empty + s);  // the pieces of this row have been read once these MMAs retire
+                    umma_commit(q_empty + s);  // this thread's MMAs on the row's pieces have retired (at once, if it issued none)
                     ++li;
                 }
                 if (!ok) { *fail_slot = 1; raise_status(status, GLMB_STATUS_WAIT_TIMEOUT); }
             }
         } else {
             // ---- epilogue: thread = key ------------------------------------------------------------------------------
-            const int quarter = warp & 3;
+            const int quarter = warp & 3, group = (warp - 2) >> 2;  // a warp reads the TMEM lanes of its quarter; group g takes accumulators n = g (mod 2)
             const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
             bool ok = true;
             int li = 0, n = 0;
@@ -221,13 +239,15 @@ indexer_score_rows_kernel(const __grid_constant__ CUtensorMap map_keys, const __
                 const int tiles = min(IR_TILES, (own - j0 + IR_KEYS - 1) / IR_KEYS);
                 const int r = r0 + i;
                 for (int t = 0; t < tiles; ++t, ++n) {
+                    if ((n & 1) != group) continue;
                     const int b = n % IR_BUFS, blap = n / IR_BUFS;
                     if (!mbar_wait(t_full + b, blap & 1)) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     uint32_t c0[32], c1[32], c2[32];
-                    tmem_ld32(lane_addr + b * IR_N, c0);
-                    tmem_ld32(lane_addr + b * IR_N + 32, c1);
-                    tmem_ld32(lane_addr + b * IR_N + 64, c2);
+                    ir_tmem_ld32_issue(lane_addr + b * IR_N, c0);  // three loads in flight, one wait
+                    ir_tmem_ld32_issue(lane_addr + b * IR_N + 32, c1);
+                    ir_tmem_ld32_issue(lane_addr + b * IR_N + 64, c2);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     __syncwarp();
                     if (lane == 0) mbar_arrive(t_empty + b);  // the accumulator is in registers: the tensor core may overwrite it
