@@ -56,7 +56,13 @@ def main(argv=None) -> int:
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
 
     def timed(fn):
+        # every call is fenced by a synchronize and a barrier, warm-ups included: the in-kernel exchanges assume ranks at most one
+        # exchange apart (in the model the MLP's all-reduce between two attention blocks sees to that), and their waits give up
+        # after about a second, less than the skew of ranks that have just filled their caches at their own pace
         for _ in range(3):
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
             fn()
         samples = []
         for _ in range(args.iters):
@@ -73,10 +79,22 @@ def main(argv=None) -> int:
             if world > 1:
                 dist.all_reduce(t, op=dist.ReduceOp.MAX)
             samples.append(float(t[0]))
+        if rank == 0 and max(samples) > 5 * min(samples):
+            print("uneven samples (ms):", " ".join(f"{v:.2f}" for v in samples), flush=True)
         return statistics.median(samples) * 1e3, min(samples) * 1e3
 
+    flagged = []
+
+    def status_of(case: str) -> str:
+        """The device status word after a case (0 = clean); a wait that ran out or a clamped index is reported beside its case."""
+        torch.cuda.synchronize()
+        value = runner.peer.read_status()
+        if value:
+            flagged.append((case, value))
+        return "ok" if not value else f"status {value:#x}"
+
     lines = [f"DSA attention block at GLM-5.3 dims on {world} GPU(s), kv layout {runner.kv_layout}, 32,768-slot cache, chats {args.depth} tokens deep, eager launches", "",
-             "| case | rows | median us | best us |", "|---|---|---|---|"]
+             "| case | rows | median us | best us | device status |", "|---|---|---|---|---|"]
     ws = runner.decode_ws
     frozen = torch.zeros(4, dtype=torch.int32, device=dev)  # inactive rows: the block runs in full but writes no cache row and advances nothing
     for rows in (1, 4):
@@ -86,7 +104,7 @@ def main(argv=None) -> int:
             model._attention(ws, lw, 0, rows, st.positions, st.lane_ids, frozen, st, True, runner.cache.context_capacity)
 
         med, best = timed(decode_block)
-        lines.append(f"| decode, {rows} chat(s) at depth {args.depth} | {rows} | {med:.1f} | {best:.1f} |")
+        lines.append(f"| decode, {rows} chat(s) at depth {args.depth} | {rows} | {med:.1f} | {best:.1f} | {status_of(f'decode {rows}')} |")
     pws = runner._ensure_prefill_ws()
     rows = 4096
     pws.x[:rows].copy_(torch.randn(rows, g.hidden_size, generator=torch.Generator().manual_seed(9)).to(torch.bfloat16))
@@ -98,7 +116,8 @@ def main(argv=None) -> int:
         model._attention(pws, lw, 0, rows, pos, lane_t, None, st, False, start + rows, 0)
 
     med, best = timed(prefill_block)
-    lines.append(f"| prefill chunk of 4,096 rows at positions {start}..{start + rows - 1} (every row selects 2,048 of > 28k keys) | {rows} | {med:.1f} | {best:.1f} |")
+    lines.append(f"| prefill chunk of 4,096 rows at positions {start}..{start + rows - 1} (every row selects 2,048 of > 28k keys) | {rows} | {med:.1f} | {best:.1f} | "
+                 f"{status_of('prefill chunk')} |")
     from glm_tpu_b200.ops import native
 
     with native.kernel_timeline() as tl:  # one more pass with every launch bracketed by events: where the chunk's time goes
@@ -111,7 +130,9 @@ def main(argv=None) -> int:
             agg[name][1] += ms
     lines += ["", "| kernel of the prefill chunk | launches | total ms |", "|---|---|---|"]
     lines += [f"| {k} | {c} | {t:.2f} |" for k, (c, t) in sorted(agg.items(), key=lambda kv: -kv[1][1])]
-    runner.peer.check_status()
+    status_of("timeline pass")
+    if flagged:
+        print(f"rank {rank}: device status raised in {flagged}", flush=True)
     if rank == 0:
         text = "\n".join(lines) + "\n"
         print(text)
@@ -121,7 +142,7 @@ def main(argv=None) -> int:
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
-    return 0
+    return 1 if flagged else 0
 
 
 if __name__ == "__main__":

@@ -61,6 +61,8 @@ def main(argv=None) -> int:
         lw.router_bias.copy_(ramp * amplitude)
         model._mlp(cal, lw, 0, n_cal, False)
         torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()  # ranks stay in step: the in-kernel exchanges assume ranks at most one exchange apart
         load = torch.bincount(cal.topk_ids[:n_cal].flatten().long(), minlength=g.num_routed_experts).float().sort().values
         return float(load[int(0.95 * (len(load) - 1))] / load[int(0.05 * (len(load) - 1))].clamp_min(1.0))
 
@@ -90,7 +92,9 @@ def main(argv=None) -> int:
 
         for _ in range(3):
             step()
-        torch.cuda.synchronize()
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
         launch = step
         if decode:  # decode steps are replayed from a CUDA graph, as the engine's decode program is
             graph, side = torch.cuda.CUDAGraph(), torch.cuda.Stream()

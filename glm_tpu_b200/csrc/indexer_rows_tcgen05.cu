@@ -9,8 +9,8 @@
 //      straight from the q_b projection) split exactly into three bf16 pieces, [row][piece * 32 + head][128] in global memory;
 //   2. `indexer_score_rows_kernel`: one CTA keeps 4 key tiles (512 keys x 128 features, 128 KB) resident in shared memory and
 //      walks up to 128 rows: a 3-stage TMA ring streams each row's 24 KB of pieces and its 32 head weights, one lane issues
-//      8 tcgen05.mma (M 128 keys, N 96, K 16) per (row, key tile) into a ring of five 96-column TMEM accumulators (four
-//      issuing threads take the accumulators in turn: one thread cannot issue as fast as these small MMAs retire), and two
+//      8 tcgen05.mma (M 128 keys, N 96, K 16) per (row, key tile) into a ring of four 96-column TMEM accumulators (four
+//      issuing threads, one per accumulator: one thread cannot issue as fast as these small MMAs retire), and two
 //      groups of four epilogue warps (thread = key), taking the accumulators alternately, apply relu, the head weights and the
 //      sum over heads and store the scores.
 //
@@ -29,7 +29,7 @@
 #define IR_N (3 * IR_IH)
 #define IR_TILES 4
 #define IR_QSTAGES 3
-#define IR_BUFS 5
+#define IR_BUFS 4                                  // TMEM accumulators: accumulator b belongs to issuing thread b and to epilogue group b & 1
 #define IR_ROWS 128
 #define IR_ISSUERS 4                               // one lane of each of four warps issues the MMAs of every fourth accumulator
 #define IR_THREADS 416                             // TMA warp, MMA warp, two epilogue groups of 4 warps, three more MMA warps
@@ -38,6 +38,7 @@
 #define IR_W_BYTES (IR_IH * 4)
 #define IR_STAGE_BYTES (IR_Q_BYTES + 1024)         // pieces, then the head weights (padding keeps every stage 1024-byte aligned)
 #define IR_TMEM_COLS 512
+static_assert(IR_BUFS == IR_ISSUERS && IR_BUFS % 2 == 0 && IR_BUFS * IR_N <= IR_TMEM_COLS, "one accumulator per issuing thread, alternating between the two epilogue groups");
 #define IR_SMEM_BYTES (1024 + IR_TILES * IR_A_BYTES + IR_QSTAGES * IR_STAGE_BYTES + 256 + IR_ROWS * 4)
 
 struct IndexerRowsQuery {
@@ -205,6 +206,9 @@ indexer_score_rows_kernel(const __grid_constant__ CUtensorMap map_keys, const __
                     const uint32_t b_addr = smem_u32(q_s + s * IR_STAGE_BYTES);
                     const int tiles = min(IR_TILES, (own - j0 + IR_KEYS - 1) / IR_KEYS);
                     for (int t = 0; t < tiles; ++t, ++n) {
+                        // IR_BUFS == IR_ISSUERS: accumulator b is filled by thread b alone and drained by epilogue group b & 1 alone,
+                        // each in increasing n.  A parity wait can only tell the current phase of an mbarrier from the previous one,
+                        // so no two threads that may drift apart by a lap of the ring may share one of these barriers.
                         if (n % IR_ISSUERS != issuer) continue;
                         const int b = n % IR_BUFS, blap = n / IR_BUFS;
                         if (blap > 0 && !mbar_wait(t_empty + b, (blap - 1) & 1)) { ok = false; break; }

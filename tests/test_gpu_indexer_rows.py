@@ -72,3 +72,35 @@ def test_rows_indexer_rotates_a_raw_query_like_the_one_row_kernel(native_lib):
     assert torch.equal(torch.isnan(one), torch.isnan(many))
     assert torch.equal(one.nan_to_num(0.0), many.nan_to_num(0.0))
     assert bool((many[-1, :cap] != 0).any())
+
+
+def test_rows_indexer_is_stable_over_many_launches(native_lib):
+    """The accumulator ring is shared by several issuing threads and two epilogue groups: repeated launches on a deep context (every
+    CTA walks 128 rows x 4 key tiles) must keep giving bit-identical scores and a clean status word."""
+    n = native_lib
+    torch.manual_seed(31)
+    rows, IH, D, cap = 512, 32, 128, 8192
+    q = (torch.randn(rows, IH, D) * 2.0).to(DEV)
+    hw = (torch.randn(rows, IH) * 0.2).to(DEV)
+    keys = torch.randn(1, 1, cap, D).to(torch.bfloat16).to(DEV)
+    pos = torch.arange(cap - rows, cap, dtype=torch.int32, device=DEV)
+    lane = torch.zeros(rows, dtype=torch.int32, device=DEV)
+    scale = float(torch.tensor(D**-0.5, dtype=torch.float32))
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    pieces = torch.empty(n.indexer_rows_scratch_bytes(rows), dtype=torch.uint8, device=DEV)
+    first = None
+    noise = torch.empty(64 << 20, dtype=torch.uint8, device=DEV)
+    for it in range(40):
+        out = torch.full((rows, cap), float("nan"), device=DEV)
+        if it % 3 == 0:
+            noise.fill_(it)  # vary what is in L2 and how the CTAs' loads are timed
+        n.indexer_score(q, hw, keys, pos, lane, rows, IH, D, 0, 1, cap, 64, 1, 0, cap, cap, cap, scale, out, status=status, pieces=pieces, lane=0)
+        if first is None:
+            first = out
+        else:
+            assert torch.equal(first.nan_to_num(0.0), out.nan_to_num(0.0)), it
+    assert int(status.item()) == 0
+    one = torch.full((64, cap), float("nan"), device=DEV)
+    n.indexer_score(q[:64].contiguous(), hw[:64].contiguous(), keys, pos[:64].contiguous(), lane[:64].contiguous(), 64, IH, D, 0, 1, cap, 64, 1, 0, cap, cap,
+                    cap, scale, one)
+    assert torch.equal(one.nan_to_num(0.0), first[:64].nan_to_num(0.0))
