@@ -287,6 +287,12 @@ def indexer_takes_raw_query(IH: int, D: int) -> bool:
     return D == 128 and IH == 32 and _indexer_tensor_cores()
 
 
+def _indexer_rows_kernel() -> bool:
+    import os
+
+    return os.environ.get("GLM_B200_INDEXER_ROWS", "1") != "0"  # '0': prefill chunks use the one-row kernel too (A/B runs)
+
+
 def _indexer_tensor_cores() -> bool:
     import os
 
@@ -308,7 +314,7 @@ def indexer_score(q_idx, head_w, index_cache, row_pos, row_lane, rows, IH, D, in
 
     ``pieces`` (scratch of :func:`indexer_rows_scratch_bytes`) with ``lane`` selects the many-rows kernel: every row belongs to
     the chat in cache lane ``lane`` (a prefill chunk), the key tiles stay resident while the rows stream past them."""
-    if pieces is not None and rows >= INDEXER_ROWS_MIN and indexer_takes_raw_query(IH, D):
+    if pieces is not None and rows >= INDEXER_ROWS_MIN and indexer_takes_raw_query(IH, D) and _indexer_rows_kernel():
         if lane is None:
             raise ValueError("the many-rows indexer needs the cache lane that all rows share")
         if pieces.numel() * pieces.element_size() < indexer_rows_scratch_bytes(rows):
