@@ -21,6 +21,16 @@ def main(args) -> int:
             by_dtype[t.dtype] = by_dtype.get(t.dtype, 0) + (t.end - t.begin)
         report = {"ok": True, "source": str(args.source), "inventory_sha256": inv.sha256, "tensors": len(inv.tensors),
                   "shards": len(inv.shards), "total_bytes": sum(inv.shards.values()), "bytes_by_dtype": dict(sorted(by_dtype.items()))}
+        from pathlib import Path
+
+        config = Path(args.source) / "config.json"
+        if config.is_file():  # is this the architecture the package pins (models/glm_moe_dsa/hf_config)?
+            from glm_tpu_b200.config.model import ModelGeometry
+            from glm_tpu_b200.models.glm_moe_dsa import assets
+
+            g = ModelGeometry.from_hf_config(json.loads(config.read_text()))
+            report["geometry_hash"] = g.geometry_hash
+            report["matches_pinned_glm53"] = g.geometry_hash == assets.load_pinned_geometry().geometry_hash
     elif args.action == "mark-source":
         marker = source_marker.mark_source(args.source)
         report = {"ok": True, "source": str(args.source), "inventory_sha256": marker["inventory_sha256"],
