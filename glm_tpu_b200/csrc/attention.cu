@@ -261,12 +261,15 @@ sparse_mla_rows_kernel(const bf16* __restrict__ q_full, const bf16* __restrict__
             row_s[threadIdx.x] = row;
         }
         __syncthreads();  // also: every warp has finished reading kv_s / p_s of the previous chunk
-        for (int i = threadIdx.x; i < AT_CHUNK * vec_per_row; i += AT_THREADS) {
-            const int c = i / vec_per_row, v = i % vec_per_row;
+        // a warp per key row, lanes across its 16-byte pieces: no division by the (runtime) row width in the copy loop
+        for (int c = warp; c < AT_CHUNK; c += AT_WARPS) {
             const int row = row_s[c];
-            bf16* dst = kv_s + c * WP + v * 8;
-            if (row >= 0) cp_async16(dst, cache + (int64_t)row * W + v * 8);
-            else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+            bf16* dst = kv_s + c * WP;
+            const bf16* src = cache + (int64_t)max(row, 0) * W;
+            for (int v = lane; v < vec_per_row; v += 32) {
+                if (row >= 0) cp_async16(dst + v * 8, src + v * 8);
+                else *reinterpret_cast<uint4*>(dst + v * 8) = make_uint4(0, 0, 0, 0);
+            }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
         asm volatile("cp.async.wait_group 0;" ::: "memory");
