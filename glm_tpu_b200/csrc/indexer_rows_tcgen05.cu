@@ -22,6 +22,7 @@
 #include "common.cuh"
 #include "peer.cuh"
 #include "tcgen05.cuh"
+#include "indexer_query.cuh"
 
 #define IR_KEYS 128
 #define IR_D 128
@@ -41,13 +42,6 @@
 static_assert(IR_BUFS == IR_ISSUERS && IR_BUFS % 2 == 0 && IR_BUFS * IR_N <= IR_TMEM_COLS, "one accumulator per issuing thread, alternating between the two epilogue groups");
 #define IR_SMEM_BYTES (1024 + IR_TILES * IR_A_BYTES + IR_QSTAGES * IR_STAGE_BYTES + 256 + IR_ROWS * 4)
 
-struct IndexerRowsQuery {
-    const float* q;      // [rows, q_stride] fp32, index head h at q_offset + h * 128
-    int64_t q_stride, q_offset;
-    const float* inv_freq;  // [rd / 2] when the rotation is still to be applied, else null
-    int rd;
-};
-
 // positions < ctx of a position-striped cache that this rank stores
 __device__ __forceinline__ int ir_owned(int pos, int capacity, int stripe, int world, int rank) {
     const int ctx = min(max(pos, 0), capacity - 1) + 1;
@@ -57,43 +51,17 @@ __device__ __forceinline__ int ir_owned(int pos, int capacity, int stripe, int w
 }
 
 __global__ void __launch_bounds__(256)
-indexer_split_rows_kernel(IndexerRowsQuery src, const int* __restrict__ row_pos, int capacity, __nv_bfloat16* __restrict__ pieces) {
+indexer_split_rows_kernel(IndexerQuerySource src, const int* __restrict__ row_pos, int capacity, __nv_bfloat16* __restrict__ pieces) {
     GLMB_PDL_PROLOGUE();
     const int r = blockIdx.x;
     const int pos = min(max(row_pos[r], 0), capacity - 1);
-    const float* q = src.q + (int64_t)r * src.q_stride + src.q_offset;
     for (int i = threadIdx.x; i < IR_IH * IR_D / 8; i += blockDim.x) {  // one 8-feature chunk of one head per step
         const int h = i / (IR_D / 8), c8 = i % (IR_D / 8);
-        const float4 x0 = *reinterpret_cast<const float4*>(q + h * IR_D + c8 * 8);
-        const float4 x1 = *reinterpret_cast<const float4*>(q + h * IR_D + c8 * 8 + 4);
-        float v[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
-        if (src.inv_freq && c8 * 8 < src.rd) {
+        uint4 piece[3];
+        indexer_query_pieces(src, r, h, c8, IR_D, pos, piece);
 #pragma unroll
-            for (int pr = 0; pr < 4; ++pr) {
-                const int d = c8 * 8 + 2 * pr;
-                if (d < src.rd) {  // interleaved pairs, fp32 angle = position * inv_freq: the arithmetic of the q_post kernel
-                    const float angle = __fmul_rn((float)pos, src.inv_freq[d >> 1]);
-                    const float cs = cosf(angle), sn = sinf(angle);
-                    const float even = v[2 * pr], odd = v[2 * pr + 1];
-                    v[2 * pr] = __fsub_rn(__fmul_rn(even, cs), __fmul_rn(odd, sn));
-                    v[2 * pr + 1] = __fadd_rn(__fmul_rn(odd, cs), __fmul_rn(even, sn));
-                }
-            }
-        }
-        float hi[8], mid[8], lo[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {  // q = hi + mid + lo exactly (to 2^-24 of |q|)
-            hi[e] = bf16_round(v[e]);
-            const float r1 = v[e] - hi[e];
-            mid[e] = bf16_round(r1);
-            lo[e] = bf16_round(r1 - mid[e]);
-        }
-#pragma unroll
-        for (int piece = 0; piece < 3; ++piece) {
-            const float* s = piece == 0 ? hi : (piece == 1 ? mid : lo);
-            __nv_bfloat16* dst = pieces + ((int64_t)r * IR_N + piece * IR_IH + h) * IR_D + c8 * 8;
-            *reinterpret_cast<uint4*>(dst) = make_uint4(pack_bf16(s[0], s[1]), pack_bf16(s[2], s[3]), pack_bf16(s[4], s[5]), pack_bf16(s[6], s[7]));
-        }
+        for (int p = 0; p < 3; ++p)
+            *reinterpret_cast<uint4*>(pieces + ((int64_t)r * IR_N + p * IR_IH + h) * IR_D + c8 * 8) = piece[p];
     }
 }
 
@@ -320,7 +288,7 @@ GLMB_API int glmb_indexer_score_tc_rows(const float* q, int64_t q_stride, int64_
         if (e != cudaSuccess) return (int)e;
         attr_set = true;
     }
-    IndexerRowsQuery src;
+    IndexerQuerySource src;
     src.q = q; src.q_stride = q_stride; src.q_offset = q_offset; src.inv_freq = inv_freq; src.rd = rd;
     GLMB_LAUNCH(indexer_split_rows_kernel, dim3(rows), 256, 0, (cudaStream_t)stream, src, row_pos, capacity, reinterpret_cast<__nv_bfloat16*>(pieces));
     const int page = stripe * world;

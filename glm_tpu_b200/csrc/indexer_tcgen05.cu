@@ -20,6 +20,7 @@
 #include "common.cuh"
 #include "peer.cuh"
 #include "tcgen05.cuh"
+#include "indexer_query.cuh"
 
 #define IT_KEYS 128
 #define IT_D 128
@@ -80,41 +81,22 @@ indexer_score_tc_kernel(const __grid_constant__ CUtensorMap map_keys, const floa
             asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
         }
         // query row -> three exact bf16 pieces, rows [piece * 32 + head] of the N operand
-        const float* q = raw.q_raw ? raw.q_raw + (int64_t)r * raw.q_stride + raw.q_offset : q_idx + (int64_t)r * IT_IH * IT_D;
+        IndexerQuerySource src;
+        src.q = raw.q_raw ? raw.q_raw : q_idx;
+        src.q_stride = raw.q_raw ? raw.q_stride : (int64_t)IT_IH * IT_D;
+        src.q_offset = raw.q_raw ? raw.q_offset : 0;
+        src.inv_freq = raw.q_raw ? raw.inv_freq : nullptr;
+        src.rd = raw.q_raw ? raw.rd : 0;
         for (int i = threadIdx.x; i < IT_IH * IT_D / 8; i += IT_THREADS) {  // one 8-feature chunk of one head per step
             const int h = i / (IT_D / 8), c8 = i % (IT_D / 8);             // c8: 16-byte chunk index along K (0..15)
-            const float4 x0 = *reinterpret_cast<const float4*>(q + h * IT_D + c8 * 8);
-            const float4 x1 = *reinterpret_cast<const float4*>(q + h * IT_D + c8 * 8 + 4);
-            float v[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
-            if (raw.q_raw && c8 * 8 < raw.rd) {
-#pragma unroll
-                for (int pr = 0; pr < 4; ++pr) {
-                    const int d = c8 * 8 + 2 * pr;
-                    if (d < raw.rd) {
-                        const float angle = __fmul_rn((float)pos, raw.inv_freq[d >> 1]);
-                        const float cs = cosf(angle), sn = sinf(angle);
-                        const float even = v[2 * pr], odd = v[2 * pr + 1];
-                        v[2 * pr] = __fsub_rn(__fmul_rn(even, cs), __fmul_rn(odd, sn));
-                        v[2 * pr + 1] = __fadd_rn(__fmul_rn(odd, cs), __fmul_rn(even, sn));
-                    }
-                }
-            }
-            float hi[8], mid[8], lo[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                hi[e] = bf16_round(v[e]);
-                const float r1 = v[e] - hi[e];
-                mid[e] = bf16_round(r1);
-                lo[e] = bf16_round(r1 - mid[e]);
-            }
+            uint4 piece[3];
+            indexer_query_pieces(src, r, h, c8, IT_D, pos, piece);
             const int khalf = c8 >> 3, chunk = c8 & 7;
 #pragma unroll
-            for (int piece = 0; piece < 3; ++piece) {
-                const float* src = piece == 0 ? hi : (piece == 1 ? mid : lo);
-                const int n = piece * IT_IH + h;
+            for (int p = 0; p < 3; ++p) {
+                const int n = p * IT_IH + h;
                 unsigned char* line = b_s + khalf * (IT_N * 128) + (n >> 3) * 1024 + (n & 7) * 128;
-                *reinterpret_cast<uint4*>(line + ((chunk ^ (n & 7)) << 4)) =
-                    make_uint4(pack_bf16(src[0], src[1]), pack_bf16(src[2], src[3]), pack_bf16(src[4], src[5]), pack_bf16(src[6], src[7]));
+                *reinterpret_cast<uint4*>(line + ((chunk ^ (n & 7)) << 4)) = piece[p];
             }
         }
         if (threadIdx.x < IT_IH) w_s[threadIdx.x] = head_w[(int64_t)r * IT_IH + threadIdx.x];
