@@ -138,6 +138,7 @@ class Workspace:
         self.kv_new = bf(rows, W)
         self.idx_key_new = bf(rows, D)
         self._sorted = None
+        self._route = None
         # many-row workspaces on several GPUs: output and partial-tile slots of the GEMM with the fused all-reduce
         self.r_gemm_out = self.r_gemm_part = None
         if rows > 8 and peer.world > 1 and model.comm_mode == "fused":
@@ -147,6 +148,14 @@ class Workspace:
                 self.gemm_out = peer.tensor(self.r_gemm_out, (rows, H), torch.bfloat16)
             except MemoryError:  # staging sized without it: the caller falls back to the library all-reduce
                 self.r_gemm_out = self.r_gemm_part = None
+
+    def route_buffers(self, routes: int, el: int):
+        """``tiles [routes / 128 + el, 4]``, ``n_tiles [1]``, ``perm [routes]`` of the expert sort, allocated on first use."""
+        if self._route is None or self._route[2].shape[0] < routes or self._route[0].shape[0] < routes // 128 + el:
+            dev = self.residual.device
+            self._route = (torch.zeros((routes // 128 + el, 4), dtype=torch.int32, device=dev), torch.zeros(1, dtype=torch.int32, device=dev),
+                           torch.empty(routes, dtype=torch.int32, device=dev))
+        return self._route[0][: routes // 128 + el], self._route[1], self._route[2][:routes]
 
     def sorted_buffers(self, routes: int, H: int, I: int):
         """Expert-sorted activations and SwiGLU outputs of the grouped (prefill) expert GEMM, allocated on first use."""
@@ -191,6 +200,7 @@ class GlmMoeDsaModel:
         self.side = torch.cuda.Stream(device=self.device) if os.environ.get("GLM_B200_OVERLAP", "1") != "0" else None
         self.fold_q_post = os.environ.get("GLM_B200_FOLD_Q_POST", "1") != "0"
         self.nvtx = os.environ.get("GLM_B200_NVTX", "0") == "1"
+        self.route_sort_kernel = os.environ.get("GLM_B200_ROUTE_SORT", "kernel") != "torch"  # 'torch': the library-op expert sort (A/B runs)
         self.prefill_rows_attention = os.environ.get("GLM_B200_PREFILL_ATTENTION", "rows") != "split"
         # Prefill projections whose K is split over the GPUs use the GEMM with the all-reduce in its epilogue (about 1.2x the
         # GEMM + library all-reduce on 2 and on 8 GPUs); GLM_B200_PREFILL_GEMM_AR=nccl selects the library path.
@@ -481,7 +491,11 @@ class GlmMoeDsaModel:
             self.trace.setdefault("topk_w", {})[layer] = ws.topk_w[:rows].clone()
         if not decode and rows * tk >= 128 and H % 16 == 0 and I % 16 == 0:
             # many rows: expert-sorted routes through the tcgen05 grouped GEMM (FP8 decoded inside the kernel)
-            tiles_t, n_tiles, perm = self._route_tiles128(ws.topk_ids[:rows], ebase, el)
+            if self.route_sort_kernel and el <= 256 and ws.topk_ids[:rows].is_contiguous():
+                tiles_t, n_tiles, perm = ws.route_buffers(rows * tk, el)
+                native.route_sort128(ws.topk_ids[:rows], ebase, el, tiles_t, n_tiles, perm)
+            else:
+                tiles_t, n_tiles, perm = self._route_tiles128(ws.topk_ids[:rows], ebase, el)
             xs, acts = ws.sorted_buffers(rows * tk, H, I)
             native.gather_rows(x, perm, tk, xs)
             native.moe_grouped_fp8w(xs, lw.exp_gate_bits, lw.exp_up_bits, lw.exp_gate_scale, lw.exp_up_scale, tiles_t, n_tiles, 0, acts,

@@ -225,6 +225,14 @@ def moe_grouped_fp8w(a_sorted, w0, w1, s0, s1, tiles, n_tiles, mode, out, *, per
     )
 
 
+def route_sort128(topk_ids, ebase: int, el: int, tiles, n_tiles, perm) -> None:
+    """Stable sort of this GPU's routes by expert, cut into 128-route tiles, in one launch (see csrc/route_sort.cu).
+
+    ``topk_ids``: int32 ``[rows, top_k]`` contiguous; ``tiles``: int32 ``[>= P / 128 + el, 4]``; ``n_tiles``: int32 ``[1]``; ``perm``: int32 ``[P]``."""
+    P = topk_ids.numel()
+    _check(lib().glmb_route_sort128(_p(topk_ids), P, int(ebase), int(el), tiles.shape[0], _p(tiles), _p(n_tiles), _p(perm), _stream()), "route_sort128")
+
+
 def gather_rows(src, idx, divisor, dst):
     """``dst[i] = src[idx[i] // divisor]`` (a row of zeros where ``idx[i] < 0``); bf16 rows, width a multiple of 8."""
     _check(lib().glmb_gather_rows(_p(src), C.c_int64(src.stride(0)), _p(idx), divisor, _p(dst), dst.shape[0], dst.shape[1], _stream()),

@@ -75,3 +75,28 @@ def test_grouped_fp8_experts(native_lib, rows, tk, E, el, H, I):
     assert bool(torch.isnan(got_dw[foreign]).all())
     # padding rows of the sorted activation buffer were overwritten with zeros, and no NaN reached a real route
     assert bool((got_x[checked:] == 0).all()) and not bool(torch.isnan(got_dw[(ids.reshape(-1) < el).nonzero().flatten()]).any())
+
+
+@pytest.mark.parametrize("rows,tk,E,ebase,el", [(64, 4, 8, 0, 8), (300, 8, 16, 6, 6), (4096, 8, 256, 32, 32), (1000, 8, 256, 0, 256), (37, 8, 256, 224, 32)])
+def test_route_sort_kernel_matches_the_stable_sort(native_lib, rows, tk, E, ebase, el):
+    """One launch gives the permutation of a stable argsort by local expert, the 128-route tiles and their count."""
+    n = native_lib
+    gen = torch.Generator().manual_seed(rows * 7 + el)
+    skew = torch.rand(E, generator=gen) ** 3 + 0.01  # some experts get many routes, some almost none
+    ids = torch.multinomial(skew.expand(rows, E), tk, replacement=False, generator=gen).to(torch.int32)
+    if rows == 37:
+        ids[:] = torch.arange(tk, dtype=torch.int32)  # nothing for this GPU's experts [224, 256)
+    P = rows * tk
+    tiles_ref, n_ref, perm_ref = _tiles(ids.reshape(-1).long() - ebase, el)
+    max_tiles = P // 128 + el
+    tiles = torch.full((max_tiles, 4), 7, dtype=torch.int32, device=DEV)
+    n_tiles = torch.full((1,), -5, dtype=torch.int32, device=DEV)
+    perm = torch.full((P,), 12345, dtype=torch.int32, device=DEV)
+    for _ in range(2):  # the second launch overwrites the first completely
+        n.route_sort128(ids.to(DEV), ebase, el, tiles, n_tiles, perm)
+    torch.cuda.synchronize()
+    count = int(n_tiles.item())
+    assert count == int(n_ref.item())
+    assert torch.equal(perm.cpu(), perm_ref)
+    assert torch.equal(tiles[:count].cpu(), tiles_ref[:count])
+    assert bool((tiles[count:] == 0).all())
