@@ -258,6 +258,14 @@ class GlmMoeDsaModel:
         native.wait_signal(self.peer.comm, native.SIG_GEMM)
         return ws.gemm_out[:rows]
 
+    @staticmethod
+    def _swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+        """``bf16(g * sigmoid(g) * u)`` of the bf16 gate / up projections of a prefill chunk (written over ``gate``)."""
+        if gate.is_contiguous() and up.is_contiguous() and gate.numel() % 8 == 0 and gate.dtype == torch.bfloat16:
+            return native.swiglu_rows(gate, up, gate)
+        g32, u32 = gate.float(), up.float()
+        return (g32 * torch.sigmoid(g32) * u32).to(torch.bfloat16)
+
     def _linear_f32(self, x, w, out, decode: bool):
         """``out[:, :N] = x @ w.T`` in fp32."""
         n = w.shape[0]
@@ -463,8 +471,7 @@ class GlmMoeDsaModel:
                     native.skinny_bf16(ws.dense_act[:rows], lw.dense_down, ws.partial, native.SK_OUT_F32)
                     ws.update[:rows] = self._allreduce_rows(ws.partial[:rows]).to(torch.bfloat16)
             else:
-                gate, up = self._mm(x, lw.dense_gate).float(), self._mm(x, lw.dense_up).float()
-                act = (gate * torch.sigmoid(gate) * up).to(torch.bfloat16)
+                act = self._swiglu(self._mm(x, lw.dense_gate), self._mm(x, lw.dense_up))
                 if self.world == 1:
                     ws.update[:rows] = self._mm(act, lw.dense_down)
                 else:
@@ -519,8 +526,7 @@ class GlmMoeDsaModel:
                 native.skinny_bf16(ws.act_shared[:rows], lw.shared_down, ws.partial, native.SK_OUT_F32)
             shared_partial = ws.partial
         else:
-            gate, up = self._mm(x, lw.shared_gate).float(), self._mm(x, lw.shared_up).float()
-            act = (gate * torch.sigmoid(gate) * up).to(torch.bfloat16)
+            act = self._swiglu(self._mm(x, lw.shared_gate), self._mm(x, lw.shared_up))
             shared_partial = self._mm(act, lw.shared_down, f32=True)
         if fused or self.world == 1:
             native.moe_combine(ws.dw, ws.topk_ids, shared_partial, rows, tk, H, ebase, el, g.routed_scaling_factor, False, ws.update,

@@ -225,6 +225,16 @@ def moe_grouped_fp8w(a_sorted, w0, w1, s0, s1, tiles, n_tiles, mode, out, *, per
     )
 
 
+def swiglu_rows(gate, up, act=None):
+    """``bf16(g * sigmoid(g) * u)`` of two contiguous bf16 tensors (fp32 arithmetic, one rounding) in one launch; returns ``act``."""
+    if act is None:
+        act = torch.empty_like(gate)
+    if not (gate.is_contiguous() and up.is_contiguous() and act.is_contiguous()) or gate.dtype != torch.bfloat16 or up.dtype != torch.bfloat16:
+        raise ValueError("swiglu_rows takes contiguous bf16 tensors")
+    _check(lib().glmb_swiglu_rows(_p(gate), _p(up), _p(act), C.c_int64(gate.numel()), _stream()), "swiglu_rows")
+    return act
+
+
 def route_sort128(topk_ids, ebase: int, el: int, tiles, n_tiles, perm) -> None:
     """Stable sort of this GPU's routes by expert, cut into 128-route tiles, in one launch (see csrc/route_sort.cu).
 

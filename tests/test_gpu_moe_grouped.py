@@ -100,3 +100,18 @@ def test_route_sort_kernel_matches_the_stable_sort(native_lib, rows, tk, E, ebas
     assert torch.equal(perm.cpu(), perm_ref)
     assert torch.equal(tiles[:count].cpu(), tiles_ref[:count])
     assert bool((tiles[count:] == 0).all())
+
+
+def test_swiglu_rows_matches_the_elementwise_expression(native_lib):
+    n = native_lib
+    gen = torch.Generator().manual_seed(5)
+    gate = (torch.randn(300, 1024, generator=gen) * 3.0).to(torch.bfloat16).to(DEV)
+    up = torch.randn(300, 1024, generator=gen).to(torch.bfloat16).to(DEV)
+    gate[0, :4] = torch.tensor([0.0, -0.0, 80.0, -80.0], dtype=torch.bfloat16)
+    g32, u32 = gate.float(), up.float()
+    ref = (g32 * torch.sigmoid(g32) * u32).to(torch.bfloat16)
+    out = n.swiglu_rows(gate.clone(), up)
+    assert torch.allclose(out.float(), ref.float(), rtol=2**-7, atol=1e-30)
+    assert float((out != ref).float().mean()) < 1e-3  # at most a last-place difference of the exponential here and there
+    inplace = gate.clone()
+    assert n.swiglu_rows(inplace, up, inplace) is inplace and torch.equal(inplace, out)
