@@ -100,5 +100,8 @@ def describe() -> dict[str, str]:
         if var.secret:
             out[name] = "<set>" if name in os.environ else "<unset>"
         else:
-            out[name] = str(var.getter()) if name in os.environ else "<unset>"
+            try:
+                out[name] = str(var.getter()) if name in os.environ else "<unset>"
+            except ValueError as exc:  # an environment report lists a bad value, it does not die of it
+                out[name] = f"<invalid: {exc}>"
     return out
