@@ -58,6 +58,15 @@ def _flag(name: str, default: bool = False) -> bool:
     return value == "1"
 
 
+def _choice(name: str, allowed: tuple[str, ...]) -> str:
+    value = os.environ.get(name, "")
+    if not value:
+        return allowed[0]
+    if value not in allowed:
+        raise ValueError(f"{name} must be one of {', '.join(allowed)}")
+    return value
+
+
 environment_variables: dict[str, EnvVar] = {
     "GLM_B200_CONFIG_ROOT": EnvVar(_config_root, "Directory of site.toml (default $XDG_CONFIG_HOME/glm-b200 or ~/.config/glm-b200)."),
     "GLM_B200_SITE_CONFIG": EnvVar(
@@ -73,6 +82,17 @@ environment_variables: dict[str, EnvVar] = {
     "GLM_B200_WAIT_LIMIT": EnvVar(
         lambda: int(_positive("GLM_B200_WAIT_LIMIT", 20_000_000)), "Iteration limit of every device-side wait on a peer flag."
     ),
+    # kernel-path switches for A/B runs: read where the path is chosen (ops/native.py, models/glm_moe_dsa/model.py), listed here
+    # so that the environment report shows them and refuses a value that would silently select the default
+    "GLM_B200_PDL": EnvVar(lambda: _flag("GLM_B200_PDL", True), "Programmatic dependent launch between consecutive kernels (1) or plain stream order (0)."),
+    "GLM_B200_OVERLAP": EnvVar(lambda: _flag("GLM_B200_OVERLAP", True), "Independent branches of a layer on a second stream (1) or one stream (0)."),
+    "GLM_B200_FOLD_Q_POST": EnvVar(lambda: _flag("GLM_B200_FOLD_Q_POST", True), "Decode: query RoPE folded into q-absorb and the indexer (1) or a kernel of its own (0)."),
+    "GLM_B200_NVTX": EnvVar(lambda: _flag("GLM_B200_NVTX", False), "NVTX ranges per layer and block."),
+    "GLM_B200_INDEXER": EnvVar(lambda: _choice("GLM_B200_INDEXER", ("tcgen05", "cuda")), "DSA indexer on tcgen05 or the CUDA-core kernel."),
+    "GLM_B200_INDEXER_ROWS": EnvVar(lambda: _flag("GLM_B200_INDEXER_ROWS", True), "Prefill chunks: many-rows tcgen05 indexer (1) or the one-row kernel per row (0)."),
+    "GLM_B200_ROUTE_SORT": EnvVar(lambda: _choice("GLM_B200_ROUTE_SORT", ("kernel", "torch")), "Prefill expert sort: one launch or library operations."),
+    "GLM_B200_PREFILL_ATTENTION": EnvVar(lambda: _choice("GLM_B200_PREFILL_ATTENTION", ("rows", "split")), "Prefill attention: one kernel per row block, or split partials + merge."),
+    "GLM_B200_PREFILL_GEMM_AR": EnvVar(lambda: _choice("GLM_B200_PREFILL_GEMM_AR", ("fused", "nccl")), "Prefill o_proj / down projections: all-reduce inside the GEMM, or GEMM then NCCL."),
     "GLM_B200_API_KEY_FILE": EnvVar(lambda: _abs_path("GLM_B200_API_KEY_FILE"), "Bearer key file (0600) for /v1.", secret=True),
     "GLM_B200_TEST_TIMEOUT_SCALE": EnvVar(lambda: _positive("GLM_B200_TEST_TIMEOUT_SCALE", 1.0), "Tests: multiplier for subprocess timeouts."),
 }
