@@ -1,0 +1,105 @@
+"""A model of the accumulator ring of the many-rows indexer (`glm_tpu_b200/csrc/indexer_rows_tcgen05.cu`) under every interleaving a
+random scheduler finds: issuing threads fill TMEM accumulators, two epilogue groups drain them, and the only synchronisation is mbarrier
+parity waits.  A parity wait tells the current phase from the previous one and nothing else, so two agents that share a barrier and may
+drift a lap apart can pass a wait early.  The model shows that the layout in use (accumulator b owned by issuing thread b and by epilogue
+group b & 1) is safe, and that a shared ring of five accumulators, the first design, is not.
+
+No GPU is involved: this is the host-side stand-in for a race detector on the kernel's protocol.
+"""
+
+import random
+
+import pytest
+
+
+class Barrier:
+    """mbarrier: `count` arrivals complete a phase; `passed(parity)` is what try_wait.parity reports."""
+
+    def __init__(self, count):
+        self.count, self.pending, self.phase = count, count, 0
+
+    def arrive(self):
+        self.pending -= 1
+        if self.pending == 0:
+            self.pending, self.phase = self.count, self.phase + 1
+
+    def passed(self, parity):
+        return (self.phase & 1) != parity  # true when the phase of that parity is not the one in progress
+
+
+class Violation(Exception):
+    pass
+
+
+def run(tiles, issuers, buffers, rng, bias=None):
+    """One random schedule.  Returns when every tile went through; raises Violation on an overwritten or misread accumulator."""
+    full = [Barrier(1) for _ in range(buffers)]
+    empty = [Barrier(1) for _ in range(buffers)]
+    content = [None] * buffers  # which tile's accumulator a buffer holds
+
+    def issuer(me):
+        for n in range(tiles):
+            if n % issuers != me:
+                continue
+            b, lap = n % buffers, n // buffers
+            if lap > 0:
+                yield lambda b=b, lap=lap: empty[b].passed((lap - 1) & 1)
+            if content[b] is not None:
+                raise Violation(f"tile {n} overwrites the live accumulator of tile {content[b]} in buffer {b}")
+            content[b] = n
+            yield  # the MMAs run
+            full[b].arrive()
+            yield
+
+    def epilogue(group):
+        for n in range(tiles):
+            if n & 1 != group:
+                continue
+            b, lap = n % buffers, n // buffers
+            yield lambda b=b, lap=lap: full[b].passed(lap & 1)
+            if content[b] != n:
+                raise Violation(f"the epilogue of tile {n} reads buffer {b} holding {content[b]}")
+            content[b] = None
+            yield  # the accumulator is in registers
+            empty[b].arrive()
+            yield
+
+    agents = [issuer(i) for i in range(issuers)] + [epilogue(g) for g in range(2)]
+    weights = bias or [1.0] * len(agents)
+    waiting = {i: None for i in range(len(agents))}  # the wait an agent sits in (a predicate), None when it can simply run
+    steps = 0
+    while waiting:
+        runnable = [i for i, wait in waiting.items() if wait is None or wait()]
+        if not runnable:
+            raise Violation("no agent can proceed: the barriers are out of step")
+        k = rng.choices(runnable, weights=[weights[i] for i in runnable])[0]
+        try:
+            waiting[k] = next(agents[k])
+        except StopIteration:
+            del waiting[k]
+        steps += 1
+    return steps
+
+
+@pytest.mark.parametrize("issuers,buffers", [(4, 4), (2, 2), (1, 5), (1, 4)])
+def test_owned_accumulators_are_safe_under_random_schedules(issuers, buffers):
+    """One issuing thread per accumulator (or a single issuing thread with any ring): no schedule breaks it, slow agents included."""
+    rng = random.Random(7)
+    for trial in range(300):
+        bias = [rng.choice([0.02, 1.0, 5.0]) for _ in range(issuers + 2)]  # some agents almost never get a turn
+        run(60, issuers, buffers, rng, bias)
+
+
+def test_a_shared_ring_of_five_breaks_when_an_issuing_thread_lags():
+    """Four issuing threads over five accumulators: thread n % 4 and buffer n % 5 drift apart, and a lagging thread lets another one
+    pass its parity wait a lap early."""
+    rng = random.Random(11)
+    failures = 0
+    for trial in range(300):
+        bias = [1.0] * 6
+        bias[rng.randrange(4)] = 0.02  # one issuing thread is slow
+        try:
+            run(60, 4, 5, rng, bias)
+        except Violation:
+            failures += 1
+    assert failures > 0
