@@ -103,3 +103,75 @@ def test_a_shared_ring_of_five_breaks_when_an_issuing_thread_lags():
         except Violation:
             failures += 1
     assert failures > 0
+
+
+# ------------------------------------------------------------------------------------------------------------------------------------
+# The in-kernel all-reduce (`glm_tpu_b200/csrc/peer.cuh`, cta_allreduce_f32): every rank stores its partial into every peer's inbox of
+# the channel, raises a sequence-numbered flag there, waits for all flags of this round and sums the inbox.  There is no second
+# handshake: what keeps a fast rank from overwriting an inbox that a slow rank has not read yet is the rule that two consecutive
+# all-reduces never use the same channel (`runner/admission.py:check_collective_plan`).  The model shows both halves of that statement.
+def run_allreduces(world, channels, rng, bias):
+    inbox = [[[None] * world for _ in range(2)] for _ in range(world)]   # [receiver][channel][source] = (round, value)
+    flag = [[[0] * world for _ in range(2)] for _ in range(world)]       # [receiver][channel][source] = round number
+    results = [[] for _ in range(world)]
+
+    def rank(me):
+        rounds = [0, 0]
+        for step, ch in enumerate(channels):
+            rounds[ch] += 1
+            e = rounds[ch]
+            for p in range(world):
+                if p != me:
+                    inbox[p][ch][me] = (step, 100 * step + me)
+                    yield
+                    flag[p][ch][me] = e
+                    yield
+            for p in range(world):
+                if p != me:
+                    yield lambda p=p, ch=ch, e=e: flag[me][ch][p] >= e
+            total = 100 * step + me
+            for p in range(world):
+                if p != me:
+                    got_step, value = inbox[me][ch][p]
+                    if got_step != step:
+                        raise Violation(f"rank {me} sums the partial of step {got_step} from rank {p} in step {step}")
+                    total += value
+                    yield
+            results[me].append(total)
+
+    agents = [rank(r) for r in range(world)]
+    waiting = {i: None for i in range(world)}
+    while waiting:
+        runnable = [i for i, wait in waiting.items() if wait is None or wait()]
+        if not runnable:
+            raise Violation("no rank can proceed")
+        k = rng.choices(runnable, weights=[bias[i] for i in runnable])[0]
+        try:
+            waiting[k] = next(agents[k])
+        except StopIteration:
+            del waiting[k]
+    return results
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_alternating_channels_keep_the_one_handshake_all_reduce_safe(world):
+    rng = random.Random(world)
+    channels = [0, 1] * 6  # attention, MLP, attention, MLP, ...
+    for trial in range(100):
+        bias = [rng.choice([0.02, 1.0, 5.0]) for _ in range(world)]
+        results = run_allreduces(world, channels, rng, bias)
+        want = [sum(100 * step + r for r in range(world)) for step in range(len(channels))]
+        assert all(r == want for r in results)
+
+
+def test_reusing_a_channel_back_to_back_lets_a_fast_rank_overwrite_an_unread_inbox():
+    rng = random.Random(3)
+    failures = 0
+    for trial in range(200):
+        bias = [1.0] * 4
+        bias[rng.randrange(4)] = 0.02
+        try:
+            run_allreduces(4, [0, 0, 0, 0], rng, bias)
+        except Violation:
+            failures += 1
+    assert failures > 0
