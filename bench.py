@@ -89,6 +89,10 @@ class ClockSampler:
         }
 
 
+class _SkipExtras(Exception):
+    pass
+
+
 def reference_arm() -> int:
     line = {
         "impl": "reference",
@@ -221,9 +225,20 @@ def main() -> int:
     clocks = sampler.stop() if rank == 0 else None
     runner.peer.check_status()
 
+    times = torch.tensor([device_ms, e2e_ms], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    device_ms, e2e_ms = float(times[0]), float(times[1])
+    ms_per_step = device_ms / args.steps
+    tok_s = args.chats * 1000.0 / ms_per_step
+    e2e_tok_s = args.chats * 1000.0 / (e2e_ms / args.steps)
+
     # ---- the rest of the headline metric, outside the timed region: time to first token, four concurrent chats ----------
     extras = {}
-    if not args.no_extras:
+    weights, kv_layout = runner.weights, runner.kv_layout
+    try:
+        if args.no_extras:
+            raise _SkipExtras
         def timed_prefill(r, lane, n):
             prompt = torch.randint(0, geometry.vocab_size, (n,), generator=gen).tolist()
             barrier()
@@ -245,9 +260,8 @@ def main() -> int:
         if args.chats == 1:
             from glm_tpu_b200.runner.gpu_runner import GpuModelRunner
 
-            weights = runner.weights
             runner.close()
-            del runner
+            runner = None
             torch.cuda.empty_cache()
             barrier()
             r4 = GpuModelRunner(weights, context_capacity=args.context, lanes=4, comm=args.comm, use_graphs=not args.no_graphs, prefill_chunk=1024,
@@ -273,14 +287,11 @@ def main() -> int:
                                     "vs_baseline_per_chat": round(1000.0 / step4 / BASELINE_FOUR_CHAT_TOK_S, 3), "launches_per_step": rec4.launches,
                                     "timing": "CUDA events around the same number of steps, max over ranks"}
             runner = r4
+    except _SkipExtras:
+        pass
+    except Exception as exc:  # the timed figures above stand on their own: an extra that fails is reported, not fatal
+        extras["error"] = f"{type(exc).__name__}: {exc}"[:300]
 
-    times = torch.tensor([device_ms, e2e_ms], dtype=torch.float64, device=device)
-    if world > 1:
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    device_ms, e2e_ms = float(times[0]), float(times[1])
-    ms_per_step = device_ms / args.steps
-    tok_s = args.chats * 1000.0 / ms_per_step
-    e2e_tok_s = args.chats * 1000.0 / (e2e_ms / args.steps)
     baseline = BASELINE_SINGLE_CHAT_TOK_S if args.chats == 1 else BASELINE_FOUR_CHAT_TOK_S * args.chats
     if rank == 0:
         line = {
@@ -309,7 +320,7 @@ def main() -> int:
                 "context_fill": "synthetic random cache rows (no prefill)" if args.depth else "real prefill of the prompt",
                 "parallelism": f"tp{world}(heads,mlp)+ep{world}(experts)" if world > 1 else "single gpu",
                 "comm": args.comm,
-                "kv_layout": runner.kv_layout,
+                "kv_layout": kv_layout,
                 "decode_program": rec.kind,
                 "l2": "each step streams more weight bytes than the 126 MB L2 (inputs larger than L2)",
                 "per_chat_tok_s": round(tok_s / args.chats, 3),
@@ -327,12 +338,13 @@ def main() -> int:
             "clocks": clocks,
             "load_seconds": round(load_s, 2),
             "prefill_seconds": round(prefill_s, 3),
-            "resident_bytes_per_gpu": runner.weights.bytes_resident,
+            "resident_bytes_per_gpu": weights.bytes_resident,
             "first_tokens": first,
             "extras": extras,
         }
         print(json.dumps(line))
-    runner.close()
+    if runner is not None:
+        runner.close()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
