@@ -91,6 +91,40 @@ def decode_step_bytes(g: ModelGeometry, world: int, *, chats: int = 1, depth: in
             "experts_per_layer_mean": mean_e, "experts_per_layer_busiest": max_e}
 
 
+def measured_tflops() -> tuple[float, str]:
+    path = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
+    if path.exists():
+        return float(json.loads(path.read_text())["bf16_tflops"]), "measured"
+    return 1590.0, "fallback"
+
+
+def prefill_flops(g: ModelGeometry, world: int, tokens: int) -> dict:
+    """Floating-point operations one GPU performs to prefill a fresh prompt of ``tokens`` (2 per multiply-add; the three-piece index
+    query counts once: it is the useful work that is reported, not the issued one).  Routed work is spread evenly over the GPUs."""
+    lay = ParallelLayout(g, world, 0)
+    H, Q, L = g.hidden_size, g.q_lora_rank, g.kv_lora_rank
+    hl = lay.heads_local
+    keys = sum(min(p + 1, g.index_top_k) for p in range(tokens))  # attended keys, summed over the rows
+    context = tokens * (tokens + 1) // 2                           # scored keys, summed over the rows
+    proj = attn = index = mlp = routed = 0
+    for layer in range(g.num_layers):
+        full = g.indexer_types[layer] == "full"
+        n_qkv = Q + L + g.qk_rope_head_dim + ((g.index_head_dim + g.index_heads) if full else 0)
+        n_qb = hl * g.qk_head_dim + (g.index_heads * g.index_head_dim if full else 0)
+        proj += 2 * tokens * (n_qkv * H + n_qb * Q + hl * g.kv_b_rows_per_head * L + H * hl * g.v_head_dim)
+        attn += 2 * keys * hl * (g.kv_row_width + L)
+        if full:
+            index += 2 * context * g.index_heads * g.index_head_dim  # replicated cache: every GPU scores every row
+        if g.mlp_layer_types[layer] == "dense":
+            mlp += 2 * tokens * 3 * lay.dense_cols_local * H
+        else:
+            mlp += 2 * tokens * (3 * lay.shared_cols_local * H + g.num_routed_experts * H)
+            routed += 2 * tokens * g.routed_top_k * 3 * g.moe_intermediate_size * H // world
+    head = 2 * lay.vocab_local * H
+    return {"projections": proj, "attention": attn, "indexer": index, "dense_shared_router": mlp, "routed_experts": routed, "lm_head": head,
+            "total": proj + attn + index + mlp + routed + head}
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--gpus", default="1,2,4,8")
@@ -99,6 +133,8 @@ def main(argv=None) -> int:
     ap.add_argument("--layers", type=int, default=0)
     ap.add_argument("--striped", action="store_true")
     ap.add_argument("--measured", default="", help="N:ms per step, comma separated, to print the achieved fraction")
+    ap.add_argument("--prefill", type=int, default=0, help="also print the compute bound of prefilling a fresh prompt of this many tokens")
+    ap.add_argument("--measured-prefill", default="", help="N:ms of that prefill, comma separated")
     args = ap.parse_args(argv)
     bw, kind = measured_hbm_gbs()
     measured = {int(k): float(v) for k, v in (item.split(":") for item in args.measured.split(",") if item)}
@@ -115,6 +151,21 @@ def main(argv=None) -> int:
         print(f"| {world} | {layers} | {mb(b['attention'])} | {mb(b['dense_mlp'] + b['shared_expert'] + b['router'])} | {mb(b['routed_mean'])} / {mb(b['routed_busiest'])} | "
               f"{mb(b['caches'])} | {mb(b['lm_head'])} | {b['total_busiest'] / 1e9:.2f} | {roof_ms:.3f} | {'' if got is None else f'{got:.3f}'} | "
               f"{'' if got is None else f'{roof_ms / got:.2f}'} |")
+    if args.prefill:
+        tf, kind = measured_tflops()
+        got_p = {int(k): float(v) for k, v in (item.split(":") for item in args.measured_prefill.split(",") if item)}
+        print(f"\nprefill of a fresh {args.prefill}-token prompt; bound = FLOPs of one GPU / {tf:.0f} TFLOP/s ({kind} library GEMM peak)\n")
+        print("| GPUs | layers | projections | attention | indexer | dense + shared + router | routed experts | total TFLOP per GPU | bound ms | measured ms | bound / measured |")
+        print("|---|---|---|---|---|---|---|---|---|---|---|")
+        for world in (int(v) for v in args.gpus.split(",")):
+            layers = args.layers or (78 if world >= 8 else max(4, round(78 * world / 8)))
+            g = glm53_geometry() if layers == 78 else glm53_geometry().truncated(layers)
+            f = prefill_flops(g, world, args.prefill)
+            bound = f["total"] / (tf * 1e12) * 1e3
+            got = got_p.get(world)
+            t = lambda x: f"{x / 1e12:.1f}"  # noqa: E731
+            print(f"| {world} | {layers} | {t(f['projections'])} | {t(f['attention'])} | {t(f['indexer'])} | {t(f['dense_shared_router'])} | {t(f['routed_experts'])} | "
+                  f"{t(f['total'])} | {bound:.1f} | {'' if got is None else f'{got:.1f}'} | {'' if got is None else f'{bound / got:.3f}'} |")
     return 0
 
 

@@ -41,3 +41,14 @@ def test_four_chats_touch_fewer_than_four_times_the_experts():
     one, four = rm.decode_step_bytes(g, 1, chats=1), rm.decode_step_bytes(g, 1, chats=4)
     assert 3.5 * one["routed_mean"] < four["routed_mean"] < 4 * one["routed_mean"]  # some of 32 routes share an expert
     assert rm.main(["--gpus", "1,8", "--measured", "1:2.175"]) == 0
+
+
+def test_prefill_flops_follow_the_shapes():
+    g = glm53_geometry().truncated(4)
+    f1, f8 = rm.prefill_flops(g, 1, 4096), rm.prefill_flops(g, 8, 4096)
+    assert f1["routed_experts"] == 2 * 4096 * 8 * 3 * 2048 * 6144 and f8["routed_experts"] * 8 == f1["routed_experts"]
+    keys = sum(min(p + 1, 2048) for p in range(4096))
+    assert f1["attention"] == 4 * 2 * keys * 64 * (576 + 512) and f8["attention"] * 8 == f1["attention"]
+    assert f8["indexer"] == f1["indexer"] > 0  # with a replicated cache every GPU scores every row
+    assert f1["total"] == sum(v for k, v in f1.items() if k != "total")
+    assert rm.main(["--gpus", "1", "--prefill", "1024", "--measured-prefill", "1:100"]) == 0
