@@ -175,3 +175,58 @@ def test_reusing_a_channel_back_to_back_lets_a_fast_rank_overwrite_an_unread_inb
         except Violation:
             failures += 1
     assert failures > 0
+
+
+# ------------------------------------------------------------------------------------------------------------------------------------
+# Signals (`grid_signal_peers` / `cta_wait_signal`): a producer kernel stores its data into ONE buffer on every peer and raises the
+# round's number; the consumer kernel of each rank waits for every rank's number and reads.  Nothing tells the producer that the peers
+# have read: what protects the buffer is that an all-reduce, which no rank leaves before every rank has entered it, separates two rounds
+# of the same signal.  The model shows the protected sequence to be safe and the unprotected one to break.
+def run_signal_rounds(world, rounds, separated, rng, bias):
+    data = [[None] * world for _ in range(world)]   # [receiver][source]: the round whose data sits in the buffer
+    flag = [[0] * world for _ in range(world)]      # [receiver][source]
+    entered = [0] * world                            # all-reduces a rank has entered
+
+    def rank(me):
+        for e in range(1, rounds + 1):
+            for p in range(world):                   # producer kernel
+                data[p][me] = e
+                yield
+                flag[p][me] = e
+                yield
+            for p in range(world):                   # consumer kernel
+                yield lambda p=p, e=e: flag[me][p] >= e
+            for p in range(world):
+                if data[me][p] != e:
+                    raise Violation(f"rank {me} reads round {data[me][p]} from rank {p} in round {e}")
+                yield
+            if separated:                            # the all-reduce that ends the layer: nobody leaves before everybody entered
+                entered[me] = e
+                for p in range(world):
+                    yield lambda p=p, e=e: entered[p] >= e
+
+    agents = [rank(r) for r in range(world)]
+    waiting = {i: None for i in range(world)}
+    while waiting:
+        runnable = [i for i, wait in waiting.items() if wait is None or wait()]
+        if not runnable:
+            raise Violation("no rank can proceed")
+        k = rng.choices(runnable, weights=[bias[i] for i in runnable])[0]
+        try:
+            waiting[k] = next(agents[k])
+        except StopIteration:
+            del waiting[k]
+
+
+def test_signal_rounds_are_safe_when_an_all_reduce_separates_them_and_break_when_none_does():
+    rng = random.Random(5)
+    broken = 0
+    for trial in range(150):
+        bias = [1.0] * 4
+        bias[rng.randrange(4)] = 0.02
+        run_signal_rounds(4, 8, True, rng, bias)
+        try:
+            run_signal_rounds(4, 8, False, rng, bias)
+        except Violation:
+            broken += 1
+    assert broken > 0
