@@ -1,15 +1,18 @@
-"""What the engine emits: one ``TokenEvent`` per generated token (a wire format: one JSON object per line in
-``tokens.jsonl``) and the split of the generated text into reasoning and final answer.
+"""What the engine emits.
 
-Parity: reference ``glm_tpu/engine/outputs.py:10-23``.
+``TokenEvent`` is the record of one generated token; its ``wire()`` form is one line of ``tokens.jsonl`` (``batch_round`` appears only
+when several chats decode together).  ``final_channel`` splits generated text into the model's reasoning and its answer: GLM opens its
+output with a ``<think>`` section, the answer follows ``</think>`` and ends at the first marker that would start another turn.
+
+Behaviour parity: reference ``glm_tpu/engine/outputs.py`` (same event fields, same split).
 """
 
 from __future__ import annotations
 
-import re
-from dataclasses import asdict, dataclass
+from dataclasses import dataclass
 
-_STOP_MARKERS = re.compile(r"<\|(?:user|endoftext|observation)\|>")
+THINK_OPEN, THINK_CLOSE = "<think>", "</think>"
+TURN_MARKERS = ("<|user|>", "<|endoftext|>", "<|observation|>")
 
 
 @dataclass(frozen=True)
@@ -18,19 +21,23 @@ class TokenEvent:
     index: int
     token_id: int
     finish_reason: str | None
-    batch_round: int | None = None  # only in concurrent mode
+    batch_round: int | None = None
 
     def wire(self) -> dict:
-        out = asdict(self)
-        if self.batch_round is None:
-            del out["batch_round"]
-        return out
+        record = {"request_id": self.request_id, "index": self.index, "token_id": self.token_id, "finish_reason": self.finish_reason}
+        if self.batch_round is not None:
+            record["batch_round"] = self.batch_round
+        return record
+
+
+def _without_opening_tag(reasoning: str) -> str:
+    return (reasoning[len(THINK_OPEN):] if reasoning.startswith(THINK_OPEN) else reasoning).strip()
 
 
 def final_channel(text: str) -> tuple[str, str]:
-    """``(thinking, answer)``: everything before ``</think>`` is reasoning; the answer stops at the next turn marker."""
-    if "</think>" not in text:
-        return text.removeprefix("<think>").strip(), ""
-    thinking, answer = text.split("</think>", 1)
-    answer = _STOP_MARKERS.split(answer, maxsplit=1)[0]
-    return thinking.removeprefix("<think>").strip(), answer.strip()
+    """``(reasoning, answer)``.  Text whose reasoning section has not been closed yet is all reasoning."""
+    reasoning, closed, rest = text.partition(THINK_CLOSE)
+    if not closed:
+        return _without_opening_tag(text), ""
+    cut = min((at for at in (rest.find(marker) for marker in TURN_MARKERS) if at >= 0), default=len(rest))
+    return _without_opening_tag(reasoning), rest[:cut].strip()

@@ -1,14 +1,17 @@
-"""``POST /v1/chat/completions``: stateless request shaping in front of the sequential resident queue.
+"""``POST /v1/chat/completions`` in front of the sequential resident queue.
 
-Supported fields: ``model`` (``glm-5.3`` or an alias that forces the reasoning effort), ``messages``, ``tools``,
-``tool_choice`` (rendered as an in-band system instruction), ``max_tokens``, ``stream``, ``reasoning_effort``
-(low / high / max), ``n`` (must be 1).  Sampling parameters are accepted and ignored: decoding is greedy.  The answer
-separates ``reasoning_content`` from ``content``; ``finish_reason`` is ``stop``, ``tool_calls`` or ``length``; streaming
-sends SSE chunks (role, reasoning deltas, content deltas -- held back once a ``<tool_call>`` opens -- tool calls, the
-finish chunk with ``usage``) and ``[DONE]``.  Errors: 400 invalid request, 404 unknown model, 429 ten jobs waiting,
-503 queue stopped, 504 server deadline.
+The endpoint is stateless: a request is read into a ``ChatCall`` (every field validated, refusals are ``ApiError``), handed to the queue
+under a fresh key, and then *followed*: ``_follow`` yields the job's snapshots until it reaches a terminal state or the server's deadline
+passes.  ``completion`` keeps the last snapshot; ``stream`` turns the growth between snapshots into server-sent events.
 
-Parity: reference ``glm_tpu/entrypoints/openai/serving_chat.py:18-163``.
+Accepted fields: ``model`` (``glm-5.3``, or an alias that fixes the reasoning effort), ``messages``, ``tools``, ``tool_choice`` (stated
+in-band, see ``chat_utils.instruct``), ``max_tokens``, ``stream``, ``reasoning_effort`` (low / high / max), ``n`` (1 only).  Sampling
+parameters are ignored: decoding is greedy.  Replies keep ``reasoning_content`` apart from ``content``; ``finish_reason`` is ``stop``,
+``tool_calls`` or ``length``.  A stream sends the role, reasoning deltas, content deltas (held back from the moment a ``<tool_call>``
+opens, because that text is not content), the tool calls, a finish event with ``usage``, then ``[DONE]``.  Status codes: 400 bad request,
+404 unknown model, 429 queue full (raised by the queue), 503 queue stopped, 504 server deadline.
+
+Behaviour parity: reference ``glm_tpu/entrypoints/openai/serving_chat.py`` (same fields, event order and status codes).
 """
 
 from __future__ import annotations
@@ -16,54 +19,81 @@ from __future__ import annotations
 import json
 import time
 import uuid
+from dataclasses import dataclass
 
 from glm_tpu_b200.entrypoints.openai.chat_utils import check_tools, convert, instruct
 from glm_tpu_b200.entrypoints.openai.protocol import ALIASES, EFFORTS, MODEL_NAME, ApiError
 from glm_tpu_b200.entrypoints.openai.tool_parser import OPEN, parse
 from glm_tpu_b200.entrypoints.serve.job_queue import DONE
 
+LENGTH_CAUSES = ("context_exhausted", "output_cap")
+DEADLINE_SENTENCE = "the resident model did not finish within the server deadline"
 
-def finish_reason(job: dict, calls: list) -> str:
+
+@dataclass(frozen=True)
+class ChatCall:
+    """A validated request."""
+
+    model: str
+    effort: str
+    budget: int | None
+    messages: list
+    tools: list | None
+
+    @classmethod
+    def read(cls, body) -> "ChatCall":
+        if not isinstance(body, dict):
+            raise ApiError("expected a JSON object")
+        model = body.get("model") or MODEL_NAME
+        if model not in ALIASES:
+            raise ApiError(f"unknown model: {model}", status=404, kind="model_not_found")
+        if body.get("n", 1) not in (None, 1):
+            raise ApiError("only one choice per request is supported")
+        asked = body.get("reasoning_effort", "max")
+        if asked not in EFFORTS:
+            raise ApiError("reasoning_effort must be low, high or max")
+        budget = body.get("max_tokens")
+        if budget is not None and (type(budget) is not int or budget < 1):
+            raise ApiError("max_tokens must be a positive integer")
+        tools = check_tools(body.get("tools"))
+        messages = instruct(convert(body.get("messages")), body.get("tool_choice"), tools)
+        # an alias outranks the field: some clients can choose a model name but cannot send extra fields
+        return cls(model, ALIASES[model] or asked, budget, messages, tools)
+
+
+def _why_it_ended(job: dict, calls: list) -> str:
     if calls:
         return "tool_calls"
-    if job["status"] == "complete":
-        return "stop"
-    return "length" if job.get("stop_cause") in ("context_exhausted", "output_cap") else "stop"
+    cut_short = job["status"] != "complete" and job.get("stop_cause") in LENGTH_CAUSES
+    return "length" if cut_short else "stop"
 
 
-def usage(job: dict) -> dict:
-    return {"prompt_tokens": job["prompt_tokens"], "completion_tokens": job["output_tokens"],
-            "total_tokens": job["prompt_tokens"] + job["output_tokens"]}
+def _token_counts(job: dict) -> dict:
+    asked, produced = job["prompt_tokens"], job["output_tokens"]
+    return {"prompt_tokens": asked, "completion_tokens": produced, "total_tokens": asked + produced}
 
 
 class OpenAIServingChat:
     def __init__(self, queue, backend, *, capacity: int, wait_seconds: float = 1800, poll_seconds: float = 0.2):
-        self.queue, self.backend = queue, backend
-        self.capacity, self.wait_seconds, self.poll_seconds = capacity, wait_seconds, poll_seconds
+        self.queue, self.backend, self.capacity = queue, backend, capacity
+        self.wait_seconds, self.poll_seconds = wait_seconds, poll_seconds
 
-    def prepare(self, data):
-        if type(data) is not dict:
-            raise ApiError("expected a JSON object")
-        name = data.get("model") or MODEL_NAME
-        if name not in ALIASES:
-            raise ApiError("unknown model: " + str(name), status=404, kind="model_not_found")
-        if data.get("n") not in (None, 1):
-            raise ApiError("only one choice per request is supported")
-        effort = data.get("reasoning_effort", "max")
-        if effort not in EFFORTS:
-            raise ApiError("reasoning_effort must be low, high or max")
-        effort = ALIASES[name] or effort  # the alias wins, for clients that cannot send the field
-        budget = data.get("max_tokens")
-        if budget is not None and (type(budget) is not int or budget <= 0):
-            raise ApiError("max_tokens must be a positive integer")
-        tools = check_tools(data.get("tools"))
-        messages = instruct(convert(data.get("messages")), data.get("tool_choice"), tools)
+    # ------------------------------------------------------------------------------------------------------------------ admission
+    def prepare(self, body):
+        """``(prepared request, key, model name)``; raises ``ApiError`` for anything the endpoint does not take."""
+        call = ChatCall.read(body)
         key = uuid.uuid4().hex
-        payload = self.backend.prepare_api(messages, key, tools=tools, effort=effort, max_new_tokens=budget,
-                                           context_capacity=self.capacity)
-        return payload, key, name
+        prepared = self.backend.prepare_api(call.messages, key, tools=call.tools, effort=call.effort, max_new_tokens=call.budget,
+                                            context_capacity=self.capacity)
+        return prepared, key, call.model
 
-    def _job(self, key: str) -> dict:
+    def _admit(self, body):
+        prepared, key, model = self.prepare(body)
+        self.queue.submit(prepared, key, label="api")
+        return key, model
+
+    # ------------------------------------------------------------------------------------------------------------------ following a job
+    def _snapshot(self, key: str) -> dict:
         job = self.queue.job(key)
         if job is None:
             raise ApiError("request was not retained", status=500, kind="server_error")
@@ -71,66 +101,62 @@ class OpenAIServingChat:
             raise ApiError(job["error"], status=503, kind="server_error")
         return job
 
-    def wait(self, key: str, *, deadline: float) -> dict:
+    def _follow(self, key: str, hint: str = ""):
+        """Yield snapshots of the job; the last one is terminal.  Raises 504 once the server's deadline has passed."""
+        give_up = time.time() + self.wait_seconds
         while True:
-            job = self._job(key)
+            job = self._snapshot(key)
+            yield job
             if job["status"] in DONE:
-                return job
-            if time.time() > deadline:
-                raise ApiError("the resident model did not finish within the server deadline; use stream=true for long answers",
-                               status=504, kind="timeout")
+                return
+            if time.time() > give_up:
+                raise ApiError(DEADLINE_SENTENCE + hint, status=504, kind="timeout")
             time.sleep(self.poll_seconds)
 
-    def completion(self, data) -> dict:
-        payload, key, name = self.prepare(data)
-        self.queue.submit(payload, key, label="api")
-        job = self.wait(key, deadline=time.time() + self.wait_seconds)
+    # ------------------------------------------------------------------------------------------------------------------ one reply
+    def completion(self, body) -> dict:
+        key, model = self._admit(body)
+        job = None
+        for job in self._follow(key, hint="; use stream=true for long answers"):
+            pass
         content, calls = parse(job["answer"])
-        message = {"role": "assistant", "content": content or None}
+        reply = {"role": "assistant", "content": content or None}
         if job["thinking"]:
-            message["reasoning_content"] = job["thinking"]
+            reply["reasoning_content"] = job["thinking"]
         if calls:
-            message["tool_calls"] = [{"id": c["id"], "type": "function", "function": c["function"]} for c in calls]
-        return {"id": "chatcmpl-" + key, "object": "chat.completion", "created": int(job["created"]), "model": name,
-                "choices": [{"index": 0, "message": message, "logprobs": None, "finish_reason": finish_reason(job, calls)}],
-                "usage": usage(job)}
+            reply["tool_calls"] = [{k: c[k] for k in ("id", "type", "function")} for c in calls]
+        choice = {"index": 0, "message": reply, "logprobs": None, "finish_reason": _why_it_ended(job, calls)}
+        return {"id": "chatcmpl-" + key, "object": "chat.completion", "created": int(job["created"]), "model": model, "choices": [choice],
+                "usage": _token_counts(job)}
 
-    def stream(self, data):
-        """Yield SSE chunks (bytes).  Tool calls are emitted once the final channel is known."""
-        payload, key, name = self.prepare(data)
-        self.queue.submit(payload, key, label="api")
-        ident = {"id": "chatcmpl-" + key, "object": "chat.completion.chunk", "model": name, "created": int(time.time())}
+    # ------------------------------------------------------------------------------------------------------------------ a stream
+    def stream(self, body):
+        """Server-sent events (bytes)."""
+        key, model = self._admit(body)
+        ident = {"id": "chatcmpl-" + key, "object": "chat.completion.chunk", "model": model, "created": int(time.time())}
         yield self.chunk(ident, {"role": "assistant", "content": ""}, None)
-        deadline = time.time() + self.wait_seconds
-        sent_thinking = sent_answer = 0
-        while True:
-            job = self._job(key)
-            terminal = job["status"] in DONE
-            thinking, answer = job["thinking"], job["answer"]
-            if len(thinking) > sent_thinking:
-                yield self.chunk(ident, {"reasoning_content": thinking[sent_thinking:]}, None)
-                sent_thinking = len(thinking)
-            visible = answer if terminal else answer.split(OPEN, 1)[0]  # hold text back while a tool call may be forming
-            if not terminal and len(visible) > sent_answer:
-                yield self.chunk(ident, {"content": visible[sent_answer:]}, None)
-                sent_answer = len(visible)
-            if terminal:
-                break
-            if time.time() > deadline:
-                raise ApiError("the resident model did not finish within the server deadline", status=504, kind="timeout")
-            time.sleep(self.poll_seconds)
+        told = {"reasoning_content": 0, "content": 0}  # characters already sent, per channel
+        job = None
+        for job in self._follow(key):
+            running = job["status"] not in DONE
+            # while the job runs, text after an opening tool-call tag is withheld: it will become a tool call, not content;
+            # the final snapshot's content is sent below, after the calls have been parsed out of it
+            grown = {"reasoning_content": job["thinking"], "content": job["answer"].split(OPEN, 1)[0] if running else None}
+            for channel, text in grown.items():
+                if text is not None and len(text) > told[channel]:
+                    yield self.chunk(ident, {channel: text[told[channel]:]}, None)
+                    told[channel] = len(text)
         content, calls = parse(job["answer"])
-        if len(content) > sent_answer:
-            yield self.chunk(ident, {"content": content[sent_answer:]}, None)
+        if len(content) > told["content"]:
+            yield self.chunk(ident, {"content": content[told["content"]:]}, None)
         for call in calls:
-            yield self.chunk(ident, {"tool_calls": [{"index": call["index"], "id": call["id"], "type": "function",
-                                                     "function": dict(call["function"])}]}, None)
-        yield self.chunk(ident, {}, finish_reason(job, calls), extra={"usage": usage(job)})
+            entry = {"index": call["index"], "id": call["id"], "type": "function", "function": dict(call["function"])}
+            yield self.chunk(ident, {"tool_calls": [entry]}, None)
+        yield self.chunk(ident, {}, _why_it_ended(job, calls), extra={"usage": _token_counts(job)})
         yield b"data: [DONE]\n\n"
 
     @staticmethod
     def chunk(ident: dict, delta: dict, finish, *, extra=None) -> bytes:
-        body = dict(ident, choices=[{"index": 0, "delta": delta, "logprobs": None, "finish_reason": finish}])
-        if extra:
-            body.update(extra)
-        return b"data: " + json.dumps(body, ensure_ascii=False).encode() + b"\n\n"
+        """One event: the identifying fields, a single choice with ``delta`` and ``finish_reason``, then ``extra`` (usage)."""
+        event = {**ident, "choices": [{"index": 0, "delta": delta, "logprobs": None, "finish_reason": finish}], **(extra or {})}
+        return b"data: " + json.dumps(event, ensure_ascii=False).encode() + b"\n\n"
