@@ -16,41 +16,53 @@ from typing import Any
 
 from glm_tpu_b200.utils.json_utils import canonical_wire_bytes
 
+# ---- who runs what: `python -m` targets, and the flag a controller sets so that a worker started by hand refuses to run
 CONTROLLER_MODULE = "glm_tpu_b200.executor.multiproc_executor"
 WORKER_MODULE = "glm_tpu_b200.worker.gpu_worker"
 PACK_WORKER_MODULE = "glm_tpu_b200.model_loader.pack_worker"
 WORKER_ENV_FLAG = "GLM_B200_WORKER"
 
-INBOX_DIR = "inbox"
-STOP_FILE = "stop.json"
-STOP_COMMAND = b'{"stop":true}\n'
-READY_FILE = "resident-ready.json"
-MEASUREMENT_FILE = "resident-measurement.json"
-CONTROLLER_IDENTITY_FILE = "controller_identity.json"
-CONTROLLER_TERMINAL_FILE = "controller_terminal.json"
-SUMMARY_FILE = "summary.json"
-TOKENS_FILE = "tokens.jsonl"
-ANSWER_FILE = "answer.txt"
-PRODUCER_LOCK = "producer.lock"
+# ---- lines on a controller's stdout that front ends look for
 STDOUT_RUN = "RUN "
 STDOUT_RESIDENT_RESULT = "RESIDENT_RESULT "
 
+# ---- names inside a run directory
+INBOX_DIR = "inbox"
+STOP_FILE, STOP_COMMAND = "stop.json", b'{"stop":true}\n'
+PRODUCER_LOCK = "producer.lock"
+READY_FILE = "resident-ready.json"
+MEASUREMENT_FILE = "resident-measurement.json"
+SUMMARY_FILE = "summary.json"
+CONTROLLER_IDENTITY_FILE, CONTROLLER_TERMINAL_FILE = "controller_identity.json", "controller_terminal.json"
+TOKENS_FILE, ANSWER_FILE = "tokens.jsonl", "answer.txt"
+SEQUENCE_DIGITS = 4
+
+
+def _numbered(sequence: int) -> str:
+    if sequence < 0:
+        raise ValueError("sequence numbers start at 0")
+    return str(sequence).zfill(SEQUENCE_DIGITS)
+
 
 def inbox_name(sequence: int) -> str:
-    return f"{sequence:04d}.json"
+    """File name of request ``sequence`` in the inbox."""
+    return _numbered(sequence) + ".json"
 
 
 def result_dir(root: Path, sequence: int) -> Path:
-    return Path(root) if sequence == 0 else Path(root) / f"resident-{sequence:04d}"
+    """Where a sequence's records go: the first request (0) writes into the run directory itself."""
+    root = Path(root)
+    return root / ("resident-" + _numbered(sequence)) if sequence else root
 
 
 def runner_file(rank: int) -> str:
-    return f"runner.rank{rank}.json"
+    return "runner.rank%d.json" % rank
 
 
 def worker_started_file(rank: int) -> str:
-    return f"worker_started.rank{rank}.json"
+    return "worker_started.rank%d.json" % rank
 
 
 def encode_command(sequence: int, request: Any) -> bytes:
-    return canonical_wire_bytes({"sequence": sequence, "request": request}) + b"\n"
+    """One line for a worker's stdin."""
+    return canonical_wire_bytes({"request": request, "sequence": sequence}) + b"\n"

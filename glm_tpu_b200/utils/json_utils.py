@@ -1,10 +1,10 @@
-"""Two canonical JSON encodings.
+"""Two canonical JSON encodings of one value.
 
-``canonical_wire_bytes`` is what goes over a wire or into a file that another process reads
-(sorted keys, compact, UTF-8, NaN refused).  ``canonical_hash_bytes`` is the input of every
-content hash (same, but ASCII-escaped so the digest does not depend on an encoding choice).
+Both sort keys, use the most compact separators and refuse NaN / infinity.  They differ in how text leaves the process: the *wire* form
+keeps characters as UTF-8 (what is written to files, pipes and sockets), the *hash* form escapes everything outside ASCII (what is fed to
+SHA-256, so that a digest never depends on an encoding choice).  ``fingerprint`` is the SHA-256 of the hash form.
 
-Parity: reference ``glm_tpu/utils/json_utils.py:13-34``.
+Parity: reference ``glm_tpu/utils/json_utils.py`` (the same two contracts).
 """
 
 from __future__ import annotations
@@ -14,12 +14,16 @@ import json
 from typing import Any
 
 
+def _canonical_text(value: Any, *, ascii_only: bool) -> str:
+    return json.dumps(value, ensure_ascii=ascii_only, allow_nan=False, sort_keys=True, separators=(",", ":"))
+
+
 def canonical_wire_bytes(value: Any) -> bytes:
-    return json.dumps(value, sort_keys=True, separators=(",", ":"), ensure_ascii=False, allow_nan=False).encode("utf-8")
+    return _canonical_text(value, ascii_only=False).encode("utf-8")
 
 
 def canonical_hash_bytes(value: Any) -> bytes:
-    return json.dumps(value, sort_keys=True, separators=(",", ":"), ensure_ascii=True, allow_nan=False).encode("ascii")
+    return _canonical_text(value, ascii_only=True).encode("ascii")
 
 
 def fingerprint(value: Any) -> str:
