@@ -1,10 +1,11 @@
-"""``ask``: prepare one to ten questions and hand them to the controller.
+"""``ask``: turn one to ten questions into prepared requests and hand them to the controller.
 
-Questions are rendered with the chat format, tokenized with the session's tokenizer and written as prepared requests
-into a fresh owner-only directory under the run root (never inside the checkout); one batch (sequential, or up to four
-concurrent chats at the 32K profile) is queued before the single launch.
+The questions never touch the checkout: they are staged in a fresh owner-only directory under the run root, each as the chat messages
+it was asked as (``messages-NNN.json``) and as the prepared request made from them (``prepared-NNN.json``: rendered with the chat
+format, tokenized with the session's tokenizer, budgeted for the context profile), plus the one ``request.json`` the controller is
+started with: the single request, or a batch (answered in order, or as up to four concurrent chats at the concurrent profile).
 
-Parity: reference ``glm_tpu/entrypoints/cli/ask.py:12-93``.
+Parity: reference ``glm_tpu/entrypoints/cli/ask.py`` (same staging names, limits and refusals).
 """
 
 from __future__ import annotations
@@ -12,6 +13,7 @@ from __future__ import annotations
 import json
 import os
 import time
+from dataclasses import dataclass
 from pathlib import Path
 
 from glm_tpu_b200.engine import request as rq
@@ -19,37 +21,64 @@ from glm_tpu_b200.utils.io_utils import create_private_exclusive, read_bounded
 from glm_tpu_b200.utils.json_utils import canonical_wire_bytes
 
 
-def prepare_questions(questions, *, tokenizer, profile, output_root: Path, context_capacity: int, max_new_tokens, concurrent=False,
-                      repo: Path | None = None) -> Path:
-    if type(questions) is not list or not 1 <= len(questions) <= rq.QUEUE_LIMIT or any(type(q) is not str or not q.strip() for q in questions):
-        raise ValueError("provide one to ten nonempty question strings")
-    if repo is not None and Path(output_root).resolve().is_relative_to(Path(repo).resolve()):
-        raise ValueError("private questions must stay outside the repository")
-    if concurrent and (len(questions) > profile.concurrent_limit or context_capacity != profile.concurrent_capacity):
-        raise ValueError("concurrent mode accepts up to four questions at the concurrent capacity profile")
-    if max_new_tokens is not None and (type(max_new_tokens) is not int or max_new_tokens < 1):
-        raise ValueError("output budget must be a positive integer")
-    output_root = Path(output_root)
-    output_root.mkdir(mode=0o700, parents=True)
-    values = []
-    for index, question in enumerate(questions):
-        messages = [{"role": "user", "content": question}]
-        create_private_exclusive(output_root / f"messages-{index:03d}.json", canonical_wire_bytes(messages) + b"\n")
-        ids = tokenizer.apply_chat_template(messages, reasoning_effort="max")
-        budget = max_new_tokens if max_new_tokens is not None else rq.default_max_new_tokens(len(ids), context_capacity, profile)
+def _stage(directory: Path, name: str, value) -> bytes:
+    """Write ``value`` as one canonical JSON line into a new private file; returns the bytes written."""
+    line = canonical_wire_bytes(value) + b"\n"
+    create_private_exclusive(directory / name, line)
+    return line
+
+
+@dataclass(frozen=True)
+class QuestionSet:
+    """What one ``ask`` invocation wants answered, checked against the profile before anything is written."""
+
+    questions: list
+    concurrent: bool
+    context_capacity: int
+    max_new_tokens: int | None
+
+    def check(self, profile) -> None:
+        texts = self.questions
+        well_formed = isinstance(texts, list) and all(isinstance(t, str) and t.strip() for t in texts)
+        if not well_formed or not 1 <= len(texts) <= rq.QUEUE_LIMIT:
+            raise ValueError("provide one to ten nonempty question strings")
+        if self.concurrent and (len(texts) > profile.concurrent_limit or self.context_capacity != profile.concurrent_capacity):
+            raise ValueError("concurrent mode accepts up to four questions at the concurrent capacity profile")
+        if self.max_new_tokens is not None and (type(self.max_new_tokens) is not int or self.max_new_tokens < 1):
+            raise ValueError("output budget must be a positive integer")
+
+    def prepared(self, number: int, tokenizer, profile, directory: Path) -> dict:
+        """Stage question ``number`` (0-based) and return its prepared request."""
+        messages = [{"role": "user", "content": self.questions[number]}]
+        _stage(directory, f"messages-{number:03d}.json", messages)
+        prompt = tokenizer.apply_chat_template(messages, reasoning_effort="max")
+        budget = self.max_new_tokens
+        if budget is None:
+            budget = rq.default_max_new_tokens(len(prompt), self.context_capacity, profile)
         if budget < 1:
             raise ValueError("the question leaves no room for an answer at this context capacity")
-        prepared = rq.from_token_ids(ids, request_id=f"question-{index + 1:02d}", max_new_tokens=budget,
-                                     context_capacity=context_capacity, profile=profile)
-        create_private_exclusive(output_root / f"prepared-{index:03d}.json", canonical_wire_bytes(prepared) + b"\n")
-        values.append(prepared)
-    value = values[0] if len(values) == 1 and not concurrent else rq.batch(values, concurrent=concurrent, profile=profile)
-    raw = canonical_wire_bytes(value) + b"\n"
-    if len(raw) > rq.PAYLOAD_CAP:
+        request = rq.from_token_ids(prompt, request_id=f"question-{number + 1:02d}", max_new_tokens=budget,
+                                    context_capacity=self.context_capacity, profile=profile)
+        _stage(directory, f"prepared-{number:03d}.json", request)
+        return request
+
+
+def prepare_questions(questions, *, tokenizer, profile, output_root: Path, context_capacity: int, max_new_tokens, concurrent=False,
+                      repo: Path | None = None) -> Path:
+    """Stage everything under ``output_root`` (which must not exist yet) and return the path of ``request.json``."""
+    wanted = QuestionSet(questions, bool(concurrent), context_capacity, max_new_tokens)
+    wanted.check(profile)
+    directory = Path(output_root)
+    if repo is not None and directory.resolve().is_relative_to(Path(repo).resolve()):
+        raise ValueError("private questions must stay outside the repository")
+    directory.mkdir(mode=0o700, parents=True)
+    requests = [wanted.prepared(number, tokenizer, profile, directory) for number in range(len(questions))]
+    alone = len(requests) == 1 and not wanted.concurrent
+    bundle = requests[0] if alone else rq.batch(requests, concurrent=wanted.concurrent, profile=profile)
+    if len(canonical_wire_bytes(bundle)) + 1 > rq.PAYLOAD_CAP:
         raise ValueError("combined request payload is too large")
-    path = output_root / "request.json"
-    create_private_exclusive(path, raw)
-    return path
+    _stage(directory, "request.json", bundle)
+    return directory / "request.json"
 
 
 def main(args) -> int:
