@@ -23,6 +23,17 @@ def test_import_closures_only_shrink():
     assert driver.check({"g6_import_closures"}) == {}
 
 
+def test_executed_function_set_matches_golden():
+    from tools.equivalence import executed
+
+    assert driver.check({"g7_executed_functions"}) == {}
+    golden = driver.load("g7_executed_functions")["functions"]
+    assert "glm_tpu_b200.engine.llm_engine:LLMEngine.generate" in golden and "glm_tpu_b200.oracle.contract:top_k_positions" in golden
+    assert not any(name.startswith(("glm_tpu_b200.ops", "glm_tpu_b200.runner.gpu_runner")) for name in golden)  # the CPU scenario stays device-free
+    moved = executed.difference({"functions": ["a:f", "a:g"]}, {"functions": ["a:g", "b:h"]})
+    assert moved == {"no_longer_executed": ["a:f"], "newly_executed": ["b:h"]}
+
+
 def test_entry_points_stay_light():
     golden = driver.load("g6_import_closures")
     assert golden["glm_tpu_b200.entrypoints.cli.main"]["heavy"] == []  # `info` and `--help` never import torch

@@ -10,10 +10,10 @@ DATA = Path(__file__).resolve().parents[2] / "tests" / "golden" / "data"
 
 
 def gates() -> dict:
-    from tools.equivalence import digests, imports, wire
+    from tools.equivalence import digests, executed, imports, wire
 
     return {"g3_oracle_digests": digests.oracle_digests, "g4_checkpoint_identity": digests.checkpoint_identity, "g6_import_closures": imports.collect,
-            "g9_wire_formats": wire.collect}
+            "g7_executed_functions": executed.collect, "g9_wire_formats": wire.collect}
 
 
 def load(name: str):
@@ -21,7 +21,7 @@ def load(name: str):
 
 
 def check(names=None) -> dict:
-    from tools.equivalence import imports
+    from tools.equivalence import executed, imports
 
     failures = {}
     for name, fn in gates().items():
@@ -32,6 +32,10 @@ def check(names=None) -> dict:
             extra = imports.grown(golden, current)
             if extra:
                 failures[name] = extra
+        elif name == "g7_executed_functions":
+            moved = executed.difference(golden, current)
+            if moved["no_longer_executed"] or moved["newly_executed"]:
+                failures[name] = moved
         elif current != golden:
             failures[name] = {k: {"golden": golden.get(k), "current": current.get(k)} for k in sorted(set(golden) | set(current)) if golden.get(k) != current.get(k)}
     return failures
