@@ -88,10 +88,10 @@ __device__ __forceinline__ bool wait_flag_reached(const uint32_t* p, uint32_t ex
 
 // Sum `count` fp32 values held in shared memory `sh` over all ranks, in rank order (bitwise identical on
 // every rank).  Every thread of the CTA must call it; count <= GLMB_AR_SLICE; blockDim.x >= world.
-__device__ __forceinline__ void cta_allreduce_f32(const PeerComm& c, int channel, float* sh, int count) {
+// `cta` (< GLMB_AR_MAX_CTAS) names the exchange slot: the same number on every rank for the same slice.
+__device__ __forceinline__ void cta_allreduce_f32_slot(const PeerComm& c, int channel, int cta, float* sh, int count) {
     if (c.world == 1) return;
     __shared__ uint32_t s_epoch;
-    const int cta = blockIdx.x + blockIdx.y * gridDim.x;
     const int slot = channel * GLMB_AR_MAX_CTAS + cta;
     if (threadIdx.x == 0) s_epoch = c.seq[slot] + 1;
     __syncthreads();
@@ -119,6 +119,11 @@ __device__ __forceinline__ void cta_allreduce_f32(const PeerComm& c, int channel
     }
     if (threadIdx.x == 0) c.seq[slot] = e;
     __syncthreads();
+}
+
+// The slot is this CTA's index in its grid.
+__device__ __forceinline__ void cta_allreduce_f32(const PeerComm& c, int channel, float* sh, int count) {
+    cta_allreduce_f32_slot(c, channel, blockIdx.x + blockIdx.y * gridDim.x, sh, count);
 }
 
 // Producer side of a signal: call once per CTA after the CTA's pushes.  The last CTA of the grid bumps the

@@ -406,6 +406,32 @@ class GlmMoeDsaModel:
             self.trace.setdefault("attn_out", {})[layer] = ws.attn_out[:rows].clone()
             self.trace.setdefault("kv_new", {})[layer] = ws.kv_new[:rows].clone()
 
+    def select_keys_decode(self, ws: Workspace, state: DecoderState, layer: int, rows: int) -> None:
+        """Indexer scores and the exact top-k of a layer with its own indexer, for the rows of a decode step whose q_b projection
+        (``ws.q_proj``), head weights and index-cache row are already in place: the two launches between two stretches of the
+        persistent decode kernel.  Keys of this GPU's cache only (one GPU, or a replicated cache)."""
+        g, lay, cache = self.g, self.layout, self.cache
+        IH, D, rd, L = g.index_heads, g.index_head_dim, g.qk_rope_head_dim, g.kv_lora_rank
+        hl = lay.heads_local
+        row_pos, row_lane = state.positions, state.lane_ids
+        raw = native.indexer_takes_raw_query(IH, D)
+        if not raw:  # head shapes the tcgen05 indexer does not take: rotate the index query with the stand-alone kernel first
+            b = native.QPostArgs()
+            b.q, b.q_stride = ws.q_proj.data_ptr(), ws.q_proj.stride(0)
+            b.rope_table, b.inv_freq, b.row_pos = self.rope.data_ptr(), self.inv_freq.data_ptr(), row_pos.data_ptr()
+            b.q_nope, b.q_full, b.q_idx = ws.q_nope.data_ptr(), ws.q_full.data_ptr(), ws.q_idx.data_ptr()
+            b.heads_local, b.head_base, b.heads_total = hl, self.head_base, self.attn_heads
+            b.nope, b.rd, b.L, b.IH, b.D = g.qk_nope_head_dim, rd, L, IH, D
+            b.has_indexer, b.capacity = 1, cache.context_capacity
+            native.q_post(b, rows)
+        native.indexer_score(ws.q_idx, ws.head_w, state.index_cache, row_pos, row_lane, rows, IH, D, g.index_slot(layer),
+                             len(g.full_layers), cache.local_capacity, cache.stripe, cache.world, self.cache_rank,
+                             cache.context_capacity, cache.context_capacity, ws.score_stride, self.index_scale, ws.scores, 0, None,
+                             native.SIG_SCORES, self.peer.status_ptr,
+                             **(dict(q_raw=ws.q_proj, q_offset=hl * g.qk_head_dim, inv_freq=self.inv_freq, rd=rd) if raw else {}))
+        native.topk_select(ws.scores, row_pos, rows, cache.context_capacity, ws.score_stride, g.index_top_k, cache.stripe, cache.world,
+                           self.cache_rank, ws.sel_global, ws.sel_local, ws.sel_counts, None, native.SIG_SCORES)
+
     # NCCL baseline pieces ---------------------------------------------------------------------
     def _allgather_heads(self, q_full: torch.Tensor) -> None:
         import torch.distributed as dist

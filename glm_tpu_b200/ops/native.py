@@ -509,6 +509,11 @@ def wait_signal(comm, sig):
     _check(lib().glmb_wait_signal(_comm(comm), sig, _stream()), "wait_signal")
 
 
+def set_mega_cooperative(enabled: int) -> None:
+    """1 (default): the persistent decode kernel is launched cooperatively; 0: as an ordinary launch of the same grid."""
+    lib().glmb_set_mega_cooperative(int(enabled))
+
+
 def set_gemm_variant(variant: int) -> None:
     """0: pick by problem size (default); 1: one 128x128 tile per CTA; 2: the persistent 128x256 kernel."""
     lib().glmb_set_gemm_variant(int(variant))

@@ -71,7 +71,8 @@ class _LaunchCounter:
 class GpuModelRunner:
     def __init__(self, weights: DeviceWeights, *, context_capacity: int, lanes: int = 1, stripe: int = 64, comm: str = "fused",
                  group=None, prefill_chunk: int = 512, use_graphs: bool = True, wait_limit: int = 2_000_000,
-                 staging_bytes: int | None = None, kv_layout: str = "auto", replica_budget_bytes: int = 32 << 30):
+                 staging_bytes: int | None = None, kv_layout: str = "auto", replica_budget_bytes: int = 32 << 30,
+                 decode_path: str = "auto", mega_compat_ksplit: bool | None = None):
         self.weights = weights
         self.g, self.layout = weights.geometry, weights.layout
         self.device = weights.embed.device
@@ -103,6 +104,26 @@ class GpuModelRunner:
             self.model = GlmMoeDsaModel(weights, self.cache, self.peer, comm=comm, group=group)
             self.state = DecoderState.allocate(self.cache, self.device)
             self.decode_ws = Workspace(self.model, lanes, "decode")
+            # decode program: the persistent kernel (a step is a few dozen launches) where its shapes and cache layout allow,
+            # else the per-kernel sequence.  GLM_B200_DECODE=kernels|mega overrides 'auto'.
+            import os
+
+            if decode_path == "auto":
+                decode_path = os.environ.get("GLM_B200_DECODE", "auto")
+            if decode_path not in ("auto", "mega", "kernels"):
+                raise ValueError("decode_path is 'auto', 'mega' or 'kernels'")
+            if mega_compat_ksplit is None:
+                mega_compat_ksplit = os.environ.get("GLM_B200_MEGA_KSPLIT", "balanced") == "compat"
+            self.mega = None
+            if decode_path != "kernels":
+                from glm_tpu_b200.models.glm_moe_dsa.mega import MegaDecoder
+
+                mega = MegaDecoder(self.model, self.decode_ws, self.state, compat_ksplit=mega_compat_ksplit)
+                if mega.supported:
+                    self.mega = mega
+                elif decode_path == "mega":
+                    raise ValueError(f"the persistent decode kernel does not take this configuration (code {mega.supported_code})")
+            self.decode_path = "mega" if self.mega is not None else "kernels"
             self.prefill_ws = None
             self._prefill_out = torch.zeros(1, dtype=torch.int32, device=self.device)
             self._graph = None
@@ -115,6 +136,9 @@ class GpuModelRunner:
     # ------------------------------------------------------------------ decode program
     def _decode_body(self) -> None:
         st, ws, m = self.state, self.decode_ws, self.model
+        if self.mega is not None:
+            self.mega.step()
+            return
         logits = m.run_rows(ws, st, st.tokens, st.positions, st.lane_ids, st.active, self.lanes, decode=True,
                             max_ctx=self.cache.context_capacity, head="argmax")
         m.sample(ws, st, logits, self.lanes, st.active, advance=3)
@@ -131,9 +155,21 @@ class GpuModelRunner:
             torch.cuda.synchronize(self.device)
             kind = "eager"
             if self.use_graphs and self.model.comm_mode == "fused" or (self.use_graphs and self.world == 1):
-                graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(graph, stream=self._graph_stream):
-                    self._decode_body()
+                try:
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(graph, stream=self._graph_stream):
+                        self._decode_body()
+                except RuntimeError:
+                    if self.mega is None:
+                        raise
+                    # a driver that will not record a cooperative launch: the same grid as an ordinary launch (it fits the GPU
+                    # and nothing else runs beside it, so every CTA is resident all the same)
+                    torch.cuda.synchronize(self.device)
+                    native.set_mega_cooperative(0)
+                    self.report.phases["mega_cooperative_capture"] = "refused: ordinary launch"
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(graph, stream=self._graph_stream):
+                        self._decode_body()
                 self._graph = graph
                 kind = "cuda_graph"
             self.state.active.copy_(saved)
@@ -141,7 +177,7 @@ class GpuModelRunner:
             self.steps_issued = 0
             torch.cuda.synchronize(self.device)
             self.peer.check_status()
-        rec = ProgramRecord("decode", kind, self.lanes, self.decode_launches, time.perf_counter() - t0)
+        rec = ProgramRecord("decode:" + self.decode_path, kind, self.lanes, self.decode_launches, time.perf_counter() - t0)
         self.report.programs.append(rec)
         return rec
 
