@@ -38,6 +38,8 @@
 //
 // Replaces the launch sequence of reference `glm_tpu/models/glm_moe_dsa/model.py:86-135`, `decoder_layer.py:656-740`.
 #include "common.cuh"
+
+#include <string.h>
 #include "attention_core.cuh"
 #include "gemv_core.cuh"
 #include "moe_mma_core.cuh"
@@ -45,6 +47,12 @@
 #include "peer.cuh"
 
 #define MG_THREADS 256
+#ifndef MG_CALL
+#define MG_CALL __noinline__  // phases and their shared pieces are functions of their own (code size, register allocation per phase)
+#endif
+#ifndef MG_CTAS_PER_SM
+#define MG_CTAS_PER_SM 2  // resident CTAs per SM the kernel is compiled and launched for
+#endif
 #define MG_WARPS 8
 #define MG_MAX_TOPK 32
 #define MG_BIG_BYTES (100 * 1024)
@@ -54,11 +62,16 @@
 enum { MG_QKV_A = 1, MG_Q_B, MG_ABSORB, MG_ATTN, MG_MERGE, MG_VPROJ, MG_OPROJ, MG_MLP_A, MG_MLP_B, MG_MOE_DOWN, MG_COMBINE };
 enum { MG_HEAD_LOGITS = 1, MG_HEAD_FINALIZE = 2 };
 
+// The words of the grid barrier, each on a cache line of its own: the arrival counter takes one atomic per CTA, the
+// generation word is polled by every waiting CTA, and the two must not queue behind each other at one L2 line.
 struct MegaBarrier {
     unsigned int arrive;
+    unsigned int pad0[31];
     unsigned int gen;
+    unsigned int pad1[31];
     unsigned int abort;
-    unsigned int pad;
+    unsigned int pad2[31];
+    unsigned int flags[1024];  // variant 2 of the barrier: one arrival word per CTA
 };
 
 // One per layer, in device memory (pointers first: no padding).
@@ -144,7 +157,8 @@ struct MegaArgs {
     unsigned long long* cand;
     MegaBarrier* bar;
     uint32_t* status;
-    int64_t proj_stride, q_stride, act_shared_stride, dense_act_stride, cand_offset;
+    unsigned long long* timeline;  // optional: [0] = entries written, then (code, globaltimer ns) pairs; code = layer << 8 | phase
+    int64_t proj_stride, q_stride, act_shared_stride, dense_act_stride, cand_offset, timeline_cap, prefetch_cap;
     // geometry and layout
     int rows, H, Q, L, rd, nope, vdim, D, IH;
     int heads_local, head_base, heads_total, E, top_k, I, experts_local, expert_base, shared_cols, dense_cols;
@@ -157,6 +171,8 @@ struct MegaArgs {
 };
 
 struct MgSmall {
+    MegaArgs args;    // the kernel's argument block, copied once: phase functions read it here, not through a generic pointer
+    MegaLayer layer;  // the pointer-table entry of the layer in progress
     float red[MG_WARPS][2][GLMB_MAX_ROWS];
     float sh[GLMB_AR_SLICE];
     float scratch[3][40];
@@ -168,29 +184,93 @@ struct MgSmall {
     float w_s[MG_MERGE_MAX_CHUNKS];
     float red_s[8];
     int n_loc;
-    int pad_[3];
+    int big_bytes;                 // size of the big region behind this block (a launch-time choice)
+    int stamping;                  // this thread block's first thread writes per-phase time stamps (measurements)
+    unsigned long long stamp_at;   // next free entry of the stamp buffer
 };
+
+// (code, %globaltimer) into the stamp buffer; CTA 0's first thread only.  code = layer << 8 | phase (bit 7: before the
+// phase's grid barrier; bits 16..: a step inside the phase).
+__device__ __forceinline__ void mg_stamp(MgSmall& sm, unsigned long long code) {
+    if (!sm.stamping || threadIdx.x != 0) return;
+    const MegaArgs& a = sm.args;
+    if ((int64_t)sm.stamp_at < a.timeline_cap) {
+        unsigned long long now;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+        a.timeline[1 + 2 * sm.stamp_at] = code;
+        a.timeline[2 + 2 * sm.stamp_at] = now;
+    }
+    ++sm.stamp_at;
+}
 
 // ---------------------------------------------------------------------------------------------------
 // Grid barrier over all CTAs of the (cooperative) launch.  `epoch` is each thread's copy of the generation the
 // grid has completed; it starts from the value every CTA reads at kernel entry (no barrier is in flight then).
-__device__ __forceinline__ void mg_grid_barrier(MegaBarrier* b, unsigned int& epoch, uint32_t limit, uint32_t* status) {
+__device__ __forceinline__ unsigned int mg_ld_relaxed(const unsigned int* p) {
+    unsigned int v;
+    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// VARIANT 1: one atomic per CTA on the arrival counter, the last arriver publishes the generation, the others poll it
+// with relaxed loads (a fence on either side orders the data).  VARIANT 2: every CTA stores its own arrival word, CTA 0
+// gathers them (one word per thread) and publishes.  VARIANT 0: counter and generation on neighbouring words, acquire
+// polling (the first form, kept for the measurement in `glmb_mega_barrier_bench`).
+template <int VARIANT>
+__device__ __forceinline__ void mg_grid_barrier_v(MegaBarrier* b, unsigned int& epoch, uint32_t limit, uint32_t* status) {
+    const unsigned int target = epoch + 1;
+    if (VARIANT == 2) {
+        const bool live = __syncthreads_or(mg_ld_relaxed(&b->abort) != 0u) == 0;  // the same answer in every thread of the CTA
+        if (threadIdx.x == 0 && live) {
+            __threadfence();
+            asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(&b->flags[blockIdx.x]), "r"(target) : "memory");
+        }
+        if (blockIdx.x == 0 && live) {
+            bool ok = true;
+            for (unsigned int c = threadIdx.x; c < gridDim.x; c += blockDim.x) {
+                bool seen = false;
+                for (uint32_t i = 0; i < limit; ++i) {
+                    if ((int)(mg_ld_relaxed(&b->flags[c]) - target) >= 0) { seen = true; break; }
+                    if (i > 4096) { if (mg_ld_relaxed(&b->abort)) break; __nanosleep(64); }
+                }
+                ok = ok && seen;
+            }
+            if (!ok) { atomicExch(&b->abort, 1u); raise_status(status, GLMB_STATUS_WAIT_TIMEOUT); }
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                __threadfence();
+                asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(&b->gen), "r"(target) : "memory");
+            }
+        } else if (threadIdx.x == 0 && live) {
+            bool ok = false;
+            for (uint32_t i = 0; i < limit; ++i) {
+                if ((int)(mg_ld_relaxed(&b->gen) - target) >= 0) { ok = true; break; }
+                if (i > 4096) { if (mg_ld_relaxed(&b->abort)) break; __nanosleep(64); }
+            }
+            if (!ok) { atomicExch(&b->abort, 1u); raise_status(status, GLMB_STATUS_WAIT_TIMEOUT); }
+        }
+        if (threadIdx.x == 0) __threadfence();
+        epoch += 1;
+        __syncthreads();
+        return;
+    }
     __syncthreads();
-    if (threadIdx.x == 0 && *reinterpret_cast<volatile unsigned int*>(&b->abort) == 0u) {
-        const unsigned int target = epoch + 1;
+    if (threadIdx.x == 0 && mg_ld_relaxed(&b->abort) == 0u) {
+        unsigned int* gen = VARIANT == 0 ? &b->pad0[0] : &b->gen;
         __threadfence();
         if (atomicAdd(&b->arrive, 1u) == gridDim.x - 1) {
             b->arrive = 0;  // nobody arrives at the next barrier before the release below
             __threadfence();
-            asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(&b->gen), "r"(target) : "memory");
+            asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(gen), "r"(target) : "memory");
         } else {
             bool ok = false;
             for (uint32_t i = 0; i < limit; ++i) {
                 unsigned int g;
-                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(g) : "l"(&b->gen) : "memory");
+                if (VARIANT == 0) asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(g) : "l"(gen) : "memory");
+                else g = mg_ld_relaxed(gen);
                 if ((int)(g - target) >= 0) { ok = true; break; }
                 if (i > 4096) {
-                    if (*reinterpret_cast<volatile unsigned int*>(&b->abort)) break;
+                    if (mg_ld_relaxed(&b->abort)) break;
                     __nanosleep(64);
                 }
             }
@@ -203,6 +283,13 @@ __device__ __forceinline__ void mg_grid_barrier(MegaBarrier* b, unsigned int& ep
     }
     epoch += 1;
     __syncthreads();
+}
+
+#ifndef MG_BARRIER_VARIANT
+#define MG_BARRIER_VARIANT 1
+#endif
+__device__ __forceinline__ void mg_grid_barrier(MegaBarrier* b, unsigned int& epoch, uint32_t limit, uint32_t* status) {
+    mg_grid_barrier_v<MG_BARRIER_VARIANT>(b, epoch, limit, status);
 }
 
 // ---------------------------------------------------------------------------------------------------
@@ -225,6 +312,73 @@ __device__ __forceinline__ int mg_pick_ks(int units, int K, bool compat, int max
         if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = ks; }
     }
     return best;
+}
+
+// warp_dot_bf16 (gemv_core.cuh) with U steps of loads issued before their arithmetic: the same products added in the same
+// order, but 2 * U 16-byte loads in flight per lane, which the 16 resident warps of an SM need to keep HBM busy.
+template <int R, int U>
+__device__ __forceinline__ void mg_warp_dot(const bf16* const (&xr)[R], const bf16* const (&wp)[2], int kbeg, int kend, int lane,
+                                            float (&acc)[2][R]) {
+    int k = kbeg + lane * 8;
+    for (; k + (U - 1) * 256 < kend; k += U * 256) {
+        uint4 wv[U][2];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+#pragma unroll
+            for (int j = 0; j < 2; ++j) wv[u][j] = ld_stream16(wp[j] + k + u * 256);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            float wf[2][8];
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const uint4 v = wv[u][j];
+                wf[j][0] = bf16_lo(v.x); wf[j][1] = bf16_hi(v.x); wf[j][2] = bf16_lo(v.y); wf[j][3] = bf16_hi(v.y);
+                wf[j][4] = bf16_lo(v.z); wf[j][5] = bf16_hi(v.z); wf[j][6] = bf16_lo(v.w); wf[j][7] = bf16_hi(v.w);
+            }
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const uint4 v = ld_hot16(xr[r] + k + u * 256);
+                const float xf[8] = {bf16_lo(v.x), bf16_hi(v.x), bf16_lo(v.y), bf16_hi(v.y),
+                                     bf16_lo(v.z), bf16_hi(v.z), bf16_lo(v.w), bf16_hi(v.w)};
+#pragma unroll
+                for (int j = 0; j < 2; ++j)
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) acc[j][r] = fmaf(wf[j][i], xf[i], acc[j][r]);
+            }
+        }
+    }
+    if (k < kend) {  // the tail, one step at a time, in the same order
+        const int done = k - (kbeg + lane * 8);
+        warp_dot_bf16<R, 2>(xr, wp, kbeg + done, kend, lane, acc);
+    }
+}
+
+// Ask the L2 for `bytes` at p (capped): every CTA requests its slice, one thread issues, nothing waits for it.
+__device__ __forceinline__ void mg_prefetch_l2(const void* p, size_t bytes, size_t cap) {
+    if (threadIdx.x != 0 || p == nullptr) return;
+    if (bytes > cap) bytes = cap;
+    const size_t per = ((bytes + gridDim.x - 1) / gridDim.x + 127) & ~(size_t)127;
+    const size_t off = per * blockIdx.x;
+    if (off >= bytes) return;
+    const size_t n = (per < bytes - off ? per : bytes - off) & ~(size_t)15;
+    if (n) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(reinterpret_cast<const char*>(p) + off), "r"((uint32_t)n) : "memory");
+}
+
+// Shared-memory scratch of the balanced projections: what is left of the big region after `used_bytes`.
+__device__ __forceinline__ float* mg_scratch(unsigned char* big, size_t used_bytes, int* floats) {
+    const size_t at = (used_bytes + 15) & ~(size_t)15;
+    const MgSmall* sm = reinterpret_cast<const MgSmall*>(big - ((sizeof(MgSmall) + 15) & ~(size_t)15));
+    *floats = (int)(((size_t)sm->big_bytes - at) / sizeof(float));
+    return reinterpret_cast<float*>(big + at);
+}
+
+// fp32 store of a pass of the balanced projection: out[r][first + i] = vals[i][r]
+template <int R>
+__device__ __forceinline__ void mg_store_f32(float* out, int64_t stride, int rows, int p0, int cnt, const float* vals) {
+    for (int t = threadIdx.x; t < cnt * R; t += MG_THREADS) {
+        const int i = t / R, r = t % R;
+        if (r < rows) out[(int64_t)r * stride + p0 + i] = vals[t];
+    }
 }
 
 struct MgUnit {
@@ -256,7 +410,7 @@ __device__ __forceinline__ void mg_gemv(int units, int K, int ks, int rows, MgSm
 #pragma unroll
             for (int r = 0; r < R; ++r) xr[r] = m.x + (int64_t)(r < rows ? r : 0) * m.xs;
             const bf16* wp[2] = {m.w0, m.w1};
-            warp_dot_bf16<R, 2>(xr, wp, kpart * kspan, (kpart + 1) * kspan, lane, acc);
+            mg_warp_dot<R, (R <= 2 ? 8 : (R <= 4 ? 4 : 2))>(xr, wp, kpart * kspan, (kpart + 1) * kspan, lane, acc);
             warp_reduce_all<R, 2>(acc);
         }
         if (ks > 1) {
@@ -280,13 +434,189 @@ __device__ __forceinline__ void mg_gemv(int units, int K, int ks, int rows, MgSm
     }
 }
 
+// ---------------------------------------------------------------------------------------------------
+// Balanced form of the projections: the weight rows are dealt to the CTAs in contiguous blocks (a CTA's share is one
+// contiguous piece of memory), `kw` warps split K for the same rows and the remaining warps take other rows of the block.
+// A warp walks its rows G at a time with G x U independent 16-byte loads in flight per lane and the activation vector of
+// a K step reused for the G rows; partial sums meet in shared memory once per pass, so a phase is one or two memory
+// round trips and one pair of CTA barriers, however the rows divide among the CTAs.  The activations are in shared
+// memory (two resident CTAs leave the SM almost no L1).  The pass is ONE function shared by every projection of the
+// step, so its code stays in the instruction cache from phase to phase.
+
+// Row v of a weight table: plain tables are base0 + v * stride; a gate / up pair interleaves two tables (row 2u is gate
+// row u, row 2u + 1 is up row u), so that the two halves of a SwiGLU unit land in the same CTA.
+struct MgRowMap {
+    const bf16* base0;
+    const bf16* base1;
+    int64_t stride;
+    int pair;
+    __device__ __forceinline__ const bf16* row(int v) const {
+        return pair ? ((v & 1) ? base1 : base0) + (int64_t)(v >> 1) * stride : base0 + (int64_t)v * stride;
+    }
+};
+
+template <int R, int G, int U>
+__device__ __forceinline__ void mg_block_pass_impl(const bf16* x, int64_t xs, int rows, const MgRowMap& m, int n_first, int n_cnt, int K,
+                                                   int kw, float* red) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int rg = MG_WARPS / kw, grp = warp / kw, kpart = warp % kw;
+    const int span = K / kw, kbeg = kpart * span, kend = kbeg + span;
+    const bf16* xr[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) xr[r] = x + (int64_t)(r < rows ? r : 0) * xs;
+    for (int i0 = grp * G; i0 < n_cnt; i0 += rg * G) {
+        const bf16* wp[G];
+#pragma unroll
+        for (int g = 0; g < G; ++g) wp[g] = m.row(n_first + min(i0 + g, n_cnt - 1));
+        float acc[G][R];
+#pragma unroll
+        for (int g = 0; g < G; ++g)
+#pragma unroll
+            for (int r = 0; r < R; ++r) acc[g][r] = 0.f;
+        int k = kbeg + lane * 8;
+        for (; k + (U - 1) * 256 < kend; k += U * 256) {
+            uint4 wv[U][G];
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+#pragma unroll
+                for (int g = 0; g < G; ++g) wv[u][g] = ld_stream16(wp[g] + k + u * 256);
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    float xf[8];
+                    unpack8(ld_hot16(xr[r] + k + u * 256), xf);
+#pragma unroll
+                    for (int g = 0; g < G; ++g) {
+                        float wf[8];
+                        unpack8(wv[u][g], wf);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) acc[g][r] = fmaf(wf[i], xf[i], acc[g][r]);
+                    }
+                }
+        }
+        if (U > 1)
+            for (; k < kend; k += 256) {
+                uint4 wv[G];
+#pragma unroll
+                for (int g = 0; g < G; ++g) wv[g] = ld_stream16(wp[g] + k);
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    float xf[8];
+                    unpack8(ld_hot16(xr[r] + k), xf);
+#pragma unroll
+                    for (int g = 0; g < G; ++g) {
+                        float wf[8];
+                        unpack8(wv[g], wf);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) acc[g][r] = fmaf(wf[i], xf[i], acc[g][r]);
+                    }
+                }
+            }
+#pragma unroll
+        for (int g = 0; g < G; ++g)
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const float v = warp_sum(acc[g][r]);
+                if (lane == 0 && i0 + g < n_cnt) red[((i0 + g) * kw + kpart) * R + r] = v;
+            }
+    }
+}
+
+// One pass: rows n_first .. n_first + n_cnt - 1 of the table against the activation rows x (shared memory); partial sums
+// of the kw K-splitters into red[i][kpart][r], then summed in split order into vals[i * R + r].  Ends with a CTA barrier.
+template <int R>
+__device__ MG_CALL void mg_block_pass(const bf16* x, int64_t xs, int rows, MgRowMap m, int n_first, int n_cnt, int K, int kw, float* red,
+                                           float* vals) {
+    constexpr int G1 = R <= 2 ? 12 : (R <= 4 ? 8 : 4), G3 = R <= 4 ? 4 : 2;
+    if ((K / kw + 255) / 256 == 1) mg_block_pass_impl<R, G1, 1>(x, xs, rows, m, n_first, n_cnt, K, kw, red);
+    else mg_block_pass_impl<R, G3, 3>(x, xs, rows, m, n_first, n_cnt, K, kw, red);
+    __syncthreads();
+    for (int t = threadIdx.x; t < n_cnt * R; t += MG_THREADS) {
+        const int i = t / R, r = t % R;
+        float sum = 0.f;
+        for (int kp = 0; kp < kw; ++kp) sum += red[(i * kw + kp) * R + r];
+        vals[t] = sum;
+    }
+    __syncthreads();
+}
+
+// NV weight rows (K bf16 values each) against the step's activation rows x.  The rows of a CTA come in multiples of
+// `align`.  `scratch` is shared memory of `scratch_floats` floats.  After every pass all threads call
+// post(first_row, count, vals) with vals[i * R + r] = x_r . w_(first_row + i), fp32.
+template <int R, typename Post>
+__device__ __forceinline__ void mg_gemv_blocks(int NV, int align, int K, int rows, const bf16* x, int64_t xs, const MgRowMap& m, float* scratch,
+                                               int scratch_floats, Post post) {
+    int rpc = (NV + (int)gridDim.x - 1) / (int)gridDim.x;
+    rpc = (rpc + align - 1) / align * align;
+    const int n_begin = (int)blockIdx.x * rpc, n_end = min(NV, n_begin + rpc);
+    int kw = MG_WARPS;
+    while (kw > 1 && (K / kw < 256 || K % (kw * 8))) kw >>= 1;
+    int P = scratch_floats / ((kw + 1) * R);
+    P = P / align * align;
+    if (P > 256) P = 256;
+    float* red = scratch;
+    float* vals = scratch + (size_t)P * kw * R;
+    for (int p0 = n_begin; p0 < n_end; p0 += P) {
+        const int cnt = min(P, n_end - p0);
+        mg_block_pass<R>(x, xs, rows, m, p0, cnt, K, kw, red, vals);
+        post(p0, cnt, vals);
+        __syncthreads();
+    }
+}
+
+// Activation rows from global memory into shared memory (16-byte pieces); returns the bytes used.  Ends with a CTA barrier.
+__device__ __forceinline__ size_t mg_stage_rows(bf16* dst, const bf16* src, int64_t src_stride, int rows, int K) {
+    const int vec = K >> 3;
+    for (int i = threadIdx.x; i < rows * vec; i += MG_THREADS) {
+        const int r = i / vec, v = i % vec;
+        reinterpret_cast<uint4*>(dst)[i] = *reinterpret_cast<const uint4*>(src + (int64_t)r * src_stride + v * 8);
+    }
+    __syncthreads();
+    return (size_t)rows * K * 2;
+}
+
+// The balanced form of mg_gemv_allreduce: every CTA's block of output columns is summed over the GPUs in one exchange.
+template <int R>
+__device__ __forceinline__ void mg_blocks_allreduce(const bf16* x, int64_t xs, const bf16* w, int64_t ws, int N, int K, int rows, bf16* out,
+                                                    int64_t os, int channel, const MegaArgs& a, MgSmall& sm, unsigned char* big) {
+    const int rpc = (N + (int)gridDim.x - 1) / (int)gridDim.x;
+    const int n_begin = (int)blockIdx.x * rpc, n_cnt = min(N, n_begin + rpc) - n_begin;
+    if (rpc * R > GLMB_AR_SLICE) {
+        if (threadIdx.x == 0 && blockIdx.x == 0) raise_status(a.status, GLMB_STATUS_BAD_SHAPE);
+        return;
+    }
+    if (n_cnt <= 0) return;  // the same CTAs on every GPU
+    // the activations go to shared memory when they fit beside the scratch; rows wider than that are read in place
+    const bf16* xs_ptr = x;
+    int64_t x_stride = xs;
+    size_t used = 0;
+    if ((size_t)rows * K * 2 + 8192 <= (size_t)sm.big_bytes) {
+        used = mg_stage_rows(reinterpret_cast<bf16*>(big), x, xs, rows, K);
+        xs_ptr = reinterpret_cast<const bf16*>(big);
+        x_stride = K;
+    }
+    int nf;
+    float* scratch = mg_scratch(big, used, &nf);
+    const MgRowMap m{w, w, ws, 0};
+    mg_gemv_blocks<R>(N, 1, K, rows, xs_ptr, x_stride, m, scratch, nf, [&](int p0, int cnt, const float* vals) {
+        for (int t = threadIdx.x; t < cnt * R; t += MG_THREADS) sm.sh[(p0 - n_begin) * R + t] = vals[t];
+    });
+    cta_allreduce_f32_slot(a.comm, channel, blockIdx.x, sm.sh, n_cnt * R);
+    for (int t = threadIdx.x; t < n_cnt * R; t += MG_THREADS) {
+        const int i = t / R, r = t % R;
+        if (r < rows) out[(int64_t)r * os + n_begin + i] = __float2bfloat16_rn(sm.sh[t]);
+    }
+    __syncthreads();
+}
+
 // out[r][n] = bf16(sum over the GPUs of x_r . w_n) for a K-split projection: the sums of every round are parked in shared
 // memory, one all-reduce per CTA (slot = CTA index) adds the GPUs' partials in rank order, then the owners store.
 template <int R>
 __device__ __forceinline__ void mg_gemv_allreduce(const bf16* x, int64_t xs, const bf16* w, int64_t ws, int N, int K, int rows, bf16* out,
                                                   int64_t os, int channel, const MegaArgs& a, MgSmall& sm) {
     const int units = (N + 1) / 2;
-    const int ks = mg_pick_ks(units, K, a.compat_ksplit != 0, GLMB_AR_SLICE, 2 * R);
+    const int ks = mg_pick_ks(units, K, true, GLMB_AR_SLICE, 2 * R);
     const int tpc = MG_WARPS / ks;
     const int total_teams = gridDim.x * tpc;
     const int rounds = (units + total_teams - 1) / total_teams;
@@ -323,7 +653,7 @@ __device__ __forceinline__ void mg_gemv_allreduce(const bf16* x, int64_t xs, con
 // ---------------------------------------------------------------------------------------------------
 // add + RMSNorm of one row with the stand-alone kernel's thread mapping and reduction tree (add_rmsnorm_kernel), by the whole
 // CTA.  x_out: shared memory; res_out / x_glob (may be null): global copies.
-__device__ __forceinline__ void mg_addnorm_block(const bf16* update, const bf16* residual, const bf16* weight, bf16* x_out,
+__device__ MG_CALL void mg_addnorm_block(const bf16* update, const bf16* residual, const bf16* weight, bf16* x_out,
                                                  bf16* res_out, bf16* x_glob, int H, float eps, float* scratch) {
     const int nvec = H >> 3;
     uint4 rv[RN_VECS], uv[RN_VECS], wv[RN_VECS];
@@ -377,7 +707,7 @@ __device__ __forceinline__ void mg_addnorm_block(const bf16* update, const bf16*
 
 // The same row by ONE warp, which plays the eight warps of the CTA version one after the other (same per-thread order,
 // same warp sums, same final tree), so that the rows of a step are normalised side by side, one per warp.
-__device__ __forceinline__ void mg_addnorm_warp(const bf16* update, const bf16* residual, const bf16* weight, bf16* x_out, bf16* res_out,
+__device__ MG_CALL void mg_addnorm_warp(const bf16* update, const bf16* residual, const bf16* weight, bf16* x_out, bf16* res_out,
                                                 bf16* x_glob, int H, float eps) {
     const int lane = threadIdx.x & 31, nvec = H >> 3;
     float mine = 0.f;
@@ -445,7 +775,7 @@ __device__ __forceinline__ void mg_addnorm_warp(const bf16* update, const bf16* 
 
 // x_s[r] = RMSNorm(update[r] + residual_in[r]) for every row of the step, in every CTA; CTA 0 also stores the new residual
 // (and the normalised rows when x_glob is given).  layer0 rows come straight from the embedding table.
-__device__ __noinline__ void mg_norm_rows(const MegaArgs& a, const bf16* update, const bf16* res_in, bool from_embedding,
+__device__ __forceinline__ void mg_norm_rows(const MegaArgs& a, const bf16* update, const bf16* res_in, bool from_embedding,
                                              const bf16* weight, bf16* x_s, bf16* res_out, bf16* x_glob, MgSmall& sm) {
     const int H = a.H, rows = a.rows, warp = threadIdx.x >> 5;
     const bool writer = blockIdx.x == 0;
@@ -469,7 +799,7 @@ __device__ __noinline__ void mg_norm_rows(const MegaArgs& a, const bf16* update,
 }
 
 // q_resid row (the q_a LoRA RMSNorm) with the thread mapping and reduction tree of qkv_a_post_row: by the CTA ...
-__device__ __forceinline__ void mg_qnorm_block(const float* p, int Q, const bf16* q_norm_w, float eps, bf16* dst, float (*scratch)[40]) {
+__device__ MG_CALL void mg_qnorm_block(const float* p, int Q, const bf16* q_norm_w, float eps, bf16* dst, float (*scratch)[40]) {
     const int tid = threadIdx.x;
     float4 qv[2];
     uint2 qw[2];
@@ -502,7 +832,7 @@ __device__ __forceinline__ void mg_qnorm_block(const float* p, int Q, const bf16
 }
 
 // ... and by one warp playing the eight warps in turn.
-__device__ __forceinline__ void mg_qnorm_warp(const float* p, int Q, const bf16* q_norm_w, float eps, bf16* dst) {
+__device__ MG_CALL void mg_qnorm_warp(const float* p, int Q, const bf16* q_norm_w, float eps, bf16* dst) {
     const int lane = threadIdx.x & 31;
     float mine = 0.f;
     for (int vw = 0; vw < 8; ++vw) {
@@ -539,8 +869,52 @@ __device__ __forceinline__ void mg_qnorm_warp(const float* p, int Q, const bf16*
 
 // ---------------------------------------------------------------------------------------------------
 // Router choice of one row by one warp (the selection of router_topk256_kernel / router_topk_kernel, misc.cu).
-__device__ __forceinline__ void mg_router_topk_warp(const float* lg, const float* bias, int E, int top_k, int* ids, float* weights) {
+__device__ MG_CALL void mg_router_topk_warp(const float* lg, const float* bias, int E, int top_k, int* ids, float* weights) {
     const int lane = threadIdx.x & 31;
+    if (E <= 256) {
+        // router_topk256_kernel: every lane loads its (up to 8) logits once and keeps score and key in registers
+        float lv[8], bv[8], sc[8];
+        uint32_t key[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int e = lane + 32 * i;
+            lv[i] = e < E ? lg[e] : 0.f;
+            bv[i] = e < E ? bias[e] : 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            sc[i] = sigmoidf_precise(lv[i]);
+            key[i] = orderable_u32(__fadd_rn(sc[i], bv[i]));
+        }
+        uint32_t taken = 0;
+        float picked_sum = 0.f, my_score = 0.f;
+        for (int s = 0; s < top_k; ++s) {
+            uint32_t best_key = 0;
+            int best_e = 0x7fffffff;
+            float best_score = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int e = lane + 32 * i;
+                if (e < E && !((taken >> i) & 1u) && (best_e == 0x7fffffff || key[i] > best_key)) {
+                    best_key = key[i]; best_e = e; best_score = sc[i];
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const uint32_t k2 = __shfl_xor_sync(0xffffffffu, best_key, o);
+                const int e2 = __shfl_xor_sync(0xffffffffu, best_e, o);
+                const float s2 = __shfl_xor_sync(0xffffffffu, best_score, o);
+                const bool theirs = e2 != 0x7fffffff && (best_e == 0x7fffffff || k2 > best_key || (k2 == best_key && e2 < best_e));
+                if (theirs) { best_key = k2; best_e = e2; best_score = s2; }
+            }
+            if (best_e != 0x7fffffff && (best_e & 31) == lane) taken |= 1u << (best_e >> 5);
+            if (lane == s) my_score = best_score;
+            picked_sum += best_score;
+            if (lane == 0) ids[s] = best_e == 0x7fffffff ? 0 : best_e;
+        }
+        if (lane < top_k) weights[lane] = my_score / (picked_sum + 1e-20f);
+        return;
+    }
     const int per = (E + 31) / 32;  // <= 32
     uint32_t taken = 0;
     float picked_sum = 0.f, my_score = 0.f;
@@ -586,15 +960,22 @@ __device__ __forceinline__ void mg_local_routes(const int* ids, int n, int exper
 }
 
 // ---------------------------------------------------------------------------------------------------
-template <int R>
-__device__ __noinline__ void mg_qkv_a(const MegaArgs& a, const MegaLayer& lw, int layer, MgSmall& sm, unsigned char* big) {
+template <int R, bool COMPAT>
+__device__ MG_CALL void mg_qkv_a(const MegaArgs& a, const MegaLayer& lw, int layer, MgSmall& sm, unsigned char* big) {
     const int rows = a.rows, H = a.H;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const bool compat = a.compat_ksplit != 0;
+    constexpr bool compat = COMPAT;
     (void)rows; (void)H; (void)warp; (void)lane; (void)compat; (void)layer; (void)big;
         bf16* x_s = reinterpret_cast<bf16*>(big);
         mg_norm_rows(a, layer == 0 ? nullptr : a.update, a.residual_a, layer == 0, lw.input_norm, x_s, a.residual_b, nullptr, sm);
         const int N = lw.n_qkv_a, units = (N + 1) / 2;
+        if (!compat) {
+            int nf;
+            float* scratch = mg_scratch(big, (size_t)rows * H * 2, &nf);
+            mg_gemv_blocks<R>(N, 1, H, rows, x_s, H, MgRowMap{lw.w_qkv_a, lw.w_qkv_a, H, 0}, scratch, nf,
+                              [&](int p0, int cnt, const float* vals) { mg_store_f32<R>(a.proj_a, a.proj_stride, rows, p0, cnt, vals); });
+            return;
+        }
         const int ks = mg_pick_ks(units, H, compat, 0, 0);
         mg_gemv<R>(units, H, ks, rows, sm,
                    [&](int u) {
@@ -610,11 +991,11 @@ __device__ __noinline__ void mg_qkv_a(const MegaArgs& a, const MegaLayer& lw, in
                    });
 }
 
-template <int R>
-__device__ __noinline__ void mg_q_b(const MegaArgs& a, const MegaLayer& lw, int layer, MgSmall& sm, unsigned char* big) {
+template <int R, bool COMPAT>
+__device__ MG_CALL void mg_q_b(const MegaArgs& a, const MegaLayer& lw, int layer, MgSmall& sm, unsigned char* big) {
     const int rows = a.rows, H = a.H;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const bool compat = a.compat_ksplit != 0;
+    constexpr bool compat = COMPAT;
     (void)rows; (void)H; (void)warp; (void)lane; (void)compat; (void)layer; (void)big;
         bf16* q_s = reinterpret_cast<bf16*>(big);  // [rows][Q]
         const int Q = a.Q;
@@ -642,6 +1023,13 @@ __device__ __noinline__ void mg_q_b(const MegaArgs& a, const MegaLayer& lw, int 
             __syncthreads();
         }
         const int N = lw.n_q_b, units = (N + 1) / 2;
+        if (!compat) {
+            int nf;
+            float* scratch = mg_scratch(big, (size_t)rows * Q * 2, &nf);
+            mg_gemv_blocks<R>(N, 1, Q, rows, q_s, Q, MgRowMap{lw.w_q_b, lw.w_q_b, Q, 0}, scratch, nf,
+                              [&](int p0, int cnt, const float* vals) { mg_store_f32<R>(a.q_proj, a.q_stride, rows, p0, cnt, vals); });
+            return;
+        }
         const int ks = mg_pick_ks(units, Q, compat, 0, 0);
         mg_gemv<R>(units, Q, ks, rows, sm,
                    [&](int u) {
@@ -657,11 +1045,11 @@ __device__ __noinline__ void mg_q_b(const MegaArgs& a, const MegaLayer& lw, int 
                    });
 }
 
-template <int R>
-__device__ __noinline__ void mg_absorb(const MegaArgs& a, const MegaLayer& lw, int layer, MgSmall& sm, unsigned char* big) {
+template <int R, bool COMPAT>
+__device__ MG_CALL void mg_absorb(const MegaArgs& a, const MegaLayer& lw, int layer, MgSmall& sm, unsigned char* big) {
     const int rows = a.rows, H = a.H;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const bool compat = a.compat_ksplit != 0;
+    constexpr bool compat = COMPAT;
     (void)rows; (void)H; (void)warp; (void)lane; (void)compat; (void)layer; (void)big;
         float(*red)[R][QA_COLS] = reinterpret_cast<float(*)[R][QA_COLS]>(big);
         float(*qs)[QA_MAX_NOPE] = reinterpret_cast<float(*)[QA_MAX_NOPE]>(big + sizeof(float) * 8 * R * QA_COLS);
@@ -678,11 +1066,11 @@ __device__ __noinline__ void mg_absorb(const MegaArgs& a, const MegaLayer& lw, i
         }
 }
 
-template <int R>
-__device__ __noinline__ void mg_attn(const MegaArgs& a, const MegaLayer& lw, int layer, MgSmall& sm, unsigned char* big) {
+template <int R, bool COMPAT>
+__device__ MG_CALL void mg_attn(const MegaArgs& a, const MegaLayer& lw, int layer, MgSmall& sm, unsigned char* big) {
     const int rows = a.rows, H = a.H;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const bool compat = a.compat_ksplit != 0;
+    constexpr bool compat = COMPAT;
     (void)rows; (void)H; (void)warp; (void)lane; (void)compat; (void)layer; (void)big;
         const int nhz = (a.heads_total + AT_HEADS - 1) / AT_HEADS;
         const int items = rows * nhz * a.max_chunks;
@@ -701,11 +1089,11 @@ __device__ __noinline__ void mg_attn(const MegaArgs& a, const MegaLayer& lw, int
         }
 }
 
-template <int R>
-__device__ __noinline__ void mg_merge(const MegaArgs& a, const MegaLayer& lw, int layer, MgSmall& sm, unsigned char* big) {
+template <int R, bool COMPAT>
+__device__ MG_CALL void mg_merge(const MegaArgs& a, const MegaLayer& lw, int layer, MgSmall& sm, unsigned char* big) {
     const int rows = a.rows, H = a.H;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const bool compat = a.compat_ksplit != 0;
+    constexpr bool compat = COMPAT;
     (void)rows; (void)H; (void)warp; (void)lane; (void)compat; (void)layer; (void)big;
         // attn_local_merge_kernel (attention.cu), single-GPU form: o_lat[r][h] = bf16(sum_c o_c w_c / l)
         const int Hh = a.heads_total, L = a.L;
@@ -759,11 +1147,11 @@ __device__ __noinline__ void mg_merge(const MegaArgs& a, const MegaLayer& lw, in
         }
 }
 
-template <int R>
-__device__ __noinline__ void mg_vproj(const MegaArgs& a, const MegaLayer& lw, int layer, MgSmall& sm, unsigned char* big) {
+template <int R, bool COMPAT>
+__device__ MG_CALL void mg_vproj(const MegaArgs& a, const MegaLayer& lw, int layer, MgSmall& sm, unsigned char* big) {
     const int rows = a.rows, H = a.H;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const bool compat = a.compat_ksplit != 0;
+    constexpr bool compat = COMPAT;
     (void)rows; (void)H; (void)warp; (void)lane; (void)compat; (void)layer; (void)big;
         const int hl = a.heads_local, vd = a.vdim, L = a.L, per_head = (vd + 1) / 2;
         const int units = hl * per_head;
@@ -785,25 +1173,44 @@ __device__ __noinline__ void mg_vproj(const MegaArgs& a, const MegaLayer& lw, in
                    });
 }
 
-template <int R>
-__device__ __noinline__ void mg_oproj(const MegaArgs& a, const MegaLayer& lw, int layer, MgSmall& sm, unsigned char* big) {
+template <int R, bool COMPAT>
+__device__ MG_CALL void mg_oproj(const MegaArgs& a, const MegaLayer& lw, int layer, MgSmall& sm, unsigned char* big) {
     const int rows = a.rows, H = a.H;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const bool compat = a.compat_ksplit != 0;
+    constexpr bool compat = COMPAT;
     (void)rows; (void)H; (void)warp; (void)lane; (void)compat; (void)layer; (void)big;
         const int K = a.heads_local * a.vdim;
+        if (!compat) {
+            mg_blocks_allreduce<R>(a.attn_v, K, lw.w_o, K, H, K, rows, a.attn_out, H, 0, a, sm, big);
+            return;
+        }
         mg_gemv_allreduce<R>(a.attn_v, K, lw.w_o, K, H, K, rows, a.attn_out, H, 0, a, sm);
 }
 
-template <int R>
-__device__ __noinline__ void mg_mlp_a(const MegaArgs& a, const MegaLayer& lw, int layer, MgSmall& sm, unsigned char* big) {
+template <int R, bool COMPAT>
+__device__ MG_CALL void mg_mlp_a(const MegaArgs& a, const MegaLayer& lw, int layer, MgSmall& sm, unsigned char* big) {
     const int rows = a.rows, H = a.H;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const bool compat = a.compat_ksplit != 0;
+    constexpr bool compat = COMPAT;
     (void)rows; (void)H; (void)warp; (void)lane; (void)compat; (void)layer; (void)big;
         bf16* x_s = reinterpret_cast<bf16*>(big);
         mg_norm_rows(a, a.attn_out, a.residual_b, false, lw.post_norm, x_s, a.residual_a, lw.dense ? nullptr : a.x, sm);
+        int nf;
+        float* scratch = mg_scratch(big, (size_t)rows * H * 2, &nf);
         auto swiglu = [&](const bf16* wg, const bf16* wu, int N, bf16* act, int64_t as) {
+            if (!compat) {  // gate row u and up row u are the virtual rows 2u and 2u + 1: a pair never straddles two CTAs
+                mg_gemv_blocks<R>(2 * N, 2, H, rows, x_s, H, MgRowMap{wg, wu, H, 1}, scratch, nf,
+                                  [&](int p0, int cnt, const float* vals) {
+                                      for (int t = threadIdx.x; t < (cnt / 2) * R; t += MG_THREADS) {
+                                          const int i = t / R, r = t % R;
+                                          if (r < rows) {
+                                              const float g = bf16_round(vals[(2 * i) * R + r]), v = bf16_round(vals[(2 * i + 1) * R + r]);
+                                              act[(int64_t)r * as + (p0 >> 1) + i] = __float2bfloat16_rn(g * sigmoidf_precise(g) * v);
+                                          }
+                                      }
+                                  });
+                return;
+            }
             const int ks = mg_pick_ks(N, H, compat, 0, 0);
             mg_gemv<R>(N, H, ks, rows, sm,
                        [&](int u) { return MgUnit{x_s, H, wg + (int64_t)u * H, wu + (int64_t)u * H}; },
@@ -820,6 +1227,12 @@ __device__ __noinline__ void mg_mlp_a(const MegaArgs& a, const MegaLayer& lw, in
             swiglu(lw.dense_gate, lw.dense_up, a.dense_cols, a.dense_act, a.dense_act_stride);
         } else {
             const int E = a.E, units = (E + 1) / 2;
+            if (!compat) {
+                mg_gemv_blocks<R>(E, 1, H, rows, x_s, H, MgRowMap{lw.router_w, lw.router_w, H, 0}, scratch, nf,
+                                  [&](int p0, int cnt, const float* vals) { mg_store_f32<R>(a.router_logits, E, rows, p0, cnt, vals); });
+                swiglu(lw.shared_gate, lw.shared_up, a.shared_cols, a.act_shared, a.act_shared_stride);
+                return;
+            }
             const int ks = mg_pick_ks(units, H, compat, 0, 0);
             mg_gemv<R>(units, H, ks, rows, sm,
                        [&](int u) {
@@ -838,13 +1251,17 @@ __device__ __noinline__ void mg_mlp_a(const MegaArgs& a, const MegaLayer& lw, in
         }
 }
 
-template <int R>
-__device__ __noinline__ void mg_mlp_b(const MegaArgs& a, const MegaLayer& lw, int layer, MgSmall& sm, unsigned char* big) {
+template <int R, bool COMPAT>
+__device__ MG_CALL void mg_mlp_b(const MegaArgs& a, const MegaLayer& lw, int layer, MgSmall& sm, unsigned char* big) {
     const int rows = a.rows, H = a.H;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const bool compat = a.compat_ksplit != 0;
+    constexpr bool compat = COMPAT;
     (void)rows; (void)H; (void)warp; (void)lane; (void)compat; (void)layer; (void)big;
         if (lw.dense) {
+            if (!compat) {
+                mg_blocks_allreduce<R>(a.dense_act, a.dense_act_stride, lw.dense_down, a.dense_cols, H, a.dense_cols, rows, a.update, H, 1, a, sm, big);
+                return;
+            }
             mg_gemv_allreduce<R>(a.dense_act, a.dense_act_stride, lw.dense_down, a.dense_cols, H, a.dense_cols, rows, a.update, H, 1, a, sm);
             return;
         }
@@ -866,9 +1283,17 @@ __device__ __noinline__ void mg_mlp_b(const MegaArgs& a, const MegaLayer& lw, in
             sm.n_loc = c;
         }
         __syncthreads();
+        mg_stamp(sm, ((unsigned long long)layer << 8) | MG_MLP_B | (1ull << 16));  // router choice done
+        if (a.prefetch_cap > 0)  // the down projections of the chosen experts are next: ask the L2 for them now
+            for (int i = 0; i < sm.n_loc; ++i) {
+                const int p = sm.loc[i];
+                mg_prefetch_l2(lw.exp_down + (int64_t)(sm.ids[p / tk][p % tk] - a.expert_base) * H * a.I, (size_t)H * a.I, (size_t)a.prefetch_cap);
+            }
         // routed gate/up of this GPU's routes: one item = (route, 16 output rows), moe_gateup_fp8_mma_kernel<1>
         {
-            float(*red)[2][MG_MM_ROWS][8] = reinterpret_cast<float(*)[2][MG_MM_ROWS][8]>(big);
+            bf16* x_sm = reinterpret_cast<bf16*>(big);  // the normalised rows, staged once (two resident CTAs leave almost no L1)
+            const size_t x_bytes = (mg_stage_rows(x_sm, a.x, H, rows, H) + 15) & ~(size_t)15;
+            float(*red)[2][MG_MM_ROWS][8] = reinterpret_cast<float(*)[2][MG_MM_ROWS][8]>(big + x_bytes);
             const int I = a.I, blocks = (I + MG_MM_ROWS - 1) / MG_MM_ROWS;
             const int items = sm.n_loc * blocks;
             const int g = lane >> 2, t = lane & 3;
@@ -877,21 +1302,35 @@ __device__ __noinline__ void mg_mlp_b(const MegaArgs& a, const MegaLayer& lw, in
                 const int p = sm.loc[item / blocks], n0 = (item % blocks) * MG_MM_ROWS;
                 const int e = sm.ids[p / tk][p % tk] - a.expert_base;
                 const int route = g == 0 ? p : -1;
-                const bf16* xr = a.x + (int64_t)(route >= 0 ? route / tk : 0) * H;
+                const bf16* xr = x_sm + (int64_t)(route >= 0 ? route / tk : 0) * H;
                 const uint8_t* wg_lo = lw.exp_gate + ((int64_t)e * I + n0 + g) * H;
                 const uint8_t* wu_lo = lw.exp_up + ((int64_t)e * I + n0 + g) * H;
                 const int64_t hi_off = (int64_t)8 * H;
                 const int64_t sofs = ((int64_t)e * ((I + 127) >> 7) + (n0 >> 7)) * kb;
                 float acc_g[4] = {0.f, 0.f, 0.f, 0.f}, acc_u[4] = {0.f, 0.f, 0.f, 0.f};
-                for (int c = warp; c < chunks; c += MG_WARPS) {
-                    const int k = (c << 6) + t * 16;
-                    const uint4 g_lo = ld_stream16(wg_lo + k), g_hi = ld_stream16(wg_lo + hi_off + k);
-                    const uint4 u_lo = ld_stream16(wu_lo + k), u_hi = ld_stream16(wu_lo + hi_off + k);
-                    uint4 x0 = make_uint4(0, 0, 0, 0), x1 = x0;
-                    if (route >= 0) { x0 = ld_hot16(xr + k); x1 = ld_hot16(xr + k + 8); }
-                    const float s_g = lw.exp_gate_scale[sofs + (c >> 1)], s_u = lw.exp_up_scale[sofs + (c >> 1)];
-                    chunk_mma(acc_g, g_lo, g_hi, s_g, x0, x1);
-                    chunk_mma(acc_u, u_lo, u_hi, s_u, x0, x1);
+                // this warp's chunks in ascending order, three at a time with their twelve weight loads in flight together
+                constexpr int UC = 3;
+                for (int c0 = warp; c0 < chunks; c0 += MG_WARPS * UC) {
+                    uint4 g_lo[UC], g_hi[UC], u_lo[UC], u_hi[UC], x0[UC], x1[UC];
+                    float s_g[UC], s_u[UC];
+#pragma unroll
+                    for (int u = 0; u < UC; ++u) {
+                        const int c = c0 + u * MG_WARPS;
+                        if (c < chunks) {
+                            const int k = (c << 6) + t * 16;
+                            g_lo[u] = ld_stream16(wg_lo + k); g_hi[u] = ld_stream16(wg_lo + hi_off + k);
+                            u_lo[u] = ld_stream16(wu_lo + k); u_hi[u] = ld_stream16(wu_lo + hi_off + k);
+                            x0[u] = x1[u] = make_uint4(0, 0, 0, 0);
+                            if (route >= 0) { x0[u] = ld_hot16(xr + k); x1[u] = ld_hot16(xr + k + 8); }
+                            s_g[u] = lw.exp_gate_scale[sofs + (c >> 1)]; s_u[u] = lw.exp_up_scale[sofs + (c >> 1)];
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < UC; ++u)
+                        if (c0 + u * MG_WARPS < chunks) {
+                            chunk_mma(acc_g, g_lo[u], g_hi[u], s_g[u], x0[u], x1[u]);
+                            chunk_mma(acc_u, u_lo[u], u_hi[u], s_u[u], x0[u], x1[u]);
+                        }
                 }
                 __syncthreads();
                 red[warp][0][g][2 * t] = acc_g[0]; red[warp][0][g][2 * t + 1] = acc_g[1];
@@ -912,9 +1351,19 @@ __device__ __noinline__ void mg_mlp_b(const MegaArgs& a, const MegaLayer& lw, in
             }
             __syncthreads();
         }
+        mg_stamp(sm, ((unsigned long long)layer << 8) | MG_MLP_B | (2ull << 16));  // routed gate / up done
         // this GPU's K-slice of the shared expert's down projection (fp32 partial)
         {
             const int K = a.shared_cols, units = (H + 1) / 2;
+            if (!compat) {
+                __syncthreads();
+                const size_t used = mg_stage_rows(reinterpret_cast<bf16*>(big), a.act_shared, a.act_shared_stride, rows, K);
+                int nf;
+                float* scratch = mg_scratch(big, used, &nf);
+                mg_gemv_blocks<R>(H, 1, K, rows, reinterpret_cast<const bf16*>(big), K, MgRowMap{lw.shared_down, lw.shared_down, K, 0}, scratch, nf,
+                                  [&](int p0, int cnt, const float* vals) { mg_store_f32<R>(a.partial, H, rows, p0, cnt, vals); });
+                return;
+            }
             const int ks = mg_pick_ks(units, K, compat, 0, 0);
             mg_gemv<R>(units, K, ks, rows, sm,
                        [&](int u) {
@@ -932,16 +1381,24 @@ __device__ __noinline__ void mg_mlp_b(const MegaArgs& a, const MegaLayer& lw, in
         }
 }
 
-template <int R>
-__device__ __noinline__ void mg_moe_down(const MegaArgs& a, const MegaLayer& lw, int layer, MgSmall& sm, unsigned char* big) {
+template <int R, bool COMPAT>
+__device__ MG_CALL void mg_moe_down(const MegaArgs& a, const MegaLayer& lw, int layer, MgSmall& sm, unsigned char* big) {
     const int rows = a.rows, H = a.H;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const bool compat = a.compat_ksplit != 0;
+    constexpr bool compat = COMPAT;
     (void)rows; (void)H; (void)warp; (void)lane; (void)compat; (void)layer; (void)big;
         if (lw.dense) return;
         const int tk = a.top_k, I = a.I;
         mg_local_routes(a.topk_ids, rows * tk, a.expert_base, a.experts_local, sm);
         float(*red)[MG_MM_ROWS][8] = reinterpret_cast<float(*)[MG_MM_ROWS][8]>(big);
+        bf16* act_sm = reinterpret_cast<bf16*>(big + sizeof(float) * MG_WARPS * MG_MM_ROWS * 8);
+        const bool staged = sizeof(float) * MG_WARPS * MG_MM_ROWS * 8 + (size_t)sm.n_loc * I * 2 <= (size_t)sm.big_bytes;
+        if (staged) {
+            const int vec = I >> 3;
+            for (int i = threadIdx.x; i < sm.n_loc * vec; i += MG_THREADS)
+                reinterpret_cast<uint4*>(act_sm)[i] = *reinterpret_cast<const uint4*>(a.act + (int64_t)sm.loc[i / vec] * I + (i % vec) * 8);
+            __syncthreads();
+        }
         const int blocks = (H + MG_MM_ROWS - 1) / MG_MM_ROWS;
         const int items = sm.n_loc * blocks;
         const int g = lane >> 2, t = lane & 3;
@@ -950,17 +1407,29 @@ __device__ __noinline__ void mg_moe_down(const MegaArgs& a, const MegaLayer& lw,
             const int p = sm.loc[item / blocks], n0 = (item % blocks) * MG_MM_ROWS;
             const int e = a.topk_ids[p] - a.expert_base;
             const int route = g == 0 ? p : -1;
-            const bf16* xr = a.act + (int64_t)(route >= 0 ? route : 0) * I;
+            const bf16* xr = staged ? act_sm + (int64_t)(item / blocks) * I : a.act + (int64_t)(route >= 0 ? route : 0) * I;
             const uint8_t* w_lo = lw.exp_down + ((int64_t)e * H + n0 + g) * I;
             const int64_t hi_off = (int64_t)8 * I;
             const int64_t sofs = ((int64_t)e * ((H + 127) >> 7) + (n0 >> 7)) * kb;
             float acc[4] = {0.f, 0.f, 0.f, 0.f};
-            for (int c = warp; c < chunks; c += MG_WARPS) {
-                const int k = (c << 6) + t * 16;
-                const uint4 lo = ld_stream16(w_lo + k), hi = ld_stream16(w_lo + hi_off + k);
-                uint4 x0 = make_uint4(0, 0, 0, 0), x1 = x0;
-                if (route >= 0) { x0 = ld_hot16(xr + k); x1 = ld_hot16(xr + k + 8); }
-                chunk_mma(acc, lo, hi, lw.exp_down_scale[sofs + (c >> 1)], x0, x1);
+            constexpr int UC = 4;  // this warp's chunks in ascending order, four at a time with their loads in flight together
+            for (int c0 = warp; c0 < chunks; c0 += MG_WARPS * UC) {
+                uint4 lo[UC], hi[UC], x0[UC], x1[UC];
+                float sc[UC];
+#pragma unroll
+                for (int u = 0; u < UC; ++u) {
+                    const int c = c0 + u * MG_WARPS;
+                    if (c < chunks) {
+                        const int k = (c << 6) + t * 16;
+                        lo[u] = ld_stream16(w_lo + k); hi[u] = ld_stream16(w_lo + hi_off + k);
+                        x0[u] = x1[u] = make_uint4(0, 0, 0, 0);
+                        if (route >= 0) { x0[u] = ld_hot16(xr + k); x1[u] = ld_hot16(xr + k + 8); }
+                        sc[u] = lw.exp_down_scale[sofs + (c >> 1)];
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < UC; ++u)
+                    if (c0 + u * MG_WARPS < chunks) chunk_mma(acc, lo[u], hi[u], sc[u], x0[u], x1[u]);
             }
             __syncthreads();
             red[warp][g][2 * t] = acc[0]; red[warp][g][2 * t + 1] = acc[1];
@@ -978,11 +1447,11 @@ __device__ __noinline__ void mg_moe_down(const MegaArgs& a, const MegaLayer& lw,
         }
 }
 
-template <int R>
-__device__ __noinline__ void mg_combine(const MegaArgs& a, const MegaLayer& lw, int layer, MgSmall& sm, unsigned char* big) {
+template <int R, bool COMPAT>
+__device__ MG_CALL void mg_combine(const MegaArgs& a, const MegaLayer& lw, int layer, MgSmall& sm, unsigned char* big) {
     const int rows = a.rows, H = a.H;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const bool compat = a.compat_ksplit != 0;
+    constexpr bool compat = COMPAT;
     (void)rows; (void)H; (void)warp; (void)lane; (void)compat; (void)layer; (void)big;
         if (lw.dense) return;
         // moe_combine_kernel (gemv.cu) over column slices: CTA-slice s owns `cols` columns of every row
@@ -1023,33 +1492,51 @@ __device__ __noinline__ void mg_combine(const MegaArgs& a, const MegaLayer& lw, 
         }
 }
 
-template <int R>
+template <int R, bool COMPAT>
 __device__ __forceinline__ void mg_phase(const MegaArgs& a, const MegaLayer& lw, int layer, int phase, MgSmall& sm, unsigned char* big) {
     switch (phase) {
-    case MG_QKV_A: mg_qkv_a<R>(a, lw, layer, sm, big); break;
-    case MG_Q_B: mg_q_b<R>(a, lw, layer, sm, big); break;
-    case MG_ABSORB: mg_absorb<R>(a, lw, layer, sm, big); break;
-    case MG_ATTN: mg_attn<R>(a, lw, layer, sm, big); break;
-    case MG_MERGE: mg_merge<R>(a, lw, layer, sm, big); break;
-    case MG_VPROJ: mg_vproj<R>(a, lw, layer, sm, big); break;
-    case MG_OPROJ: mg_oproj<R>(a, lw, layer, sm, big); break;
-    case MG_MLP_A: mg_mlp_a<R>(a, lw, layer, sm, big); break;
-    case MG_MLP_B: mg_mlp_b<R>(a, lw, layer, sm, big); break;
-    case MG_MOE_DOWN: mg_moe_down<R>(a, lw, layer, sm, big); break;
-    case MG_COMBINE: mg_combine<R>(a, lw, layer, sm, big); break;
+    case MG_QKV_A: mg_qkv_a<R, COMPAT>(a, lw, layer, sm, big); break;
+    case MG_Q_B: mg_q_b<R, COMPAT>(a, lw, layer, sm, big); break;
+    case MG_ABSORB: mg_absorb<R, COMPAT>(a, lw, layer, sm, big); break;
+    case MG_ATTN: mg_attn<R, COMPAT>(a, lw, layer, sm, big); break;
+    case MG_MERGE: mg_merge<R, COMPAT>(a, lw, layer, sm, big); break;
+    case MG_VPROJ: mg_vproj<R, COMPAT>(a, lw, layer, sm, big); break;
+    case MG_OPROJ: mg_oproj<R, COMPAT>(a, lw, layer, sm, big); break;
+    case MG_MLP_A: mg_mlp_a<R, COMPAT>(a, lw, layer, sm, big); break;
+    case MG_MLP_B: mg_mlp_b<R, COMPAT>(a, lw, layer, sm, big); break;
+    case MG_MOE_DOWN: mg_moe_down<R, COMPAT>(a, lw, layer, sm, big); break;
+    case MG_COMBINE: mg_combine<R, COMPAT>(a, lw, layer, sm, big); break;
     default: break;
     }
 }
 
-template <int R>
-__device__ __noinline__ void mg_head_phase(const MegaArgs& a, int phase, MgSmall& sm, unsigned char* big) {
+template <int R, bool COMPAT>
+__device__ MG_CALL void mg_head_phase(const MegaArgs& a, int phase, MgSmall& sm, unsigned char* big) {
     const int rows = a.rows, H = a.H;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (phase == MG_HEAD_LOGITS) {
         bf16* x_s = reinterpret_cast<bf16*>(big);
         mg_norm_rows(a, a.num_layers == 0 ? nullptr : a.update, a.residual_a, a.num_layers == 0, a.final_norm, x_s, nullptr, nullptr, sm);
         const int N = a.vocab_local, units = (N + 1) / 2;
-        const int ks = mg_pick_ks(units, H, a.compat_ksplit != 0, 0, 0);
+        const int ks = mg_pick_ks(units, H, COMPAT, 0, 0);
+        if (!COMPAT) {
+            int nf;
+            float* scratch = mg_scratch(big, (size_t)rows * H * 2, &nf);
+            unsigned long long mine = 0ull;  // thread r keeps the best candidate of row r over this CTA's vocabulary block
+            mg_gemv_blocks<R>(N, 1, H, rows, x_s, H, MgRowMap{a.lm_head, a.lm_head, H, 0}, scratch, nf,
+                              [&](int p0, int cnt, const float* vals) {
+                                  const int r = threadIdx.x;
+                                  if (r < rows && r < R)
+                                      for (int i = 0; i < cnt; ++i) {
+                                          const float v = bf16_round(vals[i * R + r]);
+                                          if (!isfinite(v)) raise_status(a.status, GLMB_STATUS_NONFINITE);
+                                          const unsigned long long k2 = candidate_key(v, a.vocab_base + p0 + i);
+                                          mine = k2 > mine ? k2 : mine;
+                                      }
+                              });
+            if ((int)threadIdx.x < rows && (int)threadIdx.x < R && mine) atomicMax(a.local_best + threadIdx.x, mine);
+            return;
+        }
         unsigned long long run[R];
 #pragma unroll
         for (int r = 0; r < R; ++r) run[r] = 0ull;
@@ -1126,27 +1613,178 @@ __device__ __noinline__ void mg_head_phase(const MegaArgs& a, int phase, MgSmall
     if (threadIdx.x == 0 && a.step_counter) *a.step_counter = step + 1;
 }
 
-template <int R>
-__global__ void __launch_bounds__(MG_THREADS, 2) decode_mega_kernel(const __grid_constant__ MegaArgs a) {
+// Weights that later phases will stream are requested into the L2 a few phases ahead (they do not depend on the activations),
+// so that the dependent chain of small phases finds them there instead of waiting for HBM each time.  Requests are capped
+// (prefetch_cap bytes per table) so that large tables on few GPUs do not sweep the L2.
+__device__ __forceinline__ void mg_prefetch_ahead(const MegaArgs& a, const MegaLayer& lw, int layer, int phase) {
+    if (a.prefetch_cap <= 0) return;
+    const size_t cap = (size_t)a.prefetch_cap, H = a.H;
+    switch (phase) {
+    case MG_QKV_A:
+        mg_prefetch_l2(lw.w_q_b, (size_t)lw.n_q_b * a.Q * 2, cap);
+        mg_prefetch_l2(lw.kv_b, (size_t)a.heads_local * (a.nope + a.vdim) * a.L * 2, cap);
+        break;
+    case MG_Q_B:
+        mg_prefetch_l2(lw.w_o, H * a.heads_local * a.vdim * 2, cap);
+        break;
+    case MG_ABSORB:
+        if (lw.dense) {
+            mg_prefetch_l2(lw.dense_gate, (size_t)a.dense_cols * H * 2, cap);
+            mg_prefetch_l2(lw.dense_up, (size_t)a.dense_cols * H * 2, cap);
+        } else {
+            mg_prefetch_l2(lw.router_w, (size_t)a.E * H * 2, cap);
+            mg_prefetch_l2(lw.shared_gate, (size_t)a.shared_cols * H * 2, cap);
+            mg_prefetch_l2(lw.shared_up, (size_t)a.shared_cols * H * 2, cap);
+        }
+        break;
+    case MG_ATTN:
+        if (lw.dense) mg_prefetch_l2(lw.dense_down, H * a.dense_cols * 2, cap);
+        else mg_prefetch_l2(lw.shared_down, H * a.shared_cols * 2, cap);
+        break;
+    case MG_MLP_A:
+        if (layer + 1 < a.num_layers) mg_prefetch_l2(a.layers[layer + 1].w_qkv_a, (size_t)a.layers[layer + 1].n_qkv_a * H * 2, cap);
+        else mg_prefetch_l2(a.lm_head, (size_t)a.vocab_local * H * 2, cap);
+        break;
+    default:
+        break;
+    }
+}
+
+template <int R, bool COMPAT>
+__global__ void __launch_bounds__(MG_THREADS, MG_CTAS_PER_SM) decode_mega_kernel(const MegaArgs* __restrict__ gargs, int layer0, int phase0, int layer1,
+                                                                    int phase1) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     MgSmall& sm = *reinterpret_cast<MgSmall*>(smem_raw);
     unsigned char* big = smem_raw + ((sizeof(MgSmall) + 15) & ~(size_t)15);
-    unsigned int epoch = *reinterpret_cast<volatile unsigned int*>(&a.bar->gen);
+    {
+        // the argument block lives in device memory (no per-thread copy of a by-value parameter); the stretch comes as scalars
+        const uint32_t* src = reinterpret_cast<const uint32_t*>(gargs);
+        uint32_t* dst = reinterpret_cast<uint32_t*>(&sm.args);
+        for (int i = threadIdx.x; i < (int)(sizeof(MegaArgs) / 4); i += MG_THREADS) dst[i] = src[i];
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        sm.args.layer0 = layer0; sm.args.phase0 = phase0; sm.args.layer1 = layer1; sm.args.phase1 = phase1;
+        sm.big_bytes = MG_BIG_BYTES;
+    }
+    __syncthreads();
+    const MegaArgs& a = sm.args;
+    unsigned int epoch = mg_ld_relaxed(&a.bar->gen);
+    // per-phase stamps (measurements only): CTA 0's first thread owns the buffer; stretches of a stream run one after the other
+    if (threadIdx.x == 0) {
+        sm.stamping = a.timeline != nullptr && blockIdx.x == 0;
+        sm.stamp_at = sm.stamping ? *reinterpret_cast<volatile unsigned long long*>(a.timeline) : 0ull;
+    }
+    __syncthreads();
+    mg_stamp(sm, 0ull);  // code 0: the stretch begins
     for (int layer = a.layer0; layer <= a.layer1; ++layer) {
         const bool head = layer >= a.num_layers;
+        if (!head) {
+            __syncthreads();
+            const uint32_t* src = reinterpret_cast<const uint32_t*>(a.layers + layer);
+            uint32_t* dst = reinterpret_cast<uint32_t*>(&sm.layer);
+            for (int i = threadIdx.x; i < (int)(sizeof(MegaLayer) / 4); i += MG_THREADS) dst[i] = src[i];
+            __syncthreads();
+        }
+        const MegaLayer& lw = sm.layer;
         const int first = layer == a.layer0 ? a.phase0 : 1;
         const int last = layer == a.layer1 ? a.phase1 : (head ? MG_HEAD_FINALIZE : MG_COMBINE);
         for (int phase = first; phase <= last; ++phase) {
             if (head) {
-                mg_head_phase<R>(a, phase, sm, big);
+                mg_head_phase<R, COMPAT>(a, phase, sm, big);
             } else {
-                const MegaLayer& lw = a.layers[layer];
                 if (lw.dense && (phase == MG_MOE_DOWN || phase == MG_COMBINE)) continue;  // no work and no barrier
-                mg_phase<R>(a, lw, layer, phase, sm, big);
+                mg_prefetch_ahead(a, lw, layer, phase);
+                mg_phase<R, COMPAT>(a, lw, layer, phase, sm, big);
+                if (a.compat_ksplit == 2) {  // measurement: the same phase once more, with its code and operands warm
+                    __syncthreads();
+                    mg_stamp(sm, (((unsigned long long)layer << 8) | (unsigned long long)phase) | 0x80ull | (7ull << 16));
+                    mg_grid_barrier(a.bar, epoch, a.bar_limit, a.status);
+                    mg_stamp(sm, (((unsigned long long)layer << 8) | (unsigned long long)phase) | (8ull << 16));
+                    mg_phase<R, COMPAT>(a, lw, layer, phase, sm, big);
+                }
             }
-            if (!(layer == a.layer1 && phase == last)) mg_grid_barrier(a.bar, epoch, a.bar_limit, a.status);
+            const unsigned long long code = ((unsigned long long)layer << 8) | (unsigned long long)phase;
+            if (!(layer == a.layer1 && phase == last)) {
+                __syncthreads();
+                mg_stamp(sm, code | 0x80ull);  // this CTA's work of the phase is done
+                mg_grid_barrier(a.bar, epoch, a.bar_limit, a.status);
+            }
+            mg_stamp(sm, code);
         }
     }
+    if (threadIdx.x == 0 && sm.stamping) *reinterpret_cast<volatile unsigned long long*>(a.timeline) = sm.stamp_at;
+}
+
+// ---------------------------------------------------------------------------------------------------
+// The same phases as kernels of their own (`decode_path = "phases"`): a kernel boundary with programmatic dependent launch
+// takes the place of the grid barrier.  A phase then has the occupancy, the L1 and the instruction footprint of a small kernel,
+// which the persistent form gives up (two 100 KB CTAs per SM leave no L1, every phase starts on cold code), and the chain is
+// still 11 launches per layer instead of 17.  Before it waits for its predecessor, a projection kernel asks the L2 for its own
+// block of weight rows: the fetch overlaps the tail of the previous kernel.
+__device__ __forceinline__ void mg_prefetch_rows(const bf16* base, int N, int align, size_t row_bytes) {
+    if (threadIdx.x != 0 || base == nullptr) return;
+    int rpc = (N + (int)gridDim.x - 1) / (int)gridDim.x;
+    rpc = (rpc + align - 1) / align * align;
+    const int n_begin = (int)blockIdx.x * rpc, n_cnt = min(N, n_begin + rpc) - n_begin;
+    if (n_cnt <= 0) return;
+    const size_t bytes = ((size_t)n_cnt * row_bytes) & ~(size_t)15;
+    const char* p = reinterpret_cast<const char*>(base) + (size_t)n_begin * row_bytes;
+    if (bytes && !((uintptr_t)p & 15)) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"((uint32_t)bytes) : "memory");
+}
+
+__device__ __forceinline__ void mg_prefetch_own(const MegaArgs& a, const MegaLayer& lw, int layer, int phase) {
+    const size_t H2 = (size_t)a.H * 2;
+    if (layer >= a.num_layers) {
+        if (phase == MG_HEAD_LOGITS) mg_prefetch_rows(a.lm_head, a.vocab_local, 1, H2);
+        return;
+    }
+    switch (phase) {
+    case MG_QKV_A: mg_prefetch_rows(lw.w_qkv_a, lw.n_qkv_a, 1, H2); break;
+    case MG_Q_B: mg_prefetch_rows(lw.w_q_b, lw.n_q_b, 1, (size_t)a.Q * 2); break;
+    case MG_OPROJ: mg_prefetch_rows(lw.w_o, a.H, 1, (size_t)a.heads_local * a.vdim * 2); break;
+    case MG_MLP_A:
+        if (lw.dense) {
+            mg_prefetch_rows(lw.dense_gate, a.dense_cols, 1, H2);
+            mg_prefetch_rows(lw.dense_up, a.dense_cols, 1, H2);
+        } else {
+            mg_prefetch_rows(lw.router_w, a.E, 1, H2);
+            mg_prefetch_rows(lw.shared_gate, a.shared_cols, 1, H2);
+            mg_prefetch_rows(lw.shared_up, a.shared_cols, 1, H2);
+        }
+        break;
+    case MG_MLP_B:
+        if (lw.dense) mg_prefetch_rows(lw.dense_down, a.H, 1, (size_t)a.dense_cols * 2);
+        else mg_prefetch_rows(lw.shared_down, a.H, 1, (size_t)a.shared_cols * 2);
+        break;
+    default: break;
+    }
+}
+
+// PHASE: 1..11 a layer's phases, 12 / 13 the head's two (a kernel per phase: its own registers, occupancy and code).
+// Resident CTAs per SM a phase kernel is compiled for: the streaming phases want many small CTAs (every byte of the table
+// requested at once), which bounds their registers; the tile phases keep the registers they need.
+template <int R, int PHASE>
+struct MgPhaseBlocks {
+    static constexpr bool streaming = PHASE == MG_QKV_A || PHASE == MG_Q_B || PHASE == MG_VPROJ || PHASE == MG_OPROJ || PHASE == MG_MLP_A ||
+                                      PHASE == MG_MLP_B || PHASE == MG_COMBINE + MG_HEAD_LOGITS;
+    static constexpr int value = !streaming ? 2 : (R <= 2 ? 4 : (R <= 4 ? 3 : 2));
+};
+
+template <int R, bool COMPAT, int PHASE>
+__global__ void __launch_bounds__(MG_THREADS, (MgPhaseBlocks<R, PHASE>::value)) mega_phase_kernel(const __grid_constant__ MegaArgs args, const __grid_constant__ MegaLayer lwp,
+                                                                int layer, int big_bytes) {
+    constexpr int phase = PHASE > MG_COMBINE ? PHASE - MG_COMBINE : PHASE;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    MgSmall& sm = *reinterpret_cast<MgSmall*>(smem_raw);
+    unsigned char* big = smem_raw + ((sizeof(MgSmall) + 15) & ~(size_t)15);
+    asm volatile("griddepcontrol.launch_dependents;");
+    mg_prefetch_own(args, lwp, layer, phase);  // weights only: nothing the previous kernel writes
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (threadIdx.x == 0) { sm.big_bytes = big_bytes; sm.stamping = 0; }
+    __syncthreads();
+    if (PHASE > MG_COMBINE) mg_head_phase<R, COMPAT>(args, phase, sm, big);
+    else mg_phase<R, COMPAT>(args, lwp, layer, phase, sm, big);
 }
 
 // ===================================================================================================
@@ -1160,7 +1798,7 @@ static int g_mega_cooperative = 1;
 // same grid, for drivers that refuse to capture a cooperative launch in a CUDA graph.
 GLMB_API void glmb_set_mega_cooperative(int enabled) { g_mega_cooperative = enabled ? 1 : 0; }
 
-template <int R>
+template <int R, bool COMPAT>
 static int mega_grid_for(int* grid) {
     static int cached[GLMB_MAX_WORLD * 2] = {0};
     int dev = 0;
@@ -1168,23 +1806,23 @@ static int mega_grid_for(int* grid) {
     if (e != cudaSuccess) return (int)e;
     if (dev < 0 || dev >= GLMB_MAX_WORLD * 2) return 1;
     if (!cached[dev]) {
-        if ((e = cudaFuncSetAttribute(decode_mega_kernel<R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)mega_smem_bytes())) != cudaSuccess)
+        if ((e = cudaFuncSetAttribute(decode_mega_kernel<R, COMPAT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)mega_smem_bytes())) != cudaSuccess)
             return (int)e;
         int per_sm = 0, sms = 0;
-        if ((e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_mega_kernel<R>, MG_THREADS, mega_smem_bytes())) != cudaSuccess)
+        if ((e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_mega_kernel<R, COMPAT>, MG_THREADS, mega_smem_bytes())) != cudaSuccess)
             return (int)e;
         if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return (int)e;
         if (per_sm < 1) return 2;
-        cached[dev] = sms * (per_sm > 2 ? 2 : per_sm);
+        cached[dev] = sms * (per_sm > MG_CTAS_PER_SM ? MG_CTAS_PER_SM : per_sm);
     }
     *grid = cached[dev];
     return 0;
 }
 
-template <int R>
-static int mega_launch(const MegaArgs& a, cudaStream_t stream) {
+template <int R, bool COMPAT>
+static int mega_launch(const MegaArgs* device_args, int layer0, int phase0, int layer1, int phase1, cudaStream_t stream) {
     int grid = 0;
-    const int rc = mega_grid_for<R>(&grid);
+    const int rc = mega_grid_for<R, COMPAT>(&grid);
     if (rc) return rc;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
@@ -1196,16 +1834,16 @@ static int mega_launch(const MegaArgs& a, cudaStream_t stream) {
     attr[0].val.cooperative = g_mega_cooperative ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return (int)cudaLaunchKernelEx(&cfg, decode_mega_kernel<R>, a);
+    return (int)cudaLaunchKernelEx(&cfg, decode_mega_kernel<R, COMPAT>, device_args, layer0, phase0, layer1, phase1);
 }
 
 // Number of CTAs a stretch is launched with on the current device (the same on every GPU of a box), 0 on error.
 GLMB_API int glmb_mega_grid(int rows) {
     int grid = 0, rc;
-    if (rows <= 1) rc = mega_grid_for<1>(&grid);
-    else if (rows <= 2) rc = mega_grid_for<2>(&grid);
-    else if (rows <= 4) rc = mega_grid_for<4>(&grid);
-    else rc = mega_grid_for<8>(&grid);
+    if (rows <= 1) rc = mega_grid_for<1, false>(&grid);
+    else if (rows <= 2) rc = mega_grid_for<2, false>(&grid);
+    else if (rows <= 4) rc = mega_grid_for<4, false>(&grid);
+    else rc = mega_grid_for<8, false>(&grid);
     return rc ? 0 : grid;
 }
 
@@ -1227,17 +1865,170 @@ GLMB_API int glmb_mega_supported(const MegaArgs* a) {
     return 0;
 }
 
-// Run the stretch (layer0, phase0) .. (layer1, phase1) of `args` (both ends inclusive; layer == num_layers is the head).
-GLMB_API int glmb_mega_decode(const MegaArgs* args, int layer0, int phase0, int layer1, int phase1, void* stream) {
-    if (glmb_mega_supported(args)) return 1;
+// Run the stretch (layer0, phase0) .. (layer1, phase1) (both ends inclusive; layer == num_layers is the head).  `args` is the host
+// copy of the argument block (checked here), `device_args` the same bytes in device memory, which is what the kernel reads.
+GLMB_API int glmb_mega_decode(const MegaArgs* args, const void* device_args, int layer0, int phase0, int layer1, int phase1, void* stream) {
+    if (glmb_mega_supported(args) || !device_args) return 1;
     if (layer0 < 0 || layer1 > args->num_layers || layer0 > layer1 || phase0 < 1 || phase1 < 1) return 1;
-    MegaArgs a = *args;
-    a.layer0 = layer0; a.phase0 = phase0; a.layer1 = layer1; a.phase1 = phase1;
+    const MegaArgs* d = reinterpret_cast<const MegaArgs*>(device_args);
     cudaStream_t st = (cudaStream_t)stream;
-    if (a.rows <= 1) return mega_launch<1>(a, st);
-    if (a.rows <= 2) return mega_launch<2>(a, st);
-    if (a.rows <= 4) return mega_launch<4>(a, st);
-    return mega_launch<8>(a, st);
+    const int rows = args->rows;
+#define MG_GO(RR, CC) return mega_launch<RR, CC>(d, layer0, phase0, layer1, phase1, st)
+    if (args->compat_ksplit == 1) {
+        if (rows <= 1) MG_GO(1, true);
+        if (rows <= 2) MG_GO(2, true);
+        if (rows <= 4) MG_GO(4, true);
+        MG_GO(8, true);
+    }
+    if (rows <= 1) MG_GO(1, false);
+    if (rows <= 2) MG_GO(2, false);
+    if (rows <= 4) MG_GO(4, false);
+    MG_GO(8, false);
+#undef MG_GO
+}
+
+// ---------------------------------------------------------------------------------------------------
+// One phase as a kernel of its own.  Grid and shared memory follow from the shapes alone, so every GPU of a box launches the
+// same grid (the exchanges inside the all-reduce phases pair CTA j of every rank).
+static size_t phase_big_bytes(const MegaArgs& a, const MegaLayer& lw, int layer, int phase, int Rt) {
+    const size_t xH = (size_t)a.rows * a.H * 2, scratch = 16384;
+    if (layer >= a.num_layers) return phase == MG_HEAD_LOGITS ? xH + scratch : 16;
+    auto staged = [&](size_t K) { const size_t x = (size_t)a.rows * K * 2; return (x <= 65536 ? x : 0) + scratch + 8192; };
+    switch (phase) {
+    case MG_QKV_A: case MG_MLP_A: return xH + scratch;
+    case MG_Q_B: return (size_t)a.rows * a.Q * 2 + scratch;
+    case MG_ABSORB: return sizeof(float) * (8 * (size_t)Rt * QA_COLS + (size_t)Rt * QA_MAX_NOPE);
+    case MG_ATTN: return sparse_mla_tile_smem(a.L + a.rd);
+    case MG_OPROJ: return staged((size_t)a.heads_local * a.vdim);
+    case MG_MLP_B: {
+        if (lw.dense) return staged(a.dense_cols);
+        const size_t gate_up = xH + 16 + sizeof(float) * MG_WARPS * 2 * MG_MM_ROWS * 8;
+        const size_t shared_down = (size_t)a.rows * a.shared_cols * 2 + scratch;
+        return gate_up > shared_down ? gate_up : shared_down;
+    }
+    case MG_MOE_DOWN: {
+        const int routes = a.rows * a.top_k < 16 ? a.rows * a.top_k : 16;
+        return sizeof(float) * MG_WARPS * MG_MM_ROWS * 8 + (size_t)routes * a.I * 2;
+    }
+    default: return 16;
+    }
+}
+
+static int host_pick_ks(int units, int K) {
+    int ks = 1;
+    while (ks < MG_WARPS && units * ks < 148 * 4 * MG_WARPS && K % (ks * 2 * 256) == 0 && K / (ks * 2) >= 512) ks *= 2;
+    return ks;
+}
+// CTAs that give every unit of a projection its team of warps in one round (units: pairs of rows, or gate / up pairs)
+static int one_round(int units, int K) { return (units + MG_WARPS / host_pick_ks(units, K) - 1) / (MG_WARPS / host_pick_ks(units, K)); }
+
+static int phase_grid(const MegaArgs& a, const MegaLayer& lw, int layer, int phase, int sms, int per_sm) {
+    per_sm = per_sm < 1 ? 1 : (per_sm > 4 ? 4 : per_sm);
+    const int wide = sms * per_sm;
+    auto at_most = [&](int items) { return items < 1 ? 1 : (items < wide ? items : wide); };
+    auto capped = [&](int ctas) { return ctas < 1 ? 1 : (ctas > GLMB_AR_MAX_CTAS ? GLMB_AR_MAX_CTAS : ctas); };
+    const int H = a.H;
+    if (layer >= a.num_layers) return phase == MG_HEAD_LOGITS ? (a.compat_ksplit == 1 ? sms * 8 : wide) : 1;
+    if (a.compat_ksplit == 1) {
+        switch (phase) {
+        case MG_QKV_A: return capped(one_round((lw.n_qkv_a + 1) / 2, H));
+        case MG_Q_B: { const int g = one_round((lw.n_q_b + 1) / 2, a.Q); return g < a.rows ? a.rows : g; }
+        case MG_OPROJ: return capped(one_round((H + 1) / 2, a.heads_local * a.vdim));
+        case MG_MLP_A: {
+            if (lw.dense) return capped(one_round(a.dense_cols, H));
+            const int r = one_round((a.E + 1) / 2, H), sg = one_round(a.shared_cols, H);
+            return capped(r > sg ? r : sg);
+        }
+        case MG_MLP_B:
+            if (lw.dense) return capped(one_round((H + 1) / 2, a.dense_cols));
+            break;
+        default: break;
+        }
+    }
+    switch (phase) {
+    case MG_ABSORB: return at_most(a.heads_local * ((a.L + QA_COLS - 1) / QA_COLS));
+    case MG_ATTN: return at_most(a.rows * ((a.heads_total + AT_HEADS - 1) / AT_HEADS) * a.max_chunks);
+    case MG_MERGE: return at_most(a.heads_total * a.rows);
+    case MG_VPROJ: return at_most((a.heads_local * ((a.vdim + 1) / 2) + MG_WARPS - 1) / MG_WARPS);
+    case MG_COMBINE: return at_most(sms * 2);
+    case MG_MOE_DOWN: return lw.dense ? 1 : wide;
+    default: return wide;
+    }
+}
+
+template <int R, bool COMPAT, int PHASE>
+static int mega_phase_launch_one(const MegaArgs& a, const MegaLayer& lw, int layer, cudaStream_t stream) {
+    constexpr int phase = PHASE > MG_COMBINE ? PHASE - MG_COMBINE : PHASE;
+    static int sm_count[GLMB_MAX_WORLD * 2] = {0};
+    static size_t occ_smem[GLMB_MAX_WORLD * 2] = {0};  // the occupancy answer is cached per shared-memory size
+    static int occ[GLMB_MAX_WORLD * 2] = {0};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= GLMB_MAX_WORLD * 2) return 1;
+    if (!sm_count[dev]) {
+        if ((e = cudaFuncSetAttribute(mega_phase_kernel<R, COMPAT, PHASE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)) != cudaSuccess)
+            return (int)e;
+        int sms = 0;
+        if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return (int)e;
+        sm_count[dev] = sms;
+    }
+    const size_t big = (phase_big_bytes(a, lw, layer, phase, R) + 15) & ~(size_t)15;
+    const size_t smem = ((sizeof(MgSmall) + 15) & ~(size_t)15) + big;
+    if (smem > 200 * 1024) return 2;
+    if (occ_smem[dev] != smem) {
+        int n = 0;
+        if ((e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, mega_phase_kernel<R, COMPAT, PHASE>, MG_THREADS, smem)) != cudaSuccess) return (int)e;
+        occ[dev] = n;
+        occ_smem[dev] = smem;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(phase_grid(a, lw, layer, phase, sm_count[dev], occ[dev]));
+    cfg.blockDim = dim3(MG_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = g_glmb_pdl_enabled ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return (int)cudaLaunchKernelEx(&cfg, mega_phase_kernel<R, COMPAT, PHASE>, a, lw, layer, (int)big);
+}
+
+template <int R, bool COMPAT>
+static int mega_phase_launch(const MegaArgs& a, const MegaLayer& lw, int layer, int phase, cudaStream_t stream) {
+    const int id = layer >= a.num_layers ? MG_COMBINE + phase : phase;
+    switch (id) {
+#define MG_P(N) case N: return mega_phase_launch_one<R, COMPAT, N>(a, lw, layer, stream)
+        MG_P(1); MG_P(2); MG_P(3); MG_P(4); MG_P(5); MG_P(6); MG_P(7); MG_P(8); MG_P(9); MG_P(10); MG_P(11); MG_P(12); MG_P(13);
+#undef MG_P
+    default: return 1;
+    }
+}
+
+// Launch phase `phase` of `layer` (layer == num_layers: the head) as a kernel of its own.  `entry`: the layer's pointer-table
+// entry (host copy; ignored for the head).
+GLMB_API int glmb_mega_phase(const MegaArgs* args, const MegaLayer* entry, int layer, int phase, void* stream) {
+    if (glmb_mega_supported(args)) return 1;
+    if (layer < 0 || layer > args->num_layers || phase < 1 || phase > MG_COMBINE) return 1;
+    MegaLayer none;
+    memset(&none, 0, sizeof(none));
+    const MegaLayer& lw = layer < args->num_layers && entry ? *entry : none;
+    if (layer < args->num_layers && !entry) return 1;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int rows = args->rows;
+#define MG_GO(RR, CC) return mega_phase_launch<RR, CC>(*args, lw, layer, phase, st)
+    if (args->compat_ksplit == 1) {
+        if (rows <= 1) MG_GO(1, true);
+        if (rows <= 2) MG_GO(2, true);
+        if (rows <= 4) MG_GO(4, true);
+        MG_GO(8, true);
+    }
+    if (rows <= 1) MG_GO(1, false);
+    if (rows <= 2) MG_GO(2, false);
+    if (rows <= 4) MG_GO(4, false);
+    MG_GO(8, false);
+#undef MG_GO
 }
 
 // Byte offsets of a few members, so that the binding can check that it lays the structure out as the compiler does.
@@ -1246,5 +2037,46 @@ GLMB_API void glmb_mega_args_offsets(size_t* out) {
     out[1] = offsetof(MegaArgs, rows);
     out[2] = offsetof(MegaArgs, eps);
     out[3] = offsetof(MegaArgs, comm);
+    out[5] = offsetof(MegaArgs, timeline_cap);
     out[4] = offsetof(MegaLayer, full);
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Cost of the grid barrier by itself: `iters` barriers back to back on the grid of the decode kernel; CTA 0 reports the
+// nanoseconds of the device's global timer.  variant: see mg_grid_barrier_v.
+template <int VARIANT>
+__global__ void __launch_bounds__(MG_THREADS, 2) mega_barrier_bench_kernel(MegaBarrier* bar, int iters, uint32_t limit, uint32_t* status,
+                                                                             unsigned long long* ns) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    (void)smem_raw;
+    unsigned int epoch = mg_ld_relaxed(VARIANT == 0 ? &bar->pad0[0] : &bar->gen);
+    unsigned long long t0 = 0, t1 = 0;
+    mg_grid_barrier_v<VARIANT>(bar, epoch, limit, status);
+    if (blockIdx.x == 0 && threadIdx.x == 0) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
+    for (int i = 0; i < iters; ++i) mg_grid_barrier_v<VARIANT>(bar, epoch, limit, status);
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t1));
+        *ns = t1 - t0;
+    }
+}
+
+GLMB_API int glmb_mega_barrier_bench(void* bar, int iters, int variant, uint32_t limit, uint32_t* status, unsigned long long* ns, void* stream) {
+    int grid = 0;
+    const int rc = mega_grid_for<1, false>(&grid);
+    if (rc) return rc;
+    void (*kernel)(MegaBarrier*, int, uint32_t, uint32_t*, unsigned long long*) =
+        variant == 0 ? mega_barrier_bench_kernel<0> : (variant == 2 ? mega_barrier_bench_kernel<2> : mega_barrier_bench_kernel<1>);
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)mega_smem_bytes());
+    if (e != cudaSuccess) return (int)e;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(MG_THREADS);
+    cfg.dynamicSmemBytes = mega_smem_bytes();
+    cfg.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative;
+    attr[0].val.cooperative = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return (int)cudaLaunchKernelEx(&cfg, kernel, (MegaBarrier*)bar, iters, limit, status, ns);
 }

@@ -33,9 +33,9 @@ _ARG_POINTERS = (
     "out_tokens", "step_counter", "kv_cache", "index_cache", "residual_a", "residual_b", "x", "update", "attn_out", "proj_a",
     "q_resid", "head_w", "kv_new", "idx_key_new", "q_proj", "q_full", "sel_local", "sel_counts", "part_o", "part_ml", "o_lat",
     "attn_v", "router_logits", "topk_ids", "topk_w", "act_shared", "dense_act", "partial", "act", "dw", "local_best", "cand",
-    "bar", "status",
+    "bar", "status", "timeline",
 )
-_ARG_INT64 = ("proj_stride", "q_stride", "act_shared_stride", "dense_act_stride", "cand_offset")
+_ARG_INT64 = ("proj_stride", "q_stride", "act_shared_stride", "dense_act_stride", "cand_offset", "timeline_cap", "prefetch_cap")
 _ARG_INTS = (
     "rows", "H", "Q", "L", "rd", "nope", "vdim", "D", "IH",
     "heads_local", "head_base", "heads_total", "E", "top_k", "I", "experts_local", "expert_base", "shared_cols", "dense_cols",
@@ -66,9 +66,10 @@ class MegaArgs(C.Structure):
 def _check_layout(lib) -> None:
     lib.glmb_mega_args_sizeof.restype = C.c_size_t
     lib.glmb_mega_layer_sizeof.restype = C.c_size_t
-    offsets = (C.c_size_t * 5)()
+    offsets = (C.c_size_t * 6)()
     lib.glmb_mega_args_offsets(offsets)
-    mine = (MegaArgs.proj_stride.offset, MegaArgs.rows.offset, MegaArgs.eps.offset, MegaArgs.comm.offset, MegaLayer.full.offset)
+    mine = (MegaArgs.proj_stride.offset, MegaArgs.rows.offset, MegaArgs.eps.offset, MegaArgs.comm.offset, MegaLayer.full.offset,
+            MegaArgs.timeline_cap.offset)
     if lib.glmb_mega_args_sizeof() != C.sizeof(MegaArgs) or lib.glmb_mega_layer_sizeof() != C.sizeof(MegaLayer) or tuple(offsets) != mine:
         raise RuntimeError("MegaArgs / MegaLayer layout differs between Python and the CUDA library")
 
@@ -80,7 +81,14 @@ def _ptr(t) -> int | None:
 class MegaDecoder:
     """One decode step of ``model`` over the rows of ``ws`` (the decode workspace) as stretches of the persistent kernel."""
 
-    def __init__(self, model, ws, state, *, compat_ksplit: bool = False):
+    def __init__(self, model, ws, state, *, compat_ksplit: bool | None = None, prefetch_bytes: int | None = None, mode: str = "phases"):
+        if mode not in ("phases", "persistent"):
+            raise ValueError("mode is 'phases' (a kernel per phase) or 'persistent' (stretches of one cooperative kernel)")
+        if compat_ksplit is None:
+            # a kernel per phase keeps the K split and the grids of the stand-alone projection kernels (many small CTAs, every
+            # byte of a table requested at once); the persistent grid has a fixed 296 CTAs and balances the rows over them
+            compat_ksplit = mode == "phases"
+        self.mode = mode
         self.model, self.ws, self.state = model, ws, state
         lib = native.lib()
         _check_layout(lib)
@@ -100,12 +108,14 @@ class MegaDecoder:
             entry.index_slot = g.index_slot(i) if entry.full else 0
             entry.n_qkv_a = lw.w_qkv_a.shape[0]
             entry.n_q_b = lw.w_q_b.shape[0]
+        self._table = table
         raw = bytes(table) if g.num_layers else b"\0" * C.sizeof(MegaLayer)
         self.layer_table = torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(dev)
         H = g.hidden_size
         self.residual_a = torch.zeros((rows, H), dtype=torch.bfloat16, device=dev)
         self.residual_b = torch.zeros((rows, H), dtype=torch.bfloat16, device=dev)
-        self.barrier = torch.zeros(4, dtype=torch.int32, device=dev)
+        lib.glmb_mega_barrier_sizeof.restype = C.c_size_t
+        self.barrier = torch.zeros(int(lib.glmb_mega_barrier_sizeof()) // 4, dtype=torch.int32, device=dev)
         a = MegaArgs()
         fused = ws.peer_visible
         pointers = dict(
@@ -135,6 +145,12 @@ class MegaDecoder:
         a.local_cap, a.stripe, a.cache_world, a.cache_rank = cache.local_capacity, cache.stripe, cache.world, model.cache_rank
         a.capacity, a.ring, a.compat_ksplit = cache.context_capacity, state.out_tokens.shape[0], int(compat_ksplit)
         a.bar_limit = min(4 * max(1, model.peer.wait_limit), 0xFFFFFFFF)
+        if prefetch_bytes is None:
+            import os
+
+            prefetch_bytes = int(os.environ.get("GLM_B200_MEGA_PREFETCH", str(24 << 20)))
+        a.prefetch_cap = max(0, int(prefetch_bytes))  # per weight table, requested into the L2 a few phases ahead; 0: off
+        self.timeline = None
         a.eps, a.key_eps, a.head_scale = g.rms_norm_eps, cache.dsa.key_norm_eps, model.head_scale
         a.softmax_scale, a.routed_scale = model.softmax_scale, g.routed_scaling_factor
         comm = model.peer.comm if fused else None
@@ -143,10 +159,43 @@ class MegaDecoder:
         else:
             a.comm.world, a.comm.rank, a.comm.status = 1, 0, model.peer.status_ptr
         self.args = a
+        self._device_args = torch.zeros(C.sizeof(MegaArgs), dtype=torch.uint8, device=dev)
+        self._uploaded = None
         self.supported_code = int(lib.glmb_mega_supported(C.byref(a)))
-        if model.world > 1 and not fused:
+        if model.world > 1 and not fused and not getattr(model, "emulated_shard", False):
             self.supported_code = self.supported_code or 100  # the library-collective baseline keeps the per-kernel path
         self.launches = 0
+
+    # ------------------------------------------------------------------ per-phase timing
+    def enable_timeline(self, entries: int = 8192) -> None:
+        """Make CTA 0 stamp the global timer after every phase (with its barrier) into a device buffer; for measurements only."""
+        self.timeline = torch.zeros(1 + 2 * entries, dtype=torch.int64, device=self.model.device)
+        self.args.timeline, self.args.timeline_cap = int(self.timeline.data_ptr()), entries
+
+    def read_timeline(self, reset: bool = True) -> list[tuple[int, int, float]]:
+        """``[(layer, code, microseconds since the previous stamp), ...]``.  code 0: a stretch began; code = phase once the
+        phase's grid barrier is passed; phase | 0x80 when CTA 0 finished its own work of the phase (so the next entry is the
+        wait for the slowest CTA plus the barrier); phase | step << 16 for a step inside a phase.  Synchronizes."""
+        torch.cuda.synchronize(self.model.device)
+        host = self.timeline.cpu().tolist()
+        n = min(host[0], (len(host) - 1) // 2)
+        out, prev = [], None
+        for i in range(n):
+            code, t = host[1 + 2 * i], host[2 + 2 * i]
+            out.append(((code >> 8) & 255, (code & 255) | (code >> 16 << 16), 0.0 if prev is None else (t - prev) / 1e3))
+            prev = t
+        if reset:
+            self.timeline.zero_()
+        return out
+
+    def barrier_nanoseconds(self, iters: int = 2000, variant: int = 1) -> float:
+        """Device time of one grid barrier of the persistent kernel's grid, measured over ``iters`` back-to-back barriers."""
+        ns = torch.zeros(1, dtype=torch.int64, device=self.model.device)
+        native._check(self._lib.glmb_mega_barrier_bench(C.c_void_p(self.barrier.data_ptr()), int(iters), int(variant), C.c_uint32(self.args.bar_limit),
+                                                        C.c_void_p(self.model.peer.status_ptr), C.c_void_p(ns.data_ptr()), native._stream()),
+                      "mega_barrier_bench")
+        torch.cuda.synchronize(self.model.device)
+        return float(ns.item()) / iters
 
     @property
     def supported(self) -> bool:
@@ -155,13 +204,43 @@ class MegaDecoder:
     def grid(self) -> int:
         return int(self._lib.glmb_mega_grid(self.rows))
 
+    def _sync_args(self) -> None:
+        """The kernel reads its argument block from device memory: upload it whenever the host copy has changed."""
+        raw = bytes(self.args)
+        if raw != self._uploaded:
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError("the argument block of the persistent decode kernel changed during a graph capture")
+            self._device_args.copy_(torch.frombuffer(bytearray(raw), dtype=torch.uint8))
+            torch.cuda.synchronize(self.model.device)
+            self._uploaded = raw
+
     def stretch(self, first: tuple[int, int], last: tuple[int, int]) -> None:
         """Launch the persistent kernel over the phases ``first .. last`` (``(layer, phase)`` pairs, both inclusive)."""
-        native._check(self._lib.glmb_mega_decode(C.byref(self.args), first[0], first[1], last[0], last[1], native._stream()), "mega_decode")
+        self._sync_args()
+        native._check(self._lib.glmb_mega_decode(C.byref(self.args), C.c_void_p(self._device_args.data_ptr()), first[0], first[1], last[0], last[1],
+                                                 native._stream()), "mega_decode")
+
+    def phase(self, layer: int, phase: int) -> None:
+        """Launch one phase as a kernel of its own (``layer == num_layers``: the head)."""
+        entry = C.byref(self._table[layer]) if layer < self.model.g.num_layers else None
+        native._check(self._lib.glmb_mega_phase(C.byref(self.args), entry, layer, phase, native._stream()), "mega_phase")
 
     def plan(self) -> list[tuple]:
-        """The launch list of one step: ``("stretch", first, last)`` and ``("indexer", layer)`` entries, in order."""
+        """The launch list of one step, in order: ``("stretch", first, last)`` (persistent mode) or ``("phase", layer, phase)``
+        entries, and ``("indexer", layer)`` where a layer computes its own selection."""
         g = self.model.g
+        if self.mode == "phases":
+            out = []
+            for i in range(g.num_layers):
+                dense = g.mlp_layer_types[i] == "dense"
+                for ph in range(QKV_A, COMBINE + 1):
+                    if dense and ph in (MOE_DOWN, COMBINE):
+                        continue
+                    out.append(("phase", i, ph))
+                    if ph == ABSORB and g.indexer_types[i] == "full":
+                        out.append(("indexer", i))
+            out += [("phase", g.num_layers, HEAD_LOGITS), ("phase", g.num_layers, HEAD_FINALIZE)]
+            return out
         out, start = [], (0, QKV_A)
         for i in range(g.num_layers):
             if g.indexer_types[i] == "full":
@@ -176,5 +255,7 @@ class MegaDecoder:
         for entry in self.plan():
             if entry[0] == "stretch":
                 self.stretch(entry[1], entry[2])
+            elif entry[0] == "phase":
+                self.phase(entry[1], entry[2])
             else:
                 self.model.select_keys_decode(self.ws, self.state, entry[1], self.rows)

@@ -193,6 +193,7 @@ class GlmMoeDsaModel:
         self.index_scale = _f32(g.index_head_dim**-0.5)
         self.head_scale = _f32(g.index_heads**-0.5)
         self.trace = None  # set to a dict to record intermediates (tests)
+        self.emulated_shard = False  # measurements: this process holds one rank's shard and skips every exchange (see GpuModelRunner)
         import os
 
         # independent branches of the decode step (shared expert | routed experts; absorbed query | indexer + top-k) run on two
@@ -385,7 +386,7 @@ class GlmMoeDsaModel:
         if decode:
             native.skinny_bf16(ws.o_lat, lw.kv_b[:, g.qk_nope_head_dim :, :], ws.attn_v, native.SK_OUT_BF16, rows=rows, N=g.v_head_dim,
                                K=L, xs=hl * L, ws=L, os_=hl * g.v_head_dim, batch=hl, xb=L, wb=g.kv_b_rows_per_head * L, ob=g.v_head_dim)
-            if fused or self.world == 1:
+            if fused or self.world == 1 or self.emulated_shard:
                 native.skinny_bf16(ws.attn_v[:rows], lw.w_o, ws.attn_out, native.SK_OUT_ALLREDUCE_BF16, comm=kc, channel=native.CH_ATTN)
             else:
                 native.skinny_bf16(ws.attn_v[:rows], lw.w_o, ws.partial, native.SK_OUT_F32)
@@ -490,7 +491,7 @@ class GlmMoeDsaModel:
         if g.mlp_layer_types[layer] == "dense":
             if decode:
                 native.skinny_bf16_swiglu(x, lw.dense_gate, lw.dense_up, ws.dense_act)
-                if fused or self.world == 1:
+                if fused or self.world == 1 or self.emulated_shard:
                     native.skinny_bf16(ws.dense_act[:rows], lw.dense_down, ws.update, native.SK_OUT_ALLREDUCE_BF16, comm=kc,
                                        channel=native.CH_MLP)
                 else:
@@ -554,7 +555,7 @@ class GlmMoeDsaModel:
         else:
             act = self._swiglu(self._mm(x, lw.shared_gate), self._mm(x, lw.shared_up))
             shared_partial = self._mm(act, lw.shared_down, f32=True)
-        if fused or self.world == 1:
+        if fused or self.world == 1 or self.emulated_shard:
             native.moe_combine(ws.dw, ws.topk_ids, shared_partial, rows, tk, H, ebase, el, g.routed_scaling_factor, False, ws.update,
                                None, kc, native.CH_MLP)
         else:
@@ -672,7 +673,7 @@ class GlmMoeDsaModel:
         local_best = None
         if logits is None:
             local_best = ws.local_best  # filled by the lm_head kernel in argmax mode
-            if self.world > 1 and not fused:
+            if self.world > 1 and not fused and not self.emulated_shard:
                 ws.cand[0, :rows] = ws.local_best[:rows]
                 ws.local_best.zero_()
                 local_best = None
@@ -680,7 +681,7 @@ class GlmMoeDsaModel:
             native.argmax_rows(logits, rows, lay.vocab_local, self.rank * lay.vocab_local, ws.cand, ws.r_cand.offset if fused else 0,
                                kc, native.SIG_SAMPLE, self.peer.status_ptr)
         cand = ws.cand
-        if self.world > 1 and not fused:
+        if self.world > 1 and not fused and not self.emulated_shard:
             import torch.distributed as dist
 
             mine = ws.cand[0, :rows].contiguous()  # without a PeerComm the kernel writes set 0

@@ -72,7 +72,7 @@ class GpuModelRunner:
     def __init__(self, weights: DeviceWeights, *, context_capacity: int, lanes: int = 1, stripe: int = 64, comm: str = "fused",
                  group=None, prefill_chunk: int = 512, use_graphs: bool = True, wait_limit: int = 2_000_000,
                  staging_bytes: int | None = None, kv_layout: str = "auto", replica_budget_bytes: int = 32 << 30,
-                 decode_path: str = "auto", mega_compat_ksplit: bool | None = None):
+                 decode_path: str = "auto", mega_compat_ksplit: bool | None = None, emulate_shard: bool = False):
         self.weights = weights
         self.g, self.layout = weights.geometry, weights.layout
         self.device = weights.embed.device
@@ -99,9 +99,17 @@ class GpuModelRunner:
             if self.world > 1 and prefill_chunk > 8:  # output + partial-tile slots of the prefill GEMM with the fused all-reduce
                 staging_bytes += prefill_chunk * g.hidden_size * 2 + native.gemm_allreduce_part_bytes(prefill_chunk, g.hidden_size, self.world) + 8192
         with torch.cuda.device(self.device):
-            self.peer = PeerGroup(self.world, self.rank, staging_bytes=staging_bytes if self.world > 1 else 0,
-                                  wait_limit=wait_limit, group=group, device=self.device)
+            # emulate_shard (measurements only): this process holds rank `rank`'s shard of a `world`-GPU layout but runs alone:
+            # every exchange is skipped, so the outputs mean nothing and the decode step costs what one GPU of the box spends
+            # outside the exchanges (persistent decode kernel only)
+            self.emulate_shard = bool(emulate_shard) and self.world > 1
+            if self.emulate_shard:
+                self.peer = PeerGroup(1, 0, staging_bytes=0, wait_limit=wait_limit, group=None, device=self.device)
+            else:
+                self.peer = PeerGroup(self.world, self.rank, staging_bytes=staging_bytes if self.world > 1 else 0,
+                                      wait_limit=wait_limit, group=group, device=self.device)
             self.model = GlmMoeDsaModel(weights, self.cache, self.peer, comm=comm, group=group)
+            self.model.emulated_shard = self.emulate_shard
             self.state = DecoderState.allocate(self.cache, self.device)
             self.decode_ws = Workspace(self.model, lanes, "decode")
             # decode program: the persistent kernel (a step is a few dozen launches) where its shapes and cache layout allow,
@@ -110,20 +118,21 @@ class GpuModelRunner:
 
             if decode_path == "auto":
                 decode_path = os.environ.get("GLM_B200_DECODE", "auto")
-            if decode_path not in ("auto", "mega", "kernels"):
-                raise ValueError("decode_path is 'auto', 'mega' or 'kernels'")
-            if mega_compat_ksplit is None:
-                mega_compat_ksplit = os.environ.get("GLM_B200_MEGA_KSPLIT", "balanced") == "compat"
+            if decode_path not in ("auto", "phases", "mega", "kernels"):
+                raise ValueError("decode_path is 'auto', 'phases', 'mega' or 'kernels'")
+            if mega_compat_ksplit is None and "GLM_B200_MEGA_KSPLIT" in os.environ:
+                mega_compat_ksplit = os.environ["GLM_B200_MEGA_KSPLIT"] == "compat"
             self.mega = None
             if decode_path != "kernels":
                 from glm_tpu_b200.models.glm_moe_dsa.mega import MegaDecoder
 
-                mega = MegaDecoder(self.model, self.decode_ws, self.state, compat_ksplit=mega_compat_ksplit)
+                mega = MegaDecoder(self.model, self.decode_ws, self.state, compat_ksplit=mega_compat_ksplit,
+                                   mode="persistent" if decode_path == "mega" else "phases")
                 if mega.supported:
                     self.mega = mega
-                elif decode_path == "mega":
-                    raise ValueError(f"the persistent decode kernel does not take this configuration (code {mega.supported_code})")
-            self.decode_path = "mega" if self.mega is not None else "kernels"
+                elif decode_path != "auto":
+                    raise ValueError(f"the fused decode phases do not take this configuration (code {mega.supported_code})")
+            self.decode_path = ("mega" if self.mega.mode == "persistent" else "phases") if self.mega is not None else "kernels"
             self.prefill_ws = None
             self._prefill_out = torch.zeros(1, dtype=torch.int32, device=self.device)
             self._graph = None
@@ -154,7 +163,7 @@ class GpuModelRunner:
             self.decode_launches = counter.count
             torch.cuda.synchronize(self.device)
             kind = "eager"
-            if self.use_graphs and self.model.comm_mode == "fused" or (self.use_graphs and self.world == 1):
+            if self.use_graphs and self.model.comm_mode == "fused" or (self.use_graphs and self.world == 1):  # noqa: E129
                 try:
                     graph = torch.cuda.CUDAGraph()
                     with torch.cuda.graph(graph, stream=self._graph_stream):
@@ -252,7 +261,7 @@ class GpuModelRunner:
             "weights_bytes": int(self.model.w.bytes_resident),
             "kv_cache_bytes": int(st.kv_cache.numel() * st.kv_cache.element_size()),
             "index_cache_bytes": int(st.index_cache.numel() * st.index_cache.element_size()),
-            "staging_bytes": int(self.peer._total) if self.world > 1 else 0,
+            "staging_bytes": int(self.peer._total) if self.peer.world > 1 else 0,
             "kv_layout": self.kv_layout,
         }
 
@@ -279,7 +288,7 @@ class GpuModelRunner:
 
     def close(self) -> None:
         self._graph = None
-        if self.world > 1:
+        if self.peer.world > 1:
             torch.cuda.synchronize(self.device)
             self.peer.check_canaries()  # a kernel (of any rank) that overran a staging region wrote into its guard band
         self.peer.close()
