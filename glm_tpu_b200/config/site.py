@@ -12,7 +12,8 @@ Tables::
     [paths]      run_root, model_path, packed_path, state_root
     [checkpoint] manifest_sha256, source_marker_sha256      # optional pins ("" = unpinned)
     [topology]   binding_sha256                              # optional pin of the captured GPU topology
-    [launch]     policy = "record" | "strict", master_port, wall_seconds
+    [launch]     policy = "record" | "strict", master_port, wall_seconds,
+                 allowed_branches = ["main", "release/*"], expected_origin = "", require_pushed = false   (rules of "strict")
     [serve]      port
 
 Parity: reference ``glm_tpu/config/site.py:92-684`` (7 tables, exact key sets, 0600, 64-hex pins, resolved JSON + SHA).
@@ -33,13 +34,14 @@ from glm_tpu_b200.utils.json_utils import canonical_wire_bytes
 
 _HEX64 = re.compile(r"[0-9a-f]{64}")
 _PLAIN = re.compile(r"[A-Za-z0-9_./+@:-]+")
+_PLAIN_GLOB = re.compile(r"[A-Za-z0-9_./+@:*?\[\]-]+")
 SUPPORTED_GPUS = (1, 2, 4, 8)
 TABLE_KEYS = {
     "box": {"gpus"},
     "paths": {"run_root", "model_path", "packed_path", "state_root"},
     "checkpoint": {"manifest_sha256", "source_marker_sha256"},
     "topology": {"binding_sha256"},
-    "launch": {"policy", "master_port", "wall_seconds"},
+    "launch": {"policy", "master_port", "wall_seconds", "allowed_branches", "expected_origin", "require_pushed"},
     "serve": {"port"},
 }
 
@@ -60,6 +62,9 @@ class SiteConfig:
     source_marker_sha256: str = ""
     topology_binding_sha256: str = ""
     policy: str = "record"
+    allowed_branches: tuple = ("main", "release/*")
+    expected_origin: str = ""
+    require_pushed: bool = False
     master_port: int = 29577
     wall_seconds: int = 86400
     serve_port: int = 8011
@@ -125,9 +130,19 @@ class SiteConfig:
         gpus = integer("box", "gpus", 8, 1, 8)
         if gpus not in SUPPORTED_GPUS:
             raise ConfigValidationError(f"[box] gpus must be one of {SUPPORTED_GPUS}")
-        policy = doc.get("launch", {}).get("policy", "record")
+        launch = doc.get("launch", {})
+        policy = launch.get("policy", "record")
         if policy not in ("record", "strict"):
             raise ConfigValidationError("[launch] policy must be 'record' or 'strict'")
+        branches = launch.get("allowed_branches", ["main", "release/*"])
+        if type(branches) is not list or not branches or any(type(b) is not str or not b or not _PLAIN_GLOB.fullmatch(b) for b in branches):
+            raise ConfigValidationError("[launch] allowed_branches must be a non-empty list of branch patterns")
+        expected_origin = launch.get("expected_origin", "")
+        if type(expected_origin) is not str or any(c.isspace() for c in expected_origin):
+            raise ConfigValidationError("[launch] expected_origin must be a string without spaces")
+        require_pushed = launch.get("require_pushed", False)
+        if type(require_pushed) is not bool:
+            raise ConfigValidationError("[launch] require_pushed must be true or false")
         return cls(
             gpus=gpus,
             paths=Paths(plain("run_root"), plain("model_path"), plain("packed_path"), plain("state_root")),
@@ -135,6 +150,9 @@ class SiteConfig:
             source_marker_sha256=pin("checkpoint", "source_marker_sha256"),
             topology_binding_sha256=pin("topology", "binding_sha256"),
             policy=policy,
+            allowed_branches=tuple(branches),
+            expected_origin=expected_origin,
+            require_pushed=require_pushed,
             master_port=integer("launch", "master_port", 29577, 1024, 65535),
             wall_seconds=integer("launch", "wall_seconds", 86400, 1, 30 * 86400),
             serve_port=integer("serve", "port", 8011, 1024, 65535),
@@ -157,8 +175,40 @@ class SiteConfig:
     def resolved(self) -> dict:
         out = asdict(self)
         out["paths"] = {k: (str(v) if v is not None else None) for k, v in out["paths"].items()}
+        out["allowed_branches"] = list(self.allowed_branches)
         del out["source"]
         return out
+
+    @classmethod
+    def from_staged(cls, path: Path, expected_sha256: str) -> "SiteConfig":
+        """The site a controller staged for its workers (``resolved_json`` bytes): refused unless the bytes have the digest the
+        controller put on the worker's command line and they parse back to a site with the same canonical form."""
+        raw = Path(path).read_bytes()
+        if hashlib.sha256(raw).hexdigest() != expected_sha256:
+            raise ConfigValidationError("the staged site is not the controller's (digest differs)")
+        import json
+
+        doc = json.loads(raw)
+        try:
+            paths = Paths(**{k: (Path(v) if v is not None else None) for k, v in doc.pop("paths").items()})
+            doc["allowed_branches"] = tuple(doc["allowed_branches"])
+            site = cls(paths=paths, source=str(path), **doc)
+        except (TypeError, KeyError) as exc:
+            raise ConfigValidationError("the staged site does not have the fields of a resolved site") from exc
+        if site.resolved_json() != raw:
+            raise ConfigValidationError("the staged site is not in canonical form")
+        return site
+
+    @property
+    def launch_rules(self):
+        from glm_tpu_b200.executor.launch_policy import LaunchRules
+
+        return LaunchRules(self.policy, self.allowed_branches, self.expected_origin, self.require_pushed)
+
+    @property
+    def checkpoint_pins(self) -> dict:
+        """What a worker hands to the checkpoint loader: an empty pin means unpinned."""
+        return {"manifest_sha256": self.manifest_sha256, "source_marker_sha256": self.source_marker_sha256}
 
     def resolved_json(self) -> bytes:
         return canonical_wire_bytes(self.resolved())

@@ -2031,6 +2031,49 @@ GLMB_API int glmb_mega_phase(const MegaArgs* args, const MegaLayer* entry, int l
 #undef MG_GO
 }
 
+// The exchange a phase performs between the GPUs, for the collective-plan check: out = {kind (0 none, 1 all-reduce, 2 signal),
+// channel or signal, CTAs that exchange, floats per CTA}.  `persistent_grid` > 0: the phase runs inside the persistent kernel of
+// that many CTAs; 0: as a kernel of its own (its grid follows from the shapes; needs a CUDA device for the occupancy query).
+GLMB_API int glmb_mega_phase_exchange(const MegaArgs* a, const MegaLayer* entry, int layer, int phase, int persistent_grid, int* out) {
+    out[0] = out[1] = out[2] = out[3] = 0;
+    if (layer >= a->num_layers) {
+        if (phase == MG_HEAD_FINALIZE) { out[0] = 2; out[1] = 3; }
+        return 0;
+    }
+    if (!entry) return 1;
+    const bool dense = entry->dense != 0;
+    const int Rt = a->rows <= 1 ? 1 : (a->rows <= 2 ? 2 : (a->rows <= 4 ? 4 : 8));
+    const bool ar_gemv = phase == MG_OPROJ || (phase == MG_MLP_B && dense);
+    if (!ar_gemv && !(phase == MG_COMBINE && !dense)) return 0;
+    int grid = persistent_grid;
+    if (grid <= 0) {
+        int dev = 0, sms = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 2;
+        grid = phase_grid(*a, *entry, layer, phase, sms, 4);
+    }
+    out[0] = 1;
+    out[1] = phase == MG_OPROJ ? 0 : 1;
+    if (ar_gemv) {
+        const int K = phase == MG_OPROJ ? a->heads_local * a->vdim : a->dense_cols, units = (a->H + 1) / 2;
+        if (a->compat_ksplit == 1) {
+            const int tpc = MG_WARPS / host_pick_ks(units, K), teams = grid * tpc, rounds = (units + teams - 1) / teams;
+            out[2] = (units + tpc - 1) / tpc < grid ? (units + tpc - 1) / tpc : grid;
+            out[3] = rounds * tpc * 2 * Rt;
+        } else {
+            const int rpc = (a->H + grid - 1) / grid;
+            out[2] = (a->H + rpc - 1) / rpc;
+            out[3] = rpc * Rt;
+        }
+    } else {
+        int cols = ((a->H + grid - 1) / grid + 3) & ~3;
+        const int cap = (GLMB_AR_SLICE / (2 * a->rows)) & ~3;
+        if (cols > cap) cols = cap;
+        out[2] = (a->H + cols - 1) / cols;
+        out[3] = 2 * a->rows * cols;
+    }
+    return 0;
+}
+
 // Byte offsets of a few members, so that the binding can check that it lays the structure out as the compiler does.
 GLMB_API void glmb_mega_args_offsets(size_t* out) {
     out[0] = offsetof(MegaArgs, proj_stride);

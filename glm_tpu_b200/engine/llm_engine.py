@@ -40,6 +40,19 @@ class LLMEngine:
         if self.poisoned:
             raise EngineFailure("this engine failed earlier and refuses further requests")
 
+    def _admit(self) -> None:
+        """Memory admission before every request (the runner's projection against the live device): refused on every rank
+        together, so that no rank starts a prefill its peers will not join."""
+        admit = getattr(self.runner, "admit_request", None)
+        error = None
+        if admit is not None:
+            try:
+                admit()
+            except Exception as exc:  # noqa: BLE001
+                error = exc
+        if not self.vote.all(error is None, "admission"):
+            raise error if error is not None else EngineFailure("a peer refused the request at memory admission")
+
     def _check_capacity(self, capacity: int, lanes: int) -> None:
         if capacity != self.runner.cache.context_capacity:
             raise RequestValidationError(f"the loaded model serves capacity {self.runner.cache.context_capacity}, not {capacity}")
@@ -79,6 +92,7 @@ class LLMEngine:
         request_schema.validate(request, self.profile)
         self._check_capacity(request["context_capacity"], 1)
         try:
+            self._admit()
             t0 = self.clock()
             session = RequestSession(self.runner, request, self.vote, sink, lane=0, deadline=deadline, clock=self.clock)
             for lane in range(1, self.runner.lanes):  # a single chat on a multi-lane model: the other lanes stay frozen
@@ -107,6 +121,7 @@ class LLMEngine:
         requests = batch["requests"]
         self._check_capacity(batch["context_capacity"], len(requests))
         try:
+            self._admit()
             session = BatchedSession(self.runner, requests, self.vote, sink, deadline=deadline, clock=self.clock)
             prefill_seconds, ttft = [], []
             for lane, req in enumerate(requests):  # sequential prefills, each into its own lane

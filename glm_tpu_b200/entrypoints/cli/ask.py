@@ -104,6 +104,8 @@ def main(args) -> int:
     argv = ["--request", str(request_path), "--run-root", str(site.paths.run_root), "--gpus", str(args.gpus or site.gpus), "--model", model,
             "--backend", args.backend, "--context", str(capacity), "--wall-seconds", str(args.wall_seconds), "--policy", site.policy,
             "--master-port", str(site.master_port), "--print-answers"]
+    if site.source != "<defaults>":
+        argv += ["--site", site.source]  # its pins (checkpoint manifest, topology binding, launch rules) bind the workers
     if args.concurrent:
         argv += ["--lanes", str(len(questions))]
     if args.keep_loaded:

@@ -49,7 +49,58 @@ def parse_args(argv=None):
     ap.add_argument("--policy", default="record", choices=["record", "strict"])
     ap.add_argument("--master-port", type=int, default=29577)
     ap.add_argument("--poll-seconds", type=float, default=0.5)
+    ap.add_argument("--site", default=None, help="site file whose pins (checkpoint manifest, topology binding, launch rules) bind this launch")
+    ap.add_argument("--binding", default=None, help="topology binding file (default: <state_root>/topology_binding.json when the site pins one)")
     return ap.parse_args(argv)
+
+
+def stage_site(run_dir: Path, site) -> list[str]:
+    """Write the resolved site for the workers; returns the worker arguments that name it and its digest."""
+    from glm_tpu_b200.utils.io_utils import create_private_exclusive
+
+    path = run_dir / "site.json"
+    create_private_exclusive(path, site.resolved_json())
+    return ["--site-json", str(path), "--site-sha256", site.sha256]
+
+
+def stage_source_manifest(run_dir: Path, repo: Path) -> list[str]:
+    from glm_tpu_b200.executor import source_manifest
+    from glm_tpu_b200.utils.io_utils import create_private_exclusive
+
+    manifest = source_manifest.build(repo)
+    path = run_dir / source_manifest.MANIFEST_FILE
+    create_private_exclusive(path, source_manifest.to_bytes(manifest))
+    return ["--source-manifest", str(path), "--source-manifest-sha256", source_manifest.digest(manifest)]
+
+
+def stage_binding(run_dir: Path, site, binding_path: Path | None, gpus: int, nvml=None) -> tuple[list[str], dict]:
+    """Authenticate the topology binding the site pins against the live box and hand it to the workers.
+
+    Returns ``(worker arguments, extra environment)``: the environment makes ``cuda:<local_rank>`` the bound GPU in every worker
+    (``CUDA_VISIBLE_DEVICES`` = the bound UUIDs in rank order).  Without a pin nothing is staged."""
+    pin = site.topology_binding_sha256 if site is not None else ""
+    if not pin and binding_path is None:
+        return [], {}
+    from glm_tpu_b200.exceptions import ConfigValidationError
+    from glm_tpu_b200.parallel import topology as topo
+    from glm_tpu_b200.utils.io_utils import create_private_exclusive
+    from glm_tpu_b200.utils.json_utils import canonical_wire_bytes
+
+    if binding_path is None:
+        if site.paths.state_root is None:
+            raise ConfigValidationError("[topology] binding_sha256 is set but neither --binding nor [paths] state_root says where the binding is")
+        binding_path = site.paths.state_root / "topology_binding.json"
+    binding = topo.load_topology_binding(binding_path, pin)
+    if binding["gpus"] != gpus:
+        raise ConfigValidationError(f"the topology binding is for {binding['gpus']} GPUs, the launch for {gpus}")
+    try:
+        live = topo.discover_topology(nvml)
+    except ImportError as exc:
+        raise ConfigValidationError("a pinned topology binding needs NVML (pynvml) to authenticate the live GPUs") from exc
+    topo.validate_live(binding, live)
+    staged = run_dir / "topology_binding.json"
+    create_private_exclusive(staged, canonical_wire_bytes(binding) + b"\n")
+    return ["--binding", str(staged), "--binding-sha256", binding["binding_sha256"]], {"CUDA_VISIBLE_DEVICES": topo.visible_devices(binding)}
 
 
 def default_run_root() -> Path:
@@ -132,11 +183,17 @@ def resident_controller(fl: fleet_mod.Fleet, run_dir: Path, world: int, profile_
 
 def main(argv=None) -> int:
     args = parse_args(argv)
-    run_root = Path(args.run_root) if args.run_root else default_run_root()
+    site = None
+    if args.site:
+        from glm_tpu_b200.config.site import SiteConfig
+
+        site = SiteConfig.load(Path(args.site), required=True)
+    run_root = Path(args.run_root) if args.run_root else (site.paths.run_root if site is not None else default_run_root())
     payload = json.loads(read_bounded(Path(args.request), request_schema.PAYLOAD_CAP)) if args.request else None
     if payload is None and not args.keep_loaded:
         raise SystemExit("--request is required unless --keep-loaded starts a resident session")
-    with jobs.fleet_job(run_root, repo=REPO, policy=args.policy, require_idle=args.backend == "gpu") as job:
+    rules = site.launch_rules if site is not None else args.policy
+    with jobs.fleet_job(run_root, repo=REPO, policy=rules, require_idle=args.backend == "gpu") as job:
         run_dir = staging.new_run_dir(run_root)
         print(proto.STDOUT_RUN + str(run_dir), flush=True)
         staged = staging.stage_request(run_dir, payload)
@@ -149,7 +206,16 @@ def main(argv=None) -> int:
             worker_args += ["--request", str(staged), "--request-sha256", payload["request_sha256"]]
         if args.keep_loaded:
             worker_args.append("--keep-loaded")
-        specs = fleet_mod.worker_specs(world=args.gpus, run_dir=run_dir, worker_args=worker_args, master_port=args.master_port)
+        # what binds this launch: the resolved site (pins), a digest of every source file the workers import, the GPU binding
+        extra_env: dict = {}
+        if site is not None:
+            worker_args += stage_site(run_dir, site)
+        worker_args += stage_source_manifest(run_dir, REPO)
+        if args.backend == "gpu":
+            binding_args, extra_env = stage_binding(run_dir, site, Path(args.binding) if args.binding else None, args.gpus)
+            worker_args += binding_args
+        specs = fleet_mod.worker_specs(world=args.gpus, run_dir=run_dir, worker_args=worker_args, master_port=args.master_port,
+                                       extra_env=extra_env)
         deadline = time.monotonic() + args.wall_seconds
         fl = job.start(specs, keep_stdin=args.keep_loaded)
         terminal: dict = {"run_dir": str(run_dir)}

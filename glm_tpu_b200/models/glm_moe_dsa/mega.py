@@ -217,11 +217,32 @@ class MegaDecoder:
     def stretch(self, first: tuple[int, int], last: tuple[int, int]) -> None:
         """Launch the persistent kernel over the phases ``first .. last`` (``(layer, phase)`` pairs, both inclusive)."""
         self._sync_args()
+        if native._exchanges is not None and self.args.comm.world > 1:
+            g, grid = self.model.g, self.grid()
+            for layer in range(first[0], last[0] + 1):
+                head = layer >= g.num_layers
+                lo = first[1] if layer == first[0] else 1
+                hi = last[1] if layer == last[0] else (HEAD_FINALIZE if head else COMBINE)
+                for ph in range(lo, hi + 1):
+                    self._note_exchange(layer, ph, grid)
         native._check(self._lib.glmb_mega_decode(C.byref(self.args), C.c_void_p(self._device_args.data_ptr()), first[0], first[1], last[0], last[1],
                                                  native._stream()), "mega_decode")
 
+    def _note_exchange(self, layer: int, phase: int, persistent_grid: int = 0) -> None:
+        """Tell the collective-plan recorder what this phase exchanges between the GPUs."""
+        if native._exchanges is None or self.args.comm.world <= 1:
+            return
+        entry = C.byref(self._table[layer]) if layer < self.model.g.num_layers else None
+        out = (C.c_int * 4)()
+        native._check(self._lib.glmb_mega_phase_exchange(C.byref(self.args), entry, layer, phase, persistent_grid, out), "mega_phase_exchange")
+        if out[0] == 1:
+            native._exchanges.append({"kind": "allreduce", "channel": out[1], "ctas": out[2], "floats_per_cta": out[3], "op": f"phase{phase}"})
+        elif out[0] == 2:
+            native._exchanges.append({"kind": "signal", "signal": out[1], "op": f"phase{phase}"})
+
     def phase(self, layer: int, phase: int) -> None:
         """Launch one phase as a kernel of its own (``layer == num_layers``: the head)."""
+        self._note_exchange(layer, phase)
         entry = C.byref(self._table[layer]) if layer < self.model.g.num_layers else None
         native._check(self._lib.glmb_mega_phase(C.byref(self.args), entry, layer, phase, native._stream()), "mega_phase")
 

@@ -138,6 +138,42 @@ class kernel_timeline:
         return [(name, ints, start.elapsed_time(end)) for name, ints, start, end in self.events]
 
 
+_exchanges = None  # when a list: every launch that exchanges data between GPUs appends what it does (the collective plan)
+
+
+class record_exchanges:
+    """``with record_exchanges() as plan:`` collects the cross-GPU exchanges of the launches issued inside, in order:
+    ``{"kind": "allreduce", "channel": c, "ctas": n, "floats_per_cta": f, "op": name}`` or ``{"kind": "signal", "signal": s,
+    "op": name}``.  The runner checks the list against the rules the in-kernel protocol depends on before it captures a program."""
+
+    def __enter__(self):
+        global _exchanges
+        self.plan = _exchanges = []
+        return self.plan
+
+    def __exit__(self, *exc):
+        global _exchanges
+        _exchanges = None
+
+
+def _note_allreduce(op: str, comm, channel: int, ctas: int, floats_per_cta: int) -> None:
+    if _exchanges is not None and comm is not None and comm.world > 1:
+        _exchanges.append({"kind": "allreduce", "channel": int(channel), "ctas": int(ctas), "floats_per_cta": int(floats_per_cta), "op": op})
+
+
+def _note_signal(op: str, comm, sig: int) -> None:
+    if _exchanges is not None and comm is not None and comm.world > 1:
+        _exchanges.append({"kind": "signal", "signal": int(sig), "op": op})
+
+
+def _skinny_ksplit(units: int, K: int) -> int:
+    """The K split the skinny kernels pick (``pick_ksplit`` in csrc/gemv.cu)."""
+    ks = 1
+    while ks < 8 and units * ks < 148 * 4 * 8 and K % (ks * 2 * 256) == 0 and K // (ks * 2) >= 512:
+        ks *= 2
+    return ks
+
+
 def _p(t):
     if t is None:
         return None
@@ -173,6 +209,9 @@ def skinny_bf16(x, w, out, mode=SK_OUT_F32, *, rows=None, comm=None, channel=0, 
     xs = x.stride(0) if xs is None else xs
     ws = w.stride(-2) if ws is None else ws
     os_ = out.stride(0) if os_ is None else os_
+    if mode == SK_OUT_ALLREDUCE_BF16 and _exchanges is not None:
+        groups = 8 // _skinny_ksplit(-(-N // 2) * batch, K)
+        _note_allreduce("skinny_bf16", comm, channel, -(-N // (groups * 2)) * batch, groups * 2 * (1 if rows <= 1 else 2 if rows <= 2 else 4 if rows <= 4 else 8))
     _check(
         lib().glmb_skinny_bf16(_p(x), C.c_int64(xs), rows, _p(w), C.c_int64(ws), N, K, _p(out), C.c_int64(os_), mode, batch,
                                C.c_int64(xb), C.c_int64(wb), C.c_int64(ob), _comm(comm), channel, _stream()),
@@ -251,6 +290,8 @@ def gather_rows(src, idx, divisor, dst):
 
 def moe_combine(dw, topk_ids, shared_partial, rows, top_k, H, expert_base, experts_local, scale, plain, out, routed_partial=None,
                 comm=None, channel=CH_MLP):
+    if routed_partial is None:
+        _note_allreduce("moe_combine", comm, channel, -(-H // 16) * -(-rows // MAX_ROWS), (1 if plain else 2) * min(rows, MAX_ROWS) * 16)
     _check(
         lib().glmb_moe_combine(_p(dw), _p(topk_ids), _p(shared_partial), rows, top_k, H, expert_base, experts_local, f32(scale),
                                int(plain), _p(out), _p(routed_partial), _comm(comm), channel, _stream()),
@@ -285,6 +326,7 @@ def q_post(args: QPostArgs, rows: int):
 def q_absorb(q_nope, rows, kv_b, heads_local, head_base, heads_total, nope, vdim, L, rd, q_full, q_full_offset=0, comm=None,
              sig=SIG_Q, *, q_proj=None, rope_table=None, row_pos=None, capacity=0):
     """``q_proj`` (fp32 output of the q_b projection) replaces ``q_nope`` and makes the kernel do the q_post work of its heads too."""
+    _note_signal("q_absorb", comm, sig)
     if q_proj is not None:
         _check(
             lib().glmb_q_absorb_from_proj(_p(q_proj), C.c_int64(q_proj.stride(0)), _p(rope_table), _p(row_pos), capacity, rows, _p(kv_b),
@@ -332,6 +374,7 @@ def indexer_score(q_idx, head_w, index_cache, row_pos, row_lane, rows, IH, D, in
 
     ``pieces`` (scratch of :func:`indexer_rows_scratch_bytes`) with ``lane`` selects the many-rows kernel: every row belongs to
     the chat in cache lane ``lane`` (a prefill chunk), the key tiles stay resident while the rows stream past them."""
+    _note_signal("indexer_score", comm, sig)
     if pieces is not None and rows >= INDEXER_ROWS_MIN and indexer_takes_raw_query(IH, D) and _indexer_rows_kernel():
         if lane is None:
             raise ValueError("the many-rows indexer needs the cache lane that all rows share")
@@ -420,6 +463,7 @@ def sparse_mla_rows(q_full, kv_cache, sel_local, sel_counts, row_lane, rows, H, 
 
 def attn_local_merge(part_o, part_ml, sel_counts, rows, H, L, top_k, max_chunks, o_lat, heads_local, xpart_offset=0, comm=None,
                      sig=SIG_ATTN):
+    _note_signal("attn_local_merge", comm, sig)
     _check(
         lib().glmb_attn_local_merge(_p(part_o), _p(part_ml), _p(sel_counts), rows, H, L, top_k, max_chunks, _p(o_lat), heads_local,
                                     C.c_int64(xpart_offset), _comm(comm), sig, _stream()),
@@ -439,6 +483,7 @@ def router_topk(logits, bias, top_k, ids, weights):
 
 
 def argmax_rows(logits, rows, V, vocab_base, cand, cand_offset=0, comm=None, sig=SIG_SAMPLE, status=None):
+    _note_signal("argmax_rows", comm, sig)
     _check(
         lib().glmb_argmax_rows(_p(logits), C.c_int64(logits.stride(0)), rows, V, vocab_base, _p(cand), C.c_int64(cand_offset),
                                _comm(comm), sig, _p(status), _stream()),
@@ -453,6 +498,8 @@ def step_finalize(cand, n_sets, rows, row_active, tokens, positions, out_tokens,
     ``local_best`` (``[rows]`` int64 filled by the lm_head kernel in argmax mode) is first published as this rank's
     candidate.  advance: bit 0 writes the sampled token into ``tokens``, bit 1 increments ``positions``.
     """
+    if local_best is not None:
+        _note_signal("step_finalize", comm, sig)
     _check(
         lib().glmb_step_finalize(_p(cand), C.c_int64(cand_offset), _p(local_best), n_sets, rows, _p(row_active), _p(tokens),
                                  _p(positions), _p(out_tokens), _p(step_counter), ring, int(advance), _comm(comm), sig, _stream()),

@@ -43,6 +43,17 @@ def project_memory(geometry, layout, cache, weight_bytes: int, staging_bytes: in
     return out
 
 
+def project_live(projection: dict, free_bytes: int, total_bytes: int, *, already_resident: int, reserve_bytes: int = 512 << 20) -> dict:
+    """The projection against what the driver reports right now: what is still to be allocated (the projected total minus
+    what is already resident, e.g. the weights) plus a reserve must fit into the free memory of the device."""
+    to_allocate = max(0, projection["total"] - already_resident)
+    out = dict(projection, device_free=int(free_bytes), device_total=int(total_bytes), to_allocate=int(to_allocate), reserve=int(reserve_bytes))
+    out["admitted"] = bool(projection["admitted"]) and to_allocate + reserve_bytes <= free_bytes
+    if not out["admitted"]:
+        out["limit"] = min(projection["limit"], already_resident + max(0, free_bytes - reserve_bytes))
+    return out
+
+
 def require_admitted(projection: dict) -> None:
     if not projection["admitted"]:
         need, limit = projection["total"] / 2**30, projection["limit"] / 2**30

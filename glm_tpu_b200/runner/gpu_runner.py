@@ -26,7 +26,7 @@ from glm_tpu_b200.models.glm_moe_dsa.model import RING, DecoderState, GlmMoeDsaM
 from glm_tpu_b200.models.glm_moe_dsa.weights import DeviceWeights
 from glm_tpu_b200.ops import native
 from glm_tpu_b200.parallel.peer import PeerGroup
-from glm_tpu_b200.runner.admission import project_memory
+from glm_tpu_b200.runner.admission import check_collective_plan, project_live, project_memory, require_admitted
 
 
 @dataclass
@@ -98,6 +98,11 @@ class GpuModelRunner:
                                      + self.world * self.layout.heads_local * (g.kv_lora_rank + 2) * 4 + self.world * 8) + (1 << 20)
             if self.world > 1 and prefill_chunk > 8:  # output + partial-tile slots of the prefill GEMM with the fused all-reduce
                 staging_bytes += prefill_chunk * g.hidden_size * 2 + native.gemm_allreduce_part_bytes(prefill_chunk, g.hidden_size, self.world) + 8192
+        # memory admission BEFORE anything large is allocated: the projection (weights already resident + caches of every lane
+        # + staging + workspaces) against the device's size and against what the driver reports as free right now
+        self.report.memory = self._project(weights.bytes_resident, staging_bytes, already_resident=weights.bytes_resident)
+        require_admitted(self.report.memory)
+        self._staging_bytes = staging_bytes
         with torch.cuda.device(self.device):
             # emulate_shard (measurements only): this process holds rank `rank`'s shard of a `world`-GPU layout but runs alone:
             # every exchange is skipped, so the outputs mean nothing and the decode step costs what one GPU of the box spends
@@ -112,12 +117,14 @@ class GpuModelRunner:
             self.model.emulated_shard = self.emulate_shard
             self.state = DecoderState.allocate(self.cache, self.device)
             self.decode_ws = Workspace(self.model, lanes, "decode")
-            # decode program: the persistent kernel (a step is a few dozen launches) where its shapes and cache layout allow,
-            # else the per-kernel sequence.  GLM_B200_DECODE=kernels|mega overrides 'auto'.
+            # decode program: 'kernels' (default) is the per-kernel sequence; 'phases' runs the fused phases of
+            # csrc/decode_mega.cu as 11 kernels per layer, 'mega' as stretches of one persistent cooperative kernel.  Both fused
+            # forms agree with 'kernels' bit for bit and are slower on B200 as measured (they give up occupancy, the L1 and a
+            # small instruction footprint for fewer launches), so 'auto' means 'kernels'.  GLM_B200_DECODE overrides 'auto'.
             import os
 
             if decode_path == "auto":
-                decode_path = os.environ.get("GLM_B200_DECODE", "auto")
+                decode_path = os.environ.get("GLM_B200_DECODE", "kernels")
             if decode_path not in ("auto", "phases", "mega", "kernels"):
                 raise ValueError("decode_path is 'auto', 'phases', 'mega' or 'kernels'")
             if mega_compat_ksplit is None and "GLM_B200_MEGA_KSPLIT" in os.environ:
@@ -138,9 +145,22 @@ class GpuModelRunner:
             self._graph = None
             self._graph_stream = torch.cuda.Stream(device=self.device)
         self.report.phases["allocate"] = time.perf_counter() - t0
-        self.report.memory = project_memory(self.g, self.layout, self.cache, weights.bytes_resident, staging_bytes)
         self.decode_launches = 0
         self.steps_issued = 0
+
+    # ------------------------------------------------------------------ admission
+    def _project(self, weight_bytes: int, staging_bytes: int, *, already_resident: int, mem_info=None) -> dict:
+        projection = project_memory(self.g, self.layout, self.cache, weight_bytes, staging_bytes)
+        free, total = mem_info if mem_info is not None else torch.cuda.mem_get_info(self.device)
+        return project_live(projection, free, total, already_resident=already_resident)
+
+    def admit_request(self, mem_info=None) -> dict:
+        """Before every request: everything this runner projected is resident by now, so the device must still have the reserve
+        free (another process on the GPU, a leak) and the status word must be clean.  Raises ``PlanValidationError``."""
+        admitted = self._project(self.weights.bytes_resident, self._staging_bytes, already_resident=1 << 62, mem_info=mem_info)
+        require_admitted(admitted)
+        self.report.memory["last_request"] = {"device_free": admitted["device_free"], "reserve": admitted["reserve"]}
+        return admitted
 
     # ------------------------------------------------------------------ decode program
     def _decode_body(self) -> None:
@@ -158,9 +178,13 @@ class GpuModelRunner:
         with torch.cuda.device(self.device):
             saved = self.state.active.clone()
             self.state.active.zero_()
-            with _LaunchCounter() as counter:
+            with _LaunchCounter() as counter, native.record_exchanges() as plan:
                 self._decode_body()
             self.decode_launches = counter.count
+            # the cross-GPU exchanges of the step, in launch order, against the rules the in-kernel protocol rests on (alternating
+            # all-reduce channels, a signal at most once between two all-reduces, payloads within the slots): refused before capture
+            check_collective_plan(plan, world=self.peer.world)
+            self.report.phases["collective_plan"] = {"exchanges": len(plan), "allreduces": sum(1 for op in plan if op["kind"] == "allreduce")}
             torch.cuda.synchronize(self.device)
             kind = "eager"
             if self.use_graphs and self.model.comm_mode == "fused" or (self.use_graphs and self.world == 1):  # noqa: E129

@@ -46,12 +46,62 @@ def parse_args(argv=None):
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
     ap.add_argument("--kv-layout", default="auto")
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--site-json", help="the controller's resolved site (staged in the run directory)")
+    ap.add_argument("--site-sha256", help="digest of --site-json as the controller computed it")
+    ap.add_argument("--source-manifest", help="digest of every source file, taken by the controller")
+    ap.add_argument("--source-manifest-sha256")
+    ap.add_argument("--binding", help="topology binding: which physical GPU each rank uses")
+    ap.add_argument("--binding-sha256")
     ap.add_argument("--preflight-only", action="store_true")
     ap.add_argument("--no-warmup", action="store_true")
     return ap.parse_args(argv)
 
 
 # ------------------------------------------------------------------------------------------------ preflight
+REPO = Path(__file__).resolve().parents[2]
+SELF = Path(__file__).resolve().relative_to(REPO).as_posix()
+
+
+def authenticate_launch(args) -> dict:
+    """What binds this worker to its controller, checked before a device is opened: the staged site (digest given on the
+    command line; its run root must be where the run directory is), the source manifest (every listed file re-hashed, this
+    file among them) and the topology binding (self-digest, the command line's digest, the site's pin).  Returns
+    ``{"site", "pins", "binding"}`` (None where nothing was staged: a launch without a site file pins nothing)."""
+    from glm_tpu_b200.utils.io_utils import read_bounded
+
+    out: dict = {"site": None, "pins": None, "binding": None}
+    for flag, digest in (("site_json", "site_sha256"), ("source_manifest", "source_manifest_sha256"), ("binding", "binding_sha256")):
+        if bool(getattr(args, flag)) != bool(getattr(args, digest)):
+            raise SystemExit(f"--{flag.replace('_', '-')} and --{digest.replace('_', '-')} come together")
+    if args.site_json:
+        from glm_tpu_b200.config.site import SiteConfig
+
+        site = SiteConfig.from_staged(Path(args.site_json), args.site_sha256)
+        if Path(args.run_dir).resolve().parent != site.paths.run_root.resolve():
+            raise SystemExit("the run directory is not under the staged site's run_root")
+        out["site"], out["pins"] = site, site.checkpoint_pins
+    if args.source_manifest:
+        import hashlib
+
+        from glm_tpu_b200.executor import source_manifest
+
+        raw = read_bounded(Path(args.source_manifest), 4 << 20)
+        if hashlib.sha256(raw).hexdigest() != args.source_manifest_sha256:
+            raise SystemExit("the source manifest is not the controller's (digest differs)")
+        source_manifest.verify(REPO, json.loads(raw), must_contain=SELF)
+    if args.binding:
+        from glm_tpu_b200.parallel import topology as topo
+
+        binding = topo.load_topology_binding(Path(args.binding), args.binding_sha256)
+        pinned = out["site"].topology_binding_sha256 if out["site"] is not None else ""
+        if pinned and binding["binding_sha256"] != pinned:
+            raise SystemExit("the topology binding is not the one the site pins")
+        out["binding"] = binding
+    elif out["site"] is not None and out["site"].topology_binding_sha256 and args.backend == "gpu":
+        raise SystemExit("the site pins a topology binding but the controller staged none")
+    return out
+
+
 def preflight(args) -> dict:
     """Checks that need no device.  Returns the validated payload (or None)."""
     if os.environ.get(proto.WORKER_ENV_FLAG) != "1":
@@ -59,6 +109,7 @@ def preflight(args) -> dict:
     run_dir = Path(args.run_dir)
     if not run_dir.is_dir():
         raise SystemExit(f"run directory {run_dir} does not exist")
+    args.launch = authenticate_launch(args)
     payload = None
     if args.request:
         raw = Path(args.request).read_bytes()
@@ -108,6 +159,7 @@ class Worker:
         self.gloo = None
         self.engine = None
         self.tokenizer = None
+        self.launch = getattr(args, "launch", None) or {"site": None, "pins": None, "binding": None}
 
     def phase(self, name: str, fn):
         """Run ``fn``; whatever happens, all ranks vote on the outcome before anyone continues."""
@@ -140,7 +192,30 @@ class Worker:
                 dist.init_process_group("gloo")
                 self.gloo = dist.group.WORLD
             self.vote = ProcessGroupVote(self.gloo)
+        self.check_bound_device()
 
+    def check_bound_device(self, device_uuid=None) -> None:
+        """With a topology binding, ``cuda:<local_rank>`` must be the GPU the binding gives this rank, and every rank must hold the
+        same binding.  ``device_uuid`` is injectable for tests (default: what the CUDA runtime reports)."""
+        binding = self.launch["binding"]
+        digest = binding["binding_sha256"] if binding is not None else ""
+        self.record["topology_binding_sha256"] = digest or None
+        ok, why = True, ""
+        if binding is not None and self.args.backend == "gpu":
+            if binding["gpus"] != self.world:
+                ok, why = False, f"the binding is for {binding['gpus']} GPUs, the fleet has {self.world} ranks"
+            else:
+                if device_uuid is None:
+                    import torch
+
+                    def device_uuid(index):
+                        return "GPU-" + str(torch.cuda.get_device_properties(index).uuid)
+                want, have = binding["ranks"][self.rank]["uuid"], device_uuid(self.local_rank)
+                if have != want:
+                    ok, why = False, f"rank {self.rank} sits on {have}, the binding says {want}"
+        agreed = self.digest_consensus("binding:" + digest)
+        if not self.vote.all(ok and agreed, "topology_binding"):
+            raise SystemExit(why or "the ranks do not hold the same topology binding")
     def digest_consensus(self, digest: str) -> bool:
         if self.world == 1:
             return True
@@ -179,7 +254,9 @@ class Worker:
             if kind == "checkpoint":
                 from glm_tpu_b200.model_loader.sharded_state import loader
 
-                checkpoint = loader.load_rank_checkpoint(path, self.rank, self.world)
+                # the site's pins travel with the load: another packed checkpoint than the pinned one is refused here
+                checkpoint = loader.load_rank_checkpoint(path, self.rank, self.world, pins=self.launch["pins"])
+                self.record["checkpoint_pins"] = {k: v for k, v in (self.launch["pins"] or {}).items() if v}
             elif geometry.num_layers <= 8 and geometry.hidden_size <= 1024:
                 from glm_tpu_b200.models.glm_moe_dsa.weights import random_checkpoint
 

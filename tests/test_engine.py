@@ -84,8 +84,8 @@ def test_generate_schedule_and_report():
     report = engine.generate(make(n=4), events.append)
     assert [e.index for e in events] == [0, 1, 2, 3] and events[-1].finish_reason == "length"
     assert report["emitted"] == 4 and report["timed_decode_tokens"] == 3 and report["stop_cause"] == "output_cap"
-    # prefill pair, then (validity, delivery) per decode step, in this exact order
-    assert [p for p, _ in vote.log] == ["prefill_validity", "prefill_delivery"] + ["validity", "delivery"] * 3
+    # memory admission first, the prefill pair, then (validity, delivery) per decode step, in this exact order
+    assert [p for p, _ in vote.log] == ["admission", "prefill_validity", "prefill_delivery"] + ["validity", "delivery"] * 3
     assert ("deactivate", 0) in runner.log
     assert report["token_sha256"] and report["prompt_tokens"] == 3
 
