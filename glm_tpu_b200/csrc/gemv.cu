@@ -17,6 +17,26 @@
 #define SK_WARPS 8
 #define SK_THREADS (SK_WARPS * 32)
 
+// With programmatic dependent launch a kernel's CTAs become resident while its predecessor still runs and then wait for it.
+// The weights do not depend on the predecessor, so before waiting a CTA asks the L2 for the rows it is about to stream: the HBM
+// fetch overlaps the predecessor's tail instead of starting after it.  Tables larger than SK_PREFETCH_LIMIT are left alone (they
+// would only sweep the L2).
+#define SK_PREFETCH_LIMIT ((int64_t)48 << 20)
+__device__ __forceinline__ void sk_prefetch_rows(const void* first_row, int rows, int64_t row_stride_elems, int K, int elem_bytes) {
+    if (threadIdx.x != 0 || rows <= 0) return;
+    const char* p = reinterpret_cast<const char*>(first_row);
+    if (row_stride_elems == K) {
+        const uint32_t bytes = (uint32_t)(((int64_t)rows * K * elem_bytes) & ~(int64_t)15);
+        if (bytes && !((uintptr_t)p & 15)) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+        return;
+    }
+    for (int r = 0; r < rows; ++r) {
+        const char* q = p + (int64_t)r * row_stride_elems * elem_bytes;
+        const uint32_t bytes = (uint32_t)(((int64_t)K * elem_bytes) & ~(int64_t)15);
+        if (bytes && !((uintptr_t)q & 15)) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(q), "r"(bytes) : "memory");
+    }
+}
+
 // ---------------------------------------------------------------------------------------------------
 // out[r][n] = sum_k x[r][k] * w[n][k]          (bf16 weights)
 enum { SK_OUT_F32 = 0, SK_OUT_BF16 = 1, SK_OUT_ALLREDUCE_BF16 = 2, SK_OUT_ARGMAX = 3 };
@@ -28,7 +48,12 @@ __global__ void __launch_bounds__(SK_THREADS)
 skinny_bf16_kernel(const bf16* __restrict__ x, int64_t xs, int rows, const bf16* __restrict__ w, int64_t ws, int N, int K,
                    void* __restrict__ out, int64_t os, int mode, int ks, int64_t xb, int64_t wb, int64_t ob, PeerComm comm,
                    int channel) {
-    GLMB_PDL_PROLOGUE();
+    asm volatile("griddepcontrol.launch_dependents;");
+    if ((int64_t)N * K * 2 * gridDim.y <= SK_PREFETCH_LIMIT) {
+        const int first = blockIdx.x * (SK_WARPS / ks) * 2;
+        sk_prefetch_rows(w + (int64_t)blockIdx.y * wb + (int64_t)first * ws, min((SK_WARPS / ks) * 2, N - first), ws, K, 2);
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     __shared__ float red[SK_WARPS][2][R];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int group = warp / ks, kpart = warp % ks, groups = SK_WARPS / ks;
@@ -133,7 +158,13 @@ template <int R>
 __global__ void __launch_bounds__(SK_THREADS)
 skinny_bf16_swiglu_kernel(const bf16* __restrict__ x, int64_t xs, int rows, const bf16* __restrict__ wg,
                           const bf16* __restrict__ wu, int64_t ws, int N, int K, bf16* __restrict__ act, int64_t as, int ks) {
-    GLMB_PDL_PROLOGUE();
+    asm volatile("griddepcontrol.launch_dependents;");
+    if ((int64_t)N * K * 4 <= SK_PREFETCH_LIMIT) {
+        const int first = blockIdx.x * (SK_WARPS / ks), cnt = min(SK_WARPS / ks, N - first);
+        sk_prefetch_rows(wg + (int64_t)first * ws, cnt, ws, K, 2);
+        sk_prefetch_rows(wu + (int64_t)first * ws, cnt, ws, K, 2);
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     __shared__ float red[SK_WARPS][2][R];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int group = warp / ks, kpart = warp % ks;

@@ -3,7 +3,8 @@ the batched decode program (``BatchedSession``), with the all-rank vote schedule
 
 Every rank (one process per GPU) runs the same session.  A step is
 
-    decode on the device  ->  read the produced token(s) and the device status word
+    feed (the host hands the device the token(s) it committed last: a few bytes from pinned memory)
+    ->  decode on the device  ->  read the produced token(s) and the device status word
     ->  vote 1 "validity" (all ranks: status clean, token inside the vocabulary, deadline not passed)
     ->  commit (the token becomes part of the session state; finish reasons are decided here)
     ->  deliver (rank 0 appends the TokenEvent line to the sink and flushes)
@@ -112,6 +113,13 @@ class _SessionBase:
     def _in_time(self) -> bool:
         return self.deadline is None or self.clock() < self.deadline
 
+    def _feed(self, tokens: dict) -> None:
+        """Hand the device the tokens the fleet committed (``lane -> token``): what the next step consumes is what the votes
+        agreed on, not whatever a rank's device happened to keep.  Runners without device-side token registers ignore it."""
+        feed = getattr(self.runner, "feed_tokens", None)
+        if feed is not None:
+            feed(tokens)
+
 
 class RequestSession(_SessionBase):
     """One chat on one lane."""
@@ -140,6 +148,7 @@ class RequestSession(_SessionBase):
         if st.finished:
             raise EngineFailure("step on a finished session")
         t0 = self.clock()
+        self._feed({st.lane: st.tokens[-1]})
         self.runner.decode_step()
         token = self.runner.read_last_tokens()[st.lane]
         status = self.runner.read_status()
@@ -180,6 +189,7 @@ class BatchedSession(_SessionBase):
         if not active:
             raise EngineFailure("step on a finished batch")
         t0 = self.clock()
+        self._feed({st.lane: st.tokens[-1] for st in active})
         self.runner.decode_step()
         tokens = self.runner.read_last_tokens()
         status = self.runner.read_status()

@@ -147,6 +147,8 @@ class GpuModelRunner:
         self.report.phases["allocate"] = time.perf_counter() - t0
         self.decode_launches = 0
         self.steps_issued = 0
+        self._feed_host = None
+        self.fed_bytes_per_step = 0
 
     # ------------------------------------------------------------------ admission
     def _project(self, weight_bytes: int, staging_bytes: int, *, already_resident: int, mem_info=None) -> dict:
@@ -223,6 +225,18 @@ class GpuModelRunner:
         else:
             self._decode_body()
         self.steps_issued += 1
+
+    def feed_tokens(self, tokens: dict) -> None:
+        """Copy the committed tokens of the given lanes (``lane -> token``) from pinned host memory into the device's token
+        registers (asynchronous, on the current stream: the next decode step reads them).  4 bytes per lane; a lane that is not
+        named keeps being fed what it was fed last, which a frozen lane never uses."""
+        if self._feed_host is None:
+            self._feed_host = torch.zeros(self.lanes, dtype=torch.int32).pin_memory()
+        for lane, token in tokens.items():
+            self._feed_host[lane] = int(token)
+        with torch.cuda.device(self.device):
+            self.state.tokens.copy_(self._feed_host, non_blocking=True)
+        self.fed_bytes_per_step = 4 * self.lanes
 
     def read_last_tokens(self) -> list[int]:
         """Tokens of the most recent decode step, one per lane (-1 for a frozen lane).  Synchronizes."""
