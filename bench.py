@@ -413,7 +413,9 @@ def main() -> int:
                 "prompt_tokens": args.prompt if not args.depth else None,
                 "context_depth": args.depth or args.prompt,
                 "context_fill": "synthetic random cache rows (no prefill)" if args.depth else "real prefill of the prompt",
-                "parallelism": f"tp{b.world}(heads,mlp)+ep{b.world}(experts)" if b.world > 1 else "single gpu",
+                "parallelism": (f"tp{b.world}(heads, mlp, shared expert" + (", routed experts by column)" if runner.model.layout.sliced
+                                else f")+ep{b.world}(routed experts)")) if b.world > 1 else "single gpu",
+                "expert_split": runner.model.layout.expert_split,
                 "comm": args.comm,
                 "kv_layout": kv_layout,
                 "decode_program": rec.kind,

@@ -5,7 +5,14 @@ One process drives one GPU.  Between blocks the hidden state is *replicated* on 
 
 * attention heads (q_b, kv_b, o_proj) are split over the GPUs (``heads_local = heads / world``);
 * the dense MLP and the shared expert are split by intermediate columns;
-* routed experts are expert-parallel: expert ``e`` lives on GPU ``e // experts_local``;
+* routed experts, one of two splits (``expert_split``):
+  ``"whole"``: expert-parallel, expert ``e`` lives whole on GPU ``e // experts_local``.  A decode token's eight routes then land
+  on the GPUs unevenly (the busiest GPU of eight streams ~2.6 experts where the average is one) and every GPU waits for the
+  busiest at the all-reduce that follows.
+  ``"sliced"``: every GPU holds a ``1/world`` slice of the intermediate columns of EVERY expert (the same cut as the shared expert
+  and the dense MLP).  Each GPU then streams exactly ``top_k / world`` experts' worth of bytes per token whatever the routing,
+  and the partial sums ride the all-reduce that the whole-expert split needs anyway; the hidden state is replicated, so neither
+  split dispatches tokens.  Resident bytes are identical;
 * the KV and index caches are striped by position (``config/cache.py``);
 * lm_head is split by vocabulary rows; the embedding, router, q_a/kv_a and indexer tables are replicated.
 
@@ -29,9 +36,16 @@ class ParallelLayout:
     geometry: ModelGeometry
     world: int = 1
     rank: int = 0
+    expert_split: str = "whole"
 
     def __post_init__(self) -> None:
         g = self.geometry
+        if self.expert_split not in ("whole", "sliced"):
+            raise PlanValidationError("expert_split is 'whole' or 'sliced'")
+        if self.expert_split == "sliced" and g.num_routed_experts:
+            cols, block = g.moe_intermediate_size // max(self.world, 1), g.fp8_block_shape
+            if g.moe_intermediate_size % self.world or cols % block[0] or cols % block[1]:
+                raise PlanValidationError(f"sliced experts need moe_intermediate_size / world = {cols} to be a multiple of the FP8 block {block}")
         if not 0 <= self.rank < self.world:
             raise PlanValidationError("rank must lie in [0, world)")
         for name, value in (
@@ -61,6 +75,30 @@ class ParallelLayout:
         return range(self.rank * self.experts_local, (self.rank + 1) * self.experts_local)
 
     @property
+    def sliced(self) -> bool:
+        return self.expert_split == "sliced"
+
+    @property
+    def experts_resident(self) -> int:
+        """How many experts this GPU holds a part of: all of them when sliced, its own when whole."""
+        return self.geometry.num_routed_experts if self.sliced else self.experts_local
+
+    @property
+    def expert_base(self) -> int:
+        """Global id of the first expert this GPU holds."""
+        return 0 if self.sliced else self.rank * self.experts_local
+
+    @property
+    def moe_cols_local(self) -> int:
+        """Intermediate columns of a routed expert that this GPU holds."""
+        return self.geometry.moe_intermediate_size // self.world if self.sliced else self.geometry.moe_intermediate_size
+
+    @property
+    def moe_col_range(self) -> range:
+        c = self.moe_cols_local
+        return range(self.rank * c, (self.rank + 1) * c) if self.sliced else range(0, c)
+
+    @property
     def dense_cols_local(self) -> int:
         return self.geometry.dense_intermediate_size // self.world
 
@@ -87,7 +125,11 @@ class ParallelLayout:
             "indexer_q": "replicated",
             "dense_mlp": f"by column: {self.dense_cols_local} per GPU; down partials all-reduced",
             "shared_expert": f"by column: {self.shared_cols_local} per GPU; summed with the routed partials in one all-reduce",
-            "routed_experts": f"whole experts: {self.experts_local} of {self.geometry.num_routed_experts} per GPU (FP8 resident); route sums all-reduced",
+            "routed_experts": (
+                f"sliced by column: {self.moe_cols_local} of {self.geometry.moe_intermediate_size} columns of every expert per GPU (FP8 resident); partial route sums all-reduced"
+                if self.sliced
+                else f"whole experts: {self.experts_local} of {self.geometry.num_routed_experts} per GPU (FP8 resident); route sums all-reduced"
+            ),
             "router": "replicated",
             "lm_head": f"by vocabulary row: {self.vocab_local} per GPU; packed (logit, id) candidates exchanged",
             "kv_cache,index_cache": "replicated, or striped by position in 64-row stripes (runner choice)",
@@ -110,6 +152,8 @@ class ParallelLayout:
             "hidden": "replicated",
             "heads_local": self.heads_local,
             "experts_local": self.experts_local,
+            "expert_split": self.expert_split,
+            "moe_cols_local": self.moe_cols_local,
             "dense_cols_local": self.dense_cols_local,
             "shared_cols_local": self.shared_cols_local,
             "vocab_local": self.vocab_local,

@@ -18,6 +18,7 @@
 // shapes these kernels do not take.  Replaces reference `glm_tpu/kernels/fp8_grouped_matmul/kernel.py:51-191` (decode).
 #include "common.cuh"
 #include "moe_mma_core.cuh"
+#include "peer.cuh"
 
 #define MM_WARPS 8
 #define MM_THREADS (32 * MM_WARPS)
@@ -119,6 +120,86 @@ moe_down_fp8_mma_kernel(const bf16* __restrict__ act, const float* __restrict__ 
             dw[(int64_t)p * H + n0 + n] = __float2bfloat16_rn(bf16_round(s) * bf16_round(route_weight[p]));
         }
     }
+}
+
+// Experts sliced by intermediate column (every GPU holds I columns of EVERY expert): the down projection of all routes of a
+// row, the route sum, the shared expert's partial and the all-reduce over the GPUs in one kernel.  A route's whole K (= this GPU's
+// I columns, a few hundred) fits one warp, so warp w takes route w of the row and nothing is reduced across warps but the route
+// sum itself.  A CTA owns 16 output columns of up to GLMB_MAX_ROWS rows: the same slices, the same route order and the same
+// roundings as `moe_down_fp8_mma_kernel` followed by `moe_combine_kernel` (gemv.cu) in one launch instead of two (the fp32 sum
+// over K runs inside one warp's accumulator instead of across eight warps, so a value may land on the neighbouring bf16).
+//   dw[p][n] = bf16( bf16(act[p] . wd[e_p][n]) * bf16(route_weight[p]) );  routed = sum_p dw[p][n] (fp32, route order)
+//   out[r][n] = bf16( bf16(bf16(allreduce(routed)) * scale) + bf16(allreduce(shared_partial[r][n])) )
+// I % 64 == 0, H % 16 == 0, top_k <= MM_WARPS.
+__global__ void __launch_bounds__(MM_THREADS)
+moe_down_combine_kernel(const bf16* __restrict__ act, const float* __restrict__ route_weight, const int* __restrict__ topk_ids,
+                        const uint8_t* __restrict__ wd, const float* __restrict__ sd, int experts, int I, int H, int rows_total, int top_k,
+                        const float* __restrict__ shared_partial, float scale, bf16* __restrict__ out, PeerComm comm, int channel) {
+    GLMB_PDL_PROLOGUE();
+    __shared__ float red[GLMB_MAX_ROWS][MM_WARPS][MM_ROWS];
+    __shared__ float sh[2 * GLMB_MAX_ROWS * MM_ROWS];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int n0 = blockIdx.x * MM_ROWS;
+    const int r0 = blockIdx.y * GLMB_MAX_ROWS;
+    const int rows = min(GLMB_MAX_ROWS, rows_total - r0);
+    const int kb = (I + 127) >> 7, chunks = I >> 6;
+    const int64_t hi_off = (int64_t)8 * I;
+    for (int r = 0; r < rows; ++r) {
+        float lo_sum = 0.f, hi_sum = 0.f;
+        if (warp < top_k) {
+            const int p = (r0 + r) * top_k + warp;
+            const int e = topk_ids[p];
+            if (e >= 0 && e < experts) {
+                const bf16* xr = act + (int64_t)p * I;
+                const uint8_t* w_lo = wd + ((int64_t)e * H + n0 + g) * I;
+                const int64_t sofs = ((int64_t)e * ((H + 127) >> 7) + (n0 >> 7)) * kb;
+                float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+                for (int c = 0; c < chunks; ++c) {
+                    const int k = (c << 6) + t * 16;
+                    const uint4 lo = ld_stream16(w_lo + k), hi = ld_stream16(w_lo + hi_off + k);
+                    uint4 x0 = make_uint4(0, 0, 0, 0), x1 = x0;
+                    if (g == 0) { x0 = ld_hot16(xr + k); x1 = ld_hot16(xr + k + 8); }  // the route is column 0 of the B operand
+                    chunk_mma(acc, lo, hi, sd[sofs + (c >> 1)], x0, x1);
+                }
+                // column 0 of the C fragment: lanes with t == 0 hold (row g) in acc[0] and (row g + 8) in acc[2]
+                const float wgt = bf16_round(route_weight[p]);
+                lo_sum = bf16_round(bf16_round(acc[0]) * wgt);
+                hi_sum = bf16_round(bf16_round(acc[2]) * wgt);
+            }
+        }
+        if (t == 0) { red[r][warp][g] = lo_sum; red[r][warp][g + 8] = hi_sum; }
+    }
+    __syncthreads();
+    const int per = rows * MM_ROWS;
+    for (int i = threadIdx.x; i < per; i += blockDim.x) {
+        const int r = i / MM_ROWS, c = i % MM_ROWS;
+        float routed = 0.f;
+#pragma unroll
+        for (int w = 0; w < MM_WARPS; ++w) routed += red[r][w][c];
+        sh[i] = shared_partial ? shared_partial[(int64_t)(r0 + r) * H + n0 + c] : 0.f;
+        sh[per + i] = routed;
+    }
+    __syncthreads();
+    cta_allreduce_f32(comm, channel, sh, 2 * per);
+    for (int i = threadIdx.x; i < per; i += blockDim.x) {
+        const int r = i / MM_ROWS, c = i % MM_ROWS;
+        out[(int64_t)(r0 + r) * H + n0 + c] = __float2bfloat16_rn(bf16_round(bf16_round(sh[per + i]) * scale) + bf16_round(sh[i]));
+    }
+}
+
+GLMB_API int glmb_moe_down_combine(const void* act, const float* route_weight, const int* topk_ids, const void* wd, const float* sd,
+                                   int experts, int I, int H, int rows, int top_k, const float* shared_partial, float scale, void* out,
+                                   const PeerComm* comm, int channel, void* stream) {
+    if (rows < 1 || top_k < 1 || top_k > MM_WARPS || (I & 63) || (H & 15)) return 1;
+    PeerComm c;
+    if (comm) c = *comm;
+    else { memset(&c, 0, sizeof(c)); c.world = 1; }
+    const dim3 grid(H / MM_ROWS, ceil_div(rows, GLMB_MAX_ROWS));
+    if (c.world > 1 && (int)(grid.x * grid.y) > GLMB_AR_MAX_CTAS) return 2;
+    GLMB_LAUNCH(moe_down_combine_kernel, grid, MM_THREADS, 0, (cudaStream_t)stream, (const bf16*)act, route_weight, topk_ids, (const uint8_t*)wd,
+                sd, experts, I, H, rows, top_k, shared_partial, scale, (bf16*)out, c, channel);
+    return (int)cudaGetLastError();
 }
 
 // ===================================================================================================

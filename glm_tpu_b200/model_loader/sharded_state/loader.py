@@ -45,6 +45,7 @@ def load_rank_checkpoint(target: Path, rank: int, world: int, *, pins: dict | No
     arrays = _read_all(target / fmt.SHARED_FILE)
     arrays.update(_read_all(target / fmt.expert_file(rank, world)))
     arrays["__experts_presliced__"] = torch.tensor([rank, world])
+    arrays["__expert_split__"] = report.get("expert_split", "whole")
     return arrays
 
 

@@ -164,6 +164,8 @@ class MegaDecoder:
         self.supported_code = int(lib.glmb_mega_supported(C.byref(a)))
         if model.world > 1 and not fused and not getattr(model, "emulated_shard", False):
             self.supported_code = self.supported_code or 100  # the library-collective baseline keeps the per-kernel path
+        if lay.sliced and lay.world > 1:
+            self.supported_code = self.supported_code or 101  # column-sliced experts exist in the per-kernel path only
         self.launches = 0
 
     # ------------------------------------------------------------------ per-phase timing

@@ -126,7 +126,7 @@ class Workspace:
         self.attn_v = bf(rows, hl * g.v_head_dim)
         self.attn_out = bf(rows, H)
         self.partial = f32(rows, H)
-        E, tk, I = g.num_routed_experts, g.routed_top_k, g.moe_intermediate_size
+        E, tk, I = g.num_routed_experts, g.routed_top_k, lay.moe_cols_local
         self.router_logits = f32(rows, E)
         self.topk_ids, self.topk_w = i32(rows, tk), f32(rows, tk)
         self.act = bf(rows * tk, I)
@@ -508,8 +508,10 @@ class GlmMoeDsaModel:
                     else:
                         ws.update[:rows] = self._allreduce_rows(self._mm(act, lw.dense_down, f32=True)).to(torch.bfloat16)
             return
-        tk, I, E = g.routed_top_k, g.moe_intermediate_size, g.num_routed_experts
-        el, ebase = lay.experts_local, self.rank * lay.experts_local
+        # whole experts: this GPU's `el` experts from `ebase`, full width; sliced: I columns of every expert
+        tk, I, E = g.routed_top_k, lay.moe_cols_local, g.num_routed_experts
+        el, ebase = lay.experts_resident, lay.expert_base
+        one_launch = decode and lay.sliced and (fused or self.world == 1 or self.emulated_shard) and tk <= 8 and I % 64 == 0 and H % 16 == 0
         forked = None
         if decode and self.side is not None:
             # the shared expert needs only the normalized hidden state: it runs on the side stream while the main stream
@@ -543,8 +545,9 @@ class GlmMoeDsaModel:
                 tile_expert, tile_routes, n_tiles, tiles, rt = self._route_tiles(ws.topk_ids[:rows], E)
             native.moe_gateup_fp8(x, tk, tile_expert, tile_routes, n_tiles, tiles, rt, lw.exp_gate_bits, lw.exp_up_bits,
                                   lw.exp_gate_scale, lw.exp_up_scale, ebase, ws.act)
-            native.moe_down_fp8(ws.act, ws.topk_w, tile_expert, tile_routes, n_tiles, tiles, rt, lw.exp_down_bits, lw.exp_down_scale,
-                                ebase, ws.dw)
+            if not one_launch:
+                native.moe_down_fp8(ws.act, ws.topk_w, tile_expert, tile_routes, n_tiles, tiles, rt, lw.exp_down_bits, lw.exp_down_scale,
+                                    ebase, ws.dw)
         if decode:
             if forked is not None:
                 self._join(forked)
@@ -555,7 +558,10 @@ class GlmMoeDsaModel:
         else:
             act = self._swiglu(self._mm(x, lw.shared_gate), self._mm(x, lw.shared_up))
             shared_partial = self._mm(act, lw.shared_down, f32=True)
-        if fused or self.world == 1 or self.emulated_shard:
+        if one_launch:
+            native.moe_down_combine(ws.act, ws.topk_w, ws.topk_ids, lw.exp_down_bits, lw.exp_down_scale, shared_partial, rows, tk,
+                                    g.routed_scaling_factor, ws.update, kc, native.CH_MLP)
+        elif fused or self.world == 1 or self.emulated_shard:
             native.moe_combine(ws.dw, ws.topk_ids, shared_partial, rows, tk, H, ebase, el, g.routed_scaling_factor, False, ws.update,
                                None, kc, native.CH_MLP)
         else:

@@ -10,7 +10,8 @@ block); bf16 tables are ``<prefix>.weight``.  Routed experts are *stacked* per l
 to bf16 with ``bf16(f32(e4m3) * scale_inv)`` and cut by the parallel layout (heads, MLP columns, vocabulary
 rows); small tables every GPU needs are replicated and several projections that consume the same activation are
 concatenated so that one streaming kernel serves them.  Routed experts stay FP8: each GPU keeps its
-``experts_local`` experts whole.
+``experts_local`` experts whole, or (``ParallelLayout.expert_split == "sliced"``) its slice of the intermediate columns of
+every expert, cut on FP8 block boundaries so that the block scales are cut with the bits.
 
 Parity: reference ``glm_tpu/models/glm_moe_dsa/weights.py:37-216`` (trees, specs, bf16 residency),
 ``:338-445`` (exact tensor names), ``glm_tpu/model_loader/placement.py:75-196`` (source shapes).
@@ -166,11 +167,11 @@ class LayerWeights:
     # MoE
     router_w: torch.Tensor | None = None  # [E, H] bf16
     router_bias: torch.Tensor | None = None  # [E] fp32
-    exp_gate_bits: torch.Tensor | None = None  # [E_local, I, H] uint8
+    exp_gate_bits: torch.Tensor | None = None  # [E_local, I, H] uint8 (whole experts) or [E, I / world, H] (sliced)
     exp_gate_scale: torch.Tensor | None = None
     exp_up_bits: torch.Tensor | None = None
     exp_up_scale: torch.Tensor | None = None
-    exp_down_bits: torch.Tensor | None = None  # [E_local, H, I]
+    exp_down_bits: torch.Tensor | None = None  # [E_local, H, I] or [E, H, I / world]
     exp_down_scale: torch.Tensor | None = None
     shared_gate: torch.Tensor | None = None  # [Is_local, H]
     shared_up: torch.Tensor | None = None
@@ -261,17 +262,19 @@ def shard_checkpoint(arrays: Mapping[str, torch.Tensor], layout: ParallelLayout,
             lw.dense_up = _decode(arrays, p + ".mlp.up_proj", g, dev, use_kernel)[r * c : (r + 1) * c].contiguous()
             lw.dense_down = _decode(arrays, p + ".mlp.down_proj", g, dev, use_kernel)[:, r * c : (r + 1) * c].contiguous()
         else:
-            el, c = layout.experts_local, layout.shared_cols_local
+            c = layout.shared_cols_local
             lw.router_w = to_dev(p + ".mlp.gate.weight", torch.bfloat16)
             lw.router_bias = to_dev(p + ".mlp.gate.e_score_correction_bias", torch.float32)
             for proj, attr in (("gate_proj", "exp_gate"), ("up_proj", "exp_up"), ("down_proj", "exp_down")):
                 prefix = f"{p}.mlp.experts.{proj}"
                 if prefix + ".weight_bits" not in arrays:
                     raise ValueError(f"{prefix} must be stored as FP8 (weight_bits + scale_inv)")
-                cut = slice(None) if presliced else slice(r * el, (r + 1) * el)
-                bits, scale = arrays[prefix + ".weight_bits"][cut], arrays[prefix + ".scale_inv"][cut]
-                if bits.shape[0] != el:
-                    raise ValueError(f"{prefix}: {bits.shape[0]} experts where this GPU holds {el}")
+                bits, scale = arrays[prefix + ".weight_bits"], arrays[prefix + ".scale_inv"]
+                if not presliced:
+                    bits, scale = cut_routed(bits, scale, proj, layout)
+                want = routed_shape(layout, proj)
+                if tuple(bits.shape) != want:
+                    raise ValueError(f"{prefix}: shape {tuple(bits.shape)} where this GPU holds {want}")
                 setattr(lw, attr + "_bits", bits.to(dev).contiguous())
                 setattr(lw, attr + "_scale", scale.to(dev, torch.float32).contiguous())
             lw.shared_gate = _decode(arrays, p + ".mlp.shared_experts.gate_proj", g, dev, use_kernel)[r * c : (r + 1) * c].contiguous()
@@ -289,6 +292,26 @@ def shard_checkpoint(arrays: Mapping[str, torch.Tensor], layout: ParallelLayout,
     )
     weights.count_bytes()
     return weights
+
+
+def routed_shape(layout: ParallelLayout, proj: str) -> tuple[int, int, int]:
+    """Shape of the resident FP8 table of one routed projection ('gate_proj', 'up_proj' or 'down_proj') on one GPU."""
+    g = layout.geometry
+    e, c, h = layout.experts_resident, layout.moe_cols_local, g.hidden_size
+    return (e, h, c) if proj == "down_proj" else (e, c, h)
+
+
+def cut_routed(bits: torch.Tensor, scale: torch.Tensor, proj: str, layout: ParallelLayout):
+    """One GPU's part of a stacked routed table ``[E, N, K]`` and of its block scales."""
+    r = layout.rank
+    if not layout.sliced:
+        el = layout.experts_local
+        return bits[r * el : (r + 1) * el], scale[r * el : (r + 1) * el]
+    c = layout.moe_cols_local
+    bn, bk = layout.geometry.fp8_block_shape
+    if proj == "down_proj":  # [E, H, I]: a slice of K
+        return bits[:, :, r * c : (r + 1) * c], scale[:, :, r * c // bk : (r + 1) * c // bk]
+    return bits[:, r * c : (r + 1) * c], scale[:, r * c // bn : (r + 1) * c // bn]
 
 
 def _seed_of(name: str, seed: int) -> int:
@@ -354,12 +377,12 @@ def random_device_weights(layout: ParallelLayout, device, seed: int = 0) -> Devi
             lw.dense_up = bf16(p + ".dense_up", (c, H), sharded=True)
             lw.dense_down = bf16(p + ".dense_down", (H, c), sharded=True)
         else:
-            el, c, I = layout.experts_local, layout.shared_cols_local, g.moe_intermediate_size
+            c = layout.shared_cols_local
             lw.router_w = bf16(p + ".router", (g.num_routed_experts, H))
             lw.router_bias = f32(p + ".router_bias", (g.num_routed_experts,), 0.0, 0.02)
-            lw.exp_gate_bits, lw.exp_gate_scale = fp8(p + ".exp_gate", (el, I, H))
-            lw.exp_up_bits, lw.exp_up_scale = fp8(p + ".exp_up", (el, I, H))
-            lw.exp_down_bits, lw.exp_down_scale = fp8(p + ".exp_down", (el, H, I))
+            lw.exp_gate_bits, lw.exp_gate_scale = fp8(p + ".exp_gate", routed_shape(layout, "gate_proj"))
+            lw.exp_up_bits, lw.exp_up_scale = fp8(p + ".exp_up", routed_shape(layout, "up_proj"))
+            lw.exp_down_bits, lw.exp_down_scale = fp8(p + ".exp_down", routed_shape(layout, "down_proj"))
             lw.shared_gate = bf16(p + ".shared_gate", (c, H), sharded=True)
             lw.shared_up = bf16(p + ".shared_up", (c, H), sharded=True)
             lw.shared_down = bf16(p + ".shared_down", (H, c), sharded=True)

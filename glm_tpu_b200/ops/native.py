@@ -250,6 +250,18 @@ def moe_down_fp8(act, route_weight, tile_expert, tile_routes, n_tiles, tiles, rt
     )
 
 
+def moe_down_combine(act, route_weight, topk_ids, wd, sd, shared_partial, rows, top_k, scale, out, comm=None, channel=CH_MLP):
+    """Column-sliced experts, decode: down projection of every route, route sum, shared partial and all-reduce in one launch
+    (``moe_down_combine_kernel``); the roundings of ``moe_down_fp8`` followed by ``moe_combine``."""
+    experts, H, I = wd.shape
+    _note_allreduce("moe_down_combine", comm, channel, (H // 16) * -(-rows // MAX_ROWS), 2 * min(rows, MAX_ROWS) * 16)
+    _check(
+        lib().glmb_moe_down_combine(_p(act), _p(route_weight), _p(topk_ids), _p(wd), _p(sd), experts, I, H, rows, top_k, _p(shared_partial),
+                                    f32(scale), _p(out), _comm(comm), channel, _stream()),
+        "moe_down_combine",
+    )
+
+
 def moe_grouped_fp8w(a_sorted, w0, w1, s0, s1, tiles, n_tiles, mode, out, *, perm=None, route_weight=None, status=None):
     """Grouped expert GEMM over expert-sorted routes with in-kernel FP8 decode (tcgen05); see ``glmb_moe_grouped_fp8w``.
 

@@ -15,6 +15,7 @@ Parity: reference ``glm_tpu/runner/tpu_runner.py:29-289`` (load phases, program 
 
 from __future__ import annotations
 
+import os
 import time
 from dataclasses import dataclass, field
 
@@ -332,12 +333,28 @@ class GpuModelRunner:
         self.peer.close()
 
 
-def build_runner(geometry, *, world: int = 1, rank: int = 0, device=None, checkpoint=None, seed: int = 0, **kwargs) -> GpuModelRunner:
+def default_expert_split(geometry, world: int) -> str:
+    """``GLM_B200_EXPERT_SPLIT`` if set; else column-sliced experts wherever the slices fall on FP8 block boundaries (a decode
+    token's routed bytes are then the same on every GPU whatever the routing), whole experts otherwise."""
+    chosen = os.environ.get("GLM_B200_EXPERT_SPLIT", "").strip().lower()
+    if chosen in ("whole", "sliced"):
+        return chosen
+    if world > 1 and geometry.num_routed_experts and geometry.moe_intermediate_size % world == 0:
+        cols, (bn, bk) = geometry.moe_intermediate_size // world, geometry.fp8_block_shape
+        if cols % bn == 0 and cols % bk == 0 and cols % 64 == 0:
+            return "sliced"
+    return "whole"
+
+
+def build_runner(geometry, *, world: int = 1, rank: int = 0, device=None, checkpoint=None, seed: int = 0, expert_split: str | None = None,
+                 **kwargs) -> GpuModelRunner:
     """Convenience constructor: shard ``checkpoint`` (a runtime-layout mapping) or random-init on the device."""
     from glm_tpu_b200.models.glm_moe_dsa.weights import random_device_weights, shard_checkpoint
 
     device = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
-    layout = ParallelLayout(geometry, world, rank)
+    if expert_split is None and checkpoint is not None and "__expert_split__" in checkpoint:
+        expert_split = checkpoint["__expert_split__"]  # a packed checkpoint was cut one way: the layout follows it
+    layout = ParallelLayout(geometry, world, rank, expert_split or default_expert_split(geometry, world))
     with torch.cuda.device(device):
         weights = shard_checkpoint(checkpoint, layout, device) if checkpoint is not None else random_device_weights(layout, device, seed)
     return GpuModelRunner(weights, **kwargs)

@@ -16,11 +16,14 @@ import torch  # noqa: E402
 import torch.distributed as dist  # noqa: E402
 
 
-def run(g, ckpt, prompt, new_tokens, capacity, stripe, comm, use_graphs, record, world, rank, device, lanes=1, kv_layout="striped"):
+def run(g, ckpt, prompt, new_tokens, capacity, stripe, comm, use_graphs, record, world, rank, device, lanes=1, kv_layout="striped",
+        expert_split=None):
     from glm_tpu_b200.runner.gpu_runner import build_runner
 
     runner = build_runner(g, world=world, rank=rank, device=device, checkpoint=ckpt, context_capacity=capacity, lanes=lanes,
-                          stripe=stripe, use_graphs=use_graphs, prefill_chunk=32, comm=comm, wait_limit=4_000_000, kv_layout=kv_layout)
+                          stripe=stripe, use_graphs=use_graphs, prefill_chunk=32, comm=comm, wait_limit=4_000_000, kv_layout=kv_layout,
+                          expert_split=expert_split)
+    split = runner.model.layout.expert_split
     decisions = {"selected": {i: [] for i in g.full_layers}, "experts": {i: [] for i in g.sparse_layers}}
     if record:
         inner = runner.model.run_rows
@@ -53,6 +56,7 @@ def run(g, ckpt, prompt, new_tokens, capacity, stripe, comm, use_graphs, record,
     runner.peer.check_status()
     kind = runner.report.programs[-1].kind
     runner.close()
+    run.last_split = split
     return out, decisions, kind
 
 
@@ -104,13 +108,25 @@ def main():
     from glm_tpu_b200.config.model import small_geometry
     from glm_tpu_b200.models.glm_moe_dsa.weights import random_checkpoint
 
-    g = small_geometry(4)
+    import dataclasses
+
+    # the routed experts' width grows with the GPU count so that a column slice stays a whole FP8 block at every world size
+    g = dataclasses.replace(small_geometry(4), moe_intermediate_size=128 * world)
     ckpt = random_checkpoint(g, seed=5)
     gen = torch.Generator().manual_seed(5)
     prompt = [torch.randint(0, g.vocab_size, (70,), generator=gen).tolist()]
-    result = {"world": world}
+    result = {"world": world, "moe_intermediate_size": g.moe_intermediate_size}
     fused, decisions, _ = run(g, ckpt, prompt, 10, 128, 16, "fused", False, True, world, rank, device)
     result["fused_eager"] = fused[0]
+    result["default_split"] = run.last_split
+    # the other split of the routed experts (whole experts per GPU), eager with recorded decisions and as a graph
+    other = "whole" if run.last_split == "sliced" else "sliced"
+    alt, alt_dec, _ = run(g, ckpt, prompt, 10, 128, 16, "fused", False, True, world, rank, device, expert_split=other)
+    result["other_split"], result["other_split_eager"] = other, alt[0]
+    result["other_split_decisions"] = {"selected": {str(k): v for k, v in alt_dec["selected"].items()},
+                                       "experts": {str(k): v for k, v in alt_dec["experts"].items()}}
+    alt_graph, _, _ = run(g, ckpt, prompt, 10, 128, 16, "fused", True, False, world, rank, device, expert_split=other)
+    result["other_split_graph"] = alt_graph[0]
     result["decisions"] = {"selected": {str(k): v for k, v in decisions["selected"].items()},
                            "experts": {str(k): v for k, v in decisions["experts"].items()}}
     graph, _, kind = run(g, ckpt, prompt, 10, 128, 16, "fused", True, False, world, rank, device)

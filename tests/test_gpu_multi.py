@@ -1,4 +1,4 @@
-"""Two-GPU model test: in-kernel peer-memory collectives vs the NCCL baseline vs the CPU oracle.
+"""Multi-GPU model test (2, 4 and 8 ranks, as many as the machine has): in-kernel peer-memory collectives vs the NCCL baseline vs the CPU oracle.
 
 The ranks run as child processes (torch.distributed.run, 127.0.0.1 rendezvous) with NVLS off; every device wait is
 bounded, so a protocol bug shows up as a status word, not as a hang.
@@ -21,10 +21,18 @@ pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
 ROOT = Path(__file__).resolve().parents[1]
 
 
+def _free_port() -> int:
+    import socket
+
+    with socket.socket() as sock:
+        sock.bind(("127.0.0.1", 0))
+        return sock.getsockname()[1]
+
+
 def _launch(world, out):
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=str(ROOT))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
-           "--master-port", "29533", str(ROOT / "tests" / "multi_gpu_worker.py"), "--out", str(out)]
+           "--master-port", str(_free_port()), str(ROOT / "tests" / "multi_gpu_worker.py"), "--out", str(out)]
     done = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert done.returncode == 0, done.stdout[-3000:] + done.stderr[-3000:]
     return json.loads(Path(out).read_text())
@@ -45,10 +53,15 @@ def _bad_tokens(g, ckpt, prompt, generated, capacity, decisions):
     return bad
 
 
-def test_two_gpu_fused_matches_oracle_and_nccl(native_lib, tmp_path):
-    world = 2
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_fused_exchanges_match_oracle_and_nccl(native_lib, tmp_path, world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    import dataclasses
+
     res = _launch(world, tmp_path / "out.json")
-    g = small_geometry(4)
+    g = dataclasses.replace(small_geometry(4), moe_intermediate_size=128 * world)
+    assert res["moe_intermediate_size"] == g.moe_intermediate_size
     ckpt = random_checkpoint(g, seed=5)
     assert res["all_ranks_agree"]
     assert res["fused_graph_kind"] == "cuda_graph"
@@ -57,6 +70,10 @@ def test_two_gpu_fused_matches_oracle_and_nccl(native_lib, tmp_path):
     assert not bad, bad
     # the baseline sums partials in another order, so compare it with the oracle under the same decisions
     assert not _bad_tokens(g, ckpt, res["prompt"], res["nccl"], 128, res["decisions"]) or res["nccl"] == res["fused_eager"]
+    # both splits of the routed experts (column slices of every expert / whole experts) give the oracle's tokens
+    assert {res["default_split"], res["other_split"]} == {"sliced", "whole"}
+    assert not _bad_tokens(g, ckpt, res["prompt"], res["other_split_eager"], 128, res["other_split_decisions"])
+    assert res["other_split_graph"] == res["other_split_eager"]
     assert len(res["two_lanes"]) == 2 and all(len(t) == 6 for t in res["two_lanes"])
     # the tcgen05 GEMM whose epilogue all-reduces over NVLink: bf16 rounding of the fp32 sum, clean status, three rounds
     for shape, record in res["gemm_allreduce"].items():

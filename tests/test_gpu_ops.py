@@ -152,6 +152,42 @@ def test_routed_experts(native_lib, rows, tiled, mma):
     assert ok, err
 
 
+@pytest.mark.parametrize("rows,tk", [(1, 8), (4, 8), (8, 2), (11, 8)])
+def test_down_combine_in_one_launch_equals_the_two_launches(native_lib, rows, tk):
+    """Column-sliced experts: the fused down + route sum + shared + (one-GPU) all-reduce kernel against ``moe_down_fp8`` followed by
+    ``moe_combine`` (same roundings; the fp32 sum over K runs in another order, so a value may land on the neighbouring bf16) and
+    against a plain fp32 computation."""
+    n = native_lib
+    torch.manual_seed(9)
+    E, I, H = 16, 256, 512
+    fx = _routed_fixture(E, I, H, 9)
+    d = {k: (v[0].to(DEV), v[1].to(DEV)) for k, v in fx.items()}
+    ids = torch.stack([torch.randperm(E)[:tk] for _ in range(rows)]).to(torch.int32).to(DEV)
+    wts = torch.rand(rows, tk)
+    wts = (wts / wts.sum(-1, keepdim=True)).to(DEV)
+    act = bf(torch.randn(rows * tk, I) * 0.3).to(DEV)
+    shared = torch.randn(rows, H).to(DEV)
+    dw = torch.zeros(rows * tk, H, dtype=torch.bfloat16, device=DEV)
+    two = torch.zeros(rows, H, dtype=torch.bfloat16, device=DEV)
+    one = torch.zeros(rows, H, dtype=torch.bfloat16, device=DEV)
+    n.moe_down_fp8(act, wts, ids, None, None, rows * tk, 1, d["down"][0], d["down"][1], 0, dw)
+    n.moe_combine(dw, ids, shared, rows, tk, H, 0, E, 2.5, False, two)
+    n.moe_down_combine(act, wts, ids, d["down"][0], d["down"][1], shared, rows, tk, 2.5, one)
+    torch.cuda.synchronize()
+    ok, err = close(one, two.float().cpu(), rtol=2**-7, atol=2e-3)
+    assert ok, err
+    assert (one != two).float().mean().item() < 0.25  # a near-tie at one of the sixteen bf16 roundings per value
+    deq = contract.dequantize_fp8(*fx["down"])
+    routed = torch.zeros(rows, H)
+    for r in range(rows):
+        for s_ in range(tk):
+            p = r * tk + s_
+            routed[r] += (act[p].float().cpu() @ deq[int(ids[r, s_])].float().T) * float(wts[r, s_])
+    ref = routed * 2.5 + shared.cpu()
+    ok, err = close(one, ref, rtol=2**-6, atol=4e-3)
+    assert ok, err
+
+
 def test_router_topk(native_lib):
     n = native_lib
     torch.manual_seed(6)
