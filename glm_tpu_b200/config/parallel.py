@@ -23,12 +23,26 @@ gone (hidden is replicated).
 
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 
 from glm_tpu_b200.config.model import ModelGeometry
 from glm_tpu_b200.exceptions import PlanValidationError
 
 RANK_AXIS = "gpu"
+
+
+def default_expert_split(geometry, world: int) -> str:
+    """``GLM_B200_EXPERT_SPLIT`` if set; else column-sliced experts wherever the slices fall on FP8 block boundaries (a decode
+    token's routed bytes are then the same on every GPU whatever the routing), whole experts otherwise."""
+    chosen = os.environ.get("GLM_B200_EXPERT_SPLIT", "").strip().lower()
+    if chosen in ("whole", "sliced"):
+        return chosen
+    if world > 1 and geometry.num_routed_experts and geometry.moe_intermediate_size % world == 0:
+        cols, (bn, bk) = geometry.moe_intermediate_size // world, geometry.fp8_block_shape
+        if cols % bn == 0 and cols % bk == 0 and cols % 64 == 0:
+            return "sliced"
+    return "whole"
 
 
 @dataclass(frozen=True)

@@ -1054,7 +1054,7 @@ __device__ MG_CALL void mg_absorb(const MegaArgs& a, const MegaLayer& lw, int la
         float(*red)[R][QA_COLS] = reinterpret_cast<float(*)[R][QA_COLS]>(big);
         float(*qs)[QA_MAX_NOPE] = reinterpret_cast<float(*)[QA_MAX_NOPE]>(big + sizeof(float) * 8 * R * QA_COLS);
         PeerComm single;
-        single.world = 1; single.rank = 0; single.wait_limit = 0; single.pad_ = 0; single.status = a.status; single.seq = nullptr;
+        single.world = 1; single.rank = 0; single.wait_limit = 0; single.protocol = 0; single.status = a.status; single.seq = nullptr;
         QAbsorbSource src;
         src.q_proj = a.q_proj; src.q_stride = a.q_stride; src.rope_table = a.rope_table; src.row_pos = a.positions; src.capacity = a.capacity;
         const int col_blocks = (a.L + QA_COLS - 1) / QA_COLS;

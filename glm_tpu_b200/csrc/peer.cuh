@@ -41,14 +41,17 @@
 #define GLMB_SEQ_DONE_BASE (GLMB_SEQ_SIG_BASE + GLMB_SIGNALS)
 #define GLMB_SEQ_GEMM (GLMB_SEQ_DONE_BASE + GLMB_SIGNALS)  // number of fused GEMM all-reduces completed
 #define GLMB_SEQ_WORDS (GLMB_SEQ_GEMM + 1)
-// Bytes at the start of the staging buffer reserved for the all-reduce channels.
-#define GLMB_AR_BYTES ((size_t)GLMB_AR_CHANNELS * GLMB_AR_MAX_CTAS * GLMB_MAX_WORLD * GLMB_AR_SLICE * 4)
+// Bytes at the start of the staging buffer reserved for the all-reduce channels: one (value, sequence number) pair per fp32 value.
+#define GLMB_AR_BYTES ((size_t)GLMB_AR_CHANNELS * GLMB_AR_MAX_CTAS * GLMB_MAX_WORLD * GLMB_AR_SLICE * 8)
+// How a CTA's all-reduce hands its values to the peers (PeerComm::protocol).
+#define GLMB_AR_FENCE_FLAG 0  // values, system fence, one flag per (CTA, source rank) with release; the reader acquires the flag
+#define GLMB_AR_PAIRS 1       // every value travels as an 8-byte (value, sequence number) pair: no fence, no separate flag
 
 struct PeerComm {
     int world;
     int rank;
     uint32_t wait_limit;            // iteration limit of every spin
-    uint32_t pad_;
+    uint32_t protocol;              // GLMB_AR_FENCE_FLAG or GLMB_AR_PAIRS: the same on every rank
     uint32_t* status;               // local status word
     uint32_t* seq;                  // local sequence numbers [GLMB_SEQ_WORDS]
     char* data[GLMB_MAX_WORLD];     // data[p]: rank p's staging buffer as mapped here
@@ -77,6 +80,15 @@ __device__ __forceinline__ uint4 ld_sys_u4(const void* p) {
     return v;
 }
 
+__device__ __forceinline__ void st_sys_u2(void* p, uint32_t a, uint32_t b) {
+    asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(a), "r"(b) : "memory");
+}
+__device__ __forceinline__ uint2 ld_sys_u2(const void* p) {
+    uint2 v;
+    asm volatile("ld.relaxed.sys.global.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+    return v;
+}
+
 // Spin until *p has reached `expect` (sequence numbers only grow).  Returns false when the limit ran out.
 __device__ __forceinline__ bool wait_flag_reached(const uint32_t* p, uint32_t expect, uint32_t limit) {
     for (uint32_t i = 0; i < limit; ++i) {
@@ -97,6 +109,38 @@ __device__ __forceinline__ void cta_allreduce_f32_slot(const PeerComm& c, int ch
     __syncthreads();
     const uint32_t e = s_epoch;
     const size_t mine = ((size_t)slot * GLMB_MAX_WORLD + c.rank) * GLMB_AR_SLICE;
+    if (c.protocol == GLMB_AR_PAIRS) {
+        // An aligned 8-byte store lands whole, so the sequence number beside a value says that the value is this round's: the
+        // sender neither fences nor raises a flag, and the reader polls the very words it is going to add.  One NVLink crossing
+        // instead of the fence's round trip plus the flag's crossing.
+        for (int i = threadIdx.x; i < count; i += blockDim.x) {
+            const uint32_t bits = __float_as_uint(sh[i]);
+            for (int p = 0; p < c.world; ++p)
+                if (p != c.rank) st_sys_u2(reinterpret_cast<uint2*>(c.data[p]) + mine + i, bits, e);
+        }
+        const uint2* inbox = reinterpret_cast<const uint2*>(c.data[c.rank]) + (size_t)slot * GLMB_MAX_WORLD * GLMB_AR_SLICE;
+        bool late = false;
+        for (int i = threadIdx.x; i < count; i += blockDim.x) {
+            float vals[GLMB_MAX_WORLD];
+            uint32_t pending = ((1u << c.world) - 1u) & ~(1u << c.rank);
+            for (uint32_t it = 0; pending && it < c.wait_limit; ++it) {
+                for (int p = 0; p < c.world; ++p) {
+                    if (!(pending >> p & 1u)) continue;
+                    const uint2 v = ld_sys_u2(inbox + (size_t)p * GLMB_AR_SLICE + i);
+                    if (v.y == e) { vals[p] = __uint_as_float(v.x); pending &= ~(1u << p); }
+                }
+                if (it > 128) __nanosleep(64);
+            }
+            if (pending) late = true;
+            float sum = 0.f;
+            for (int p = 0; p < c.world; ++p) sum += (p == c.rank) ? sh[i] : ((pending >> p & 1u) ? 0.f : vals[p]);
+            sh[i] = sum;
+        }
+        if (late) raise_status(c.status, GLMB_STATUS_WAIT_TIMEOUT);
+        if (threadIdx.x == 0) c.seq[slot] = e;
+        __syncthreads();
+        return;
+    }
     for (int p = 0; p < c.world; ++p) {
         if (p == c.rank) continue;
         float* dst = reinterpret_cast<float*>(c.data[p]) + mine;

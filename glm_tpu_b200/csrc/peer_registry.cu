@@ -80,11 +80,17 @@ GLMB_API int glmb_peer_import(PeerRegistry* r, int peer, const unsigned char* ha
     return 0;
 }
 
+// Which protocol the all-reduces of communicators handed out from now on use (GLMB_AR_*); every rank must choose the same.
+static int g_ar_protocol = GLMB_AR_PAIRS;
+GLMB_API void glmb_set_ar_protocol(int protocol) { g_ar_protocol = protocol == GLMB_AR_FENCE_FLAG ? GLMB_AR_FENCE_FLAG : GLMB_AR_PAIRS; }
+GLMB_API int glmb_get_ar_protocol(void) { return g_ar_protocol; }
+
 GLMB_API int glmb_peer_comm(PeerRegistry* r, uint32_t wait_limit, PeerComm* out) {
     memset(out, 0, sizeof(*out));
     out->world = r->world;
     out->rank = r->rank;
     out->wait_limit = wait_limit;
+    out->protocol = (uint32_t)g_ar_protocol;
     out->status = r->status;
     out->seq = r->seq;
     for (int p = 0; p < r->world; ++p) {

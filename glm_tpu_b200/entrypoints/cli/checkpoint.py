@@ -39,11 +39,13 @@ def main(args) -> int:
         from glm_tpu_b200.executor.pack_job import pack_checkpoint
 
         site = SiteConfig.load(getattr(args, "site", None))
-        report = pack_checkpoint(args.source, args.target, args.gpus, run_root=site.paths.run_root, layers=args.layers)
+        report = pack_checkpoint(args.source, args.target, args.gpus, run_root=site.paths.run_root, layers=args.layers,
+                                 expert_split=getattr(args, "expert_split", "auto"))
     else:
         from glm_tpu_b200.model_loader.sharded_state.verify import verify_runtime_checkpoint
 
         site = SiteConfig.load(getattr(args, "site", None))
         report = verify_runtime_checkpoint(args.target, pins={"manifest_sha256": site.manifest_sha256})
+        report.pop("manifest_files", None)  # the per-tensor records stay in manifest.json
     print(json.dumps(report, indent=2, sort_keys=True))
     return 0

@@ -129,6 +129,8 @@ def build_parser() -> argparse.ArgumentParser:
     pack.add_argument("target", type=Path)
     pack.add_argument("--gpus", type=int, default=8)
     pack.add_argument("--layers", type=int, default=0)
+    pack.add_argument("--expert-split", default="auto", choices=["auto", "whole", "sliced"],
+                      help="routed experts per GPU: whole experts, or a column slice of every expert (auto: sliced where the FP8 blocks allow)")
     ver = cks.add_parser("verify", help="re-hash a packed checkpoint against its manifest and seal")
     ver.add_argument("target", type=Path)
     ck.set_defaults(fn=_checkpoint)

@@ -24,13 +24,17 @@ from glm_tpu_b200.model_loader.sharded_state import seal, verify
 
 
 def pack_checkpoint(source: Path, target: Path, world: int, *, run_root: Path | None = None, layers: int = 0, jobs: int = 0,
-                    require_marker: bool = True, timeout: float = 24 * 3600.0) -> dict:
+                    require_marker: bool = True, timeout: float = 24 * 3600.0, expert_split: str = "auto") -> dict:
     source, target = Path(source), Path(target)
     if (target / "SUCCESS").exists():
         raise CheckpointValidationError(f"{target} is already a sealed checkpoint")
     marker = source_marker.require_marker(source) if require_marker else None
     inv = source_inventory.read_source_inventory(source)
     geometry = pack_worker.source_geometry(source, layers)
+    if expert_split == "auto":  # the split the runner would choose for this geometry on this many GPUs
+        from glm_tpu_b200.config.parallel import default_expert_split
+
+        expert_split = default_expert_split(geometry, world)
     target.mkdir(parents=True, exist_ok=True, mode=0o700)
     files = ["shared"] + [str(r) for r in range(world)]
     jobs = max(1, min(jobs or len(files), len(files)))
@@ -40,7 +44,7 @@ def pack_checkpoint(source: Path, target: Path, world: int, *, run_root: Path | 
 
     def body() -> dict:
         if jobs == 1:
-            receipts = [pack_worker.run(source, target, world, files, inv.sha256, layers)]
+            receipts = [pack_worker.run(source, target, world, files, inv.sha256, layers, expert_split)]
         else:
             procs = []
             for j in range(jobs):
@@ -48,7 +52,7 @@ def pack_checkpoint(source: Path, target: Path, world: int, *, run_root: Path | 
                 receipt = receipts_dir / f"receipt.{j}.json"
                 argv = [sys.executable, "-m", "glm_tpu_b200.model_loader.pack_worker", "--source", str(source), "--target", str(target),
                         "--world", str(world), "--files", ",".join(mine), "--inventory-sha256", inv.sha256, "--receipt", str(receipt),
-                        "--layers", str(layers)]
+                        "--layers", str(layers), "--expert-split", expert_split]
                 log = (receipts_dir / f"worker.{j}.log").open("wb")
                 procs.append((subprocess.Popen(argv, stdout=log, stderr=subprocess.STDOUT, stdin=subprocess.DEVNULL), receipt, log))
             failed = []
@@ -65,10 +69,10 @@ def pack_checkpoint(source: Path, target: Path, world: int, *, run_root: Path | 
             if failed:
                 raise CheckpointValidationError(f"pack workers failed: {failed}; see {receipts_dir}")
             receipts = [json.loads(r.read_text()) for _, r, _ in procs]
-        man = manifest_mod.assemble_manifest(receipts, geometry, world, inv.sha256)
+        man = manifest_mod.assemble_manifest(receipts, geometry, world, inv.sha256, expert_split)
         sealed = seal.install(target, geometry, man)
         report = verify.verify_runtime_checkpoint(target)
-        return {"ok": True, "target": str(target), "world": world, "files": report["files"], "total_bytes": man["total_bytes"],
+        return {"ok": True, "target": str(target), "world": world, "expert_split": expert_split, "files": report["files"], "total_bytes": man["total_bytes"],
                 "manifest_sha256": sealed["manifest_sha256"], "geometry_sha256": geometry.geometry_hash,
                 "source_inventory_sha256": inv.sha256, "source_marker": bool(marker), "seconds": round(time.time() - started, 3)}
 

@@ -3,8 +3,10 @@
 Source names are the Hugging Face ones (``...experts.{e}.gate_proj.weight`` + ``.weight_scale_inv`` per expert,
 ``...q_a_proj.weight`` + ``.weight_scale_inv``, bf16 norms/router/indexer tables).  Packed (runtime) names are the ones
 of ``models/glm_moe_dsa/weights.py``: FP8 pairs become ``<prefix>.weight_bits`` / ``<prefix>.scale_inv``, routed experts
-are stacked per layer and cut by expert-parallel rank, everything else goes to the shared file whole (each GPU decodes
-and slices it at load).  ``require_source_contract`` binds every source role to the exact dtype and shape the geometry
+are stacked per layer and cut per GPU -- whole experts (``split="whole"``: expert ``e`` goes to GPU ``e // experts_local``) or
+a column slice of every expert (``split="sliced"``: GPU ``r`` gets rows ``[r c, (r + 1) c)`` of every gate/up table and the same
+columns of every down table, with the block scales cut alongside) -- everything else goes to the shared file whole (each GPU
+decodes and slices it at load).  ``require_source_contract`` binds every source role to the exact dtype and shape the geometry
 implies; tensors of layers beyond ``num_layers`` (a truncation, the unused multi-token-prediction layer) are skipped.
 
 Parity: reference ``glm_tpu/model_loader/placement.py:24-39,75-196,416-570``.
@@ -28,10 +30,24 @@ class Placement:
     source: str
     target: str  # packed tensor name
     file: str  # "shared" or "experts"
-    rank: int | None  # owning GPU for expert tensors
+    rank: int | None  # owning GPU for expert tensors (None: shared file, or every GPU takes a slice)
     expert_slot: int | None  # index inside the stacked per-rank tensor
     dtype: str
-    shape: tuple
+    shape: tuple  # of the source tensor
+    axis: int | None = None  # sliced experts: the axis of the source tensor that is cut over the GPUs ...
+    unit: int = 0  # ... and how many entries of it each GPU takes
+
+    def piece_shape(self) -> tuple:
+        """Shape of what one GPU stores of this source tensor."""
+        if self.axis is None:
+            return tuple(self.shape)
+        return tuple(self.unit if a == self.axis else d for a, d in enumerate(self.shape))
+
+    def cut(self, tensor, rank: int):
+        """One GPU's part of the source tensor."""
+        if self.axis is None:
+            return tensor
+        return tensor.narrow(self.axis, rank * self.unit, self.unit)
 
 
 def _blocks(shape, block):
@@ -70,11 +86,22 @@ def require_source_contract(name: str, dtype: str, shape: tuple, g: ModelGeometr
     return True
 
 
-def placements(g: ModelGeometry, world: int) -> list[Placement]:
-    """The full plan, in a fixed order."""
+def _check_split(g: ModelGeometry, world: int, split: str) -> None:
+    if split not in ("whole", "sliced"):
+        raise PlanValidationError("split is 'whole' or 'sliced'")
     if g.num_routed_experts % world:
         raise PlanValidationError("experts do not divide over the GPUs")
+    if split == "sliced":
+        cols, (bn, bk) = g.moe_intermediate_size // world, g.fp8_block_shape
+        if g.moe_intermediate_size % world or cols % bn or cols % bk:
+            raise PlanValidationError(f"sliced experts need moe_intermediate_size / world = {cols} to be a multiple of the FP8 block")
+
+
+def placements(g: ModelGeometry, world: int, split: str = "whole") -> list[Placement]:
+    """The full plan, in a fixed order."""
+    _check_split(g, world, split)
     per = g.num_routed_experts // world
+    cols, (bn, bk) = g.moe_intermediate_size // world, g.fp8_block_shape
     plan = []
     for name, (dtype, shape) in expected_sources(g).items():
         m = _ROUTED.fullmatch(name)
@@ -82,7 +109,12 @@ def placements(g: ModelGeometry, world: int) -> list[Placement]:
             stem, _, expert, proj, role = m.groups()
             e = int(expert)
             suffix = "weight_bits" if role == "weight" else "scale_inv"
-            plan.append(Placement(name, f"{stem}.{proj}.{suffix}", "experts", e // per, e % per, dtype, shape))
+            if split == "whole":
+                plan.append(Placement(name, f"{stem}.{proj}.{suffix}", "experts", e // per, e % per, dtype, shape))
+            else:  # gate/up [I, H]: rows; down [H, I]: columns; scales in blocks
+                axis = 1 if proj == "down_proj" else 0
+                unit = cols if role == "weight" else cols // (bk if axis == 1 else bn)
+                plan.append(Placement(name, f"{stem}.{proj}.{suffix}", "experts", None, e, dtype, shape, axis, unit))
         elif name.endswith(".weight_scale_inv"):
             plan.append(Placement(name, name[: -len(".weight_scale_inv")] + ".scale_inv", "shared", None, None, dtype, shape))
         elif dtype == "F8_E4M3":
@@ -92,13 +124,13 @@ def placements(g: ModelGeometry, world: int) -> list[Placement]:
     return plan
 
 
-def packed_tensor_shapes(g: ModelGeometry, world: int, rank: int | None) -> dict:
+def packed_tensor_shapes(g: ModelGeometry, world: int, rank: int | None, split: str = "whole") -> dict:
     """Names, dtypes and shapes a packed file must hold (``rank=None``: the shared file)."""
-    per = g.num_routed_experts // world
+    stacked = g.num_routed_experts if split == "sliced" else g.num_routed_experts // world
     out = {}
-    for p in placements(g, world):
+    for p in placements(g, world, split):
         if rank is None and p.file == "shared":
             out[p.target] = (p.dtype, p.shape)
-        elif rank is not None and p.file == "experts" and p.rank == rank:
-            out[p.target] = (p.dtype, (per, *p.shape))
+        elif rank is not None and p.file == "experts" and p.rank in (None, rank):
+            out[p.target] = (p.dtype, (stacked, *p.piece_shape()))
     return out

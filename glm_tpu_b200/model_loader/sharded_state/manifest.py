@@ -13,7 +13,7 @@ def expected_files(world: int) -> list[str]:
     return [fmt.SHARED_FILE] + [fmt.expert_file(r, world) for r in range(world)]
 
 
-def assemble_manifest(receipts: list[dict], geometry, world: int, source_inventory_sha256: str) -> dict:
+def assemble_manifest(receipts: list[dict], geometry, world: int, source_inventory_sha256: str, expert_split: str = "whole") -> dict:
     files: dict = {}
     for receipt in receipts:
         for name, record in receipt.items():
@@ -23,6 +23,6 @@ def assemble_manifest(receipts: list[dict], geometry, world: int, source_invento
     want = expected_files(world)
     if sorted(files) != sorted(want):
         raise CheckpointValidationError(f"receipts cover {sorted(files)}, the checkpoint needs {sorted(want)}")
-    return {"schema": "glm_b200_manifest_v1", "format": fmt.FORMAT_VERSION, "geometry_sha256": geometry.geometry_hash,
-            "world": world, "source_inventory_sha256": source_inventory_sha256, "files": {n: files[n] for n in sorted(files)},
+    return {"schema": "glm_b200_manifest_v2", "format": fmt.FORMAT_VERSION, "geometry_sha256": geometry.geometry_hash,
+            "world": world, "expert_split": expert_split, "source_inventory_sha256": source_inventory_sha256, "files": {n: files[n] for n in sorted(files)},
             "total_bytes": sum(r["size"] for r in files.values())}

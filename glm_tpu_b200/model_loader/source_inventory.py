@@ -86,14 +86,47 @@ def authenticated_inventory(root: Path, expected_sha256: str) -> SourceInventory
     return inv
 
 
-def read_source_tensor(inv: SourceInventory, name: str):
+def read_source_pieces(inv: SourceInventory, name: str, piece_bytes: int | None = None, rows: tuple | None = None):
+    """The source tensor ``name`` (or its rows ``[rows[0], rows[1])``) as a sequence of flat CPU tensors of at most
+    ``piece_bytes`` bytes each (whole elements), front to back: a large table passes through without ever being whole in memory."""
+    import os
+
     import torch
 
     t = inv.tensors[name]
-    dtype = fmt.DTYPES[t.dtype][0]
-    with (inv.root / t.shard).open("rb") as f:
-        f.seek(t.begin)
-        raw = f.read(t.end - t.begin)
-    if len(raw) != t.end - t.begin:
-        raise CheckpointValidationError(f"short read for {name!r}")
-    return torch.frombuffer(bytearray(raw), dtype=dtype).reshape(t.shape) if raw else torch.empty(t.shape, dtype=dtype)
+    dtype, item = fmt.DTYPES[t.dtype]
+    cap = piece_bytes or fmt.PIECE_BYTES
+    cap -= cap % item
+    first, last = t.begin, t.end
+    if rows is not None:
+        row_bytes = (t.end - t.begin) // max(t.shape[0], 1)
+        if not 0 <= rows[0] <= rows[1] <= t.shape[0]:
+            raise CheckpointValidationError(f"rows {rows} outside {name!r}")
+        first, last = t.begin + rows[0] * row_bytes, t.begin + rows[1] * row_bytes
+    fd = os.open(inv.root / t.shard, os.O_RDONLY)
+    try:
+        at = first
+        while at < last:
+            n = min(cap, last - at)
+            buf = bytearray(n)
+            view, got = memoryview(buf), 0
+            while got < n:
+                k = os.preadv(fd, [view[got:]], at + got)
+                if k <= 0:
+                    raise CheckpointValidationError(f"short read for {name!r}")
+                got += k
+            yield torch.frombuffer(buf, dtype=dtype)
+            at += n
+    finally:
+        os.close(fd)
+
+
+def read_source_tensor(inv: SourceInventory, name: str, rows: tuple | None = None):
+    """One whole source tensor, or a run of its rows (an expert's table, a scale table: tens of megabytes at most)."""
+    import torch
+
+    t = inv.tensors[name]
+    parts = list(read_source_pieces(inv, name, rows=rows))
+    flat = parts[0] if len(parts) == 1 else (torch.cat(parts) if parts else torch.empty(0, dtype=fmt.DTYPES[t.dtype][0]))
+    shape = t.shape if rows is None else (rows[1] - rows[0], *t.shape[1:])
+    return flat.reshape(shape)

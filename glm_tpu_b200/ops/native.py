@@ -30,7 +30,7 @@ class PeerComm(C.Structure):
         ("world", C.c_int),
         ("rank", C.c_int),
         ("wait_limit", C.c_uint32),
-        ("pad_", C.c_uint32),
+        ("protocol", C.c_uint32),
         ("status", C.c_void_p),
         ("seq", C.c_void_p),
         ("data", C.c_void_p * MAX_WORLD),
@@ -89,6 +89,8 @@ def lib() -> C.CDLL:
 
         if os.environ.get("GLM_B200_PDL", "1") == "0":  # programmatic dependent launch off: plain stream order
             _lib.glmb_set_pdl(0)
+        if os.environ.get("GLM_B200_AR", "pairs") == "flags":  # all-reduce with fence + flag instead of (value, sequence) pairs
+            _lib.glmb_set_ar_protocol(0)
     return _lib if _timeline is None else _TimedLib(_lib)
 
 

@@ -22,7 +22,7 @@ from dataclasses import dataclass, field
 import torch
 
 from glm_tpu_b200.config.cache import CacheConfig
-from glm_tpu_b200.config.parallel import ParallelLayout
+from glm_tpu_b200.config.parallel import ParallelLayout, default_expert_split
 from glm_tpu_b200.models.glm_moe_dsa.model import RING, DecoderState, GlmMoeDsaModel, Workspace
 from glm_tpu_b200.models.glm_moe_dsa.weights import DeviceWeights
 from glm_tpu_b200.ops import native
@@ -331,19 +331,6 @@ class GpuModelRunner:
             torch.cuda.synchronize(self.device)
             self.peer.check_canaries()  # a kernel (of any rank) that overran a staging region wrote into its guard band
         self.peer.close()
-
-
-def default_expert_split(geometry, world: int) -> str:
-    """``GLM_B200_EXPERT_SPLIT`` if set; else column-sliced experts wherever the slices fall on FP8 block boundaries (a decode
-    token's routed bytes are then the same on every GPU whatever the routing), whole experts otherwise."""
-    chosen = os.environ.get("GLM_B200_EXPERT_SPLIT", "").strip().lower()
-    if chosen in ("whole", "sliced"):
-        return chosen
-    if world > 1 and geometry.num_routed_experts and geometry.moe_intermediate_size % world == 0:
-        cols, (bn, bk) = geometry.moe_intermediate_size // world, geometry.fp8_block_shape
-        if cols % bn == 0 and cols % bk == 0 and cols % 64 == 0:
-            return "sliced"
-    return "whole"
 
 
 def build_runner(geometry, *, world: int = 1, rank: int = 0, device=None, checkpoint=None, seed: int = 0, expert_split: str | None = None,

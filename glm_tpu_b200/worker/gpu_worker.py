@@ -255,7 +255,7 @@ class Worker:
                 from glm_tpu_b200.model_loader.sharded_state import loader
 
                 # the site's pins travel with the load: another packed checkpoint than the pinned one is refused here
-                checkpoint = loader.load_rank_checkpoint(path, self.rank, self.world, pins=self.launch["pins"])
+                checkpoint = loader.load_rank_checkpoint(path, self.rank, self.world, pins=self.launch["pins"], device=device)
                 self.record["checkpoint_pins"] = {k: v for k, v in (self.launch["pins"] or {}).items() if v}
             elif geometry.num_layers <= 8 and geometry.hidden_size <= 1024:
                 from glm_tpu_b200.models.glm_moe_dsa.weights import random_checkpoint
@@ -273,7 +273,8 @@ class Worker:
         self.record["geometry_hash"] = geometry.geometry_hash
         from glm_tpu_b200.config.parallel import ParallelLayout
 
-        layout_hash = ParallelLayout(geometry, self.world, self.rank).layout_hash  # which tensor is split how: must agree on every rank
+        model = getattr(runner, "model", None)  # which tensor is split how: must agree on every rank
+        layout_hash = (model.layout if model is not None else ParallelLayout(geometry, self.world, self.rank)).layout_hash
         self.record["layout_hash"] = layout_hash
         self.vote.all(self.digest_consensus(layout_hash), "layout_agreed")
         self.record["context_capacity"] = capacity

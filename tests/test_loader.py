@@ -49,6 +49,102 @@ def test_header_bounds(tmp_path):
         fmt.read_header(p)
 
 
+def _raw_file(path, header: dict, payload: bytes):
+    import struct
+
+    raw = json.dumps(header).encode()
+    path.write_bytes(struct.pack("<Q", len(raw)) + raw + payload)
+    return path
+
+
+def test_header_ranges_must_tile_the_payload(tmp_path):
+    ok = {"a": {"dtype": "U8", "shape": [4], "data_offsets": [0, 4]}, "b": {"dtype": "U8", "shape": [4], "data_offsets": [4, 8]}}
+    fmt.read_header(_raw_file(tmp_path / "ok.safetensors", ok, b"\0" * 8))
+    gap = {"a": ok["a"], "b": {"dtype": "U8", "shape": [4], "data_offsets": [6, 10]}}
+    with pytest.raises(CheckpointValidationError, match="gap"):
+        fmt.read_header(_raw_file(tmp_path / "gap.safetensors", gap, b"\0" * 10))
+    overlap = {"a": ok["a"], "b": {"dtype": "U8", "shape": [4], "data_offsets": [2, 6]}}
+    with pytest.raises(CheckpointValidationError, match="overlapping"):
+        fmt.read_header(_raw_file(tmp_path / "overlap.safetensors", overlap, b"\0" * 6))
+    with pytest.raises(CheckpointValidationError, match="follow the last tensor"):
+        fmt.read_header(_raw_file(tmp_path / "tail.safetensors", ok, b"\0" * 9))
+
+
+def test_writer_fills_tensors_piece_by_piece_and_refuses_holes(tmp_path, monkeypatch):
+    monkeypatch.setattr(fmt, "PIECE_BYTES", 64)
+    specs = {"w": ("F8_E4M3", (4, 100)), "s": ("F32", (10,))}
+    w = fmt.FileWriter(tmp_path / "f.safetensors", specs, {"k": "v"})
+    bits = (torch.arange(400) % 100).to(torch.uint8).reshape(4, 100)
+    for row in bits:  # one "expert" at a time, never stacked
+        w.append("w", row)
+    with pytest.raises(CheckpointValidationError, match="not written completely"):
+        w.close()
+    assert not (tmp_path / "f.safetensors").exists()
+    w.abort()
+    w = fmt.FileWriter(tmp_path / "f.safetensors", specs, {"k": "v"})
+    for row in bits:
+        w.append("w", row)
+    w.append("s", torch.arange(10, dtype=torch.float32))
+    receipt = w.close()
+    whole = fmt.write_file(tmp_path / "g.safetensors", {"w": bits, "s": torch.arange(10, dtype=torch.float32)}, {"k": "v"}, {"w"})
+    assert receipt == whole and (tmp_path / "f.safetensors").read_bytes() == (tmp_path / "g.safetensors").read_bytes()
+    reader = fmt.TensorReader(tmp_path / "f.safetensors")
+    assert torch.equal(reader.read("w", expect_sha256=receipt["tensors"]["w"]["sha256"]), bits)
+    assert reader.largest_piece <= 64 and reader.bytes_read == 400
+    with pytest.raises(CheckpointValidationError, match="content digest"):
+        reader.read("s", expect_sha256="0" * 64)
+    nan = fmt.FileWriter(tmp_path / "n.safetensors", {"s": ("F32", (2,))}, {})
+    with pytest.raises(CheckpointValidationError, match="non-finite"):
+        nan.append("s", torch.tensor([1.0, float("inf")]))
+    nan.abort()
+
+
+def test_rank_load_streams_every_byte_once_in_bounded_pieces(packed, monkeypatch):
+    g, arrays, root, _ = packed
+    monkeypatch.setattr(fmt, "PIECE_BYTES", 4096)
+    streamed = loader.load_rank_checkpoint(root / "packed", 0, 2)
+    assert streamed.io_stats() == {"bytes_read": 0, "largest_piece": 0}  # nothing is read before a tensor is asked for
+    shard_checkpoint(streamed, ParallelLayout(g, world=2, rank=0, expert_split=streamed["__expert_split__"]), "cpu", use_kernel=False)
+    payload = 0
+    for name in (fmt.SHARED_FILE, fmt.expert_file(0, 2)):
+        header, start = fmt.read_header(root / "packed" / name)
+        payload += (root / "packed" / name).stat().st_size - start
+    stats = streamed.io_stats()
+    assert stats["bytes_read"] == payload and 0 < stats["largest_piece"] <= 4096
+
+
+def test_sliced_experts_pack_and_load(tmp_path):
+    import dataclasses
+
+    g = dataclasses.replace(tiny_geometry(), moe_intermediate_size=256)
+    arrays = random_checkpoint(g, seed=4)
+    export.export_source(arrays, g, tmp_path / "src", shards=2)
+    source_marker.mark_source(tmp_path / "src")
+    report = pack_checkpoint(tmp_path / "src", tmp_path / "sliced", 2, jobs=2, expert_split="sliced")
+    assert report["expert_split"] == "sliced" and verify.verify_runtime_checkpoint(tmp_path / "sliced")["expert_split"] == "sliced"
+    whole = pack_checkpoint(tmp_path / "src", tmp_path / "whole", 2, jobs=1, expert_split="whole")
+    assert whole["manifest_sha256"] != report["manifest_sha256"] and abs(whole["total_bytes"] - report["total_bytes"]) < 4096  # the same payload; the headers differ in a few digits
+    full = loader.load_full_checkpoint(tmp_path / "sliced")
+    assert set(full) == set(arrays) and all(torch.equal(full[n], arrays[n]) for n in arrays)
+    for rank in range(2):
+        layout = ParallelLayout(g, world=2, rank=rank, expert_split="sliced")
+        want = shard_checkpoint(arrays, layout, "cpu", use_kernel=False)
+        loaded = loader.load_rank_checkpoint(tmp_path / "sliced", rank, 2)
+        assert loaded["__expert_split__"] == "sliced"
+        got = shard_checkpoint(loaded, layout, "cpu", use_kernel=False)
+        for lw, lg in zip(want.layers, got.layers):
+            for key, value in vars(lw).items():
+                if isinstance(value, torch.Tensor):
+                    assert torch.equal(getattr(lg, key), value), key
+        if lg.exp_down_bits is not None:
+            assert lg.exp_down_bits.shape == (g.num_routed_experts, g.hidden_size, 128)
+        # a checkpoint cut one way does not load into the other layout
+        with pytest.raises(ValueError, match="shape"):
+            shard_checkpoint(loaded, ParallelLayout(g, world=2, rank=rank, expert_split="whole"), "cpu", use_kernel=False)
+    with pytest.raises(PlanValidationError, match="FP8 block"):
+        pack_checkpoint(tmp_path / "src", tmp_path / "bad", 4, jobs=1, expert_split="sliced")
+
+
 def test_inventory_is_header_only_and_content_addressed(packed):
     g, arrays, root, _ = packed
     inv = source_inventory.read_source_inventory(root / "src")
@@ -83,7 +179,7 @@ def test_pack_verify_load_round_trip(packed):
 def test_rank_load_equals_sharding_the_full_checkpoint(packed):
     g, arrays, root, _ = packed
     for rank in range(2):
-        layout = ParallelLayout(g, world=2, rank=rank)
+        layout = ParallelLayout(g, world=2, rank=rank, expert_split=loader.load_rank_checkpoint(root / "packed", rank, 2)["__expert_split__"])
         want = shard_checkpoint(arrays, layout, "cpu", use_kernel=False)
         got = shard_checkpoint(loader.load_rank_checkpoint(root / "packed", rank, 2), layout, "cpu", use_kernel=False)
         assert torch.equal(got.lm_head, want.lm_head) and torch.equal(got.embed, want.embed)
@@ -112,7 +208,7 @@ def test_unmarked_or_changed_source_is_refused(packed, tmp_path):
     shard = sorted((tmp_path / "src2").glob("*.safetensors"))[0]
     with shard.open("ab") as f:
         f.write(b"\0" * 8)
-    with pytest.raises(CheckpointValidationError, match="changed"):
+    with pytest.raises(CheckpointValidationError, match="changed|follow the last tensor"):
         pack_checkpoint(tmp_path / "src2", tmp_path / "p", 2, jobs=1)
 
 
@@ -134,8 +230,13 @@ def test_tampering_is_detected(packed, tmp_path):
     with pytest.raises(CheckpointValidationError, match="digest"):
         verify.verify_runtime_checkpoint(bad)
     assert verify.verify_runtime_checkpoint(bad, files=[fmt.SHARED_FILE])["ok"]  # a worker checks only its own files
-    with pytest.raises(CheckpointValidationError):
-        loader.load_rank_checkpoint(bad, 1, 2)
+    with pytest.raises(CheckpointValidationError, match="digest"):
+        loader.load_rank_checkpoint(bad, 1, 2, rehash=True)
+    # without the whole-file pass the flipped byte is caught when its tensor streams in (the last tensor of the file here)
+    streamed = loader.load_rank_checkpoint(bad, 1, 2)
+    last = max(streamed._readers[fmt.expert_file(1, 2)].names(), key=lambda n: streamed._readers[fmt.expert_file(1, 2)].header[n]["data_offsets"][1])
+    with pytest.raises(CheckpointValidationError, match="content digest of"):
+        streamed[last]
     # a missing seal, an edited manifest, an edited seal
     bad = _copy(root / "packed", tmp_path / "noseal")
     os.remove(bad / fmt.SEAL_FILE)
