@@ -310,11 +310,12 @@ static int launch_partial(const void* q_full, const void* kv_cache, const int* s
     const int W = 8 * TPW * PVW + rd;
     const size_t smem = sparse_mla_tile_smem(W);
     if (smem > 200 * 1024) return 2;
-    static bool attr_set = false;
-    if (!attr_set) {
+    static DeviceOnce attr_set;
+    const int attr_set_dev = attr_set.pending();
+    if (attr_set_dev != DeviceOnce::SET) {
         cudaError_t e = cudaFuncSetAttribute(sparse_mla_partial_kernel<TPW, PVW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (e != cudaSuccess) return (int)e;
-        attr_set = true;
+        attr_set.mark(attr_set_dev);
     }
     dim3 grid(max_chunks, rows, (H + AT_HEADS - 1) / AT_HEADS);
     GLMB_LAUNCH((sparse_mla_partial_kernel<TPW, PVW>), grid, AT_THREADS, smem, stream, (const bf16*)q_full, (const bf16*)kv_cache, sel_local,
@@ -349,11 +350,12 @@ static int launch_rows(const void* q_full, const void* kv_cache, const int* sel_
     const int W = 8 * TPW * PVW + rd;
     const size_t smem = (size_t)(AT_HEADS + AT_CHUNK) * (W + 8) * 2 + (size_t)AT_HEADS * AT_PSTRIDE * 2 + 2 * AT_WARPS * AT_HEADS * 4;
     if (smem > 200 * 1024) return 2;
-    static bool attr_set = false;
-    if (!attr_set) {
+    static DeviceOnce attr_set;
+    const int attr_set_dev = attr_set.pending();
+    if (attr_set_dev != DeviceOnce::SET) {
         cudaError_t e = cudaFuncSetAttribute(sparse_mla_rows_kernel<TPW, PVW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (e != cudaSuccess) return (int)e;
-        attr_set = true;
+        attr_set.mark(attr_set_dev);
     }
     dim3 grid(rows, (H + AT_HEADS - 1) / AT_HEADS);
     GLMB_LAUNCH((sparse_mla_rows_kernel<TPW, PVW>), grid, AT_THREADS, smem, stream, (const bf16*)q_full, (const bf16*)kv_cache, sel_local, sel_counts,

@@ -7,6 +7,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #define GLMB_API extern "C" __attribute__((visibility("default")))
 
 typedef __nv_bfloat16 bf16;
@@ -122,3 +124,20 @@ static inline cudaError_t glmb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 #define GLMB_LAUNCH(kernel, grid, block, smem, stream, ...) (void)glmb_launch(kernel, dim3(grid), dim3(block), smem, stream, __VA_ARGS__)
+
+// A once-per-device latch for settings that belong to a device, not to the process (cudaFuncSetAttribute: the opt-in to large
+// dynamic shared memory has to be repeated on every GPU a process drives).  `pending()` names the current device if the setting
+// has not been made there yet, SET if it has; `mark(d)` records it.  Two threads racing on a device both make the (idempotent)
+// setting.
+struct DeviceOnce {
+    static constexpr int SET = -2, UNKNOWN = -1, MAX_DEVICES = 64;
+    std::atomic<bool> made[MAX_DEVICES] = {};
+    int pending() {
+        int dev = UNKNOWN;
+        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return UNKNOWN;  // make the setting every time
+        return made[dev].load(std::memory_order_acquire) ? SET : dev;
+    }
+    void mark(int dev) {
+        if (dev >= 0 && dev < MAX_DEVICES) made[dev].store(true, std::memory_order_release);
+    }
+};

@@ -483,13 +483,14 @@ GLMB_API int glmb_gemm_bf16_tcgen05(const void* a, int64_t lda, const void* b, i
     const bool persistent = g_gemm_variant == 2 || (g_gemm_variant == 0 && total2 >= 64);
     if (make_map(&map_a, a, (uint64_t)rows, (uint64_t)K, (uint64_t)lda)) return 3;
     if (make_map(&map_b, b, (uint64_t)experts * N, (uint64_t)K, (uint64_t)ldb, persistent ? T2_BN : TC_BN)) return 3;
-    static bool attr_set = false;
-    if (!attr_set) {
+    static DeviceOnce attr_set;
+    const int attr_set_dev = attr_set.pending();
+    if (attr_set_dev != DeviceOnce::SET) {
         cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES);
         if (e == cudaSuccess)
             e = cudaFuncSetAttribute(gemm_bf16_tcgen05_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T2_SMEM_BYTES);
         if (e != cudaSuccess) return (int)e;
-        attr_set = true;
+        attr_set.mark(attr_set_dev);
     }
     if (persistent) {
         GLMB_LAUNCH(gemm_bf16_tcgen05_persistent_kernel, dim3(total2 < sm_count ? total2 : sm_count), TC_THREADS, T2_SMEM_BYTES,
@@ -519,11 +520,12 @@ GLMB_API int glmb_gemm_bf16_tcgen05_allreduce(const void* a, int64_t lda, const 
     CUtensorMap map_a, map_b;
     if (make_map(&map_a, a, (uint64_t)rows, (uint64_t)K, (uint64_t)lda)) return 3;
     if (make_map(&map_b, b, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, T2_BN)) return 3;
-    static bool attr_set = false;
-    if (!attr_set) {
+    static DeviceOnce attr_set;
+    const int attr_set_dev = attr_set.pending();
+    if (attr_set_dev != DeviceOnce::SET) {
         cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tcgen05_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T2_SMEM_BYTES);
         if (e != cudaSuccess) return (int)e;
-        attr_set = true;
+        attr_set.mark(attr_set_dev);
     }
     int dev = 0, sm_count = 0;
     cudaGetDevice(&dev);

@@ -519,13 +519,14 @@ GLMB_API int glmb_topk_select(const float* scores, const int* row_pos, int rows,
     // rows of 30k scores).
     if (g_topk_cluster && rows <= TKC_MAX_ROWS && seg_bytes <= TK_SMEM_LIMIT) {
         // 8-CTA cluster per row (distributed shared memory): contexts up to 8 x 51,200 positions
-        static bool cluster_attr_set = false;
-        if (!cluster_attr_set) {
+        static DeviceOnce cluster_attr_set;
+        const int cluster_attr_set_dev = cluster_attr_set.pending();
+        if (cluster_attr_set_dev != DeviceOnce::SET) {
             cudaError_t e = cudaFuncSetAttribute(topk_select_cluster_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, TK_SMEM_LIMIT);
             if (e == cudaSuccess)
                 e = cudaFuncSetAttribute(topk_select_cluster_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, TK_SMEM_LIMIT);
             if (e != cudaSuccess) return (int)e;
-            cluster_attr_set = true;
+            cluster_attr_set.mark(cluster_attr_set_dev);
         }
         dim3 grid(TKC_CTAS, rows);
         if (pow2)
@@ -541,13 +542,14 @@ GLMB_API int glmb_topk_select(const float* scores, const int* row_pos, int rows,
     GLMB_LAUNCH((topk_select_kernel<S, P>), rows, TK_THREADS, BYTES, (cudaStream_t)stream, scores, row_pos, capacity, score_stride, top_k, \
                 stripe, world, rank, sel_global, sel_local, sel_counts, c, sig)
     if (smem <= TK_SMEM_LIMIT) {
-        static bool attr_set = false;
-        if (!attr_set) {
+        static DeviceOnce attr_set;
+        const int attr_set_dev = attr_set.pending();
+        if (attr_set_dev != DeviceOnce::SET) {
             cudaError_t e = cudaFuncSetAttribute(topk_select_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, TK_SMEM_LIMIT);
             if (e == cudaSuccess)
                 e = cudaFuncSetAttribute(topk_select_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, TK_SMEM_LIMIT);
             if (e != cudaSuccess) return (int)e;
-            attr_set = true;
+            attr_set.mark(attr_set_dev);
         }
         if (pow2) { TK_LAUNCH(true, true, smem); } else { TK_LAUNCH(true, false, smem); }
     } else {

@@ -282,11 +282,12 @@ GLMB_API int glmb_indexer_score_tc_rows(const float* q, int64_t q_stride, int64_
     CUtensorMap map_keys, map_q;
     if (make_map(&map_keys, index_cache, (uint64_t)cache_rows, (uint64_t)IR_D, (uint64_t)IR_D, IR_KEYS)) return 3;
     if (make_map(&map_q, pieces, (uint64_t)rows * IR_N, (uint64_t)IR_D, (uint64_t)IR_D, IR_N)) return 3;
-    static bool attr_set = false;
-    if (!attr_set) {
+    static DeviceOnce attr_set;
+    const int attr_set_dev = attr_set.pending();
+    if (attr_set_dev != DeviceOnce::SET) {
         cudaError_t e = cudaFuncSetAttribute(indexer_score_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, IR_SMEM_BYTES);
         if (e != cudaSuccess) return (int)e;
-        attr_set = true;
+        attr_set.mark(attr_set_dev);
     }
     IndexerQuerySource src;
     src.q = q; src.q_stride = q_stride; src.q_offset = q_offset; src.inv_freq = inv_freq; src.rd = rd;

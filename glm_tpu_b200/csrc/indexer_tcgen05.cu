@@ -201,11 +201,12 @@ static int indexer_tc_launch(const float* q_idx, const IndexerRawQuery& raw, con
     if (comm) c = *comm; else { memset(&c, 0, sizeof(c)); c.world = 1; }
     CUtensorMap map_keys;
     if (make_map(&map_keys, index_cache, (uint64_t)cache_rows, (uint64_t)IT_D, (uint64_t)IT_D, IT_KEYS)) return 3;
-    static bool attr_set = false;
-    if (!attr_set) {
+    static DeviceOnce attr_set;
+    const int attr_set_dev = attr_set.pending();
+    if (attr_set_dev != DeviceOnce::SET) {
         cudaError_t e = cudaFuncSetAttribute(indexer_score_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, IT_SMEM_BYTES);
         if (e != cudaSuccess) return (int)e;
-        attr_set = true;
+        attr_set.mark(attr_set_dev);
     }
     const int page = stripe * world;
     const int owned_max = (max_ctx / page) * stripe + min(max_ctx % page, stripe);

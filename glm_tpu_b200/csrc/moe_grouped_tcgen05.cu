@@ -263,11 +263,12 @@ GLMB_API int glmb_moe_grouped_fp8w(const void* a_sorted, int sorted_rows, const 
     if (make_map(&map_a, a_sorted, (uint64_t)sorted_rows, (uint64_t)K, (uint64_t)K, MG_BM)) return 3;
     if (make_map_u8(&map_w0, w0, (uint64_t)experts * N, (uint64_t)K, (uint64_t)K, 128)) return 3;
     if (make_map_u8(&map_w1, mode == 0 ? w1 : w0, (uint64_t)experts * N, (uint64_t)K, (uint64_t)K, 128)) return 3;
-    static bool attr_set = false;
-    if (!attr_set) {
+    static DeviceOnce attr_set;
+    const int attr_set_dev = attr_set.pending();
+    if (attr_set_dev != DeviceOnce::SET) {
         cudaError_t e = cudaFuncSetAttribute(moe_grouped_fp8w_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, MG_SMEM_BYTES);
         if (e != cudaSuccess) return (int)e;
-        attr_set = true;
+        attr_set.mark(attr_set_dev);
     }
     MoeGroupedArgs args;
     args.tiles = (const TcTile*)tiles;

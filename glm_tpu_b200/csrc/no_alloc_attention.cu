@@ -43,9 +43,12 @@ extern "C" __attribute__((visibility("default")))
 int glmb_sparse_mla_attention_noalloc(const void* q_full, const void* kv_cache, const int* sel_local, const int* sel_counts,
                                       const int* row_lane, int rows, int H, int L, int rd, int layer, int layers, int local_cap,
                                       int top_k, float scale, void* o_lat, uint32_t* status, void* stream) {
-    if (rows < 1 || H < 1 || L < 1 || top_k < 1) return GLMB_NOALLOC_BAD_SHAPE;
-    if (rows > GLMB_NOALLOC_MAX_ROWS || H > GLMB_NOALLOC_MAX_HEADS || L > GLMB_NOALLOC_MAX_LATENT || top_k > GLMB_NOALLOC_MAX_TOPK)
+    if (rows < 1 || H < 1 || L < 1 || top_k < 1 || rd < 0 || layers < 1 || layer < 0 || layer >= layers || local_cap < 1)
+        return GLMB_NOALLOC_BAD_SHAPE;
+    if (rows > GLMB_NOALLOC_MAX_ROWS || H > GLMB_NOALLOC_MAX_HEADS || L > GLMB_NOALLOC_MAX_LATENT || top_k > GLMB_NOALLOC_MAX_TOPK ||
+        rd > GLMB_NOALLOC_MAX_ROPE)
         return GLMB_NOALLOC_TOO_LARGE;
+    if ((L != 64 && L != 128 && L != 512) || ((L + rd) & 15)) return GLMB_NOALLOC_BAD_SHAPE;
     if (glmb_attn_chunk() != GLMB_NOALLOC_CHUNK) return GLMB_NOALLOC_BAD_SHAPE;
     const int max_chunks = (top_k + GLMB_NOALLOC_CHUNK - 1) / GLMB_NOALLOC_CHUNK;
     // layout inside the scratch: partial outputs [rows, max_chunks, H, L], then statistics [rows, max_chunks, H, 2]
@@ -59,9 +62,12 @@ int glmb_sparse_mla_attention_noalloc(const void* q_full, const void* kv_cache, 
     float* part_ml = scratch + part_o_floats;
     int code = glmb_sparse_mla_partial(q_full, kv_cache, sel_local, sel_counts, row_lane, rows, H, L, rd, layer, layers, local_cap,
                                        top_k, max_chunks, scale, part_o, part_ml, nullptr, -1, status, stream);
-    if (code == 1) return GLMB_NOALLOC_BAD_SHAPE;
+    // the inner entry points answer 1 (a shape they do not take) or 2 (a tile that does not fit shared memory) before they launch
+    // anything; both are refusals of the shape, not CUDA errors.  Larger values are the cudaError_t of a launch.
+    if (code == 1 || code == 2) return GLMB_NOALLOC_BAD_SHAPE;
     if (code != 0) return code;
-    return glmb_attn_local_merge(part_o, part_ml, sel_counts, rows, H, L, top_k, max_chunks, o_lat, H, 0, nullptr, 0, stream);
+    code = glmb_attn_local_merge(part_o, part_ml, sel_counts, rows, H, L, top_k, max_chunks, o_lat, H, 0, nullptr, 0, stream);
+    return (code == 1 || code == 2) ? GLMB_NOALLOC_BAD_SHAPE : code;
 }
 
 extern "C" __attribute__((visibility("default")))
@@ -69,10 +75,10 @@ const char* glmb_noalloc_strerror(int code) {
     switch (code) {
         case GLMB_NOALLOC_OK: return "ok";
         case GLMB_NOALLOC_TOO_LARGE:
-            return "problem exceeds the built-in scratch: at most 2 rows, 64 heads, latent 512, top_k 2048 per call";
+            return "problem exceeds the built-in scratch: at most 2 rows, 64 heads, latent 512, rope 256, top_k 2048 per call";
         case GLMB_NOALLOC_BAD_SHAPE:
-            return "unsupported shape: latent must be 64, 128 or 512 and latent + rope width a multiple of 16";
+            return "unsupported shape: counts must be positive, rope width non-negative, latent 64, 128 or 512 and latent + rope width a multiple of 16";
         case GLMB_NOALLOC_NO_SYMBOL: return "the scratch array could not be resolved on the current device";
-        default: return "CUDA error (the value is the cudaError_t of the failed call)";
+        default: return code > 0 ? "CUDA error (the value is the cudaError_t of the failed call)" : "unknown code";
     }
 }

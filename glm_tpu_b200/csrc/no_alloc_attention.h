@@ -39,12 +39,15 @@ extern "C" {
     ((GLMB_NOALLOC_MAX_ROWS) * (GLMB_NOALLOC_MAX_TOPK / GLMB_NOALLOC_CHUNK) * (GLMB_NOALLOC_MAX_HEADS) * (GLMB_NOALLOC_MAX_LATENT + 2))
 #define GLMB_NOALLOC_SCRATCH_BYTES (4ull * GLMB_NOALLOC_SCRATCH_FLOATS)  // about 8.4 MB per GPU
 
-// Return codes.
+#define GLMB_NOALLOC_MAX_ROPE 256     // rope width (q_full and the cache rows are latent + rope wide)
+
+// Return codes.  The entry point's own refusals are negative, so they cannot be mistaken for a cudaError_t (all positive).
 #define GLMB_NOALLOC_OK 0
-#define GLMB_NOALLOC_TOO_LARGE 100    // rows, heads, latent width or top_k beyond the limits above
-#define GLMB_NOALLOC_BAD_SHAPE 101    // a size the attention kernels do not support (see glmb_sparse_mla_partial)
-#define GLMB_NOALLOC_NO_SYMBOL 102    // the scratch array's address could not be resolved on this device
-// Any other non-zero value is the CUDA error code of a failed launch.
+#define GLMB_NOALLOC_TOO_LARGE (-1)   // rows, heads, latent width, rope width or top_k beyond the limits above
+#define GLMB_NOALLOC_BAD_SHAPE (-2)   // a size the attention kernels do not support: a count below 1, rd below 0, a latent other than
+                                      // 64, 128 or 512, latent + rope not a multiple of 16
+#define GLMB_NOALLOC_NO_SYMBOL (-3)   // the scratch array's address could not be resolved on this device
+// Any positive value is the cudaError_t of a failed launch.
 
 // q_full     [rows, H, L + rd] bf16   absorbed queries (q_c | q_rope)
 // kv_cache   [lanes, layers, local_cap, L + rd] bf16

@@ -4,7 +4,7 @@ import re
 from pathlib import Path
 
 ROOT = Path(__file__).resolve().parents[1]
-DOCS = [ROOT / "README.md", ROOT / "DESIGN.md", *sorted((ROOT / "docs").glob("*.md")), *sorted((ROOT / "profiles").glob("*.md"))]
+DOCS = [ROOT / "README.md", *sorted((ROOT / "docs").glob("*.md")), *sorted((ROOT / "profiles").glob("*.md"))]
 PATH = re.compile(r"`((?:glm_tpu_b200|tests|tools|docs|examples|profiles|csrc)/[A-Za-z0-9_./{},*<>-]+)`")
 
 
