@@ -24,6 +24,7 @@
 // partial/LSE-merge of `kernels/sparse_mla/partial_kernel.py:45-78`, `layers/attention/mla.py:288-376`.
 #include "common.cuh"
 #include "attention_core.cuh"
+#include "gemv_core.cuh"
 #include "peer.cuh"
 
 // One CTA: one tile of attention_core.cuh (16 heads x 64 gathered keys).
@@ -387,6 +388,108 @@ GLMB_API int glmb_attn_local_merge(const float* part_o, const float* part_ml, co
     dim3 grid(H, rows);
     GLMB_LAUNCH(attn_local_merge_kernel, grid, 128, 0, (cudaStream_t)stream, part_o, part_ml, sel_counts, H, L, top_k, max_chunks,
                                                                     (bf16*)o_lat, heads_local, xpart_offset, c, sig);
+    return (int)cudaGetLastError();
+}
+
+// Decode with every key local: the merge of a (row, head)'s chunk partials AND that head's value projection in one launch.
+//   o_lat[r][h] = bf16(sum_c w_c o_c / l)   exactly as attn_local_merge_kernel (same thread-to-column map, same order over chunks)
+//   attn_v[r][h * N + n] = bf16(o_lat[r][h] . w_v[h][n])   exactly as skinny_bf16_kernel with one K part (same lane-to-k map, xor tree)
+// grid (H, rows, N / MV_COLS): a (row, head) is merged redundantly by the N / MV_COLS CTAs that share its value projection (64 KB of
+// L2-resident partials each) so that the 256 KB of a head's value table are streamed by 8 SMs instead of 1; every chunk row a thread
+// needs is requested before the first is used, and the CTA's slice of the value table is asked into L2 before the wait for the
+// attention kernel.  One launch and ~3 memory round trips where merge + projection took two launches and ~8.
+#define MV_THREADS 256
+#define MV_COLS 32
+#define MV_BATCH 16
+__global__ void __launch_bounds__(MV_THREADS)
+attn_merge_vproj_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, const int* __restrict__ sel_counts, int H, int L,
+                        int top_k, int max_chunks, const bf16* __restrict__ w_v, int64_t w_head_stride, int N, bf16* __restrict__ o_lat,
+                        bf16* __restrict__ attn_v) {
+    asm volatile("griddepcontrol.launch_dependents;");
+    const int h = blockIdx.x, r = blockIdx.y, n_base = blockIdx.z * MV_COLS;
+    const int n_here = min(MV_COLS, N - n_base);
+    const bf16* w_head = w_v + (int64_t)h * w_head_stride;
+    if (threadIdx.x == 0) {
+        const char* p = reinterpret_cast<const char*>(w_head + (int64_t)n_base * L);
+        const uint32_t bytes = (uint32_t)(((int64_t)n_here * L * 2) & ~(int64_t)15);
+        if (bytes && !((uintptr_t)p & 15)) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    __shared__ float w_s[AM_MAX_CHUNKS];
+    __shared__ float red_s[8];
+    __shared__ __align__(16) bf16 o_s[512];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int count = min(max(sel_counts[2 * r + 1], 0), top_k);
+    const int chunks = min((count + AT_CHUNK - 1) / AT_CHUNK, AM_MAX_CHUNKS);
+    const int64_t base = (int64_t)r * max_chunks * H + h;
+    // ---- merge: the first 128 threads are the 128 threads of attn_local_merge_kernel
+    float my_m = -INFINITY, my_l = 0.f;
+    if ((int)threadIdx.x < chunks) {
+        const float2 ml = *reinterpret_cast<const float2*>(part_ml + (base + (int64_t)threadIdx.x * H) * 2);
+        my_m = ml.x; my_l = ml.y;
+    }
+    float M = my_m;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+    if (lane == 0 && warp < 4) red_s[warp] = M;
+    __syncthreads();
+    M = fmaxf(fmaxf(red_s[0], red_s[1]), fmaxf(red_s[2], red_s[3]));
+    const float my_w = (int)threadIdx.x < chunks ? expf(my_m - M) : 0.f;
+    if (threadIdx.x < AM_MAX_CHUNKS) w_s[threadIdx.x] = my_w;
+    float l = my_l * my_w;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+    if (lane == 0 && warp < 4) red_s[4 + warp] = l;
+    __syncthreads();
+    l = (red_s[4] + red_s[5]) + (red_s[6] + red_s[7]);
+    if (threadIdx.x < 128) {
+        for (int j = threadIdx.x * 4; j < L; j += 128 * 4) {
+            float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int c0 = 0; c0 < chunks; c0 += MV_BATCH) {
+                float4 v[MV_BATCH];
+#pragma unroll
+                for (int u = 0; u < MV_BATCH; ++u)
+                    v[u] = c0 + u < chunks ? *reinterpret_cast<const float4*>(part_o + (base + (int64_t)(c0 + u) * H) * L + j)
+                                           : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int u = 0; u < MV_BATCH; ++u) {
+                    const float wgt = c0 + u < chunks ? w_s[c0 + u] : 0.f;
+                    o.x = fmaf(v[u].x, wgt, o.x); o.y = fmaf(v[u].y, wgt, o.y);
+                    o.z = fmaf(v[u].z, wgt, o.z); o.w = fmaf(v[u].w, wgt, o.w);
+                }
+            }
+            if (chunks > 0) { o.x /= l; o.y /= l; o.z /= l; o.w /= l; }  // the contract divides (no reciprocal)
+            uint2 packed;
+            packed.x = pack_bf16(o.x, o.y);
+            packed.y = pack_bf16(o.z, o.w);
+            *reinterpret_cast<uint2*>(o_s + j) = packed;
+            if (o_lat && blockIdx.z == 0) *reinterpret_cast<uint2*>(o_lat + ((int64_t)r * H + h) * L + j) = packed;
+        }
+    }
+    __syncthreads();
+    // ---- value projection of this CTA's columns: a warp per pair of output columns over the whole K = L
+    const bf16* const xr[1] = {o_s};
+    for (int pair = warp; pair * 2 < n_here; pair += MV_THREADS / 32) {
+        const int n0 = n_base + pair * 2;
+        const bf16* const wp[2] = {w_head + (int64_t)n0 * L, w_head + (int64_t)min(n0 + 1, N - 1) * L};
+        float acc[2][1] = {{0.f}, {0.f}};
+        warp_dot_bf16<1, 2>(xr, wp, 0, L, lane, acc);
+        warp_reduce_all<1, 2>(acc);
+        if (lane == 0) {
+            bf16* dst = attn_v + ((int64_t)r * H + h) * N + n0;
+            dst[0] = __float2bfloat16_rn(acc[0][0]);
+            if (n0 + 1 < N) dst[1] = __float2bfloat16_rn(acc[1][0]);
+        }
+    }
+}
+
+// w_v: the value rows of head 0 ([N, L] bf16, rows L apart); the next head's start w_head_stride elements later.
+GLMB_API int glmb_attn_merge_vproj(const float* part_o, const float* part_ml, const int* sel_counts, int rows, int H, int L, int top_k,
+                                   int max_chunks, const void* w_v, int64_t w_head_stride, int N, void* o_lat, void* attn_v, void* stream) {
+    if ((L & 7) || L > 512 || max_chunks > AM_MAX_CHUNKS || N < 1 || rows < 1 || H < 1 || (w_head_stride & 7)) return 1;
+    dim3 grid(H, rows, (N + MV_COLS - 1) / MV_COLS);
+    GLMB_LAUNCH(attn_merge_vproj_kernel, grid, MV_THREADS, 0, (cudaStream_t)stream, part_o, part_ml, sel_counts, H, L, top_k, max_chunks,
+                (const bf16*)w_v, w_head_stride, N, (bf16*)o_lat, (bf16*)attn_v);
     return (int)cudaGetLastError();
 }
 

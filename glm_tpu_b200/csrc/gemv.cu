@@ -373,9 +373,13 @@ GLMB_API int glmb_skinny_bf16(const void* x, int64_t xs, int rows, const void* w
                               int mode, int batch, int64_t xb, int64_t wb, int64_t ob, const PeerComm* comm, int channel,
                               void* stream) {
     if (rows < 1 || rows > GLMB_MAX_ROWS || (K & 7) || (xs & 7) || (ws & 7) || (xb & 7) || (wb & 7) || batch < 1) return 1;
-    const int ks = pick_ksplit(ceil_div(N, 2) * batch, K);
-    const dim3 grid(ceil_div(N, (SK_WARPS / ks) * 2), batch);
+    int ks = pick_ksplit(ceil_div(N, 2) * batch, K);
     PeerComm c = comm ? *comm : single_comm();
+    // A CTA that all-reduces waits for the same CTA of every peer before it retires.  CTAs beyond the first wave would start only
+    // after such a wait and then wait again: keep the grid within one wave (three CTAs per SM fit whatever the row count).
+    if (mode == SK_OUT_ALLREDUCE_BF16 && c.world > 1)
+        while (ks > 1 && ceil_div(N, (SK_WARPS / ks) * 2) * batch > 148 * 3) ks >>= 1;
+    const dim3 grid(ceil_div(N, (SK_WARPS / ks) * 2), batch);
     if (mode == SK_OUT_ALLREDUCE_BF16 && c.world > 1 && (int)(grid.x * grid.y) > GLMB_AR_MAX_CTAS) return 2;
     if (mode == SK_OUT_ALLREDUCE_BF16 && c.world == 1) mode = SK_OUT_BF16;
 #define CALL(RR)                                                                                                   \

@@ -25,7 +25,9 @@
 #define MM_ROWS 16  // output rows per CTA
 
 // act[p][n] = bf16( silu(bf16(x_p . wg[e][n])) * bf16(x_p . wu[e][n]) ) for the routes p of tile t.  H % 64 == 0, I % 16 == 0.
-template <int RT>
+// MM_DEPTH: chunks of a warp whose loads are in flight together (4 for grids of up to two CTAs per SM, where DRAM latency is the
+// bound; 1 for large grids, where the registers of a deep pipeline would cost resident CTAs).
+template <int RT, int MM_DEPTH>
 __global__ void __launch_bounds__(MM_THREADS)
 moe_gateup_fp8_mma_kernel(const bf16* __restrict__ x, int64_t xs, int top_k, const int* __restrict__ tile_expert,
                           const int* __restrict__ tile_routes, const int* __restrict__ n_tiles, const uint8_t* __restrict__ wg,
@@ -49,15 +51,31 @@ moe_gateup_fp8_mma_kernel(const bf16* __restrict__ x, int64_t xs, int top_k, con
     const int64_t sofs = ((int64_t)e * ((I + 127) >> 7) + (n0 >> 7)) * kb;
     float acc_g[4] = {0.f, 0.f, 0.f, 0.f}, acc_u[4] = {0.f, 0.f, 0.f, 0.f};
     const int chunks = H >> 6;
-    for (int c = warp; c < chunks; c += MM_WARPS) {
-        const int k = (c << 6) + t * 16;
-        const uint4 g_lo = ld_stream16(wg_lo + k), g_hi = ld_stream16(wg_lo + hi_off + k);
-        const uint4 u_lo = ld_stream16(wu_lo + k), u_hi = ld_stream16(wu_lo + hi_off + k);
-        uint4 x0 = make_uint4(0, 0, 0, 0), x1 = x0;
-        if (route >= 0) { x0 = ld_hot16(xr + k); x1 = ld_hot16(xr + k + 8); }
-        const float s_g = sg[sofs + (c >> 1)], s_u = su[sofs + (c >> 1)];
-        chunk_mma(acc_g, g_lo, g_hi, s_g, x0, x1);
-        chunk_mma(acc_u, u_lo, u_hi, s_u, x0, x1);
+    // MM_DEPTH chunks of every warp are in flight at once (all their loads are issued before the first multiply): with one CTA per
+    // 16 output rows a grid is a few hundred CTAs, and a warp that waited for one chunk at a time would spend its life in DRAM
+    // latency.  The chunks still enter the accumulators in ascending order, so the sums are the same bits at any depth.
+    for (int c0 = warp; c0 < chunks; c0 += MM_WARPS * MM_DEPTH) {
+        uint4 g_lo[MM_DEPTH], g_hi[MM_DEPTH], u_lo[MM_DEPTH], u_hi[MM_DEPTH], x0[MM_DEPTH], x1[MM_DEPTH];
+        float s_g[MM_DEPTH], s_u[MM_DEPTH];
+#pragma unroll
+        for (int u = 0; u < MM_DEPTH; ++u) {
+            const int c = c0 + u * MM_WARPS;
+            x0[u] = make_uint4(0, 0, 0, 0); x1[u] = x0[u];
+            if (c < chunks) {
+                const int k = (c << 6) + t * 16;
+                g_lo[u] = ld_stream16(wg_lo + k); g_hi[u] = ld_stream16(wg_lo + hi_off + k);
+                u_lo[u] = ld_stream16(wu_lo + k); u_hi[u] = ld_stream16(wu_lo + hi_off + k);
+                if (route >= 0) { x0[u] = ld_hot16(xr + k); x1[u] = ld_hot16(xr + k + 8); }
+                s_g[u] = sg[sofs + (c >> 1)]; s_u[u] = su[sofs + (c >> 1)];
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < MM_DEPTH; ++u) {
+            if (c0 + u * MM_WARPS < chunks) {
+                chunk_mma(acc_g, g_lo[u], g_hi[u], s_g[u], x0[u], x1[u]);
+                chunk_mma(acc_u, u_lo[u], u_hi[u], s_u[u], x0[u], x1[u]);
+            }
+        }
     }
     // C fragment: (row g, routes 2t, 2t+1), (row g + 8, routes 2t, 2t+1)
     red[warp][0][g][2 * t] = acc_g[0]; red[warp][0][g][2 * t + 1] = acc_g[1];
@@ -79,7 +97,7 @@ moe_gateup_fp8_mma_kernel(const bf16* __restrict__ x, int64_t xs, int top_k, con
 }
 
 // dw[p][n] = bf16( bf16(act[p] . wd[e][n]) * bf16(route_weight[p]) ).  I % 64 == 0, H % 16 == 0.
-template <int RT>
+template <int RT, int MM_DEPTH>
 __global__ void __launch_bounds__(MM_THREADS)
 moe_down_fp8_mma_kernel(const bf16* __restrict__ act, const float* __restrict__ route_weight, const int* __restrict__ tile_expert,
                         const int* __restrict__ tile_routes, const int* __restrict__ n_tiles, const uint8_t* __restrict__ wd,
@@ -100,12 +118,23 @@ moe_down_fp8_mma_kernel(const bf16* __restrict__ act, const float* __restrict__ 
     const int64_t sofs = ((int64_t)e * ((H + 127) >> 7) + (n0 >> 7)) * kb;
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     const int chunks = I >> 6;
-    for (int c = warp; c < chunks; c += MM_WARPS) {
-        const int k = (c << 6) + t * 16;
-        const uint4 lo = ld_stream16(w_lo + k), hi = ld_stream16(w_lo + hi_off + k);
-        uint4 x0 = make_uint4(0, 0, 0, 0), x1 = x0;
-        if (route >= 0) { x0 = ld_hot16(xr + k); x1 = ld_hot16(xr + k + 8); }
-        chunk_mma(acc, lo, hi, sd[sofs + (c >> 1)], x0, x1);
+    for (int c0 = warp; c0 < chunks; c0 += MM_WARPS * MM_DEPTH) {  // MM_DEPTH chunks in flight, entered in ascending order
+        uint4 lo[MM_DEPTH], hi[MM_DEPTH], x0[MM_DEPTH], x1[MM_DEPTH];
+        float sc[MM_DEPTH];
+#pragma unroll
+        for (int u = 0; u < MM_DEPTH; ++u) {
+            const int c = c0 + u * MM_WARPS;
+            x0[u] = make_uint4(0, 0, 0, 0); x1[u] = x0[u];
+            if (c < chunks) {
+                const int k = (c << 6) + t * 16;
+                lo[u] = ld_stream16(w_lo + k); hi[u] = ld_stream16(w_lo + hi_off + k);
+                if (route >= 0) { x0[u] = ld_hot16(xr + k); x1[u] = ld_hot16(xr + k + 8); }
+                sc[u] = sd[sofs + (c >> 1)];
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < MM_DEPTH; ++u)
+            if (c0 + u * MM_WARPS < chunks) chunk_mma(acc, lo[u], hi[u], sc[u], x0[u], x1[u]);
     }
     red[warp][g][2 * t] = acc[0]; red[warp][g][2 * t + 1] = acc[1];
     red[warp][g + 8][2 * t] = acc[2]; red[warp][g + 8][2 * t + 1] = acc[3];
@@ -202,18 +231,31 @@ GLMB_API int glmb_moe_down_combine(const void* act, const float* route_weight, c
     return (int)cudaGetLastError();
 }
 
+// How many CTAs of a (rows x tiles) grid are expected to do work: a tile whose expert lives on another GPU returns at once, and
+// with E experts of which this GPU holds `experts_local` a route is local with probability experts_local / E.  The model tells the
+// library E once (0: every tile is local); the estimate only selects the pipeline depth, never the result.
+static int g_moe_experts_total = 0;
+GLMB_API void glmb_set_moe_experts_total(int experts) { g_moe_experts_total = experts > 0 ? experts : 0; }
+static long live_ctas(unsigned per_tile, int tiles, int experts_local) {
+    long live_tiles = tiles;
+    if (g_moe_experts_total > experts_local && experts_local > 0)
+        live_tiles = max(1L, ((long)tiles * experts_local * 2 + g_moe_experts_total - 1) / g_moe_experts_total);  // twice the mean: the busy GPU
+    return (long)per_tile * live_tiles;
+}
+
 // ===================================================================================================
 // Launchers used by glmb_moe_gateup_fp8 / glmb_moe_down_fp8 (gemv.cu) when the shape fits.  rt in {1, 8}.
 int glmb_launch_moe_gateup_mma(const void* x, int64_t xs, int top_k, const int* tile_expert, const int* tile_routes, const int* n_tiles,
                                int tiles, int rt, const void* wg, const void* wu, const float* sg, const float* su, int expert_base,
                                int experts_local, int I, int H, void* act, cudaStream_t stream) {
     dim3 grid(ceil_div(I, MM_ROWS), tiles);
-    if (rt == 1)
-        GLMB_LAUNCH(moe_gateup_fp8_mma_kernel<1>, grid, MM_THREADS, 0, stream, (const bf16*)x, xs, top_k, tile_expert, tile_routes, n_tiles,
-                    (const uint8_t*)wg, (const uint8_t*)wu, sg, su, expert_base, experts_local, I, H, (bf16*)act);
-    else
-        GLMB_LAUNCH(moe_gateup_fp8_mma_kernel<8>, grid, MM_THREADS, 0, stream, (const bf16*)x, xs, top_k, tile_expert, tile_routes, n_tiles,
-                    (const uint8_t*)wg, (const uint8_t*)wu, sg, su, expert_base, experts_local, I, H, (bf16*)act);
+    const long live = live_ctas(grid.x, tiles, experts_local);
+#define CALL(RT_, D_)                                                                                                                      \
+    GLMB_LAUNCH((moe_gateup_fp8_mma_kernel<RT_, D_>), grid, MM_THREADS, 0, stream, (const bf16*)x, xs, top_k, tile_expert, tile_routes, n_tiles, \
+                (const uint8_t*)wg, (const uint8_t*)wu, sg, su, expert_base, experts_local, I, H, (bf16*)act)
+    if (rt == 1) { if (live <= 2 * 148) CALL(1, 4); else if (live <= 4 * 148) CALL(1, 2); else CALL(1, 1); }
+    else CALL(8, 1);
+#undef CALL
     return (int)cudaGetLastError();
 }
 
@@ -221,11 +263,12 @@ int glmb_launch_moe_down_mma(const void* act, const float* route_weight, const i
                              int tiles, int rt, const void* wd, const float* sd, int expert_base, int experts_local, int I, int H, void* dw,
                              cudaStream_t stream) {
     dim3 grid(ceil_div(H, MM_ROWS), tiles);
-    if (rt == 1)
-        GLMB_LAUNCH(moe_down_fp8_mma_kernel<1>, grid, MM_THREADS, 0, stream, (const bf16*)act, route_weight, tile_expert, tile_routes, n_tiles,
-                    (const uint8_t*)wd, sd, expert_base, experts_local, I, H, (bf16*)dw);
-    else
-        GLMB_LAUNCH(moe_down_fp8_mma_kernel<8>, grid, MM_THREADS, 0, stream, (const bf16*)act, route_weight, tile_expert, tile_routes, n_tiles,
-                    (const uint8_t*)wd, sd, expert_base, experts_local, I, H, (bf16*)dw);
+    const long live = live_ctas(grid.x, tiles, experts_local);
+#define CALL(RT_, D_)                                                                                                                        \
+    GLMB_LAUNCH((moe_down_fp8_mma_kernel<RT_, D_>), grid, MM_THREADS, 0, stream, (const bf16*)act, route_weight, tile_expert, tile_routes, n_tiles, \
+                (const uint8_t*)wd, sd, expert_base, experts_local, I, H, (bf16*)dw)
+    if (rt == 1) { if (live <= 2 * 148) CALL(1, 4); else if (live <= 4 * 148) CALL(1, 2); else CALL(1, 1); }
+    else CALL(8, 1);
+#undef CALL
     return (int)cudaGetLastError();
 }

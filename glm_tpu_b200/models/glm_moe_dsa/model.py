@@ -193,6 +193,8 @@ class GlmMoeDsaModel:
         self.index_scale = _f32(g.index_head_dim**-0.5)
         self.head_scale = _f32(g.index_heads**-0.5)
         self.trace = None  # set to a dict to record intermediates (tests)
+        native.set_moe_experts_total(self.g.num_routed_experts)
+        self.fallbacks: dict[str, int] = {}  # library routines taken in place of the hand-written kernels (see note_fallback)
         self.emulated_shard = False  # measurements: this process holds one rank's shard and skips every exchange (see GpuModelRunner)
         import os
 
@@ -202,6 +204,7 @@ class GlmMoeDsaModel:
         self.fold_q_post = os.environ.get("GLM_B200_FOLD_Q_POST", "1") != "0"
         self.nvtx = os.environ.get("GLM_B200_NVTX", "0") == "1"
         self.route_sort_kernel = os.environ.get("GLM_B200_ROUTE_SORT", "kernel") != "torch"  # 'torch': the library-op expert sort (A/B runs)
+        self.merge_vproj = os.environ.get("GLM_B200_MERGE_VPROJ", "1") != "0"  # decode: chunk merge + value projection in one launch
         self.prefill_rows_attention = os.environ.get("GLM_B200_PREFILL_ATTENTION", "rows") != "split"
         # Prefill projections whose K is split over the GPUs use the GEMM with the all-reduce in its epilogue (about 1.2x the
         # GEMM + library all-reduce on 2 and on 8 GPUs); GLM_B200_PREFILL_GEMM_AR=nccl selects the library path.
@@ -212,6 +215,17 @@ class GlmMoeDsaModel:
     def _kc(self):
         """PeerComm for kernels with fused communication (None: single GPU or NCCL baseline)."""
         return self.peer.kernel_comm if self.comm_mode == "fused" else None
+
+    def note_fallback(self, what: str, why: str) -> None:
+        """A hand-written kernel was passed over for a library routine: counted per (what, why) for the runner's report and
+        logged the first time, so a slow path never hides."""
+        key = f"{what}: {why}"
+        seen = self.fallbacks.get(key, 0)
+        self.fallbacks[key] = seen + 1
+        if not seen:
+            import logging
+
+            logging.getLogger("glm_tpu_b200.fallback").warning("rank %d falls back to %s", self.rank, key)
 
     def _allreduce_rows(self, partial_f32: torch.Tensor) -> torch.Tensor:
         import torch.distributed as dist
@@ -231,6 +245,7 @@ class GlmMoeDsaModel:
             out = torch.empty((rows, N), dtype=dtype, device=x.device)
             native.gemm_bf16_tc(x, w, out, status=self.peer.status_ptr)
             return out
+        self.note_fallback("library GEMM", f"operands [{rows}x{K}] x [{N}x{K}] are not 16-byte aligned rows of a multiple of 8")
         return torch.mm(x, w.t(), out_dtype=torch.float32) if f32 else torch.mm(x, w.t())
 
     def _fork(self):
@@ -254,6 +269,9 @@ class GlmMoeDsaModel:
             return None
         if ws.r_gemm_out is None or w.shape[0] != self.g.hidden_size or K % 8 or x.stride(1) != 1 or x.stride(0) % 8 \
                 or x.data_ptr() % 16 or w.data_ptr() % 16 or w.stride(0) % 8:
+            if self.comm_mode == "fused":
+                self.note_fallback("GEMM then library all-reduce", "no staging for the fused GEMM all-reduce in this workspace" if ws.r_gemm_out is None
+                                   else f"shape [{rows}x{K}] x [{w.shape[0]}x{K}] does not fit the fused GEMM all-reduce")
             return None
         native.gemm_bf16_tc_allreduce(x, w, self.peer.comm, ws.r_gemm_part.offset, ws.r_gemm_out.offset, status=self.peer.status_ptr)
         native.wait_signal(self.peer.comm, native.SIG_GEMM)
@@ -264,7 +282,7 @@ class GlmMoeDsaModel:
         """``bf16(g * sigmoid(g) * u)`` of the bf16 gate / up projections of a prefill chunk (written over ``gate``)."""
         if gate.is_contiguous() and up.is_contiguous() and gate.numel() % 8 == 0 and gate.dtype == torch.bfloat16:
             return native.swiglu_rows(gate, up, gate)
-        g32, u32 = gate.float(), up.float()
+        g32, u32 = gate.float(), up.float()  # odd shapes of fixtures only
         return (g32 * torch.sigmoid(g32) * u32).to(torch.bfloat16)
 
     def _linear_f32(self, x, w, out, decode: bool):
@@ -368,13 +386,18 @@ class GlmMoeDsaModel:
             # many rows, every key local: one kernel, running softmax per (row, 16 heads), bf16 output, no partials
             native.sparse_mla_rows(ws.q_full, state.kv_cache, ws.sel_local, ws.sel_counts, row_lane, rows, ht, L, rd, layer, g.num_layers,
                                    cache.local_capacity, g.index_top_k, self.softmax_scale, ws.o_lat, self.peer.status_ptr)
+        # decode with every key local and all rows in one pass: the merge and the value projection share a launch
+        merged_vproj = decode and not gather and rows <= ws.attn_rows and self.merge_vproj and L % 8 == 0 and L <= 512 and g.v_head_dim % 2 == 0
         # owner-local partial attention for ALL heads, in passes of attn_rows query rows
         for r0 in range(0, rows, ws.attn_rows) if (decode or gather or not self.prefill_rows_attention) else ():
             n = min(ws.attn_rows, rows - r0)
             native.sparse_mla_partial(ws.q_full[r0:], state.kv_cache, ws.sel_local[r0:], ws.sel_counts[r0:], row_lane[r0:], n, ht, L, rd,
                                       layer, g.num_layers, cache.local_capacity, g.index_top_k, ws.max_chunks, self.softmax_scale,
                                       ws.part_o, ws.part_ml, kx, native.SIG_Q if xf else -1, self.peer.status_ptr)
-            if not gather:
+            if merged_vproj:
+                native.attn_merge_vproj(ws.part_o, ws.part_ml, ws.sel_counts, rows, ht, L, g.index_top_k, ws.max_chunks, lw.kv_b,
+                                        g.qk_nope_head_dim, ws.o_lat, ws.attn_v)
+            elif not gather:
                 native.attn_local_merge(ws.part_o, ws.part_ml, ws.sel_counts[r0:], n, ht, L, g.index_top_k, ws.max_chunks, ws.o_lat[r0:], hl)
             elif xf:
                 native.attn_local_merge(ws.part_o, ws.part_ml, ws.sel_counts[r0:], n, ht, L, g.index_top_k, ws.max_chunks, None, hl,
@@ -384,8 +407,9 @@ class GlmMoeDsaModel:
                 self._merge_partials_nccl(ws, r0, n)
         # value projection per head, then the K-split output projection with its reduction
         if decode:
-            native.skinny_bf16(ws.o_lat, lw.kv_b[:, g.qk_nope_head_dim :, :], ws.attn_v, native.SK_OUT_BF16, rows=rows, N=g.v_head_dim,
-                               K=L, xs=hl * L, ws=L, os_=hl * g.v_head_dim, batch=hl, xb=L, wb=g.kv_b_rows_per_head * L, ob=g.v_head_dim)
+            if not merged_vproj:
+                native.skinny_bf16(ws.o_lat, lw.kv_b[:, g.qk_nope_head_dim :, :], ws.attn_v, native.SK_OUT_BF16, rows=rows, N=g.v_head_dim,
+                                   K=L, xs=hl * L, ws=L, os_=hl * g.v_head_dim, batch=hl, xb=L, wb=g.kv_b_rows_per_head * L, ob=g.v_head_dim)
             if fused or self.world == 1 or self.emulated_shard:
                 native.skinny_bf16(ws.attn_v[:rows], lw.w_o, ws.attn_out, native.SK_OUT_ALLREDUCE_BF16, comm=kc, channel=native.CH_ATTN)
             else:

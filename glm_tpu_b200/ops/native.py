@@ -212,7 +212,10 @@ def skinny_bf16(x, w, out, mode=SK_OUT_F32, *, rows=None, comm=None, channel=0, 
     ws = w.stride(-2) if ws is None else ws
     os_ = out.stride(0) if os_ is None else os_
     if mode == SK_OUT_ALLREDUCE_BF16 and _exchanges is not None:
-        groups = 8 // _skinny_ksplit(-(-N // 2) * batch, K)
+        ks = _skinny_ksplit(-(-N // 2) * batch, K)
+        while ks > 1 and -(-N // ((8 // ks) * 2)) * batch > 148 * 3:  # the all-reduce keeps its grid within one wave (csrc/gemv.cu)
+            ks //= 2
+        groups = 8 // ks
         _note_allreduce("skinny_bf16", comm, channel, -(-N // (groups * 2)) * batch, groups * 2 * (1 if rows <= 1 else 2 if rows <= 2 else 4 if rows <= 4 else 8))
     _check(
         lib().glmb_skinny_bf16(_p(x), C.c_int64(xs), rows, _p(w), C.c_int64(ws), N, K, _p(out), C.c_int64(os_), mode, batch,
@@ -227,6 +230,12 @@ def skinny_bf16_swiglu(x, wg, wu, act):
                                       wg.shape[0], wg.shape[1], _p(act), C.c_int64(act.stride(0)), _stream()),
         "skinny_bf16_swiglu",
     )
+
+
+def set_moe_experts_total(experts: int) -> None:
+    """Tell the expert GEMV launchers how many routed experts the model has in all (they see only this GPU's share): the
+    expected number of local routes selects how deep the kernels pipeline their loads."""
+    lib().glmb_set_moe_experts_total(int(experts))
 
 
 def set_moe_mma(enabled: int) -> None:
@@ -472,6 +481,19 @@ def sparse_mla_rows(q_full, kv_cache, sel_local, sel_counts, row_lane, rows, H, 
         lib().glmb_sparse_mla_rows(_p(q_full), _p(kv_cache), _p(sel_local), _p(sel_counts), _p(row_lane), rows, H, L, rd, layer, layers,
                                    local_cap, top_k, f32(scale), _p(o_lat), _p(status), _stream()),
         "sparse_mla_rows",
+    )
+
+
+def attn_merge_vproj(part_o, part_ml, sel_counts, rows, H, L, top_k, max_chunks, kv_b, nope, o_lat, attn_v):
+    """Decode, every key local: merge of the chunk partials and the per-head value projection in one launch
+    (``attn_merge_vproj_kernel``; the bits of ``attn_local_merge`` followed by the batched ``skinny_bf16``).
+    ``kv_b``: ``[H, nope + v, L]`` bf16, the value rows start at row ``nope`` of every head."""
+    per_head, v = kv_b.shape[1], kv_b.shape[1] - nope
+    w_v = kv_b.data_ptr() + nope * L * 2
+    _check(
+        lib().glmb_attn_merge_vproj(_p(part_o), _p(part_ml), _p(sel_counts), rows, H, L, top_k, max_chunks, C.c_void_p(w_v),
+                                    C.c_int64(per_head * L), v, _p(o_lat), _p(attn_v), _stream()),
+        "attn_merge_vproj",
     )
 
 

@@ -302,6 +302,7 @@ class GpuModelRunner:
             "index_cache_bytes": int(st.index_cache.numel() * st.index_cache.element_size()),
             "staging_bytes": int(self.peer._total) if self.peer.world > 1 else 0,
             "kv_layout": self.kv_layout,
+            "fallbacks": dict(self.model.fallbacks),  # library routines taken in place of the hand-written kernels, with counts
         }
 
     def synthetic_context(self, lane: int, depth: int, seed: int = 0) -> None:
