@@ -18,6 +18,14 @@ def test_gate_matches_golden(gate):
     assert driver.check({gate}) == {}
 
 
+@pytest.mark.gpu
+def test_launch_programs_match_golden():
+    """The ordered launch list (entry point + integer arguments) of a decode step and a prefill chunk, per configuration."""
+    golden = driver.load("g1_launch_programs")
+    assert {"glm53x8.shard-of-8.chats1", "glm53x8.shard-of-8.chats4", "small4.gpus1.chats1"} <= set(golden)
+    assert driver.check({"g1_launch_programs"}) == {}
+
+
 @pytest.mark.slow
 def test_import_closures_only_shrink():
     assert driver.check({"g6_import_closures"}) == {}

@@ -10,9 +10,9 @@ DATA = Path(__file__).resolve().parents[2] / "tests" / "golden" / "data"
 
 
 def gates() -> dict:
-    from tools.equivalence import digests, executed, imports, wire
+    from tools.equivalence import digests, executed, imports, programs, wire
 
-    return {"g3_oracle_digests": digests.oracle_digests, "g4_checkpoint_identity": digests.checkpoint_identity, "g6_import_closures": imports.collect,
+    return {"g1_launch_programs": programs.collect, "g3_oracle_digests": digests.oracle_digests, "g4_checkpoint_identity": digests.checkpoint_identity, "g6_import_closures": imports.collect,
             "g7_executed_functions": executed.collect, "g9_wire_formats": wire.collect}
 
 
@@ -23,10 +23,14 @@ def load(name: str):
 def check(names=None) -> dict:
     from tools.equivalence import executed, imports
 
+    from tools.equivalence import programs
+
     failures = {}
     for name, fn in gates().items():
         if names and name not in names:
             continue
+        if name == "g1_launch_programs" and not programs.available():
+            continue  # the launch programs are recorded on a GPU
         current, golden = json.loads(json.dumps(fn())), load(name)
         if name == "g6_import_closures":
             extra = imports.grown(golden, current)
@@ -43,8 +47,12 @@ def check(names=None) -> dict:
 
 def update(names=None) -> None:
     DATA.mkdir(parents=True, exist_ok=True)
+    from tools.equivalence import programs
+
     for name, fn in gates().items():
         if names and name not in names:
+            continue
+        if name == "g1_launch_programs" and not programs.available():
             continue
         (DATA / f"{name}.json").write_text(json.dumps(fn(), indent=1, sort_keys=True) + "\n")
 
