@@ -10,6 +10,7 @@
 //   fill_random_*     counter-based random initialisation of weights directly in device memory
 #include "common.cuh"
 #include "peer.cuh"
+#include "tail_ops.cuh"
 
 // ---------------------------------------------------------------------------------------------------
 // One warp per row.  E <= 1024.
@@ -53,7 +54,7 @@ router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ b
     if (lane < top_k) weights[(int64_t)r * top_k + lane] = my_score / (picked_sum + 1e-20f);
 }
 
-// Same selection for E <= 256: every lane loads its (up to 8) logits once and keeps score and key in registers.
+// Same selection for E <= 256: every lane loads its (up to 8) logits once and keeps score and key in registers (tail_ops.cuh).
 __global__ void __launch_bounds__(128)
 router_topk256_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int rows, int E, int top_k,
                       int* __restrict__ ids, float* __restrict__ weights) {
@@ -61,47 +62,7 @@ router_topk256_kernel(const float* __restrict__ logits, const float* __restrict_
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = blockIdx.x * (blockDim.x >> 5) + warp;
     if (r >= rows) return;
-    const float* lg = logits + (int64_t)r * E;
-    float lv[8], bv[8], sc[8];
-    uint32_t key[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const int e = lane + 32 * i;
-        lv[i] = e < E ? lg[e] : 0.f;
-        bv[i] = e < E ? bias[e] : 0.f;
-    }
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        sc[i] = sigmoidf_precise(lv[i]);
-        key[i] = orderable_u32(__fadd_rn(sc[i], bv[i]));
-    }
-    uint32_t taken = 0;
-    float picked_sum = 0.f, my_score = 0.f;
-    for (int s = 0; s < top_k; ++s) {
-        uint32_t best_key = 0;
-        int best_e = 0x7fffffff;
-        float best_score = 0.f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const int e = lane + 32 * i;
-            if (e < E && !((taken >> i) & 1u) && (best_e == 0x7fffffff || key[i] > best_key)) {
-                best_key = key[i]; best_e = e; best_score = sc[i];
-            }
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const uint32_t k2 = __shfl_xor_sync(0xffffffffu, best_key, o);
-            const int e2 = __shfl_xor_sync(0xffffffffu, best_e, o);
-            const float s2 = __shfl_xor_sync(0xffffffffu, best_score, o);
-            const bool theirs = e2 != 0x7fffffff && (best_e == 0x7fffffff || k2 > best_key || (k2 == best_key && e2 < best_e));
-            if (theirs) { best_key = k2; best_e = e2; best_score = s2; }
-        }
-        if (best_e != 0x7fffffff && (best_e & 31) == lane) taken |= 1u << (best_e >> 5);
-        if (lane == s) my_score = best_score;
-        picked_sum += best_score;
-        if (lane == 0) ids[(int64_t)r * top_k + s] = best_e == 0x7fffffff ? 0 : best_e;
-    }
-    if (lane < top_k) weights[(int64_t)r * top_k + lane] = my_score / (picked_sum + 1e-20f);
+    router_topk256_row<false>(logits + (int64_t)r * E, bias, E, top_k, ids + (int64_t)r * top_k, weights + (int64_t)r * top_k, lane);
 }
 
 // ---------------------------------------------------------------------------------------------------

@@ -31,61 +31,14 @@ __global__ void embed_rows_kernel(const int* __restrict__ tokens, const bf16* __
 }
 
 // ---------------------------------------------------------------------------------------------------
-// One CTA per row; every thread owns up to RN_VECS 8-element vectors, all loaded before any arithmetic so the
-// row costs one memory round trip.  H % 8 == 0 and H <= 256 * 8 * RN_VECS.
+// One CTA per row (see add_rmsnorm_row in norm_rope_core.cuh).  H % 8 == 0 and H <= 256 * 8 * RN_VECS.
 __global__ void __launch_bounds__(256)
 add_rmsnorm_kernel(const bf16* __restrict__ update, bf16* __restrict__ residual, const bf16* __restrict__ weight,
                    bf16* __restrict__ out, int H, float eps) {
     GLMB_PDL_PROLOGUE();
     __shared__ float scratch[40];
     const int64_t base = (int64_t)blockIdx.x * H;
-    const int nvec = H >> 3;
-    uint4 rv[RN_VECS], uv[RN_VECS], wv[RN_VECS];
-#pragma unroll
-    for (int i = 0; i < RN_VECS; ++i) {
-        const int v = threadIdx.x + i * 256;
-        if (v < nvec) {
-            rv[i] = *reinterpret_cast<const uint4*>(residual + base + v * 8);
-            uv[i] = update ? *reinterpret_cast<const uint4*>(update + base + v * 8) : make_uint4(0, 0, 0, 0);
-            wv[i] = *reinterpret_cast<const uint4*>(weight + v * 8);
-        }
-    }
-    float s[RN_VECS][8];
-    float ss = 0.f;
-#pragma unroll
-    for (int i = 0; i < RN_VECS; ++i) {
-        const int v = threadIdx.x + i * 256;
-        if (v < nvec) {
-            float r8[8], u8[8];
-            unpack8(rv[i], r8);
-            unpack8(uv[i], u8);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                s[i][e] = update ? __fadd_rn(u8[e], r8[e]) : r8[e];
-                ss = fmaf(s[i][e], s[i][e], ss);
-            }
-        }
-    }
-    const float total = block_sum(ss, scratch);
-    const float inv = 1.0f / sqrtf(total / (float)H + eps);
-#pragma unroll
-    for (int i = 0; i < RN_VECS; ++i) {
-        const int v = threadIdx.x + i * 256;
-        if (v < nvec) {
-            float w8[8];
-            unpack8(wv[i], w8);
-            uint4 o, rr;
-            uint32_t* op = reinterpret_cast<uint32_t*>(&o);
-            uint32_t* rp = reinterpret_cast<uint32_t*>(&rr);
-#pragma unroll
-            for (int e = 0; e < 8; e += 2) {
-                op[e >> 1] = pack_bf16(bf16_round(s[i][e] * inv) * w8[e], bf16_round(s[i][e + 1] * inv) * w8[e + 1]);
-                rp[e >> 1] = pack_bf16(s[i][e], s[i][e + 1]);
-            }
-            *reinterpret_cast<uint4*>(out + base + v * 8) = o;
-            *reinterpret_cast<uint4*>(residual + base + v * 8) = rr;
-        }
-    }
+    add_rmsnorm_row<false>(update ? update + base : nullptr, residual + base, weight, out + base, H, eps, scratch);
 }
 
 // ---------------------------------------------------------------------------------------------------
@@ -98,7 +51,10 @@ __global__ void __launch_bounds__(256) qkv_a_post_generic_kernel(QkvPostArgs a) 
     int pos = a.row_pos[r];
     const int lane_id = a.row_lane[r];
     const bool active = a.row_active ? a.row_active[r] != 0 : true;
-    if (pos < 0 || pos >= a.capacity) {
+    // A position outside the context is reported and the row is computed at a clamped position (no address leaves the
+    // tables), but it is NOT stored: bad metadata leaves the caches as they were and the host poisons the engine.
+    const bool bad_pos = pos < 0 || pos >= a.capacity;
+    if (bad_pos) {
         if (threadIdx.x == 0) raise_status(a.status, GLMB_STATUS_BAD_INDEX);
         pos = min(max(pos, 0), a.capacity - 1);
     }
@@ -107,7 +63,7 @@ __global__ void __launch_bounds__(256) qkv_a_post_generic_kernel(QkvPostArgs a) 
     const int local_row = (pos / page) * a.stripe + pos % a.stripe;
     const int W = a.L + a.rd;
     bf16* cache_row = a.kv_cache + (((int64_t)lane_id * a.layers + a.layer) * a.local_cap + local_row) * W;
-    const bool write_cache = owner && active;
+    const bool write_cache = owner && active && !bad_pos;
 
     // q_a RMSNorm
     // (both sums of squares are accumulated in one sweep of float4 loads and reduced together)
@@ -281,7 +237,8 @@ GLMB_API int glmb_add_rmsnorm(const void* update, void* residual, const void* we
 }
 
 static int g_qkv_fast = 1;
-// 1 (default): the single-round-trip kernel; 0: the generic one (comparison runs).
+// The generic kernel serves geometries beyond the limits of the single-round-trip kernel (q_lora_rank > 2048, kv_lora_rank > 1024,
+// rope > 512, more than 256 index heads); the switch lets the tests run both on a geometry both take.
 GLMB_API void glmb_set_qkv_fast(int enabled) { g_qkv_fast = enabled ? 1 : 0; }
 
 GLMB_API int glmb_qkv_a_post(const QkvPostArgs* args, int rows, void* stream) {

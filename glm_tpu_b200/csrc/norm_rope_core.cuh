@@ -56,6 +56,64 @@ struct QkvPostArgs {
 };
 
 
+// residual <- bf16(update + residual);  out <- bf16(bf16(residual * rsqrt(mean(residual^2) + eps)) * weight)   for one row.
+// Every thread of a 256-thread CTA calls it; every thread owns up to RN_VECS 8-element vectors, all loaded before any arithmetic
+// so the row costs one memory round trip.  FRESH: `update` was written earlier by other CTAs of the SAME launch (a kernel tail):
+// read it past the L1.
+template <bool FRESH>
+__device__ __forceinline__ void add_rmsnorm_row(const bf16* update, bf16* residual, const bf16* weight, bf16* out, int H, float eps,
+                                                float* scratch) {
+    const int nvec = H >> 3;
+    uint4 rv[RN_VECS], uv[RN_VECS], wv[RN_VECS];
+#pragma unroll
+    for (int i = 0; i < RN_VECS; ++i) {
+        const int v = threadIdx.x + i * 256;
+        if (v < nvec) {
+            rv[i] = *reinterpret_cast<const uint4*>(residual + v * 8);
+            if (!update) uv[i] = make_uint4(0, 0, 0, 0);
+            else if (FRESH) uv[i] = __ldcg(reinterpret_cast<const uint4*>(update + v * 8));
+            else uv[i] = *reinterpret_cast<const uint4*>(update + v * 8);
+            wv[i] = *reinterpret_cast<const uint4*>(weight + v * 8);
+        }
+    }
+    float s[RN_VECS][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < RN_VECS; ++i) {
+        const int v = threadIdx.x + i * 256;
+        if (v < nvec) {
+            float r8[8], u8[8];
+            unpack8(rv[i], r8);
+            unpack8(uv[i], u8);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                s[i][e] = update ? __fadd_rn(u8[e], r8[e]) : r8[e];
+                ss = fmaf(s[i][e], s[i][e], ss);
+            }
+        }
+    }
+    const float total = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(total / (float)H + eps);
+#pragma unroll
+    for (int i = 0; i < RN_VECS; ++i) {
+        const int v = threadIdx.x + i * 256;
+        if (v < nvec) {
+            float w8[8];
+            unpack8(wv[i], w8);
+            uint4 o, rr;
+            uint32_t* op = reinterpret_cast<uint32_t*>(&o);
+            uint32_t* rp = reinterpret_cast<uint32_t*>(&rr);
+#pragma unroll
+            for (int e = 0; e < 8; e += 2) {
+                op[e >> 1] = pack_bf16(bf16_round(s[i][e] * inv) * w8[e], bf16_round(s[i][e + 1] * inv) * w8[e + 1]);
+                rp[e >> 1] = pack_bf16(s[i][e], s[i][e + 1]);
+            }
+            *reinterpret_cast<uint4*>(out + v * 8) = o;
+            *reinterpret_cast<uint4*>(residual + v * 8) = rr;
+        }
+    }
+}
+
 // Three block sums with the reduction tree of block_sum (so each is bit-identical to a separate call), one barrier set.
 __device__ __forceinline__ void block_sum3(float& a, float& b, float& c, float (*scratch)[40]) {
     a = warp_sum(a); b = warp_sum(b); c = warp_sum(c);
@@ -82,7 +140,10 @@ __device__ __forceinline__ void qkv_a_post_row(const QkvPostArgs& a, int r, floa
     int pos = a.row_pos[r];
     const int lane_id = a.row_lane[r];
     const bool active = a.row_active ? a.row_active[r] != 0 : true;
-    if (pos < 0 || pos >= a.capacity) {
+    // A position outside the context is reported and the row is computed at a clamped position (no address leaves the
+    // tables), but it is NOT stored: bad metadata leaves the caches as they were and the host poisons the engine.
+    const bool bad_pos = pos < 0 || pos >= a.capacity;
+    if (bad_pos) {
         if (tid == 0) raise_status(a.status, GLMB_STATUS_BAD_INDEX);
         pos = min(max(pos, 0), a.capacity - 1);
     }
@@ -91,7 +152,7 @@ __device__ __forceinline__ void qkv_a_post_row(const QkvPostArgs& a, int r, floa
     const int local_row = (pos / page) * a.stripe + pos % a.stripe;
     const int W = a.L + a.rd, half = a.rd / 2;
     bf16* cache_row = a.kv_cache + (((int64_t)lane_id * a.layers + a.layer) * a.local_cap + local_row) * W;
-    const bool write_cache = owner && active;
+    const bool write_cache = owner && active && !bad_pos;
     const float* c = p + a.Q;
     const float* kx = c + W;
 

@@ -89,11 +89,11 @@ TABLE: dict[str, Row] = {
     "GLM_B200_PDL": Row("flag", True, "Programmatic dependent launch between consecutive kernels (1) or plain stream order (0)."),
     "GLM_B200_OVERLAP": Row("flag", True, "Independent branches of a layer on a second stream (1) or one stream (0)."),
     "GLM_B200_FOLD_Q_POST": Row("flag", True, "Decode: query RoPE folded into q-absorb and the indexer (1) or a kernel of its own (0)."),
+    "GLM_B200_TAILS": Row("flag", True, "Decode: residual add + RMSNorm and router top-k as tails of the kernels before them (1) or launches of their own (0)."),
     "GLM_B200_MERGE_VPROJ": Row("flag", True, "Decode, local keys: chunk merge and value projection in one launch (1) or two (0)."),
     "GLM_B200_NVTX": Row("flag", False, "NVTX ranges per layer and block."),
     "GLM_B200_INDEXER": Row("choice", "tcgen05", "DSA indexer on tcgen05 or the CUDA-core kernel.", ("tcgen05", "cuda")),
     "GLM_B200_INDEXER_ROWS": Row("flag", True, "Prefill chunks: many-rows tcgen05 indexer (1) or the one-row kernel per row (0)."),
-    "GLM_B200_ROUTE_SORT": Row("choice", "kernel", "Prefill expert sort: one launch or library operations.", ("kernel", "torch")),
     "GLM_B200_PREFILL_ATTENTION": Row("choice", "rows", "Prefill attention: one kernel per row block, or split partials + merge.", ("rows", "split")),
     "GLM_B200_PREFILL_GEMM_AR": Row("choice", "fused", "Prefill o_proj / down projections: all-reduce inside the GEMM, or GEMM then NCCL.", ("fused", "nccl")),
     "GLM_B200_TEST_TIMEOUT_SCALE": Row("number", 1.0, "Tests: multiplier for subprocess timeouts."),

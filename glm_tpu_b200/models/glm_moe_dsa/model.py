@@ -137,6 +137,7 @@ class Workspace:
         self.logits = bf(rows, lay.vocab_local)
         self.kv_new = bf(rows, W)
         self.idx_key_new = bf(rows, D)
+        self.tail_counters = torch.zeros(4, dtype=torch.int32, device=dev)  # arrival counters of the kernel tails (left at zero)
         self._sorted = None
         self._route = None
         # many-row workspaces on several GPUs: output and partial-tile slots of the GEMM with the fused all-reduce
@@ -203,7 +204,11 @@ class GlmMoeDsaModel:
         self.side = torch.cuda.Stream(device=self.device) if os.environ.get("GLM_B200_OVERLAP", "1") != "0" else None
         self.fold_q_post = os.environ.get("GLM_B200_FOLD_Q_POST", "1") != "0"
         self.nvtx = os.environ.get("GLM_B200_NVTX", "0") == "1"
-        self.route_sort_kernel = os.environ.get("GLM_B200_ROUTE_SORT", "kernel") != "torch"  # 'torch': the library-op expert sort (A/B runs)
+        # the one-launch expert sort takes up to 256 resident experts and contiguous ids; other shapes use the library-op sort
+        # (`_route_tiles128`), and tests set this attribute to compare the two on shapes both take
+        self.route_sort_kernel = True
+        # decode: residual add + RMSNorm and the router's top-k run as the tail of the kernel before them (last CTA), not as launches
+        self.kernel_tails = os.environ.get("GLM_B200_TAILS", "1") != "0"
         self.merge_vproj = os.environ.get("GLM_B200_MERGE_VPROJ", "1") != "0"  # decode: chunk merge + value projection in one launch
         self.prefill_rows_attention = os.environ.get("GLM_B200_PREFILL_ATTENTION", "rows") != "split"
         # Prefill projections whose K is split over the GPUs use the GEMM with the all-reduce in its epilogue (about 1.2x the
@@ -226,6 +231,16 @@ class GlmMoeDsaModel:
             import logging
 
             logging.getLogger("glm_tpu_b200.fallback").warning("rank %d falls back to %s", self.rank, key)
+
+    def _norm_tail(self, ws: "Workspace", slot: int, update: torch.Tensor, weight: torch.Tensor | None, rows: int):
+        """The residual add + RMSNorm that consumes ``update`` as a tail of the kernel that writes it, or None where it stays a launch
+        of its own (several rows, tracing, switched off, no norm follows)."""
+        if weight is None or not self.kernel_tails or self.trace is not None or rows > native.TAIL_MAX_NORM_ROWS:
+            return None
+        H = self.g.hidden_size
+        if H % 8 or H > 8192 or not update.is_contiguous():
+            return None
+        return native.add_rmsnorm_tail(ws.tail_counters[slot:], update, ws.residual, weight, ws.x, rows, H, self.g.rms_norm_eps)
 
     def _allreduce_rows(self, partial_f32: torch.Tensor) -> torch.Tensor:
         import torch.distributed as dist
@@ -295,7 +310,8 @@ class GlmMoeDsaModel:
 
     # ------------------------------------------------------------------------------ attention
     def _attention(self, ws: Workspace, lw: LayerWeights, layer: int, rows: int, row_pos, row_lane, row_active, state: DecoderState,
-                   decode: bool, max_ctx: int, lane_of_rows: int | None = None):
+                   decode: bool, max_ctx: int, lane_of_rows: int | None = None) -> bool:
+        """Returns True when the post-attention residual add + RMSNorm already ran (as the tail of the output projection)."""
         g, lay, cache = self.g, self.layout, self.cache
         full = g.indexer_types[layer] == "full"
         Q, L, rd, W = g.q_lora_rank, g.kv_lora_rank, g.qk_rope_head_dim, g.kv_row_width
@@ -406,12 +422,15 @@ class GlmMoeDsaModel:
             else:
                 self._merge_partials_nccl(ws, r0, n)
         # value projection per head, then the K-split output projection with its reduction
+        normed = False
         if decode:
             if not merged_vproj:
                 native.skinny_bf16(ws.o_lat, lw.kv_b[:, g.qk_nope_head_dim :, :], ws.attn_v, native.SK_OUT_BF16, rows=rows, N=g.v_head_dim,
                                    K=L, xs=hl * L, ws=L, os_=hl * g.v_head_dim, batch=hl, xb=L, wb=g.kv_b_rows_per_head * L, ob=g.v_head_dim)
             if fused or self.world == 1 or self.emulated_shard:
-                native.skinny_bf16(ws.attn_v[:rows], lw.w_o, ws.attn_out, native.SK_OUT_ALLREDUCE_BF16, comm=kc, channel=native.CH_ATTN)
+                tail = self._norm_tail(ws, 1, ws.attn_out, lw.post_norm, rows)
+                native.skinny_bf16(ws.attn_v[:rows], lw.w_o, ws.attn_out, native.SK_OUT_ALLREDUCE_BF16, comm=kc, channel=native.CH_ATTN, tail=tail)
+                normed = tail is not None
             else:
                 native.skinny_bf16(ws.attn_v[:rows], lw.w_o, ws.partial, native.SK_OUT_F32)
                 ws.attn_out[:rows] = self._allreduce_rows(ws.partial[:rows]).to(torch.bfloat16)
@@ -430,6 +449,7 @@ class GlmMoeDsaModel:
         if self.trace is not None:
             self.trace.setdefault("attn_out", {})[layer] = ws.attn_out[:rows].clone()
             self.trace.setdefault("kv_new", {})[layer] = ws.kv_new[:rows].clone()
+        return normed
 
     def select_keys_decode(self, ws: Workspace, state: DecoderState, layer: int, rows: int) -> None:
         """Indexer scores and the exact top-k of a layer with its own indexer, for the rows of a decode step whose q_b projection
@@ -506,7 +526,9 @@ class GlmMoeDsaModel:
         ws.o_lat[r0 : r0 + n] = out.to(torch.bfloat16)
 
     # ------------------------------------------------------------------------------ MLP
-    def _mlp(self, ws: Workspace, lw: LayerWeights, layer: int, rows: int, decode: bool):
+    def _mlp(self, ws: Workspace, lw: LayerWeights, layer: int, rows: int, decode: bool, next_norm: torch.Tensor | None = None) -> bool:
+        """``next_norm``: the weight of the RMSNorm that consumes this block's output (the next layer's input norm, or the final
+        norm).  Returns True when that residual add + RMSNorm already ran as the tail of the block's last kernel."""
         g, lay = self.g, self.layout
         H = g.hidden_size
         fused = ws.peer_visible
@@ -516,8 +538,10 @@ class GlmMoeDsaModel:
             if decode:
                 native.skinny_bf16_swiglu(x, lw.dense_gate, lw.dense_up, ws.dense_act)
                 if fused or self.world == 1 or self.emulated_shard:
+                    tail = self._norm_tail(ws, 2, ws.update, next_norm, rows)
                     native.skinny_bf16(ws.dense_act[:rows], lw.dense_down, ws.update, native.SK_OUT_ALLREDUCE_BF16, comm=kc,
-                                       channel=native.CH_MLP)
+                                       channel=native.CH_MLP, tail=tail)
+                    return tail is not None
                 else:
                     native.skinny_bf16(ws.dense_act[:rows], lw.dense_down, ws.partial, native.SK_OUT_F32)
                     ws.update[:rows] = self._allreduce_rows(ws.partial[:rows]).to(torch.bfloat16)
@@ -531,7 +555,7 @@ class GlmMoeDsaModel:
                         ws.update[:rows] = fused_out
                     else:
                         ws.update[:rows] = self._allreduce_rows(self._mm(act, lw.dense_down, f32=True)).to(torch.bfloat16)
-            return
+            return False
         # whole experts: this GPU's `el` experts from `ebase`, full width; sliced: I columns of every expert
         tk, I, E = g.routed_top_k, lay.moe_cols_local, g.num_routed_experts
         el, ebase = lay.experts_resident, lay.expert_base
@@ -544,8 +568,12 @@ class GlmMoeDsaModel:
             with torch.cuda.stream(self.side):
                 native.skinny_bf16_swiglu(x, lw.shared_gate, lw.shared_up, ws.act_shared)
                 native.skinny_bf16(ws.act_shared[:rows], lw.shared_down, ws.partial, native.SK_OUT_F32)
-        self._linear_f32(x, lw.router_w, ws.router_logits, decode)
-        native.router_topk(ws.router_logits[:rows], lw.router_bias, tk, ws.topk_ids, ws.topk_w)
+        if decode and self.kernel_tails and E <= 256 and tk <= 32 and ws.topk_ids.is_contiguous():
+            native.skinny_bf16(x, lw.router_w, ws.router_logits, native.SK_OUT_F32, N=E, K=lw.router_w.shape[1],
+                               tail=native.router_topk_tail(ws.tail_counters[0:], ws.router_logits, lw.router_bias, tk, ws.topk_ids, ws.topk_w, rows))
+        else:
+            self._linear_f32(x, lw.router_w, ws.router_logits, decode)
+            native.router_topk(ws.router_logits[:rows], lw.router_bias, tk, ws.topk_ids, ws.topk_w)
         if self.trace is not None:
             self.trace.setdefault("topk_ids", {})[layer] = ws.topk_ids[:rows].clone()
             self.trace.setdefault("topk_w", {})[layer] = ws.topk_w[:rows].clone()
@@ -583,8 +611,10 @@ class GlmMoeDsaModel:
             act = self._swiglu(self._mm(x, lw.shared_gate), self._mm(x, lw.shared_up))
             shared_partial = self._mm(act, lw.shared_down, f32=True)
         if one_launch:
+            tail = self._norm_tail(ws, 2, ws.update, next_norm, rows)
             native.moe_down_combine(ws.act, ws.topk_w, ws.topk_ids, lw.exp_down_bits, lw.exp_down_scale, shared_partial, rows, tk,
-                                    g.routed_scaling_factor, ws.update, kc, native.CH_MLP)
+                                    g.routed_scaling_factor, ws.update, kc, native.CH_MLP, tail=tail)
+            return tail is not None
         elif fused or self.world == 1 or self.emulated_shard:
             native.moe_combine(ws.dw, ws.topk_ids, shared_partial, rows, tk, H, ebase, el, g.routed_scaling_factor, False, ws.update,
                                None, kc, native.CH_MLP)
@@ -664,19 +694,27 @@ class GlmMoeDsaModel:
         update = None
         mark = torch.cuda.nvtx.range_push if self.nvtx else (lambda name: None)
         done = torch.cuda.nvtx.range_pop if self.nvtx else (lambda: None)
-        for i, lw in enumerate(self.w.layers):
+        # Each residual add + RMSNorm runs as the tail of the kernel whose output it consumes where that kernel can carry it
+        # (decode, one or two rows); `normed` says that ws.residual and ws.x are already those of the next block.
+        normed = False
+        layers = self.w.layers
+        for i, lw in enumerate(layers):
             mark(f"layer{i}.attention.{g.indexer_types[i]}")  # region names for profilers (GLM_B200_NVTX=1)
-            native.add_rmsnorm(update, ws.residual[:rows], lw.input_norm, ws.x, g.rms_norm_eps)
-            self._attention(ws, lw, i, rows, row_pos, row_lane, row_active, state, decode, max_ctx, lane_of_rows)
+            if not normed:
+                native.add_rmsnorm(update, ws.residual[:rows], lw.input_norm, ws.x, g.rms_norm_eps)
+            normed = self._attention(ws, lw, i, rows, row_pos, row_lane, row_active, state, decode, max_ctx, lane_of_rows)
             done()
             mark(f"layer{i}.mlp.{g.mlp_layer_types[i]}")
-            native.add_rmsnorm(ws.attn_out, ws.residual[:rows], lw.post_norm, ws.x, g.rms_norm_eps)
-            self._mlp(ws, lw, i, rows, decode)
+            if not normed:
+                native.add_rmsnorm(ws.attn_out, ws.residual[:rows], lw.post_norm, ws.x, g.rms_norm_eps)
+            next_norm = layers[i + 1].input_norm if i + 1 < len(layers) else self.w.final_norm
+            normed = bool(self._mlp(ws, lw, i, rows, decode, next_norm))
             done()
             update = ws.update
             if self.trace is not None:
                 self.trace.setdefault("update", {})[i] = ws.update[:rows].clone()
-        native.add_rmsnorm(update, ws.residual[:rows], self.w.final_norm, ws.x, g.rms_norm_eps)
+        if not normed:
+            native.add_rmsnorm(update, ws.residual[:rows], self.w.final_norm, ws.x, g.rms_norm_eps)
         hs = head_rows or slice(0, rows)
         xh = ws.x[hs]
         n = xh.shape[0]

@@ -190,3 +190,52 @@ def test_inactive_lane_is_frozen(native_lib):
     assert int(runner.state.positions[0]) == 17 + 5
     runner.peer.check_status()
     runner.close()
+
+
+def test_bad_cache_metadata_is_reported_and_leaves_the_caches_unchanged(native_lib):
+    """A position outside the context (corrupted device metadata): the step reports BAD_INDEX, stores nothing into the KV and
+    index caches, faults nothing, and the engine refuses to go on (the status word fails the validity vote)."""
+    from glm_tpu_b200.engine import request as rq
+    from glm_tpu_b200.engine.llm_engine import LLMEngine
+    from glm_tpu_b200.exceptions import EngineFailure
+    from glm_tpu_b200.ops import native
+    from glm_tpu_b200.runner.gpu_runner import build_runner
+
+    g = tiny_geometry()
+    ckpt = random_checkpoint(g, seed=2)
+    for graphs in (False, True):
+        runner = build_runner(g, checkpoint=ckpt, context_capacity=64, lanes=2, stripe=16, use_graphs=graphs, prefill_chunk=16)
+        runner.prefill(0, list(range(3, 20)))
+        runner.prefill(1, list(range(40, 52)))
+        runner.build_decode_program()
+        runner.decode_step()
+        torch.cuda.synchronize()
+        assert runner.peer.read_status() == 0
+        runner.state.positions[1] = 64 + 9  # beyond the 64-slot context
+        kv, idx = runner.state.kv_cache.clone(), runner.state.index_cache.clone()
+        runner.decode_step()
+        torch.cuda.synchronize()
+        assert runner.peer.read_status() & native.STATUS_BAD_INDEX
+        assert torch.equal(runner.state.kv_cache[1].view(torch.int16), kv[1].view(torch.int16))  # the bad lane stored nothing
+        assert torch.equal(runner.state.index_cache[1].view(torch.int16), idx[1].view(torch.int16))
+        assert not torch.equal(runner.state.kv_cache[0].view(torch.int16), kv[0].view(torch.int16))  # the healthy lane did
+        runner.close()
+    # through the engine: the same corruption in the middle of a request poisons it
+    runner = build_runner(g, checkpoint=ckpt, context_capacity=64, lanes=1, stripe=16, use_graphs=True, prefill_chunk=16)
+    profile = rq.RequestProfile(vocab_size=g.vocab_size, eos_ids=tuple(g.eos_ids), capacities=(64,), prompt_limits={64: 32},
+                                concurrent_capacity=64, max_new=32)
+    engine = LLMEngine(runner, profile=profile)
+    inner, calls = runner.decode_step, [0]
+
+    def corrupting():
+        calls[0] += 1
+        if calls[0] == 3:
+            runner.state.positions[0] = -5
+        inner()
+
+    runner.decode_step = corrupting
+    request = rq.from_token_ids(list(range(3, 12)), request_id="r", max_new_tokens=10, context_capacity=64, profile=profile)
+    with pytest.raises(EngineFailure):
+        engine.generate(request)
+    assert engine.poisoned
+    runner.close()
