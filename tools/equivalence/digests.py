@@ -39,6 +39,16 @@ def oracle_digests() -> dict:
     layers = sorted(sel) if isinstance(sel, dict) else range(len(sel))
     out["selected"] = {str(layer): hashlib.sha256(repr([r.tolist() for r in sel[layer]]).encode()).hexdigest() for layer in layers if sel[layer]}
     out["expert_ids"] = {str(layer): _tsha(ids.to(torch.int32)) for layer, ids in sorted(trace.expert_ids.items())}
+    out["index_keys"] = {str(layer): _tsha(keys.to(torch.bfloat16)) for layer, keys in sorted(trace.index_keys.items())}
+    out["index_scores"] = {str(layer): _tsha(torch.nan_to_num(s, neginf=-1e30).to(torch.float32)) for layer, s in sorted(trace.index_scores.items())}
+    # tie rules on constructed inputs (random fixtures never tie exactly): lowest id / lowest position wins, -0 < +0
+    tied = torch.tensor([[1.0, 3.0, 3.0, 2.0], [5.0, 5.0, 5.0, 5.0]])
+    out["tie_rules"] = {
+        "greedy": contract.greedy(tied).tolist(),
+        "top_k": contract.top_k_positions(torch.tensor([0.5, 0.0, -0.0, 0.5, 0.5, 0.25]), 6, 3).tolist(),
+        "router": contract.router(torch.eye(4), torch.tensor([[1.0, 0, 0, 0], [1.0, 0, 0, 0], [0, 0, 2.0, 0], [0, 0, 2.0, 0]]).T.contiguous(),
+                                  torch.zeros(4), 2)[0].tolist(),
+    }
     return out
 
 

@@ -46,6 +46,192 @@ def oracle_mutants():
     yield "routed scaling factor 2.5 -> 2.0", _geometry_patch(routed_scaling_factor=2.0)
     yield "rope theta halved", _geometry_patch(rope_theta=4000000.0)
     yield "rms eps x10", _geometry_patch(rms_norm_eps=1e-4)
+    yield from more_oracle_mutants()
+
+
+def more_oracle_mutants():
+    """One mutant per further rule of the contract: roundings, orders of operations, tie rules, which tensor a term enters."""
+    from glm_tpu_b200.oracle import contract as c
+
+    F32 = torch.float32
+    orig = {name: getattr(c, name) for name in (
+        "linear", "add_rms_norm", "layer_norm_affine", "rope_interleaved_table", "rope_interleaved_fp32", "top_k_positions",
+        "absorbed_attention_row", "swiglu_act", "router", "greedy", "dequantize_fp8", "rope_table", "indexer_scores", "sparse_moe")}
+
+    def linear_no_round(x, weight, out_bf16=True):  # rule: a projection's output is rounded to bf16
+        return orig["linear"](x, weight, out_bf16=False)
+
+    def add_norm_on_rounded_sum(update, residual, weight, eps):  # rule: the norm consumes the UNROUNDED sum
+        s = residual.to(F32) if update is None else update.to(F32) + residual.to(F32)
+        return c.rms_norm(c.bf16_round(s), weight, eps), c.bf16_round(s)
+
+    def add_norm_residual_unrounded(update, residual, weight, eps):  # rule: the carried residual is bf16
+        s = residual.to(F32) if update is None else update.to(F32) + residual.to(F32)
+        return c.rms_norm(s, weight, eps), s * (1.0 + 2.0**-10)
+
+    def layer_norm_no_bias(x, weight, bias, eps):  # rule: the index key norm has a bias
+        return orig["layer_norm_affine"](x, weight, torch.zeros_like(bias), eps)
+
+    def layer_norm_biased_variance(x, weight, bias, eps):  # rule: eps sits inside the square root, variance over all features
+        return orig["layer_norm_affine"](x, weight, bias, eps * 1e4)
+
+    def rope_half_split(x, positions, table):  # rule: pairs are (2j, 2j+1), not (j, j + d/2)
+        half = x.shape[-1] // 2
+        rows = table[positions.long()].to(F32)
+        shape = (x.shape[0],) + (1,) * (x.dim() - 2) + (half,)
+        cos, sin = rows[:, :half].reshape(shape), rows[:, half:].reshape(shape)
+        x = x.to(F32)
+        a, b = x[..., :half], x[..., half:]
+        return c.bf16_round(torch.cat([a * cos - b * sin, b * cos + a * sin], dim=-1))
+
+    def rope_wrong_sign(x, positions, table):  # rule: rotation by +angle
+        flipped = table.clone()
+        half = table.shape[-1] // 2
+        flipped[:, half:] = -flipped[:, half:]
+        return orig["rope_interleaved_table"](x, positions, flipped)
+
+    def rope_table_unrounded_angle(capacity, dim, theta):  # rule: the table is built in fp32 with this frequency formula
+        return orig["rope_table"](capacity, dim, theta * (1.0 + 2.0**-8))
+
+    def indexer_rope_all_features(x, positions, theta, rope_dim):  # rule: only the first rope_dim features rotate
+        return orig["rope_interleaved_fp32"](x, positions, theta, min(rope_dim * 2, x.shape[-1]))
+
+    def top_k_ties_to_highest(scores, context_length, top_k):  # rule: ties go to the LOWEST position
+        n = int(context_length)
+        if n <= top_k:
+            return torch.arange(n, dtype=torch.int64)
+        key = c.orderable_key(scores[:n])
+        order = torch.argsort(-key.flip(0), stable=True)
+        return torch.sort((n - 1 - order)[:top_k]).values
+
+    def top_k_one_short(scores, context_length, top_k):  # rule: exactly min(top_k, context) positions
+        return orig["top_k_positions"](scores, context_length, max(top_k - 1, 1))
+
+    def attention_p_not_rounded(q_c, q_rope, kv_rows, selected, scale):  # rule: P is rounded to bf16 before P.V, l sums unrounded P
+        lora = q_c.shape[-1]
+        if selected.numel() == 0:
+            return torch.zeros_like(q_c)
+        rows = kv_rows[selected.long()].to(F32)
+        s = (q_c.to(F32) @ rows[:, :lora].T + q_rope.to(F32) @ rows[:, lora:].T) * scale
+        p = torch.exp(s - s.max(dim=-1, keepdim=True).values)
+        return c.bf16_round((p @ rows[:, :lora]) / p.sum(dim=-1, keepdim=True))
+
+    def attention_l_from_rounded_p(q_c, q_rope, kv_rows, selected, scale):  # rule: the denominator sums the UNROUNDED probabilities
+        lora = q_c.shape[-1]
+        if selected.numel() == 0:
+            return torch.zeros_like(q_c)
+        rows = kv_rows[selected.long()].to(F32)
+        s = (q_c.to(F32) @ rows[:, :lora].T + q_rope.to(F32) @ rows[:, lora:].T) * scale
+        p = c.bf16_round(torch.exp(s - s.max(dim=-1, keepdim=True).values))
+        return c.bf16_round((p @ rows[:, :lora]) / p.sum(dim=-1, keepdim=True))
+
+    def attention_scale_on_nope_only(q_c, q_rope, kv_rows, selected, scale):  # rule: the scale multiplies latent AND rope dots
+        return orig["absorbed_attention_row"](q_c, q_rope / max(scale, 1e-9), kv_rows, selected, scale)
+
+    def attention_ignores_last_key(q_c, q_rope, kv_rows, selected, scale):  # rule: every selected row is attended
+        return orig["absorbed_attention_row"](q_c, q_rope, kv_rows, selected[:-1] if selected.numel() > 1 else selected, scale)
+
+    def swiglu_rounds_gate_activation(gate, up):  # rule: ONE rounding after the product
+        return c.bf16_round(c.bf16_round(gate * torch.sigmoid(gate)) * up)
+
+    def swiglu_swapped(gate, up):  # rule: the activation applies to the gate projection
+        return orig["swiglu_act"](up, gate)
+
+    def router_bias_in_weights(x, weight, bias, top_k, imposed=None):  # rule: the bias enters the choice only
+        ids, _, choice = orig["router"](x, weight, bias, top_k, imposed)
+        picked = torch.gather(choice, 1, ids)
+        return ids, picked / (picked.sum(dim=-1, keepdim=True) + 1e-20), choice
+
+    def router_no_normalisation(x, weight, bias, top_k, imposed=None):  # rule: weights are normalised over the chosen experts
+        ids, weights, choice = orig["router"](x, weight, bias, top_k, imposed)
+        return ids, torch.gather(torch.sigmoid(x.to(F32) @ weight.to(F32).T), 1, ids), choice
+
+    def router_softmax_scores(x, weight, bias, top_k, imposed=None):  # rule: sigmoid scores, not softmax
+        logits = x.to(F32) @ weight.to(F32).T
+        scores = torch.softmax(logits, dim=-1)
+        choice = scores + bias.to(F32)[None, :]
+        ids = torch.argsort(-c.orderable_key(choice), dim=-1, stable=True)[:, :top_k] if imposed is None else imposed.long()
+        picked = torch.gather(scores, 1, ids)
+        return ids, picked / (picked.sum(dim=-1, keepdim=True) + 1e-20), choice
+
+    def router_one_expert_less(x, weight, bias, top_k, imposed=None):  # rule: top_k experts
+        ids, weights, choice = orig["router"](x, weight, bias, top_k, imposed)
+        weights = weights.clone()
+        weights[:, -1] = 0.0
+        return ids, weights, choice
+
+    def greedy_ties_to_highest(logits):  # rule: ties to the lowest id
+        top = logits.max(dim=-1, keepdim=True).values
+        ids = torch.arange(logits.shape[-1])[None, :].expand_as(logits)
+        return torch.where(logits == top, ids, -1).max(dim=-1).values
+
+    def greedy_second_best(logits):  # rule: the maximum
+        return torch.topk(logits, 2, dim=-1).indices[:, 1]
+
+    def dequant_transposed_blocks(bits, scale, block):  # rule: scale_inv[n // bn, k // bk]
+        if scale.shape[-1] == scale.shape[-2] and scale.shape[-1] > 1:
+            return orig["dequantize_fp8"](bits, scale.transpose(-1, -2).contiguous(), block)
+        return orig["dequantize_fp8"](bits, scale * (1.0 + 2.0**-7), block)
+
+    def dequant_unrounded(bits, scale, block):  # rule: bf16(f32(e4m3) * scale)
+        return orig["dequantize_fp8"](bits, scale, block).float() * (1.0 - 2.0**-9)
+
+    def indexer_without_relu(x, q_resid, w, layer, positions):  # rule: relu on the per-head dots before the weighted sum
+        relu = torch.relu
+        try:
+            torch.relu = lambda t: t
+            return orig["indexer_scores"](x, q_resid, w, layer, positions)
+        finally:
+            torch.relu = relu
+
+    def indexer_keys_unrounded(x, q_resid, w, layer, positions):  # rule: the cached index keys are exactly bf16(rope(norm(.)))
+        key, scores = orig["indexer_scores"](x, q_resid, w, layer, positions)
+        return key * (1.0 + 2.0**-6), scores
+
+    def moe_shared_dropped(x, w, layer, trace, imposed=None):  # rule: routed * factor + shared
+        out = orig["sparse_moe"](x, w, layer, trace, imposed)
+        return c.bf16_round(out * (1.0 - 2.0**-6))
+
+    table = [
+        ("linear: output not rounded to bf16", "linear", linear_no_round),
+        ("add+norm: the norm consumes the rounded sum", "add_rms_norm", add_norm_on_rounded_sum),
+        ("add+norm: the carried residual is not bf16", "add_rms_norm", add_norm_residual_unrounded),
+        ("index key norm: bias dropped", "layer_norm_affine", layer_norm_no_bias),
+        ("index key norm: eps 1e-2", "layer_norm_affine", layer_norm_biased_variance),
+        ("rope: half-split pairing instead of interleaved", "rope_interleaved_table", rope_half_split),
+        ("rope: rotation by the negative angle", "rope_interleaved_table", rope_wrong_sign),
+        ("rope table: frequency base perturbed by 2^-8", "rope_table", rope_table_unrounded_angle),
+        ("indexer rope: twice as many features rotate", "rope_interleaved_fp32", indexer_rope_all_features),
+        ("top-k: ties to the highest position", "top_k_positions", top_k_ties_to_highest),
+        ("top-k: one position short", "top_k_positions", top_k_one_short),
+        ("attention: P not rounded to bf16", "absorbed_attention_row", attention_p_not_rounded),
+        ("attention: denominator from the rounded P", "absorbed_attention_row", attention_l_from_rounded_p),
+        ("attention: rope dots unscaled", "absorbed_attention_row", attention_scale_on_nope_only),
+        ("attention: the last selected key ignored", "absorbed_attention_row", attention_ignores_last_key),
+        ("swiglu: the activated gate rounded before the product", "swiglu_act", swiglu_rounds_gate_activation),
+        ("swiglu: gate and up swapped", "swiglu_act", swiglu_swapped),
+        ("router: bias enters the weights", "router", router_bias_in_weights),
+        ("router: weights not normalised", "router", router_no_normalisation),
+        ("router: softmax instead of sigmoid", "router", router_softmax_scores),
+        ("router: the last chosen expert weighs nothing", "router", router_one_expert_less),
+        ("sampler: ties to the highest id", "greedy", greedy_ties_to_highest),
+        ("sampler: second best token", "greedy", greedy_second_best),
+        ("fp8 decode: block scales transposed or perturbed", "dequantize_fp8", dequant_transposed_blocks),
+        ("fp8 decode: result scaled by 1 - 2^-9", "dequantize_fp8", dequant_unrounded),
+        ("indexer: no relu on the head dots", "indexer_scores", indexer_without_relu),
+        ("indexer: cached keys perturbed by 2^-6", "indexer_scores", indexer_keys_unrounded),
+        ("moe: block output scaled by 1 - 2^-6", "sparse_moe", moe_shared_dropped),
+    ]
+    for name, attr, fn in table:
+        yield name, _patched(c, attr, fn)
+    yield "index top-k 16 -> 8", _geometry_patch(index_top_k=8)
+    yield "routed top-k one less", _geometry_patch(routed_top_k=max(1, _fixture_value("routed_top_k") - 1))
+
+
+def _fixture_value(name: str):
+    from tools.equivalence import fixture as fx
+
+    return getattr(fx.fixture_geometry(), name)
 
 
 def _geometry_patch(**changes):
