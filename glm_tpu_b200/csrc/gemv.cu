@@ -380,6 +380,7 @@ GLMB_API int glmb_skinny_bf16(const void* x, int64_t xs, int rows, const void* w
     if (rows < 1 || rows > GLMB_MAX_ROWS || (K & 7) || (xs & 7) || (ws & 7) || (xb & 7) || (wb & 7) || batch < 1) return 1;
     const KernelTail tail = tail_or_null ? *tail_or_null : no_tail();
     if (tail.kind == TAIL_ADD_RMSNORM && (mode != SK_OUT_ALLREDUCE_BF16 || tail.rows > 2 || (tail.H & 7) || tail.H > 256 * 8 * RN_VECS)) return 1;
+    if (tail.kind == TAIL_QKV_A_POST && (mode != SK_OUT_F32 || tail.rows > 2 || !tail.qkv)) return 1;
     if (tail.kind == TAIL_ROUTER_TOPK && (mode != SK_OUT_F32 || tail.rows > SK_WARPS || tail.E > 256 || tail.top_k > 32 || tail.top_k > tail.E)) return 1;
     int ks = pick_ksplit(ceil_div(N, 2) * batch, K);
     PeerComm c = comm ? *comm : single_comm();

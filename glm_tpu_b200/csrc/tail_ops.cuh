@@ -5,6 +5,8 @@
 //   TAIL_ADD_RMSNORM  residual <- bf16(update + residual); x <- RMSNorm(residual) * weight, where `update` is the bf16 output of the
 //                     kernel itself (an all-reduced projection); rows <= 2, blockDim.x == 256
 //   TAIL_ROUTER_TOPK  top-k of the router logits the kernel just produced (fp32 output), one warp per row; E <= 256
+//   TAIL_QKV_A_POST   the LoRA norms, RoPE and cache-row write that consume the fused q_a | kv_a | index projection the kernel just
+//                     produced (fp32 output); rows <= 2; its arguments are a QkvPostArgs block in device memory
 // The arithmetic is that of add_rmsnorm_kernel / router_topk256_kernel (the same device functions), so the bits are the same; the
 // counter is left at zero, so a captured graph replays the kernel unchanged.
 #pragma once
@@ -12,7 +14,7 @@
 #include "common.cuh"
 #include "norm_rope_core.cuh"
 
-enum { TAIL_NONE = 0, TAIL_ADD_RMSNORM = 1, TAIL_ROUTER_TOPK = 2 };
+enum { TAIL_NONE = 0, TAIL_ADD_RMSNORM = 1, TAIL_ROUTER_TOPK = 2, TAIL_QKV_A_POST = 3 };
 
 struct KernelTail {
     int kind;
@@ -33,6 +35,8 @@ struct KernelTail {
     int64_t logits_stride;
     int E;
     int top_k;
+    // TAIL_QKV_A_POST
+    const QkvPostArgs* qkv;  // device memory; proj = the host kernel's output
 };
 
 // Router choice of one row by one warp (E <= 256): sigmoid scores, the correction bias enters the choice only, ties to the lowest
@@ -81,10 +85,12 @@ __device__ __forceinline__ void router_topk256_row(const float* lg, const float*
     if (lane < top_k) weights[lane] = my_score / (picked_sum + 1e-20f);
 }
 
-// Every thread of the CTA calls it once, after the CTA's last store.  `scratch`: >= 40 floats of shared memory.
+// Every thread of the CTA (256 threads) calls it once, after the CTA's last store.  `scratch`: >= 40 floats of shared memory.
 __device__ __forceinline__ void run_kernel_tail(const KernelTail& t, float* scratch) {
     if (t.kind == TAIL_NONE) return;
     __shared__ int s_last;
+    __shared__ float s_qkv_scratch[3][40];
+    __shared__ float s_qkv_key[256];
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -99,6 +105,12 @@ __device__ __forceinline__ void run_kernel_tail(const KernelTail& t, float* scra
         for (int r = 0; r < t.rows; ++r)
             add_rmsnorm_row<true>(t.update + (int64_t)r * t.H, t.residual + (int64_t)r * t.H, t.weight, t.x_out + (int64_t)r * t.H, t.H, t.eps,
                                   scratch);
+    } else if (t.kind == TAIL_QKV_A_POST) {
+        const QkvPostArgs a = *t.qkv;
+        for (int r = 0; r < t.rows; ++r) {
+            qkv_a_post_row(a, r, s_qkv_scratch, s_qkv_key);
+            __syncthreads();
+        }
     } else if (t.kind == TAIL_ROUTER_TOPK) {
         const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
         if (warp < t.rows)

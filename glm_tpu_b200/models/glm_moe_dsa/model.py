@@ -138,6 +138,7 @@ class Workspace:
         self.kv_new = bf(rows, W)
         self.idx_key_new = bf(rows, D)
         self.tail_counters = torch.zeros(4, dtype=torch.int32, device=dev)  # arrival counters of the kernel tails (left at zero)
+        self.qkv_args: dict = {}  # layer -> (bytes, device block) of the QkvPostArgs the projection's tail reads
         self._sorted = None
         self._route = None
         # many-row workspaces on several GPUs: output and partial-tile slots of the GEMM with the fused all-reduce
@@ -207,8 +208,12 @@ class GlmMoeDsaModel:
         # the one-launch expert sort takes up to 256 resident experts and contiguous ids; other shapes use the library-op sort
         # (`_route_tiles128`), and tests set this attribute to compare the two on shapes both take
         self.route_sort_kernel = True
-        # decode: residual add + RMSNorm and the router's top-k run as the tail of the kernel before them (last CTA), not as launches
-        self.kernel_tails = os.environ.get("GLM_B200_TAILS", "1") != "0"
+        # decode: residual add + RMSNorm ("norm"), the router's top-k ("router") and the q_a / kv_a post-processing ("qkv") can run as
+        # the tail of the kernel before them (its last CTA) instead of as launches of their own.  Off by default: with programmatic
+        # dependent launch a kernel boundary costs less than the fence + arrival counter + single-CTA work of a tail (measured).
+        from glm_tpu_b200 import envs
+
+        self.tail_kinds = set(envs.GLM_B200_TAILS)
         self.merge_vproj = os.environ.get("GLM_B200_MERGE_VPROJ", "1") != "0"  # decode: chunk merge + value projection in one launch
         self.prefill_rows_attention = os.environ.get("GLM_B200_PREFILL_ATTENTION", "rows") != "split"
         # Prefill projections whose K is split over the GPUs use the GEMM with the all-reduce in its epilogue (about 1.2x the
@@ -232,10 +237,28 @@ class GlmMoeDsaModel:
 
             logging.getLogger("glm_tpu_b200.fallback").warning("rank %d falls back to %s", self.rank, key)
 
+    def _qkv_args_on_device(self, ws: "Workspace", layer: int, a) -> torch.Tensor | None:
+        """The layer's ``QkvPostArgs`` in device memory (the kernel tail reads them there).  They are constant for a workspace and a
+        decoder state, so the upload happens on the first eager step; a block that changes while a graph is being captured means
+        the capture would freeze stale arguments, which is refused."""
+        if not native.qkv_a_post_fits_tail(a):
+            return None
+        raw = bytes(a)
+        cached = ws.qkv_args.get(layer)
+        if cached is None or cached[0] != raw:
+            if torch.cuda.is_current_stream_capturing():
+                return None  # fall back to the separate launch for this capture (never seen in practice: the warm-up step uploads)
+            block = cached[1] if cached is not None else torch.empty(len(raw), dtype=torch.uint8, device=self.device)
+            block.copy_(torch.frombuffer(bytearray(raw), dtype=torch.uint8))
+            torch.cuda.current_stream(self.device).synchronize()
+            ws.qkv_args[layer] = (raw, block)
+            cached = ws.qkv_args[layer]
+        return cached[1]
+
     def _norm_tail(self, ws: "Workspace", slot: int, update: torch.Tensor, weight: torch.Tensor | None, rows: int):
         """The residual add + RMSNorm that consumes ``update`` as a tail of the kernel that writes it, or None where it stays a launch
         of its own (several rows, tracing, switched off, no norm follows)."""
-        if weight is None or not self.kernel_tails or self.trace is not None or rows > native.TAIL_MAX_NORM_ROWS:
+        if weight is None or "norm" not in self.tail_kinds or self.trace is not None or rows > native.TAIL_MAX_NORM_ROWS:
             return None
         H = self.g.hidden_size
         if H % 8 or H > 8192 or not update.is_contiguous():
@@ -324,7 +347,6 @@ class GlmMoeDsaModel:
         xf = fused and gather                      # ... inside the kernels
         kx = kc if xf else None
         x = ws.x[:rows]
-        self._linear_f32(x, lw.w_qkv_a, ws.proj_a, decode)
         a = native.QkvPostArgs()
         a.proj, a.proj_stride = ws.proj_a.data_ptr(), ws.proj_a.stride(0)
         a.q_norm_w, a.kv_norm_w = lw.q_a_norm.data_ptr(), lw.kv_a_norm.data_ptr()
@@ -343,7 +365,14 @@ class GlmMoeDsaModel:
         a.local_cap, a.stripe, a.world, a.rank, a.capacity = cache.local_capacity, cache.stripe, cw, cr, cache.context_capacity
         a.eps, a.key_eps, a.head_scale = g.rms_norm_eps, cache.dsa.key_norm_eps, self.head_scale
         a.status = self.peer.status_ptr
-        native.qkv_a_post(a, rows)
+        args_dev = self._qkv_args_on_device(ws, layer, a) if decode and rows <= native.TAIL_MAX_NORM_ROWS and "qkv" in self.tail_kinds else None
+        if args_dev is not None:
+            # the norms, RoPE and cache-row write ride the projection as its tail: one launch instead of two
+            native.skinny_bf16(x, lw.w_qkv_a, ws.proj_a, native.SK_OUT_F32, N=lw.w_qkv_a.shape[0], K=lw.w_qkv_a.shape[1],
+                               tail=native.qkv_a_post_tail(ws.tail_counters[3:], args_dev, rows))
+        else:
+            self._linear_f32(x, lw.w_qkv_a, ws.proj_a, decode)
+            native.qkv_a_post(a, rows)
 
         self._linear_f32(ws.q_resid[:rows], lw.w_q_b, ws.q_proj, decode)
         b = native.QPostArgs()
@@ -568,7 +597,7 @@ class GlmMoeDsaModel:
             with torch.cuda.stream(self.side):
                 native.skinny_bf16_swiglu(x, lw.shared_gate, lw.shared_up, ws.act_shared)
                 native.skinny_bf16(ws.act_shared[:rows], lw.shared_down, ws.partial, native.SK_OUT_F32)
-        if decode and self.kernel_tails and E <= 256 and tk <= 32 and ws.topk_ids.is_contiguous():
+        if decode and "router" in self.tail_kinds and E <= 256 and tk <= 32 and ws.topk_ids.is_contiguous():
             native.skinny_bf16(x, lw.router_w, ws.router_logits, native.SK_OUT_F32, N=E, K=lw.router_w.shape[1],
                                tail=native.router_topk_tail(ws.tail_counters[0:], ws.router_logits, lw.router_bias, tk, ws.topk_ids, ws.topk_w, rows))
         else:

@@ -62,11 +62,11 @@ class KernelTail(C.Structure):
         ("kind", C.c_int), ("rows", C.c_int), ("counter", C.c_void_p),
         ("update", C.c_void_p), ("residual", C.c_void_p), ("weight", C.c_void_p), ("x_out", C.c_void_p), ("H", C.c_int), ("eps", C.c_float),
         ("logits", C.c_void_p), ("bias", C.c_void_p), ("ids", C.c_void_p), ("wts", C.c_void_p), ("logits_stride", C.c_int64),
-        ("E", C.c_int), ("top_k", C.c_int),
+        ("E", C.c_int), ("top_k", C.c_int), ("qkv", C.c_void_p),
     ]
 
 
-TAIL_ADD_RMSNORM, TAIL_ROUTER_TOPK = 1, 2
+TAIL_ADD_RMSNORM, TAIL_ROUTER_TOPK, TAIL_QKV_A_POST = 1, 2, 3
 TAIL_MAX_NORM_ROWS = 2  # more rows than this cost one CTA more than a launch of their own
 
 
@@ -84,6 +84,20 @@ def router_topk_tail(counter, logits, bias, top_k: int, ids, wts, rows: int) -> 
     t.kind, t.rows, t.counter = TAIL_ROUTER_TOPK, rows, counter.data_ptr()
     t.logits, t.bias, t.ids, t.wts = logits.data_ptr(), bias.data_ptr(), ids.data_ptr(), wts.data_ptr()
     t.logits_stride, t.E, t.top_k = logits.stride(0), bias.shape[0], top_k
+    return t
+
+
+def qkv_a_post_fits_tail(a: "QkvPostArgs") -> bool:
+    """The limits of the single-round-trip row function (the same as ``glmb_qkv_a_post`` applies before it picks that kernel)."""
+    return (a.Q <= 2048 and a.L <= 1024 and a.rd <= 512 and a.IH <= 256 and a.D <= 256 and not (a.L + a.rd) & 3 and not a.rd & 1
+            and not a.Q & 3 and not a.L & 3 and not a.proj_stride & 3)
+
+
+def qkv_a_post_tail(counter, args_device, rows: int) -> "KernelTail":
+    """LoRA norms, RoPE and the cache-row write as the tail of the fused q_a | kv_a | index projection.  ``args_device``: a uint8
+    tensor in device memory holding the ``QkvPostArgs`` of the layer."""
+    t = KernelTail()
+    t.kind, t.rows, t.counter, t.qkv = TAIL_QKV_A_POST, rows, counter.data_ptr(), args_device.data_ptr()
     return t
 
 
