@@ -21,6 +21,8 @@ def test_gate_matches_golden(gate):
 @pytest.mark.gpu
 def test_launch_programs_match_golden():
     """The ordered launch list (entry point + integer arguments) of a decode step and a prefill chunk, per configuration."""
+    if not (driver.DATA / "g1_launch_programs.json").exists():
+        pytest.skip("no launch programs recorded yet: python -m tools.equivalence.driver update g1_launch_programs on a B200")
     golden = driver.load("g1_launch_programs")
     assert {"glm53x8.shard-of-8.chats1", "glm53x8.shard-of-8.chats4", "small4.gpus1.chats1"} <= set(golden)
     assert driver.check({"g1_launch_programs"}) == {}

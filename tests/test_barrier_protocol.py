@@ -178,6 +178,82 @@ def test_reusing_a_channel_back_to_back_lets_a_fast_rank_overwrite_an_unread_inb
 
 
 # ------------------------------------------------------------------------------------------------------------------------------------
+# The same all-reduce with (value, sequence number) PAIRS (`GLMB_AR_PAIRS`, the protocol in use): there is no flag and no fence; every
+# value is one aligned 8-byte store that lands whole, in any order relative to the other values, and the reader polls each word until
+# its sequence number is this round's.  The model lets every word of a slice arrive on its own (a scheduler step per store) and lets a
+# reader start summing words while others are still on their way.  Safe with alternating channels, for the same reason as above; a
+# reused channel lets a fast rank overwrite a word a slow rank has not read yet, which the reader then takes for... nothing: it keeps
+# polling for a round number that has already been overwritten by a later one, so the fault shows as a wait that never ends (on the
+# device: the bounded wait gives up and raises the status word), never as a wrong sum.
+def run_pair_allreduces(world, channels, rng, bias, width=3):
+    word = [[[[(0, None)] * width for _ in range(world)] for _ in range(2)] for _ in range(world)]  # [receiver][channel][source][i] = (round, value)
+    results = [[] for _ in range(world)]
+
+    def rank(me):
+        rounds = [0, 0]
+        for step, ch in enumerate(channels):
+            rounds[ch] += 1
+            e = rounds[ch]
+            mine = [1000 * step + 10 * me + i for i in range(width)]
+            order = [(p, i) for p in range(world) if p != me for i in range(width)]
+            rng.shuffle(order)  # the stores of a slice reach the peers in no particular order
+            for p, i in order:
+                word[p][ch][me][i] = (e, mine[i])
+                yield
+            sums = list(mine)
+            for i in range(width):
+                for p in range(world):
+                    if p == me:
+                        continue
+                    yield lambda p=p, ch=ch, i=i, e=e: word[me][ch][p][i][0] == e  # exactly this round: a later one means the word was lost
+                    got_round, value = word[me][ch][p][i]
+                    if got_round != e or value != 1000 * step + 10 * p + i:
+                        raise Violation(f"rank {me} adds {value} (round {got_round}) from rank {p} in step {step}")
+                    sums[i] += value
+            results[me].append(sums)
+
+    agents = [rank(r) for r in range(world)]
+    waiting = {i: None for i in range(world)}
+    while waiting:
+        runnable = [i for i, wait in waiting.items() if wait is None or wait()]
+        if not runnable:
+            raise Violation("no rank can proceed")
+        k = rng.choices(runnable, weights=[bias[i] for i in runnable])[0]
+        try:
+            waiting[k] = next(agents[k])
+        except StopIteration:
+            del waiting[k]
+    return results
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_pair_all_reduce_is_safe_with_alternating_channels(world):
+    rng = random.Random(10 + world)
+    channels = [0, 1] * 5
+    for trial in range(60):
+        bias = [rng.choice([0.02, 1.0, 5.0]) for _ in range(world)]
+        results = run_pair_allreduces(world, channels, rng, bias)
+        want = [[sum(1000 * step + 10 * r + i for r in range(world)) for i in range(3)] for step in range(len(channels))]
+        assert all(r == want for r in results)
+
+
+def test_pair_all_reduce_on_a_reused_channel_loses_words_and_stalls_instead_of_summing_wrong():
+    rng = random.Random(5)
+    stalled = wrong = 0
+    for trial in range(200):
+        bias = [1.0] * 4
+        bias[rng.randrange(4)] = 0.02
+        try:
+            run_pair_allreduces(4, [0, 0, 0, 0], rng, bias)
+        except Violation as exc:
+            if "no rank can proceed" in str(exc):
+                stalled += 1
+            else:
+                wrong += 1
+    assert stalled > 0 and wrong == 0
+
+
+# ------------------------------------------------------------------------------------------------------------------------------------
 # Signals (`grid_signal_peers` / `cta_wait_signal`): a producer kernel stores its data into ONE buffer on every peer and raises the
 # round's number; the consumer kernel of each rank waits for every rank's number and reads.  Nothing tells the producer that the peers
 # have read: what protects the buffer is that an all-reduce, which no rank leaves before every rank has entered it, separates two rounds
