@@ -96,7 +96,6 @@ def main(argv=None) -> int:
     lines = [f"DSA attention block at GLM-5.3 dims on {world} GPU(s), kv layout {runner.kv_layout}, 32,768-slot cache, chats {args.depth} tokens deep, eager launches", "",
              "| case | rows | median us | best us | device status |", "|---|---|---|---|---|"]
     ws = runner.decode_ws
-    model.tail_kinds = set()  # the block alone: without the residual add + RMSNorm that the output projection otherwise carries as its tail
     frozen = torch.zeros(4, dtype=torch.int32, device=dev)  # inactive rows: the block runs in full but writes no cache row and advances nothing
     for rows in (1, 4):
         ws.x[:rows].copy_(torch.randn(rows, g.hidden_size, generator=torch.Generator().manual_seed(rows)).to(torch.bfloat16))

@@ -13,7 +13,6 @@
 #include "common.cuh"
 #include "gemv_core.cuh"
 #include "peer.cuh"
-#include "tail_ops.cuh"
 
 #define SK_WARPS 8
 #define SK_THREADS (SK_WARPS * 32)
@@ -48,7 +47,7 @@ template <int R>
 __global__ void __launch_bounds__(SK_THREADS)
 skinny_bf16_kernel(const bf16* __restrict__ x, int64_t xs, int rows, const bf16* __restrict__ w, int64_t ws, int N, int K,
                    void* __restrict__ out, int64_t os, int mode, int ks, int64_t xb, int64_t wb, int64_t ob, PeerComm comm,
-                   int channel, KernelTail tail) {
+                   int channel) {
     asm volatile("griddepcontrol.launch_dependents;");
     if ((int64_t)N * K * 2 * gridDim.y <= SK_PREFETCH_LIMIT) {
         const int first = blockIdx.x * (SK_WARPS / ks) * 2;
@@ -113,8 +112,6 @@ skinny_bf16_kernel(const bf16* __restrict__ x, int64_t xs, int rows, const bf16*
                     if (n0 + j < N && r < rows)
                         reinterpret_cast<bf16*>(out)[(int64_t)r * os + n0 + j] = __float2bfloat16_rn(sh[(group * 2 + j) * R + r]);
         }
-        __shared__ float tail_scratch_ar[40];
-        run_kernel_tail(tail, tail_scratch_ar);  // e.g. the residual add + RMSNorm that consumes the all-reduced rows
         return;
     }
     if (mode == SK_OUT_ARGMAX) {
@@ -154,8 +151,6 @@ skinny_bf16_kernel(const bf16* __restrict__ x, int64_t xs, int rows, const bf16*
                     else reinterpret_cast<bf16*>(out)[(int64_t)r * os + n0 + j] = __float2bfloat16_rn(acc[j][r]);
                 }
     }
-    __shared__ float tail_scratch[40];
-    run_kernel_tail(tail, tail_scratch);  // e.g. the router's top-k over the logits this launch produced
 }
 
 // act[r][n] = bf16( silu(bf16(x.w_gate[n])) * bf16(x.w_up[n]) )       (bf16 weights; dense MLP / shared expert)
@@ -376,12 +371,8 @@ static PeerComm single_comm() {
 // batch > 1 runs `batch` independent problems whose x / w / out start xb / wb / ob elements apart.
 GLMB_API int glmb_skinny_bf16(const void* x, int64_t xs, int rows, const void* w, int64_t ws, int N, int K, void* out, int64_t os,
                               int mode, int batch, int64_t xb, int64_t wb, int64_t ob, const PeerComm* comm, int channel,
-                              const KernelTail* tail_or_null, void* stream) {
+                              void* stream) {
     if (rows < 1 || rows > GLMB_MAX_ROWS || (K & 7) || (xs & 7) || (ws & 7) || (xb & 7) || (wb & 7) || batch < 1) return 1;
-    const KernelTail tail = tail_or_null ? *tail_or_null : no_tail();
-    if (tail.kind == TAIL_ADD_RMSNORM && (mode != SK_OUT_ALLREDUCE_BF16 || tail.rows > 2 || (tail.H & 7) || tail.H > 256 * 8 * RN_VECS)) return 1;
-    if (tail.kind == TAIL_QKV_A_POST && (mode != SK_OUT_F32 || tail.rows > 2 || !tail.qkv)) return 1;
-    if (tail.kind == TAIL_ROUTER_TOPK && (mode != SK_OUT_F32 || tail.rows > SK_WARPS || tail.E > 256 || tail.top_k > 32 || tail.top_k > tail.E)) return 1;
     int ks = pick_ksplit(ceil_div(N, 2) * batch, K);
     PeerComm c = comm ? *comm : single_comm();
     // A CTA that all-reduces waits for the same CTA of every peer before it retires.  CTAs beyond the first wave would start only
@@ -393,7 +384,7 @@ GLMB_API int glmb_skinny_bf16(const void* x, int64_t xs, int rows, const void* w
     if (mode == SK_OUT_ALLREDUCE_BF16 && c.world == 1) mode = SK_OUT_BF16;
 #define CALL(RR)                                                                                                   \
     GLMB_LAUNCH(skinny_bf16_kernel<RR>, grid, SK_THREADS, 0, (cudaStream_t)stream, (const bf16*)x, xs, rows, (const bf16*)w, ws, N, K, \
-                                                                          out, os, mode, ks, xb, wb, ob, c, channel, tail)
+                                                                          out, os, mode, ks, xb, wb, ob, c, channel)
     DISPATCH_R(rows, CALL);
 #undef CALL
     return (int)cudaGetLastError();

@@ -10,7 +10,7 @@
 //   fill_random_*     counter-based random initialisation of weights directly in device memory
 #include "common.cuh"
 #include "peer.cuh"
-#include "tail_ops.cuh"
+#include "router_core.cuh"
 
 // ---------------------------------------------------------------------------------------------------
 // One warp per row.  E <= 1024.
@@ -54,7 +54,7 @@ router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ b
     if (lane < top_k) weights[(int64_t)r * top_k + lane] = my_score / (picked_sum + 1e-20f);
 }
 
-// Same selection for E <= 256: every lane loads its (up to 8) logits once and keeps score and key in registers (tail_ops.cuh).
+// Same selection for E <= 256: every lane loads its (up to 8) logits once and keeps score and key in registers (router_core.cuh).
 __global__ void __launch_bounds__(128)
 router_topk256_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int rows, int E, int top_k,
                       int* __restrict__ ids, float* __restrict__ weights) {

@@ -19,7 +19,6 @@
 #include "common.cuh"
 #include "moe_mma_core.cuh"
 #include "peer.cuh"
-#include "tail_ops.cuh"
 
 #define MM_WARPS 8
 #define MM_THREADS (32 * MM_WARPS)
@@ -164,8 +163,7 @@ moe_down_fp8_mma_kernel(const bf16* __restrict__ act, const float* __restrict__ 
 __global__ void __launch_bounds__(MM_THREADS)
 moe_down_combine_kernel(const bf16* __restrict__ act, const float* __restrict__ route_weight, const int* __restrict__ topk_ids,
                         const uint8_t* __restrict__ wd, const float* __restrict__ sd, int experts, int I, int H, int rows_total, int top_k,
-                        const float* __restrict__ shared_partial, float scale, bf16* __restrict__ out, PeerComm comm, int channel,
-                        KernelTail tail) {
+                        const float* __restrict__ shared_partial, float scale, bf16* __restrict__ out, PeerComm comm, int channel) {
     GLMB_PDL_PROLOGUE();
     __shared__ float red[GLMB_MAX_ROWS][MM_WARPS][MM_ROWS];
     __shared__ float sh[2 * GLMB_MAX_ROWS * MM_ROWS];
@@ -217,22 +215,19 @@ moe_down_combine_kernel(const bf16* __restrict__ act, const float* __restrict__ 
         const int r = i / MM_ROWS, c = i % MM_ROWS;
         out[(int64_t)(r0 + r) * H + n0 + c] = __float2bfloat16_rn(bf16_round(bf16_round(sh[per + i]) * scale) + bf16_round(sh[i]));
     }
-    run_kernel_tail(tail, &red[0][0][0]);  // the next layer's residual add + RMSNorm over the rows this launch completed
 }
 
 GLMB_API int glmb_moe_down_combine(const void* act, const float* route_weight, const int* topk_ids, const void* wd, const float* sd,
                                    int experts, int I, int H, int rows, int top_k, const float* shared_partial, float scale, void* out,
-                                   const PeerComm* comm, int channel, const KernelTail* tail_or_null, void* stream) {
+                                   const PeerComm* comm, int channel, void* stream) {
     if (rows < 1 || top_k < 1 || top_k > MM_WARPS || (I & 63) || (H & 15)) return 1;
-    const KernelTail tail = tail_or_null ? *tail_or_null : no_tail();
-    if (tail.kind != TAIL_NONE && (tail.kind != TAIL_ADD_RMSNORM || tail.rows > 2 || tail.H != H || H > 256 * 8 * RN_VECS)) return 1;
     PeerComm c;
     if (comm) c = *comm;
     else { memset(&c, 0, sizeof(c)); c.world = 1; }
     const dim3 grid(H / MM_ROWS, ceil_div(rows, GLMB_MAX_ROWS));
     if (c.world > 1 && (int)(grid.x * grid.y) > GLMB_AR_MAX_CTAS) return 2;
     GLMB_LAUNCH(moe_down_combine_kernel, grid, MM_THREADS, 0, (cudaStream_t)stream, (const bf16*)act, route_weight, topk_ids, (const uint8_t*)wd,
-                sd, experts, I, H, rows, top_k, shared_partial, scale, (bf16*)out, c, channel, tail);
+                sd, experts, I, H, rows, top_k, shared_partial, scale, (bf16*)out, c, channel);
     return (int)cudaGetLastError();
 }
 

@@ -4,7 +4,7 @@
 after import.  Precedence everywhere: CLI flag > environment > site file > default.
 
 Every variable is one row of ``TABLE``: a *kind* that names its parser in ``PARSERS`` (``path``, ``flag``, ``choice``,
-``number``, ``count``, ``subset``), a default (a value, or a function for defaults that depend on other variables) and a help line.
+``number``, ``count``), a default (a value, or a function for defaults that depend on other variables) and a help line.
 There is one code path from a row to a value (``value_of``): look the text up, hand it to the kind's parser, fall back to
 the default when it is unset or empty.  A text the parser refuses raises ``ValueError`` naming the variable, so a typo
 never silently selects the default.
@@ -52,22 +52,12 @@ def _parse_number(text: str, row: Row) -> float:
     return number
 
 
-def _parse_subset(text: str, row: Row) -> frozenset:
-    if text in ("0", "1"):
-        return frozenset(row.choices) if text == "1" else frozenset()
-    chosen = frozenset(text.split(","))
-    if not chosen <= set(row.choices):
-        raise ValueError("must be 0, 1 or a comma-separated subset of " + ", ".join(row.choices))
-    return chosen
-
-
 PARSERS: dict[str, Callable[[str, Row], Any]] = {
     "path": _parse_path,
     "flag": _parse_flag,
     "choice": _parse_choice,
     "number": _parse_number,
     "count": lambda text, row: int(_parse_number(text, row)),
-    "subset": _parse_subset,
 }
 
 
@@ -99,8 +89,6 @@ TABLE: dict[str, Row] = {
     "GLM_B200_PDL": Row("flag", True, "Programmatic dependent launch between consecutive kernels (1) or plain stream order (0)."),
     "GLM_B200_OVERLAP": Row("flag", True, "Independent branches of a layer on a second stream (1) or one stream (0)."),
     "GLM_B200_FOLD_Q_POST": Row("flag", True, "Decode: query RoPE folded into q-absorb and the indexer (1) or a kernel of its own (0)."),
-    "GLM_B200_TAILS": Row("subset", frozenset(), "Decode: which small steps run in the last CTA of the kernel before them instead of as launches "
-                          "of their own (measured slower than the launches under programmatic dependent launch: off by default).", ("norm", "router", "qkv")),
     "GLM_B200_MERGE_VPROJ": Row("flag", True, "Decode, local keys: chunk merge and value projection in one launch (1) or two (0)."),
     "GLM_B200_NVTX": Row("flag", False, "NVTX ranges per layer and block."),
     "GLM_B200_INDEXER": Row("choice", "tcgen05", "DSA indexer on tcgen05 or the CUDA-core kernel.", ("tcgen05", "cuda")),

@@ -137,8 +137,6 @@ class Workspace:
         self.logits = bf(rows, lay.vocab_local)
         self.kv_new = bf(rows, W)
         self.idx_key_new = bf(rows, D)
-        self.tail_counters = torch.zeros(4, dtype=torch.int32, device=dev)  # arrival counters of the kernel tails (left at zero)
-        self.qkv_args: dict = {}  # layer -> (bytes, device block) of the QkvPostArgs the projection's tail reads
         self._sorted = None
         self._route = None
         # many-row workspaces on several GPUs: output and partial-tile slots of the GEMM with the fused all-reduce
@@ -208,12 +206,6 @@ class GlmMoeDsaModel:
         # the one-launch expert sort takes up to 256 resident experts and contiguous ids; other shapes use the library-op sort
         # (`_route_tiles128`), and tests set this attribute to compare the two on shapes both take
         self.route_sort_kernel = True
-        # decode: residual add + RMSNorm ("norm"), the router's top-k ("router") and the q_a / kv_a post-processing ("qkv") can run as
-        # the tail of the kernel before them (its last CTA) instead of as launches of their own.  Off by default: with programmatic
-        # dependent launch a kernel boundary costs less than the fence + arrival counter + single-CTA work of a tail (measured).
-        from glm_tpu_b200 import envs
-
-        self.tail_kinds = set(envs.GLM_B200_TAILS)
         self.merge_vproj = os.environ.get("GLM_B200_MERGE_VPROJ", "1") != "0"  # decode: chunk merge + value projection in one launch
         self.prefill_rows_attention = os.environ.get("GLM_B200_PREFILL_ATTENTION", "rows") != "split"
         # Prefill projections whose K is split over the GPUs use the GEMM with the all-reduce in its epilogue (about 1.2x the
@@ -236,34 +228,6 @@ class GlmMoeDsaModel:
             import logging
 
             logging.getLogger("glm_tpu_b200.fallback").warning("rank %d falls back to %s", self.rank, key)
-
-    def _qkv_args_on_device(self, ws: "Workspace", layer: int, a) -> torch.Tensor | None:
-        """The layer's ``QkvPostArgs`` in device memory (the kernel tail reads them there).  They are constant for a workspace and a
-        decoder state, so the upload happens on the first eager step; a block that changes while a graph is being captured means
-        the capture would freeze stale arguments, which is refused."""
-        if not native.qkv_a_post_fits_tail(a):
-            return None
-        raw = bytes(a)
-        cached = ws.qkv_args.get(layer)
-        if cached is None or cached[0] != raw:
-            if torch.cuda.is_current_stream_capturing():
-                return None  # fall back to the separate launch for this capture (never seen in practice: the warm-up step uploads)
-            block = cached[1] if cached is not None else torch.empty(len(raw), dtype=torch.uint8, device=self.device)
-            block.copy_(torch.frombuffer(bytearray(raw), dtype=torch.uint8))
-            torch.cuda.current_stream(self.device).synchronize()
-            ws.qkv_args[layer] = (raw, block)
-            cached = ws.qkv_args[layer]
-        return cached[1]
-
-    def _norm_tail(self, ws: "Workspace", slot: int, update: torch.Tensor, weight: torch.Tensor | None, rows: int):
-        """The residual add + RMSNorm that consumes ``update`` as a tail of the kernel that writes it, or None where it stays a launch
-        of its own (several rows, tracing, switched off, no norm follows)."""
-        if weight is None or "norm" not in self.tail_kinds or self.trace is not None or rows > native.TAIL_MAX_NORM_ROWS:
-            return None
-        H = self.g.hidden_size
-        if H % 8 or H > 8192 or not update.is_contiguous():
-            return None
-        return native.add_rmsnorm_tail(ws.tail_counters[slot:], update, ws.residual, weight, ws.x, rows, H, self.g.rms_norm_eps)
 
     def _allreduce_rows(self, partial_f32: torch.Tensor) -> torch.Tensor:
         import torch.distributed as dist
@@ -333,8 +297,7 @@ class GlmMoeDsaModel:
 
     # ------------------------------------------------------------------------------ attention
     def _attention(self, ws: Workspace, lw: LayerWeights, layer: int, rows: int, row_pos, row_lane, row_active, state: DecoderState,
-                   decode: bool, max_ctx: int, lane_of_rows: int | None = None) -> bool:
-        """Returns True when the post-attention residual add + RMSNorm already ran (as the tail of the output projection)."""
+                   decode: bool, max_ctx: int, lane_of_rows: int | None = None):
         g, lay, cache = self.g, self.layout, self.cache
         full = g.indexer_types[layer] == "full"
         Q, L, rd, W = g.q_lora_rank, g.kv_lora_rank, g.qk_rope_head_dim, g.kv_row_width
@@ -365,14 +328,8 @@ class GlmMoeDsaModel:
         a.local_cap, a.stripe, a.world, a.rank, a.capacity = cache.local_capacity, cache.stripe, cw, cr, cache.context_capacity
         a.eps, a.key_eps, a.head_scale = g.rms_norm_eps, cache.dsa.key_norm_eps, self.head_scale
         a.status = self.peer.status_ptr
-        args_dev = self._qkv_args_on_device(ws, layer, a) if decode and rows <= native.TAIL_MAX_NORM_ROWS and "qkv" in self.tail_kinds else None
-        if args_dev is not None:
-            # the norms, RoPE and cache-row write ride the projection as its tail: one launch instead of two
-            native.skinny_bf16(x, lw.w_qkv_a, ws.proj_a, native.SK_OUT_F32, N=lw.w_qkv_a.shape[0], K=lw.w_qkv_a.shape[1],
-                               tail=native.qkv_a_post_tail(ws.tail_counters[3:], args_dev, rows))
-        else:
-            self._linear_f32(x, lw.w_qkv_a, ws.proj_a, decode)
-            native.qkv_a_post(a, rows)
+        self._linear_f32(x, lw.w_qkv_a, ws.proj_a, decode)
+        native.qkv_a_post(a, rows)
 
         self._linear_f32(ws.q_resid[:rows], lw.w_q_b, ws.q_proj, decode)
         b = native.QPostArgs()
@@ -451,15 +408,12 @@ class GlmMoeDsaModel:
             else:
                 self._merge_partials_nccl(ws, r0, n)
         # value projection per head, then the K-split output projection with its reduction
-        normed = False
         if decode:
             if not merged_vproj:
                 native.skinny_bf16(ws.o_lat, lw.kv_b[:, g.qk_nope_head_dim :, :], ws.attn_v, native.SK_OUT_BF16, rows=rows, N=g.v_head_dim,
                                    K=L, xs=hl * L, ws=L, os_=hl * g.v_head_dim, batch=hl, xb=L, wb=g.kv_b_rows_per_head * L, ob=g.v_head_dim)
             if fused or self.world == 1 or self.emulated_shard:
-                tail = self._norm_tail(ws, 1, ws.attn_out, lw.post_norm, rows)
-                native.skinny_bf16(ws.attn_v[:rows], lw.w_o, ws.attn_out, native.SK_OUT_ALLREDUCE_BF16, comm=kc, channel=native.CH_ATTN, tail=tail)
-                normed = tail is not None
+                native.skinny_bf16(ws.attn_v[:rows], lw.w_o, ws.attn_out, native.SK_OUT_ALLREDUCE_BF16, comm=kc, channel=native.CH_ATTN)
             else:
                 native.skinny_bf16(ws.attn_v[:rows], lw.w_o, ws.partial, native.SK_OUT_F32)
                 ws.attn_out[:rows] = self._allreduce_rows(ws.partial[:rows]).to(torch.bfloat16)
@@ -478,7 +432,6 @@ class GlmMoeDsaModel:
         if self.trace is not None:
             self.trace.setdefault("attn_out", {})[layer] = ws.attn_out[:rows].clone()
             self.trace.setdefault("kv_new", {})[layer] = ws.kv_new[:rows].clone()
-        return normed
 
     def select_keys_decode(self, ws: Workspace, state: DecoderState, layer: int, rows: int) -> None:
         """Indexer scores and the exact top-k of a layer with its own indexer, for the rows of a decode step whose q_b projection
@@ -555,9 +508,7 @@ class GlmMoeDsaModel:
         ws.o_lat[r0 : r0 + n] = out.to(torch.bfloat16)
 
     # ------------------------------------------------------------------------------ MLP
-    def _mlp(self, ws: Workspace, lw: LayerWeights, layer: int, rows: int, decode: bool, next_norm: torch.Tensor | None = None) -> bool:
-        """``next_norm``: the weight of the RMSNorm that consumes this block's output (the next layer's input norm, or the final
-        norm).  Returns True when that residual add + RMSNorm already ran as the tail of the block's last kernel."""
+    def _mlp(self, ws: Workspace, lw: LayerWeights, layer: int, rows: int, decode: bool):
         g, lay = self.g, self.layout
         H = g.hidden_size
         fused = ws.peer_visible
@@ -567,10 +518,8 @@ class GlmMoeDsaModel:
             if decode:
                 native.skinny_bf16_swiglu(x, lw.dense_gate, lw.dense_up, ws.dense_act)
                 if fused or self.world == 1 or self.emulated_shard:
-                    tail = self._norm_tail(ws, 2, ws.update, next_norm, rows)
                     native.skinny_bf16(ws.dense_act[:rows], lw.dense_down, ws.update, native.SK_OUT_ALLREDUCE_BF16, comm=kc,
-                                       channel=native.CH_MLP, tail=tail)
-                    return tail is not None
+                                       channel=native.CH_MLP)
                 else:
                     native.skinny_bf16(ws.dense_act[:rows], lw.dense_down, ws.partial, native.SK_OUT_F32)
                     ws.update[:rows] = self._allreduce_rows(ws.partial[:rows]).to(torch.bfloat16)
@@ -584,7 +533,7 @@ class GlmMoeDsaModel:
                         ws.update[:rows] = fused_out
                     else:
                         ws.update[:rows] = self._allreduce_rows(self._mm(act, lw.dense_down, f32=True)).to(torch.bfloat16)
-            return False
+            return
         # whole experts: this GPU's `el` experts from `ebase`, full width; sliced: I columns of every expert
         tk, I, E = g.routed_top_k, lay.moe_cols_local, g.num_routed_experts
         el, ebase = lay.experts_resident, lay.expert_base
@@ -597,12 +546,8 @@ class GlmMoeDsaModel:
             with torch.cuda.stream(self.side):
                 native.skinny_bf16_swiglu(x, lw.shared_gate, lw.shared_up, ws.act_shared)
                 native.skinny_bf16(ws.act_shared[:rows], lw.shared_down, ws.partial, native.SK_OUT_F32)
-        if decode and "router" in self.tail_kinds and E <= 256 and tk <= 32 and ws.topk_ids.is_contiguous():
-            native.skinny_bf16(x, lw.router_w, ws.router_logits, native.SK_OUT_F32, N=E, K=lw.router_w.shape[1],
-                               tail=native.router_topk_tail(ws.tail_counters[0:], ws.router_logits, lw.router_bias, tk, ws.topk_ids, ws.topk_w, rows))
-        else:
-            self._linear_f32(x, lw.router_w, ws.router_logits, decode)
-            native.router_topk(ws.router_logits[:rows], lw.router_bias, tk, ws.topk_ids, ws.topk_w)
+        self._linear_f32(x, lw.router_w, ws.router_logits, decode)
+        native.router_topk(ws.router_logits[:rows], lw.router_bias, tk, ws.topk_ids, ws.topk_w)
         if self.trace is not None:
             self.trace.setdefault("topk_ids", {})[layer] = ws.topk_ids[:rows].clone()
             self.trace.setdefault("topk_w", {})[layer] = ws.topk_w[:rows].clone()
@@ -640,10 +585,8 @@ class GlmMoeDsaModel:
             act = self._swiglu(self._mm(x, lw.shared_gate), self._mm(x, lw.shared_up))
             shared_partial = self._mm(act, lw.shared_down, f32=True)
         if one_launch:
-            tail = self._norm_tail(ws, 2, ws.update, next_norm, rows)
             native.moe_down_combine(ws.act, ws.topk_w, ws.topk_ids, lw.exp_down_bits, lw.exp_down_scale, shared_partial, rows, tk,
-                                    g.routed_scaling_factor, ws.update, kc, native.CH_MLP, tail=tail)
-            return tail is not None
+                                    g.routed_scaling_factor, ws.update, kc, native.CH_MLP)
         elif fused or self.world == 1 or self.emulated_shard:
             native.moe_combine(ws.dw, ws.topk_ids, shared_partial, rows, tk, H, ebase, el, g.routed_scaling_factor, False, ws.update,
                                None, kc, native.CH_MLP)
@@ -723,27 +666,19 @@ class GlmMoeDsaModel:
         update = None
         mark = torch.cuda.nvtx.range_push if self.nvtx else (lambda name: None)
         done = torch.cuda.nvtx.range_pop if self.nvtx else (lambda: None)
-        # Each residual add + RMSNorm runs as the tail of the kernel whose output it consumes where that kernel can carry it
-        # (decode, one or two rows); `normed` says that ws.residual and ws.x are already those of the next block.
-        normed = False
-        layers = self.w.layers
-        for i, lw in enumerate(layers):
+        for i, lw in enumerate(self.w.layers):
             mark(f"layer{i}.attention.{g.indexer_types[i]}")  # region names for profilers (GLM_B200_NVTX=1)
-            if not normed:
-                native.add_rmsnorm(update, ws.residual[:rows], lw.input_norm, ws.x, g.rms_norm_eps)
-            normed = self._attention(ws, lw, i, rows, row_pos, row_lane, row_active, state, decode, max_ctx, lane_of_rows)
+            native.add_rmsnorm(update, ws.residual[:rows], lw.input_norm, ws.x, g.rms_norm_eps)
+            self._attention(ws, lw, i, rows, row_pos, row_lane, row_active, state, decode, max_ctx, lane_of_rows)
             done()
             mark(f"layer{i}.mlp.{g.mlp_layer_types[i]}")
-            if not normed:
-                native.add_rmsnorm(ws.attn_out, ws.residual[:rows], lw.post_norm, ws.x, g.rms_norm_eps)
-            next_norm = layers[i + 1].input_norm if i + 1 < len(layers) else self.w.final_norm
-            normed = bool(self._mlp(ws, lw, i, rows, decode, next_norm))
+            native.add_rmsnorm(ws.attn_out, ws.residual[:rows], lw.post_norm, ws.x, g.rms_norm_eps)
+            self._mlp(ws, lw, i, rows, decode)
             done()
             update = ws.update
             if self.trace is not None:
                 self.trace.setdefault("update", {})[i] = ws.update[:rows].clone()
-        if not normed:
-            native.add_rmsnorm(update, ws.residual[:rows], self.w.final_norm, ws.x, g.rms_norm_eps)
+        native.add_rmsnorm(update, ws.residual[:rows], self.w.final_norm, ws.x, g.rms_norm_eps)
         hs = head_rows or slice(0, rows)
         xh = ws.x[hs]
         n = xh.shape[0]

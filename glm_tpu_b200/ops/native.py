@@ -55,52 +55,6 @@ class QkvPostArgs(C.Structure):
     ]
 
 
-class KernelTail(C.Structure):
-    """A small grid-wide step run by the last CTA of the kernel it follows (csrc/tail_ops.cuh)."""
-
-    _fields_ = [
-        ("kind", C.c_int), ("rows", C.c_int), ("counter", C.c_void_p),
-        ("update", C.c_void_p), ("residual", C.c_void_p), ("weight", C.c_void_p), ("x_out", C.c_void_p), ("H", C.c_int), ("eps", C.c_float),
-        ("logits", C.c_void_p), ("bias", C.c_void_p), ("ids", C.c_void_p), ("wts", C.c_void_p), ("logits_stride", C.c_int64),
-        ("E", C.c_int), ("top_k", C.c_int), ("qkv", C.c_void_p),
-    ]
-
-
-TAIL_ADD_RMSNORM, TAIL_ROUTER_TOPK, TAIL_QKV_A_POST = 1, 2, 3
-TAIL_MAX_NORM_ROWS = 2  # more rows than this cost one CTA more than a launch of their own
-
-
-def add_rmsnorm_tail(counter, update, residual, weight, x_out, rows: int, H: int, eps: float) -> "KernelTail":
-    """``residual <- update + residual; x_out <- RMSNorm(residual) * weight`` as the tail of the kernel that produces ``update``."""
-    t = KernelTail()
-    t.kind, t.rows, t.counter = TAIL_ADD_RMSNORM, rows, counter.data_ptr()
-    t.update, t.residual, t.weight, t.x_out, t.H, t.eps = update.data_ptr(), residual.data_ptr(), weight.data_ptr(), x_out.data_ptr(), H, eps
-    return t
-
-
-def router_topk_tail(counter, logits, bias, top_k: int, ids, wts, rows: int) -> "KernelTail":
-    """The router's top-k as the tail of the GEMV that produces the logits."""
-    t = KernelTail()
-    t.kind, t.rows, t.counter = TAIL_ROUTER_TOPK, rows, counter.data_ptr()
-    t.logits, t.bias, t.ids, t.wts = logits.data_ptr(), bias.data_ptr(), ids.data_ptr(), wts.data_ptr()
-    t.logits_stride, t.E, t.top_k = logits.stride(0), bias.shape[0], top_k
-    return t
-
-
-def qkv_a_post_fits_tail(a: "QkvPostArgs") -> bool:
-    """The limits of the single-round-trip row function (the same as ``glmb_qkv_a_post`` applies before it picks that kernel)."""
-    return (a.Q <= 2048 and a.L <= 1024 and a.rd <= 512 and a.IH <= 256 and a.D <= 256 and not (a.L + a.rd) & 3 and not a.rd & 1
-            and not a.Q & 3 and not a.L & 3 and not a.proj_stride & 3)
-
-
-def qkv_a_post_tail(counter, args_device, rows: int) -> "KernelTail":
-    """LoRA norms, RoPE and the cache-row write as the tail of the fused q_a | kv_a | index projection.  ``args_device``: a uint8
-    tensor in device memory holding the ``QkvPostArgs`` of the layer."""
-    t = KernelTail()
-    t.kind, t.rows, t.counter, t.qkv = TAIL_QKV_A_POST, rows, counter.data_ptr(), args_device.data_ptr()
-    return t
-
-
 class QPostArgs(C.Structure):
     _fields_ = [
         ("q", C.c_void_p), ("q_stride", C.c_int64),
@@ -249,7 +203,7 @@ def f32(x: float) -> C.c_float:
 
 # ----------------------------------------------------------------------------- projections
 def skinny_bf16(x, w, out, mode=SK_OUT_F32, *, rows=None, comm=None, channel=0, batch=1, xb=0, wb=0, ob=0, N=None, K=None,
-                xs=None, ws=None, os_=None, tail=None):
+                xs=None, ws=None, os_=None):
     """``out[r, n] = sum_k x[r, k] w[n, k]`` for 1..8 rows; see ``glmb_skinny_bf16``."""
     rows = x.shape[0] if rows is None else rows
     N = w.shape[-2] if N is None else N
@@ -265,8 +219,7 @@ def skinny_bf16(x, w, out, mode=SK_OUT_F32, *, rows=None, comm=None, channel=0, 
         _note_allreduce("skinny_bf16", comm, channel, -(-N // (groups * 2)) * batch, groups * 2 * (1 if rows <= 1 else 2 if rows <= 2 else 4 if rows <= 4 else 8))
     _check(
         lib().glmb_skinny_bf16(_p(x), C.c_int64(xs), rows, _p(w), C.c_int64(ws), N, K, _p(out), C.c_int64(os_), mode, batch,
-                               C.c_int64(xb), C.c_int64(wb), C.c_int64(ob), _comm(comm), channel, C.byref(tail) if tail is not None else None,
-                               _stream()),
+                               C.c_int64(xb), C.c_int64(wb), C.c_int64(ob), _comm(comm), channel, _stream()),
         "skinny_bf16",
     )
 
@@ -308,14 +261,14 @@ def moe_down_fp8(act, route_weight, tile_expert, tile_routes, n_tiles, tiles, rt
     )
 
 
-def moe_down_combine(act, route_weight, topk_ids, wd, sd, shared_partial, rows, top_k, scale, out, comm=None, channel=CH_MLP, tail=None):
+def moe_down_combine(act, route_weight, topk_ids, wd, sd, shared_partial, rows, top_k, scale, out, comm=None, channel=CH_MLP):
     """Column-sliced experts, decode: down projection of every route, route sum, shared partial and all-reduce in one launch
     (``moe_down_combine_kernel``); the roundings of ``moe_down_fp8`` followed by ``moe_combine``."""
     experts, H, I = wd.shape
     _note_allreduce("moe_down_combine", comm, channel, (H // 16) * -(-rows // MAX_ROWS), 2 * min(rows, MAX_ROWS) * 16)
     _check(
         lib().glmb_moe_down_combine(_p(act), _p(route_weight), _p(topk_ids), _p(wd), _p(sd), experts, I, H, rows, top_k, _p(shared_partial),
-                                    f32(scale), _p(out), _comm(comm), channel, C.byref(tail) if tail is not None else None, _stream()),
+                                    f32(scale), _p(out), _comm(comm), channel, _stream()),
         "moe_down_combine",
     )
 
