@@ -239,3 +239,46 @@ def test_bad_cache_metadata_is_reported_and_leaves_the_caches_unchanged(native_l
         engine.generate(request)
     assert engine.poisoned
     runner.close()
+
+
+def test_packed_checkpoint_streams_to_the_device_and_decodes_like_the_arrays_it_came_from(native_lib, tmp_path, monkeypatch):
+    """export -> pack -> load on the GPU: tensors travel file -> pinned staging -> device in bounded pieces, digests are checked on
+    the way, and the resident weights equal those cut from the in-memory checkpoint; the runner built from them decodes the same tokens."""
+    from glm_tpu_b200.config.parallel import ParallelLayout
+    from glm_tpu_b200.executor.pack_job import pack_checkpoint
+    from glm_tpu_b200.model_loader import export, source_marker
+    from glm_tpu_b200.model_loader.sharded_state import format as fmt
+    from glm_tpu_b200.model_loader.sharded_state import loader
+    from glm_tpu_b200.models.glm_moe_dsa.weights import shard_checkpoint
+    from glm_tpu_b200.runner.gpu_runner import build_runner
+
+    g = tiny_geometry()
+    ckpt = random_checkpoint(g, seed=6)
+    export.export_source(ckpt, g, tmp_path / "src", shards=2)
+    source_marker.mark_source(tmp_path / "src")
+    pack_checkpoint(tmp_path / "src", tmp_path / "packed", 1, jobs=1)
+    monkeypatch.setattr(fmt, "PIECE_BYTES", 8192)  # many pieces per tensor through one small pinned buffer
+    streamed = loader.load_rank_checkpoint(tmp_path / "packed", 0, 1, device="cuda:0")
+    layout = ParallelLayout(g, 1, 0)
+    got = shard_checkpoint(streamed, layout, "cuda:0")
+    want = shard_checkpoint(ckpt, layout, "cuda:0")
+    stats = streamed.io_stats()
+    assert 0 < stats["largest_piece"] <= 8192 and stats["bytes_read"] > 0
+    assert torch.equal(got.embed, want.embed) and torch.equal(got.lm_head, want.lm_head)
+    for lw, lg in zip(want.layers, got.layers):
+        for key, value in vars(lw).items():
+            if isinstance(value, torch.Tensor):
+                assert torch.equal(getattr(lg, key), value), key
+    prompt = list(range(5, 25))
+    tokens = []
+    for arrays in (loader.load_rank_checkpoint(tmp_path / "packed", 0, 1, device="cuda:0"), ckpt):
+        runner = build_runner(g, checkpoint=arrays, context_capacity=64, lanes=1, stripe=16, use_graphs=True, prefill_chunk=16)
+        out = [runner.prefill(0, prompt)]
+        runner.build_decode_program()
+        for step in range(5):
+            runner.decode_step()
+            out.append(runner.read_step_tokens(step)[0])
+        runner.peer.check_status()
+        runner.close()
+        tokens.append(out)
+    assert tokens[0] == tokens[1]
