@@ -416,6 +416,8 @@ def main() -> int:
                 "parallelism": (f"tp{b.world}(heads, mlp, shared expert" + (", routed experts by column)" if runner.model.layout.sliced
                                 else f")+ep{b.world}(routed experts)")) if b.world > 1 else "single gpu",
                 "expert_split": runner.model.layout.expert_split,
+                "all_reduce": ("(value, sequence) pairs" if os.environ.get("GLM_B200_AR", "pairs") != "flags" else "values + fence + flag") if b.world > 1 else "none",
+                "fallbacks": dict(runner.model.fallbacks),
                 "comm": args.comm,
                 "kv_layout": kv_layout,
                 "decode_program": rec.kind,

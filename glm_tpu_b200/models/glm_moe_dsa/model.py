@@ -146,8 +146,9 @@ class Workspace:
                 self.r_gemm_out = peer.region(f"{tag}.gemm_out", rows * H * 2)
                 self.r_gemm_part = peer.region(f"{tag}.gemm_part", native.gemm_allreduce_part_bytes(rows, H, peer.world))
                 self.gemm_out = peer.tensor(self.r_gemm_out, (rows, H), torch.bfloat16)
-            except MemoryError:  # staging sized without it: the caller falls back to the library all-reduce
+            except MemoryError:  # staging sized without it: the caller falls back to the library all-reduce, and says so
                 self.r_gemm_out = self.r_gemm_part = None
+                model.note_fallback("GEMM then library all-reduce", f"the staging buffer has no room for the fused GEMM all-reduce of {rows} rows")
 
     def route_buffers(self, routes: int, el: int):
         """``tiles [routes / 128 + el, 4]``, ``n_tiles [1]``, ``perm [routes]`` of the expert sort, allocated on first use."""
