@@ -121,19 +121,24 @@ __device__ __forceinline__ void cta_allreduce_f32_slot(const PeerComm& c, int ch
         const uint2* inbox = reinterpret_cast<const uint2*>(c.data[c.rank]) + (size_t)slot * GLMB_MAX_WORLD * GLMB_AR_SLICE;
         bool late = false;
         for (int i = threadIdx.x; i < count; i += blockDim.x) {
+            // fully unrolled over the largest world so that the arrived values stay in registers
             float vals[GLMB_MAX_WORLD];
             uint32_t pending = ((1u << c.world) - 1u) & ~(1u << c.rank);
             for (uint32_t it = 0; pending && it < c.wait_limit; ++it) {
-                for (int p = 0; p < c.world; ++p) {
-                    if (!(pending >> p & 1u)) continue;
-                    const uint2 v = ld_sys_u2(inbox + (size_t)p * GLMB_AR_SLICE + i);
-                    if (v.y == e) { vals[p] = __uint_as_float(v.x); pending &= ~(1u << p); }
+#pragma unroll
+                for (int p = 0; p < GLMB_MAX_WORLD; ++p) {
+                    if (pending >> p & 1u) {
+                        const uint2 v = ld_sys_u2(inbox + (size_t)p * GLMB_AR_SLICE + i);
+                        if (v.y == e) { vals[p] = __uint_as_float(v.x); pending &= ~(1u << p); }
+                    }
                 }
                 if (it > 128) __nanosleep(64);
             }
             if (pending) late = true;
             float sum = 0.f;
-            for (int p = 0; p < c.world; ++p) sum += (p == c.rank) ? sh[i] : ((pending >> p & 1u) ? 0.f : vals[p]);
+#pragma unroll
+            for (int p = 0; p < GLMB_MAX_WORLD; ++p)
+                if (p < c.world) sum += (p == c.rank) ? sh[i] : ((pending >> p & 1u) ? 0.f : vals[p]);
             sh[i] = sum;
         }
         if (late) raise_status(c.status, GLMB_STATUS_WAIT_TIMEOUT);
