@@ -394,20 +394,21 @@ GLMB_API int glmb_attn_local_merge(const float* part_o, const float* part_ml, co
 // Decode with every key local: the merge of a (row, head)'s chunk partials AND that head's value projection in one launch.
 //   o_lat[r][h] = bf16(sum_c w_c o_c / l)   exactly as attn_local_merge_kernel (same thread-to-column map, same order over chunks)
 //   attn_v[r][h * N + n] = bf16(o_lat[r][h] . w_v[h][n])   exactly as skinny_bf16_kernel with one K part (same lane-to-k map, xor tree)
-// grid (H, rows, N / MV_COLS): a (row, head) is merged redundantly by the N / MV_COLS CTAs that share its value projection (64 KB of
-// L2-resident partials each) so that the 256 KB of a head's value table are streamed by 8 SMs instead of 1; every chunk row a thread
+// grid (H, rows, N / cols): a (row, head) is merged redundantly by the N / cols CTAs that share its value projection (64 KB of
+// L2-resident partials each) so that the 256 KB of a head's value table are streamed by several SMs instead of 1 (8 when a GPU holds 8
+// heads of one row; fewer slices when rows x heads alone fill the machine, where the repeated merges would only cost); every chunk row a thread
 // needs is requested before the first is used, and the CTA's slice of the value table is asked into L2 before the wait for the
 // attention kernel.  One launch and ~3 memory round trips where merge + projection took two launches and ~8.
 #define MV_THREADS 256
-#define MV_COLS 32
+#define MV_MIN_COLS 32
 #define MV_BATCH 16
 __global__ void __launch_bounds__(MV_THREADS)
 attn_merge_vproj_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, const int* __restrict__ sel_counts, int H, int L,
-                        int top_k, int max_chunks, const bf16* __restrict__ w_v, int64_t w_head_stride, int N, bf16* __restrict__ o_lat,
-                        bf16* __restrict__ attn_v) {
+                        int top_k, int max_chunks, const bf16* __restrict__ w_v, int64_t w_head_stride, int N, int cols,
+                        bf16* __restrict__ o_lat, bf16* __restrict__ attn_v) {
     asm volatile("griddepcontrol.launch_dependents;");
-    const int h = blockIdx.x, r = blockIdx.y, n_base = blockIdx.z * MV_COLS;
-    const int n_here = min(MV_COLS, N - n_base);
+    const int h = blockIdx.x, r = blockIdx.y, n_base = blockIdx.z * cols;
+    const int n_here = min(cols, N - n_base);
     const bf16* w_head = w_v + (int64_t)h * w_head_stride;
     if (threadIdx.x == 0) {
         const char* p = reinterpret_cast<const char*>(w_head + (int64_t)n_base * L);
@@ -487,9 +488,13 @@ attn_merge_vproj_kernel(const float* __restrict__ part_o, const float* __restric
 GLMB_API int glmb_attn_merge_vproj(const float* part_o, const float* part_ml, const int* sel_counts, int rows, int H, int L, int top_k,
                                    int max_chunks, const void* w_v, int64_t w_head_stride, int N, void* o_lat, void* attn_v, void* stream) {
     if ((L & 7) || L > 512 || max_chunks > AM_MAX_CHUNKS || N < 1 || rows < 1 || H < 1 || (w_head_stride & 7)) return 1;
-    dim3 grid(H, rows, (N + MV_COLS - 1) / MV_COLS);
+    // slices of the value columns per (row, head): enough CTAs for two per SM, never narrower than MV_MIN_COLS columns
+    int slices = 1;
+    while (slices * 2 * MV_MIN_COLS <= N && (long)H * rows * slices < 2 * 148) slices *= 2;
+    const int cols = ((N + slices - 1) / slices + 1) & ~1;
+    dim3 grid(H, rows, (N + cols - 1) / cols);
     GLMB_LAUNCH(attn_merge_vproj_kernel, grid, MV_THREADS, 0, (cudaStream_t)stream, part_o, part_ml, sel_counts, H, L, top_k, max_chunks,
-                (const bf16*)w_v, w_head_stride, N, (bf16*)o_lat, (bf16*)attn_v);
+                (const bf16*)w_v, w_head_stride, N, cols, (bf16*)o_lat, (bf16*)attn_v);
     return (int)cudaGetLastError();
 }
 
