@@ -126,6 +126,8 @@ class Bench:
         torch.cuda.set_device(self.local_rank)
         self.device = torch.device("cuda", self.local_rank)
         self.gloo = None
+        self._vote_dir, self._votes = None, 0
+        os.environ.setdefault("NCCL_DEBUG", "WARN")  # the version banner of NCCL_DEBUG=VERSION would share stdout with the JSON line
         if self.world > 1:
             dist.init_process_group("nccl", device_id=self.device)
             self.gloo = dist.new_group(backend="gloo")  # the engine's host votes
@@ -168,14 +170,25 @@ class Bench:
 
     # ------------------------------------------------------------------ through the engine
     def engine_run(self, runner, geometry, prompts: list[list[int]], new_tokens: int, capacity: int) -> dict:
-        """``LLMEngine.generate`` / ``generate_concurrent`` with the fleet vote over gloo and a flushed token file on rank 0."""
+        """``LLMEngine.generate`` / ``generate_concurrent`` with the fleet vote (shared memory between the ranks of the box, as the
+        workers use it) and a flushed token file on rank 0."""
         from glm_tpu_b200.engine import request as rq
         from glm_tpu_b200.engine.llm_engine import LLMEngine
-        from glm_tpu_b200.engine.request_session import LocalVote, ProcessGroupVote
+        from glm_tpu_b200.engine.request_session import LocalVote, fleet_vote
         from glm_tpu_b200.worker.gpu_worker import profile_for
 
         profile = profile_for(geometry, capacity)
-        vote = ProcessGroupVote(self.gloo) if self.world > 1 else LocalVote()
+        if self.world > 1:
+            if self._vote_dir is None:
+                import tempfile
+
+                made = [tempfile.mkdtemp(prefix="glm_b200_bench_vote_") if self.rank == 0 else None]
+                self.dist.broadcast_object_list(made, src=0, group=self.gloo)
+                self._vote_dir = made[0]
+            self._votes += 1
+            vote = fleet_vote(self.gloo, self.rank, self.world, self._vote_dir, name=f"vote{self._votes}.shm")
+        else:
+            vote = LocalVote()
         vote_seconds = [0.0]
         inner = vote.all
 

@@ -60,6 +60,106 @@ class ProcessGroupVote:
         return bool(flag.item())
 
 
+class SharedMemoryVote:
+    """All-rank AND for ranks that share one machine: every rank publishes (round number, verdict, vote point) in its own
+    cache line of a small memory-mapped file and spins until every rank has reached the round.  A vote costs a few
+    microseconds instead of the ~100 us of a TCP all-reduce, which matters because the engine votes twice per token.
+
+    Rounds alternate between two verdict slots per rank, so a rank that is one vote ahead never overwrites what a slower
+    rank is still reading; no rank can be two ahead, because leaving round r needs every rank to have entered it.  Ranks that
+    vote at different points (a diverged schedule) and a rank that never arrives within ``timeout`` seconds raise
+    ``EngineFailure`` on everybody who waits -- the vote never hangs.
+
+    Parity: reference ``glm_tpu/distributed/health.py`` (all-host agreement before anything irreversible), here without a
+    network between the ranks.
+    """
+
+    LINE = 64  # bytes per rank: int64 round | int64 verdict[2] | int64 point[2]
+
+    def __init__(self, path, rank: int, world: int, *, timeout: float = 600.0, create: bool = False):
+        import mmap
+        import os
+
+        import numpy as np
+
+        self.rank, self.world, self.timeout = rank, world, timeout
+        size = self.LINE * world
+        if create:
+            fd = os.open(path, os.O_RDWR | os.O_CREAT | os.O_TRUNC, 0o600)
+            os.ftruncate(fd, size)
+        else:
+            fd = os.open(path, os.O_RDWR)
+            if os.fstat(fd).st_size != size:
+                os.close(fd)
+                raise EngineFailure("the vote file was made for another number of ranks")
+        try:
+            self._map = mmap.mmap(fd, size)
+        finally:
+            os.close(fd)
+        self._words = np.frombuffer(self._map, dtype=np.int64).reshape(world, self.LINE // 8)
+        self.round = 0
+        self.log: list[tuple[str, bool]] = []
+
+    @staticmethod
+    def _point_code(point: str) -> int:
+        import zlib
+
+        return zlib.crc32(point.encode()) + 1
+
+    def all(self, ok: bool, point: str) -> bool:
+        import time
+
+        self.round += 1
+        r, slot, words = self.round, self.round & 1, self._words
+        code = self._point_code(point)
+        words[self.rank, 1 + slot] = 1 if ok else 0
+        words[self.rank, 3 + slot] = code
+        words[self.rank, 0] = r  # published last: the verdict and the point are in place when the round number shows
+        deadline = time.monotonic() + self.timeout
+        spins = 0
+        while True:
+            rounds = words[:, 0]
+            if int(rounds.min()) >= r:
+                break
+            spins += 1
+            if spins & 0x3FF == 0:
+                if time.monotonic() > deadline:
+                    behind = [i for i in range(self.world) if int(rounds[i]) < r]
+                    raise EngineFailure(f"rank {self.rank} waited {self.timeout:.0f} s at vote {point!r} (round {r}) for ranks {behind}")
+                time.sleep(0)
+        if any(int(words[i, 3 + slot]) != code for i in range(self.world)):
+            raise EngineFailure(f"the ranks vote at different points in round {r} (this rank: {point!r})")
+        result = all(int(words[i, 1 + slot]) == 1 for i in range(self.world))
+        self.log.append((point, result))
+        return result
+
+    def close(self) -> None:
+        self._words = None
+        try:
+            self._map.close()
+        except (BufferError, ValueError):
+            pass
+
+
+def fleet_vote(group, rank: int, world: int, directory, *, name: str = "vote.shm", timeout: float = 600.0):
+    """The vote for ``world`` ranks of one machine that already share a CPU process group: rank 0 creates the vote file in
+    ``directory``, a barrier publishes it, everybody maps it.  ``GLM_B200_VOTE=gloo`` keeps the votes on the process group."""
+    import os
+    from pathlib import Path
+
+    import torch.distributed as dist
+
+    if os.environ.get("GLM_B200_VOTE", "shm") == "gloo":
+        return ProcessGroupVote(group)
+    path = Path(directory) / name
+    vote = SharedMemoryVote(path, rank, world, timeout=timeout, create=True) if rank == 0 else None
+    dist.barrier(group=group)
+    if vote is None:
+        vote = SharedMemoryVote(path, rank, world, timeout=timeout)
+    dist.barrier(group=group)  # nobody votes before everybody has mapped the file
+    return vote
+
+
 @dataclass
 class LaneState:
     request: dict

@@ -82,6 +82,7 @@ TABLE: dict[str, Row] = {
                            ("kernels", "phases", "mega")),
     "GLM_B200_EXPERT_SPLIT": Row("choice", "", "Routed experts per GPU: whole experts or a column slice of every expert (unset: sliced where the FP8 blocks allow).",
                                  ("", "whole", "sliced")),
+    "GLM_B200_VOTE": Row("choice", "shm", "Host votes of the ranks of one box: through a memory-mapped file, or over the gloo process group.", ("shm", "gloo")),
     "GLM_B200_AR": Row("choice", "pairs", "In-kernel all-reduce: (value, sequence number) pairs, or values + fence + flag.", ("pairs", "flags")),
     "GLM_B200_MEGA_KSPLIT": Row("choice", "", "Fused decode phases: the stand-alone kernels' K decomposition (compat) or an even one (balanced).",
                                 ("", "compat", "balanced")),

@@ -29,7 +29,7 @@ from glm_tpu_b200.engine import request as request_schema
 from glm_tpu_b200.engine import resident_protocol as proto
 from glm_tpu_b200.engine.llm_engine import LLMEngine
 from glm_tpu_b200.engine.outputs import final_channel
-from glm_tpu_b200.engine.request_session import LocalVote, ProcessGroupVote
+from glm_tpu_b200.engine.request_session import LocalVote, fleet_vote
 from glm_tpu_b200.utils.io_utils import persist_json
 
 
@@ -191,7 +191,8 @@ class Worker:
             else:
                 dist.init_process_group("gloo")
                 self.gloo = dist.group.WORLD
-            self.vote = ProcessGroupVote(self.gloo)
+            # the ranks of one box vote through shared memory (a few microseconds a vote; the engine votes twice per token)
+            self.vote = fleet_vote(self.gloo, self.rank, self.world, self.args.run_dir)
         self.check_bound_device()
 
     def check_bound_device(self, device_uuid=None) -> None:

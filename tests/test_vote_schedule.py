@@ -165,3 +165,49 @@ def test_two_ranks_clean_run_has_the_single_rank_schedule():
     fleet, out = two_ranks([Script(), Script()], n=4)
     assert all(isinstance(o, dict) for o in out) and out[0]["token_sha256"] == out[1]["token_sha256"]
     assert fleet.log == HEAD + step(3)
+
+
+# ------------------------------------------------------------------------------------------------ the shared-memory vote itself
+def _shm_rank(path, rank, world, rounds, bad, point_of, out, timeout):
+    from glm_tpu_b200.engine.request_session import SharedMemoryVote
+
+    try:
+        vote = SharedMemoryVote(path, rank, world, timeout=timeout)
+        out.put((rank, [vote.all((rank, i) not in bad, point_of(rank, i)) for i in range(rounds)]))
+    except Exception as exc:  # noqa: BLE001
+        out.put((rank, f"{type(exc).__name__}: {exc}"))
+
+
+def _run_shm(tmp_path, world, rounds, bad=(), point_of=None, absent=(), timeout=10.0):
+    import multiprocessing as mp
+
+    from glm_tpu_b200.engine.request_session import SharedMemoryVote
+
+    path = tmp_path / "vote.shm"
+    SharedMemoryVote(path, 0, world, create=True).close()
+    ctx = mp.get_context("fork")
+    out = ctx.Queue()
+    point_of = point_of or (lambda rank, i: ("validity", "delivery")[i & 1])
+    procs = [ctx.Process(target=_shm_rank, args=(path, r, world, rounds, set(bad), point_of, out, timeout)) for r in range(world) if r not in absent]
+    for p in procs:
+        p.start()
+    results = dict(out.get(timeout=60) for _ in procs)
+    for p in procs:
+        p.join(10)
+    return results
+
+
+def test_shared_memory_vote_is_an_all_rank_and(tmp_path):
+    results = _run_shm(tmp_path, 4, 300, bad={(2, 17), (0, 150), (3, 150)})
+    want = [i not in (17, 150) for i in range(300)]
+    assert all(results[r] == want for r in range(4))  # every rank sees the same verdict in every round, one round apart at most
+
+
+def test_shared_memory_vote_refuses_a_diverged_schedule(tmp_path):
+    results = _run_shm(tmp_path, 2, 5, point_of=lambda rank, i: "delivery" if (rank, i) == (1, 3) else "validity")
+    assert all(isinstance(results[r], str) and "different points" in results[r] for r in range(2))
+
+
+def test_shared_memory_vote_times_out_on_a_missing_rank_instead_of_hanging(tmp_path):
+    results = _run_shm(tmp_path, 3, 2, absent={2}, timeout=0.5)
+    assert all(isinstance(results[r], str) and "waited" in results[r] and "[2]" in results[r] for r in (0, 1))
