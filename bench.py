@@ -34,6 +34,7 @@ import os
 import statistics
 import subprocess
 import sys
+from pathlib import Path
 import tempfile
 import threading
 import time
@@ -337,6 +338,7 @@ def main() -> int:
     extras: dict = {}
     r4 = None
     weights, kv_layout = runner.weights, runner.kv_layout
+    layout, fallbacks = runner.model.layout, runner.model.fallbacks  # the line below names them even if an extra loses the runner
     if not args.no_extras and not incomplete:
         try:
             def timed_prefill(r, lane, n):
@@ -393,7 +395,11 @@ def main() -> int:
                                       "ms_per_step": round(statistics.median(blocks12) / args.steps, 4), "layers": SMALL_BOX_LAYERS}
                 runner = small
         except Exception as exc:
-            extras["error"] = f"{type(exc).__name__}: {exc}"[:300]
+            import traceback
+
+            where = traceback.extract_tb(exc.__traceback__)[-1]
+            extras["error"] = f"{type(exc).__name__}: {exc}"[:300] + f" ({Path(where.filename).name}:{where.lineno})"
+            print(f"[bench rank {b.rank}] extras failed: {extras['error']}", file=sys.stderr, flush=True)
             incomplete = True
 
     baseline = BASELINE_SINGLE_CHAT_TOK_S if args.chats == 1 else BASELINE_FOUR_CHAT_TOK_S * args.chats
@@ -426,11 +432,11 @@ def main() -> int:
                 "prompt_tokens": args.prompt if not args.depth else None,
                 "context_depth": args.depth or args.prompt,
                 "context_fill": "synthetic random cache rows (no prefill)" if args.depth else "real prefill of the prompt",
-                "parallelism": (f"tp{b.world}(heads, mlp, shared expert" + (", routed experts by column)" if runner.model.layout.sliced
+                "parallelism": (f"tp{b.world}(heads, mlp, shared expert" + (", routed experts by column)" if layout.sliced
                                 else f")+ep{b.world}(routed experts)")) if b.world > 1 else "single gpu",
-                "expert_split": runner.model.layout.expert_split,
+                "expert_split": layout.expert_split,
                 "all_reduce": ("(value, sequence) pairs" if os.environ.get("GLM_B200_AR", "pairs") != "flags" else "values + fence + flag") if b.world > 1 else "none",
-                "fallbacks": dict(runner.model.fallbacks),
+                "fallbacks": dict(fallbacks),
                 "comm": args.comm,
                 "kv_layout": kv_layout,
                 "decode_program": rec.kind,
