@@ -130,15 +130,19 @@ class Bench:
         self._vote_dir, self._votes = None, 0
         os.environ.setdefault("NCCL_DEBUG", "WARN")  # the version banner of NCCL_DEBUG=VERSION would share stdout with the JSON line
         if self.world > 1:
-            dist.init_process_group("nccl", device_id=self.device)
-            self.gloo = dist.new_group(backend="gloo")  # the engine's host votes
+            from datetime import timedelta
+
+            # bounded waits everywhere: a rank that fails must cost its peers minutes at most, never the default half hour
+            dist.init_process_group("nccl", device_id=self.device, timeout=timedelta(seconds=300))
+            self.gloo = dist.new_group(backend="gloo", timeout=timedelta(seconds=120))  # host barriers, the vote's rendezvous
             dist.barrier()
         self.gen = torch.Generator().manual_seed(1234)
 
     def barrier(self):
-        if self.world > 1:
-            self.dist.barrier()
+        """Device idle on every rank, then a host barrier (gloo: a peer that never arrives raises here after two minutes)."""
         self.torch.cuda.synchronize()
+        if self.world > 1:
+            self.dist.barrier(group=self.gloo)
 
     def max_over_ranks(self, values: list[float]) -> list[float]:
         t = self.torch.tensor(values, dtype=self.torch.float64, device=self.device)
@@ -181,13 +185,11 @@ class Bench:
         profile = profile_for(geometry, capacity)
         if self.world > 1:
             if self._vote_dir is None:
-                import tempfile
-
                 made = [tempfile.mkdtemp(prefix="glm_b200_bench_vote_") if self.rank == 0 else None]
                 self.dist.broadcast_object_list(made, src=0, group=self.gloo)
                 self._vote_dir = made[0]
             self._votes += 1
-            vote = fleet_vote(self.gloo, self.rank, self.world, self._vote_dir, name=f"vote{self._votes}.shm")
+            vote = fleet_vote(self.gloo, self.rank, self.world, self._vote_dir, name=f"vote{self._votes}.shm", timeout=60.0)
         else:
             vote = LocalVote()
         vote_seconds = [0.0]
@@ -459,7 +461,10 @@ def main() -> int:
     if runner is not None:
         runner.close()
     if b.world > 1:
-        b.dist.barrier()
+        try:
+            b.barrier()
+        except Exception:  # noqa: BLE001 - a peer that failed earlier must not keep this rank from finishing
+            pass
         b.dist.destroy_process_group()
     return 0  # an incomplete run says so in its line ('incomplete': true); the device-timed figure above still stands
 
