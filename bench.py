@@ -128,14 +128,25 @@ class Bench:
         self.device = torch.device("cuda", self.local_rank)
         self.gloo = None
         self._vote_dir, self._votes = None, 0
-        os.environ.setdefault("NCCL_DEBUG", "WARN")  # the version banner of NCCL_DEBUG=VERSION would share stdout with the JSON line
+        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"  # the version banner would share stdout with the JSON line
         if self.world > 1:
             from datetime import timedelta
 
             # bounded waits everywhere: a rank that fails must cost its peers minutes at most, never the default half hour
-            dist.init_process_group("nccl", device_id=self.device, timeout=timedelta(seconds=300))
-            self.gloo = dist.new_group(backend="gloo", timeout=timedelta(seconds=120))  # host barriers, the vote's rendezvous
-            dist.barrier()
+            # the library announces its version on file descriptor 1 when the first communicator comes up: that line belongs on
+            # stderr, stdout carries the one JSON line
+            sys.stdout.flush()
+            saved_stdout = os.dup(1)
+            os.dup2(2, 1)
+            try:
+                dist.init_process_group("nccl", device_id=self.device, timeout=timedelta(seconds=300))
+                self.gloo = dist.new_group(backend="gloo", timeout=timedelta(seconds=120))  # host barriers, the vote's rendezvous
+                dist.barrier()
+                torch.cuda.synchronize()
+            finally:
+                os.dup2(saved_stdout, 1)
+                os.close(saved_stdout)
         self.gen = torch.Generator().manual_seed(1234)
 
     def barrier(self):
