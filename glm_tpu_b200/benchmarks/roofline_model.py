@@ -63,7 +63,9 @@ def busiest_gpu_experts(g: ModelGeometry, world: int, chats: int, samples: int =
     return total_mean / samples, total_max / samples
 
 
-def decode_step_bytes(g: ModelGeometry, world: int, *, chats: int = 1, depth: int = 200, striped: bool = False) -> dict:
+def decode_step_bytes(g: ModelGeometry, world: int, *, chats: int = 1, depth: int = 200, striped: bool = False,
+                      expert_split: str = "whole") -> dict:
+    """``expert_split='sliced'``: every GPU streams ``1 / world`` of every touched expert, so mean and busiest coincide."""
     lay = ParallelLayout(g, world, 0)
     H, Q, L, rd = g.hidden_size, g.q_lora_rank, g.kv_lora_rank, g.qk_rope_head_dim
     hl = lay.heads_local
@@ -83,6 +85,8 @@ def decode_step_bytes(g: ModelGeometry, world: int, *, chats: int = 1, depth: in
             shared += 2 * 3 * lay.shared_cols_local * H
     moe_layers = sum(1 for t in g.mlp_layer_types if t != "dense")
     mean_e, max_e = busiest_gpu_experts(g, world, chats)
+    if expert_split == "sliced" and world > 1:
+        mean_e = max_e = mean_e  # the touched experts of the whole box, divided evenly: what `mean` already is
     routed_mean, routed_max = moe_layers * mean_e * expert_bytes(g), moe_layers * max_e * expert_bytes(g)
     head = 2 * lay.vocab_local * H
     fixed = attention + caches + dense + shared + router + head
@@ -132,19 +136,21 @@ def main(argv=None) -> int:
     ap.add_argument("--depth", type=int, default=200)
     ap.add_argument("--layers", type=int, default=0)
     ap.add_argument("--striped", action="store_true")
+    ap.add_argument("--expert-split", default="sliced", choices=["sliced", "whole"], help="routed experts per GPU (several GPUs)")
+    ap.add_argument("--small-box-layers", type=int, default=12, help="layers on fewer than 8 GPUs (0: round(78 N / 8), the earlier scheme)")
     ap.add_argument("--measured", default="", help="N:ms per step, comma separated, to print the achieved fraction")
     ap.add_argument("--prefill", type=int, default=0, help="also print the compute bound of prefilling a fresh prompt of this many tokens")
     ap.add_argument("--measured-prefill", default="", help="N:ms of that prefill, comma separated")
     args = ap.parse_args(argv)
     bw, kind = measured_hbm_gbs()
     measured = {int(k): float(v) for k, v in (item.split(":") for item in args.measured.split(",") if item)}
-    print(f"decode step, {args.chats} chat(s) at depth {args.depth}; roofline = bytes of the busiest GPU / {bw:.0f} GB/s ({kind} copy bandwidth)\n")
+    print(f"decode step, {args.chats} chat(s) at depth {args.depth}, routed experts {args.expert_split}; roofline = bytes of the busiest GPU / {bw:.0f} GB/s ({kind} copy bandwidth)\n")
     print("| GPUs | layers | attention MB | dense + shared + router MB | routed experts MB (mean / busiest) | caches MB | lm_head MB | total GB (busiest) | roofline ms | measured ms | roofline / measured |")
     print("|---|---|---|---|---|---|---|---|---|---|---|")
     for world in (int(v) for v in args.gpus.split(",")):
-        layers = args.layers or (78 if world >= 8 else max(4, round(78 * world / 8)))
+        layers = args.layers or (78 if world >= 8 else (args.small_box_layers or max(4, round(78 * world / 8))))
         g = glm53_geometry() if layers == 78 else glm53_geometry().truncated(layers)
-        b = decode_step_bytes(g, world, chats=args.chats, depth=args.depth, striped=args.striped)
+        b = decode_step_bytes(g, world, chats=args.chats, depth=args.depth, striped=args.striped, expert_split=args.expert_split)
         roof_ms = b["total_busiest"] / (bw * 1e9) * 1e3
         got = measured.get(world)
         mb = lambda x: f"{x / 1e6:,.0f}"  # noqa: E731
@@ -158,7 +164,7 @@ def main(argv=None) -> int:
         print("| GPUs | layers | projections | attention | indexer | dense + shared + router | routed experts | total TFLOP per GPU | bound ms | measured ms | bound / measured |")
         print("|---|---|---|---|---|---|---|---|---|---|---|")
         for world in (int(v) for v in args.gpus.split(",")):
-            layers = args.layers or (78 if world >= 8 else max(4, round(78 * world / 8)))
+            layers = args.layers or (78 if world >= 8 else (args.small_box_layers or max(4, round(78 * world / 8))))
             g = glm53_geometry() if layers == 78 else glm53_geometry().truncated(layers)
             f = prefill_flops(g, world, args.prefill)
             bound = f["total"] / (tf * 1e12) * 1e3
