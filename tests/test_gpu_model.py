@@ -282,3 +282,24 @@ def test_packed_checkpoint_streams_to_the_device_and_decodes_like_the_arrays_it_
         runner.close()
         tokens.append(out)
     assert tokens[0] == tokens[1]
+
+
+def test_glm53_dimensions_match_the_oracle(native_lib):
+    """The flagship's tensor shapes end to end against the CPU oracle: hidden 6144, 64 heads, MLA ranks 2048 / 512 + 64, the 32 x 128
+    indexer with top-2048, 12,288-wide dense MLPs, 2,048-wide FP8 experts in 128 x 128 blocks -- the first four layers of the
+    architecture (three dense, one MoE; three with their own indexer, one sharing), with 16 routed experts and an 8,192-token
+    vocabulary so that the oracle stays affordable on the CPU.  Tokens are compared under the engine's own discrete decisions."""
+    import dataclasses
+
+    from glm_tpu_b200.config.model import glm53_geometry
+
+    g = dataclasses.replace(glm53_geometry().truncated(4), num_routed_experts=16, vocab_size=8192, eos_ids=(8189, 8190, 8191))
+    ckpt = random_checkpoint(g, seed=11)
+    torch.manual_seed(11)
+    prompt = torch.randint(0, g.vocab_size - 8, (45,)).tolist()
+    out, decisions = _run_engine(g, ckpt, prompt, 6, capacity=256, stripe=64, use_graphs=False, prefill_chunk=32, record=True)
+    assert len(out) == 6 and all(0 <= t < g.vocab_size for t in out)
+    bad, _ = _bad_tokens(g, ckpt, prompt, out, 256, decisions)
+    assert not bad, bad
+    graph_out, _ = _run_engine(g, ckpt, prompt, 6, capacity=256, stripe=64, use_graphs=True, prefill_chunk=32)
+    assert graph_out == out

@@ -6,7 +6,10 @@ in another framework's pool, a loop that cannot afford the allocator's implicit 
 test checks that it returns exactly what the ordinary two-call path returns (and what a plain fp32 softmax attention
 gives, within bf16), on consecutive calls that share that array; that the driver's free-memory figure does not move
 across a call; that the status word reports a clamped index; and that it refuses problems larger than the array or of a
-shape the kernels do not take, with codes that cannot be mistaken for CUDA errors.  It is collected last on purpose.
+shape the kernels do not take, with codes that cannot be mistaken for CUDA errors.  It is collected last on purpose (the file name sorts behind every
+other test file): the free-memory comparison is only meaningful once everything that allocates lazily in this process --
+the CUDA context, the library's module image on the device, handles other tests create -- already exists, and a test
+that leaked device memory before it would show up here as a moving baseline rather than hide.
 """
 
 import ctypes as C
