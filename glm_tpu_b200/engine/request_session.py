@@ -115,7 +115,7 @@ class SharedMemoryVote:
         words[self.rank, 1 + slot] = 1 if ok else 0
         words[self.rank, 3 + slot] = code
         words[self.rank, 0] = r  # published last: the verdict and the point are in place when the round number shows
-        deadline = time.monotonic() + self.timeout
+        started = time.monotonic()
         spins = 0
         while True:
             rounds = words[:, 0]
@@ -123,10 +123,13 @@ class SharedMemoryVote:
                 break
             spins += 1
             if spins & 0x3FF == 0:
-                if time.monotonic() > deadline:
+                # per-token votes meet within microseconds and never get here twice; a vote that waits for a peer's long phase
+                # (a checkpoint load) backs off to a sleep instead of burning a core
+                waited = time.monotonic() - started
+                if waited > self.timeout:
                     behind = [i for i in range(self.world) if int(rounds[i]) < r]
                     raise EngineFailure(f"rank {self.rank} waited {self.timeout:.0f} s at vote {point!r} (round {r}) for ranks {behind}")
-                time.sleep(0)
+                time.sleep(0 if waited < 0.002 else 0.0005 if waited < 1.0 else 0.01)
         if any(int(words[i, 3 + slot]) != code for i in range(self.world)):
             raise EngineFailure(f"the ranks vote at different points in round {r} (this rank: {point!r})")
         result = all(int(words[i, 1 + slot]) == 1 for i in range(self.world))
@@ -141,7 +144,7 @@ class SharedMemoryVote:
             pass
 
 
-def fleet_vote(group, rank: int, world: int, directory, *, name: str = "vote.shm", timeout: float = 600.0):
+def fleet_vote(group, rank: int, world: int, directory, *, name: str = "vote.shm", timeout: float = 3600.0):
     """The vote for ``world`` ranks of one machine that already share a CPU process group: rank 0 creates the vote file in
     ``directory``, a barrier publishes it, everybody maps it.  ``GLM_B200_VOTE=gloo`` keeps the votes on the process group."""
     import os
