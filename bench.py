@@ -107,7 +107,8 @@ def reference_arm() -> int:
         "unavailable": "the reference is JAX 0.10.1 + Pallas/Mosaic TPU kernels on a 32-chip TPU v4 slice; jax, jaxlib and libtpu are not "
                        "installed and cannot be installed offline, and there is no TPU; compare with its published 13.57 tok/s",
     }
-    print(json.dumps(line))
+    if int(os.environ.get("RANK", "0")) == 0:  # one line however many ranks the launcher started
+        print(json.dumps(line))
     return 0
 
 
