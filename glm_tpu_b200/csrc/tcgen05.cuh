@@ -3,6 +3,9 @@
 // encoder (resolved through the runtime's driver entry point, so nothing links against libcuda).
 #pragma once
 
+#include <mutex>
+#include <unordered_map>
+
 #include "common.cuh"
 
 #include <cuda.h>
@@ -90,18 +93,54 @@ static inline EncodeTiledFn encode_tiled() {
     return fn;
 }
 
+// A tensor map is a pure function of (element type, base, extents, leading dimension, box): the same workspaces and weight tables
+// come back on every layer and every chunk, so the encoded maps are kept (per translation unit, under a mutex) instead of asking
+// the driver again for each GEMM call.  The table is emptied when it has grown to 8,192 entries.
+struct TensorMapKey {
+    int kind;
+    const void* base;
+    uint64_t rows, K, ld;
+    uint32_t box_rows;
+    bool operator==(const TensorMapKey& o) const {
+        return kind == o.kind && base == o.base && rows == o.rows && K == o.K && ld == o.ld && box_rows == o.box_rows;
+    }
+};
+struct TensorMapKeyHash {
+    size_t operator()(const TensorMapKey& k) const {
+        size_t h = std::hash<const void*>()(k.base);
+        for (uint64_t v : {(uint64_t)k.kind, k.rows, k.K, k.ld, (uint64_t)k.box_rows}) h = h * 1099511628211ull ^ std::hash<uint64_t>()(v);
+        return h;
+    }
+};
+template <typename Encode>
+static inline int cached_map(CUtensorMap* map, const TensorMapKey& key, Encode encode) {
+    static std::mutex mutex;
+    static std::unordered_map<TensorMapKey, CUtensorMap, TensorMapKeyHash> table;
+    std::lock_guard<std::mutex> lock(mutex);
+    auto hit = table.find(key);
+    if (hit != table.end()) { *map = hit->second; return 0; }
+    const int code = encode(map);
+    if (code == 0) {
+        if (table.size() >= 8192) table.clear();
+        table.emplace(key, *map);
+    }
+    return code;
+}
+
 // [rows, K] bf16 row-major (leading dimension ld elements), box `box_rows` rows x 64 columns, 128-byte swizzle.
 static inline int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t K, uint64_t ld, uint32_t box_rows = 128) {
     EncodeTiledFn fn = encode_tiled();
     if (!fn) return 1;
-    const cuuint64_t dims[2] = {K, rows};
-    const cuuint64_t strides[1] = {ld * 2};
-    const cuuint32_t box[2] = {64, box_rows};
-    const cuuint32_t elem[2] = {1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? 0 : 2;
+    return cached_map(map, TensorMapKey{0, base, rows, K, ld, box_rows}, [&](CUtensorMap* out) {
+        const cuuint64_t dims[2] = {K, rows};
+        const cuuint64_t strides[1] = {ld * 2};
+        const cuuint32_t box[2] = {64, box_rows};
+        const cuuint32_t elem[2] = {1, 1};
+        CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        return r == CUDA_SUCCESS ? 0 : 2;
+    });
 }
 
 
@@ -110,12 +149,14 @@ static inline int make_map(CUtensorMap* map, const void* base, uint64_t rows, ui
 static inline int make_map_u8(CUtensorMap* map, const void* base, uint64_t rows, uint64_t K, uint64_t ld, uint32_t box_rows) {
     EncodeTiledFn fn = encode_tiled();
     if (!fn) return 1;
-    const cuuint64_t dims[2] = {K, rows};
-    const cuuint64_t strides[1] = {ld};
-    const cuuint32_t box[2] = {64, box_rows};
-    const cuuint32_t elem[2] = {1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? 0 : 2;
+    return cached_map(map, TensorMapKey{1, base, rows, K, ld, box_rows}, [&](CUtensorMap* out) {
+        const cuuint64_t dims[2] = {K, rows};
+        const cuuint64_t strides[1] = {ld};
+        const cuuint32_t box[2] = {64, box_rows};
+        const cuuint32_t elem[2] = {1, 1};
+        CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        return r == CUDA_SUCCESS ? 0 : 2;
+    });
 }
