@@ -13,7 +13,7 @@ import time
 
 import pytest
 
-from glm_tpu_b200.config.model import glm53_geometry, tiny_geometry
+from glm_tpu_b200.config.model import glm53_geometry, small_geometry, tiny_geometry
 from glm_tpu_b200.config.parallel import ParallelLayout
 from glm_tpu_b200.engine import resident_protocol as proto
 from glm_tpu_b200.entrypoints.serve.security import api_token
@@ -168,3 +168,39 @@ def test_layout_hash_separates_worlds_and_geometries_and_refuses_uneven_splits()
         ParallelLayout(g, 3, 0)
     with pytest.raises(PlanValidationError, match="rank"):
         ParallelLayout(tiny_geometry(), 2, 2)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_sliced_experts_partition_the_columns_of_every_expert(world, monkeypatch):
+    import torch
+
+    from glm_tpu_b200.config.parallel import default_expert_split
+    from glm_tpu_b200.models.glm_moe_dsa.weights import cut_routed, routed_shape
+
+    g = glm53_geometry()
+    monkeypatch.delenv("GLM_B200_EXPERT_SPLIT", raising=False)
+    assert default_expert_split(g, world) == "sliced" and default_expert_split(g, 1) == "whole"
+    monkeypatch.setenv("GLM_B200_EXPERT_SPLIT", "whole")
+    assert default_expert_split(g, world) == "whole"
+    layouts = [ParallelLayout(g, world, r, "sliced") for r in range(world)]
+    cols = g.moe_intermediate_size // world
+    assert all(lay.experts_resident == g.num_routed_experts and lay.expert_base == 0 and lay.moe_cols_local == cols for lay in layouts)
+    assert sorted(c for lay in layouts for c in lay.moe_col_range) == list(range(g.moe_intermediate_size))
+    assert routed_shape(layouts[0], "gate_proj") == (g.num_routed_experts, cols, g.hidden_size)
+    assert routed_shape(layouts[0], "down_proj") == (g.num_routed_experts, g.hidden_size, cols)
+    assert ParallelLayout(g, world, 0, "sliced").layout_hash != ParallelLayout(g, world, 0, "whole").layout_hash  # the ranks must agree on the split
+    # the cuts of a small stacked table put every weight and every block scale on exactly one GPU
+    import dataclasses
+
+    small = dataclasses.replace(small_geometry(4), moe_intermediate_size=128 * world)  # 8 heads, 16 experts: divisible by 8
+    E, I, H = small.num_routed_experts, small.moe_intermediate_size, small.hidden_size
+    bits_up = torch.arange(E * I * H, dtype=torch.int64).reshape(E, I, H)
+    scale_up = torch.arange(E * (I // 128) * -(-H // 128), dtype=torch.float32).reshape(E, I // 128, -(-H // 128))
+    bits_down = torch.arange(E * H * I, dtype=torch.int64).reshape(E, H, I)
+    scale_down = torch.arange(E * -(-H // 128) * (I // 128), dtype=torch.float32).reshape(E, -(-H // 128), I // 128)
+    ups = [cut_routed(bits_up, scale_up, "up_proj", ParallelLayout(small, world, r, "sliced")) for r in range(world)]
+    downs = [cut_routed(bits_down, scale_down, "down_proj", ParallelLayout(small, world, r, "sliced")) for r in range(world)]
+    assert torch.equal(torch.cat([b for b, _ in ups], dim=1), bits_up) and torch.equal(torch.cat([s for _, s in ups], dim=1), scale_up)
+    assert torch.equal(torch.cat([b for b, _ in downs], dim=2), bits_down) and torch.equal(torch.cat([s for _, s in downs], dim=2), scale_down)
+    with pytest.raises(PlanValidationError, match="FP8 block"):
+        ParallelLayout(dataclasses.replace(small_geometry(4), moe_intermediate_size=64 * world), world, 0, "sliced")  # half a block per GPU
