@@ -343,6 +343,29 @@ moe_combine_kernel(const bf16* __restrict__ dw, const int* __restrict__ topk_ids
     }
 }
 
+// Many rows, several GPUs, library all-reduce: what follows the all-reduce of the routed and the shared partial sums of a prefill
+// chunk, in one launch:  out = bf16( bf16(bf16(routed) * scale) + bf16(shared) )  -- the last line of moe_combine_kernel.
+__global__ void __launch_bounds__(256)
+moe_finish_kernel(const float* __restrict__ routed, const float* __restrict__ shared, int64_t n, float scale, bf16* __restrict__ out) {
+    GLMB_PDL_PROLOGUE();
+    const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i + 3 < n) {
+        const float4 r = *reinterpret_cast<const float4*>(routed + i), s = *reinterpret_cast<const float4*>(shared + i);
+        uint2 packed;
+        packed.x = pack_bf16(bf16_round(bf16_round(r.x) * scale) + bf16_round(s.x), bf16_round(bf16_round(r.y) * scale) + bf16_round(s.y));
+        packed.y = pack_bf16(bf16_round(bf16_round(r.z) * scale) + bf16_round(s.z), bf16_round(bf16_round(r.w) * scale) + bf16_round(s.w));
+        *reinterpret_cast<uint2*>(out + i) = packed;
+    } else {
+        for (int64_t j = i; j < n; ++j) out[j] = __float2bfloat16_rn(bf16_round(bf16_round(routed[j]) * scale) + bf16_round(shared[j]));
+    }
+}
+
+GLMB_API int glmb_moe_finish(const float* routed, const float* shared, int64_t n, float scale, void* out, void* stream) {
+    if (n < 1 || (reinterpret_cast<uintptr_t>(routed) & 15) || (reinterpret_cast<uintptr_t>(shared) & 15) || (reinterpret_cast<uintptr_t>(out) & 7)) return 1;
+    GLMB_LAUNCH(moe_finish_kernel, (unsigned)((n / 4 + 255) / 256 + 1), 256, 0, (cudaStream_t)stream, routed, shared, n, scale, (bf16*)out);
+    return (int)cudaGetLastError();
+}
+
 // ===================================================================================================
 // Host launchers
 #define DISPATCH_R(rows, CALL)                                \

@@ -139,6 +139,7 @@ class Workspace:
         self.idx_key_new = bf(rows, D)
         self._sorted = None
         self._route = None
+        self._pairs: dict = {}
         # many-row workspaces on several GPUs: output and partial-tile slots of the GEMM with the fused all-reduce
         self.r_gemm_out = self.r_gemm_part = None
         if rows > 8 and peer.world > 1 and model.comm_mode == "fused":
@@ -149,6 +150,15 @@ class Workspace:
             except MemoryError:  # staging sized without it: the caller falls back to the library all-reduce, and says so
                 self.r_gemm_out = self.r_gemm_part = None
                 model.note_fallback("GEMM then library all-reduce", f"the staging buffer has no room for the fused GEMM all-reduce of {rows} rows")
+
+    def partial_pair(self, rows: int, H: int) -> torch.Tensor:
+        """``[2, rows, H]`` fp32 (routed and shared partial sums of a chunk, all-reduced together), kept per row count."""
+        pair = self._pairs.get(rows)
+        if pair is None:
+            if len(self._pairs) >= 4:
+                self._pairs.clear()
+            pair = self._pairs[rows] = torch.empty((2, rows, H), dtype=torch.float32, device=self.residual.device)
+        return pair
 
     def route_buffers(self, routes: int, el: int):
         """``tiles [routes / 128 + el, 4]``, ``n_tiles [1]``, ``perm [routes]`` of the expert sort, allocated on first use."""
@@ -237,19 +247,28 @@ class GlmMoeDsaModel:
             dist.all_reduce(partial_f32, group=self.group)
         return partial_f32
 
-    def _mm(self, x: torch.Tensor, w: torch.Tensor, f32: bool = False) -> torch.Tensor:
+    def _mm(self, x: torch.Tensor, w: torch.Tensor, f32: bool = False, out: torch.Tensor | None = None) -> torch.Tensor:
         """``x @ w.T`` (bf16 operands, fp32 accumulate) for many rows: the tcgen05 GEMM; shapes it does not take
-        (a dimension that is not a multiple of 8) go to the library GEMM."""
+        (a dimension that is not a multiple of 8) go to the library GEMM.  ``out``: a ``[rows, N]`` view (unit column stride,
+        16-byte aligned rows) that the kernel writes in place of a fresh tensor."""
         rows, K = x.shape
         N = w.shape[0]
         dtype = torch.float32 if f32 else torch.bfloat16
         if K % 8 == 0 and N % 8 == 0 and x.stride(1) == 1 and w.stride(1) == 1 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 \
                 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0:
-            out = torch.empty((rows, N), dtype=dtype, device=x.device)
-            native.gemm_bf16_tc(x, w, out, status=self.peer.status_ptr)
-            return out
+            direct = (out is not None and out.dtype == dtype and tuple(out.shape) == (rows, N) and out.stride(1) == 1
+                      and out.stride(0) % (4 if f32 else 8) == 0 and out.data_ptr() % 16 == 0)
+            target = out if direct else torch.empty((rows, N), dtype=dtype, device=x.device)
+            native.gemm_bf16_tc(x, w, target, status=self.peer.status_ptr)
+            if out is not None and not direct:
+                out.copy_(target)
+            return out if out is not None else target
         self.note_fallback("library GEMM", f"operands [{rows}x{K}] x [{N}x{K}] are not 16-byte aligned rows of a multiple of 8")
-        return torch.mm(x, w.t(), out_dtype=torch.float32) if f32 else torch.mm(x, w.t())
+        result = torch.mm(x, w.t(), out_dtype=torch.float32) if f32 else torch.mm(x, w.t())
+        if out is not None:
+            out.copy_(result)
+            return out
+        return result
 
     def _fork(self):
         """Make the side stream wait for everything issued so far on the current stream; returns the current stream."""
@@ -294,7 +313,7 @@ class GlmMoeDsaModel:
         if decode:
             native.skinny_bf16(x, w, out, native.SK_OUT_F32, N=n, K=w.shape[1])
         else:
-            out[: x.shape[0], :n] = self._mm(x, w, f32=True)
+            self._mm(x, w, f32=True, out=out[: x.shape[0], :n])
 
     # ------------------------------------------------------------------------------ attention
     def _attention(self, ws: Workspace, lw: LayerWeights, layer: int, rows: int, row_pos, row_lane, row_active, state: DecoderState,
@@ -422,7 +441,7 @@ class GlmMoeDsaModel:
             w_v = lw.kv_b[:, g.qk_nope_head_dim :, :]  # [hl, v, L]
             v = torch.einsum("rhc,hvc->rhv", ws.o_lat[:rows], w_v).reshape(rows, hl * g.v_head_dim)
             if self.world == 1:
-                ws.attn_out[:rows] = self._mm(v, lw.w_o)
+                self._mm(v, lw.w_o, out=ws.attn_out[:rows])
             else:
                 fused_out = self._mm_allreduce(ws, v, lw.w_o)
                 if fused_out is not None:
@@ -527,7 +546,7 @@ class GlmMoeDsaModel:
             else:
                 act = self._swiglu(self._mm(x, lw.dense_gate), self._mm(x, lw.dense_up))
                 if self.world == 1:
-                    ws.update[:rows] = self._mm(act, lw.dense_down)
+                    self._mm(act, lw.dense_down, out=ws.update[:rows])
                 else:
                     fused_out = self._mm_allreduce(ws, act, lw.dense_down)
                     if fused_out is not None:
@@ -584,7 +603,10 @@ class GlmMoeDsaModel:
             shared_partial = ws.partial
         else:
             act = self._swiglu(self._mm(x, lw.shared_gate), self._mm(x, lw.shared_up))
-            shared_partial = self._mm(act, lw.shared_down, f32=True)
+            library_reduce = not (fused or self.world == 1 or self.emulated_shard)
+            # with a library all-reduce ahead the shared partial sums are produced where they will travel from
+            both = ws.partial_pair(rows, H) if library_reduce else None
+            shared_partial = self._mm(act, lw.shared_down, f32=True, out=both[1] if both is not None else None)
         if one_launch:
             native.moe_down_combine(ws.act, ws.topk_w, ws.topk_ids, lw.exp_down_bits, lw.exp_down_scale, shared_partial, rows, tk,
                                     g.routed_scaling_factor, ws.update, kc, native.CH_MLP)
@@ -592,12 +614,13 @@ class GlmMoeDsaModel:
             native.moe_combine(ws.dw, ws.topk_ids, shared_partial, rows, tk, H, ebase, el, g.routed_scaling_factor, False, ws.update,
                                None, kc, native.CH_MLP)
         else:
-            native.moe_combine(ws.dw, ws.topk_ids, shared_partial, rows, tk, H, ebase, el, g.routed_scaling_factor, False, None,
-                               ws.routed_partial)
-            both = torch.stack([ws.routed_partial[:rows], shared_partial[:rows]])
+            # library all-reduce (the NCCL baseline, and prefill chunks): both partial sums travel as one buffer, one kernel finishes
+            if decode:  # (the NCCL baseline of the decode step keeps its shared partial sums in the workspace)
+                both = ws.partial_pair(rows, H)
+                both[1].copy_(shared_partial[:rows])
+            native.moe_combine(ws.dw, ws.topk_ids, None, rows, tk, H, ebase, el, g.routed_scaling_factor, False, None, both[0])
             self._allreduce_rows(both)
-            routed = (both[0].to(torch.bfloat16).float() * g.routed_scaling_factor).to(torch.bfloat16).float()
-            ws.update[:rows] = (routed + both[1].to(torch.bfloat16).float()).to(torch.bfloat16)
+            native.moe_finish(both[0], both[1], g.routed_scaling_factor, ws.update[:rows])
 
     def _route_tiles128(self, topk_ids: torch.Tensor, ebase: int, el: int):
         """Sort this GPU's routes by expert and cut them into 128-route tiles (device-side, no host sync).
@@ -690,7 +713,7 @@ class GlmMoeDsaModel:
         if n <= native.MAX_ROWS:
             native.skinny_bf16(xh, self.w.lm_head, ws.logits, native.SK_OUT_BF16)
         else:
-            ws.logits[:n] = self._mm(xh, self.w.lm_head)
+            self._mm(xh, self.w.lm_head, out=ws.logits[:n])
         return ws.logits[:n]
 
     def sample(self, ws: Workspace, state: DecoderState, logits: torch.Tensor, rows: int, row_active, *, advance: int,

@@ -311,6 +311,14 @@ def gather_rows(src, idx, divisor, dst):
            "gather_rows")
 
 
+def moe_finish(routed_sum, shared_sum, scale, out):
+    """``out = bf16(bf16(bf16(routed_sum) * scale) + bf16(shared_sum))`` over contiguous fp32 tensors of one shape: the step after a
+    library all-reduce of the two partial sums of a prefill chunk."""
+    if not (routed_sum.is_contiguous() and shared_sum.is_contiguous() and out.is_contiguous()) or routed_sum.shape != shared_sum.shape:
+        raise ValueError("moe_finish takes contiguous tensors of one shape")
+    _check(lib().glmb_moe_finish(_p(routed_sum), _p(shared_sum), C.c_int64(routed_sum.numel()), f32(scale), _p(out), _stream()), "moe_finish")
+
+
 def moe_combine(dw, topk_ids, shared_partial, rows, top_k, H, expert_base, experts_local, scale, plain, out, routed_partial=None,
                 comm=None, channel=CH_MLP):
     if routed_partial is None:
