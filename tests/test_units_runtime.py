@@ -204,3 +204,45 @@ def test_sliced_experts_partition_the_columns_of_every_expert(world, monkeypatch
     assert torch.equal(torch.cat([b for b, _ in downs], dim=2), bits_down) and torch.equal(torch.cat([s for _, s in downs], dim=2), scale_down)
     with pytest.raises(PlanValidationError, match="FP8 block"):
         ParallelLayout(dataclasses.replace(small_geometry(4), moe_intermediate_size=64 * world), world, 0, "sliced")  # half a block per GPU
+
+
+def test_checkpoint_tokenizer_json_and_template_file_are_used_and_pinned(tmp_path):
+    """A checkpoint directory with a real ``tokenizer.json`` (a small BPE model trained here, with the chat format's special
+    tokens) and a ``chat_template.jinja``: ``load_tokenizer`` uses the fast tokenizer, renders the checkpoint's own template, and
+    reports the digests of the files it read (they are pinned into every prepared request)."""
+    import hashlib
+
+    tokenizers = pytest.importorskip("tokenizers")
+    pytest.importorskip("jinja2")
+    from tokenizers import models, pre_tokenizers, trainers
+
+    from glm_tpu_b200.tokenizer import SPECIAL_TOKENS, HfTokenizer, chat_template
+
+    tok = tokenizers.Tokenizer(models.BPE(unk_token=None))
+    tok.pre_tokenizer = pre_tokenizers.ByteLevel(add_prefix_space=False)
+    tok.decoder = tokenizers.decoders.ByteLevel()
+    corpus = ["Why is the sky blue?", "Name three prime numbers.", "the quick brown fox jumps over the lazy dog"] * 20
+    tok.train_from_iterator(corpus, trainers.BpeTrainer(vocab_size=400, special_tokens=list(SPECIAL_TOKENS),
+                                                        initial_alphabet=pre_tokenizers.ByteLevel.alphabet()))
+    tok.save(str(tmp_path / "tokenizer.json"))
+    (tmp_path / "tokenizer_config.json").write_text('{"model_max_length": 202752}')
+    template = "[gMASK]<sop>{% for m in messages %}<|{{ m['role'] }}|>{{ m['content'] }}{% endfor %}{% if add_generation_prompt %}<|assistant|>{% endif %}"
+    (tmp_path / "chat_template.jinja").write_text(template)
+
+    loaded = load_tokenizer(tmp_path, vocab_size=1024)
+    assert isinstance(loaded, HfTokenizer) and loaded.vocab_size == tok.get_vocab_size()
+    text = "Why is the sky blue?"
+    ids = loaded.encode(text)
+    assert ids and loaded.decode(ids) == text and len(ids) < len(text.encode())  # merges learned: fewer tokens than bytes
+    assert loaded.files == {name: hashlib.sha256((tmp_path / name).read_bytes()).hexdigest() for name in ("tokenizer.json", "tokenizer_config.json")}
+    assert loaded.template_sha256 == hashlib.sha256(template.encode()).hexdigest()
+    prompt = loaded.apply_chat_template([{"role": "user", "content": text}])
+    user, assistant, gmask = (tok.token_to_id(t) for t in ("<|user|>", "<|assistant|>", "[gMASK]"))
+    assert prompt[0] == gmask and user in prompt and prompt[-1] == assistant  # the checkpoint's template, special tokens as single ids
+    assert loaded.decode(prompt) == "[gMASK]<sop><|user|>" + text + "<|assistant|>"
+    # without the template file the built-in chat format is rendered, and its digest is the pinned one
+    (tmp_path / "chat_template.jinja").unlink()
+    plain = load_tokenizer(tmp_path)
+    assert plain.template_sha256 == hashlib.sha256(open(chat_template.__file__, "rb").read()).hexdigest()
+    assert plain.decode(plain.apply_chat_template([{"role": "user", "content": text}])) == chat_template.render(
+        [{"role": "user", "content": text}], tools=None, reasoning_effort=None, add_generation_prompt=True)
