@@ -184,7 +184,15 @@ def _p(t):
     return C.c_void_p(t.data_ptr())
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_raw_device = getattr(torch._C, "_cuda_getDevice", None)
+
+
 def _stream():
+    """The current CUDA stream of the current device as a pointer.  Asked for on every launch, so it goes through the two raw
+    accessors of the framework (well under a microsecond) instead of building a ``torch.cuda.Stream`` object (~15 us)."""
+    if _raw_stream is not None and _raw_device is not None:
+        return C.c_void_p(_raw_stream(_raw_device()))
     return C.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
