@@ -151,6 +151,62 @@ moe_down_fp8_mma_kernel(const bf16* __restrict__ act, const float* __restrict__ 
     }
 }
 
+// The same projection for a SHORT K (experts sliced by intermediate column: I is a few hundred) and tiles of several routes (prefill
+// chunks of few rows): with K split over the warps a CTA would stream 16 x I bytes and spend its life starting and ending, so here a
+// warp walks the whole K of its own 16 output rows (up to four 64-wide chunks in flight) and a CTA covers 16 * MM_WARPS rows; nothing
+// crosses warps.  Same slices and roundings as `moe_down_fp8_mma_kernel`; the fp32 sum over K runs in one accumulator.
+template <int RT>
+__global__ void __launch_bounds__(MM_THREADS)
+moe_down_fp8_mma_shortk_kernel(const bf16* __restrict__ act, const float* __restrict__ route_weight, const int* __restrict__ tile_expert,
+                               const int* __restrict__ tile_routes, const int* __restrict__ n_tiles, const uint8_t* __restrict__ wd,
+                               const float* __restrict__ sd, int expert_base, int experts_local, int I, int H, bf16* __restrict__ dw) {
+    GLMB_PDL_PROLOGUE();
+    const int tile = blockIdx.y;
+    if (n_tiles && tile >= *n_tiles) return;
+    const int e = tile_expert[tile] - expert_base;
+    if (e < 0 || e >= experts_local) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int n0 = (blockIdx.x * MM_WARPS + warp) * MM_ROWS;
+    if (n0 >= H) return;
+    const int route = g < RT ? tile_routes[tile * RT + g] : -1;
+    const bf16* xr = act + (int64_t)(route >= 0 ? route : 0) * I;
+    const int kb = (I + 127) >> 7;
+    const uint8_t* w_lo = wd + ((int64_t)e * H + n0 + g) * I;
+    const int64_t hi_off = (int64_t)8 * I;
+    const int64_t sofs = ((int64_t)e * ((H + 127) >> 7) + (n0 >> 7)) * kb;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    const int chunks = I >> 6;
+    for (int c0 = 0; c0 < chunks; c0 += 4) {
+        uint4 lo[4], hi[4], x0[4], x1[4];
+        float sc[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int c = c0 + u;
+            x0[u] = make_uint4(0, 0, 0, 0); x1[u] = x0[u];
+            if (c < chunks) {
+                const int k = (c << 6) + t * 16;
+                lo[u] = ld_stream16(w_lo + k); hi[u] = ld_stream16(w_lo + hi_off + k);
+                if (route >= 0) { x0[u] = ld_hot16(xr + k); x1[u] = ld_hot16(xr + k + 8); }
+                sc[u] = sd[sofs + (c >> 1)];
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (c0 + u < chunks) chunk_mma(acc, lo[u], hi[u], sc[u], x0[u], x1[u]);
+    }
+    // C fragment: (row g, routes 2t, 2t+1), (row g + 8, routes 2t, 2t+1)
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        const int col = 2 * t + j;
+        const int p = col < RT ? tile_routes[tile * RT + col] : -1;
+        if (p >= 0) {
+            const float rw = bf16_round(route_weight[p]);
+            dw[(int64_t)p * H + n0 + g] = __float2bfloat16_rn(bf16_round(acc[j]) * rw);
+            dw[(int64_t)p * H + n0 + g + 8] = __float2bfloat16_rn(bf16_round(acc[2 + j]) * rw);
+        }
+    }
+}
+
 // Experts sliced by intermediate column (every GPU holds I columns of EVERY expert): the down projection of all routes of a
 // row, the route sum, the shared expert's partial and the all-reduce over the GPUs in one kernel.  A route's whole K (= this GPU's
 // I columns, a few hundred) fits one warp, so warp w takes route w of the row and nothing is reduced across warps but the route
@@ -268,7 +324,10 @@ int glmb_launch_moe_down_mma(const void* act, const float* route_weight, const i
     GLMB_LAUNCH((moe_down_fp8_mma_kernel<RT_, D_>), grid, MM_THREADS, 0, stream, (const bf16*)act, route_weight, tile_expert, tile_routes, n_tiles, \
                 (const uint8_t*)wd, sd, expert_base, experts_local, I, H, (bf16*)dw)
     if (rt == 1) { if (live <= 2 * 148) CALL(1, 4); else if (live <= 4 * 148) CALL(1, 2); else CALL(1, 1); }
-    else CALL(8, 1);
+    else if (tile_routes && I <= 512) {  // a short K: one warp per 16 output rows
+        GLMB_LAUNCH(moe_down_fp8_mma_shortk_kernel<8>, dim3(ceil_div(H, MM_ROWS * MM_WARPS), tiles), MM_THREADS, 0, stream, (const bf16*)act,
+                    route_weight, tile_expert, tile_routes, n_tiles, (const uint8_t*)wd, sd, expert_base, experts_local, I, H, (bf16*)dw);
+    } else CALL(8, 1);
 #undef CALL
     return (int)cudaGetLastError();
 }

@@ -139,6 +139,7 @@ class Workspace:
         self.idx_key_new = bf(rows, D)
         self._sorted = None
         self._route = None
+        self._route8 = None
         self._pairs: dict = {}
         # many-row workspaces on several GPUs: output and partial-tile slots of the GEMM with the fused all-reduce
         self.r_gemm_out = self.r_gemm_part = None
@@ -167,6 +168,15 @@ class Workspace:
             self._route = (torch.zeros((routes // 128 + el, 4), dtype=torch.int32, device=dev), torch.zeros(1, dtype=torch.int32, device=dev),
                            torch.empty(routes, dtype=torch.int32, device=dev))
         return self._route[0][: routes // 128 + el], self._route[1], self._route[2][:routes]
+
+    def route_buffers8(self, routes: int, el: int):
+        """``tile_expert [routes / 8 + el]``, ``tile_routes [.., 8]``, ``n_tiles [1]``, ``perm [routes]`` of the 8-route expert sort."""
+        tiles = routes // 8 + el
+        if self._route8 is None or self._route8[3].shape[0] < routes or self._route8[0].shape[0] < tiles:
+            dev = self.residual.device
+            self._route8 = (torch.full((tiles,), -1, dtype=torch.int32, device=dev), torch.full((tiles, 8), -1, dtype=torch.int32, device=dev),
+                            torch.zeros(1, dtype=torch.int32, device=dev), torch.empty(routes, dtype=torch.int32, device=dev))
+        return self._route8[0][:tiles], self._route8[1][:tiles], self._route8[2], self._route8[3][:routes]
 
     def sorted_buffers(self, routes: int, H: int, I: int):
         """Expert-sorted activations and SwiGLU outputs of the grouped (prefill) expert GEMM, allocated on first use."""
@@ -217,6 +227,7 @@ class GlmMoeDsaModel:
         # the one-launch expert sort takes up to 256 resident experts and contiguous ids; other shapes use the library-op sort
         # (`_route_tiles128`), and tests set this attribute to compare the two on shapes both take
         self.route_sort_kernel = True
+        self.few_routes_gemv = True  # prefill chunks with <= 8 routes per expert on average: GEMV kernels on 8-route tiles (tests compare)
         self.merge_vproj = os.environ.get("GLM_B200_MERGE_VPROJ", "1") != "0"  # decode: chunk merge + value projection in one launch
         self.prefill_rows_attention = os.environ.get("GLM_B200_PREFILL_ATTENTION", "rows") != "split"
         # Prefill projections whose K is split over the GPUs use the GEMM with the all-reduce in its epilogue (about 1.2x the
@@ -243,7 +254,7 @@ class GlmMoeDsaModel:
     def _allreduce_rows(self, partial_f32: torch.Tensor) -> torch.Tensor:
         import torch.distributed as dist
 
-        if self.world > 1:
+        if self.world > 1 and not self.emulated_shard:
             dist.all_reduce(partial_f32, group=self.group)
         return partial_f32
 
@@ -571,9 +582,14 @@ class GlmMoeDsaModel:
         if self.trace is not None:
             self.trace.setdefault("topk_ids", {})[layer] = ws.topk_ids[:rows].clone()
             self.trace.setdefault("topk_w", {})[layer] = ws.topk_w[:rows].clone()
-        if not decode and rows * tk >= 128 and H % 16 == 0 and I % 16 == 0:
+        sort_kernel = self.route_sort_kernel and el <= 256 and ws.topk_ids[:rows].is_contiguous()
+        # A chunk with at most ~8 routes per expert (a short prompt: 200 rows x 8 routes over 256 experts) is bound by streaming and
+        # decoding the weights of nearly every expert once: the tensor-core GEMV kernels on 8-route tiles do that at a third of the
+        # instructions per weight of the grouped GEMM, whose 128-row tiles would be 95 % padding.
+        few_per_expert = self.few_routes_gemv and sort_kernel and rows * tk <= 8 * E
+        if not decode and not few_per_expert and rows * tk >= 128 and H % 16 == 0 and I % 16 == 0:
             # many rows: expert-sorted routes through the tcgen05 grouped GEMM (FP8 decoded inside the kernel)
-            if self.route_sort_kernel and el <= 256 and ws.topk_ids[:rows].is_contiguous():
+            if sort_kernel:
                 tiles_t, n_tiles, perm = ws.route_buffers(rows * tk, el)
                 native.route_sort128(ws.topk_ids[:rows], ebase, el, tiles_t, n_tiles, perm)
             else:
@@ -587,6 +603,10 @@ class GlmMoeDsaModel:
         else:
             if decode:
                 tile_expert, tile_routes, n_tiles, tiles, rt = ws.topk_ids, None, None, rows * tk, 1
+            elif sort_kernel:
+                tile_expert, tile_routes, n_tiles, scratch = ws.route_buffers8(rows * tk, el)
+                native.route_sort8(ws.topk_ids[:rows], ebase, el, tile_expert, tile_routes, n_tiles, scratch)
+                tiles, rt = tile_expert.shape[0], 8
             else:
                 tile_expert, tile_routes, n_tiles, tiles, rt = self._route_tiles(ws.topk_ids[:rows], E)
             native.moe_gateup_fp8(x, tk, tile_expert, tile_routes, n_tiles, tiles, rt, lw.exp_gate_bits, lw.exp_up_bits,

@@ -313,6 +313,18 @@ def route_sort128(topk_ids, ebase: int, el: int, tiles, n_tiles, perm) -> None:
     _check(lib().glmb_route_sort128(_p(topk_ids), P, int(ebase), int(el), tiles.shape[0], _p(tiles), _p(n_tiles), _p(perm), _stream()), "route_sort128")
 
 
+def route_sort8(topk_ids, ebase: int, el: int, tile_expert, tile_routes, n_tiles, perm) -> None:
+    """The same stable sort cut into tiles of 8 routes for the tensor-core GEMV expert kernels (few routes per expert).
+
+    ``tile_expert``: int32 ``[>= P / 8 + el]`` (global expert ids, -1 past the last tile); ``tile_routes``: int32 ``[tiles, 8]`` (route ids,
+    -1 in empty slots); ``n_tiles``: int32 ``[1]``; ``perm``: int32 ``[P]`` scratch."""
+    P = topk_ids.numel()
+    if tile_routes.shape[0] < tile_expert.shape[0] or tile_routes.shape[1] != 8 or not tile_routes.is_contiguous():
+        raise ValueError("route_sort8: tile_routes must be a contiguous [tiles, 8] tensor with a row per tile_expert entry")
+    _check(lib().glmb_route_sort8(_p(topk_ids), P, int(ebase), int(el), tile_expert.shape[0], _p(tile_expert), _p(tile_routes), _p(n_tiles),
+                                  _p(perm), _stream()), "route_sort8")
+
+
 def gather_rows(src, idx, divisor, dst):
     """``dst[i] = src[idx[i] // divisor]`` (a row of zeros where ``idx[i] < 0``); bf16 rows, width a multiple of 8."""
     _check(lib().glmb_gather_rows(_p(src), C.c_int64(src.stride(0)), _p(idx), divisor, _p(dst), dst.shape[0], dst.shape[1], _stream()),

@@ -102,6 +102,38 @@ def test_route_sort_kernel_matches_the_stable_sort(native_lib, rows, tk, E, ebas
     assert bool((tiles[count:] == 0).all())
 
 
+@pytest.mark.parametrize("rows,tk,E,ebase,el", [(64, 4, 8, 0, 8), (200, 8, 256, 0, 256), (256, 8, 256, 32, 32), (37, 8, 256, 224, 32), (1, 8, 256, 0, 256)])
+def test_route_sort_in_tiles_of_eight(native_lib, rows, tk, E, ebase, el):
+    """The same launch cut into 8-route tiles: per expert of this GPU, in expert order, its routes in route order, eight to a tile
+    (global expert id per tile, -1 in the empty slots of an expert's last tile and in the tiles past the count)."""
+    n = native_lib
+    gen = torch.Generator().manual_seed(rows * 11 + el)
+    skew = torch.rand(E, generator=gen) ** 3 + 0.01
+    ids = torch.multinomial(skew.expand(rows, E), tk, replacement=False, generator=gen).to(torch.int32)
+    if rows == 37:
+        ids[:] = torch.arange(tk, dtype=torch.int32)  # nothing for this GPU's experts [224, 256)
+    flat = ids.reshape(-1).tolist()
+    want_expert, want_routes = [], []
+    for e in range(ebase, ebase + el):
+        mine = [i for i, x in enumerate(flat) if x == e]
+        for j in range(0, len(mine), 8):
+            want_expert.append(e)
+            want_routes.append(mine[j : j + 8] + [-1] * (8 - len(mine[j : j + 8])))
+    P = rows * tk
+    max_tiles = P // 8 + el
+    tile_expert = torch.full((max_tiles,), 7, dtype=torch.int32, device=DEV)
+    tile_routes = torch.full((max_tiles, 8), 7, dtype=torch.int32, device=DEV)
+    n_tiles = torch.full((1,), -5, dtype=torch.int32, device=DEV)
+    scratch = torch.full((P,), 12345, dtype=torch.int32, device=DEV)
+    for _ in range(2):
+        n.route_sort8(ids.to(DEV), ebase, el, tile_expert, tile_routes, n_tiles, scratch)
+    torch.cuda.synchronize()
+    count = int(n_tiles.item())
+    assert count == len(want_expert) <= max_tiles
+    assert tile_expert[:count].cpu().tolist() == want_expert and bool((tile_expert[count:] == -1).all())
+    assert tile_routes[:count].cpu().tolist() == want_routes
+
+
 def test_swiglu_rows_matches_the_elementwise_expression(native_lib):
     n = native_lib
     gen = torch.Generator().manual_seed(5)

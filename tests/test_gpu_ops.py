@@ -109,7 +109,7 @@ def _routed_fixture(E, I, H, seed):
 
 
 @pytest.mark.parametrize("mma", [1, 0], ids=["mma_sync", "fp32_fma"])
-@pytest.mark.parametrize("rows,tiled", [(3, False), (40, True)])
+@pytest.mark.parametrize("rows,tiled", [(3, False), (40, True), (40, "sort_kernel"), (150, "sort_kernel")])
 def test_routed_experts(native_lib, rows, tiled, mma):
     n = native_lib
     n.set_moe_mma(mma)
@@ -135,6 +135,14 @@ def test_routed_experts(native_lib, rows, tiled, mma):
         from glm_tpu_b200.models.glm_moe_dsa.model import GlmMoeDsaModel
 
         te, tr, nt, tiles, rt = GlmMoeDsaModel._route_tiles(None, ids_d, E)
+        if tiled == "sort_kernel":  # the one-launch sort gives the same tiles as the library-op sort
+            te2 = torch.full((tiles,), -7, dtype=torch.int32, device=DEV)
+            tr2 = torch.full((tiles, 8), -7, dtype=torch.int32, device=DEV)
+            nt2, scratch = torch.zeros(1, dtype=torch.int32, device=DEV), torch.empty(rows * tk, dtype=torch.int32, device=DEV)
+            n.route_sort8(ids_d, 0, E, te2, tr2, nt2, scratch)
+            live = int(nt2)
+            assert live == int(nt) and torch.equal(te2, te) and torch.equal(tr2[:live], tr[:live])
+            te, tr, nt = te2, tr2, nt2
     else:
         te, tr, nt, tiles, rt = ids_d, None, None, rows * tk, 1
     n.moe_gateup_fp8(x_d, tk, te, tr, nt, tiles, rt, d["gate"][0], d["up"][0], d["gate"][1], d["up"][1], 0, act)
