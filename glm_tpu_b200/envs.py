@@ -91,6 +91,7 @@ TABLE: dict[str, Row] = {
     "GLM_B200_OVERLAP": Row("flag", True, "Independent branches of a layer on a second stream (1) or one stream (0)."),
     "GLM_B200_FOLD_Q_POST": Row("flag", True, "Decode: query RoPE folded into q-absorb and the indexer (1) or a kernel of its own (0)."),
     "GLM_B200_MERGE_VPROJ": Row("flag", True, "Decode, local keys: chunk merge and value projection in one launch (1) or two (0)."),
+    "GLM_B200_FEW_ROUTES": Row("count", 12, "Prefill chunks below this mean number of routes per expert run the routed experts on the GEMV kernels (8-route tiles)."),
     "GLM_B200_NVTX": Row("flag", False, "NVTX ranges per layer and block."),
     "GLM_B200_INDEXER": Row("choice", "tcgen05", "DSA indexer on tcgen05 or the CUDA-core kernel.", ("tcgen05", "cuda")),
     "GLM_B200_INDEXER_ROWS": Row("flag", True, "Prefill chunks: many-rows tcgen05 indexer (1) or the one-row kernel per row (0)."),

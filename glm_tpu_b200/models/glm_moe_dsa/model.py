@@ -227,7 +227,8 @@ class GlmMoeDsaModel:
         # the one-launch expert sort takes up to 256 resident experts and contiguous ids; other shapes use the library-op sort
         # (`_route_tiles128`), and tests set this attribute to compare the two on shapes both take
         self.route_sort_kernel = True
-        self.few_routes_gemv = True  # prefill chunks with <= 8 routes per expert on average: GEMV kernels on 8-route tiles (tests compare)
+        self.few_routes_gemv = True  # prefill chunks with few routes per expert on average: GEMV kernels on 8-route tiles (tests compare)
+        self.few_routes_limit = int(os.environ.get("GLM_B200_FEW_ROUTES", "12"))  # mean routes per expert up to which that path is taken
         self.merge_vproj = os.environ.get("GLM_B200_MERGE_VPROJ", "1") != "0"  # decode: chunk merge + value projection in one launch
         self.prefill_rows_attention = os.environ.get("GLM_B200_PREFILL_ATTENTION", "rows") != "split"
         # Prefill projections whose K is split over the GPUs use the GEMM with the all-reduce in its epilogue (about 1.2x the
@@ -583,10 +584,11 @@ class GlmMoeDsaModel:
             self.trace.setdefault("topk_ids", {})[layer] = ws.topk_ids[:rows].clone()
             self.trace.setdefault("topk_w", {})[layer] = ws.topk_w[:rows].clone()
         sort_kernel = self.route_sort_kernel and el <= 256 and ws.topk_ids[:rows].is_contiguous()
-        # A chunk with at most ~8 routes per expert (a short prompt: 200 rows x 8 routes over 256 experts) is bound by streaming and
-        # decoding the weights of nearly every expert once: the tensor-core GEMV kernels on 8-route tiles do that at a third of the
-        # instructions per weight of the grouped GEMM, whose 128-row tiles would be 95 % padding.
-        few_per_expert = self.few_routes_gemv and sort_kernel and rows * tk <= 8 * E
+        # A chunk with few routes per expert (a short prompt: 200 rows x 8 routes over 256 experts are ~6 each) is bound by streaming
+        # and decoding the weights of nearly every expert once: the tensor-core GEMV kernels on 8-route tiles do that at a third of
+        # the instructions per weight of the grouped GEMM, whose 128-row tiles would be 95 % padding.  Measured on one rank's shard
+        # of eight: 0.93 ms less per 3 MoE layers at 200 rows, 0.46 ms less at 320, level at 512; taken below a mean of 12 routes.
+        few_per_expert = self.few_routes_gemv and sort_kernel and rows * tk < self.few_routes_limit * E
         if not decode and not few_per_expert and rows * tk >= 128 and H % 16 == 0 and I % 16 == 0:
             # many rows: expert-sorted routes through the tcgen05 grouped GEMM (FP8 decoded inside the kernel)
             if sort_kernel:
