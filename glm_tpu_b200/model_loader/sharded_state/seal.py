@@ -33,16 +33,39 @@ def install(target: Path, geometry, manifest: dict) -> dict:
     return seal
 
 
+SEAL_KEYS = ("schema", "manifest_sha256", "geometry_sha256", "world", "total_bytes", "seal_sha256")
+
+
+def _read_object(path: Path, what: str) -> dict:
+    """A JSON object from ``path``; anything else (absent, unreadable, not JSON, not an object) is a validation error."""
+    try:
+        value = json.loads(path.read_text())
+    except FileNotFoundError:
+        raise CheckpointValidationError(f"{what} is missing") from None
+    except (OSError, UnicodeDecodeError, ValueError) as exc:
+        raise CheckpointValidationError(f"{what} cannot be read as JSON: {exc}") from None
+    if not isinstance(value, dict):
+        raise CheckpointValidationError(f"{what} is not a JSON object")
+    return value
+
+
 def read_seal(target: Path) -> tuple[dict, dict]:
-    """``(seal, manifest)`` after checking that both are self-consistent and belong together."""
+    """``(seal, manifest)`` after checking that both are self-consistent and belong together: the seal has exactly its keys and
+    hashes to its own digest, the manifest on disk hashes to the digest the seal names, and the facts both state (geometry,
+    GPU count, total bytes) are equal."""
     target = Path(target)
     if not (target / fmt.SEAL_FILE).exists():
         raise CheckpointValidationError("no SUCCESS seal: the checkpoint was never completed")
-    seal = json.loads((target / fmt.SEAL_FILE).read_text())
+    seal = _read_object(target / fmt.SEAL_FILE, "the SUCCESS seal")
+    if sorted(seal) != sorted(SEAL_KEYS) or seal["schema"] != "glm_b200_seal_v1":
+        raise CheckpointValidationError("the SUCCESS seal is not a glm_b200_seal_v1 record")
     body = {k: v for k, v in seal.items() if k != "seal_sha256"}
-    if seal.get("seal_sha256") != hashlib.sha256(canonical_hash_bytes(body)).hexdigest():
+    if seal["seal_sha256"] != hashlib.sha256(canonical_hash_bytes(body)).hexdigest():
         raise CheckpointValidationError("the SUCCESS seal does not match its own digest")
-    manifest = json.loads((target / fmt.MANIFEST_FILE).read_text())
+    manifest = _read_object(target / fmt.MANIFEST_FILE, "the manifest")
     if hashlib.sha256(canonical_hash_bytes(manifest)).hexdigest() != seal["manifest_sha256"]:
         raise CheckpointValidationError("the manifest on disk is not the one the seal closes")
+    for key in ("geometry_sha256", "world", "total_bytes"):
+        if manifest.get(key) != seal[key]:
+            raise CheckpointValidationError(f"seal and manifest state different {key}")
     return seal, manifest

@@ -23,10 +23,13 @@ from glm_tpu_b200.model_loader.sharded_state import seal as seal_mod
 
 
 def read_geometry(target: Path) -> ModelGeometry:
-    raw = json.loads((Path(target) / fmt.GEOMETRY_FILE).read_text())
-    for key in ("indexer_types", "mlp_layer_types", "fp8_block_shape", "eos_ids"):
-        raw[key] = tuple(raw[key])
-    return ModelGeometry(**raw)
+    raw = seal_mod._read_object(Path(target) / fmt.GEOMETRY_FILE, "the geometry file")
+    try:
+        for key in ("indexer_types", "mlp_layer_types", "fp8_block_shape", "eos_ids"):
+            raw[key] = tuple(raw[key])
+        return ModelGeometry(**raw)
+    except (KeyError, TypeError, ValueError) as exc:
+        raise CheckpointValidationError(f"the geometry file does not describe a model geometry: {exc}") from None
 
 
 def verify_runtime_checkpoint(target: Path, files: list | None = None, pins: dict | None = None, rehash: bool = True) -> dict:

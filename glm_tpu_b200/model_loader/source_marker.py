@@ -47,11 +47,33 @@ def mark_source(root: Path, *, hash_shards: bool = False) -> dict:
 
 
 def require_marker(root: Path) -> dict:
-    path = Path(root) / MARKER_FILE
+    """The marker of ``root`` after checking it against what is on disk now: the inventory (every tensor, every shard size) and
+    the digests of the small files (configuration, tokenizer, template, index) it recorded.  The shards' contents are not read
+    again here: their sizes and headers are part of the inventory, their bytes are hashed when they are packed."""
+    root = Path(root)
+    path = root / MARKER_FILE
     if not path.exists():
         raise CheckpointValidationError("the source has no SOURCE_COMPLETE.json: run `checkpoint mark-source` first")
-    marker = json.loads(path.read_text())
+    try:
+        marker = json.loads(path.read_text())
+    except (OSError, UnicodeDecodeError, ValueError) as exc:
+        raise CheckpointValidationError(f"SOURCE_COMPLETE.json cannot be read as JSON: {exc}") from None
+    if not isinstance(marker, dict) or marker.get("schema") != "glm_b200_source_marker_v1":
+        raise CheckpointValidationError("SOURCE_COMPLETE.json is not a glm_b200_source_marker_v1 record")
     inv = source_inventory.read_source_inventory(root)
     if marker.get("inventory_sha256") != inv.sha256:
         raise CheckpointValidationError("the source changed after it was marked complete")
+    shards = marker.get("shards")
+    if not isinstance(shards, dict) or {n: r.get("size") if isinstance(r, dict) else None for n, r in shards.items()} != dict(inv.shards):
+        raise CheckpointValidationError("the marker's shard list differs from the source")
+    small = marker.get("small_files")
+    if not isinstance(small, dict):
+        raise CheckpointValidationError("the marker lists no small files")
+    present = {name for name in SMALL_FILES if (root / name).exists()}
+    if present != set(small):
+        raise CheckpointValidationError("configuration files were added or removed after the source was marked: "
+                                        + ", ".join(sorted(present ^ set(small))))
+    for name, digest in sorted(small.items()):
+        if file_sha256(root / name) != digest:
+            raise CheckpointValidationError(f"{name} changed after the source was marked complete")
     return marker
