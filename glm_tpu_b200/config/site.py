@@ -94,6 +94,11 @@ class SiteConfig:
             doc = tomllib.loads(path.read_text(encoding="utf-8"))
         except tomllib.TOMLDecodeError as exc:
             raise ConfigValidationError(f"the site file is not valid TOML: {exc}") from exc
+        return cls.from_document(doc, str(path))
+
+    @classmethod
+    def from_document(cls, doc: dict, source: str) -> "SiteConfig":
+        """The tables of a site (as parsed TOML, or rebuilt from a resolved site) validated key by key."""
         unknown = set(doc) - set(TABLE_KEYS)
         if unknown:
             raise ConfigValidationError(f"unknown site tables: {sorted(unknown)}")
@@ -156,7 +161,7 @@ class SiteConfig:
             master_port=integer("launch", "master_port", 29577, 1024, 65535),
             wall_seconds=integer("launch", "wall_seconds", 86400, 1, 30 * 86400),
             serve_port=integer("serve", "port", 8011, 1024, 65535),
-            source=str(path),
+            source=source,
         )
 
     def _with_env(self) -> "SiteConfig":
@@ -188,13 +193,23 @@ class SiteConfig:
             raise ConfigValidationError("the staged site is not the controller's (digest differs)")
         import json
 
-        doc = json.loads(raw)
         try:
-            paths = Paths(**{k: (Path(v) if v is not None else None) for k, v in doc.pop("paths").items()})
-            doc["allowed_branches"] = tuple(doc["allowed_branches"])
-            site = cls(paths=paths, source=str(path), **doc)
-        except (TypeError, KeyError) as exc:
-            raise ConfigValidationError("the staged site does not have the fields of a resolved site") from exc
+            doc = json.loads(raw)
+        except ValueError as exc:
+            raise ConfigValidationError(f"the staged site is not JSON: {exc}") from exc
+        if type(doc) is not dict or set(doc) != set(cls().resolved()) or type(doc["paths"]) is not dict:
+            raise ConfigValidationError("the staged site does not have the fields of a resolved site")
+        # back into the tables of a site file, so that a staged site passes exactly the checks a site file passes
+        tables = {
+            "box": {"gpus": doc["gpus"]},
+            "paths": {k: v for k, v in doc["paths"].items() if v is not None},
+            "checkpoint": {"manifest_sha256": doc["manifest_sha256"], "source_marker_sha256": doc["source_marker_sha256"]},
+            "topology": {"binding_sha256": doc["topology_binding_sha256"]},
+            "launch": {"policy": doc["policy"], "master_port": doc["master_port"], "wall_seconds": doc["wall_seconds"],
+                       "allowed_branches": doc["allowed_branches"], "expected_origin": doc["expected_origin"], "require_pushed": doc["require_pushed"]},
+            "serve": {"port": doc["serve_port"]},
+        }
+        site = cls.from_document(tables, str(path))
         if site.resolved_json() != raw:
             raise ConfigValidationError("the staged site is not in canonical form")
         return site
