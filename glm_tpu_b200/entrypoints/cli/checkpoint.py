@@ -1,6 +1,8 @@
 """``glm-b200 checkpoint inventory|mark-source|pack|verify``.
 
-Every action prints one JSON report.  ``pack`` holds the workload lease of the site's run root while it writes.
+Every action prints one JSON report.  ``pack`` holds the workload lease of the site's run root while it writes and refuses a
+source whose marker is not the one the site pins (``[checkpoint] source_marker_sha256``, printed by ``mark-source``); ``verify``
+refuses a checkpoint that is not the pinned one (``manifest_sha256``, printed by ``pack``).
 
 Parity: reference ``glm_tpu/entrypoints/cli/checkpoint.py``.
 """
@@ -32,15 +34,16 @@ def main(args) -> int:
             report["geometry_hash"] = g.geometry_hash
             report["matches_pinned_glm53"] = g.geometry_hash == assets.load_pinned_geometry().geometry_hash
     elif args.action == "mark-source":
-        marker = source_marker.mark_source(args.source)
+        marker = source_marker.mark_source(args.source, hash_shards=getattr(args, "hash_shards", False))
         report = {"ok": True, "source": str(args.source), "inventory_sha256": marker["inventory_sha256"],
-                  "tensor_count": marker["tensor_count"], "total_bytes": marker["total_bytes"]}
+                  "tensor_count": marker["tensor_count"], "total_bytes": marker["total_bytes"],
+                  "marker_sha256": source_marker.marker_sha256(args.source)}
     elif args.action == "pack":
         from glm_tpu_b200.executor.pack_job import pack_checkpoint
 
         site = SiteConfig.load(getattr(args, "site", None))
         report = pack_checkpoint(args.source, args.target, args.gpus, run_root=site.paths.run_root, layers=args.layers,
-                                 expert_split=getattr(args, "expert_split", "auto"))
+                                 expert_split=getattr(args, "expert_split", "auto"), pins=site.checkpoint_pins)
     else:
         from glm_tpu_b200.model_loader.sharded_state.verify import verify_runtime_checkpoint
 

@@ -124,6 +124,7 @@ def build_parser() -> argparse.ArgumentParser:
     inv.add_argument("source", type=Path)
     mark = cks.add_parser("mark-source", help="write SOURCE_COMPLETE.json after checking the source against its index")
     mark.add_argument("source", type=Path)
+    mark.add_argument("--hash-shards", action="store_true", help="record a SHA-256 of every shard (reads the whole source)")
     pack = cks.add_parser("pack", help="pack a source checkpoint into per-GPU runtime shards")
     pack.add_argument("source", type=Path)
     pack.add_argument("target", type=Path)
@@ -131,8 +132,10 @@ def build_parser() -> argparse.ArgumentParser:
     pack.add_argument("--layers", type=int, default=0)
     pack.add_argument("--expert-split", default="auto", choices=["auto", "whole", "sliced"],
                       help="routed experts per GPU: whole experts, or a column slice of every expert (auto: sliced where the FP8 blocks allow)")
+    pack.add_argument("--site", type=Path, help="site file (default: the configured one); its [checkpoint] source_marker_sha256 pins the source")
     ver = cks.add_parser("verify", help="re-hash a packed checkpoint against its manifest and seal")
     ver.add_argument("target", type=Path)
+    ver.add_argument("--site", type=Path, help="site file (default: the configured one); its [checkpoint] manifest_sha256 pins the checkpoint")
     ck.set_defaults(fn=_checkpoint)
 
     topo = sub.add_parser("topology", help="capture and bind the GPU topology")
@@ -154,8 +157,18 @@ def build_parser() -> argparse.ArgumentParser:
 
 
 def main(argv: Sequence[str] | None = None) -> int:
+    """Exit status 0: done; 1: the command ran and reports a failure; 2: refused before anything ran (an invalid site file,
+    checkpoint, request or argument), with one JSON line on stderr saying which check refused and why."""
     args = build_parser().parse_args(argv)
-    return args.fn(args)
+    try:
+        return args.fn(args)
+    except ValueError as exc:
+        from glm_tpu_b200 import exceptions
+
+        if not isinstance(exc, (exceptions.ConfigValidationError, exceptions.RequestValidationError, exceptions.ApiError)):
+            raise  # not a refusal of ours: a defect, and it should look like one
+        print(json.dumps({"ok": False, "refused": type(exc).__name__, "message": str(exc)}, sort_keys=True), file=sys.stderr)
+        return 2
 
 
 if __name__ == "__main__":

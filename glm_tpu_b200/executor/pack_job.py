@@ -24,11 +24,14 @@ from glm_tpu_b200.model_loader.sharded_state import seal, verify
 
 
 def pack_checkpoint(source: Path, target: Path, world: int, *, run_root: Path | None = None, layers: int = 0, jobs: int = 0,
-                    require_marker: bool = True, timeout: float = 24 * 3600.0, expert_split: str = "auto") -> dict:
+                    require_marker: bool = True, timeout: float = 24 * 3600.0, expert_split: str = "auto", pins: dict | None = None) -> dict:
     source, target = Path(source), Path(target)
     if (target / "SUCCESS").exists():
         raise CheckpointValidationError(f"{target} is already a sealed checkpoint")
-    marker = source_marker.require_marker(source) if require_marker else None
+    pinned = (pins or {}).get("source_marker_sha256", "")
+    if pinned and not require_marker:
+        raise CheckpointValidationError("a pinned source marker cannot be waived")
+    marker = source_marker.require_marker(source, pinned) if require_marker else None
     inv = source_inventory.read_source_inventory(source)
     geometry = pack_worker.source_geometry(source, layers)
     if expert_split == "auto":  # the split the runner would choose for this geometry on this many GPUs
@@ -74,7 +77,8 @@ def pack_checkpoint(source: Path, target: Path, world: int, *, run_root: Path | 
         report = verify.verify_runtime_checkpoint(target)
         return {"ok": True, "target": str(target), "world": world, "expert_split": expert_split, "files": report["files"], "total_bytes": man["total_bytes"],
                 "manifest_sha256": sealed["manifest_sha256"], "geometry_sha256": geometry.geometry_hash,
-                "source_inventory_sha256": inv.sha256, "source_marker": bool(marker), "seconds": round(time.time() - started, 3)}
+                "source_inventory_sha256": inv.sha256, "source_marker": bool(marker),
+                "source_marker_sha256": source_marker.marker_sha256(source) if marker else "", "seconds": round(time.time() - started, 3)}
 
     if run_root is None:
         return body()

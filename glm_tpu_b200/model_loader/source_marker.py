@@ -46,8 +46,14 @@ def mark_source(root: Path, *, hash_shards: bool = False) -> dict:
     return marker
 
 
-def require_marker(root: Path) -> dict:
-    """The marker of ``root`` after checking it against what is on disk now: the inventory (every tensor, every shard size) and
+def marker_sha256(root: Path) -> str:
+    """SHA-256 of the marker file's bytes: what a site file pins as ``[checkpoint] source_marker_sha256``."""
+    return file_sha256(Path(root) / MARKER_FILE)
+
+
+def require_marker(root: Path, pin: str = "") -> dict:
+    """The marker of ``root`` after checking it against ``pin`` (the digest of the marker file, when one is pinned) and against
+    what is on disk now: the inventory (every tensor, every shard size) and
     the digests of the small files (configuration, tokenizer, template, index) it recorded.  The shards' contents are not read
     again here: their sizes and headers are part of the inventory, their bytes are hashed when they are packed."""
     root = Path(root)
@@ -60,6 +66,8 @@ def require_marker(root: Path) -> dict:
         raise CheckpointValidationError(f"SOURCE_COMPLETE.json cannot be read as JSON: {exc}") from None
     if not isinstance(marker, dict) or marker.get("schema") != "glm_b200_source_marker_v1":
         raise CheckpointValidationError("SOURCE_COMPLETE.json is not a glm_b200_source_marker_v1 record")
+    if pin and marker_sha256(root) != pin:
+        raise CheckpointValidationError("the source's marker is not the pinned one ([checkpoint] source_marker_sha256)")
     inv = source_inventory.read_source_inventory(root)
     if marker.get("inventory_sha256") != inv.sha256:
         raise CheckpointValidationError("the source changed after it was marked complete")

@@ -1,0 +1,136 @@
+"""``glm-b200 checkpoint ...`` from the command line: one JSON report per action, the two pins of the site file enforced where
+they belong (the source marker by ``pack``, the manifest by ``verify``), and every refusal as exit status 2 with one JSON line on
+stderr -- never a traceback, never a half-done target.
+
+Reference counterpart: ``tests/entrypoints/cli/test_checkpoint.py``."""
+
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+
+from glm_tpu_b200.config.model import tiny_geometry
+from glm_tpu_b200.entrypoints.cli import main as cli
+from glm_tpu_b200.model_loader import export, source_marker
+from glm_tpu_b200.model_loader.sharded_state import format as fmt
+from glm_tpu_b200.models.glm_moe_dsa.weights import random_checkpoint
+
+
+@pytest.fixture
+def source(tmp_path, monkeypatch):
+    monkeypatch.setenv("GLM_B200_RUN_ROOT", str(tmp_path / "runs"))
+    monkeypatch.setenv("GLM_B200_SITE_CONFIG", str(tmp_path / "no-site.toml"))
+    monkeypatch.delenv("GLM_B200_MODEL_PATH", raising=False)
+    g = tiny_geometry()
+    export.export_source(random_checkpoint(g, seed=6), g, tmp_path / "src", shards=2)
+    return tmp_path / "src"
+
+
+def site_file(tmp_path, **pins):
+    path = tmp_path / "site.toml"
+    path.write_text('[paths]\nrun_root = "%s"\n[checkpoint]\n' % (tmp_path / "runs") + "".join(f'{k} = "{v}"\n' for k, v in pins.items()))
+    os.chmod(path, 0o600)
+    return path
+
+
+def run(capsys, *argv):
+    code = cli.main([str(a) for a in argv])
+    captured = capsys.readouterr()
+    return code, captured.out, captured.err
+
+
+def refusal(err: str) -> dict:
+    lines = err.strip().splitlines()
+    assert len(lines) == 1, err  # one line, no traceback
+    report = json.loads(lines[0])
+    assert report["ok"] is False and set(report) == {"ok", "refused", "message"}
+    return report
+
+
+def test_each_action_prints_one_report(source, tmp_path, capsys):
+    code, out, err = run(capsys, "checkpoint", "inventory", source)
+    inv = json.loads(out)
+    assert code == 0 and err == "" and inv["ok"] and inv["shards"] == 2 and inv["tensors"] > 10 and len(inv["inventory_sha256"]) == 64
+    assert inv["matches_pinned_glm53"] is False and sum(inv["bytes_by_dtype"].values()) <= inv["total_bytes"]
+
+    code, out, _ = run(capsys, "checkpoint", "mark-source", source)
+    marked = json.loads(out)
+    assert code == 0 and marked["inventory_sha256"] == inv["inventory_sha256"] and marked["tensor_count"] == inv["tensors"]
+    assert marked["marker_sha256"] == fmt.file_sha256(source / source_marker.MARKER_FILE)  # the value a site file pins
+
+    code, out, _ = run(capsys, "checkpoint", "pack", source, tmp_path / "packed", "--gpus", "2", "--expert-split", "whole")
+    packed = json.loads(out)
+    assert code == 0 and packed["ok"] and packed["world"] == 2 and packed["expert_split"] == "whole"
+    assert packed["source_marker_sha256"] == marked["marker_sha256"] and packed["source_inventory_sha256"] == inv["inventory_sha256"]
+
+    code, out, _ = run(capsys, "checkpoint", "verify", tmp_path / "packed")
+    verified = json.loads(out)
+    assert code == 0 and verified["ok"] and verified["manifest_sha256"] == packed["manifest_sha256"] and "manifest_files" not in verified
+    assert sorted(verified["files"]) == sorted(packed["files"])
+
+
+def test_pack_enforces_the_pinned_source_marker(source, tmp_path, capsys):
+    assert run(capsys, "checkpoint", "mark-source", source)[0] == 0
+    good = fmt.file_sha256(source / source_marker.MARKER_FILE)
+    code, out, err = run(capsys, "checkpoint", "pack", source, tmp_path / "packed", "--gpus", "2", "--site", site_file(tmp_path, source_marker_sha256="0" * 64))
+    assert code == 2 and out == ""
+    assert refusal(err) == {"ok": False, "refused": "CheckpointValidationError",
+                            "message": "the source's marker is not the pinned one ([checkpoint] source_marker_sha256)"}
+    assert not (tmp_path / "packed").exists()  # refused before the target was touched
+    code, out, _ = run(capsys, "checkpoint", "pack", source, tmp_path / "packed", "--gpus", "2", "--site", site_file(tmp_path, source_marker_sha256=good))
+    assert code == 0 and json.loads(out)["source_marker_sha256"] == good
+
+
+def test_verify_enforces_the_pinned_manifest(source, tmp_path, capsys):
+    run(capsys, "checkpoint", "mark-source", source)
+    manifest = json.loads(run(capsys, "checkpoint", "pack", source, tmp_path / "packed", "--gpus", "2")[1])["manifest_sha256"]
+    code, out, err = run(capsys, "checkpoint", "verify", tmp_path / "packed", "--site", site_file(tmp_path, manifest_sha256="f" * 64))
+    assert code == 2 and out == "" and refusal(err)["message"] == "the checkpoint is not the pinned one"
+    assert run(capsys, "checkpoint", "verify", tmp_path / "packed", "--site", site_file(tmp_path, manifest_sha256=manifest))[0] == 0
+
+
+def test_refusals_are_one_json_line_and_exit_status_2(source, tmp_path, capsys):
+    code, _, err = run(capsys, "checkpoint", "pack", source, tmp_path / "packed", "--gpus", "2")  # never marked
+    assert code == 2 and "mark-source" in refusal(err)["message"]
+    empty = tmp_path / "empty"
+    empty.mkdir()
+    code, _, err = run(capsys, "checkpoint", "inventory", empty)
+    assert code == 2 and refusal(err)["refused"] == "CheckpointValidationError"
+    code, _, err = run(capsys, "checkpoint", "verify", empty)
+    assert code == 2 and "never completed" in refusal(err)["message"]
+    run(capsys, "checkpoint", "mark-source", source)
+    run(capsys, "checkpoint", "pack", source, tmp_path / "packed", "--gpus", "2")
+    code, _, err = run(capsys, "checkpoint", "pack", source, tmp_path / "packed", "--gpus", "2")
+    assert code == 2 and "already a sealed checkpoint" in refusal(err)["message"]
+    shard = tmp_path / "packed" / fmt.SHARED_FILE
+    os.chmod(shard, 0o600)
+    with open(shard, "r+b") as f:
+        f.seek(-1, os.SEEK_END)
+        last = f.read(1)
+        f.seek(-1, os.SEEK_END)
+        f.write(bytes([last[0] ^ 1]))
+    code, _, err = run(capsys, "checkpoint", "verify", tmp_path / "packed")
+    assert code == 2 and "content digest differs" in refusal(err)["message"]
+    bad_site = tmp_path / "bad.toml"
+    bad_site.write_text("[paths]\n")
+    os.chmod(bad_site, 0o644)
+    code, _, err = run(capsys, "checkpoint", "verify", tmp_path / "packed", "--site", bad_site)
+    assert code == 2 and refusal(err)["refused"] == "ConfigValidationError" and "0600" in refusal(err)["message"]
+
+
+def test_a_defect_still_looks_like_a_defect(source, tmp_path, capsys):
+    run(capsys, "checkpoint", "mark-source", source)
+    with pytest.raises(FileExistsError):  # not one of the refusals: the marker is create-once and the caller asked twice
+        cli.main(["checkpoint", "mark-source", str(source)])
+
+
+def test_a_fresh_process_reports_the_same_way(source, tmp_path):
+    env = dict(os.environ, GLM_B200_RUN_ROOT=str(tmp_path / "runs"), GLM_B200_SITE_CONFIG=str(tmp_path / "no-site.toml"))
+    done = subprocess.run([sys.executable, "-m", "glm_tpu_b200", "checkpoint", "verify", str(tmp_path / "nothing")], capture_output=True, text=True,
+                          env=env, timeout=300)
+    assert done.returncode == 2 and done.stdout == "" and "Traceback" not in done.stderr
+    assert refusal(done.stderr)["refused"] == "CheckpointValidationError"
+    done = subprocess.run([sys.executable, "-m", "glm_tpu_b200", "checkpoint", "inventory", str(source)], capture_output=True, text=True, env=env, timeout=300)
+    assert done.returncode == 0 and json.loads(done.stdout)["ok"] and done.stderr == ""
