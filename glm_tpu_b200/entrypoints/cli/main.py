@@ -69,11 +69,24 @@ def _topology(args) -> int:
     return main(args)
 
 
+def serve_arguments(args) -> list[str]:
+    """The server's own argument list: what the command line leaves open comes from the site file (``[serve] port``,
+    ``[paths] state_root``), then from the built-in default."""
+    from glm_tpu_b200.config.site import SiteConfig
+    from glm_tpu_b200.exceptions import ConfigValidationError
+
+    site = SiteConfig.load(args.site)
+    state = args.state if args.state is not None else site.paths.state_root
+    if state is None:
+        raise ConfigValidationError("where the chat state lives is not set: give --state or [paths] state_root in the site file")
+    port = args.port if args.port is not None else site.serve_port
+    return ["--run", str(args.run), "--state", str(state), "--port", str(port)] + (["--no-api"] if args.no_api else [])
+
+
 def _serve(args) -> int:
     from glm_tpu_b200.entrypoints.serve.server import main
 
-    argv = ["--run", str(args.run), "--state", str(args.state), "--port", str(args.port)] + (["--no-api"] if args.no_api else [])
-    return main(argv)
+    return main(serve_arguments(args))
 
 
 def build_parser() -> argparse.ArgumentParser:
@@ -149,9 +162,10 @@ def build_parser() -> argparse.ArgumentParser:
 
     srv = sub.add_parser("serve", help="chat UI + /v1 API attached to a resident session")
     srv.add_argument("--run", type=Path, required=True)
-    srv.add_argument("--state", type=Path, required=True)
-    srv.add_argument("--port", type=int, default=8011)
+    srv.add_argument("--state", type=Path, help="state directory (default: the site's [paths] state_root)")
+    srv.add_argument("--port", type=int, help="loopback port (default: the site's [serve] port, 8011)")
     srv.add_argument("--no-api", action="store_true")
+    srv.add_argument("--site", type=Path)
     srv.set_defaults(fn=_serve)
     return parser
 

@@ -240,3 +240,19 @@ def test_a_staged_site_passes_the_checks_of_a_site_file(tmp_path):
     assert SiteConfig.from_staged(staged, stage(site.resolved_json())).sha256 == site.sha256
     unpinned = SiteConfig.parse(write(tmp_path, '[paths]\nrun_root = "/srv/runs"\n', name="min.toml"))
     assert SiteConfig.from_staged(staged, stage(unpinned.resolved_json())).paths.model_path is None
+
+
+def test_serve_takes_what_the_command_line_leaves_open_from_the_site(tmp_path, monkeypatch):
+    from glm_tpu_b200.entrypoints.cli import main as cli
+
+    for name in ("GLM_B200_SITE_CONFIG", "GLM_B200_CONFIG_ROOT", "GLM_B200_RUN_ROOT", "GLM_B200_MODEL_PATH"):
+        monkeypatch.delenv(name, raising=False)
+    site = write(tmp_path, toml(changed("serve", "port", 8123)))
+    parse = cli.build_parser().parse_args
+    assert cli.serve_arguments(parse(["serve", "--run", "/r", "--site", str(site)])) == ["--run", "/r", "--state", "/srv/state", "--port", "8123"]
+    explicit = parse(["serve", "--run", "/r", "--state", "/elsewhere", "--port", "9000", "--no-api", "--site", str(site)])
+    assert cli.serve_arguments(explicit) == ["--run", "/r", "--state", "/elsewhere", "--port", "9000", "--no-api"]  # the command line wins
+    monkeypatch.setenv("GLM_B200_SITE_CONFIG", str(tmp_path / "absent.toml"))
+    assert cli.serve_arguments(parse(["serve", "--run", "/r", "--state", "/s"])) == ["--run", "/r", "--state", "/s", "--port", "8011"]
+    with pytest.raises(ConfigValidationError, match="--state or \\[paths\\] state_root"):
+        cli.serve_arguments(parse(["serve", "--run", "/r"]))
