@@ -67,6 +67,10 @@ def main(argv=None) -> int:
     os.umask(0o077)
     if args.state.resolve().is_relative_to(REPO):
         ap.error("Private chat state must be outside the source checkout.")
+    if args.api_key_file is None:  # command line > GLM_B200_API_KEY_FILE > <state>/api-key
+        from glm_tpu_b200 import envs
+
+        args.api_key_file = envs.GLM_B200_API_KEY_FILE
     server, queue, token = build(args.run.resolve(), args.state, port=args.port, api=not args.no_api, api_key_file=args.api_key_file)
     worker = threading.Thread(target=queue.work, daemon=True)
     worker.start()

@@ -74,7 +74,7 @@ TABLE: dict[str, Row] = {
     "GLM_B200_API_KEY_FILE": Row("path", None, "Bearer key file (0600) for /v1.", secret=True),
     "GLM_B200_COMM": Row("choice", "fused", "Cross-GPU path: in-kernel peer-memory collectives, or the NCCL baseline.", ("fused", "nccl")),
     "GLM_B200_CUDA_GRAPHS": Row("flag", True, "Replay the decode step from a CUDA graph (1) or launch eagerly (0)."),
-    "GLM_B200_WAIT_LIMIT": Row("count", 20_000_000, "Iteration limit of every device-side wait on a peer flag."),
+    "GLM_B200_WAIT_LIMIT": Row("count", 2_000_000, "Iteration limit of every device-side wait on a peer flag."),
     # kernel-path switches for A/B runs: read where the path is chosen (ops/native.py, config/parallel.py, runner/gpu_runner.py,
     # models/glm_moe_dsa/), listed here so that the environment report shows them and refuses a value that would silently select
     # the default

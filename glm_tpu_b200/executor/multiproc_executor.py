@@ -41,7 +41,7 @@ def parse_args(argv=None):
     ap.add_argument("--backend", default="gpu", choices=["gpu", "oracle"])
     ap.add_argument("--context", type=int, default=0)
     ap.add_argument("--lanes", type=int, default=1)
-    ap.add_argument("--comm", default="fused")
+    ap.add_argument("--comm", default=None, choices=["fused", "nccl"], help="default: GLM_B200_COMM, else fused")
     ap.add_argument("--kv-layout", default="auto")
     ap.add_argument("--keep-loaded", action="store_true")
     ap.add_argument("--wall-seconds", type=float, default=3600.0)
@@ -199,7 +199,9 @@ def main(argv=None) -> int:
         staged = staging.stage_request(run_dir, payload)
         jobs.write_identity(run_dir, job, {"args": vars(args)})
         worker_args = ["--run-dir", str(run_dir), "--model", args.model, "--backend", args.backend, "--lanes", str(args.lanes),
-                       "--comm", args.comm, "--kv-layout", args.kv_layout]
+                       "--kv-layout", args.kv_layout]
+        if args.comm:  # left open, the workers read GLM_B200_COMM from the environment they inherit
+            worker_args += ["--comm", args.comm]
         if args.context:
             worker_args += ["--context", str(args.context)]
         if staged is not None:

@@ -70,10 +70,18 @@ class _LaunchCounter:
 
 
 class GpuModelRunner:
-    def __init__(self, weights: DeviceWeights, *, context_capacity: int, lanes: int = 1, stripe: int = 64, comm: str = "fused",
-                 group=None, prefill_chunk: int = 512, use_graphs: bool = True, wait_limit: int = 2_000_000,
+    def __init__(self, weights: DeviceWeights, *, context_capacity: int, lanes: int = 1, stripe: int = 64, comm: str | None = None,
+                 group=None, prefill_chunk: int = 512, use_graphs: bool | None = None, wait_limit: int | None = None,
                  staging_bytes: int | None = None, kv_layout: str = "auto", replica_budget_bytes: int = 32 << 30,
                  decode_path: str = "auto", mega_compat_ksplit: bool | None = None, emulate_shard: bool = False):
+        from glm_tpu_b200 import envs
+
+        # what the caller leaves open comes from the environment registry (GLM_B200_COMM, GLM_B200_CUDA_GRAPHS, GLM_B200_WAIT_LIMIT)
+        comm = envs.GLM_B200_COMM if comm is None else comm
+        use_graphs = envs.GLM_B200_CUDA_GRAPHS if use_graphs is None else use_graphs
+        wait_limit = envs.GLM_B200_WAIT_LIMIT if wait_limit is None else wait_limit
+        if comm not in ("fused", "nccl"):
+            raise ValueError("comm is 'fused' or 'nccl'")
         self.weights = weights
         self.g, self.layout = weights.geometry, weights.layout
         self.device = weights.embed.device

@@ -43,7 +43,7 @@ def parse_args(argv=None):
     ap.add_argument("--backend", default="gpu", choices=["gpu", "oracle"], help="'oracle' runs the CPU contract reference")
     ap.add_argument("--context", type=int, default=0, help="context capacity (0: the request's)")
     ap.add_argument("--lanes", type=int, default=1)
-    ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--comm", default=None, choices=["fused", "nccl"], help="default: GLM_B200_COMM, else fused")
     ap.add_argument("--kv-layout", default="auto")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--site-json", help="the controller's resolved site (staged in the run directory)")

@@ -41,3 +41,10 @@ def native_lib():
     from glm_tpu_b200.ops import native
 
     return native
+
+
+def scaled(seconds: float) -> float:
+    """A subprocess timeout of a test, stretched by ``GLM_B200_TEST_TIMEOUT_SCALE`` (a slow or shared machine sets it above 1)."""
+    from glm_tpu_b200 import envs
+
+    return seconds * envs.GLM_B200_TEST_TIMEOUT_SCALE

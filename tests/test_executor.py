@@ -10,6 +10,8 @@ from pathlib import Path
 
 import pytest
 
+from tests.conftest import scaled
+
 from glm_tpu_b200.config.model import tiny_geometry
 from glm_tpu_b200.engine import request as rq
 from glm_tpu_b200.engine import resident_protocol as proto
@@ -32,7 +34,7 @@ def prepared(tmp_path, name="req.json", rid="q1", ids=(5, 6, 7, 8), n=3):
 def run_controller(args, timeout=240):
     env = dict(os.environ, PYTHONPATH=str(ROOT))
     return subprocess.run([sys.executable, "-m", "glm_tpu_b200.executor.multiproc_executor", *args], env=env, capture_output=True,
-                          text=True, timeout=timeout)
+                          text=True, timeout=scaled(timeout))
 
 
 def run_dir_of(stdout):
@@ -104,7 +106,7 @@ def test_worker_refuses_to_start_without_the_controller_flag(tmp_path):
     env = {k: v for k, v in os.environ.items() if k != proto.WORKER_ENV_FLAG}
     env["PYTHONPATH"] = str(ROOT)
     done = subprocess.run([sys.executable, "-m", "glm_tpu_b200.worker.gpu_worker", "--run-dir", str(tmp_path)], env=env,
-                          capture_output=True, text=True, timeout=60)
+                          capture_output=True, text=True, timeout=scaled(60))
     assert done.returncode != 0 and proto.WORKER_ENV_FLAG in done.stderr
 
 

@@ -11,6 +11,8 @@ import sys
 from pathlib import Path
 
 import pytest
+
+from tests.conftest import scaled
 import torch
 
 from glm_tpu_b200.config.model import small_geometry
@@ -33,7 +35,7 @@ def _launch(world, out):
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=str(ROOT))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
            "--master-port", str(_free_port()), str(ROOT / "tests" / "multi_gpu_worker.py"), "--out", str(out)]
-    done = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    done = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=scaled(600))
     assert done.returncode == 0, done.stdout[-3000:] + done.stderr[-3000:]
     return json.loads(Path(out).read_text())
 

@@ -4,6 +4,8 @@ import json
 import os
 
 import pytest
+
+from tests.conftest import scaled
 import torch
 from pathlib import Path
 
@@ -304,7 +306,7 @@ def test_pack_and_load_never_hold_more_than_a_few_pieces(tmp_path):
         stop.set(); watcher.join()
         print(json.dumps({{"base": base, "peak": peak[0], "read": read, "io": ckpt.io_stats()}}))
     """)
-    out = subprocess.run([sys.executable, "-c", script], capture_output=True, text=True, timeout=600, cwd=str(ROOT_DIR))
+    out = subprocess.run([sys.executable, "-c", script], capture_output=True, text=True, timeout=scaled(600), cwd=str(ROOT_DIR))
     assert out.returncode == 0, out.stderr[-2000:]
     report = json.loads(out.stdout.strip().splitlines()[-1])
     grown_mb = (report["peak"] - report["base"]) / 2**20

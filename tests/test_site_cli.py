@@ -9,6 +9,8 @@ from types import SimpleNamespace
 
 import pytest
 
+from tests.conftest import scaled
+
 from glm_tpu_b200.config.site import SiteConfig
 from glm_tpu_b200.entrypoints.cli import main as cli
 from glm_tpu_b200.exceptions import ConfigValidationError
@@ -170,7 +172,7 @@ def test_cli_argument_snapshot():
 
 def test_info_does_not_import_torch():
     code = "import sys; from glm_tpu_b200.entrypoints.cli.main import main; main(['info']); assert 'torch' not in sys.modules, 'torch imported'"
-    done = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, cwd=REPO, timeout=120)
+    done = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, cwd=REPO, timeout=scaled(120))
     assert done.returncode == 0, done.stderr
     assert json.loads(done.stdout)["decoding"].startswith("greedy")
 

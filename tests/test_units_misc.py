@@ -221,3 +221,37 @@ def test_launch_policy_on_real_repositories(tmp_path):
     _git(repo, "checkout", "-q", "--detach")
     with pytest.raises(ConfigValidationError, match="detached"):
         launch_policy.check(launch_policy.source_identity(repo), "strict")
+
+
+def test_every_registered_variable_is_read_somewhere():
+    """A variable in the registry that nothing reads would be documented, validated and without effect."""
+    import re
+    from pathlib import Path
+
+    from glm_tpu_b200 import envs
+
+    root = Path(__file__).resolve().parents[1]
+    product = "\n".join(p.read_text() for p in (root / "glm_tpu_b200").rglob("*.py") if p.name != "envs.py") + (root / "bench.py").read_text()
+    tests = "\n".join(p.read_text() for p in (root / "tests").rglob("*.py"))
+    product += "\n".join(re.findall(r'value_of\("(GLM_B200_[A-Z0-9_]+)"\)', (root / "glm_tpu_b200" / "envs.py").read_text()))  # defaults built on another variable
+    for name in envs.TABLE:
+        where = tests if name.startswith("GLM_B200_TEST_") else product
+        assert re.search(r"\b" + name + r"\b", where), f"{name} is registered but never read"
+    # and the other way round: a GLM_B200_* name the product reads is one the registry knows (a typo would silently do nothing)
+    for name in set(re.findall(r"\bGLM_B200_[A-Z0-9_]+\b", product)):
+        assert name in envs.TABLE or name == "GLM_B200_WORKER", f"{name} is read but not registered"
+
+
+def test_runner_defaults_follow_the_registry(monkeypatch):
+    from glm_tpu_b200 import envs
+
+    for name in ("GLM_B200_COMM", "GLM_B200_CUDA_GRAPHS", "GLM_B200_WAIT_LIMIT"):
+        monkeypatch.delenv(name, raising=False)
+    assert (envs.GLM_B200_COMM, envs.GLM_B200_CUDA_GRAPHS, envs.GLM_B200_WAIT_LIMIT) == ("fused", True, 2_000_000)
+    monkeypatch.setenv("GLM_B200_COMM", "nccl")
+    monkeypatch.setenv("GLM_B200_CUDA_GRAPHS", "0")
+    monkeypatch.setenv("GLM_B200_WAIT_LIMIT", "500000")
+    assert (envs.GLM_B200_COMM, envs.GLM_B200_CUDA_GRAPHS, envs.GLM_B200_WAIT_LIMIT) == ("nccl", False, 500000)
+    monkeypatch.setenv("GLM_B200_COMM", "mpi")
+    with pytest.raises(ValueError, match="GLM_B200_COMM must be one of fused, nccl"):
+        envs.GLM_B200_COMM
