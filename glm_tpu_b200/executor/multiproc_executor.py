@@ -167,18 +167,35 @@ def resident_controller(fl: fleet_mod.Fleet, run_dir: Path, world: int, profile_
                 print(proto.STDOUT_RESIDENT_RESULT + json.dumps({"sequence": sequence, **summary}), flush=True)
                 served.append(sequence)
             if (inbox / proto.STOP_FILE).exists():
-                fl.send_all(proto.STOP_COMMAND)
+                _tell(fl, proto.STOP_COMMAND)
                 return {"stopped": "stop_file", "served": served}
             nxt = inbox / proto.inbox_name(sequence + 1)
             if nxt.exists():
-                payload = json.loads(read_bounded(nxt, request_schema.PAYLOAD_CAP))
-                profile_check(payload)
+                # A request that cannot be read or does not pass the loaded profile's checks never reaches a GPU.  It ends the
+                # session in order (the workers are told to stop) instead of being skipped: sequence numbers are claimed once, and
+                # a producer that published something invalid cannot be trusted with the next number either.
+                try:
+                    payload = json.loads(read_bounded(nxt, request_schema.PAYLOAD_CAP))
+                    profile_check(payload)
+                except (OSError, ValueError) as exc:
+                    _tell(fl, proto.STOP_COMMAND)
+                    return {"stopped": "invalid_request", "sequence": sequence + 1, "error": f"{type(exc).__name__}: {exc}", "served": served}
                 sequence += 1
-                fl.send_all(proto.encode_command(sequence, payload))
+                if not _tell(fl, proto.encode_command(sequence, payload)):
+                    return {"stopped": "worker_exit", "exit_codes": fl.poll(), "served": served}
                 continue
         time.sleep(poll)
-    fl.send_all(proto.STOP_COMMAND)
+    _tell(fl, proto.STOP_COMMAND)
     return {"stopped": "deadline", "served": served}
+
+
+def _tell(fl: fleet_mod.Fleet, line: bytes) -> bool:
+    """Write one line to every worker; False when a worker's pipe is gone (it exited between the poll and the write)."""
+    try:
+        fl.send_all(line)
+    except OSError:
+        return False
+    return True
 
 
 def main(argv=None) -> int:
