@@ -106,7 +106,9 @@ class LoopbackSurface(BaseHTTPRequestHandler):
         if self.token is None:
             return False
         scheme, _, offered = self.headers.get("Authorization", "").partition(" ")
-        return scheme == "Bearer" and secrets.compare_digest(offered, self.token)
+        # compared as bytes: header text may carry any byte (http.server decodes it as latin-1), and the str form of the
+        # constant-time comparison refuses non-ASCII text with an exception instead of an answer
+        return scheme == "Bearer" and secrets.compare_digest(offered.encode("latin-1", "replace"), self.token.encode("utf-8"))
 
     def _json_body(self, cap: int, seconds: float):
         declared = int(self.headers.get("Content-Length", "0"))
