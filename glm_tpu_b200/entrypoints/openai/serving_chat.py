@@ -61,6 +61,17 @@ class ChatCall:
         return cls(model, ALIASES[model] or asked, budget, messages, tools)
 
 
+def _content_so_far(answer: str) -> str:
+    """What of a still-growing answer may already be sent as content: everything before an opening tool-call tag, and not the
+    tail that may be the beginning of one (``...<tool_c``), which is decided only when more text has arrived."""
+    head, opened, _ = answer.partition(OPEN)
+    if not opened:
+        for n in range(len(OPEN) - 1, 0, -1):
+            if head.endswith(OPEN[:n]):
+                return head[:-n]
+    return head
+
+
 def _why_it_ended(job: dict, calls: list) -> str:
     if calls:
         return "tool_calls"
@@ -141,7 +152,7 @@ class OpenAIServingChat:
             running = job["status"] not in DONE
             # while the job runs, text after an opening tool-call tag is withheld: it will become a tool call, not content;
             # the final snapshot's content is sent below, after the calls have been parsed out of it
-            grown = {"reasoning_content": job["thinking"], "content": job["answer"].split(OPEN, 1)[0] if running else None}
+            grown = {"reasoning_content": job["thinking"], "content": _content_so_far(job["answer"]) if running else None}
             for channel, text in grown.items():
                 if text is not None and len(text) > told[channel]:
                     yield self.chunk(ident, {channel: text[told[channel]:]}, None)
