@@ -89,7 +89,8 @@ class ConversationStore:
         """One action of ``POST /api/chat``; every action runs under the queue's lock and is saved before it is answered."""
         q = self.queue
         with q.mutex:
-            action = ACTIONS.get(request.get("action"))
+            name = request.get("action")
+            action = ACTIONS.get(name) if type(name) is str else None  # anything else (a list, a number) is an unknown action, not a crash
             if action is None:
                 self._find(request.get("chat"))  # an unknown conversation is reported before an unknown action
                 raise Refused("Unknown action.")
