@@ -254,6 +254,32 @@ def wire_mutants():
 
     yield "canonical JSON with spaces after commas", _patched(json_utils, "canonical_wire_bytes", spaced)
     yield "tokens file renamed", _patched(proto, "TOKENS_FILE", "tokens.ndjson")
+    yield "inbox names with six digits", _patched(proto, "SEQUENCE_DIGITS", 6)
+    yield "another marker in front of the run directory on stdout", _patched(proto, "STDOUT_RUN", "RUNDIR ")
+
+    import struct
+
+    from glm_tpu_b200.engine import outputs
+    from glm_tpu_b200.engine import request as rq
+    from glm_tpu_b200.entrypoints.openai import tool_parser
+    from glm_tpu_b200.tokenizer import chat_template
+
+    yield "prompt digest over big-endian ids", _patched(rq, "prompt_digest", lambda ids: __import__("hashlib").sha256(struct.pack(f">{len(ids)}i", *ids)).hexdigest())
+    yield "request schema renamed", _patched(rq, "SCHEMA", "glm_b200_request_v2")
+    yield "concurrent batches under the sequential schema name", _patched(rq, "CONCURRENT_SCHEMA", rq.BATCH_SCHEMA)
+    plain_wire = outputs.TokenEvent.wire
+    yield "token events without their index", _patched(outputs.TokenEvent, "wire", lambda self: {k: v for k, v in plain_wire(self).items() if k != "index"})
+    yield "an answer is not cut at the next turn marker", _patched(outputs, "TURN_MARKERS", ())
+    yield "tool-call arguments always as strings", _patched(tool_parser, "_typed", lambda raw: raw.strip())
+    yield "tool-call blocks closed by another tag", _patched(tool_parser, "CLOSE", "</call>")
+    yield "chat format: tool instructions without their last sentence", _patched(chat_template, "TOOLS_FOOTER", chat_template.TOOLS_FOOTER.split("\n\n")[0])
+    plain_assistant = chat_template._assistant
+    yield "chat format: earlier answers keep their surrounding whitespace", _patched(
+        chat_template, "_assistant", lambda m, show_reasoning: plain_assistant(dict(m, content=" " + (m.get("content") or "") + " "), show_reasoning).replace(
+            "</think>" + (m.get("content") or "").strip(), "</think> " + (m.get("content") or "") + " "))
+    plain_visible = chat_template.visible_text
+    yield "chat format: text parts joined by a newline", _patched(chat_template, "visible_text", lambda c: plain_visible(c) if isinstance(c, (str, type(None))) else "\n".join(
+        plain_visible([p]) for p in c))
 
 
 def run() -> dict:
@@ -268,9 +294,17 @@ def run() -> dict:
         with patch:
             results[name] = digests.oracle_digests() != base_oracle
     base_wire = wire.collect()
+    request_module = importlib.import_module("glm_tpu_b200.engine.request")
     for name, patch in wire_mutants():
+        rebinds = "JSON" in name  # engine.request took the function by name when it was imported: it has to be imported again to see the mutant
         with patch:
-            importlib.reload(importlib.import_module("glm_tpu_b200.engine.request")) if "JSON" in name else None
-            results[name] = wire.collect() != base_wire
-    importlib.reload(importlib.import_module("glm_tpu_b200.engine.request"))
+            if rebinds:
+                importlib.reload(request_module)
+            try:
+                results[name] = wire.collect() != base_wire
+            except Exception:  # noqa: BLE001 - a mutant that makes the collection itself fail is caught as well
+                results[name] = True
+        if rebinds:
+            importlib.reload(request_module)  # and once more without the mutant, before the next one is judged
+    assert wire.collect() == base_wire, "a mutant outlived its patch"
     return results

@@ -47,6 +47,13 @@ def collect() -> dict:
     tools = [{"type": "function", "function": {"name": "calc", "description": "adds", "parameters": {"type": "object", "properties": {"x": {"type": "number"}}}}}]
     out["chat_template_plain"] = _sha(chat_template.render(messages, reasoning_effort="max").encode())
     out["chat_template_tools"] = _sha(chat_template.render(messages, tools=tools, reasoning_effort="high").encode())
+    round_trip = [{"role": "user", "content": [{"type": "text", "text": "look: "}, {"type": "image_url", "image_url": {"url": "x"}}, {"type": "text", "text": "Köln?"}]},
+                  {"role": "assistant", "content": "", "reasoning_content": "need it",
+                   "tool_calls": [{"type": "function", "function": {"name": "calc", "arguments": {"x": 2.5, "label": "größe", "deep": {"a": [1, None]}}}}]},
+                  {"role": "tool", "content": [{"type": "text", "text": "7"}, {"type": "text", "text": " degrees"}]}, {"role": "tool", "content": "second"},
+                  {"role": "assistant", "content": " It is 7. \n"}, {"role": "user", "content": "thanks"}]
+    out["chat_template_parts_and_tool_round"] = _sha(chat_template.render(round_trip, tools=tools, reasoning_effort="low").encode())
+    out["chat_template_cleared_reasoning"] = _sha(chat_template.render(round_trip, clear_thinking=True, add_generation_prompt=False).encode())
     tok = ByteTokenizer(g.vocab_size + 1024, g.eos_ids)
     out["chat_template_token_ids"] = _sha(json.dumps(tok.apply_chat_template(messages[:2], reasoning_effort="max")).encode())
     text, calls = tool_parser.parse("I will call it.<tool_call>calc<arg_key>x</arg_key><arg_value>3</arg_value></tool_call>")
