@@ -117,8 +117,12 @@ def summarize(run_dir: Path, world: int, sequence: int = 0) -> dict:
         path = out_dir / proto.runner_file(rank)
         if not path.exists():
             path = run_dir / proto.runner_file(rank)
-        if path.exists():
-            records.append(json.loads(path.read_text()))
+        try:
+            record = json.loads(path.read_text()) if path.exists() else None
+        except (OSError, ValueError):
+            record = None  # a record that cannot be read counts like one that was never written
+        if isinstance(record, dict):
+            records.append(record)
         else:
             missing.append(rank)
     digests = [[(r["request_id"], r["token_sha256"]) for r in rec.get("requests", [])] for rec in records]

@@ -264,3 +264,11 @@ def test_ranks_that_disagree_are_reported_as_such(run_dir):
     (run_dir / proto.runner_file(1)).write_text(json.dumps(dict(record, failure_type="DeviceStatusError")))
     failed = controller.summarize(run_dir, 2)
     assert failed["agree"] is False and failed["failures"] == ["DeviceStatusError"]
+
+
+def test_a_record_that_cannot_be_read_counts_as_missing(run_dir):
+    finish(run_dir, 2, 0, "q")
+    (run_dir / proto.runner_file(1)).write_text('{"requests": [')  # a worker died while writing
+    assert controller.summarize(run_dir, 2) == {"ranks": 1, "missing_ranks": [1], "agree": False, "failures": [], "requests": []}
+    (run_dir / proto.runner_file(1)).write_text("[]")
+    assert controller.summarize(run_dir, 2)["missing_ranks"] == [1]
