@@ -78,6 +78,33 @@ class ByteTokenizer:
                                                 add_generation_prompt=add_generation_prompt))
 
 
+def render_jinja(template: str, **variables) -> str | None:
+    """``template`` (a checkpoint's ``chat_template.jinja``) rendered the way the model's own tooling renders it: sandboxed,
+    ``trim_blocks`` / ``lstrip_blocks`` on, loop controls, and the three helpers such templates rely on.  ``tojson`` is plain
+    ``json.dumps`` -- keys in their given order, text as it is (``ensure_ascii=False``), no HTML escaping -- and NOT jinja2's own filter,
+    which sorts keys and writes ``<`` as ``\\u003c``: with that one a tool signature would reach the model in other bytes than
+    the ones it was trained on.  ``None`` when jinja2 is not installed."""
+    try:
+        from jinja2.exceptions import TemplateError
+        from jinja2.sandbox import ImmutableSandboxedEnvironment
+    except ImportError:
+        return None
+    import datetime
+    import json
+
+    def tojson(value, ensure_ascii=False, indent=None, separators=None, sort_keys=False):
+        return json.dumps(value, ensure_ascii=ensure_ascii, indent=indent, separators=separators, sort_keys=sort_keys)
+
+    def raise_exception(message):
+        raise TemplateError(message)
+
+    env = ImmutableSandboxedEnvironment(trim_blocks=True, lstrip_blocks=True, extensions=["jinja2.ext.loopcontrols"])
+    env.filters["tojson"] = tojson
+    env.globals["raise_exception"] = raise_exception
+    env.globals["strftime_now"] = lambda fmt: datetime.datetime.now().strftime(fmt)
+    return env.from_string(template).render(**variables)
+
+
 class HfTokenizer:
     def __init__(self, path: Path):
         from tokenizers import Tokenizer
@@ -99,14 +126,8 @@ class HfTokenizer:
     def apply_chat_template(self, messages, *, tools=None, reasoning_effort=None, add_generation_prompt=True) -> list[int]:
         text = None
         if self._jinja is not None:
-            try:
-                from jinja2.sandbox import ImmutableSandboxedEnvironment
-
-                env = ImmutableSandboxedEnvironment(trim_blocks=True, lstrip_blocks=True, extensions=["jinja2.ext.loopcontrols"])
-                text = env.from_string(self._jinja).render(messages=messages, tools=tools, reasoning_effort=reasoning_effort,
-                                                           add_generation_prompt=add_generation_prompt)
-            except ImportError:
-                text = None
+            text = render_jinja(self._jinja, messages=messages, tools=tools, reasoning_effort=reasoning_effort,
+                                add_generation_prompt=add_generation_prompt)
         if text is None:
             text = chat_template.render(messages, tools=tools, reasoning_effort=reasoning_effort,
                                         add_generation_prompt=add_generation_prompt)
