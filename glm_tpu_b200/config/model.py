@@ -24,6 +24,17 @@ MODEL_REVISION = "aca966e4e02791568aa6a4ced368624b3d897f42"
 EOS_IDS = (154820, 154827, 154829)
 
 
+ASSUMED_SWITCHES = {
+    "hidden_act": "silu",             # SwiGLU with SiLU in dense, shared and routed MLPs
+    "norm_topk_prob": True,           # the top-k route weights are renormalised to sum to one before the scaling factor
+    "attention_bias": False,          # no bias on the attention projections
+    "tie_word_embeddings": False,     # lm_head has its own table
+    "rope_interleave": True,          # rotary pairs are (2i, 2i + 1) in the attention heads ...
+    "indexer_rope_interleave": True,  # ... and in the indexer's query and key
+    "moe_layer_freq": 1,              # every layer after the dense ones is a MoE layer (mlp_layer_types says which)
+}
+
+
 @dataclass(frozen=True)
 class ModelGeometry:
     vocab_size: int
@@ -104,6 +115,11 @@ class ModelGeometry:
             raise ValueError("only the sigmoid noaux_tc router is supported")
         if config.get("n_group", 1) != 1 or config.get("topk_group", 1) != 1:
             raise ValueError("grouped routing is not part of this model")
+        # Switches of the architecture that the kernels assume one way.  They are not part of the geometry (and not of its hash):
+        # a configuration that sets one of them the other way describes another computation and is refused, not approximated.
+        for key, assumed in ASSUMED_SWITCHES.items():
+            if config.get(key, assumed) != assumed:
+                raise ValueError(f"{key} = {config[key]!r} is not supported (the engine computes {key} = {assumed!r})")
         return cls(
             vocab_size=int(config["vocab_size"]),
             hidden_size=int(config["hidden_size"]),
