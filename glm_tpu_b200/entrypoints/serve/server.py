@@ -43,6 +43,30 @@ def resident_for_run(run: Path) -> Resident:
     return Resident(run, tokenizer, profile_for(geometry, capacity), capacity=capacity, world=int(args.get("gpus", 1)))
 
 
+class ProducerBusy(ValueError):
+    pass
+
+
+def hold_producer_lock(run: Path):
+    """The one lock of a resident session's inbox (``inbox/producer.lock``, ``flock``, non-blocking).  Sequence numbers are claimed
+    by reading the ready file and the inbox; two servers doing that at once could publish two requests under one number, so the
+    second server is refused.  The returned descriptor holds the lock until it is closed or the process ends."""
+    import fcntl
+
+    inbox = run / proto.INBOX_DIR
+    if not inbox.is_dir():
+        raise ProducerBusy(f"{run} is not the run directory of a resident session (no inbox)")
+    descriptor = os.open(inbox / proto.PRODUCER_LOCK, os.O_RDWR | os.O_CREAT | os.O_NOFOLLOW, 0o600)
+    try:
+        fcntl.flock(descriptor, fcntl.LOCK_EX | fcntl.LOCK_NB)
+    except BlockingIOError:
+        os.close(descriptor)
+        raise ProducerBusy("another server already feeds this resident session; one producer per session") from None
+    os.ftruncate(descriptor, 0)
+    os.write(descriptor, f"{os.getpid()}\n".encode())
+    return descriptor
+
+
 def build(run: Path, state: Path, *, port: int, api: bool = True, api_key_file: Path | None = None, wait_seconds: float = 1800):
     backend = resident_for_run(run)
     queue = JobQueue(state, backend)
@@ -71,6 +95,10 @@ def main(argv=None) -> int:
         from glm_tpu_b200 import envs
 
         args.api_key_file = envs.GLM_B200_API_KEY_FILE
+    try:
+        producer = hold_producer_lock(args.run.resolve())
+    except ProducerBusy as refusal:
+        ap.error(str(refusal))
     server, queue, token = build(args.run.resolve(), args.state, port=args.port, api=not args.no_api, api_key_file=args.api_key_file)
     worker = threading.Thread(target=queue.work, daemon=True)
     worker.start()
@@ -85,6 +113,7 @@ def main(argv=None) -> int:
         queue.stopping.set()
         worker.join(timeout=5)
         server.server_close()
+        os.close(producer)
     return 0
 
 

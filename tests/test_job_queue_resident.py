@@ -203,3 +203,29 @@ def test_the_state_directory_is_private_and_the_job_view_is_detached(tmp_path):
     assert "payload" not in view and view["prompt_tokens"] > 0
     view["status"] = "complete"
     assert queue.job("a")["status"] == "queued" and queue.job("missing") is None
+
+
+def test_one_server_per_session(tmp_path):
+    """The inbox has one producer: a second server on the same run directory is refused, in this process or another."""
+    import subprocess
+    import sys
+
+    from glm_tpu_b200.entrypoints.serve.server import ProducerBusy, hold_producer_lock
+
+    session = Session(tmp_path)
+    first = hold_producer_lock(session.run)
+    lock = session.run / proto.INBOX_DIR / proto.PRODUCER_LOCK
+    assert lock.read_text().strip() == str(os.getpid()) and stat.S_IMODE(lock.stat().st_mode) == 0o600
+    with pytest.raises(ProducerBusy, match="one producer per session"):
+        hold_producer_lock(session.run)
+    probe = ("import sys; from pathlib import Path; from glm_tpu_b200.entrypoints.serve.server import hold_producer_lock, ProducerBusy\n"
+             "try:\n    hold_producer_lock(Path(sys.argv[1])); print('held')\nexcept ProducerBusy as e:\n    print('busy')\n")
+    done = subprocess.run([sys.executable, "-c", probe, str(session.run)], capture_output=True, text=True, timeout=120)
+    assert done.stdout.strip() == "busy", done.stderr
+    os.close(first)
+    done = subprocess.run([sys.executable, "-c", probe, str(session.run)], capture_output=True, text=True, timeout=120)
+    assert done.stdout.strip() == "held", done.stderr  # released with the descriptor (or the process): the next server gets it
+    with pytest.raises(ProducerBusy, match="no inbox"):
+        hold_producer_lock(tmp_path / "not-a-run")
+    # the lock file is not a request: the client still claims the next number, and the controller's loop never reads it as one
+    assert session.client().next_sequence() == 1 and proto.PRODUCER_LOCK not in (proto.inbox_name(n) for n in range(3))
