@@ -144,22 +144,28 @@ def summarize(run_dir: Path, world: int, sequence: int = 0) -> dict:
     }
 
 
-def resident_controller(fl: fleet_mod.Fleet, run_dir: Path, world: int, profile_check, deadline: float, poll: float, *,
-                        initial: bool = False, print_answers: bool = False) -> dict:
+def resident_controller(fl: fleet_mod.Fleet, run_dir: Path, world: int, profile_check, deadline: float | None, poll: float, *,
+                        initial: bool = False, print_answers: bool = False, wall_seconds: float | None = None) -> dict:
     """Feed ``inbox/NNNN.json`` requests to the loaded workers until ``inbox/stop.json`` or a failure.
 
     ``initial``: the session was started with a request (sequence 0); its result is reported as soon as the workers are ready
-    for the next one, not only when the session ends."""
+    for the next one, not only when the session ends.
+
+    ``deadline`` bounds the start-up together with the first request.  With ``wall_seconds`` a loaded, idle session has no
+    deadline at all (it waits for its inbox as long as it lives) and every later request gets ``wall_seconds`` of its own from
+    the moment it is handed to the workers; without it ``deadline`` bounds the whole loop."""
     inbox = run_dir / proto.INBOX_DIR
     served, sequence = [], 0
     reported_initial = not initial
-    while time.monotonic() < deadline:
+    while deadline is None or time.monotonic() < deadline:
         codes = fl.poll()
         if any(c is not None for c in codes):
             return {"stopped": "worker_exit", "exit_codes": codes, "served": served}
         ready = run_dir / proto.READY_FILE
         ready_seq = json.loads(ready.read_text()).get("sequence", -1) if ready.exists() else -1
         if ready_seq == sequence:
+            if wall_seconds is not None:
+                deadline = None  # idle: nothing is running that could overrun
             if not reported_initial:
                 reported_initial = True
                 if print_answers and (run_dir / proto.ANSWER_FILE).exists():
@@ -185,6 +191,8 @@ def resident_controller(fl: fleet_mod.Fleet, run_dir: Path, world: int, profile_
                     _tell(fl, proto.STOP_COMMAND)
                     return {"stopped": "invalid_request", "sequence": sequence + 1, "error": f"{type(exc).__name__}: {exc}", "served": served}
                 sequence += 1
+                if wall_seconds is not None:
+                    deadline = time.monotonic() + wall_seconds
                 if not _tell(fl, proto.encode_command(sequence, payload)):
                     return {"stopped": "worker_exit", "exit_codes": fl.poll(), "served": served}
                 continue
@@ -247,7 +255,8 @@ def main(argv=None) -> int:
                 pass  # the workers validate against the loaded profile; the controller only bounds and parses
 
             terminal["resident"] = resident_controller(fl, run_dir, args.gpus, check, deadline, args.poll_seconds,
-                                                       initial=payload is not None, print_answers=args.print_answers)
+                                                       initial=payload is not None, print_answers=args.print_answers,
+                                                       wall_seconds=args.wall_seconds)
             codes = fl.wait(time.monotonic() + 30.0)
         else:
             codes = fl.wait(deadline)

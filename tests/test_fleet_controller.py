@@ -272,3 +272,37 @@ def test_a_record_that_cannot_be_read_counts_as_missing(run_dir):
     assert controller.summarize(run_dir, 2) == {"ranks": 1, "missing_ranks": [1], "agree": False, "failures": [], "requests": []}
     (run_dir / proto.runner_file(1)).write_text("[]")
     assert controller.summarize(run_dir, 2)["missing_ranks"] == [1]
+
+
+def test_an_idle_session_has_no_deadline_and_every_request_its_own(run_dir):
+    """``--wall-seconds`` bounds the start-up with the first request, then each later request; waiting for the inbox costs nothing."""
+    import threading
+
+    (run_dir / proto.READY_FILE).write_text(json.dumps({"sequence": 0}))
+    fl = ScriptedFleet(run_dir)
+    result = {}
+    worker = threading.Thread(target=lambda: result.update(controller.resident_controller(
+        fl, run_dir, 2, lambda payload: None, time.monotonic() + 0.2, 0.01, wall_seconds=0.2)))
+    worker.start()
+    time.sleep(0.6)  # three times the budget, idle: still waiting
+    assert worker.is_alive() and fl.sent == []
+    publish(run_dir, 1, {"request_id": "one"})
+    time.sleep(0.5)
+    assert worker.is_alive() and [json.loads(x).get("sequence") for x in fl.sent] == [1]  # answered within its own budget; idle again
+    (run_dir / proto.INBOX_DIR / proto.STOP_FILE).write_bytes(proto.STOP_COMMAND)
+    worker.join(10)
+    assert result == {"stopped": "stop_file", "served": [1]}
+
+    class Stuck(ScriptedFleet):  # takes the request and never finishes it
+        def send_all(self, line):
+            self.sent.append(line)
+
+    (run_dir / proto.INBOX_DIR / proto.STOP_FILE).unlink()
+    publish(run_dir, 2, {"request_id": "two"})
+    stuck = Stuck(run_dir)
+    (run_dir / proto.READY_FILE).write_text(json.dumps({"sequence": 0}))
+    started = time.monotonic()
+    outcome = controller.resident_controller(stuck, run_dir, 2, lambda payload: None, time.monotonic() + 5.0, 0.01, wall_seconds=0.3)
+    # sequence 1 is handed over at once, never answered: its own budget runs out, not the start-up one
+    assert outcome == {"stopped": "deadline", "served": []} and 0.25 < time.monotonic() - started < 3.0
+    assert stuck.sent[-1] == proto.STOP_COMMAND
