@@ -43,7 +43,8 @@ def main(args) -> int:
 
         site = SiteConfig.load(getattr(args, "site", None))
         report = pack_checkpoint(args.source, args.target, args.gpus, run_root=site.paths.run_root, layers=args.layers,
-                                 expert_split=getattr(args, "expert_split", "auto"), pins=site.checkpoint_pins)
+                                 expert_split=getattr(args, "expert_split", "auto"), pins=site.checkpoint_pins,
+                                 preflight_only=getattr(args, "preflight_only", False))
     else:
         from glm_tpu_b200.model_loader.sharded_state.verify import verify_runtime_checkpoint
 

@@ -146,6 +146,7 @@ def build_parser() -> argparse.ArgumentParser:
     pack.add_argument("--expert-split", default="auto", choices=["auto", "whole", "sliced"],
                       help="routed experts per GPU: whole experts, or a column slice of every expert (auto: sliced where the FP8 blocks allow)")
     pack.add_argument("--site", type=Path, help="site file (default: the configured one); its [checkpoint] source_marker_sha256 pins the source")
+    pack.add_argument("--preflight-only", action="store_true", help="run every check a pack makes before it writes (marker, pin, tensor set, free space) and write nothing")
     ver = cks.add_parser("verify", help="re-hash a packed checkpoint against its manifest and seal")
     ver.add_argument("target", type=Path)
     ver.add_argument("--site", type=Path, help="site file (default: the configured one); its [checkpoint] manifest_sha256 pins the checkpoint")

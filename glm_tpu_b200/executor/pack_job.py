@@ -18,13 +18,36 @@ from pathlib import Path
 
 from glm_tpu_b200.exceptions import CheckpointValidationError
 from glm_tpu_b200.executor.jobs import workload_lease
-from glm_tpu_b200.model_loader import pack_worker, source_inventory, source_marker
+from glm_tpu_b200.model_loader import pack_worker, placement, source_inventory, source_marker
 from glm_tpu_b200.model_loader.sharded_state import manifest as manifest_mod
 from glm_tpu_b200.model_loader.sharded_state import seal, verify
 
 
+def planned_bytes(geometry, world: int, expert_split: str) -> dict:
+    """Size of every file of the packed checkpoint, from the shapes alone (header + payload)."""
+    from glm_tpu_b200.model_loader.sharded_state import format as fmt
+    from glm_tpu_b200.model_loader.sharded_state import writer
+
+    sizes = {}
+    for name, rank in [(fmt.SHARED_FILE, None)] + [(fmt.expert_file(r, world), r) for r in range(world)]:
+        meta = writer._metadata(geometry, world, "shared" if rank is None else "experts", rank, expert_split)  # the header the packer will write
+        head, _, payload = fmt.layout(placement.packed_tensor_shapes(geometry, world, rank, expert_split), meta)
+        sizes[name] = len(head) + payload
+    return sizes
+
+
+def _free_bytes(target: Path) -> int:
+    import shutil
+
+    where = Path(target)
+    while not where.exists():
+        where = where.parent
+    return shutil.disk_usage(where).free
+
+
 def pack_checkpoint(source: Path, target: Path, world: int, *, run_root: Path | None = None, layers: int = 0, jobs: int = 0,
-                    require_marker: bool = True, timeout: float = 24 * 3600.0, expert_split: str = "auto", pins: dict | None = None) -> dict:
+                    require_marker: bool = True, timeout: float = 24 * 3600.0, expert_split: str = "auto", pins: dict | None = None,
+                    preflight_only: bool = False, free_bytes=None) -> dict:
     source, target = Path(source), Path(target)
     if (target / "SUCCESS").exists():
         raise CheckpointValidationError(f"{target} is already a sealed checkpoint")
@@ -38,6 +61,19 @@ def pack_checkpoint(source: Path, target: Path, world: int, *, run_root: Path | 
         from glm_tpu_b200.config.parallel import default_expert_split
 
         expert_split = default_expert_split(geometry, world)
+    plan = planned_bytes(geometry, world, expert_split)
+    needed = sum(plan.values())
+    free = (free_bytes or _free_bytes)(target)
+    if free < needed:
+        raise CheckpointValidationError(f"the packed checkpoint needs {needed:,} bytes, {free:,} are free where {target} would be written")
+    missing = [n for n in placement.expected_sources(geometry) if n not in inv.tensors]
+    if missing:
+        raise CheckpointValidationError(f"the source lacks {len(missing)} tensors, e.g. {missing[:3]}")
+    if preflight_only:  # every check a pack makes before it writes, and nothing written
+        return {"ok": True, "preflight_only": True, "target": str(target), "world": world, "expert_split": expert_split, "files": sorted(plan),
+                "planned_bytes": plan, "total_bytes": needed, "free_bytes": free, "geometry_sha256": geometry.geometry_hash,
+                "source_inventory_sha256": inv.sha256, "source_marker": bool(marker),
+                "source_marker_sha256": source_marker.marker_sha256(source) if marker else ""}
     target.mkdir(parents=True, exist_ok=True, mode=0o700)
     files = ["shared"] + [str(r) for r in range(world)]
     jobs = max(1, min(jobs or len(files), len(files)))

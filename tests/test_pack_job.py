@@ -176,3 +176,48 @@ def test_the_report_is_json_and_names_what_to_pin(source, tmp_path):
     assert report["source_inventory_sha256"] == json.loads((tmp_path / "t" / fmt.MANIFEST_FILE).read_text())["source_inventory_sha256"]
     assert verify.verify_runtime_checkpoint(tmp_path / "t", pins={"manifest_sha256": report["manifest_sha256"]})["ok"]
     assert pack_job.__doc__ and "seal" in pack_job.__doc__
+
+
+def test_preflight_checks_everything_and_writes_nothing(source, tmp_path):
+    plan = pack_checkpoint(source, tmp_path / "t", 2, jobs=1, preflight_only=True)
+    assert plan["ok"] and plan["preflight_only"] and not (tmp_path / "t").exists()
+    real = pack_checkpoint(source, tmp_path / "t", 2, jobs=1)
+    on_disk = {p.name: p.stat().st_size for p in (tmp_path / "t").glob("*.safetensors")}
+    assert plan["planned_bytes"] == on_disk and plan["total_bytes"] == real["total_bytes"] == sum(on_disk.values())  # sizes known from the shapes alone
+    assert plan["files"] == real["files"] and plan["expert_split"] == real["expert_split"] and plan["geometry_sha256"] == real["geometry_sha256"]
+    assert plan["source_marker_sha256"] == real["source_marker_sha256"] and plan["free_bytes"] > plan["total_bytes"]
+    with pytest.raises(CheckpointValidationError, match="already a sealed checkpoint"):
+        pack_checkpoint(source, tmp_path / "t", 2, jobs=1, preflight_only=True)
+    with pytest.raises(CheckpointValidationError, match="not the pinned one"):
+        pack_checkpoint(source, tmp_path / "u", 2, jobs=1, preflight_only=True, pins={"source_marker_sha256": "0" * 64})
+
+
+def test_a_target_without_room_is_refused_before_anything_is_written(source, tmp_path):
+    with pytest.raises(CheckpointValidationError, match=r"needs [\d,]+ bytes, 1,000 are free"):
+        pack_checkpoint(source, tmp_path / "deep" / "t", 2, jobs=1, free_bytes=lambda target: 1000)
+    assert not (tmp_path / "deep").exists()
+
+
+def test_a_source_that_lacks_tensors_is_refused_before_anything_is_written(source, tmp_path):
+    import shutil
+
+    from glm_tpu_b200.model_loader.sharded_state import format as fmt_mod
+    from glm_tpu_b200.model_loader import source_inventory
+
+    copy = tmp_path / "src"
+    shutil.copytree(source, copy)
+    shard = sorted(copy.glob("*.safetensors"))[0]
+    header, start = fmt_mod.read_header(shard)
+    victim = sorted(n for n in header if n != "__metadata__")[0]
+    tensors = {n: fmt_mod.read_tensor(shard, header, start, n) for n in header if n not in ("__metadata__", victim)}
+    shard.unlink()
+    fmt_mod.write_file(shard, tensors, {})
+    with pytest.raises(CheckpointValidationError, match="index names tensors that no shard holds"):
+        pack_checkpoint(copy, tmp_path / "t", 2, jobs=1, require_marker=False, preflight_only=True)  # the index still promises it
+    index = copy / source_inventory.INDEX_FILE
+    listing = json.loads(index.read_text())
+    del listing["weight_map"][victim]
+    index.write_text(json.dumps(listing))
+    with pytest.raises(CheckpointValidationError, match="lacks 1 tensors"):
+        pack_checkpoint(copy, tmp_path / "t", 2, jobs=1, require_marker=False, preflight_only=True)  # a consistent source of another model
+    assert victim not in source_inventory.read_source_inventory(copy).tensors and not (tmp_path / "t").exists()
