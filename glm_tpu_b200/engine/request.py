@@ -111,6 +111,44 @@ def from_token_ids(ids, *, request_id: str, max_new_tokens: int, context_capacit
     return dict(body, request_sha256=hashlib.sha256(canonical_wire_bytes(body)).hexdigest())
 
 
+CHAT_ROLES = ("system", "user", "assistant")
+
+
+def check_chat(messages: Any) -> list[dict]:
+    """A complete text-only conversation that the model is to continue: a bounded, non-empty list of ``{"role", "content"}`` objects
+    with string content, an optional system message in first place only, and a user message last."""
+    problem = None
+    if type(messages) is not list or not messages:
+        problem = "a non-empty list of messages"
+    elif len(canonical_wire_bytes(messages)) > MESSAGES_CAP:
+        problem = f"at most {MESSAGES_CAP} bytes of messages"
+    elif any(type(m) is not dict or set(m) != {"role", "content"} or m["role"] not in CHAT_ROLES or type(m["content"]) is not str for m in messages):
+        problem = "messages with exactly a role (system, user or assistant) and text content"
+    elif any(m["role"] == "system" for m in messages[1:]):
+        problem = "a system message in first place only"
+    elif messages[-1]["role"] != "user":
+        problem = "a user message last"
+    if problem:
+        raise RequestValidationError("a chat to prepare needs " + problem)
+    return messages
+
+
+def from_messages(messages, *, tokenizer, request_id: str, max_new_tokens: int | None = None, context_capacity: int = CAPACITY,
+                  profile: RequestProfile = GLM53_PROFILE, reasoning_effort: str = "max") -> dict:
+    """The prepared request for a whole conversation, rendered with ``tokenizer`` (the session's: its chat format is the pinned
+    one) at maximum reasoning effort unless told otherwise.  Nothing is truncated: a conversation that does not leave room for
+    one new token in ``context_capacity`` is refused.  Without ``max_new_tokens`` the answer may use whatever the capacity
+    leaves, up to the profile's ceiling.
+
+    Parity: reference ``glm_tpu/engine/request.py:180-212``."""
+    ids = tokenizer.apply_chat_template(check_chat(messages), reasoning_effort=reasoning_effort)
+    if type(context_capacity) is int and context_capacity in profile.capacities and len(ids) >= context_capacity:
+        raise RequestValidationError(f"the conversation has {len(ids)} tokens and fills the {context_capacity}-slot context; nothing is truncated")
+    if max_new_tokens is None:
+        max_new_tokens = default_max_new_tokens(len(ids), context_capacity, profile) if type(context_capacity) is int else 0
+    return from_token_ids(ids, request_id=request_id, max_new_tokens=max_new_tokens, context_capacity=context_capacity, profile=profile)
+
+
 def default_max_new_tokens(prompt_tokens: int, context_capacity: int, profile: RequestProfile = GLM53_PROFILE) -> int:
     """The input is never truncated; the default budget is whatever the capacity leaves, capped at ``max_new``."""
     return min(profile.max_new, context_capacity - prompt_tokens)

@@ -24,13 +24,15 @@ def main(args) -> int:
     profile = profile_for(geometry, capacity)
     if args.token_ids is not None:
         ids = json.loads(read_bounded(args.token_ids, rq.PAYLOAD_CAP))
+        budget = args.max_new_tokens or rq.default_max_new_tokens(len(ids), capacity, profile)
+        prepared = rq.from_token_ids(ids, request_id=args.request_id, max_new_tokens=budget, context_capacity=capacity, profile=profile)
     else:
         tokenizer = load_tokenizer(path if kind == "checkpoint" else site.paths.model_path, vocab_size=geometry.vocab_size,
                                    eos_ids=geometry.eos_ids)
         messages = json.loads(read_bounded(args.messages, rq.MESSAGES_CAP))
-        ids = tokenizer.apply_chat_template(messages, reasoning_effort=args.reasoning_effort)
-    budget = args.max_new_tokens or rq.default_max_new_tokens(len(ids), capacity, profile)
-    prepared = rq.from_token_ids(ids, request_id=args.request_id, max_new_tokens=budget, context_capacity=capacity, profile=profile)
+        prepared = rq.from_messages(messages, tokenizer=tokenizer, request_id=args.request_id, max_new_tokens=args.max_new_tokens,
+                                    context_capacity=capacity, profile=profile, reasoning_effort=args.reasoning_effort)
+    ids, budget = prepared["prompt_ids"], prepared["max_new_tokens"]
     create_private_exclusive(Path(args.output), canonical_wire_bytes(prepared) + b"\n")
     print(json.dumps({"output": str(args.output), "prompt_tokens": len(ids), "max_new_tokens": budget,
                       "request_sha256": prepared["request_sha256"]}))

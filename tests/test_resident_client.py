@@ -226,3 +226,28 @@ def test_observing_notices_a_session_that_died_mid_answer(tmp_path):
         client.observe({"id": "j", "sequence": 1, "payload": payload})
     finished(run, 1, payload, client.tokenizer.encode("</think>Four.") + [EOS[0]])
     assert client.observe({"id": "j", "sequence": 1, "payload": payload})["status"] == "complete"  # a filed answer outlives its session
+
+
+# ------------------------------------------------------------------------------------------------ preparing a conversation by hand
+def test_a_whole_conversation_becomes_one_prepared_request():
+    tok = ByteTokenizer(1024, EOS)
+    chat = [{"role": "system", "content": "Be brief."}, {"role": "user", "content": "2+2?"}, {"role": "assistant", "content": "4"},
+            {"role": "user", "content": "and 3+3?"}]
+    prepared = rq.from_messages(chat, tokenizer=tok, request_id="follow-up", context_capacity=512, profile=PROFILE)
+    rq.validate(prepared, PROFILE)
+    text = tok.decode(prepared["prompt_ids"])
+    assert text.startswith("[gMASK]<sop><|system|>Reasoning Effort: Max<|system|>Be brief.<|user|>2+2?") and text.endswith("<|user|>and 3+3?<|assistant|><think>")
+    assert prepared["max_new_tokens"] == min(PROFILE.max_new, 512 - len(prepared["prompt_ids"])) and prepared["request_id"] == "follow-up"
+    capped = rq.from_messages(chat, tokenizer=tok, request_id="r", max_new_tokens=5, context_capacity=512, profile=PROFILE, reasoning_effort="low")
+    assert capped["max_new_tokens"] == 5 and "Reasoning Effort: Low" in tok.decode(capped["prompt_ids"])
+    user = {"role": "user", "content": "q"}
+    for bad, sentence in (([], "non-empty list"), ("hi", "non-empty list"), ([user, {"role": "assistant", "content": "a"}], "a user message last"),
+                          ([user, {"role": "system", "content": "s"}, user], "first place only"), ([{"role": "tool", "content": "r"}, user], "exactly a role"),
+                          ([{"role": "user", "content": ["q"]}], "exactly a role"), ([dict(user, name="n")], "exactly a role"), ([{"role": "user"}], "exactly a role"),
+                          ([{"role": "user", "content": "x" * (rq.MESSAGES_CAP + 1)}], "bytes of messages")):
+        with pytest.raises(RequestValidationError, match=sentence):
+            rq.from_messages(bad, tokenizer=tok, request_id="r", context_capacity=512, profile=PROFILE)
+    with pytest.raises(RequestValidationError, match="fills the 512-slot context; nothing is truncated"):
+        rq.from_messages([{"role": "user", "content": "x" * 600}], tokenizer=tok, request_id="r", context_capacity=512, profile=PROFILE)  # never truncated
+    with pytest.raises(RequestValidationError, match="unsupported context capacity"):
+        rq.from_messages([user], tokenizer=tok, request_id="r", context_capacity=4096, profile=PROFILE)
