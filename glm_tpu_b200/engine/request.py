@@ -16,6 +16,7 @@ Parity: reference ``glm_tpu/engine/request.py:17-243`` (schema names, capacities
 from __future__ import annotations
 
 import hashlib
+import json
 import struct
 from dataclasses import dataclass, field
 from typing import Any, Iterable
@@ -193,6 +194,29 @@ def validate_payload(value: Any, profile: RequestProfile = GLM53_PROFILE) -> Non
             raise RequestValidationError("batch identity differs")
     else:
         validate(value, profile)
+
+
+def read(path, profile: RequestProfile = GLM53_PROFILE, *, expected_sha256: str | None = None) -> dict:
+    """A prepared request (or batch) from a file: a bounded regular file reached without links, the digest of its bytes when the
+    caller pins one, then the full validation of its content against ``profile``.
+
+    Parity: reference ``glm_tpu/engine/request.py:137-143``."""
+    from pathlib import Path
+
+    from glm_tpu_b200.utils.io_utils import read_bounded
+
+    try:
+        raw = read_bounded(Path(path), PAYLOAD_CAP)
+    except (OSError, ValueError) as exc:
+        raise RequestValidationError(f"the request file cannot be read: {exc}") from exc
+    if expected_sha256 is not None and hashlib.sha256(raw).hexdigest() != expected_sha256:
+        raise RequestValidationError("the request file is not the pinned one (digest differs)")
+    try:
+        value = json.loads(raw)
+    except ValueError as exc:
+        raise RequestValidationError("the request file is not JSON") from exc
+    validate_payload(value, profile)
+    return value
 
 
 def requests_of(value: dict, profile: RequestProfile = GLM53_PROFILE) -> list[dict]:

@@ -33,6 +33,11 @@ def main(args) -> int:
         prepared = rq.from_messages(messages, tokenizer=tokenizer, request_id=args.request_id, max_new_tokens=args.max_new_tokens,
                                     context_capacity=capacity, profile=profile, reasoning_effort=args.reasoning_effort)
     ids, budget = prepared["prompt_ids"], prepared["max_new_tokens"]
+    checkout = Path(__file__).resolve().parents[3]
+    if Path(args.output).resolve().is_relative_to(checkout):
+        from glm_tpu_b200.exceptions import ConfigValidationError
+
+        raise ConfigValidationError("private requests must be written outside the source checkout")
     create_private_exclusive(Path(args.output), canonical_wire_bytes(prepared) + b"\n")
     print(json.dumps({"output": str(args.output), "prompt_tokens": len(ids), "max_new_tokens": budget,
                       "request_sha256": prepared["request_sha256"]}))

@@ -251,3 +251,49 @@ def test_a_whole_conversation_becomes_one_prepared_request():
         rq.from_messages([{"role": "user", "content": "x" * 600}], tokenizer=tok, request_id="r", context_capacity=512, profile=PROFILE)  # never truncated
     with pytest.raises(RequestValidationError, match="unsupported context capacity"):
         rq.from_messages([user], tokenizer=tok, request_id="r", context_capacity=4096, profile=PROFILE)
+
+
+def test_reading_a_prepared_request_from_a_file(tmp_path):
+    import hashlib as hl
+
+    tok = ByteTokenizer(1024, EOS)
+    prepared = rq.from_messages([{"role": "user", "content": "q"}], tokenizer=tok, request_id="r", context_capacity=512, profile=PROFILE)
+    path = tmp_path / "request.json"
+    path.write_text(json.dumps(prepared))
+    digest = hl.sha256(path.read_bytes()).hexdigest()
+    assert rq.read(path, PROFILE) == prepared and rq.read(path, PROFILE, expected_sha256=digest) == prepared
+    batch = rq.batch([prepared], profile=PROFILE)
+    (tmp_path / "batch.json").write_text(json.dumps(batch))
+    assert rq.read(tmp_path / "batch.json", PROFILE) == batch
+    for make, sentence in ((lambda: rq.read(path, PROFILE, expected_sha256="0" * 64), "not the pinned one"),
+                           (lambda: rq.read(tmp_path / "absent.json", PROFILE), "cannot be read"),
+                           (lambda: rq.read(tmp_path, PROFILE), "cannot be read")):
+        with pytest.raises(RequestValidationError, match=sentence):
+            make()
+    (tmp_path / "link.json").symlink_to(path)
+    with pytest.raises(RequestValidationError, match="cannot be read.*symlink"):
+        rq.read(tmp_path / "link.json", PROFILE)
+    path.write_text("{not json")
+    with pytest.raises(RequestValidationError, match="not JSON"):
+        rq.read(path, PROFILE)
+    path.write_text(json.dumps(dict(prepared, max_new_tokens=prepared["max_new_tokens"] - 1)))
+    with pytest.raises(RequestValidationError, match="identity or fixed profile differs"):
+        rq.read(path, PROFILE)
+
+
+def test_prepare_request_refuses_to_write_into_the_checkout(tmp_path, capsys):
+    from pathlib import Path
+
+    from glm_tpu_b200.entrypoints.cli import main as cli
+
+    messages = tmp_path / "m.json"
+    messages.write_text(json.dumps([{"role": "user", "content": "hi"}]))
+    inside = Path(cli.__file__).resolve().parents[3] / "tests" / "would-be-private.json"
+    code = cli.main(["prepare-request", "--messages", str(messages), "--output", str(inside), "--model", "random:tiny", "--capacity", "256"])
+    assert code == 2 and "outside the source checkout" in capsys.readouterr().err and not inside.exists()
+    code = cli.main(["prepare-request", "--messages", str(messages), "--output", str(tmp_path / "p.json"), "--model", "random:tiny", "--capacity", "256"])
+    assert code == 0 and (tmp_path / "p.json").stat().st_mode & 0o077 == 0
+    bad = tmp_path / "bad.json"
+    bad.write_text(json.dumps([{"role": "assistant", "content": "I speak first"}]))
+    code = cli.main(["prepare-request", "--messages", str(bad), "--output", str(tmp_path / "q.json"), "--model", "random:tiny", "--capacity", "256"])
+    assert code == 2 and "a user message last" in capsys.readouterr().err and not (tmp_path / "q.json").exists()
