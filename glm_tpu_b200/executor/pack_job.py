@@ -30,7 +30,7 @@ def planned_bytes(geometry, world: int, expert_split: str) -> dict:
 
     sizes = {}
     for name, rank in [(fmt.SHARED_FILE, None)] + [(fmt.expert_file(r, world), r) for r in range(world)]:
-        meta = writer._metadata(geometry, world, "shared" if rank is None else "experts", rank, expert_split)  # the header the packer will write
+        meta = writer.file_metadata(geometry, world, "shared" if rank is None else "experts", rank, expert_split)  # the header the packer will write
         head, _, payload = fmt.layout(placement.packed_tensor_shapes(geometry, world, rank, expert_split), meta)
         sizes[name] = len(head) + payload
     return sizes

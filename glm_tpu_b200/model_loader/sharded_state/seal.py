@@ -36,7 +36,7 @@ def install(target: Path, geometry, manifest: dict) -> dict:
 SEAL_KEYS = ("schema", "manifest_sha256", "geometry_sha256", "world", "total_bytes", "seal_sha256")
 
 
-def _read_object(path: Path, what: str) -> dict:
+def read_json_object(path: Path, what: str) -> dict:
     """A JSON object from ``path``; anything else (absent, unreadable, not JSON, not an object) is a validation error."""
     try:
         value = json.loads(path.read_text())
@@ -56,13 +56,13 @@ def read_seal(target: Path) -> tuple[dict, dict]:
     target = Path(target)
     if not (target / fmt.SEAL_FILE).exists():
         raise CheckpointValidationError("no SUCCESS seal: the checkpoint was never completed")
-    seal = _read_object(target / fmt.SEAL_FILE, "the SUCCESS seal")
+    seal = read_json_object(target / fmt.SEAL_FILE, "the SUCCESS seal")
     if sorted(seal) != sorted(SEAL_KEYS) or seal["schema"] != "glm_b200_seal_v1":
         raise CheckpointValidationError("the SUCCESS seal is not a glm_b200_seal_v1 record")
     body = {k: v for k, v in seal.items() if k != "seal_sha256"}
     if seal["seal_sha256"] != hashlib.sha256(canonical_hash_bytes(body)).hexdigest():
         raise CheckpointValidationError("the SUCCESS seal does not match its own digest")
-    manifest = _read_object(target / fmt.MANIFEST_FILE, "the manifest")
+    manifest = read_json_object(target / fmt.MANIFEST_FILE, "the manifest")
     if hashlib.sha256(canonical_hash_bytes(manifest)).hexdigest() != seal["manifest_sha256"]:
         raise CheckpointValidationError("the manifest on disk is not the one the seal closes")
     for key in ("geometry_sha256", "world", "total_bytes"):

@@ -23,7 +23,7 @@ from glm_tpu_b200.model_loader.sharded_state import seal as seal_mod
 
 
 def read_geometry(target: Path) -> ModelGeometry:
-    raw = seal_mod._read_object(Path(target) / fmt.GEOMETRY_FILE, "the geometry file")
+    raw = seal_mod.read_json_object(Path(target) / fmt.GEOMETRY_FILE, "the geometry file")
     try:
         for key in ("indexer_types", "mlp_layer_types", "fp8_block_shape", "eos_ids"):
             raw[key] = tuple(raw[key])

@@ -24,7 +24,7 @@ from glm_tpu_b200.model_loader import placement, source_inventory
 from glm_tpu_b200.model_loader.sharded_state import format as fmt
 
 
-def _metadata(geometry, world: int, kind: str, rank, split: str) -> dict:
+def file_metadata(geometry, world: int, kind: str, rank, split: str) -> dict:
     return {"format": fmt.FORMAT_VERSION, "geometry_sha256": geometry.geometry_hash, "world": world, "kind": kind,
             "rank": "" if rank is None else rank, "expert_split": split}
 
@@ -47,7 +47,7 @@ def pack_files(inv: source_inventory.SourceInventory, target: Path, geometry, wo
         if path.exists():
             raise CheckpointValidationError(f"{name} already exists: packing never overwrites")
         specs = placement.packed_tensor_shapes(geometry, world, rank, split)
-        out = fmt.FileWriter(path, specs, _metadata(geometry, world, "shared" if rank is None else "experts", rank, split))
+        out = fmt.FileWriter(path, specs, file_metadata(geometry, world, "shared" if rank is None else "experts", rank, split))
         try:
             if rank is None:
                 for p in plan:
