@@ -28,7 +28,14 @@ def capture_topology(output: Path, nvml=None) -> dict:
 
 
 def bind_topology(capture: Path, gpus: int, output: Path | None = None, nvml=None, check_live: bool = True) -> dict:
-    raw = json.loads(Path(capture).read_text())
+    try:
+        raw = json.loads(Path(capture).read_text())
+    except FileNotFoundError:
+        raise ConfigValidationError(f"the topology capture {capture} does not exist") from None
+    except (OSError, UnicodeDecodeError, ValueError) as exc:
+        raise ConfigValidationError(f"the topology capture cannot be read as JSON: {exc}") from None
+    if not isinstance(raw, dict):
+        raise ConfigValidationError("not a topology capture")
     claimed = raw.pop("topology_sha256", None)
     captured = topo.Topology.from_dict(raw)
     if claimed != captured.topology_hash:

@@ -60,10 +60,17 @@ class Topology:
 
     @classmethod
     def from_dict(cls, raw: dict) -> "Topology":
-        if raw.get("schema") != CAPTURE_SCHEMA:
+        if not isinstance(raw, dict) or raw.get("schema") != CAPTURE_SCHEMA:
             raise ConfigValidationError("not a topology capture")
-        devices = tuple(GpuDevice(**dict(d, compute_capability=tuple(d["compute_capability"]))) for d in raw["devices"])
-        return cls(devices, tuple(tuple(bool(x) for x in row) for row in raw["peer_nvlink"]), raw["driver"])
+        try:
+            devices = tuple(GpuDevice(**dict(d, compute_capability=tuple(d["compute_capability"]))) for d in raw["devices"])
+            peers = tuple(tuple(bool(x) for x in row) for row in raw["peer_nvlink"])
+            driver = raw["driver"]
+        except (KeyError, TypeError) as exc:
+            raise ConfigValidationError(f"the topology capture is malformed: {exc}") from None
+        if len(peers) != len(devices) or any(len(row) != len(devices) for row in peers) or [d.index for d in devices] != list(range(len(devices))):
+            raise ConfigValidationError("the topology capture is malformed: the peer table does not match the device list")
+        return cls(devices, peers, driver)
 
 
 def _text(value) -> str:
@@ -138,15 +145,37 @@ def derive_topology_binding(topology: Topology, gpus: int) -> dict:
     return dict(body, binding_sha256=hashlib.sha256(canonical_hash_bytes(body)).hexdigest())
 
 
+BINDING_KEYS = ("schema", "gpus", "driver", "topology_sha256", "ranks", "binding_sha256")
+RANK_KEYS = ("rank", "uuid", "pci_bus_id", "memory_mib")
+
+
 def load_topology_binding(path: Path, pin: str = "") -> dict:
-    binding = json.loads(Path(path).read_text())
+    """The binding in ``path`` after checking that it is one: readable JSON with exactly the fields of a binding, hashing to its
+    own digest (and to ``pin`` when one is given), for a supported GPU count, with one well-formed entry per rank and no GPU twice."""
+    try:
+        binding = json.loads(Path(path).read_text())
+    except FileNotFoundError:
+        raise ConfigValidationError(f"the topology binding {path} does not exist") from None
+    except (OSError, UnicodeDecodeError, ValueError) as exc:
+        raise ConfigValidationError(f"the topology binding cannot be read as JSON: {exc}") from None
+    if not isinstance(binding, dict) or sorted(binding) != sorted(BINDING_KEYS) or binding["schema"] != BINDING_SCHEMA:
+        raise ConfigValidationError("not a topology binding")
     body = {k: v for k, v in binding.items() if k != "binding_sha256"}
-    if binding.get("schema") != BINDING_SCHEMA or binding.get("binding_sha256") != hashlib.sha256(canonical_hash_bytes(body)).hexdigest():
+    if binding["binding_sha256"] != hashlib.sha256(canonical_hash_bytes(body)).hexdigest():
         raise ConfigValidationError("the topology binding does not match its own digest")
     if pin and binding["binding_sha256"] != pin:
         raise ConfigValidationError("the topology binding is not the pinned one")
-    if [r["rank"] for r in binding["ranks"]] != list(range(binding["gpus"])):
+    ranks = binding["ranks"]
+    if binding["gpus"] not in SUPPORTED_GPUS or type(ranks) is not list or len(ranks) != binding["gpus"]:
+        raise ConfigValidationError("the binding does not name one GPU per rank of a supported box")
+    for entry in ranks:
+        if (type(entry) is not dict or sorted(entry) != sorted(RANK_KEYS) or type(entry["uuid"]) is not str or not entry["uuid"]
+                or type(entry["pci_bus_id"]) is not str or type(entry["memory_mib"]) is not int):
+            raise ConfigValidationError("a rank entry of the binding is malformed")
+    if [r["rank"] for r in ranks] != list(range(binding["gpus"])):
         raise ConfigValidationError("the binding's ranks are not 0..gpus-1")
+    if len({r["uuid"] for r in ranks}) != len(ranks) or len({r["pci_bus_id"] for r in ranks}) != len(ranks):
+        raise ConfigValidationError("the binding names one GPU for two ranks")
     return binding
 
 
