@@ -33,7 +33,17 @@ def main(args) -> int:
             g = ModelGeometry.from_hf_config(json.loads(config.read_text()))
             report["geometry_hash"] = g.geometry_hash
             report["matches_pinned_glm53"] = g.geometry_hash == assets.load_pinned_geometry().geometry_hash
+    elif args.action == "mark-source" and getattr(args, "upstream_marker", None) is not None:
+        result = source_marker.check_against_upstream(args.source, args.upstream_marker, output=getattr(args, "output", None),
+                                                      hash_shards=getattr(args, "hash_shards", False))
+        marker = result.pop("marker")
+        report = {"ok": True, "source": str(args.source), "inventory_sha256": marker["inventory_sha256"], "tensor_count": marker["tensor_count"],
+                  "total_bytes": marker["total_bytes"], **result}
     elif args.action == "mark-source":
+        if getattr(args, "output", None) is not None:
+            from glm_tpu_b200.exceptions import ConfigValidationError
+
+            raise ConfigValidationError("--output goes with --upstream-marker; a source is marked in place")
         marker = source_marker.mark_source(args.source, hash_shards=getattr(args, "hash_shards", False))
         report = {"ok": True, "source": str(args.source), "inventory_sha256": marker["inventory_sha256"],
                   "tensor_count": marker["tensor_count"], "total_bytes": marker["total_bytes"],

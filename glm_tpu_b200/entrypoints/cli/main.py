@@ -138,6 +138,8 @@ def build_parser() -> argparse.ArgumentParser:
     mark = cks.add_parser("mark-source", help="write SOURCE_COMPLETE.json after checking the source against its index")
     mark.add_argument("source", type=Path)
     mark.add_argument("--hash-shards", action="store_true", help="record a SHA-256 of every shard (reads the whole source)")
+    mark.add_argument("--upstream-marker", type=Path, help="compare this copy with the SOURCE_COMPLETE.json of another copy instead of marking it")
+    mark.add_argument("--output", type=Path, help="with --upstream-marker: where the record computed here is written (the source is not written to)")
     pack = cks.add_parser("pack", help="pack a source checkpoint into per-GPU runtime shards")
     pack.add_argument("source", type=Path)
     pack.add_argument("target", type=Path)

@@ -24,7 +24,8 @@ SMALL_FILES = ("config.json", "generation_config.json", "tokenizer.json", "token
                source_inventory.INDEX_FILE)
 
 
-def mark_source(root: Path, *, hash_shards: bool = False) -> dict:
+def compute_marker(root: Path, *, hash_shards: bool = False) -> dict:
+    """The marker record of ``root`` as it is now; nothing is written."""
     root = Path(root)
     inv = source_inventory.read_source_inventory(root)
     expected = json.loads((root / CHECKSUMS_FILE).read_text()) if (root / CHECKSUMS_FILE).exists() else {}
@@ -40,10 +41,59 @@ def mark_source(root: Path, *, hash_shards: bool = False) -> dict:
                 raise CheckpointValidationError(f"{shard}: content differs from the expected digest")
         files[shard] = record
     small = {name: file_sha256(root / name) for name in SMALL_FILES if (root / name).exists()}
-    marker = {"schema": "glm_b200_source_marker_v1", "inventory_sha256": inv.sha256, "tensor_count": len(inv.tensors),
-              "total_bytes": sum(inv.shards.values()), "shards": files, "small_files": small}
-    create_private_exclusive(root / MARKER_FILE, canonical_wire_bytes(marker) + b"\n")
+    return {"schema": "glm_b200_source_marker_v1", "inventory_sha256": inv.sha256, "tensor_count": len(inv.tensors),
+            "total_bytes": sum(inv.shards.values()), "shards": files, "small_files": small}
+
+
+def mark_source(root: Path, *, hash_shards: bool = False) -> dict:
+    marker = compute_marker(root, hash_shards=hash_shards)
+    create_private_exclusive(Path(root) / MARKER_FILE, canonical_wire_bytes(marker) + b"\n")
     return marker
+
+
+def differences(mine: dict, upstream: dict) -> list[str]:
+    """In which respects this copy of a source differs from the copy another marker describes: the tensor inventory, the shard
+    list and sizes, shard digests where both markers carry one, and the small files.  An empty list: the same source."""
+    if not isinstance(upstream, dict) or upstream.get("schema") != "glm_b200_source_marker_v1":
+        return ["the upstream file is not a glm_b200_source_marker_v1 record"]
+    out = []
+    for key in ("inventory_sha256", "tensor_count", "total_bytes"):
+        if mine.get(key) != upstream.get(key):
+            out.append(f"{key}: {mine.get(key)} here, {upstream.get(key)} upstream")
+    theirs = upstream.get("shards") if isinstance(upstream.get("shards"), dict) else {}
+    for name in sorted(set(mine["shards"]) | set(theirs)):
+        a, b = mine["shards"].get(name), theirs.get(name)
+        if a is None or b is None:
+            out.append(f"{name}: only {'upstream' if a is None else 'here'}")
+        elif a.get("size") != b.get("size"):
+            out.append(f"{name}: {a.get('size')} bytes here, {b.get('size')} upstream")
+        elif a.get("sha256") and b.get("sha256") and a["sha256"] != b["sha256"]:
+            out.append(f"{name}: content differs")
+    small = upstream.get("small_files") if isinstance(upstream.get("small_files"), dict) else {}
+    for name in sorted(set(mine["small_files"]) | set(small)):
+        if mine["small_files"].get(name) != small.get(name):
+            out.append(f"{name}: {'differs' if name in mine['small_files'] and name in small else 'present on one side only'}")
+    return out
+
+
+def check_against_upstream(root: Path, upstream_marker: Path, *, output: Path | None = None, hash_shards: bool = False) -> dict:
+    """Compare the source in ``root`` with the one ``upstream_marker`` (a ``SOURCE_COMPLETE.json`` made elsewhere) describes;
+    refuses on any difference.  The record computed here goes to ``output`` (create-once) when one is given; the source
+    directory itself is not written to."""
+    try:
+        upstream = json.loads(Path(upstream_marker).read_text())
+    except (OSError, UnicodeDecodeError, ValueError) as exc:
+        raise CheckpointValidationError(f"the upstream marker cannot be read as JSON: {exc}") from None
+    wants_digests = isinstance(upstream, dict) and isinstance(upstream.get("shards"), dict) and any(
+        isinstance(r, dict) and r.get("sha256") for r in upstream["shards"].values())
+    mine = compute_marker(root, hash_shards=hash_shards or wants_digests)
+    found = differences(mine, upstream)
+    if found:
+        raise CheckpointValidationError(f"this source differs from the upstream marker in {len(found)} respect(s): " + "; ".join(found[:5]))
+    if output is not None:
+        create_private_exclusive(Path(output), canonical_wire_bytes(mine) + b"\n")
+    return {"matches_upstream": True, "upstream_marker_sha256": file_sha256(Path(upstream_marker)), "shards_compared_by_content": bool(wants_digests),
+            "marker": mine}
 
 
 def marker_sha256(root: Path) -> str:

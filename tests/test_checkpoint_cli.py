@@ -134,3 +134,40 @@ def test_a_fresh_process_reports_the_same_way(source, tmp_path):
     assert refusal(done.stderr)["refused"] == "CheckpointValidationError"
     done = subprocess.run([sys.executable, "-m", "glm_tpu_b200", "checkpoint", "inventory", str(source)], capture_output=True, text=True, env=env, timeout=300)
     assert done.returncode == 0 and json.loads(done.stdout)["ok"] and done.stderr == ""
+
+
+def test_another_copy_of_the_source_is_checked_against_an_earlier_marker(source, tmp_path, capsys):
+    """``mark-source --upstream-marker``: this copy against the marker made from another copy; the copy itself is not written to."""
+    import shutil
+
+    assert run(capsys, "checkpoint", "mark-source", source, "--hash-shards")[0] == 0
+    upstream = tmp_path / "upstream.json"
+    shutil.copy(source / source_marker.MARKER_FILE, upstream)
+    copy = tmp_path / "copy"
+    shutil.copytree(source, copy)
+    (copy / source_marker.MARKER_FILE).unlink()
+    code, out, _ = run(capsys, "checkpoint", "mark-source", copy, "--upstream-marker", upstream, "--output", tmp_path / "scratch.json")
+    report = json.loads(out)
+    assert code == 0 and report["matches_upstream"] and report["shards_compared_by_content"] and report["upstream_marker_sha256"] == fmt.file_sha256(upstream)
+    assert not (copy / source_marker.MARKER_FILE).exists()  # compared, not marked
+    assert json.loads((tmp_path / "scratch.json").read_text()) == json.loads(upstream.read_text())  # the same source gives the same record
+
+    shard = sorted(copy.glob("*.safetensors"))[0]
+    with open(shard, "r+b") as f:
+        f.seek(-1, os.SEEK_END)
+        last = f.read(1)
+        f.seek(-1, os.SEEK_END)
+        f.write(bytes([last[0] ^ 1]))  # one bit of one weight: same size, same headers
+    code, _, err = run(capsys, "checkpoint", "mark-source", copy, "--upstream-marker", upstream)
+    assert code == 2 and f"{shard.name}: content differs" in refusal(err)["message"]
+    (copy / "config.json").write_text((copy / "config.json").read_text() + " ")
+    code, _, err = run(capsys, "checkpoint", "mark-source", copy, "--upstream-marker", upstream)
+    assert code == 2 and "2 respect(s)" in refusal(err)["message"] and "config.json: differs" in refusal(err)["message"]
+
+    upstream.write_text("{oops")
+    assert run(capsys, "checkpoint", "mark-source", source, "--upstream-marker", upstream)[0] == 2
+    upstream.write_text(json.dumps({"schema": "something_else"}))
+    code, _, err = run(capsys, "checkpoint", "mark-source", source, "--upstream-marker", upstream)
+    assert code == 2 and "not a glm_b200_source_marker_v1 record" in refusal(err)["message"]
+    code, _, err = run(capsys, "checkpoint", "mark-source", copy, "--output", tmp_path / "x.json")
+    assert code == 2 and "goes with --upstream-marker" in refusal(err)["message"]
