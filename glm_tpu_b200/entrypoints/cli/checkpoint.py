@@ -59,7 +59,9 @@ def main(args) -> int:
         from glm_tpu_b200.model_loader.sharded_state.verify import verify_runtime_checkpoint
 
         site = SiteConfig.load(getattr(args, "site", None))
-        report = verify_runtime_checkpoint(args.target, pins={"manifest_sha256": site.manifest_sha256})
+        report = verify_runtime_checkpoint(args.target, files=getattr(args, "files", None), pins={"manifest_sha256": site.manifest_sha256},
+                                           rehash=not getattr(args, "headers_only", False))
+        report["rehashed"] = not getattr(args, "headers_only", False)
         report.pop("manifest_files", None)  # the per-tensor records stay in manifest.json
     print(json.dumps(report, indent=2, sort_keys=True))
     return 0

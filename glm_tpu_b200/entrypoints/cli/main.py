@@ -152,6 +152,8 @@ def build_parser() -> argparse.ArgumentParser:
     ver = cks.add_parser("verify", help="re-hash a packed checkpoint against its manifest and seal")
     ver.add_argument("target", type=Path)
     ver.add_argument("--site", type=Path, help="site file (default: the configured one); its [checkpoint] manifest_sha256 pins the checkpoint")
+    ver.add_argument("--files", nargs="+", metavar="NAME", help="check only these files of the checkpoint (default: all), e.g. the one a GPU loads")
+    ver.add_argument("--headers-only", action="store_true", help="check seal, manifest, sizes and headers but do not re-hash the payloads")
     ck.set_defaults(fn=_checkpoint)
 
     topo = sub.add_parser("topology", help="capture and bind the GPU topology")

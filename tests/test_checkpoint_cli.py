@@ -171,3 +171,25 @@ def test_another_copy_of_the_source_is_checked_against_an_earlier_marker(source,
     assert code == 2 and "not a glm_b200_source_marker_v1 record" in refusal(err)["message"]
     code, _, err = run(capsys, "checkpoint", "mark-source", copy, "--output", tmp_path / "x.json")
     assert code == 2 and "goes with --upstream-marker" in refusal(err)["message"]
+
+
+def test_verify_can_be_limited_to_some_files_or_to_the_headers(source, tmp_path, capsys):
+    run(capsys, "checkpoint", "mark-source", source)
+    run(capsys, "checkpoint", "pack", source, tmp_path / "packed", "--gpus", "2")
+    mine = "experts.rank1of2.safetensors"
+    code, out, _ = run(capsys, "checkpoint", "verify", tmp_path / "packed", "--files", fmt.SHARED_FILE, mine)
+    assert code == 0 and sorted(json.loads(out)["files"]) == sorted([fmt.SHARED_FILE, mine]) and json.loads(out)["rehashed"] is True
+    code, _, err = run(capsys, "checkpoint", "verify", tmp_path / "packed", "--files", "experts.rank5of2.safetensors")
+    assert code == 2 and "is not part of this checkpoint" in refusal(err)["message"]
+    other = tmp_path / "packed" / "experts.rank0of2.safetensors"
+    os.chmod(other, 0o600)
+    with open(other, "r+b") as f:
+        f.seek(-1, os.SEEK_END)
+        last = f.read(1)
+        f.seek(-1, os.SEEK_END)
+        f.write(bytes([last[0] ^ 1]))
+    assert run(capsys, "checkpoint", "verify", tmp_path / "packed", "--files", mine)[0] == 0  # only what was asked for is read
+    code, out, _ = run(capsys, "checkpoint", "verify", tmp_path / "packed", "--headers-only")
+    assert code == 0 and json.loads(out)["rehashed"] is False  # sizes and headers are intact; the payload was not read
+    code, _, err = run(capsys, "checkpoint", "verify", tmp_path / "packed")
+    assert code == 2 and "experts.rank0of2.safetensors: content digest differs" in refusal(err)["message"]
