@@ -76,3 +76,37 @@ def test_compare_run(tmp_path):
     matched, diffs = compare_run.compare(a, c)
     assert matched == 1 and diffs[0]["first_difference"] == 1
     assert compare_run.main([str(a), str(b)]) == 0 and compare_run.main([str(a), str(c)]) == 1 and compare_run.main([str(a), str(tmp_path)]) in (0, 1, 2)
+
+
+def test_the_gate_command_line(tmp_path, monkeypatch, capsys):
+    """``python -m tools.equivalence.driver check|update [gate ...]``: exit status 0 and one line when the goldens match, 1 and the
+    differing keys (golden against current) when they do not; ``update`` rewrites only the gates it is given."""
+    import shutil
+
+    data = tmp_path / "data"
+    shutil.copytree(driver.DATA, data)
+    monkeypatch.setattr(driver, "DATA", data)
+    assert driver.main(["check", "g9_wire_formats", "g4_checkpoint_identity"]) == 0
+    assert capsys.readouterr().out.strip() == "all gates match"
+
+    golden = json.loads((data / "g9_wire_formats.json").read_text())
+    (data / "g9_wire_formats.json").write_text(json.dumps(dict(golden, sse_chunks="0" * 64, retired_key="x")))
+    before_g4 = (data / "g4_checkpoint_identity.json").read_bytes()
+    assert driver.main(["check", "g9_wire_formats", "g4_checkpoint_identity"]) == 1
+    report = json.loads(capsys.readouterr().out)
+    assert set(report) == {"g9_wire_formats"} and set(report["g9_wire_formats"]) == {"sse_chunks", "retired_key"}
+    assert report["g9_wire_formats"]["sse_chunks"] == {"golden": "0" * 64, "current": golden["sse_chunks"]}
+    assert report["g9_wire_formats"]["retired_key"] == {"golden": "x", "current": None}
+
+    assert driver.main(["update", "g9_wire_formats"]) == 0
+    assert json.loads((data / "g9_wire_formats.json").read_text()) == golden and (data / "g4_checkpoint_identity.json").read_bytes() == before_g4
+    assert driver.main(["check", "g9_wire_formats"]) == 0
+    assert sorted(p.name for p in data.iterdir()) == sorted(p.name for p in driver.DATA.iterdir())  # nothing else was written
+
+
+def test_goldens_are_canonical_files():
+    """Sorted keys, one-space indent, newline at the end: a regenerated golden that did not change gives no diff."""
+    for path in sorted(driver.DATA.glob("*.json")):
+        text = path.read_text()
+        assert text == json.dumps(json.loads(text), indent=1, sort_keys=True) + "\n", path.name
+    assert {p.stem for p in driver.DATA.glob("*.json")} == set(driver.gates())
