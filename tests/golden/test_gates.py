@@ -13,7 +13,7 @@ if str(ROOT) not in sys.path:
 from tools.equivalence import compare_run, driver, imports  # noqa: E402
 
 
-@pytest.mark.parametrize("gate", ["g3_oracle_digests", "g4_checkpoint_identity", "g9_wire_formats"])
+@pytest.mark.parametrize("gate", ["g2_production_defaults", "g3_oracle_digests", "g4_checkpoint_identity", "g9_wire_formats"])
 def test_gate_matches_golden(gate):
     assert driver.check({gate}) == {}
 

@@ -7,7 +7,8 @@ checkpoint bytes, import closures) plus a mutation self-test of the gates themse
     python -m tools.equivalence.compare_run RUN_A RUN_B # token-stream identity of two real runs
 
 Gate names follow the reference's (``tools/equivalence/README.md:69-132``): G1 the launch programs (``programs.py``: the ordered
-launch list of a decode step and a prefill chunk per configuration; recorded and checked on a GPU), G3 execution digests, G4 checkpoint identity,
+launch list of a decode step and a prefill chunk per configuration; recorded and checked on a GPU), G2 production defaults (``defaults.py``:
+every limit, cap, default and choice that is relied on without being named), G3 execution digests, G4 checkpoint identity,
 G6 import closures (may only shrink), G7 the set of functions a fixed CPU scenario executes (``executed.py``), G9 wire formats, G14
 mutation self-test.  There is no compiler here, so the reference's G1/G2 (StableHLO fingerprints of compiled programs) become one gate
 over the static launch list.

@@ -10,9 +10,9 @@ DATA = Path(__file__).resolve().parents[2] / "tests" / "golden" / "data"
 
 
 def gates() -> dict:
-    from tools.equivalence import digests, executed, imports, programs, wire
+    from tools.equivalence import defaults, digests, executed, imports, programs, wire
 
-    return {"g1_launch_programs": programs.collect, "g3_oracle_digests": digests.oracle_digests, "g4_checkpoint_identity": digests.checkpoint_identity, "g6_import_closures": imports.collect,
+    return {"g1_launch_programs": programs.collect, "g2_production_defaults": defaults.collect, "g3_oracle_digests": digests.oracle_digests, "g4_checkpoint_identity": digests.checkpoint_identity, "g6_import_closures": imports.collect,
             "g7_executed_functions": executed.collect, "g9_wire_formats": wire.collect}
 
 

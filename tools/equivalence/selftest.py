@@ -282,6 +282,33 @@ def wire_mutants():
         plain_visible([p]) for p in c))
 
 
+def default_mutants():
+    """Changed defaults that no functional test would notice: each must change the production-defaults gate."""
+    import dataclasses
+
+    from glm_tpu_b200 import envs
+    from glm_tpu_b200.config import site
+    from glm_tpu_b200.engine import request as rq
+    from glm_tpu_b200.entrypoints.openai import protocol as api
+    from glm_tpu_b200.entrypoints.serve import http_handler, job_queue
+
+    yield "eleven jobs may wait", _patched(job_queue, "PENDING", 11)
+    yield "answers may be twice as long", _patched(rq, "MAX_NEW", 2 * rq.MAX_NEW)
+    yield "the 128k profile admits its whole window as prompt", _patched(rq, "PROMPT_LIMITS", {**rq.PROMPT_LIMITS, rq.LONG_CAPACITY: rq.LONG_CAPACITY})
+    yield "request bodies of 40 MB", _patched(api, "BODY_CAP", 40 << 20)
+    yield "replies without the no-sniff header", _patched(http_handler, "SECURITY_HEADERS", tuple(h for h in http_handler.SECURITY_HEADERS if h[0] != "X-Content-Type-Options"))
+    yield "a model alias for a medium effort", _patched(api, "ALIASES", dict(api.ALIASES, **{"glm-5.3-medium": "high"}))
+    table = dict(envs.TABLE)
+    table["GLM_B200_COMM"] = table["GLM_B200_COMM"]._replace(default="nccl")
+    yield "the library collectives by default", _patched(envs, "TABLE", table)
+    table = dict(envs.TABLE)
+    table["GLM_B200_API_KEY_FILE"] = table["GLM_B200_API_KEY_FILE"]._replace(secret=False)
+    yield "the key file's name no longer treated as a secret", _patched(envs, "TABLE", table)
+    plain = site.SiteConfig
+    yield "a site without a file launches strictly", _patched(site, "SiteConfig", dataclasses.make_dataclass(
+        "SiteConfig", [("policy", str, dataclasses.field(default="strict"))], bases=(plain,), frozen=True))
+
+
 def run() -> dict:
     """{mutant: caught?}.  Geometry mutants are skipped for digests that do not depend on the geometry."""
     import importlib
@@ -293,6 +320,13 @@ def run() -> dict:
     for name, patch in oracle_mutants():
         with patch:
             results[name] = digests.oracle_digests() != base_oracle
+    from tools.equivalence import defaults
+
+    base_defaults = defaults.collect()
+    for name, patch in default_mutants():
+        with patch:
+            results[name] = defaults.collect() != base_defaults
+    assert defaults.collect() == base_defaults, "a mutant outlived its patch"
     base_wire = wire.collect()
     request_module = importlib.import_module("glm_tpu_b200.engine.request")
     for name, patch in wire_mutants():
