@@ -25,6 +25,13 @@ def main(args) -> int:
                   "shards": len(inv.shards), "total_bytes": sum(inv.shards.values()), "bytes_by_dtype": dict(sorted(by_dtype.items()))}
         from pathlib import Path
 
+        if getattr(args, "output", None) is not None:
+            from glm_tpu_b200.utils.io_utils import create_private_exclusive
+            from glm_tpu_b200.utils.json_utils import canonical_wire_bytes
+
+            record = {"schema": "glm_b200_source_inventory_v1", "inventory_sha256": inv.sha256, **inv.listing()}
+            create_private_exclusive(Path(args.output), canonical_wire_bytes(record) + b"\n")
+            report["output"] = str(args.output)
         config = Path(args.source) / "config.json"
         if config.is_file():  # is this the architecture the package pins (models/glm_moe_dsa/hf_config)?
             from glm_tpu_b200.config.model import ModelGeometry

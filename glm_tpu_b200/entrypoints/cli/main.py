@@ -135,6 +135,7 @@ def build_parser() -> argparse.ArgumentParser:
     cks = ck.add_subparsers(dest="action", required=True)
     inv = cks.add_parser("inventory", help="read the safetensors headers of a source checkpoint")
     inv.add_argument("source", type=Path)
+    inv.add_argument("--output", type=Path, help="also write the inventory (every tensor: dtype, shape, shard, byte range) to this file, create-once")
     mark = cks.add_parser("mark-source", help="write SOURCE_COMPLETE.json after checking the source against its index")
     mark.add_argument("source", type=Path)
     mark.add_argument("--hash-shards", action="store_true", help="record a SHA-256 of every shard (reads the whole source)")

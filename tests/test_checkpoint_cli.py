@@ -193,3 +193,23 @@ def test_verify_can_be_limited_to_some_files_or_to_the_headers(source, tmp_path,
     assert code == 0 and json.loads(out)["rehashed"] is False  # sizes and headers are intact; the payload was not read
     code, _, err = run(capsys, "checkpoint", "verify", tmp_path / "packed")
     assert code == 2 and "experts.rank0of2.safetensors: content digest differs" in refusal(err)["message"]
+
+
+def test_the_inventory_can_be_written_to_a_file(source, tmp_path, capsys):
+    import hashlib
+
+    from glm_tpu_b200.utils.json_utils import canonical_hash_bytes
+
+    code, out, _ = run(capsys, "checkpoint", "inventory", source, "--output", tmp_path / "inventory.json")
+    report = json.loads(out)
+    assert code == 0 and report["output"] == str(tmp_path / "inventory.json")
+    record = json.loads((tmp_path / "inventory.json").read_text())
+    assert record["schema"] == "glm_b200_source_inventory_v1" and record["inventory_sha256"] == report["inventory_sha256"]
+    assert len(record["tensors"]) == report["tensors"] and sum(record["shards"].values()) == report["total_bytes"]
+    # the digest is the digest of the listing itself: anyone can recompute it from the file
+    assert hashlib.sha256(canonical_hash_bytes({"tensors": record["tensors"], "shards": record["shards"]})).hexdigest() == record["inventory_sha256"]
+    name, (dtype, shape, shard, begin, end) = sorted(record["tensors"].items())[0]
+    assert (source / shard).stat().st_size >= end > begin and isinstance(shape, list) and dtype in ("BF16", "F32", "F8_E4M3")
+    assert (tmp_path / "inventory.json").stat().st_mode & 0o077 == 0
+    with pytest.raises(FileExistsError):
+        cli.main(["checkpoint", "inventory", str(source), "--output", str(tmp_path / "inventory.json")])  # create-once
