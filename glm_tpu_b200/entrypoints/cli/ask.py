@@ -17,6 +17,7 @@ from dataclasses import dataclass
 from pathlib import Path
 
 from glm_tpu_b200.engine import request as rq
+from glm_tpu_b200.exceptions import RequestValidationError
 from glm_tpu_b200.utils.io_utils import create_private_exclusive, read_bounded
 from glm_tpu_b200.utils.json_utils import canonical_wire_bytes
 
@@ -41,11 +42,11 @@ class QuestionSet:
         texts = self.questions
         well_formed = isinstance(texts, list) and all(isinstance(t, str) and t.strip() for t in texts)
         if not well_formed or not 1 <= len(texts) <= rq.QUEUE_LIMIT:
-            raise ValueError("provide one to ten nonempty question strings")
+            raise RequestValidationError("provide one to ten nonempty question strings")
         if self.concurrent and (len(texts) > profile.concurrent_limit or self.context_capacity != profile.concurrent_capacity):
-            raise ValueError("concurrent mode accepts up to four questions at the concurrent capacity profile")
+            raise RequestValidationError("concurrent mode accepts up to four questions at the concurrent capacity profile")
         if self.max_new_tokens is not None and (type(self.max_new_tokens) is not int or self.max_new_tokens < 1):
-            raise ValueError("output budget must be a positive integer")
+            raise RequestValidationError("output budget must be a positive integer")
 
     def prepared(self, number: int, tokenizer, profile, directory: Path) -> dict:
         """Stage question ``number`` (0-based) and return its prepared request."""
@@ -56,7 +57,7 @@ class QuestionSet:
         if budget is None:
             budget = rq.default_max_new_tokens(len(prompt), self.context_capacity, profile)
         if budget < 1:
-            raise ValueError("the question leaves no room for an answer at this context capacity")
+            raise RequestValidationError("the question leaves no room for an answer at this context capacity")
         request = rq.from_token_ids(prompt, request_id=f"question-{number + 1:02d}", max_new_tokens=budget,
                                     context_capacity=self.context_capacity, profile=profile)
         _stage(directory, f"prepared-{number:03d}.json", request)
@@ -70,14 +71,20 @@ def prepare_questions(questions, *, tokenizer, profile, output_root: Path, conte
     wanted.check(profile)
     directory = Path(output_root)
     if repo is not None and directory.resolve().is_relative_to(Path(repo).resolve()):
-        raise ValueError("private questions must stay outside the repository")
+        raise RequestValidationError("private questions must stay outside the repository")
     directory.mkdir(mode=0o700, parents=True)
-    requests = [wanted.prepared(number, tokenizer, profile, directory) for number in range(len(questions))]
-    alone = len(requests) == 1 and not wanted.concurrent
-    bundle = requests[0] if alone else rq.batch(requests, concurrent=wanted.concurrent, profile=profile)
-    if len(canonical_wire_bytes(bundle)) + 1 > rq.PAYLOAD_CAP:
-        raise ValueError("combined request payload is too large")
-    _stage(directory, "request.json", bundle)
+    try:
+        requests = [wanted.prepared(number, tokenizer, profile, directory) for number in range(len(questions))]
+        alone = len(requests) == 1 and not wanted.concurrent
+        bundle = requests[0] if alone else rq.batch(requests, concurrent=wanted.concurrent, profile=profile)
+        if len(canonical_wire_bytes(bundle)) + 1 > rq.PAYLOAD_CAP:
+            raise RequestValidationError("combined request payload is too large")
+        _stage(directory, "request.json", bundle)
+    except BaseException:
+        import shutil
+
+        shutil.rmtree(directory, ignore_errors=True)  # a refused question set leaves no half-staged private input behind
+        raise
     return directory / "request.json"
 
 

@@ -213,3 +213,17 @@ def test_the_inventory_can_be_written_to_a_file(source, tmp_path, capsys):
     assert (tmp_path / "inventory.json").stat().st_mode & 0o077 == 0
     with pytest.raises(FileExistsError):
         cli.main(["checkpoint", "inventory", str(source), "--output", str(tmp_path / "inventory.json")])  # create-once
+
+
+def test_ask_refuses_in_one_json_line_too(tmp_path, monkeypatch, capsys):
+    monkeypatch.setenv("GLM_B200_RUN_ROOT", str(tmp_path / "runs"))
+    monkeypatch.setenv("GLM_B200_SITE_CONFIG", str(tmp_path / "no-site.toml"))
+    questions = tmp_path / "q.json"
+    questions.write_text(json.dumps(["one"] * 11))
+    os.chmod(questions, 0o600)
+    code, out, err = run(capsys, "ask", "--questions", questions, "--model", "random:tiny", "--capacity", "128", "--prepare-only")
+    assert code == 2 and out == "" and refusal(err) == {"ok": False, "refused": "RequestValidationError", "message": "provide one to ten nonempty question strings"}
+    code, _, err = run(capsys, "ask", "x" * 400, "--model", "random:tiny", "--capacity", "128", "--prepare-only")
+    assert code == 2 and "no room for an answer" in refusal(err)["message"] or "exceed" in refusal(err)["message"]
+    code, out, _ = run(capsys, "ask", "2+2?", "--model", "random:tiny", "--capacity", "128", "--prepare-only")
+    assert code == 0 and out.startswith("PRIVATE_INPUT ")
