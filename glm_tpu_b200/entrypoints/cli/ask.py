@@ -102,7 +102,8 @@ def main(args) -> int:
     profile = profile_for(geometry, capacity)
     tokenizer = load_tokenizer(path if kind == "checkpoint" else site.paths.model_path, vocab_size=geometry.vocab_size,
                                eos_ids=geometry.eos_ids)
-    root = site.paths.run_root / ("inputs_" + time.strftime("%Y%m%dT%H%M%S") + f"_{os.getpid()}")
+    stem = "inputs_" + time.strftime("%Y%m%dT%H%M%S") + f"_{os.getpid()}"
+    root = next(candidate for candidate in (site.paths.run_root / (stem + (f".{n}" if n else "")) for n in range(1000)) if not candidate.exists())
     request_path = prepare_questions(questions, tokenizer=tokenizer, profile=profile, output_root=root, context_capacity=capacity,
                                      max_new_tokens=args.max_new_tokens, concurrent=args.concurrent, repo=launch.REPO)
     print("PRIVATE_INPUT " + str(request_path), flush=True)

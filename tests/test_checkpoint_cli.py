@@ -227,3 +227,17 @@ def test_ask_refuses_in_one_json_line_too(tmp_path, monkeypatch, capsys):
     assert code == 2 and "no room for an answer" in refusal(err)["message"] or "exceed" in refusal(err)["message"]
     code, out, _ = run(capsys, "ask", "2+2?", "--model", "random:tiny", "--capacity", "128", "--prepare-only")
     assert code == 0 and out.startswith("PRIVATE_INPUT ")
+
+
+def test_two_asks_in_the_same_second_get_their_own_input_directories(tmp_path, monkeypatch, capsys):
+    monkeypatch.setenv("GLM_B200_RUN_ROOT", str(tmp_path / "runs"))
+    monkeypatch.setenv("GLM_B200_SITE_CONFIG", str(tmp_path / "no-site.toml"))
+    import time as time_module
+
+    monkeypatch.setattr(time_module, "strftime", lambda fmt, *a: "20260101T000000")  # the clock stands still
+    staged = []
+    for question in ("one?", "two?", "three?"):
+        code, out, _ = run(capsys, "ask", question, "--model", "random:tiny", "--capacity", "128", "--prepare-only")
+        assert code == 0
+        staged.append(out.split("PRIVATE_INPUT ", 1)[1].strip())
+    assert len(set(staged)) == 3 and all(os.path.exists(p) for p in staged)
