@@ -200,7 +200,7 @@ def test_requests_are_served_in_sequence_until_the_stop_file(run_dir, capsys):
 
     (run_dir / proto.INBOX_DIR / proto.STOP_FILE).unlink()
     fl = ScriptedFleet(run_dir)
-    result = loop(run_dir, fl, seconds=1.0)
+    result = loop(run_dir, fl, seconds=3.0)
     assert result == {"stopped": "deadline", "served": [1, 2]}
     assert [json.loads(x).get("sequence") for x in fl.sent] == [1, 2, None] and fl.sent[-1] == proto.STOP_COMMAND
     lines = [json.loads(x[len(proto.STDOUT_RESIDENT_RESULT):]) for x in capsys.readouterr().out.splitlines() if x.startswith(proto.STDOUT_RESIDENT_RESULT)]
@@ -275,22 +275,30 @@ def test_a_record_that_cannot_be_read_counts_as_missing(run_dir):
 
 
 def test_an_idle_session_has_no_deadline_and_every_request_its_own(run_dir):
-    """``--wall-seconds`` bounds the start-up with the first request, then each later request; waiting for the inbox costs nothing."""
+    """``--wall-seconds`` bounds the start-up with the first request, then each later request; waiting for the inbox costs nothing.
+    (The budgets are generous against a loaded machine: what matters is their order, not their size.)"""
     import threading
+
+    def wait_for(condition, seconds=20.0):
+        end = time.monotonic() + seconds
+        while not condition() and time.monotonic() < end:
+            time.sleep(0.01)
+        return condition()
 
     (run_dir / proto.READY_FILE).write_text(json.dumps({"sequence": 0}))
     fl = ScriptedFleet(run_dir)
     result = {}
     worker = threading.Thread(target=lambda: result.update(controller.resident_controller(
-        fl, run_dir, 2, lambda payload: None, time.monotonic() + 0.2, 0.01, wall_seconds=0.2)))
+        fl, run_dir, 2, lambda payload: None, time.monotonic() + 1.0, 0.01, wall_seconds=0.3)))
     worker.start()
-    time.sleep(0.6)  # three times the budget, idle: still waiting
+    time.sleep(1.6)  # longer than the start-up budget and than a request's budget, idle: still waiting
     assert worker.is_alive() and fl.sent == []
     publish(run_dir, 1, {"request_id": "one"})
-    time.sleep(0.5)
-    assert worker.is_alive() and [json.loads(x).get("sequence") for x in fl.sent] == [1]  # answered within its own budget; idle again
+    assert wait_for(lambda: [json.loads(x).get("sequence") for x in fl.sent] == [1])
+    time.sleep(0.6)  # answered within its own budget; idle again, and again without a deadline
+    assert worker.is_alive()
     (run_dir / proto.INBOX_DIR / proto.STOP_FILE).write_bytes(proto.STOP_COMMAND)
-    worker.join(10)
+    worker.join(20)
     assert result == {"stopped": "stop_file", "served": [1]}
 
     class Stuck(ScriptedFleet):  # takes the request and never finishes it
@@ -298,11 +306,10 @@ def test_an_idle_session_has_no_deadline_and_every_request_its_own(run_dir):
             self.sent.append(line)
 
     (run_dir / proto.INBOX_DIR / proto.STOP_FILE).unlink()
-    publish(run_dir, 2, {"request_id": "two"})
     stuck = Stuck(run_dir)
     (run_dir / proto.READY_FILE).write_text(json.dumps({"sequence": 0}))
     started = time.monotonic()
-    outcome = controller.resident_controller(stuck, run_dir, 2, lambda payload: None, time.monotonic() + 5.0, 0.01, wall_seconds=0.3)
-    # sequence 1 is handed over at once, never answered: its own budget runs out, not the start-up one
-    assert outcome == {"stopped": "deadline", "served": []} and 0.25 < time.monotonic() - started < 3.0
-    assert stuck.sent[-1] == proto.STOP_COMMAND
+    outcome = controller.resident_controller(stuck, run_dir, 2, lambda payload: None, time.monotonic() + 60.0, 0.01, wall_seconds=0.3)
+    # sequence 1 is handed over at once and never answered: its own budget runs out, long before the start-up one would
+    assert outcome == {"stopped": "deadline", "served": []} and 0.25 < time.monotonic() - started < 30.0
+    assert json.loads(stuck.sent[0])["sequence"] == 1 and stuck.sent[-1] == proto.STOP_COMMAND
